@@ -1,0 +1,229 @@
+// The extern "C" surface of libmarian_i8.so: argument checks, bookkeeping and the sequencing of
+// the kernels.  No call here allocates device memory or synchronises with the host, except
+// mi8_poll_status which exists to do exactly that.
+#include <cstring>
+
+#include "mi8_internal.h"
+#include "mi8_ptx.cuh"
+
+namespace mi8 {
+
+// One status word per device (each device that loads the module gets its own instance).
+__device__ int g_status_word = 0;
+
+namespace {
+thread_local cudaError_t t_last_error = cudaSuccess;
+thread_local unsigned long long t_launches = 0;
+int* g_status_ptr[64] = {};
+int g_sm_count[64] = {};
+}  // namespace
+
+void set_last_cuda_error(cudaError_t e) { t_last_error = e; }
+void count_launch() { ++t_launches; }
+
+int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  if(e != cudaSuccess) {
+    t_last_error = e;
+    return MI8_ERR_LAUNCH;
+  }
+  return MI8_OK;
+}
+
+int* device_status_ptr() {
+  int dev = 0;
+  if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    return nullptr;
+  if(g_status_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_status_word);
+    if(e != cudaSuccess) {
+      t_last_error = e;
+      return nullptr;
+    }
+    g_status_ptr[dev] = static_cast<int*>(p);
+  }
+  return g_status_ptr[dev];
+}
+
+int sm_count() {
+  int dev = 0;
+  if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    return 148;  // B200; also what plan queries answer on a host without a GPU
+  if(g_sm_count[dev] == 0) {
+    int n = 0;
+    if(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 148;
+    }
+    g_sm_count[dev] = n;
+  }
+  return g_sm_count[dev];
+}
+
+}  // namespace mi8
+
+using namespace mi8;
+
+extern "C" {
+
+int mi8_version(void) { return 100; }
+
+const char* mi8_strerror(int status) {
+  switch(status) {
+    case MI8_OK: return "ok";
+    case MI8_ERR_BAD_ARG: return "bad argument (null pointer, negative size or unknown enum value)";
+    case MI8_ERR_MISALIGNED: return "pointer not 16-byte aligned or K not a multiple of 16";
+    case MI8_ERR_UNSUPPORTED: return "shape not supported";
+    case MI8_ERR_WORKSPACE: return "workspace missing or too small";
+    case MI8_ERR_LAUNCH: return "CUDA error at kernel launch";
+    case MI8_ERR_DEVICE: return "a kernel raised the device status word";
+    case MI8_ERR_DRIVER: return "tensor-map encoding unavailable (driver entry point)";
+    default: return "unknown status";
+  }
+}
+
+int mi8_last_cuda_error(void) { return static_cast<int>(t_last_error); }
+const char* mi8_last_cuda_error_string(void) { return cudaGetErrorString(t_last_error); }
+
+unsigned long long mi8_launch_count(void) { return t_launches; }
+void mi8_launch_count_reset(void) { t_launches = 0; }
+
+size_t mi8_workspace_bytes(int M, int N, int K) {
+  // Upper bound over every plan: at most one work item per SM is split, each parks 128 x 256 int32.
+  const size_t upper = kWsHeaderBytes + static_cast<size_t>(160) * 128 * 256 * sizeof(int32_t);
+  if(M <= 0 || N <= 0 || K <= 0)
+    return upper;
+  GemmPlan plan;
+  if(make_gemm_plan(M, N, K, 0, 0, &plan) != MI8_OK)
+    return upper;
+  return kWsHeaderBytes + plan.partial_bytes;
+}
+
+int mi8_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  if(workspace == nullptr || workspace_bytes < kWsHeaderBytes)
+    return MI8_ERR_WORKSPACE;
+  cudaError_t e = cudaMemsetAsync(workspace, 0, kWsZeroedBytes, as_stream(stream));
+  if(e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return MI8_ERR_LAUNCH;
+  }
+  return MI8_OK;
+}
+
+int mi8_poll_status(int* status) {
+  int* p = device_status_ptr();
+  if(p == nullptr)
+    return MI8_ERR_LAUNCH;
+  int v = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if(e == cudaSuccess)
+    e = cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
+  if(e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return MI8_ERR_LAUNCH;
+  }
+  if(status != nullptr)
+    *status = v;
+  return v == 0 ? MI8_OK : MI8_ERR_DEVICE;
+}
+
+int mi8_clear_status(void* stream) {
+  int* p = device_status_ptr();
+  if(p == nullptr)
+    return MI8_ERR_LAUNCH;
+  cudaError_t e = cudaMemsetAsync(p, 0, sizeof(int), as_stream(stream));
+  if(e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return MI8_ERR_LAUNCH;
+  }
+  return MI8_OK;
+}
+
+int mi8_max_absolute_f32(const float* x, size_t n, float* d_absmax, float* d_quant_mult, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  return launch_max_absolute(x, n, d_absmax, d_quant_mult, workspace, workspace_bytes, as_stream(stream));
+}
+
+int mi8_quantize_f32_i8(const float* x, size_t n, const float* d_quant_mult, int8_t* q, void* stream) {
+  return launch_quantize(x, n, d_quant_mult, q, as_stream(stream));
+}
+
+int mi8_prepare_a_f32(const float* a, int rows, int cols, int8_t* q, float* d_quant_mult, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  if(rows < 0 || cols <= 0 || d_quant_mult == nullptr)
+    return MI8_ERR_BAD_ARG;
+  if(rows == 0)
+    return MI8_OK;
+  const size_t n = static_cast<size_t>(rows) * static_cast<size_t>(cols);
+  int rc = launch_max_absolute(a, n, nullptr, d_quant_mult, workspace, workspace_bytes, as_stream(stream));
+  if(rc != MI8_OK)
+    return rc;
+  return launch_quantize(a, n, d_quant_mult, q, as_stream(stream));
+}
+
+int mi8_prepare_b_f32(const float* w, int K, int N, int w_is_nk, int8_t* bt, float* d_quant_mult, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  if(K <= 0 || N <= 0 || d_quant_mult == nullptr)
+    return MI8_ERR_BAD_ARG;
+  const size_t n = static_cast<size_t>(K) * static_cast<size_t>(N);
+  int rc = launch_max_absolute(w, n, nullptr, d_quant_mult, workspace, workspace_bytes, as_stream(stream));
+  if(rc != MI8_OK)
+    return rc;
+  if(w_is_nk)
+    return launch_quantize(w, n, d_quant_mult, bt, as_stream(stream));
+  return launch_transpose_quantize(w, K, N, d_quant_mult, bt, as_stream(stream));
+}
+
+int mi8_multiply_i8(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb,
+                    float scale, const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  return launch_gemm(aq, bt, M, N, K, d_qa, d_qb, scale, bias, relu, c, out_dtype, acc_out, workspace, workspace_bytes,
+                     as_stream(stream), 0, 0);
+}
+
+int mi8_multiply_i8_ex(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb,
+                       float scale, const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* workspace,
+                       size_t workspace_bytes, void* stream, int force_tile_m, int force_splits) {
+  if(force_tile_m < 0 || force_splits < 0)
+    return MI8_ERR_BAD_ARG;
+  return launch_gemm(aq, bt, M, N, K, d_qa, d_qb, scale, bias, relu, c, out_dtype, acc_out, workspace, workspace_bytes,
+                     as_stream(stream), force_tile_m, force_splits);
+}
+
+int mi8_affine_f32(const float* a, int M, int K, const int8_t* bt, const float* d_qb, int N, const float* bias, float scale,
+                   int relu, void* c, int out_dtype, int8_t* aq_scratch, void* workspace, size_t workspace_bytes,
+                   void* stream) {
+  if(M < 0 || K <= 0 || N <= 0 || aq_scratch == nullptr)
+    return MI8_ERR_BAD_ARG;
+  if(M == 0)
+    return MI8_OK;
+  if(K % 16 != 0)
+    return MI8_ERR_MISALIGNED;
+  float* d_qa = reinterpret_cast<float*>(aq_scratch + static_cast<size_t>(M) * K);
+  int rc = mi8_prepare_a_f32(a, M, K, aq_scratch, d_qa, workspace, workspace_bytes, stream);
+  if(rc != MI8_OK)
+    return rc;
+  return launch_gemm(aq_scratch, bt, M, N, K, d_qa, d_qb, scale, bias, relu, c, out_dtype, nullptr, workspace,
+                     workspace_bytes, as_stream(stream), 0, 0);
+}
+
+int mi8_multiply_plan(int M, int N, int K, int force_tile_m, int force_splits, int out[8]) {
+  if(out == nullptr)
+    return MI8_ERR_BAD_ARG;
+  GemmPlan plan;
+  int rc = make_gemm_plan(M, N, K, force_tile_m, force_splits, &plan);
+  if(rc != MI8_OK)
+    return rc;
+  out[0] = plan.tile_m;
+  out[1] = plan.stages;
+  out[2] = plan.splits;
+  out[3] = plan.n_tiles;
+  out[4] = plan.m_tiles;
+  out[5] = plan.grid;
+  out[6] = plan.smem_bytes;
+  out[7] = sm_count();
+  return MI8_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,524 @@
+// int8 x int8 -> int32 GEMM on the 5th-generation tensor cores (tcgen05, kind::i8) with TMEM
+// accumulators, TMA-fed shared-memory ring and a fused dequantise + bias + ReLU epilogue.
+//
+// Orientation.  Marian's converted weight is Bt[N,K] (K contiguous) and the quantised activation
+// is Aq[M,K] (K contiguous): both operands are K-major.  The kernel puts 128 rows of the WEIGHT on
+// the MMA's M dimension (TMEM lanes) and a tile of `TM` activation rows on the MMA's N dimension
+// (TMEM columns), i.e. it computes a tile of C^T.  Consequences:
+//   * every weight byte is fetched from HBM exactly once per activation tile, whatever M is;
+//   * skinny decode shapes (M = beam x batch) pick TM = 16..256 and waste no tensor work on padding;
+//   * in the epilogue a thread owns one output column n and walks over rows m, so for a fixed m the
+//     32 threads of a warp store 32 consecutive floats of C: fully coalesced without staging.
+// When there are fewer tiles than SMs the K range is split across CTAs; partial int32 accumulators
+// go through the workspace and the last CTA to arrive adds them up and runs the epilogue.  Integer
+// addition is associative, so every split factor gives bit-identical accumulators.
+//
+// Roles inside a CTA of 192 threads: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (one TMEM lane quarter each).  Two TMEM accumulator buffers let the
+// epilogue of one tile overlap the MMAs of the next.  CTAs are persistent over a static schedule.
+#include <cuda_fp16.h>
+
+#include "mi8_internal.h"
+#include "mi8_ptx.cuh"
+
+namespace mi8 {
+
+namespace {
+
+constexpr int kTileN = 128;     // weight rows per tile (MMA M)
+constexpr int kTileKBytes = 128;  // K bytes per pipeline stage = one 128-byte swizzle row
+constexpr int kMmaK = 32;       // K per tcgen05.mma kind::i8
+constexpr int kThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr int kMaxStages = 8;
+
+template <int TM>
+struct TileCfg {
+  static constexpr int kStages = TM == 256 ? 4 : (TM == 128 ? 6 : 8);
+  static constexpr int kWBytes = kTileN * kTileKBytes;
+  static constexpr int kABytes = TM * kTileKBytes;
+  static constexpr int kStageBytes = kWBytes + kABytes;
+  static constexpr int kAccStride = TM < 32 ? 32 : TM;  // TMEM columns between the two accumulators
+  static constexpr int kTmemCols = 2 * kAccStride;
+  static constexpr int kChunk = TM < 32 ? TM : 32;
+};
+
+struct Control {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort;
+  int is_last;
+};
+
+template <int TM>
+constexpr int smem_bytes_for() {
+  return TileCfg<TM>::kStages * TileCfg<TM>::kStageBytes + static_cast<int>(sizeof(Control)) + 1024;
+}
+
+struct GemmParams {
+  int M, N, K;
+  int n_tiles, m_tiles, splits, kb_total, kb_per_split, total_work;
+  const float* d_qa;
+  const float* d_qb;
+  float scale;
+  const float* bias;
+  int relu;
+  int out_f16;
+  void* c;
+  int32_t* acc_out;
+  int32_t* partials;
+  unsigned* tile_counters;
+  int* status;
+};
+
+struct WorkItem {
+  int tile, split, n_tile, m_tile, kb_begin, kb_end;
+};
+
+__device__ __forceinline__ WorkItem decode_work(const GemmParams& p, int w) {
+  WorkItem it;
+  it.split = w % p.splits;
+  it.tile = w / p.splits;
+  it.n_tile = it.tile % p.n_tiles;
+  it.m_tile = it.tile / p.n_tiles;
+  it.kb_begin = it.split * p.kb_per_split;
+  it.kb_end = min(p.kb_total, it.kb_begin + p.kb_per_split);
+  return it;
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+template <int N>
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, int32_t (&v)[N]);
+template <>
+__device__ __forceinline__ void tmem_ld_chunk<16>(uint32_t taddr, int32_t (&v)[16]) { tmem_ld_x16(taddr, v); }
+template <>
+__device__ __forceinline__ void tmem_ld_chunk<32>(uint32_t taddr, int32_t (&v)[32]) { tmem_ld_x32(taddr, v); }
+
+template <int TM>
+__global__ void __launch_bounds__(kThreads, 1)
+mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
+  using T = TileCfg<TM>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzled tiles must start on a 1024-byte boundary.
+  const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
+  uint8_t* tiles = smem_raw + pad;
+  Control* ctl = reinterpret_cast<Control*>(tiles + T::kStages * T::kStageBytes);
+  volatile int* abort_flag = &ctl->abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if(threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_a);
+    for(int s = 0; s < T::kStages; ++s) {
+      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->empty[s], 1);
+    }
+    for(int b = 0; b < 2; ++b) {
+      mbar_init(&ctl->tmem_full[b], 1);
+      mbar_init(&ctl->tmem_empty[b], kEpilogueThreads);
+    }
+    mbar_init(&ctl->drain, 1);
+    ctl->abort = 0;
+    ctl->is_last = 0;
+    fence_mbar_init();
+  }
+  if(warp == 1) {
+    tmem_alloc(&ctl->tmem_base, T::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctl->tmem_base);
+
+  bool ok = true;
+
+  if(warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    uint32_t it = 0;
+    for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+      const WorkItem wi = decode_work(p, w);
+      for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
+        const uint32_t s = it % T::kStages;
+        const uint32_t ph = (it / T::kStages) & 1u;
+        if(lane == 0)
+          ok = mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if(!ok)
+          break;
+        if(lane == 0) {
+          uint8_t* st = tiles + s * T::kStageBytes;
+          mbar_arrive_expect_tx(&ctl->full[s], T::kStageBytes);
+          tma_load_2d(st, &tmap_w, kb * kTileKBytes, wi.n_tile * kTileN, &ctl->full[s]);
+          tma_load_2d(st + T::kWBytes, &tmap_a, kb * kTileKBytes, wi.m_tile * TM, &ctl->full[s]);
+        }
+        __syncwarp();
+      }
+    }
+    if(!ok) {
+      *abort_flag = 1;
+      if(lane == 0) {
+        atomicMax(p.status, static_cast<int>(kDevTimeoutProducer));
+        // Wait (bounded) for the copies already issued, so none lands after the CTA has gone.
+        const uint32_t first = it > static_cast<uint32_t>(T::kStages) ? it - T::kStages : 0u;
+        int no_abort = 0;
+        for(uint32_t j = first; j < it; ++j)
+          mbar_wait_bounded(&ctl->full[j % T::kStages], (j / T::kStages) & 1u, &no_abort);
+      }
+      __syncwarp();
+    }
+  } else if(warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = make_idesc_i8(TM);
+    uint32_t it = 0, acc_it = 0;
+    for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++acc_it) {
+      const WorkItem wi = decode_work(p, w);
+      const uint32_t as = acc_it & 1u;
+      const uint32_t aph = (acc_it >> 1) & 1u;
+      if(lane == 0)
+        ok = mbar_wait_bounded(&ctl->tmem_empty[as], aph ^ 1u, abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if(!ok)
+        break;
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + as * T::kAccStride;
+      for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
+        const uint32_t s = it % T::kStages;
+        const uint32_t ph = (it / T::kStages) & 1u;
+        if(lane == 0)
+          ok = mbar_wait_bounded(&ctl->full[s], ph, abort_flag);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if(!ok)
+          break;
+        tc_fence_after_sync();
+        if(lane == 0) {
+          const uint32_t w_addr = smem_u32(tiles + s * T::kStageBytes);
+          const uint32_t a_addr = w_addr + T::kWBytes;
+#pragma unroll
+          for(int k = 0; k < kTileKBytes / kMmaK; ++k) {
+            tc_mma_i8(d_tmem, make_kmajor_sw128_desc(w_addr + k * kMmaK), make_kmajor_sw128_desc(a_addr + k * kMmaK), idesc,
+                      (kb > wi.kb_begin || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&ctl->empty[s]);  // frees the smem slot once these MMAs have read it
+        }
+        __syncwarp();
+      }
+      if(!ok)
+        break;
+      if(lane == 0)
+        tc_commit(&ctl->tmem_full[as]);  // accumulator complete
+      __syncwarp();
+    }
+    if(!ok) {
+      *abort_flag = 1;
+      if(lane == 0)
+        atomicMax(p.status, static_cast<int>(kDevTimeoutMma));
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) are readable by this warp
+    const int row = quarter * 32 + lane;
+    const int epi_tid = threadIdx.x - 64;
+    const float unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(*p.d_qa, *p.d_qb)), p.scale);
+    uint32_t acc_it = 0;
+    for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++acc_it) {
+      const WorkItem wi = decode_work(p, w);
+      const uint32_t as = acc_it & 1u;
+      const uint32_t aph = (acc_it >> 1) & 1u;
+      if(lane == 0)
+        ok = mbar_wait_bounded(&ctl->tmem_full[as], aph, abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if(!ok)
+        break;
+      tc_fence_after_sync();
+
+      const uint32_t t_addr = tmem_base + as * T::kAccStride + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int n = wi.n_tile * kTileN + row;
+      const bool n_ok = n < p.N;
+      const int m0 = wi.m_tile * TM;
+      const int cols_valid = min(TM, p.M - m0);  // activation rows of this tile that exist
+      bool finalize = true;
+
+      if(p.splits > 1) {
+        // Pass 1: park this split's partial accumulators, layout [column][128 rows] (coalesced).
+        int32_t* mine = p.partials + static_cast<size_t>(w) * (kTileN * TM);
+#pragma unroll 1
+        for(int c = 0; c < TM / T::kChunk; ++c) {
+          int32_t v[T::kChunk];
+          tmem_ld_chunk<T::kChunk>(t_addr + c * T::kChunk, v);
+          tc_wait_ld();
+#pragma unroll
+          for(int j = 0; j < T::kChunk; ++j)
+            if(c * T::kChunk + j < cols_valid)
+              mine[(c * T::kChunk + j) * kTileN + row] = v[j];
+        }
+        __threadfence();
+        named_bar_sync(1, kEpilogueThreads);
+        if(epi_tid == 0) {
+          const unsigned old = atomicAdd(&p.tile_counters[wi.tile], 1u);
+          const int last = (old == static_cast<unsigned>(p.splits - 1)) ? 1 : 0;
+          if(last)
+            p.tile_counters[wi.tile] = 0u;  // leave the workspace zeroed for the next call
+          *reinterpret_cast<volatile int*>(&ctl->is_last) = last;
+        }
+        named_bar_sync(1, kEpilogueThreads);
+        finalize = *reinterpret_cast<volatile int*>(&ctl->is_last) != 0;
+        if(finalize)
+          __threadfence();
+      }
+
+      if(finalize) {
+        const float bias_n = (p.bias != nullptr && n_ok) ? __ldg(p.bias + n) : 0.0f;
+        const int32_t* tile_partials = p.partials + static_cast<size_t>(wi.tile) * p.splits * (kTileN * TM);
+#pragma unroll 1
+        for(int c = 0; c < TM / T::kChunk; ++c) {
+          int32_t v[T::kChunk];
+          tmem_ld_chunk<T::kChunk>(t_addr + c * T::kChunk, v);
+          tc_wait_ld();
+          if(p.splits > 1) {
+            for(int s2 = 0; s2 < p.splits; ++s2) {
+              if(s2 == wi.split)
+                continue;
+              const int32_t* other = tile_partials + static_cast<size_t>(s2) * (kTileN * TM);
+#pragma unroll
+              for(int j = 0; j < T::kChunk; ++j)
+                if(c * T::kChunk + j < cols_valid)
+                  v[j] += __ldcg(other + (c * T::kChunk + j) * kTileN + row);
+            }
+          }
+          if(n_ok) {
+#pragma unroll
+            for(int j = 0; j < T::kChunk; ++j) {
+              const int mcol = c * T::kChunk + j;
+              if(mcol < cols_valid) {
+                const size_t idx = static_cast<size_t>(m0 + mcol) * p.N + n;
+                if(p.acc_out != nullptr)
+                  p.acc_out[idx] = v[j];
+                // float(acc) * unquant (+ bias), two separately rounded operations, then ReLU
+                float f = __fmul_rn(__int2float_rn(v[j]), unquant);
+                if(p.bias != nullptr)
+                  f = __fadd_rn(f, bias_n);
+                if(p.relu && !(f > 0.0f))
+                  f = 0.0f;
+                if(p.out_f16)
+                  reinterpret_cast<__half*>(p.c)[idx] = __float2half_rn(f);
+                else
+                  reinterpret_cast<float*>(p.c)[idx] = f;
+              }
+            }
+          }
+        }
+      }
+      // hand the accumulator buffer back to the MMA warp
+      tc_fence_before_sync();
+      mbar_arrive(&ctl->tmem_empty[as]);
+    }
+    if(!ok) {
+      *abort_flag = 1;
+      if(lane == 0)
+        atomicMax(p.status, static_cast<int>(kDevTimeoutEpilogue));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if(warp == 1) {
+    if(*abort_flag) {
+      // Something gave up: make sure no MMA is still running before the accumulators are released.
+      bool drained = true;
+      if(lane == 0) {
+        int no_abort = 0;
+        tc_commit(&ctl->drain);
+        drained = mbar_wait_bounded(&ctl->drain, 0u, &no_abort);
+        if(!drained)
+          atomicMax(p.status, static_cast<int>(kDevTimeoutDrain));
+      }
+      __syncwarp();
+    }
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, T::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+    if(e != cudaSuccess || qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// Tensor map over a row-major int8 matrix [rows, K] with a box of 128 K-bytes x box_rows rows,
+// 128-byte swizzle, zero fill outside the matrix.
+int encode_kmajor_map(CUtensorMap* map, const int8_t* base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if(fn == nullptr)
+    return MI8_ERR_DRIVER;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(K)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileKBytes), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t elem_strides[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(base), dims, strides, box, elem_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MI8_OK : MI8_ERR_DRIVER;
+}
+
+template <int TM>
+int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, const GemmPlan& plan, cudaStream_t stream) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  constexpr int smem = smem_bytes_for<TM>();
+  if(dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(mi8_gemm_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if(e != cudaSuccess) {
+      set_last_cuda_error(e);
+      return MI8_ERR_LAUNCH;
+    }
+    attr_set[dev] = true;
+  }
+  mi8_gemm_kernel<TM><<<plan.grid, kThreads, smem, stream>>>(tw, ta, p);
+  count_launch();
+  return check_launch();
+}
+
+}  // namespace
+
+int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, GemmPlan* plan) {
+  if(M <= 0 || N <= 0 || K <= 0)
+    return MI8_ERR_BAD_ARG;
+  int tm = force_tile_m;
+  if(tm == 0) {
+    tm = 256;
+    for(int cand : {16, 32, 64, 128, 256})
+      if(M <= cand) {
+        tm = cand;
+        break;
+      }
+  }
+  if(tm != 16 && tm != 32 && tm != 64 && tm != 128 && tm != 256)
+    return MI8_ERR_BAD_ARG;
+  const int sms = sm_count();
+  plan->tile_m = tm;
+  plan->stages = tm == 256 ? 4 : (tm == 128 ? 6 : 8);
+  plan->n_tiles = (N + kTileN - 1) / kTileN;
+  plan->m_tiles = (M + tm - 1) / tm;
+  plan->kb_total = (K + kTileKBytes - 1) / kTileKBytes;
+  const long long tiles = static_cast<long long>(plan->n_tiles) * plan->m_tiles;
+  if(tiles > 0x7fffffffLL / 64)
+    return MI8_ERR_UNSUPPORTED;
+  int splits = force_splits;
+  if(splits == 0) {
+    splits = 1;
+    if(tiles < sms) {
+      // Spread the weight stream over more SMs, but keep the partial-accumulator traffic
+      // (splits * M * N * 4 bytes) below about twice the weight bytes (K * N).
+      int by_sms = static_cast<int>(sms / tiles);
+      int by_traffic = K / (2 * M) > 1 ? K / (2 * M) : 1;
+      splits = by_sms < by_traffic ? by_sms : by_traffic;
+      if(splits > plan->kb_total)
+        splits = plan->kb_total;
+      if(splits < 1)
+        splits = 1;
+    }
+  }
+  if(splits < 1 || splits > plan->kb_total)
+    return MI8_ERR_BAD_ARG;
+  plan->kb_per_split = (plan->kb_total + splits - 1) / splits;
+  splits = (plan->kb_total + plan->kb_per_split - 1) / plan->kb_per_split;  // no empty split
+  plan->splits = splits;
+  if(splits > 1 && tiles > kWsMaxTileCounters)
+    return MI8_ERR_UNSUPPORTED;
+  const long long work = tiles * splits;
+  plan->grid = static_cast<int>(work < sms ? work : sms);
+  plan->smem_bytes = tm == 256 ? smem_bytes_for<256>()
+                               : tm == 128 ? smem_bytes_for<128>()
+                                           : tm == 64 ? smem_bytes_for<64>() : tm == 32 ? smem_bytes_for<32>() : smem_bytes_for<16>();
+  plan->partial_bytes = splits > 1 ? static_cast<size_t>(work) * kTileN * tm * sizeof(int32_t) : 0;
+  return MI8_OK;
+}
+
+int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb, float scale,
+                const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* ws, size_t ws_bytes,
+                cudaStream_t stream, int force_tile_m, int force_splits) {
+  if(M < 0 || N <= 0 || K <= 0)
+    return MI8_ERR_BAD_ARG;
+  if(M == 0)
+    return MI8_OK;
+  if(aq == nullptr || bt == nullptr || d_qa == nullptr || d_qb == nullptr || c == nullptr)
+    return MI8_ERR_BAD_ARG;
+  if(out_dtype != MI8_F32 && out_dtype != MI8_F16)
+    return MI8_ERR_BAD_ARG;
+  if(K % 16 != 0 || (reinterpret_cast<uintptr_t>(aq) & 15u) || (reinterpret_cast<uintptr_t>(bt) & 15u))
+    return MI8_ERR_MISALIGNED;
+  GemmPlan plan;
+  int rc = make_gemm_plan(M, N, K, force_tile_m, force_splits, &plan);
+  if(rc != MI8_OK)
+    return rc;
+  if(plan.splits > 1) {
+    if(ws == nullptr || ws_bytes < kWsHeaderBytes + plan.partial_bytes)
+      return MI8_ERR_WORKSPACE;
+  }
+  CUtensorMap tw, ta;
+  rc = encode_kmajor_map(&tw, bt, N, K, kTileN);
+  if(rc != MI8_OK)
+    return rc;
+  rc = encode_kmajor_map(&ta, aq, M, K, plan.tile_m);
+  if(rc != MI8_OK)
+    return rc;
+
+  GemmParams p;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.n_tiles = plan.n_tiles;
+  p.m_tiles = plan.m_tiles;
+  p.splits = plan.splits;
+  p.kb_total = plan.kb_total;
+  p.kb_per_split = plan.kb_per_split;
+  p.total_work = plan.n_tiles * plan.m_tiles * plan.splits;
+  p.d_qa = d_qa;
+  p.d_qb = d_qb;
+  p.scale = scale;
+  p.bias = bias;
+  p.relu = relu ? 1 : 0;
+  p.out_f16 = out_dtype == MI8_F16 ? 1 : 0;
+  p.c = c;
+  p.acc_out = acc_out;
+  uint8_t* wsb = static_cast<uint8_t*>(ws);
+  p.partials = wsb ? reinterpret_cast<int32_t*>(wsb + kWsOffPartials) : nullptr;
+  p.tile_counters = wsb ? reinterpret_cast<unsigned*>(wsb + kWsOffTileCounters) : nullptr;
+  p.status = device_status_ptr();
+  if(p.status == nullptr)
+    return MI8_ERR_LAUNCH;
+
+  switch(plan.tile_m) {
+    case 16: return launch_cfg<16>(tw, ta, p, plan, stream);
+    case 32: return launch_cfg<32>(tw, ta, p, plan, stream);
+    case 64: return launch_cfg<64>(tw, ta, p, plan, stream);
+    case 128: return launch_cfg<128>(tw, ta, p, plan, stream);
+    default: return launch_cfg<256>(tw, ta, p, plan, stream);
+  }
+}
+
+}  // namespace mi8

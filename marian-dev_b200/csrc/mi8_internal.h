@@ -1,0 +1,65 @@
+// Internal declarations shared by the translation units of libmarian_i8.so.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/marian_i8.h"
+
+namespace mi8 {
+
+// ------------------------------------------------------------------ workspace layout (bytes)
+// [0, 256)            abs-max block counter (first 4 bytes) and reserved words      } kept zero
+// [256, 16640)        split-K arrival counters, one uint32 per output tile          } between calls
+// [16640, 20736)      abs-max per-block partial maxima (1024 x uint32)
+// [20736, ...)        split-K partial accumulators, int32 [work item][column][128 rows]
+constexpr size_t kWsOffAbsmaxCounter = 0;
+constexpr size_t kWsOffTileCounters = 256;
+constexpr int kWsMaxTileCounters = 4096;
+constexpr size_t kWsOffAbsmaxPartials = kWsOffTileCounters + sizeof(uint32_t) * kWsMaxTileCounters;
+constexpr int kWsMaxAbsmaxBlocks = 1024;
+constexpr size_t kWsOffPartials = kWsOffAbsmaxPartials + sizeof(uint32_t) * kWsMaxAbsmaxBlocks;
+constexpr size_t kWsZeroedBytes = kWsOffAbsmaxPartials;  // the part that must be zero between calls
+constexpr size_t kWsHeaderBytes = kWsOffPartials;
+
+// ------------------------------------------------------------------ per-thread error / launch bookkeeping
+void set_last_cuda_error(cudaError_t e);
+void count_launch();
+
+// Device status word of the current device (address of a __device__ int, resolved once per device).
+int* device_status_ptr();
+int sm_count();
+
+// Checks cudaGetLastError() after a launch; returns MI8_OK or MI8_ERR_LAUNCH.
+int check_launch();
+
+// ------------------------------------------------------------------ GEMM plan
+struct GemmPlan {
+  int tile_m;        // activation rows per tile (MMA N): 16, 32, 64, 128 or 256
+  int stages;        // shared-memory pipeline depth
+  int splits;        // split-K factor
+  int n_tiles;       // tiles of 128 weight rows
+  int m_tiles;       // tiles of tile_m activation rows
+  int kb_total;      // 128-byte K blocks
+  int kb_per_split;
+  int grid;
+  int smem_bytes;
+  size_t partial_bytes;
+};
+int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, GemmPlan* plan);
+
+// quantisation kernels (mi8_quant.cu)
+int launch_max_absolute(const float* x, size_t n, float* d_absmax, float* d_quant_mult, void* ws, size_t ws_bytes,
+                        cudaStream_t stream);
+int launch_quantize(const float* x, size_t n, const float* d_quant_mult, int8_t* q, cudaStream_t stream);
+int launch_transpose_quantize(const float* w, int K, int N, const float* d_quant_mult, int8_t* bt, cudaStream_t stream);
+
+// GEMM (mi8_gemm.cu)
+int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb, float scale,
+                const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* ws, size_t ws_bytes,
+                cudaStream_t stream, int force_tile_m, int force_splits);
+
+inline cudaStream_t as_stream(void* s) { return s ? reinterpret_cast<cudaStream_t>(s) : cudaStreamPerThread; }
+
+}  // namespace mi8

@@ -1,0 +1,191 @@
+"""CPU checker for the int8 affine path: TEST INFRASTRUCTURE ONLY.
+
+Two independent restatements of Marian's intgemm8 affine/dot sequence
+(src/tensors/cpu/intgemm_interface.h:17-99, src/tensors/cpu/integer_common.h:101-111,169-182,
+src/tensors/cpu/expression_graph_packable.h:153-253):
+
+* ``numpy_*`` functions: plain NumPy, used for small cases and to cross-check the C build;
+* ``COracle``: ctypes binding of ``liboracle_i8.so`` (``oracle_i8.c``), used for the larger
+  parity cases and as the timed CPU baseline.
+
+PARITY UNPINNED: the arithmetic of this path lives in the un-vendored intgemm submodule and the
+reference has no test with an intgemm-typed operand, so neither restatement could be checked
+against reference outputs.  Only tests, the smoke check and the bench's CPU-baseline leg may import
+this module; the product package never does.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "liboracle_i8.so")
+
+
+# --------------------------------------------------------------------------- NumPy restatement
+def numpy_quant_mult(x: np.ndarray) -> np.float32:
+    """computeQuantMult<intgemm8>: 127.0f / max|x| (integer_common.h:169-173); all-zero -> 1."""
+    m = np.float32(np.max(np.abs(x.astype(np.float32, copy=False)))) if x.size else np.float32(0)
+    if m == 0:
+        return np.float32(1.0)
+    return np.float32(127.0) / m
+
+
+def numpy_quantize(x: np.ndarray, quant_mult: np.float32) -> np.ndarray:
+    """Int8::PrepareA: fp32 multiply, round half to even, saturate to [-127, 127]."""
+    y = np.rint(x.astype(np.float32, copy=False) * np.float32(quant_mult))
+    return np.clip(y, -127, 127).astype(np.int8)
+
+
+def numpy_prepare_b(w: np.ndarray, w_is_nk: bool = False):
+    """marian-conv intgemm8 branch: W[K,N] -> (Bt[N,K] int8, quantMult) (expression_graph_packable.h:160-201)."""
+    qm = numpy_quant_mult(w)
+    wt = w if w_is_nk else np.ascontiguousarray(w.T)
+    return numpy_quantize(wt, qm), qm
+
+
+def numpy_multiply_i32(aq: np.ndarray, bt: np.ndarray) -> np.ndarray:
+    """Exact int32 accumulators: acc[i,j] = sum_k Aq[i,k] * Bt[j,k]."""
+    return aq.astype(np.int32) @ bt.astype(np.int32).T
+
+
+def numpy_unquant_mult(qa, qb, scale=1.0) -> np.float32:
+    """1.0f / (qa*qb), then * scale, all in fp32 (intgemm_interface.h:69-70)."""
+    u = np.float32(1.0) / (np.float32(qa) * np.float32(qb))
+    return np.float32(u * np.float32(scale))
+
+
+def numpy_unquantize(acc: np.ndarray, unquant, bias=None, relu=False) -> np.ndarray:
+    """float(acc)*unquant (+bias), then the separate ReLU (expression_operators.cpp:721-731)."""
+    out = acc.astype(np.float32) * np.float32(unquant)
+    if bias is not None:
+        out = out + bias.astype(np.float32).reshape(1, -1)
+    if relu:
+        out = np.where(out > 0, out, np.float32(0)).astype(np.float32)
+    return out.astype(np.float32)
+
+
+def numpy_affine(a: np.ndarray, bt: np.ndarray, qb, bias=None, scale=1.0, relu=False):
+    """Whole affineOrDotTyped sequence; returns (out fp32, acc int32, aq int8, qa)."""
+    a2 = a.reshape(-1, a.shape[-1])
+    qa = numpy_quant_mult(a2)
+    aq = numpy_quantize(a2, qa)
+    acc = numpy_multiply_i32(aq, bt)
+    out = numpy_unquantize(acc, numpy_unquant_mult(qa, qb, scale), bias, relu)
+    return out.reshape(a.shape[:-1] + (bt.shape[0],)), acc, aq, qa
+
+
+# --------------------------------------------------------------------------- C build
+def build(force: bool = False) -> str:
+    """Compile oracle_i8.c with the Makefile beside it; returns the shared-object path."""
+    src = os.path.join(_HERE, "oracle_i8.c")
+    if force or not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-s", "-B"])
+    return _LIB
+
+
+def _p(arr, ct):
+    return arr.ctypes.data_as(ctypes.POINTER(ct)) if arr is not None else None
+
+
+class COracle:
+    """ctypes view of liboracle_i8.so."""
+
+    def __init__(self, lib_path: str | None = None):
+        if lib_path is None:
+            lib_path = _LIB if os.path.exists(_LIB) else build()
+        L = ctypes.CDLL(lib_path)
+        f32p, i8p, i32p = (ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_int8),
+                           ctypes.POINTER(ctypes.c_int32))
+        L.mo_max_absolute.restype = ctypes.c_float
+        L.mo_max_absolute.argtypes = [f32p, ctypes.c_size_t]
+        L.mo_compute_quant_mult.restype = ctypes.c_float
+        L.mo_compute_quant_mult.argtypes = [f32p, ctypes.c_size_t]
+        L.mo_prepare_a.restype = None
+        L.mo_prepare_a.argtypes = [f32p, i8p, ctypes.c_float, ctypes.c_int, ctypes.c_int, f32p]
+        L.mo_prepare_b.restype = ctypes.c_float
+        L.mo_prepare_b.argtypes = [f32p, ctypes.c_int, ctypes.c_int, ctypes.c_int, i8p]
+        L.mo_multiply_i32.restype = ctypes.c_int
+        L.mo_multiply_i32.argtypes = [i8p, i8p, ctypes.c_int, ctypes.c_int, ctypes.c_int, i32p]
+        L.mo_multiply_sat16.restype = ctypes.c_int
+        L.mo_multiply_sat16.argtypes = [i8p, i8p, ctypes.c_int, ctypes.c_int, ctypes.c_int, i32p]
+        L.mo_unquant_mult.restype = ctypes.c_float
+        L.mo_unquant_mult.argtypes = [ctypes.c_float] * 3
+        L.mo_unquantize_write.restype = None
+        L.mo_unquantize_write.argtypes = [i32p, ctypes.c_int, ctypes.c_int, ctypes.c_float, f32p, ctypes.c_int, f32p]
+        L.mo_affine.restype = ctypes.c_int
+        L.mo_affine.argtypes = [f32p, ctypes.c_int, ctypes.c_int, i8p, ctypes.c_float, ctypes.c_int, f32p,
+                                ctypes.c_float, ctypes.c_int, f32p, i8p, i32p, f32p]
+        L.mo_max_threads.restype = ctypes.c_int
+        L.mo_set_threads.argtypes = [ctypes.c_int]
+        self.L = L
+
+    def max_threads(self) -> int:
+        return int(self.L.mo_max_threads())
+
+    def set_threads(self, n: int) -> None:
+        self.L.mo_set_threads(int(n))
+
+    def quant_mult(self, x: np.ndarray) -> np.float32:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        return np.float32(self.L.mo_compute_quant_mult(_p(x, ctypes.c_float), x.size))
+
+    def quantize(self, x: np.ndarray, qm) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty(x.shape, dtype=np.int8)
+        rows = int(np.prod(x.shape[:-1])) if x.ndim > 1 else 1
+        self.L.mo_prepare_a(_p(x, ctypes.c_float), _p(out, ctypes.c_int8), ctypes.c_float(float(qm)),
+                            rows, x.shape[-1], None)
+        return out
+
+    def prepare_b(self, w: np.ndarray, w_is_nk: bool = False):
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        k, n = (w.shape[1], w.shape[0]) if w_is_nk else (w.shape[0], w.shape[1])
+        bt = np.empty((n, k), dtype=np.int8)
+        qm = self.L.mo_prepare_b(_p(w, ctypes.c_float), k, n, int(w_is_nk), _p(bt, ctypes.c_int8))
+        return bt, np.float32(qm)
+
+    def multiply_i32(self, aq: np.ndarray, bt: np.ndarray, sat16: bool = False) -> np.ndarray:
+        aq = np.ascontiguousarray(aq, dtype=np.int8)
+        bt = np.ascontiguousarray(bt, dtype=np.int8)
+        m, k = aq.shape
+        n = bt.shape[0]
+        acc = np.empty((m, n), dtype=np.int32)
+        fn = self.L.mo_multiply_sat16 if sat16 else self.L.mo_multiply_i32
+        rc = fn(_p(aq, ctypes.c_int8), _p(bt, ctypes.c_int8), m, k, n, _p(acc, ctypes.c_int32))
+        if rc != 0:
+            raise ValueError("oracle multiply rejected its arguments")
+        return acc
+
+    def unquantize(self, acc: np.ndarray, unquant, bias=None, relu=False) -> np.ndarray:
+        acc = np.ascontiguousarray(acc, dtype=np.int32)
+        m, n = acc.shape
+        out = np.empty((m, n), dtype=np.float32)
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32).reshape(-1)
+        self.L.mo_unquantize_write(_p(acc, ctypes.c_int32), m, n, ctypes.c_float(float(unquant)),
+                                   _p(b, ctypes.c_float), int(relu), _p(out, ctypes.c_float))
+        return out
+
+    def affine(self, a: np.ndarray, bt: np.ndarray, qb, bias=None, scale=1.0, relu=False, want_acc=False):
+        a2 = np.ascontiguousarray(a, dtype=np.float32).reshape(-1, a.shape[-1])
+        bt = np.ascontiguousarray(bt, dtype=np.int8)
+        m, k = a2.shape
+        n = bt.shape[0]
+        out = np.empty((m, n), dtype=np.float32)
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32).reshape(-1)
+        aq = np.empty((m, k), dtype=np.int8) if want_acc else None
+        acc = np.empty((m, n), dtype=np.int32) if want_acc else None
+        qa = ctypes.c_float(0)
+        rc = self.L.mo_affine(_p(a2, ctypes.c_float), m, k, _p(bt, ctypes.c_int8), ctypes.c_float(float(qb)), n,
+                              _p(b, ctypes.c_float), ctypes.c_float(float(scale)), int(relu),
+                              _p(out, ctypes.c_float), _p(aq, ctypes.c_int8), _p(acc, ctypes.c_int32),
+                              ctypes.byref(qa))
+        if rc != 0:
+            raise ValueError("oracle affine rejected its arguments")
+        out = out.reshape(a.shape[:-1] + (n,))
+        if want_acc:
+            return out, acc, aq, np.float32(qa.value)
+        return out

@@ -1,0 +1,242 @@
+/*
+ * CPU restatement of Marian's intgemm8 affine/dot path.  TEST INFRASTRUCTURE ONLY:
+ * this file is the checker for the CUDA engine and the timed CPU baseline; nothing
+ * shipped in the product library links, loads or calls it.
+ *
+ * PARITY UNPINNED.  The arithmetic Marian runs on this path lives in the third-party
+ * module marian-nmt/intgemm (git submodule src/3rd_party/intgemm, no recoverable pin),
+ * whose sources are not part of the reference tree, and no test of the reference
+ * exercises an intgemm-typed operand.  The functions below therefore follow the
+ * reference's own call sites and the published behaviour of the intgemm entry points
+ * they call:
+ *
+ *   MaxAbsolute            : max over |x|                              (call site src/tensors/cpu/integer_common.h:173)
+ *   computeQuantMult       : 127.0f / MaxAbsolute                      (src/tensors/cpu/integer_common.h:169-182)
+ *   Int8::PrepareA         : x*quantMult, round to nearest even, saturate to [-127,127]
+ *                                                                      (call site src/tensors/cpu/intgemm_interface.h:23)
+ *   getQuantMult           : the multiplier is stored as a float right after the last int8 element
+ *                                                                      (src/tensors/cpu/integer_common.h:101-111, src/common/types.cpp:32-37)
+ *   Multiply               : acc[i][j] = sum_k A[i][k]*B[k][j] in int32 (the AVX512-VNNI route; an optional
+ *                            saturating-int16 emulation documents the pre-VNNI kernels)
+ *                                                                      (call site src/tensors/cpu/intgemm_interface.h:74-87)
+ *   UnquantizeAndWrite / UnquantizeAndAddBiasAndWrite : out = float(acc)*unquant (+ bias[col])
+ *                                                                      (src/tensors/cpu/intgemm_interface.h:66-87)
+ *   ReLU afterwards, in place                                          (src/graph/expression_operators.cpp:721-731,
+ *                                                                       src/graph/node_operators_unary.h:1053-1068)
+ *   weight conversion      : Transpose10, 127/max|W|, plain quantise -> Bt[N,K] row-major + scale tail
+ *                                                                      (src/tensors/cpu/expression_graph_packable.h:153-253)
+ *
+ * Build with -ffp-contract=off so that "multiply then add" stays two rounded operations.
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#include <pthread.h>
+#include <unistd.h>
+
+#define MO_OK 0
+#define MO_BAD_ARG 1
+
+int mo_version(void) { return 1; }
+
+/* Row-parallel helper on POSIX threads: the GEMM and the write-back split their M rows over the
+ * worker count set with mo_set_threads (default 1, as Marian runs one GEMM per worker thread,
+ * src/common/config.cpp:245-248; the timed baseline raises it to the host's core count). */
+static int g_threads = 1;
+
+int mo_max_threads(void) {
+  long n = sysconf(_SC_NPROCESSORS_ONLN);
+  return n > 0 ? (int)n : 1;
+}
+
+void mo_set_threads(int n) { g_threads = n > 0 ? n : 1; }
+
+typedef void (*mo_row_fn)(int row_begin, int row_end, void* ctx);
+typedef struct { mo_row_fn fn; int b, e; void* ctx; } mo_job;
+
+static void* mo_job_main(void* p) {
+  mo_job* j = (mo_job*)p;
+  j->fn(j->b, j->e, j->ctx);
+  return NULL;
+}
+
+static void mo_parallel_rows(int m, mo_row_fn fn, void* ctx) {
+  int t = g_threads;
+  if(t > m) t = m;
+  if(t <= 1) { fn(0, m, ctx); return; }
+  pthread_t* th = (pthread_t*)malloc(sizeof(pthread_t) * (size_t)t);
+  mo_job* jobs = (mo_job*)malloc(sizeof(mo_job) * (size_t)t);
+  int per = (m + t - 1) / t;
+  for(int i = 0; i < t; ++i) {
+    jobs[i].fn = fn; jobs[i].ctx = ctx;
+    jobs[i].b = i * per < m ? i * per : m;
+    jobs[i].e = (i + 1) * per < m ? (i + 1) * per : m;
+    if(i > 0) pthread_create(&th[i], NULL, mo_job_main, &jobs[i]);
+  }
+  mo_job_main(&jobs[0]);
+  for(int i = 1; i < t; ++i) pthread_join(th[i], NULL);
+  free(th); free(jobs);
+}
+
+/* intgemm::MaxAbsolute(begin, end) as used by computeQuantMult (integer_common.h:173). */
+float mo_max_absolute(const float* x, size_t n) {
+  float m = 0.0f;
+  for(size_t i = 0; i < n; ++i) {
+    float a = fabsf(x[i]);
+    if(a > m) m = a;
+  }
+  return m;
+}
+
+/* computeQuantMult<intgemm8> (integer_common.h:169-173).  The reference divides by zero for an
+ * all-zero tensor; this restatement defines that case as quantMult = 1 (all quantised values 0). */
+float mo_compute_quant_mult(const float* x, size_t n) {
+  float m = mo_max_absolute(x, n);
+  if(m == 0.0f) return 1.0f;
+  return 127.0f / m;
+}
+
+static inline int8_t mo_quantize_one(float x, float quant_mult) {
+  float r = rintf(x * quant_mult); /* default rounding mode: to nearest, ties to even */
+  if(r > 127.0f) r = 127.0f;
+  if(r < -127.0f) r = -127.0f;   /* -128 is never produced */
+  if(r != r) r = 0.0f;
+  return (int8_t)r;
+}
+
+/* Int8::PrepareA(in, out, quantMult, rows, cols): element-wise quantise, same layout
+ * (intgemm_interface.h:23-27).  `tail`, when non-null, receives the multiplier the way
+ * getQuantMult(out) = quantMult does (intgemm_interface.h:28). */
+void mo_prepare_a(const float* in, int8_t* out, float quant_mult, int rows, int cols, float* tail) {
+  size_t n = (size_t)rows * (size_t)cols;
+  for(size_t i = 0; i < n; ++i) out[i] = mo_quantize_one(in[i], quant_mult);
+  if(tail) memcpy(tail, &quant_mult, sizeof(float));
+}
+
+/* marian-conv's intgemm8 branch (expression_graph_packable.h:160-201): tmp = Transpose10(W),
+ * quantMult = 127/max|W|, Int8::PrepareA(tmp) -> Bt[N,K] row-major; returns quantMult.
+ * With w_is_nk != 0 the input already is [N,K] (a tied embedding matrix used with transB) and
+ * is only quantised. */
+float mo_prepare_b(const float* w, int k, int n, int w_is_nk, int8_t* bt) {
+  size_t total = (size_t)k * (size_t)n;
+  float qm = mo_compute_quant_mult(w, total);
+  if(w_is_nk) {
+    for(size_t i = 0; i < total; ++i) bt[i] = mo_quantize_one(w[i], qm);
+  } else {
+    for(int j = 0; j < n; ++j)
+      for(int i = 0; i < k; ++i)
+        bt[(size_t)j * k + i] = mo_quantize_one(w[(size_t)i * n + j], qm);
+  }
+  return qm;
+}
+
+/* One output row against all of Bt; cloned per ISA so the same shared object runs on any x86-64 host. */
+__attribute__((target_clones("arch=icelake-server", "arch=skylake-avx512", "avx2", "default")))
+static void mo_row_times_bt(const int8_t* a_row, const int8_t* bt, int k, int n, int32_t* acc_row) {
+  for(int j = 0; j < n; ++j) {
+    const int8_t* b = bt + (size_t)j * k;
+    int32_t s = 0;
+    for(int p = 0; p < k; ++p) s += (int32_t)a_row[p] * (int32_t)b[p];
+    acc_row[j] = s;
+  }
+}
+
+/* Multiply(A, B, rowsA, colsA, colsB, callback) with exact 32-bit accumulation
+ * (intgemm_interface.h:74-87).  A is [M,K] row-major int8, Bt is [N,K] row-major int8. */
+typedef struct { const int8_t* a; const int8_t* bt; int k, n; int32_t* acc; } mo_mul_ctx;
+
+static void mo_mul_rows(int b, int e, void* p) {
+  mo_mul_ctx* c = (mo_mul_ctx*)p;
+  for(int i = b; i < e; ++i) mo_row_times_bt(c->a + (size_t)i * c->k, c->bt, c->k, c->n, c->acc + (size_t)i * c->n);
+}
+
+int mo_multiply_i32(const int8_t* a, const int8_t* bt, int m, int k, int n, int32_t* acc) {
+  if(m < 0 || k <= 0 || n <= 0) return MO_BAD_ARG;
+  mo_mul_ctx c = {a, bt, k, n, acc};
+  mo_parallel_rows(m, mo_mul_rows, &c);
+  return MO_OK;
+}
+
+static inline int16_t mo_sat16(int32_t v) {
+  if(v > 32767) return 32767;
+  if(v < -32768) return -32768;
+  return (int16_t)v;
+}
+
+/* The pre-VNNI intgemm kernels multiply with pmaddubsw: |a| (unsigned) times sign-adjusted b,
+ * adjacent pairs summed with signed 16-bit saturation, then pairs of those sums added again with
+ * 16-bit saturation before widening to 32 bits.  This emulation keeps that structure so the
+ * "reference's saturation behaviour" can be compared against; it is not the primary oracle. */
+int mo_multiply_sat16(const int8_t* a, const int8_t* bt, int m, int k, int n, int32_t* acc) {
+  if(m < 0 || k <= 0 || n <= 0 || (k % 4) != 0) return MO_BAD_ARG;
+  for(int i = 0; i < m; ++i) {
+    const int8_t* ar = a + (size_t)i * k;
+    for(int j = 0; j < n; ++j) {
+      const int8_t* b = bt + (size_t)j * k;
+      int32_t s = 0;
+      for(int p = 0; p < k; p += 4) {
+        int16_t pair[2];
+        for(int h = 0; h < 2; ++h) {
+          int a0 = ar[p + 2 * h], a1 = ar[p + 2 * h + 1];
+          int b0 = b[p + 2 * h], b1 = b[p + 2 * h + 1];
+          int ua0 = a0 < 0 ? -a0 : a0, ua1 = a1 < 0 ? -a1 : a1;
+          int sb0 = a0 < 0 ? -b0 : (a0 == 0 ? 0 : b0);
+          int sb1 = a1 < 0 ? -b1 : (a1 == 0 ? 0 : b1);
+          pair[h] = mo_sat16(ua0 * sb0 + ua1 * sb1);
+        }
+        s += (int32_t)mo_sat16((int32_t)pair[0] + (int32_t)pair[1]);
+      }
+      acc[(size_t)i * n + j] = s;
+    }
+  }
+  return MO_OK;
+}
+
+/* unquant_mult = 1.0f / (aQuantMult * bQuantMult); unquant_mult *= scale (intgemm_interface.h:69-70). */
+float mo_unquant_mult(float qa, float qb, float scale) {
+  float u = 1.0f / (qa * qb);
+  u = u * scale;
+  return u;
+}
+
+/* callbacks::UnquantizeAndWrite / UnquantizeAndAddBiasAndWrite followed by the separate in-place
+ * ReLU of affineWithReluDropout on this path (expression_operators.cpp:721-731). */
+typedef struct { const int32_t* acc; int n; float unquant; const float* bias; int relu; float* out; } mo_wr_ctx;
+
+static void mo_wr_rows(int b, int e, void* p) {
+  mo_wr_ctx* c = (mo_wr_ctx*)p;
+  for(int i = b; i < e; ++i) {
+    for(int j = 0; j < c->n; ++j) {
+      float v = (float)c->acc[(size_t)i * c->n + j] * c->unquant;
+      if(c->bias) v = v + c->bias[j];
+      if(c->relu && !(v > 0.0f)) v = 0.0f;
+      c->out[(size_t)i * c->n + j] = v;
+    }
+  }
+}
+
+void mo_unquantize_write(const int32_t* acc, int m, int n, float unquant, const float* bias, int relu, float* out) {
+  mo_wr_ctx c = {acc, n, unquant, bias, relu, out};
+  mo_parallel_rows(m, mo_wr_rows, &c);
+}
+
+/* The whole affineOrDotTyped sequence (intgemm_interface.h:46-99) for float A [M,K] and a converted
+ * weight Bt [N,K] with multiplier qb.  aq (M*K), acc (M*N) are optional outputs. */
+int mo_affine(const float* a, int m, int k, const int8_t* bt, float qb, int n, const float* bias, float scale,
+              int relu, float* out, int8_t* aq_out, int32_t* acc_out, float* qa_out) {
+  if(m < 0 || k <= 0 || n <= 0) return MO_BAD_ARG;
+  if(m == 0) return MO_OK;
+  int8_t* aq = aq_out ? aq_out : (int8_t*)malloc((size_t)m * k);
+  int32_t* acc = acc_out ? acc_out : (int32_t*)malloc((size_t)m * n * sizeof(int32_t));
+  if(!aq || !acc) return MO_BAD_ARG;
+  float qa = mo_compute_quant_mult(a, (size_t)m * k);
+  mo_prepare_a(a, aq, qa, m, k, NULL);
+  mo_multiply_i32(aq, bt, m, k, n, acc);
+  mo_unquantize_write(acc, m, n, mo_unquant_mult(qa, qb, scale), bias, relu, out);
+  if(qa_out) *qa_out = qa;
+  if(!aq_out) free(aq);
+  if(!acc_out) free(acc);
+  return MO_OK;
+}

@@ -1,0 +1,207 @@
+"""Parity of the CUDA kernels (called through the C ABI) against the CPU oracle: bit-exact for the
+abs-max, the int8 quantisation, the int32 accumulators and - because both sides round the same
+two fp32 operations - the dequantised outputs as well (the tolerance the path asks for is 1e-5
+relative; the assertion below is the stricter exact one, with the 1e-5 check kept beside it)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-5  # relative error allowed for dequantised outputs
+
+
+def _ops():
+    from marian_dev_b200 import ops
+    return ops
+
+
+def _assert_healthy():
+    assert _ops().poll_status() == 0
+
+
+@pytest.mark.parametrize("n", [1, 3, 4, 17, 1024, 4099, 256 * 512, 1 << 22])
+def test_max_absolute_and_quantize(cuda_device, oracle, n):
+    ops = _ops()
+    rng = np.random.default_rng(n)
+    x = rng.standard_normal(n).astype(np.float32) * 3
+    n_pad = ((n + 3) // 4) * 4
+    xt = torch.zeros(n_pad, dtype=torch.float32, device=cuda_device)
+    xt[:n] = torch.from_numpy(x).to(cuda_device)
+    ws = ops.default_workspace(cuda_device)
+    from marian_dev_b200.binding import check, lib
+    absmax = torch.zeros(1, dtype=torch.float32, device=cuda_device)
+    qm = torch.zeros(1, dtype=torch.float32, device=cuda_device)
+    check(lib().mi8_max_absolute_f32(xt.data_ptr(), n, absmax.data_ptr(), qm.data_ptr(), ws.ptr, ws.nbytes,
+                                     torch.cuda.current_stream().cuda_stream))
+    q = torch.zeros(n_pad + 16, dtype=torch.int8, device=cuda_device)
+    check(lib().mi8_quantize_f32_i8(xt.data_ptr(), n, qm.data_ptr(), q.data_ptr(),
+                                    torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert absmax.item() == np.abs(x).max()
+    assert np.float32(qm.item()) == oracle.quant_mult(x)
+    want = oracle.quantize(x, oracle.quant_mult(x))
+    assert np.array_equal(q[:n].cpu().numpy(), want)
+    assert int(q[n:].abs().sum()) == 0  # nothing written past the end
+    # the workspace counters are back to zero
+    from marian_dev_b200.binding import lib as _l  # noqa: F401
+    assert int(ws.buf[:16640].to(torch.int32).sum()) == 0
+    _assert_healthy()
+
+
+def test_quantize_edge_cases(cuda_device, oracle):
+    ops = _ops()
+    # all-zero tensor: multiplier defined as 1
+    z = torch.zeros(64, 64, device=cuda_device)
+    zq = ops.prepareA(z)
+    torch.cuda.synchronize()
+    assert zq.quant_mult.item() == 1.0 and int(zq.data.abs().sum()) == 0
+    # ties round to even, +-max maps to +-127, -128 never appears
+    vals = np.array([127.0, -127.0, 0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 126.5, -126.5, 63.49999, 1e-9] + [0.0] * 4,
+                    dtype=np.float32).reshape(1, 16)
+    t = torch.from_numpy(vals).to(cuda_device)
+    tq = ops.prepareA(t)
+    torch.cuda.synchronize()
+    assert tq.quant_mult.item() == 1.0
+    assert np.array_equal(tq.data.cpu().numpy(), oracle.quantize(vals, np.float32(1.0)))
+    assert tq.data.min().item() >= -127
+    _assert_healthy()
+
+
+@pytest.mark.parametrize("k,n", [(512, 2048), (1024, 1024), (256, 1536), (96, 40)])
+def test_prepare_b(cuda_device, oracle, k, n):
+    ops = _ops()
+    rng = np.random.default_rng(k * 7 + n)
+    w = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+    b = ops.prepareB(torch.from_numpy(w).to(cuda_device))
+    torch.cuda.synchronize()
+    bt, qb = oracle.prepare_b(w)
+    assert np.float32(b.quant_mult.item()) == qb
+    assert np.array_equal(b.data.cpu().numpy(), bt)
+    assert b.shape == (k, n)
+    # an [N,K] weight (tied embedding used with transB) is only quantised
+    b2 = ops.prepareB(torch.from_numpy(np.ascontiguousarray(w.T)).to(cuda_device), w_is_nk=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(b2.data.cpu().numpy(), bt) and b2.shape == (k, n)
+    _assert_healthy()
+
+
+def _run_affine(cuda_device, oracle, m, k, n, relu, with_bias, seed, out_dtype=torch.float32, tile_m=0, splits=0,
+                scale=1.0):
+    ops = _ops()
+    rng = np.random.default_rng(seed)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+    bias = (rng.standard_normal(n) * 0.01).astype(np.float32) if with_bias else None
+    bt, qb = oracle.prepare_b(w)
+    want, want_acc, want_aq, want_qa = oracle.affine(a, bt, qb, bias, scale, relu, want_acc=True)
+
+    b = ops.prepareB(torch.from_numpy(w).to(cuda_device))
+    aq = ops.prepareA(torch.from_numpy(a).to(cuda_device))
+    acc = torch.full((m, n), -7, dtype=torch.int32, device=cuda_device)
+    guard = 64
+    out_buf = torch.full((m * n + guard,), float("nan"), dtype=out_dtype, device=cuda_device)
+    out = ops.multiply(aq, b, torch.from_numpy(bias).to(cuda_device) if with_bias else None, scale, relu,
+                       out=out_buf[:m * n].view(m, n), out_dtype=out_dtype, acc_out=acc, tile_m=tile_m, splits=splits)
+    torch.cuda.synchronize()
+    assert ops.poll_status() == 0
+    assert np.array_equal(aq.data.cpu().numpy(), want_aq)
+    assert np.float32(aq.quant_mult.item()) == want_qa
+    got_acc = acc.cpu().numpy()
+    assert np.array_equal(got_acc, want_acc), f"int32 accumulators differ at {np.argwhere(got_acc != want_acc)[:5]}"
+    got = out.float().cpu().numpy()
+    if out_dtype == torch.float32:
+        denom = np.maximum(np.abs(want), 1e-30)
+        assert np.all(np.abs(got - want) <= REL_TOL * np.maximum(denom, np.abs(want).max() * 1e-3))
+        assert np.array_equal(got, want)  # both sides round identically, so in fact bit-exact
+    else:
+        assert np.array_equal(got, want.astype(np.float16).astype(np.float32))
+    assert bool(torch.isnan(out_buf[m * n:].float()).all())  # canary behind the output untouched
+    return got
+
+
+def test_config1_single_affine(cuda_device, oracle):
+    """X[256,512] ~ N(0,1), W[512,2048] ~ N(0,0.02), bias ~ N(0,0.01), ReLU, seed 0."""
+    _run_affine(cuda_device, oracle, 256, 512, 2048, True, True, 0)
+
+
+@pytest.mark.parametrize("m", [1, 2, 5, 8, 16, 17, 31, 32, 33, 64, 100, 128, 130, 256, 257, 512, 1000])
+def test_affine_m_sweep(cuda_device, oracle, m):
+    _run_affine(cuda_device, oracle, m, 512, 384, bool(m % 2), bool(m % 3), 100 + m)
+
+
+@pytest.mark.parametrize("n", [8, 40, 128, 136, 264, 1000])
+@pytest.mark.parametrize("k", [64, 128, 192, 512, 1040])
+def test_affine_ragged_nk(cuda_device, oracle, n, k):
+    _run_affine(cuda_device, oracle, 24, k, n, True, True, n * 13 + k)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+@pytest.mark.parametrize("m,tile_m", [(8, 16), (64, 64), (200, 256)])
+def test_split_k_bit_identical(cuda_device, oracle, splits, m, tile_m):
+    _run_affine(cuda_device, oracle, m, 1024, 640, False, True, 7, tile_m=tile_m, splits=splits)
+
+
+@pytest.mark.parametrize("tile_m", [16, 32, 64, 128, 256])
+def test_every_tile_width(cuda_device, oracle, tile_m):
+    # more activation rows than one tile, so several tiles along M run in every configuration
+    _run_affine(cuda_device, oracle, 300, 256, 384, True, True, tile_m, tile_m=tile_m)
+
+
+def test_persistent_schedule_many_tiles(cuda_device, oracle):
+    # 32 x 16 = 512 tiles on 148 CTAs: every CTA walks several tiles and both accumulator buffers
+    _run_affine(cuda_device, oracle, 4096, 256, 4096, True, True, 11)
+
+
+def test_fp16_output_and_scale(cuda_device, oracle):
+    _run_affine(cuda_device, oracle, 96, 512, 256, False, True, 5, out_dtype=torch.float16, scale=0.125)
+    _run_affine(cuda_device, oracle, 96, 512, 256, True, False, 6, scale=2.0)
+
+
+def test_repeated_calls_share_workspace(cuda_device, oracle):
+    a = _run_affine(cuda_device, oracle, 8, 1024, 1024, False, True, 3)
+    for _ in range(3):
+        b = _run_affine(cuda_device, oracle, 8, 1024, 1024, False, True, 3)
+        assert np.array_equal(a, b)
+
+
+def test_operator_surface(cuda_device, oracle):
+    """affine / dot / affineWithReluDropout on [..., K] inputs, float semantics of the reference's
+    own operator tests (src/tests/units/operator_tests.cpp:618-659) within int8 precision."""
+    ops = _ops()
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((3, 7, 256)).astype(np.float32)
+    w = (rng.standard_normal((256, 128)) * 0.05).astype(np.float32)
+    bias = (rng.standard_normal(128) * 0.1).astype(np.float32)
+    xt, bt_, biast = (torch.from_numpy(v).to(cuda_device) for v in (x, w, bias))
+    W = ops.prepareB(bt_)
+    bt, qb = oracle.prepare_b(w)
+    y = ops.affine(xt, W, biast)
+    y2 = ops.dot(xt, W, scale=0.5)
+    y3 = ops.affineWithReluDropout(xt, W, biast)
+    torch.cuda.synchronize()
+    assert y.shape == (3, 7, 128)
+    assert np.array_equal(y.cpu().numpy(), oracle.affine(x, bt, qb, bias))
+    assert np.array_equal(y2.cpu().numpy(), oracle.affine(x, bt, qb, None, 0.5))
+    assert np.array_equal(y3.cpu().numpy(), oracle.affine(x, bt, qb, bias, 1.0, True))
+    ref = np.maximum(x @ w + bias, 0)
+    assert np.abs(y3.cpu().numpy() - ref).max() < 0.05 * np.abs(ref).max()
+    _assert_healthy()
+
+
+def test_argument_errors(cuda_device):
+    ops = _ops()
+    from marian_dev_b200.binding import Mi8Error
+    W = ops.prepareB(torch.randn(64, 32, device=cuda_device))
+    with pytest.raises(Mi8Error):
+        ops.affine(torch.randn(4, 64, device=cuda_device).double(), W, None)
+    with pytest.raises(Mi8Error):
+        ops.affine(torch.randn(4, 48, device=cuda_device), W, None)  # inner dimension mismatch
+    with pytest.raises(Mi8Error):
+        ops.affine(torch.randn(4, 64), W, None)  # host tensor: there is no CPU path
+    with pytest.raises(Mi8Error):
+        ops.affineWithReluDropout(torch.randn(4, 64, device=cuda_device), W, None, 0.1)
+    Wbad = ops.prepareB(torch.randn(40, 32, device=cuda_device))  # K = 40 is not a multiple of 16
+    with pytest.raises(Mi8Error):
+        ops.affine(torch.randn(4, 40, device=cuda_device), Wbad, None)
+    _assert_healthy()
