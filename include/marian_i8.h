@@ -15,8 +15,10 @@
  *     wrapper turns non-zero into Marian's ABORT (src/common/logging.h:100-140).
  *
  * Workspace contract: the caller passes a workspace of at least mi8_workspace_bytes() bytes that was
- * zero-filled once (mi8_workspace_init).  Calls leave it zero-filled where it has to be, so it can be
- * reused by every later call on the same stream.  Calls that share a workspace must not overlap.
+ * zero-filled once (mi8_workspace_init).  Kernels use it for arrival counters, abs-max partials and
+ * split-K accumulation buffers and put every word they need zeroed back to zero before they finish,
+ * so one workspace serves every later call on the same stream.  Calls that share a workspace must
+ * not overlap on the device.
  */
 #ifndef MARIAN_I8_H_
 #define MARIAN_I8_H_
@@ -50,9 +52,11 @@ const char* mi8_strerror(int status);
 int mi8_last_cuda_error(void);
 const char* mi8_last_cuda_error_string(void);
 
-/* Bytes of workspace that any call with these (or smaller) dimensions needs. */
+/* Bytes of workspace a call with exactly these dimensions needs; mi8_workspace_bytes(0,0,0) is the
+ * upper bound that covers every shape (about 21 MB). */
 size_t mi8_workspace_bytes(int M, int N, int K);
-/* Zero-fills a workspace (stream-ordered).  Needed once after allocation. */
+/* Zero-fills the whole workspace (stream-ordered).  Needed once after allocation, and again after a
+ * call that ended with MI8_ERR_DEVICE. */
 int mi8_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 
 /* Reads the device status word of the current device (synchronises the device).  0 = healthy;

@@ -90,7 +90,8 @@ unsigned long long mi8_launch_count(void) { return t_launches; }
 void mi8_launch_count_reset(void) { t_launches = 0; }
 
 size_t mi8_workspace_bytes(int M, int N, int K) {
-  // Upper bound over every plan: at most one work item per SM is split, each parks 128 x 256 int32.
+  // Upper bound over every plan: only problems with fewer tiles than SMs are split, and each tile
+  // accumulates into 128 x 256 int32 at most.
   const size_t upper = kWsHeaderBytes + static_cast<size_t>(160) * 128 * 256 * sizeof(int32_t);
   if(M <= 0 || N <= 0 || K <= 0)
     return upper;
@@ -103,7 +104,7 @@ size_t mi8_workspace_bytes(int M, int N, int K) {
 int mi8_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
   if(workspace == nullptr || workspace_bytes < kWsHeaderBytes)
     return MI8_ERR_WORKSPACE;
-  cudaError_t e = cudaMemsetAsync(workspace, 0, kWsZeroedBytes, as_stream(stream));
+  cudaError_t e = cudaMemsetAsync(workspace, 0, workspace_bytes, as_stream(stream));
   if(e != cudaSuccess) {
     set_last_cuda_error(e);
     return MI8_ERR_LAUNCH;

@@ -9,12 +9,13 @@
 //   * skinny decode shapes (M = beam x batch) pick TM = 16..256 and waste no tensor work on padding;
 //   * in the epilogue a thread owns one output column n and walks over rows m, so for a fixed m the
 //     32 threads of a warp store 32 consecutive floats of C: fully coalesced without staging.
-// When there are fewer tiles than SMs the K range is split across CTAs; partial int32 accumulators
-// go through the workspace and the last CTA to arrive adds them up and runs the epilogue.  Integer
-// addition is associative, so every split factor gives bit-identical accumulators.
+// When there are fewer tiles than SMs the K range is split across CTAs; every split adds its partial
+// int32 accumulators into one buffer per tile in the workspace (red.global.add) and the last CTA to
+// arrive reads the totals, zeroes the buffer again and runs the epilogue.  Integer addition is
+// associative, so every split factor gives bit-identical accumulators.
 //
-// Roles inside a CTA of 192 threads: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..5 = epilogue (one TMEM lane quarter each).  Two TMEM accumulator buffers let the
+// Roles inside a CTA of 320 threads: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..9 = epilogue (two warps per TMEM lane quarter, alternating 32-column chunks).  Two TMEM accumulator buffers let the
 // epilogue of one tile overlap the MMAs of the next.  CTAs are persistent over a static schedule.
 #include <cuda_fp16.h>
 
@@ -28,8 +29,8 @@ namespace {
 constexpr int kTileN = 128;     // weight rows per tile (MMA M)
 constexpr int kTileKBytes = 128;  // K bytes per pipeline stage = one 128-byte swizzle row
 constexpr int kMmaK = 32;       // K per tcgen05.mma kind::i8
-constexpr int kThreads = 192;
-constexpr int kEpilogueThreads = 128;
+constexpr int kThreads = 320;
+constexpr int kEpilogueThreads = 256;
 constexpr int kMaxStages = 8;
 
 template <int TM>
@@ -224,10 +225,16 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         atomicMax(p.status, static_cast<int>(kDevTimeoutMma));
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) are readable by this warp
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    // A warp may only read the TMEM lane quarter (warp % 4); two warps share each quarter and take
+    // alternate 32-column chunks, so every scheduler has two epilogue warps to hide latency with.
+    const int quarter = warp & 3;
+    const int group = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const int epi_tid = threadIdx.x - 64;
+    constexpr int kChunks = TM / T::kChunk;
+    constexpr int kChunkStep = kChunks > 1 ? 2 : 1;
+    const bool has_chunks = kChunks > 1 || group == 0;
     const float unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(*p.d_qa, *p.d_qb)), p.scale);
     uint32_t acc_it = 0;
     for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++acc_it) {
@@ -246,20 +253,25 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const bool n_ok = n < p.N;
       const int m0 = wi.m_tile * TM;
       const int cols_valid = min(TM, p.M - m0);  // activation rows of this tile that exist
+      const float bias_n = (p.bias != nullptr && n_ok) ? __ldg(p.bias + n) : 0.0f;
+      // Split-K: every split adds its partial accumulators into one int32 buffer per tile with
+      // fire-and-forget reductions (layout [column][128 rows], coalesced); the last split to arrive
+      // reads the totals back, zeroes the buffer again and runs the write-back.
+      int32_t* tile_acc = p.partials + static_cast<size_t>(wi.tile) * (kTileN * TM);
       bool finalize = true;
 
       if(p.splits > 1) {
-        // Pass 1: park this split's partial accumulators, layout [column][128 rows] (coalesced).
-        int32_t* mine = p.partials + static_cast<size_t>(w) * (kTileN * TM);
+        if(has_chunks) {
 #pragma unroll 1
-        for(int c = 0; c < TM / T::kChunk; ++c) {
-          int32_t v[T::kChunk];
-          tmem_ld_chunk<T::kChunk>(t_addr + c * T::kChunk, v);
-          tc_wait_ld();
+          for(int c = group * (kChunkStep - 1); c < kChunks; c += kChunkStep) {
+            int32_t v[T::kChunk];
+            tmem_ld_chunk<T::kChunk>(t_addr + c * T::kChunk, v);
+            tc_wait_ld();
 #pragma unroll
-          for(int j = 0; j < T::kChunk; ++j)
-            if(c * T::kChunk + j < cols_valid)
-              mine[(c * T::kChunk + j) * kTileN + row] = v[j];
+            for(int j = 0; j < T::kChunk; ++j)
+              if(c * T::kChunk + j < cols_valid)
+                atomicAdd(tile_acc + (c * T::kChunk + j) * kTileN + row, v[j]);
+          }
         }
         __threadfence();
         named_bar_sync(1, kEpilogueThreads);
@@ -276,43 +288,67 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           __threadfence();
       }
 
-      if(finalize) {
-        const float bias_n = (p.bias != nullptr && n_ok) ? __ldg(p.bias + n) : 0.0f;
-        const int32_t* tile_partials = p.partials + static_cast<size_t>(wi.tile) * p.splits * (kTileN * TM);
+      if(finalize && has_chunks) {
 #pragma unroll 1
-        for(int c = 0; c < TM / T::kChunk; ++c) {
+        for(int c = group * (kChunkStep - 1); c < kChunks; c += kChunkStep) {
           int32_t v[T::kChunk];
-          tmem_ld_chunk<T::kChunk>(t_addr + c * T::kChunk, v);
-          tc_wait_ld();
+          const int col0 = c * T::kChunk;
           if(p.splits > 1) {
-            for(int s2 = 0; s2 < p.splits; ++s2) {
-              if(s2 == wi.split)
-                continue;
-              const int32_t* other = tile_partials + static_cast<size_t>(s2) * (kTileN * TM);
+            int32_t* src = tile_acc + col0 * kTileN + row;
 #pragma unroll
-              for(int j = 0; j < T::kChunk; ++j)
-                if(c * T::kChunk + j < cols_valid)
-                  v[j] += __ldcg(other + (c * T::kChunk + j) * kTileN + row);
-            }
+            for(int j = 0; j < T::kChunk; ++j)
+              v[j] = (col0 + j < cols_valid) ? __ldcg(src + j * kTileN) : 0;
+#pragma unroll
+            for(int j = 0; j < T::kChunk; ++j)
+              if(col0 + j < cols_valid)
+                src[j * kTileN] = 0;
+          } else {
+            tmem_ld_chunk<T::kChunk>(t_addr + col0, v);
+            tc_wait_ld();
           }
           if(n_ok) {
+            // float(acc) * unquant (+ bias): two separately rounded operations, then ReLU.  Each
+            // stage runs over the whole register chunk so the 32 columns overlap in the pipeline.
+            const size_t base = static_cast<size_t>(m0 + col0) * p.N + n;
+            const int valid = cols_valid - col0;  // columns of this chunk that exist (may exceed the chunk)
+            float f[T::kChunk];
 #pragma unroll
-            for(int j = 0; j < T::kChunk; ++j) {
-              const int mcol = c * T::kChunk + j;
-              if(mcol < cols_valid) {
-                const size_t idx = static_cast<size_t>(m0 + mcol) * p.N + n;
-                if(p.acc_out != nullptr)
-                  p.acc_out[idx] = v[j];
-                // float(acc) * unquant (+ bias), two separately rounded operations, then ReLU
-                float f = __fmul_rn(__int2float_rn(v[j]), unquant);
-                if(p.bias != nullptr)
-                  f = __fadd_rn(f, bias_n);
-                if(p.relu && !(f > 0.0f))
-                  f = 0.0f;
-                if(p.out_f16)
-                  reinterpret_cast<__half*>(p.c)[idx] = __float2half_rn(f);
-                else
-                  reinterpret_cast<float*>(p.c)[idx] = f;
+            for(int j = 0; j < T::kChunk; ++j)
+              f[j] = __fmul_rn(__int2float_rn(v[j]), unquant);
+            if(p.bias != nullptr) {
+#pragma unroll
+              for(int j = 0; j < T::kChunk; ++j)
+                f[j] = __fadd_rn(f[j], bias_n);
+            }
+            if(p.relu) {
+#pragma unroll
+              for(int j = 0; j < T::kChunk; ++j)
+                f[j] = f[j] > 0.0f ? f[j] : 0.0f;
+            }
+            if(p.acc_out != nullptr) {
+              int32_t* dst = p.acc_out + base;
+#pragma unroll
+              for(int j = 0; j < T::kChunk; ++j)
+                if(j < valid)
+                  dst[static_cast<size_t>(j) * p.N] = v[j];
+            }
+            if(p.out_f16) {
+              __half* dst = reinterpret_cast<__half*>(p.c) + base;
+#pragma unroll
+              for(int j = 0; j < T::kChunk; ++j)
+                if(j < valid)
+                  dst[static_cast<size_t>(j) * p.N] = __float2half_rn(f[j]);
+            } else {
+              float* dst = reinterpret_cast<float*>(p.c) + base;
+              if(valid >= T::kChunk) {
+#pragma unroll
+                for(int j = 0; j < T::kChunk; ++j)
+                  dst[static_cast<size_t>(j) * p.N] = f[j];
+              } else {
+#pragma unroll
+                for(int j = 0; j < T::kChunk; ++j)
+                  if(j < valid)
+                    dst[static_cast<size_t>(j) * p.N] = f[j];
               }
             }
           }
@@ -454,7 +490,7 @@ int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, Gemm
   plan->smem_bytes = tm == 256 ? smem_bytes_for<256>()
                                : tm == 128 ? smem_bytes_for<128>()
                                            : tm == 64 ? smem_bytes_for<64>() : tm == 32 ? smem_bytes_for<32>() : smem_bytes_for<16>();
-  plan->partial_bytes = splits > 1 ? static_cast<size_t>(work) * kTileN * tm * sizeof(int32_t) : 0;
+  plan->partial_bytes = splits > 1 ? static_cast<size_t>(tiles) * kTileN * tm * sizeof(int32_t) : 0;
   return MI8_OK;
 }
 

@@ -10,17 +10,17 @@
 namespace mi8 {
 
 // ------------------------------------------------------------------ workspace layout (bytes)
-// [0, 256)            abs-max block counter (first 4 bytes) and reserved words      } kept zero
-// [256, 16640)        split-K arrival counters, one uint32 per output tile          } between calls
+// [0, 256)            abs-max block counter (first 4 bytes) and reserved words
+// [256, 16640)        split-K arrival counters, one uint32 per output tile
 // [16640, 20736)      abs-max per-block partial maxima (1024 x uint32)
-// [20736, ...)        split-K partial accumulators, int32 [work item][column][128 rows]
+// [20736, ...)        split-K accumulation buffers, int32 [tile][column][128 rows]
+// Everything except the abs-max partials must be zero between calls; kernels restore that.
 constexpr size_t kWsOffAbsmaxCounter = 0;
 constexpr size_t kWsOffTileCounters = 256;
 constexpr int kWsMaxTileCounters = 4096;
 constexpr size_t kWsOffAbsmaxPartials = kWsOffTileCounters + sizeof(uint32_t) * kWsMaxTileCounters;
 constexpr int kWsMaxAbsmaxBlocks = 1024;
 constexpr size_t kWsOffPartials = kWsOffAbsmaxPartials + sizeof(uint32_t) * kWsMaxAbsmaxBlocks;
-constexpr size_t kWsZeroedBytes = kWsOffAbsmaxPartials;  // the part that must be zero between calls
 constexpr size_t kWsHeaderBytes = kWsOffPartials;
 
 // ------------------------------------------------------------------ per-thread error / launch bookkeeping

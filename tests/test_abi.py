@@ -1,0 +1,93 @@
+"""CPU tests of the boundary: the shared object loads, exports every symbol the header declares,
+and its host-side logic (planning, argument checks, status text) behaves without a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "marian_i8.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mi8_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    import marian_dev_b200 as pkg
+    from marian_dev_b200.binding import EXPORTS
+    assert os.path.exists(pkg.LIB_PATH), "build the library first (python __graft_entry__.py)"
+    L = ctypes.CDLL(pkg.LIB_PATH)
+    declared = _declared_symbols()
+    assert declared, "no declarations parsed from the header"
+    for sym in declared:
+        assert hasattr(L, sym), f"{sym} declared in include/marian_i8.h but not exported"
+    assert sorted(EXPORTS) == declared
+
+
+def test_strerror_and_version():
+    from marian_dev_b200.binding import lib
+    L = lib()
+    assert L.mi8_version() >= 100
+    assert L.mi8_strerror(0) == b"ok"
+    texts = {L.mi8_strerror(i) for i in range(8)}
+    assert len(texts) == 8 and b"unknown status" not in texts
+    assert L.mi8_strerror(99) == b"unknown status"
+
+
+@pytest.mark.parametrize("m,expect_tile", [(1, 16), (16, 16), (17, 32), (64, 64), (65, 128), (200, 256), (512, 256)])
+def test_plan_tile_choice(m, expect_tile):
+    from marian_dev_b200 import multiply_plan
+    p = multiply_plan(m, 1024, 1024)
+    assert p["tile_m"] == expect_tile
+    assert p["n_tiles"] == 8 and p["m_tiles"] == (m + expect_tile - 1) // expect_tile
+    assert 1 <= p["splits"] <= 8
+    assert p["grid"] <= p["sm_count"]
+    assert p["smem_bytes"] <= 227 * 1024
+
+
+def test_plan_covers_k_without_empty_splits():
+    from marian_dev_b200 import multiply_plan
+    for k in (64, 128, 192, 1040, 4096):
+        for splits in (1, 2, 3, 5, 8):
+            kb = (k + 127) // 128
+            if splits > kb:
+                with pytest.raises(Exception):
+                    multiply_plan(8, 256, k, 0, splits)
+                continue
+            p = multiply_plan(8, 256, k, 0, splits)
+            per = (kb + p["splits"] - 1) // p["splits"]
+            assert (p["splits"] - 1) * per < kb <= p["splits"] * per
+
+
+def test_plan_rejects_bad_arguments():
+    from marian_dev_b200 import Mi8Error, multiply_plan
+    for bad in [(0, 8, 64), (8, 0, 64), (8, 8, 0)]:
+        with pytest.raises(Mi8Error):
+            multiply_plan(*bad)
+    with pytest.raises(Mi8Error):
+        multiply_plan(8, 8, 64, 48, 0)  # tile width that does not exist
+
+
+def test_workspace_size_bound():
+    from marian_dev_b200.binding import lib
+    L = lib()
+    upper = L.mi8_workspace_bytes(0, 0, 0)
+    for (m, n, k) in [(1, 512, 512), (16, 1024, 1024), (512, 32000, 1024), (4096, 4096, 4096), (8, 256, 4096)]:
+        assert L.mi8_workspace_bytes(m, n, k) <= upper
+
+
+def test_null_and_misaligned_arguments_are_rejected_before_any_launch():
+    from marian_dev_b200.binding import lib
+    L = lib()
+    assert L.mi8_multiply_i8(None, None, 4, 8, 64, None, None, 1.0, None, 0, None, 0, None, None, 0, None) == 1
+    assert L.mi8_multiply_i8(16, 32, 4, 8, 40, 48, 64, 1.0, None, 0, 80, 0, None, None, 0, None) == 2   # K % 16
+    assert L.mi8_multiply_i8(17, 32, 4, 8, 64, 48, 64, 1.0, None, 0, 80, 0, None, None, 0, None) == 2   # pointer
+    assert L.mi8_multiply_i8(16, 32, 4, 8, 64, 48, 64, 1.0, None, 0, 80, 7, None, None, 0, None) == 1   # dtype
+    assert L.mi8_multiply_i8(16, 32, 0, 8, 64, 48, 64, 1.0, None, 0, 80, 0, None, None, 0, None) == 0   # M = 0 is a no-op
+    assert L.mi8_max_absolute_f32(None, 16, None, None, None, 0, None) == 1
+    assert L.mi8_max_absolute_f32(16, 16, None, None, None, 0, None) == 4                                # no workspace
+    assert L.mi8_workspace_init(None, 0, None) == 4
+    assert L.mi8_prepare_a_f32(16, -1, 8, 32, 48, 64, 1 << 20, None) == 1

@@ -44,7 +44,6 @@ def test_max_absolute_and_quantize(cuda_device, oracle, n):
     assert np.array_equal(q[:n].cpu().numpy(), want)
     assert int(q[n:].abs().sum()) == 0  # nothing written past the end
     # the workspace counters are back to zero
-    from marian_dev_b200.binding import lib as _l  # noqa: F401
     assert int(ws.buf[:16640].to(torch.int32).sum()) == 0
     _assert_healthy()
 
@@ -117,6 +116,10 @@ def _run_affine(cuda_device, oracle, m, k, n, relu, with_bias, seed, out_dtype=t
     else:
         assert np.array_equal(got, want.astype(np.float16).astype(np.float32))
     assert bool(torch.isnan(out_buf[m * n:].float()).all())  # canary behind the output untouched
+    ws = ops.default_workspace(cuda_device)
+    # counters and split-K accumulation buffers are zero again (bytes 16640..20736 hold abs-max partials)
+    assert int(ws.buf[:16640].view(torch.int32).abs().sum()) == 0
+    assert int(ws.buf[20736:].view(torch.int32).abs().max()) == 0
     return got
 
 
