@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark of the int8 decode path: transformer-big, beam 4, mini-batch 128, synthetic sentences.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is the decode of one mini-batch (128 synthetic sentences, beam 4) on one GPU: encoder,
+then decoder steps until every hypothesis ended or 1.5 x the source width is reached, with every
+weight multiplication on the int8 engine.  With N GPUs every rank holds a full model replica and
+decodes its own K mini-batches (mini-batches are dealt round-robin, as the reference's translator
+does); the only collective is the gather of the output token matrix.  Rank 0 prints one JSON line.
+
+`value` is measured with the mini-batch's token ids and mask already resident in HBM; `e2e` is the
+same decode called with host buffers (pinned host -> device copy of ids/mask inside the timed
+region, device -> host reads of the n-best lists every step and of nothing else).
+`--impl reference` times the CPU restatement of the reference's intgemm8 path (the reference itself
+cannot be built: its int8 arithmetic lives in the un-vendored intgemm submodule).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "int8_decode_tgt_tokens_per_sec"
+UNIT = "tokens/s"
+WORKLOAD = "transformer-big decode (6+6 layers, d=1024, ffn=4096, 16 heads, tied 32000 vocab, all affines int8), beam 4, mini-batch 128, lengths clip(N(30,12),4,128), max length 1.5x source"
+MINI_BATCH = 128
+BEAM = 4
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=6)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="big", help="big (the benchmark), base, student, tiny (debugging)")
+    ap.add_argument("--cpu-sentences", type=int, default=8, help="sentences in the CPU-baseline sample")
+    return ap.parse_args()
+
+
+def build_corpus(model_mod, cfg, n_batches):
+    n = n_batches * MINI_BATCH
+    corpus = model_mod.synthetic_corpus(max(n, MINI_BATCH), cfg.vocab, seed=1, length_dist="normal", lo=4, hi=128, mean=30.0, std=12.0)
+    return model_mod.make_batches(corpus, MINI_BATCH)
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs (read-only queries)."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile(prefix="clocks_", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- GEMM attribution
+class GemmTimer:
+    """Brackets every GEMM launch of the int8 engine with CUDA events on the launching stream, so the
+    dominant kernel's achieved bandwidth / throughput is measured inside the timed region."""
+
+    def __init__(self, ops_mod, torch_mod):
+        self.ops, self.torch = ops_mod, torch_mod
+        self.records = []   # (M, N, K, out_bytes, start, end)
+        self._orig = None
+
+    def __enter__(self):
+        self._orig = self.ops.multiply
+        torch = self.torch
+
+        def timed(aq, b, bias=None, scale=1.0, relu=False, out=None, out_dtype=torch.float32, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = self._orig(aq, b, bias, scale, relu, out=out, out_dtype=out_dtype, **kw)
+            e1.record()
+            self.records.append((aq.rows, b.rows, aq.cols, 4 if out_dtype == torch.float32 else 2, e0, e1))
+            return r
+
+        self.ops.multiply = timed
+        return self
+
+    def __exit__(self, *exc):
+        self.ops.multiply = self._orig
+
+    def summary(self):
+        """Aggregate per shape class; call after a device synchronisation."""
+        total = {"launches": 0, "us": 0.0, "bytes": 0.0, "ops": 0.0}
+        classes = {}
+        for (m, n, k, ob, e0, e1) in self.records:
+            us = e0.elapsed_time(e1) * 1000.0
+            by = m * k + n * k + 4 * n + ob * m * n + 8          # int8 A in, weights, bias, C out, two multipliers
+            op = 2.0 * m * n * k
+            key = ("history K/V (M grows)" if m > 1024 and n == k else f"N={n},K={k}")
+            c = classes.setdefault(key, {"launches": 0, "us": 0.0, "bytes": 0.0, "ops": 0.0})
+            for d in (c, total):
+                d["launches"] += 1
+                d["us"] += us
+                d["bytes"] += by
+                d["ops"] += op
+        return total, classes
+
+
+# ----------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from marian_dev_b200 import decoder, model, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the int8 engine has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = model.CONFIGS[args.model]
+    params = model.random_init(cfg, seed=0)
+    net = decoder.Int8Transformer(cfg, params, dev, output_int8=True)
+    del params
+    per_rank = args.warmup + args.steps                          # both timed legs decode the same mini-batches
+    batches = build_corpus(model, cfg, per_rank * world)
+    mine = [batches[i] for i in range(rank, len(batches), world)][:per_rank]
+    search = decoder.BeamSearch(net, beam=BEAM, max_length_factor=1.5, normalize=1.0)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def gather_outputs(results):
+        """The path's one collective: every rank contributes its [sentences, max_len] token matrix."""
+        if world == 1:
+            return results
+        mat = torch.full((MINI_BATCH, 192), -1, dtype=torch.int32)       # 192 = 1.5 x the longest source
+        for r, (toks, _s) in enumerate(results):
+            mat[r, :len(toks)] = torch.tensor(toks, dtype=torch.int32)
+        g = mat.to(dev)
+        out = [torch.empty_like(g) for _ in range(world)]
+        dist.all_gather(out, g)
+        return out
+
+    # warm-up
+    for b in mine[:args.warmup]:
+        search.search(b[1], b[2])
+    torch.cuda.synchronize()
+
+    # ---- leg 1: inputs resident in HBM ------------------------------------------------------
+    leg1 = mine[args.warmup:args.warmup + args.steps]
+    resident = [(torch.from_numpy(ids.astype(np.int64)).to(dev), torch.from_numpy(mask).to(dev)) for _, ids, mask in leg1]
+    sampler = ClockSampler(local_rank)
+    ops.reset_launch_count()
+    tokens = 0
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with GemmTimer(ops, torch) as gt:
+        e0.record()
+        for ids_t, mask_t in resident:
+            res = search.search_device(ids_t, mask_t)
+            gather_outputs(res)
+            tokens += sum(len(t) for t, _ in res)
+        e1.record()
+        barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    launches = ops.launch_count()
+    gemm_total, gemm_classes = gt.summary()
+
+    # ---- leg 2: end to end through the public call with host buffers --------------------------
+    leg2 = leg1
+    pinned = [(torch.from_numpy(ids.astype(np.int64)).pin_memory(), torch.from_numpy(mask).pin_memory()) for _, ids, mask in leg2]
+    search.h2d_bytes = search.d2h_bytes = 0
+    tokens2 = 0
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for ids_p, mask_p in pinned:
+        res = search.search(ids_p, mask_p)
+        gather_outputs(res)
+        tokens2 += sum(len(t) for t, _ in res)
+    f1.record()
+    barrier()
+    ms2 = f0.elapsed_time(f1)
+    h2d, d2h = search.h2d_bytes / max(1, len(pinned)), search.d2h_bytes / max(1, len(pinned))
+    status = ops.poll_status()
+
+    if world > 1:
+        t = torch.tensor([ms, ms2], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms2 = float(t[0]), float(t[1])
+        c = torch.tensor([tokens, tokens2, launches], device=dev, dtype=torch.float64)
+        dist.all_reduce(c, op=dist.ReduceOp.SUM)
+        tokens, tokens2, launches = int(c[0]), int(c[1]), int(c[2])
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        hbm_peak = peaks.get("hbm_gbs", 6650.0)
+        peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+        achieved = gemm_total["bytes"] / max(gemm_total["us"], 1e-9) / 1e3          # GB/s
+        roofline = {
+            "kernel": "mi8_gemm_kernel (all launches of the timed region)",
+            "bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
+            "frac": round(achieved / hbm_peak, 4), "peak_source": peak_src, "traffic": None,
+            "launches": gemm_total["launches"], "avg_launch_us": round(gemm_total["us"] / max(1, gemm_total["launches"]), 2),
+            "tops": round(gemm_total["ops"] / max(gemm_total["us"], 1e-9) / 1e6, 1),
+            "gemm_share_of_step_time": round(gemm_total["us"] / 1e3 / max(ms, 1e-9), 3),
+            "by_shape": {k: {"launches": v["launches"], "us_total": round(v["us"], 1),
+                             "GBps": round(v["bytes"] / max(v["us"], 1e-9) / 1e3, 1),
+                             "TOPS": round(v["ops"] / max(v["us"], 1e-9) / 1e6, 1)} for k, v in sorted(gemm_classes.items(), key=lambda kv: -kv[1]["us"])},
+        }
+        cpu = cpu_baseline(args, cfg_name=args.model) if world == 1 else None
+        line = {
+            "metric": METRIC, "value": round(tokens / (ms / 1e3), 1), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / max(1, args.steps), 2),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 (s8 x s8 -> s32), fp32 epilogue",
+            "data": "synthetic (random-init weights, uniform token ids, seeded)",
+            "config": {"workload": WORKLOAD if args.model == "big" else f"{args.model} (debug workload)", "mini_batch": MINI_BATCH, "beam": BEAM,
+                       "tokens_counted": "best hypothesis per sentence, EOS included", "parallelism": f"replicas x{world}",
+                       "l2": "not flushed: one decode step streams ~0.2 GB of int8 weights plus fp32 logits and history, more than the 126 MB L2"},
+            "e2e": {"value": round(tokens2 / (ms2 / 1e3), 1), "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "device_status": status,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------- CPU baseline / reference arm
+def cpu_decode_sample(args, cfg_name):
+    """Times the CPU restatement on a bounded sample of the same workload: one mini-batch of a few
+    sentences, beam 4, all host threads."""
+    from marian_dev_b200 import model
+    from oracle.decode_oracle import OracleTransformer, beam_search
+    from oracle.oracle import COracle
+    cfg = model.CONFIGS[cfg_name]
+    params = model.random_init(cfg, seed=0)
+    o = COracle()
+    cores = o.max_threads()
+    net = OracleTransformer(cfg, params, oracle=o, output_int8=True, threads=cores)
+    del params
+    corpus = model.synthetic_corpus(MINI_BATCH, cfg.vocab, seed=1, length_dist="normal", lo=4, hi=128, mean=30.0, std=12.0)
+    n = args.cpu_sentences
+    # a typical slice of the length-sorted batch (around the median length)
+    order = sorted(range(len(corpus)), key=lambda i: len(corpus[i]))
+    pick = [corpus[i] for i in order[len(order) // 2 - n // 2: len(order) // 2 - n // 2 + n]]
+    batches = model.make_batches(pick, n)
+    t0 = time.time()
+    tokens = 0
+    for _sid, ids, mask in batches:
+        for toks, _s in beam_search(net, ids, mask, beam=BEAM, max_length_factor=1.5, normalize=1.0):
+            tokens += len(toks)
+    dt = time.time() - t0
+    return tokens / dt, cores, f"{n} sentences of median length from one mini-batch, beam {BEAM}, {dt:.1f} s of CPU work"
+
+
+def cpu_baseline(args, cfg_name):
+    try:
+        v, cores, sample = cpu_decode_sample(args, cfg_name)
+        return {"value": round(v, 2), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+    except Exception as e:  # the baseline must not take the GPU line down with it
+        return {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    vals = []
+    cores, sample = 0, ""
+    t_all = time.time()
+    for i in range(args.warmup + args.steps):
+        v, cores, sample = cpu_decode_sample(args, args.model)
+        if i >= args.warmup:
+            vals.append(v)
+        if time.time() - t_all > 240 and vals:       # keep the whole arm within a few minutes
+            break
+    value = statistics.mean(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": len(vals),
+        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 (s8 x s8 -> s32), fp32 epilogue", "data": "synthetic (random-init weights, uniform token ids, seeded)",
+        "config": {"workload": WORKLOAD if args.model == "big" else f"{args.model} (debug workload)", "mini_batch": MINI_BATCH, "beam": BEAM,
+                   "note": "CPU restatement of the reference's intgemm8 path (the reference itself is unbuildable here: intgemm submodule absent)"},
+        "cpu_baseline": {"value": round(value, 2), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 2), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -208,3 +208,27 @@ def test_argument_errors(cuda_device):
     with pytest.raises(Mi8Error):
         ops.affine(torch.randn(4, 40, device=cuda_device), Wbad, None)
     _assert_healthy()
+
+
+def test_against_committed_golden_vectors(cuda_device):
+    """The GPU path must hash to the committed fixtures (tests/golden/affine_golden.json): quantised
+    weights and activations, both multipliers, the int32 accumulators and the fp32 outputs."""
+    import json
+    import os
+    from tests.golden.make_golden import cases, digest, inputs
+    ops = _ops()
+    want = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "affine_golden.json")))
+    for name, spec in cases().items():
+        a, w, bias = inputs(spec)
+        m, n = spec["m"], spec["n"]
+        b = ops.prepareB(torch.from_numpy(w).to(cuda_device))
+        aq = ops.prepareA(torch.from_numpy(a).to(cuda_device))
+        acc = torch.empty((m, n), dtype=torch.int32, device=cuda_device)
+        out = ops.multiply(aq, b, torch.from_numpy(bias).to(cuda_device) if bias is not None else None, spec["scale"],
+                           spec["relu"], acc_out=acc)
+        torch.cuda.synchronize()
+        got = {"bt": b.data.cpu().numpy(), "qb": b.quant_mult.cpu().numpy(), "aq": aq.data.cpu().numpy(),
+               "qa": aq.quant_mult.cpu().numpy(), "acc": acc.cpu().numpy(), "out": out.cpu().numpy()}
+        for key, arr in got.items():
+            assert digest(arr) == want[name]["sha256"][key], f"{name}: {key} differs from the committed fixture"
+    _assert_healthy()
