@@ -129,6 +129,23 @@ int mi8_affine_f32(const float* a, int M, int K, const int8_t* bt, const float* 
                    const float* bias, float scale, int relu, void* c, int out_dtype,
                    int8_t* aq_scratch, void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * mi8_multiply_i8 for callers that cannot allocate device memory and so have no workspace to pass:
+ * code running inside Marian's forward pass after the graph arena has taken the device memory
+ * (a cudaMalloc there can fail), or a serving thread that cannot tolerate cudaMalloc's device-wide
+ * synchronisation.  This entry point has no counterpart in the reference.
+ * The split-K scratch lives in a fixed array inside the library (about 2 MiB per GPU that loads the
+ * library, held until the process exits).  Shapes whose split-K plan needs more than 2 MiB of
+ * accumulation buffers are refused with MI8_ERR_WORKSPACE (use mi8_multiply_i8 for them).
+ * The first call made on a device resolves the array's device address; make that first call outside
+ * of any stream capture.  Every call shares the array and clears the part it uses first; calls that
+ * overlap on the device race on it, so keep them ordered on one stream.  Inputs, outputs and the
+ * meaning of the arguments are those of mi8_multiply_i8; nothing is allocated or freed.
+ */
+int mi8_multiply_i8_static(const int8_t* aq, const int8_t* bt, int M, int N, int K,
+                           const float* d_qa, const float* d_qb, float scale,
+                           const float* bias, int relu, void* c, int out_dtype, void* stream);
+
 /* How mi8_multiply_i8 would tile a problem on the current device:
  * out[0]=tile_m, out[1]=pipeline stages, out[2]=splits, out[3]=tiles along N, out[4]=tiles along M,
  * out[5]=CTAs launched, out[6]=dynamic shared memory bytes, out[7]=SM count. */
