@@ -104,41 +104,35 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- GEMM attribution
 class GemmTimer:
-    """Brackets every GEMM launch of the int8 engine with CUDA events on the launching stream, so the
-    dominant kernel's achieved bandwidth / throughput is measured inside the timed region."""
+    """Has the library bracket every GEMM launch with CUDA events on the launching stream
+    (mi8_profile_begin / mi8_profile_end), so the dominant kernel's achieved bandwidth / throughput is
+    measured inside the timed region."""
 
-    def __init__(self, ops_mod, torch_mod):
-        self.ops, self.torch = ops_mod, torch_mod
-        self.records = []   # (M, N, K, out_bytes, start, end)
-        self._orig = None
+    def __init__(self, capacity=200000):
+        self.capacity = capacity
+        self.records = []
 
     def __enter__(self):
-        self._orig = self.ops.multiply
-        torch = self.torch
-
-        def timed(aq, b, bias=None, scale=1.0, relu=False, out=None, out_dtype=torch.float32, **kw):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            r = self._orig(aq, b, bias, scale, relu, out=out, out_dtype=out_dtype, **kw)
-            e1.record()
-            self.records.append((aq.rows, b.rows, aq.cols, 4 if out_dtype == torch.float32 else 2, e0, e1))
-            return r
-
-        self.ops.multiply = timed
+        from marian_dev_b200.binding import check, lib
+        check(lib().mi8_profile_begin(self.capacity))
         return self
 
     def __exit__(self, *exc):
-        self.ops.multiply = self._orig
+        import ctypes
+        from marian_dev_b200.binding import Mi8GemmRecord, check, lib
+        buf = (Mi8GemmRecord * self.capacity)()
+        n = ctypes.c_int(0)
+        check(lib().mi8_profile_end(buf, self.capacity, ctypes.byref(n)))
+        self.records = [(r.M, r.N, r.K, r.out_bytes, r.us) for r in buf[:n.value]]
 
     def summary(self):
-        """Aggregate per shape class; call after a device synchronisation."""
+        """Aggregate per shape class."""
         total = {"launches": 0, "us": 0.0, "bytes": 0.0, "ops": 0.0}
         classes = {}
-        for (m, n, k, ob, e0, e1) in self.records:
-            us = e0.elapsed_time(e1) * 1000.0
+        for (m, n, k, ob, us) in self.records:
             by = m * k + n * k + 4 * n + ob * m * n + 8          # int8 A in, weights, bias, C out, two multipliers
             op = 2.0 * m * n * k
-            key = ("history K/V (M grows)" if m > 1024 and n == k else f"N={n},K={k}")
+            key = ("history K/V re-projection (M = rows x steps)" if m > 1024 and n == k else f"N={n},K={k}")
             c = classes.setdefault(key, {"launches": 0, "us": 0.0, "bytes": 0.0, "ops": 0.0})
             for d in (c, total):
                 d["launches"] += 1
@@ -171,7 +165,8 @@ def run_ours(args):
     per_rank = args.warmup + args.steps                          # both timed legs decode the same mini-batches
     batches = build_corpus(model, cfg, per_rank * world)
     mine = [batches[i] for i in range(rank, len(batches), world)][:per_rank]
-    search = decoder.BeamSearch(net, beam=BEAM, max_length_factor=1.5, normalize=1.0)
+    stepper = decoder.NativeStepper(net, max_batch=MINI_BATCH, beam=BEAM, max_src=136, max_steps=208)
+    search = decoder.BeamSearch(net, beam=BEAM, max_length_factor=1.5, normalize=1.0, native=stepper)
 
     def barrier():
         torch.cuda.synchronize()
@@ -205,7 +200,7 @@ def run_ours(args):
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with GemmTimer(ops, torch) as gt:
+    with GemmTimer() as gt:
         e0.record()
         for ids_t, mask_t in resident:
             res = search.search_device(ids_t, mask_t)

@@ -151,6 +151,17 @@ int mi8_multiply_i8_static(const int8_t* aq, const int8_t* bt, int M, int N, int
  * out[5]=CTAs launched, out[6]=dynamic shared memory bytes, out[7]=SM count. */
 int mi8_multiply_plan(int M, int N, int K, int force_tile_m, int force_splits, int out[8]);
 
+/* Measurement aid: between mi8_profile_begin and mi8_profile_end every GEMM launch made by the calling
+ * thread is bracketed by CUDA events on its stream; mi8_profile_end waits for them and returns one record
+ * per launch (at most `capacity`).  Off by default; costs two cudaEventRecord calls per launch when on. */
+typedef struct mi8_gemm_record {
+  int M, N, K;       /* problem size of the launch */
+  int out_bytes;     /* bytes per output element (4 or 2) */
+  float us;          /* device time between the two events, microseconds */
+} mi8_gemm_record;
+int mi8_profile_begin(int max_records);
+int mi8_profile_end(mi8_gemm_record* records, int capacity, int* count);
+
 /* Number of kernels this thread has launched through the library since the last reset. */
 unsigned long long mi8_launch_count(void);
 void mi8_launch_count_reset(void);

@@ -1,0 +1,106 @@
+/*
+ * marian_i8_decode.h - C ABI of the decoder-step driver built on the int8 affine engine.
+ *
+ * One call runs the encoder, or a whole time step of Marian's transformer decoder on the device: what
+ * DecoderTransformer::step builds as graph nodes (src/models/transformer.h:713-896) followed by the
+ * log-softmax and n-best selection of BeamSearch::search (src/translator/beam_search.cpp:431-496).
+ * Every affine goes through the int8 GEMM of marian_i8.h; the glue (embedding, LayerNorm, attention,
+ * history handling, top-k) are sm_100a kernels of this library.  The beam bookkeeping stays with the
+ * caller, exactly as in the reference: per step it uploads hypothesis indices / previous words /
+ * path scores and downloads the n-best lists.
+ *
+ * Memory: the caller owns everything.  It passes one arena (mi8d_arena_bytes) for activations and
+ * decoder state and one int8 workspace (mi8_workspace_bytes(0,0,0), zero-filled); parameters are
+ * registered by pointer under Marian's parameter names and must stay alive.
+ */
+#ifndef MARIAN_I8_DECODE_H_
+#define MARIAN_I8_DECODE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct mi8d_config {
+  int dim_emb, dim_ffn, heads, enc_depth, dec_depth, vocab;   /* enc_depth 0: the caller supplies the encoder context */
+  int ssru;        /* 0: self-attention decoder, 1: transformer-decoder-autoreg rnn with the SSRU cell */
+  int max_rows;    /* beam * batch upper bound */
+  int max_batch;   /* sentences per mini-batch upper bound */
+  int max_steps;   /* target positions upper bound */
+  int max_src;     /* source width upper bound */
+} mi8d_config;
+
+typedef struct mi8d_decoder mi8d_decoder;
+
+/* Device bytes the arena must hold for this configuration. */
+size_t mi8d_arena_bytes(const mi8d_config* cfg);
+/* Creates the (host-side) driver object over caller-owned device memory. */
+int mi8d_create(const mi8d_config* cfg, void* arena, size_t arena_bytes, void* workspace, size_t workspace_bytes,
+                mi8d_decoder** out);
+void mi8d_destroy(mi8d_decoder* d);
+
+/* Registers an intgemm8 parameter (Bt[N,K] int8 followed by its fp32 multiplier) under Marian's name,
+ * e.g. "decoder_l1_self_Wq"; "Wemb_intgemm8" is the quantised tied output matrix [vocab, dim_emb]. */
+int mi8d_set_weight(mi8d_decoder* d, const char* name, const int8_t* bt, int K, int N);
+/* Registers a float32 parameter (biases, LayerNorm scale/bias, "Wemb", "decoder_ff_logit_out_b"). */
+int mi8d_set_param(mi8d_decoder* d, const char* name, const float* p);
+/* Sinusoidal position table [max_steps, dim_emb] (src/tensors/gpu/tensor_operators.cu:793-817). */
+int mi8d_set_positions(mi8d_decoder* d, const float* table);
+
+/* Starts a mini-batch: encoder context [batch, src, dim_emb] fp32 and log mask [batch, src]
+ * ((1 - mask) * -99999999, src/models/transformer.h:138-143) are copied into the arena. */
+int mi8d_start(mi8d_decoder* d, const float* context, const float* log_mask, int batch, int src, void* stream);
+
+/* Runs the encoder on token ids [batch, src] (int32, device) with log mask [batch, src] and starts the
+ * mini-batch with its output as the context (EncoderTransformer::apply, src/models/transformer.h:581-637);
+ * needs enc_depth > 0 and the "encoder_l*" parameters registered. */
+int mi8d_encode(mi8d_decoder* d, const int* ids, const float* log_mask, int batch, int src, void* stream);
+
+/*
+ * One decoder time step for beam * batch hypotheses (rows beam-major: row = beamHypIdx * batch + batchIdx).
+ *   hyp_idx [beam*batch]    row of the previous step each hypothesis descends from   (NULL at the first step)
+ *   prev_words [beam*batch] word each hypothesis ended in                            (NULL at the first step)
+ *   batch_idx [batch]       previous-step batch positions of the sentences still active (NULL: unchanged)
+ *   prev_scores [beam*batch] path scores (-inf for dummy slots); NULL = 0
+ *   n_best                  candidates returned per sentence (Marian asks for the current beam width)
+ * Outputs (device): out_score / out_beam / out_word [batch, n_best], sorted by descending path score.
+ */
+int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const int* batch_idx, const float* prev_scores,
+              int beam, int batch, int n_best, float* out_score, int* out_beam, int* out_word, void* stream);
+
+/* ---- the glue kernels on their own (what the driver sequences), exported for tests and for hosts that
+ * build their own step.  All pointers are device pointers; `absmax_slot` is an optional 4-byte slot
+ * (zeroed by the caller) into which the kernel reduces max|out| for a following mi8g_quantize_slot. ---- */
+
+/* out[r,:] = wemb[words[r],:] * scale + pos[(pos_mod ? r % pos_mod : 0),:]; words NULL = zero embedding
+ * (embedding scaling and sinusoidal positions, src/models/transformer.h:93,110-114). */
+int mi8g_embed(const float* wemb, const int* words, const float* pos, int pos_mod, float scale, int rows, int dim,
+               float* out, float* rowmax, unsigned* absmax_slot, void* stream);
+/* out = gamma * (y - mean) / sqrt(var + eps) + beta with y = a + resid (resid may be NULL): the
+ * "dan" post-processing (src/models/transformer.h:189-214, src/layers/generic.h:248-253). */
+int mi8g_add_layernorm(const float* a, const float* resid, const float* gamma, const float* beta, float eps, int rows,
+                       int dim, float* out, float* rowmax, unsigned* absmax_slot, void* stream);
+/* Int8::PrepareA with the multiplier 127/max taken from an abs-max slot; writes the multiplier to d_quant_mult. */
+int mi8g_quantize_slot(const float* x, size_t n, const unsigned* absmax_slot, int8_t* q, float* d_quant_mult, void* stream);
+/* Single-query attention softmax(q.k/sqrt(dh) + mask).v (src/models/transformer.h:240-277); mode 0: decoder
+ * self-attention over a time-major history [len, rows, dim]; 1: cross-attention over [batch, len, dim] with
+ * rows beam-major; 2: encoder self-attention with rows ordered [batch, len]. */
+int mi8g_attention1(const float* q, const float* k, const float* v, const float* log_mask, int rows, int heads,
+                    int dim_head, int len, int batch, int mode, float* out, unsigned* absmax_slot, void* stream);
+/* cand_score[r][j] = (j-th largest logit of row r - logsumexp(row r)) + prev_scores[r], cand_word[r][j]; k <= 8
+ * (LogSoftmax + per-row part of the n-best search, src/translator/nth_element.cu:366-413). */
+int mi8g_lse_topk(const float* logits, int rows, int vocab, int k, const float* prev_scores, float* cand_score,
+                  int* cand_word, void* stream);
+/* Per sentence: the k best of its beam x k row candidates, sorted; ties to the smaller (beam, word) key. */
+int mi8g_nbest_merge(const float* cand_score, const int* cand_word, int beam, int batch, int vocab, int k,
+                     float* out_score, int* out_beam, int* out_word, void* stream);
+
+/* Pointer to the last step's logits [beam*batch, vocab] (device), for tests. */
+const float* mi8d_last_logits(const mi8d_decoder* d);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MARIAN_I8_DECODE_H_ */

@@ -15,13 +15,29 @@ LIB_PATH = os.path.join(_HERE, "libmarian_i8.so")
 
 MI8_F32, MI8_F16 = 0, 1
 
+class Mi8GemmRecord(ctypes.Structure):
+    """mi8_gemm_record of include/marian_i8.h."""
+    _fields_ = [("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("out_bytes", ctypes.c_int), ("us", ctypes.c_float)]
+
+
+class Mi8dConfig(ctypes.Structure):
+    """mi8d_config of include/marian_i8_decode.h."""
+    _fields_ = [(n, ctypes.c_int) for n in ("dim_emb", "dim_ffn", "heads", "enc_depth", "dec_depth", "vocab", "ssru", "max_rows",
+                                             "max_batch", "max_steps", "max_src")]
+
+
+# Every symbol include/marian_i8_decode.h declares.
+DECODE_EXPORTS = ["mi8d_arena_bytes", "mi8d_create", "mi8d_destroy", "mi8d_set_weight", "mi8d_set_param", "mi8d_set_positions",
+                  "mi8d_start", "mi8d_encode", "mi8d_step", "mi8d_last_logits",
+                  "mi8g_embed", "mi8g_add_layernorm", "mi8g_quantize_slot", "mi8g_attention1", "mi8g_lse_topk", "mi8g_nbest_merge"]
+
 # Every symbol include/marian_i8.h declares.
 EXPORTS = [
     "mi8_version", "mi8_strerror", "mi8_last_cuda_error", "mi8_last_cuda_error_string",
     "mi8_workspace_bytes", "mi8_workspace_init", "mi8_poll_status", "mi8_clear_status",
     "mi8_max_absolute_f32", "mi8_quantize_f32_i8", "mi8_prepare_a_f32", "mi8_prepare_b_f32",
     "mi8_multiply_i8", "mi8_multiply_i8_ex", "mi8_multiply_i8_static", "mi8_affine_f32", "mi8_multiply_plan",
-    "mi8_launch_count", "mi8_launch_count_reset",
+    "mi8_launch_count", "mi8_launch_count_reset", "mi8_profile_begin", "mi8_profile_end",
 ]
 
 
@@ -74,11 +90,40 @@ def lib() -> ctypes.CDLL:
     L.mi8_multiply_i8_static.restype = ci
     L.mi8_affine_f32.argtypes = [vp, ci, ci, vp, vp, ci, vp, cf, ci, vp, ci, vp, vp, sz, vp]
     L.mi8_multiply_plan.argtypes = [ci, ci, ci, ci, ci, ctypes.POINTER(ci * 8)]
+    L.mi8_profile_begin.argtypes = [ci]
+    L.mi8_profile_begin.restype = ci
+    L.mi8_profile_end.argtypes = [ctypes.POINTER(Mi8GemmRecord), ci, ctypes.POINTER(ci)]
+    L.mi8_profile_end.restype = ci
     L.mi8_launch_count.restype = ctypes.c_ulonglong
     L.mi8_launch_count_reset.restype = None
     for name in ("mi8_workspace_init", "mi8_poll_status", "mi8_clear_status", "mi8_max_absolute_f32",
                  "mi8_quantize_f32_i8", "mi8_prepare_a_f32", "mi8_prepare_b_f32", "mi8_multiply_i8",
                  "mi8_multiply_i8_ex", "mi8_affine_f32", "mi8_multiply_plan"):
+        getattr(L, name).restype = ci
+    cfgp = ctypes.POINTER(Mi8dConfig)
+    L.mi8d_arena_bytes.restype = sz
+    L.mi8d_arena_bytes.argtypes = [cfgp]
+    L.mi8d_create.argtypes = [cfgp, vp, sz, vp, sz, ctypes.POINTER(vp)]
+    L.mi8d_destroy.argtypes = [vp]
+    L.mi8d_destroy.restype = None
+    L.mi8d_set_weight.argtypes = [vp, ctypes.c_char_p, vp, ci, ci]
+    L.mi8d_set_param.argtypes = [vp, ctypes.c_char_p, vp]
+    L.mi8d_set_positions.argtypes = [vp, vp]
+    L.mi8d_start.argtypes = [vp, vp, vp, ci, ci, vp]
+    L.mi8d_encode.argtypes = [vp, vp, vp, ci, ci, vp]
+    L.mi8d_encode.restype = ci
+    L.mi8d_step.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, vp, vp, vp, vp]
+    L.mi8d_last_logits.argtypes = [vp]
+    L.mi8d_last_logits.restype = vp
+    L.mi8g_embed.argtypes = [vp, vp, vp, ci, cf, ci, ci, vp, vp, vp, vp]
+    L.mi8g_add_layernorm.argtypes = [vp, vp, vp, vp, cf, ci, ci, vp, vp, vp, vp]
+    L.mi8g_quantize_slot.argtypes = [vp, sz, vp, vp, vp, vp]
+    L.mi8g_attention1.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp, vp, vp]
+    L.mi8g_lse_topk.argtypes = [vp, ci, ci, ci, vp, vp, vp, vp]
+    L.mi8g_nbest_merge.argtypes = [vp, vp, ci, ci, ci, ci, vp, vp, vp, vp]
+    for name in ("mi8g_embed", "mi8g_add_layernorm", "mi8g_quantize_slot", "mi8g_attention1", "mi8g_lse_topk", "mi8g_nbest_merge"):
+        getattr(L, name).restype = ci
+    for name in ("mi8d_create", "mi8d_set_weight", "mi8d_set_param", "mi8d_set_positions", "mi8d_start", "mi8d_step"):
         getattr(L, name).restype = ci
     _lib = L
     return L

@@ -209,6 +209,9 @@ int mi8_affine_f32(const float* a, int M, int K, const int8_t* bt, const float* 
                      workspace_bytes, as_stream(stream), 0, 0);
 }
 
+int mi8_profile_begin(int max_records) { return profile_begin(max_records); }
+int mi8_profile_end(mi8_gemm_record* records, int capacity, int* count) { return profile_end(records, capacity, count); }
+
 int mi8_multiply_plan(int M, int N, int K, int force_tile_m, int force_splits, int out[8]) {
   if(out == nullptr)
     return MI8_ERR_BAD_ARG;

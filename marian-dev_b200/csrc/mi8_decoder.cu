@@ -1,0 +1,522 @@
+// Host-side driver of one decoder time step (declared in include/marian_i8_decode.h): sequences the
+// int8 affines and the glue kernels on one stream, with all buffers carved out of a caller-owned
+// arena.  Restates DecoderTransformer::step (src/models/transformer.h:713-896): per layer
+// self-attention over the re-projected history (or the SSRU cell), cross-attention over cached
+// encoder keys/values, the ReLU feed-forward block, each followed by residual add + LayerNorm
+// ("transformer-postprocess: dan"), then the tied output layer, log-softmax and n-best selection.
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/marian_i8_decode.h"
+#include "mi8_internal.h"
+
+namespace mi8 {
+namespace {
+
+struct Weight {
+  const int8_t* bt = nullptr;
+  int K = 0, N = 0;
+  const float* qm() const { return reinterpret_cast<const float*>(bt + static_cast<size_t>(K) * N); }
+};
+
+size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
+
+struct Arena {
+  uint8_t* base = nullptr;
+  size_t size = 0, used = 0;
+  template <typename T>
+  T* take(size_t count) {
+    size_t bytes = align_up(count * sizeof(T));
+    T* p = base ? reinterpret_cast<T*>(base + used) : nullptr;
+    used += bytes;
+    return p;
+  }
+};
+
+struct LayerBufs {
+  float* slab = nullptr;     // [max_steps][max_rows][d]   layer inputs (self-attention decoders)
+  float* rowmax = nullptr;   // [max_steps][max_rows]
+  float* cross_k = nullptr;  // [max_batch * max_src, d]
+  float* cross_v = nullptr;
+  float* cell[2] = {nullptr, nullptr};  // SSRU state, double-buffered [max_rows, d]
+};
+
+}  // namespace
+}  // namespace mi8
+
+using namespace mi8;
+
+struct mi8d_decoder {
+  mi8d_config cfg;
+  Arena arena;
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  std::unordered_map<std::string, Weight> weights;
+  std::unordered_map<std::string, const float*> params;
+  const float* positions = nullptr;
+
+  std::vector<LayerBufs> layers;
+  float* x_in = nullptr;                 // layer-0 input when there are no slabs (SSRU) and the final layer output
+  float* x_final = nullptr;
+  float *x1 = nullptr, *x2 = nullptr;    // after self / cross blocks
+  float *qbuf = nullptr, *abuf = nullptr, *obuf = nullptr, *hbuf = nullptr, *fbuf = nullptr;
+  float *kbuf = nullptr, *vbuf = nullptr;
+  int8_t *aq = nullptr, *hq = nullptr, *cq = nullptr;
+  float* logits = nullptr;
+  float* cand_score = nullptr;
+  int* cand_word = nullptr;
+  float* enc_x[2] = {nullptr, nullptr};
+  float *enc_q = nullptr, *enc_k = nullptr, *enc_v = nullptr, *enc_h = nullptr;
+  int8_t* enc_aq = nullptr;
+  float* context[2] = {nullptr, nullptr};
+  float* log_mask[2] = {nullptr, nullptr};
+  int* anc[2] = {nullptr, nullptr};
+  unsigned* slots = nullptr;
+  int n_slots = 0;
+
+  int t = 0, batch = 0, src = 0, ctx_cur = 0, anc_cur = 0, cell_cur = 0;
+  bool cross_valid = false;
+
+  // lays the arena out; with a null base it only measures
+  void layout() {
+    const mi8d_config& c = cfg;
+    const size_t d = c.dim_emb, f = c.dim_ffn, R = c.max_rows, T = c.max_steps, B = c.max_batch, S = c.max_src;
+    arena.used = 0;
+    layers.assign(c.dec_depth, LayerBufs());
+    for(auto& L : layers) {
+      if(!c.ssru) {
+        L.slab = arena.take<float>(T * R * d);
+        L.rowmax = arena.take<float>(T * R);
+      } else {
+        L.cell[0] = arena.take<float>(R * d);
+        L.cell[1] = arena.take<float>(R * d);
+      }
+      L.cross_k = arena.take<float>(B * S * d);
+      L.cross_v = arena.take<float>(B * S * d);
+    }
+    x_in = arena.take<float>(R * d);
+    x_final = arena.take<float>(R * d);
+    x1 = arena.take<float>(R * d);
+    x2 = arena.take<float>(R * d);
+    qbuf = arena.take<float>(R * d);
+    abuf = arena.take<float>(R * d);
+    obuf = arena.take<float>(R * d);
+    fbuf = arena.take<float>(R * d);
+    hbuf = arena.take<float>(R * f);
+    aq = arena.take<int8_t>(R * (f > d ? f : d) + 256);
+    if(!c.ssru) {
+      kbuf = arena.take<float>(T * R * d);
+      vbuf = arena.take<float>(T * R * d);
+      hq = arena.take<int8_t>(T * R * d + 256);
+      anc[0] = arena.take<int>(T * R);
+      anc[1] = arena.take<int>(T * R);
+    }
+    cq = arena.take<int8_t>(B * S * d + 256);
+    logits = arena.take<float>(R * static_cast<size_t>(c.vocab));
+    cand_score = arena.take<float>(R * 8);
+    cand_word = arena.take<int>(R * 8);
+    for(int i = 0; i < 2; ++i) {
+      context[i] = arena.take<float>(B * S * d);
+      log_mask[i] = arena.take<float>(B * S);
+    }
+    if(c.enc_depth > 0) {
+      const size_t M = B * S;
+      for(int i = 0; i < 2; ++i)
+        enc_x[i] = arena.take<float>(M * d);
+      enc_q = arena.take<float>(M * d);
+      enc_k = arena.take<float>(M * d);
+      enc_v = arena.take<float>(M * d);
+      enc_h = arena.take<float>(M * f);
+      enc_aq = arena.take<int8_t>(M * (f > d ? f : d) + 256);
+    }
+    n_slots = 8 * c.dec_depth + 8 + 4 * c.enc_depth;
+    slots = arena.take<unsigned>(n_slots);
+  }
+
+  const Weight* W(const std::string& name) const {
+    auto it = weights.find(name);
+    return it == weights.end() ? nullptr : &it->second;
+  }
+  const float* P(const std::string& name) const {
+    auto it = params.find(name);
+    return it == params.end() ? nullptr : it->second;
+  }
+};
+
+namespace {
+
+// aq (already quantised, multiplier behind the data) x weight -> c
+int gemm(mi8d_decoder* d, const int8_t* a, int M, const std::string& wname, const std::string& bname, bool relu, float* c,
+         cudaStream_t s, unsigned* absmax_out = nullptr) {
+  const Weight* w = d->W(wname);
+  if(w == nullptr)
+    return MI8_ERR_BAD_ARG;
+  const float* bias = nullptr;
+  if(!bname.empty()) {
+    bias = d->P(bname);
+    if(bias == nullptr)
+      return MI8_ERR_BAD_ARG;
+  }
+  const float* qa = reinterpret_cast<const float*>(a + static_cast<size_t>(M) * w->K);
+  return launch_gemm(a, w->bt, M, w->N, w->K, qa, w->qm(), 1.0f, bias, relu ? 1 : 0, c, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0,
+                     absmax_out);
+}
+
+int quant(mi8d_decoder* /*d*/, const float* x, size_t rows, size_t dim, const unsigned* slot, int8_t* q, cudaStream_t s) {
+  return launch_quantize_slot(x, rows * dim, slot, q, reinterpret_cast<float*>(q + rows * dim), s);
+}
+
+int add_ln(mi8d_decoder* d, const float* a, const float* resid, const std::string& prefix, int rows, float* out, float* rowmax,
+           unsigned* slot, cudaStream_t s) {
+  const float* g = d->P(prefix + "_ln_scale");
+  const float* b = d->P(prefix + "_ln_bias");
+  if(g == nullptr || b == nullptr)
+    return MI8_ERR_BAD_ARG;
+  return launch_add_layernorm(a, resid, g, b, 1e-6f, rows, d->cfg.dim_emb, out, rowmax, slot, s);
+}
+
+#define MI8D_TRY(expr)      \
+  do {                      \
+    int rc_ = (expr);       \
+    if(rc_ != MI8_OK)       \
+      return rc_;           \
+  } while(0)
+
+}  // namespace
+
+extern "C" {
+
+size_t mi8d_arena_bytes(const mi8d_config* cfg) {
+  if(cfg == nullptr)
+    return 0;
+  mi8d_decoder tmp;
+  tmp.cfg = *cfg;
+  tmp.layout();
+  return tmp.arena.used + 4096;
+}
+
+int mi8d_create(const mi8d_config* cfg, void* arena, size_t arena_bytes, void* workspace, size_t workspace_bytes,
+                mi8d_decoder** out) {
+  if(cfg == nullptr || arena == nullptr || out == nullptr || workspace == nullptr)
+    return MI8_ERR_BAD_ARG;
+  if(cfg->enc_depth < 0 || cfg->dim_emb % 16 != 0 || cfg->dim_ffn % 16 != 0 || cfg->heads <= 0 || cfg->dim_emb % cfg->heads != 0 || cfg->dec_depth <= 0 ||
+     cfg->max_rows <= 0 || cfg->max_steps <= 0 || cfg->max_batch <= 0 || cfg->max_src <= 0 || cfg->vocab <= 0)
+    return MI8_ERR_BAD_ARG;
+  const int dh = cfg->dim_emb / cfg->heads;
+  if(dh != 64 && dh != 32)
+    return MI8_ERR_UNSUPPORTED;
+  if(reinterpret_cast<uintptr_t>(arena) & 255u)
+    return MI8_ERR_MISALIGNED;
+  if(arena_bytes < mi8d_arena_bytes(cfg) || workspace_bytes < mi8_workspace_bytes(0, 0, 0))
+    return MI8_ERR_WORKSPACE;
+  mi8d_decoder* d = new mi8d_decoder();
+  d->cfg = *cfg;
+  d->arena.base = static_cast<uint8_t*>(arena);
+  d->arena.size = arena_bytes;
+  d->layout();
+  d->ws = workspace;
+  d->ws_bytes = workspace_bytes;
+  *out = d;
+  return MI8_OK;
+}
+
+void mi8d_destroy(mi8d_decoder* d) { delete d; }
+
+int mi8d_set_weight(mi8d_decoder* d, const char* name, const int8_t* bt, int K, int N) {
+  if(d == nullptr || name == nullptr || bt == nullptr || K <= 0 || N <= 0)
+    return MI8_ERR_BAD_ARG;
+  if(K % 16 != 0 || (reinterpret_cast<uintptr_t>(bt) & 15u))
+    return MI8_ERR_MISALIGNED;
+  Weight w;
+  w.bt = bt;
+  w.K = K;
+  w.N = N;
+  d->weights[name] = w;
+  return MI8_OK;
+}
+
+int mi8d_set_param(mi8d_decoder* d, const char* name, const float* p) {
+  if(d == nullptr || name == nullptr || p == nullptr)
+    return MI8_ERR_BAD_ARG;
+  d->params[name] = p;
+  return MI8_OK;
+}
+
+int mi8d_set_positions(mi8d_decoder* d, const float* table) {
+  if(d == nullptr || table == nullptr)
+    return MI8_ERR_BAD_ARG;
+  d->positions = table;
+  return MI8_OK;
+}
+
+const float* mi8d_last_logits(const mi8d_decoder* d) { return d ? d->logits : nullptr; }
+
+int mi8g_embed(const float* wemb, const int* words, const float* pos, int pos_mod, float scale, int rows, int dim, float* out,
+               float* rowmax, unsigned* absmax_slot, void* stream) {
+  return launch_embed(wemb, words, pos, pos_mod, scale, rows, dim, out, rowmax, absmax_slot, as_stream(stream));
+}
+int mi8g_add_layernorm(const float* a, const float* resid, const float* gamma, const float* beta, float eps, int rows, int dim,
+                       float* out, float* rowmax, unsigned* absmax_slot, void* stream) {
+  if(gamma == nullptr || beta == nullptr)
+    return MI8_ERR_BAD_ARG;
+  return launch_add_layernorm(a, resid, gamma, beta, eps, rows, dim, out, rowmax, absmax_slot, as_stream(stream));
+}
+int mi8g_quantize_slot(const float* x, size_t n, const unsigned* absmax_slot, int8_t* q, float* d_quant_mult, void* stream) {
+  return launch_quantize_slot(x, n, absmax_slot, q, d_quant_mult, as_stream(stream));
+}
+int mi8g_attention1(const float* q, const float* k, const float* v, const float* log_mask, int rows, int heads, int dim_head,
+                    int len, int batch, int mode, float* out, unsigned* absmax_slot, void* stream) {
+  if(q == nullptr || k == nullptr || v == nullptr || out == nullptr)
+    return MI8_ERR_BAD_ARG;
+  return launch_attention1(q, k, v, log_mask, rows, heads, dim_head, len, batch, mode, out, absmax_slot, as_stream(stream));
+}
+int mi8g_lse_topk(const float* logits, int rows, int vocab, int k, const float* prev_scores, float* cand_score, int* cand_word,
+                  void* stream) {
+  if(logits == nullptr || cand_score == nullptr || cand_word == nullptr)
+    return MI8_ERR_BAD_ARG;
+  return launch_lse_topk(logits, rows, vocab, k, prev_scores, cand_score, cand_word, as_stream(stream));
+}
+int mi8g_nbest_merge(const float* cand_score, const int* cand_word, int beam, int batch, int vocab, int k, float* out_score,
+                     int* out_beam, int* out_word, void* stream) {
+  if(cand_score == nullptr || cand_word == nullptr || out_score == nullptr || out_beam == nullptr || out_word == nullptr)
+    return MI8_ERR_BAD_ARG;
+  return launch_nbest_merge(cand_score, cand_word, beam, batch, vocab, k, out_score, out_beam, out_word, as_stream(stream));
+}
+
+int mi8d_start(mi8d_decoder* d, const float* context, const float* log_mask, int batch, int src, void* stream) {
+  if(d == nullptr || context == nullptr || log_mask == nullptr || batch <= 0 || src <= 0)
+    return MI8_ERR_BAD_ARG;
+  if(batch > d->cfg.max_batch || src > d->cfg.max_src)
+    return MI8_ERR_UNSUPPORTED;
+  cudaStream_t s = as_stream(stream);
+  const size_t dm = d->cfg.dim_emb;
+  cudaError_t e = cudaMemcpyAsync(d->context[0], context, sizeof(float) * batch * src * dm, cudaMemcpyDeviceToDevice, s);
+  if(e == cudaSuccess)
+    e = cudaMemcpyAsync(d->log_mask[0], log_mask, sizeof(float) * batch * src, cudaMemcpyDeviceToDevice, s);
+  if(e == cudaSuccess && d->cfg.ssru)
+    for(auto& L : d->layers)
+      if(e == cudaSuccess)
+        e = cudaMemsetAsync(L.cell[0], 0, sizeof(float) * static_cast<size_t>(batch) * dm, s);
+  if(e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return MI8_ERR_LAUNCH;
+  }
+  d->t = 0;
+  d->batch = batch;
+  d->src = src;
+  d->ctx_cur = 0;
+  d->anc_cur = 0;
+  d->cell_cur = 0;
+  d->cross_valid = false;
+  return MI8_OK;
+}
+
+int mi8d_encode(mi8d_decoder* d, const int* ids, const float* log_mask, int batch, int src, void* stream) {
+  if(d == nullptr || ids == nullptr || log_mask == nullptr || batch <= 0 || src <= 0)
+    return MI8_ERR_BAD_ARG;
+  const mi8d_config& c = d->cfg;
+  if(c.enc_depth <= 0 || batch > c.max_batch || src > c.max_src || src > c.max_steps)
+    return MI8_ERR_UNSUPPORTED;
+  if(d->positions == nullptr || d->P("Wemb") == nullptr)
+    return MI8_ERR_BAD_ARG;
+  cudaStream_t s = as_stream(stream);
+  const int dm = c.dim_emb, M = batch * src;
+  cudaError_t e = cudaMemsetAsync(d->slots, 0, sizeof(unsigned) * d->n_slots, s);
+  if(e == cudaSuccess)
+    e = cudaMemcpyAsync(d->log_mask[0], log_mask, sizeof(float) * batch * src, cudaMemcpyDeviceToDevice, s);
+  if(e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return MI8_ERR_LAUNCH;
+  }
+  unsigned* slot = d->slots;
+  auto next_slot = [&]() { return slot++; };
+  // embeddings * sqrt(d) + positions 0..src-1 (src/models/transformer.h:93,110-114)
+  float* x = d->enc_x[0];
+  unsigned* x_slot = next_slot();
+  MI8D_TRY(launch_embed(d->P("Wemb"), ids, d->positions, src, sqrtf(static_cast<float>(dm)), M, dm, x, nullptr, x_slot, s));
+  for(int l = 0; l < c.enc_depth; ++l) {
+    const std::string li = "encoder_l" + std::to_string(l + 1);
+    const std::string pre = li + "_self", ffn = li + "_ffn";
+    unsigned *sa = next_slot(), *s1 = next_slot(), *s3 = next_slot();
+    // q, keys and values are the same tensor: one quantisation serves the three projections
+    MI8D_TRY(launch_quantize_slot(x, static_cast<size_t>(M) * dm, x_slot, d->enc_aq, reinterpret_cast<float*>(d->enc_aq + static_cast<size_t>(M) * dm), s));
+    MI8D_TRY(gemm(d, d->enc_aq, M, pre + "_Wq", pre + "_bq", false, d->enc_q, s));
+    MI8D_TRY(gemm(d, d->enc_aq, M, pre + "_Wk", pre + "_bk", false, d->enc_k, s));
+    MI8D_TRY(gemm(d, d->enc_aq, M, pre + "_Wv", pre + "_bv", false, d->enc_v, s));
+    float* a = d->enc_x[1];   // attention output, then reused as x1
+    MI8D_TRY(launch_attention1(d->enc_q, d->enc_k, d->enc_v, d->log_mask[0], M, c.heads, dm / c.heads, src, batch, 2, a, sa, s));
+    MI8D_TRY(launch_quantize_slot(a, static_cast<size_t>(M) * dm, sa, d->enc_aq, reinterpret_cast<float*>(d->enc_aq + static_cast<size_t>(M) * dm), s));
+    MI8D_TRY(gemm(d, d->enc_aq, M, pre + "_Wo", pre + "_bo", false, d->enc_q, s));
+    MI8D_TRY(add_ln(d, d->enc_q, x, pre + "_Wo", M, a, nullptr, s1, s));                       // x1 = LN(Wo(a) + x)
+    MI8D_TRY(launch_quantize_slot(a, static_cast<size_t>(M) * dm, s1, d->enc_aq, reinterpret_cast<float*>(d->enc_aq + static_cast<size_t>(M) * dm), s));
+    MI8D_TRY(gemm(d, d->enc_aq, M, ffn + "_W1", ffn + "_b1", true, d->enc_h, s, s3));
+    MI8D_TRY(launch_quantize_slot(d->enc_h, static_cast<size_t>(M) * c.dim_ffn, s3, d->enc_aq,
+                                  reinterpret_cast<float*>(d->enc_aq + static_cast<size_t>(M) * c.dim_ffn), s));
+    MI8D_TRY(gemm(d, d->enc_aq, M, ffn + "_W2", ffn + "_b2", false, d->enc_q, s));
+    const bool last = l + 1 == c.enc_depth;
+    float* nx = last ? d->context[0] : x;                                                     // the last layer writes the context
+    x_slot = next_slot();
+    MI8D_TRY(add_ln(d, d->enc_q, a, ffn + "_ffn", M, nx, nullptr, x_slot, s));
+    x = nx;
+  }
+  if(c.ssru) {
+    for(auto& L : d->layers) {
+      e = cudaMemsetAsync(L.cell[0], 0, sizeof(float) * static_cast<size_t>(batch) * dm, s);
+      if(e != cudaSuccess) {
+        set_last_cuda_error(e);
+        return MI8_ERR_LAUNCH;
+      }
+    }
+  }
+  d->t = 0;
+  d->batch = batch;
+  d->src = src;
+  d->ctx_cur = 0;
+  d->anc_cur = 0;
+  d->cell_cur = 0;
+  d->cross_valid = false;
+  return MI8_OK;
+}
+
+int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const int* batch_idx, const float* prev_scores, int beam,
+              int batch, int n_best, float* out_score, int* out_beam, int* out_word, void* stream) {
+  if(d == nullptr || beam <= 0 || batch <= 0 || n_best <= 0 || n_best > 8 || out_score == nullptr || out_beam == nullptr ||
+     out_word == nullptr)
+    return MI8_ERR_BAD_ARG;
+  const mi8d_config& c = d->cfg;
+  const int t = d->t;
+  const int R = beam * batch;
+  if(R > c.max_rows || t >= c.max_steps || batch > d->batch)
+    return MI8_ERR_UNSUPPORTED;
+  if(t > 0 && (hyp_idx == nullptr || prev_words == nullptr))
+    return MI8_ERR_BAD_ARG;
+  if(t == 0 && beam != 1)
+    return MI8_ERR_BAD_ARG;
+  if(d->positions == nullptr || d->P("Wemb") == nullptr)
+    return MI8_ERR_BAD_ARG;
+  cudaStream_t s = as_stream(stream);
+  const int dm = c.dim_emb, S = d->src;
+  const size_t slab_stride = static_cast<size_t>(c.max_rows) * dm;
+
+  cudaError_t e = cudaMemsetAsync(d->slots, 0, sizeof(unsigned) * d->n_slots, s);
+  if(e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return MI8_ERR_LAUNCH;
+  }
+  unsigned* slot = d->slots;
+  auto next_slot = [&]() { return slot++; };
+
+  // sentences that finished leave the batch: compact the encoder context, recompute cross K/V
+  if(batch != d->batch) {
+    if(batch_idx == nullptr)
+      return MI8_ERR_BAD_ARG;
+    const int nxt = d->ctx_cur ^ 1;
+    MI8D_TRY(launch_gather_rows(d->context[d->ctx_cur], batch_idx, batch, S * dm, d->context[nxt], s));
+    MI8D_TRY(launch_gather_rows(d->log_mask[d->ctx_cur], batch_idx, batch, S, d->log_mask[nxt], s));
+    d->ctx_cur = nxt;
+    d->batch = batch;
+    d->cross_valid = false;
+  }
+  const float* ctx = d->context[d->ctx_cur];
+  const float* lmask = d->log_mask[d->ctx_cur];
+  if(!d->cross_valid) {
+    // one quantisation of the context serves the key and value projections of every layer
+    const size_t n = static_cast<size_t>(batch) * S * dm;
+    float* cq_tail = reinterpret_cast<float*>(d->cq + n);
+    MI8D_TRY(launch_max_absolute(ctx, n, nullptr, cq_tail, d->ws, d->ws_bytes, s));
+    MI8D_TRY(launch_quantize(ctx, n, cq_tail, d->cq, s));
+    for(int l = 0; l < c.dec_depth; ++l) {
+      const std::string pre = "decoder_l" + std::to_string(l + 1) + "_context";
+      MI8D_TRY(gemm(d, d->cq, batch * S, pre + "_Wk", pre + "_bk", false, d->layers[l].cross_k, s));
+      MI8D_TRY(gemm(d, d->cq, batch * S, pre + "_Wv", pre + "_bv", false, d->layers[l].cross_v, s));
+    }
+    d->cross_valid = true;
+  }
+
+  const int anc_new = d->anc_cur ^ 1;
+  if(!c.ssru)
+    MI8D_TRY(launch_ancestors_update(d->anc[d->anc_cur], d->anc[anc_new], hyp_idx, t, R, c.max_rows, s));
+
+  // layer-0 input: scaled embedding of the previous word (zero at the first step) + position t
+  float* x = c.ssru ? d->x_in : d->layers[0].slab + static_cast<size_t>(t) * slab_stride;
+  float* x_rowmax = c.ssru ? nullptr : d->layers[0].rowmax + static_cast<size_t>(t) * c.max_rows;
+  unsigned* x_slot = next_slot();
+  MI8D_TRY(launch_embed(d->P("Wemb"), t == 0 ? nullptr : prev_words, d->positions + static_cast<size_t>(t) * dm, 0,
+                        sqrtf(static_cast<float>(dm)), R, dm, x, x_rowmax, x_slot, s));
+
+  const int cell_new = d->cell_cur ^ 1;
+  for(int l = 0; l < c.dec_depth; ++l) {
+    LayerBufs& L = d->layers[l];
+    const std::string li = "decoder_l" + std::to_string(l + 1);
+    unsigned* s1 = next_slot();
+    if(c.ssru) {
+      const std::string pre = li + "_rnn";
+      MI8D_TRY(quant(d, x, R, dm, x_slot, d->aq, s));
+      MI8D_TRY(gemm(d, d->aq, R, pre + "_W", "", false, d->qbuf, s));        // dot(input, W)
+      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wf", pre + "_bf", false, d->fbuf, s));  // affine(input, Wf, bf)
+      MI8D_TRY(launch_ssru_cell(L.cell[d->cell_cur], t == 0 ? nullptr : hyp_idx, d->qbuf, d->fbuf, R, dm, L.cell[cell_new], d->abuf, s));
+      MI8D_TRY(add_ln(d, d->abuf, x, pre + "_ffn", R, d->x1, nullptr, s1, s));
+    } else {
+      const std::string pre = li + "_self";
+      unsigned* sh = next_slot();
+      unsigned* sa = next_slot();
+      MI8D_TRY(quant(d, x, R, dm, x_slot, d->aq, s));
+      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wq", pre + "_bq", false, d->qbuf, s));
+      // keys and values: the whole history, re-quantised with one multiplier, re-projected
+      const int steps = t + 1;
+      MI8D_TRY(launch_history_absmax(L.rowmax, d->anc[anc_new], steps, R, c.max_rows, sh, s));
+      MI8D_TRY(launch_history_quantize(L.slab, slab_stride, d->anc[anc_new], c.max_rows, steps, R, dm, sh, d->hq,
+                                       reinterpret_cast<float*>(d->hq + static_cast<size_t>(steps) * R * dm), s));
+      MI8D_TRY(gemm(d, d->hq, steps * R, pre + "_Wk", pre + "_bk", false, d->kbuf, s));
+      MI8D_TRY(gemm(d, d->hq, steps * R, pre + "_Wv", pre + "_bv", false, d->vbuf, s));
+      MI8D_TRY(launch_attention1(d->qbuf, d->kbuf, d->vbuf, nullptr, R, c.heads, dm / c.heads, steps, batch, 0, d->abuf, sa, s));
+      MI8D_TRY(quant(d, d->abuf, R, dm, sa, d->aq, s));
+      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wo", pre + "_bo", false, d->obuf, s));
+      MI8D_TRY(add_ln(d, d->obuf, x, pre + "_Wo", R, d->x1, nullptr, s1, s));
+    }
+    {
+      const std::string pre = li + "_context";
+      unsigned* sa = next_slot();
+      unsigned* s2 = next_slot();
+      MI8D_TRY(quant(d, d->x1, R, dm, s1, d->aq, s));
+      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wq", pre + "_bq", false, d->qbuf, s));
+      MI8D_TRY(launch_attention1(d->qbuf, L.cross_k, L.cross_v, lmask, R, c.heads, dm / c.heads, S, batch, 1, d->abuf, sa, s));
+      MI8D_TRY(quant(d, d->abuf, R, dm, sa, d->aq, s));
+      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wo", pre + "_bo", false, d->obuf, s));
+      MI8D_TRY(add_ln(d, d->obuf, d->x1, pre + "_Wo", R, d->x2, nullptr, s2, s));
+
+      const std::string ffn = li + "_ffn";
+      unsigned* s3 = next_slot();
+      MI8D_TRY(quant(d, d->x2, R, dm, s2, d->aq, s));
+      MI8D_TRY(gemm(d, d->aq, R, ffn + "_W1", ffn + "_b1", true, d->hbuf, s, s3));   // ReLU and max|h| fused in the write-back
+      MI8D_TRY(quant(d, d->hbuf, R, c.dim_ffn, s3, d->aq, s));
+      MI8D_TRY(gemm(d, d->aq, R, ffn + "_W2", ffn + "_b2", false, d->obuf, s));
+      // the block's output is the next layer's input: write it straight into that layer's history slab
+      const bool last = l + 1 == c.dec_depth;
+      float* nx = last ? d->x_final : (c.ssru ? d->x_in : d->layers[l + 1].slab + static_cast<size_t>(t) * slab_stride);
+      float* nx_rowmax = (last || c.ssru) ? nullptr : d->layers[l + 1].rowmax + static_cast<size_t>(t) * c.max_rows;
+      x_slot = next_slot();
+      MI8D_TRY(add_ln(d, d->obuf, d->x2, ffn + "_ffn", R, nx, nx_rowmax, x_slot, s));
+      x = nx;
+    }
+  }
+
+  // tied output layer, then log-softmax + n-best per sentence over beam x vocabulary
+  const float* out_b = d->P("decoder_ff_logit_out_b");
+  const Weight* wout = d->W("Wemb_intgemm8");
+  if(out_b == nullptr || wout == nullptr)
+    return MI8_ERR_BAD_ARG;
+  MI8D_TRY(quant(d, x, R, dm, x_slot, d->aq, s));
+  MI8D_TRY(gemm(d, d->aq, R, "Wemb_intgemm8", "decoder_ff_logit_out_b", false, d->logits, s));
+  MI8D_TRY(launch_lse_topk(d->logits, R, c.vocab, n_best, prev_scores, d->cand_score, d->cand_word, s));
+  MI8D_TRY(launch_nbest_merge(d->cand_score, d->cand_word, beam, batch, c.vocab, n_best, out_score, out_beam, out_word, s));
+
+  d->anc_cur = anc_new;
+  d->cell_cur = cell_new;
+  d->t = t + 1;
+  return MI8_OK;
+}
+
+}  // extern "C"

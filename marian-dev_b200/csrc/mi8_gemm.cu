@@ -19,6 +19,8 @@
 // epilogue of one tile overlap the MMAs of the next.  CTAs are persistent over a static schedule.
 #include <cuda_fp16.h>
 
+#include <vector>
+
 #include "mi8_internal.h"
 #include "mi8_ptx.cuh"
 
@@ -73,6 +75,7 @@ struct GemmParams {
   int32_t* acc_out;
   int32_t* partials;
   unsigned* tile_counters;
+  unsigned* absmax_out;
   int* status;
 };
 
@@ -288,6 +291,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           __threadfence();
       }
 
+      unsigned out_max = 0u;  // max|C| over what this thread writes, for the next affine's quantisation
       if(finalize && has_chunks) {
 #pragma unroll 1
         for(int c = group * (kChunkStep - 1); c < kChunks; c += kChunkStep) {
@@ -325,6 +329,12 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
               for(int j = 0; j < T::kChunk; ++j)
                 f[j] = f[j] > 0.0f ? f[j] : 0.0f;
             }
+            if(p.absmax_out != nullptr) {
+#pragma unroll
+              for(int j = 0; j < T::kChunk; ++j)
+                if(j < valid)
+                  out_max = max(out_max, __float_as_uint(f[j]) & 0x7fffffffu);
+            }
             if(p.acc_out != nullptr) {
               int32_t* dst = p.acc_out + base;
 #pragma unroll
@@ -353,6 +363,11 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             }
           }
         }
+      }
+      if(p.absmax_out != nullptr) {
+        out_max = __reduce_max_sync(0xffffffffu, out_max);
+        if(lane == 0 && out_max != 0u)
+          atomicMax(p.absmax_out, out_max);
       }
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before_sync();
@@ -419,6 +434,30 @@ int encode_kmajor_map(CUtensorMap* map, const int8_t* base, int rows, int K, int
   return r == CUDA_SUCCESS ? MI8_OK : MI8_ERR_DRIVER;
 }
 
+// Optional bracketing of every GEMM launch with CUDA events on the launching stream (mi8_profile_begin /
+// mi8_profile_end), so a benchmark can attribute device time to this kernel inside its timed region.
+struct ProfileRecord {
+  int M, N, K, out_bytes;
+  cudaEvent_t start, stop;
+};
+struct ProfileState {
+  bool on = false;
+  size_t capacity = 0;
+  std::vector<ProfileRecord> records;
+  std::vector<cudaEvent_t> pool;   // events are created once and reused
+  size_t pool_used = 0;
+  cudaEvent_t take() {
+    if(pool_used == pool.size()) {
+      cudaEvent_t e;
+      if(cudaEventCreate(&e) != cudaSuccess)
+        return nullptr;
+      pool.push_back(e);
+    }
+    return pool[pool_used++];
+  }
+};
+thread_local ProfileState t_profile;
+
 template <int TM>
 int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, const GemmPlan& plan, cudaStream_t stream) {
   static bool attr_set[64] = {};
@@ -433,12 +472,58 @@ int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p
     }
     attr_set[dev] = true;
   }
+  ProfileRecord rec{};
+  const bool profiled = t_profile.on && t_profile.records.size() < t_profile.capacity;
+  if(profiled) {
+    rec = ProfileRecord{p.M, p.N, p.K, p.out_f16 ? 2 : 4, t_profile.take(), t_profile.take()};
+    if(rec.start != nullptr && rec.stop != nullptr)
+      cudaEventRecord(rec.start, stream);
+  }
   mi8_gemm_kernel<TM><<<plan.grid, kThreads, smem, stream>>>(tw, ta, p);
+  if(profiled && rec.start != nullptr && rec.stop != nullptr) {
+    cudaEventRecord(rec.stop, stream);
+    t_profile.records.push_back(rec);
+  }
   count_launch();
   return check_launch();
 }
 
 }  // namespace
+
+int profile_begin(int max_records) {
+  if(max_records <= 0)
+    return MI8_ERR_BAD_ARG;
+  t_profile.on = true;
+  t_profile.capacity = static_cast<size_t>(max_records);
+  t_profile.records.clear();
+  t_profile.pool_used = 0;
+  return MI8_OK;
+}
+
+int profile_end(mi8_gemm_record* out, int capacity, int* count) {
+  t_profile.on = false;
+  int n = 0;
+  for(const ProfileRecord& r : t_profile.records) {
+    if(n >= capacity || out == nullptr)
+      break;
+    float ms = 0.f;
+    if(cudaEventSynchronize(r.stop) != cudaSuccess || cudaEventElapsedTime(&ms, r.start, r.stop) != cudaSuccess) {
+      cudaGetLastError();
+      continue;
+    }
+    out[n].M = r.M;
+    out[n].N = r.N;
+    out[n].K = r.K;
+    out[n].out_bytes = r.out_bytes;
+    out[n].us = ms * 1000.f;
+    ++n;
+  }
+  if(count != nullptr)
+    *count = n;
+  t_profile.records.clear();
+  t_profile.pool_used = 0;
+  return MI8_OK;
+}
 
 int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, GemmPlan* plan) {
   if(M <= 0 || N <= 0 || K <= 0)
@@ -496,7 +581,7 @@ int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, Gemm
 
 int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb, float scale,
                 const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* ws, size_t ws_bytes,
-                cudaStream_t stream, int force_tile_m, int force_splits) {
+                cudaStream_t stream, int force_tile_m, int force_splits, unsigned* absmax_out) {
   if(M < 0 || N <= 0 || K <= 0)
     return MI8_ERR_BAD_ARG;
   if(M == 0)
@@ -544,6 +629,7 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
   uint8_t* wsb = static_cast<uint8_t*>(ws);
   p.partials = wsb ? reinterpret_cast<int32_t*>(wsb + kWsOffPartials) : nullptr;
   p.tile_counters = wsb ? reinterpret_cast<unsigned*>(wsb + kWsOffTileCounters) : nullptr;
+  p.absmax_out = absmax_out;
   p.status = device_status_ptr();
   if(p.status == nullptr)
     return MI8_ERR_LAUNCH;

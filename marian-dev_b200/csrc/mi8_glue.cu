@@ -1,0 +1,652 @@
+// Decode-step glue kernels around the int8 affines: embedding + position, residual add + LayerNorm,
+// quantisation from a pre-reduced abs-max, single-query attention over a key/value history,
+// history bookkeeping for the per-step re-projection of self-attention keys/values, and the
+// log-softmax + top-k of the output layer.  All fp32, all HBM/latency-bound streaming kernels.
+//
+// Abs-max fusion: every producer of a tensor that is quantised next (embedding, LayerNorm, attention,
+// the ReLU GEMM) reduces max|x| on the fly into a 4-byte slot (unsigned bit pattern, atomicMax), so
+// the quantisation needs one launch instead of two.  Slots are zeroed once per step by the driver.
+#include <cfloat>
+
+#include "mi8_internal.h"
+#include "mi8_math.cuh"
+#include "mi8_ptx.cuh"
+
+namespace mi8 {
+namespace {
+
+constexpr int kRowThreads = 256;
+constexpr int kMaxVec = 4;  // float4 per thread: rows of up to 4096 floats
+
+__device__ __forceinline__ unsigned abs_bits(float v) { return __float_as_uint(v) & 0x7fffffffu; }
+
+__device__ __forceinline__ unsigned block_max_u(unsigned v, unsigned* red) {
+  v = __reduce_max_sync(0xffffffffu, v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if(lane == 0)
+    red[warp] = v;
+  __syncthreads();
+  unsigned t = 0u;
+#pragma unroll
+  for(int w = 0; w < kRowThreads / 32; ++w)
+    t = max(t, red[w]);
+  return t;
+}
+
+__device__ __forceinline__ unsigned max4u(unsigned m, const float4& v) {
+  return max(max(max(m, abs_bits(v.x)), max(abs_bits(v.y), abs_bits(v.z))), abs_bits(v.w));
+}
+
+// out[r,:] = wemb[words[r],:] * scale + pos[(pos_mod ? r % pos_mod : 0),:]
+// (words == nullptr: zero embedding, the start symbol; pos_mod = source width for the encoder, 0 for a decoder step)
+__global__ void __launch_bounds__(kRowThreads)
+embed_kernel(const float* __restrict__ wemb, const int* __restrict__ words, const float* __restrict__ pos, int pos_mod, float scale,
+             int dim, float* __restrict__ out, float* __restrict__ rowmax, unsigned* absmax_slot) {
+  __shared__ unsigned red[kRowThreads / 32];
+  const int r = blockIdx.x;
+  const float4* src = words ? reinterpret_cast<const float4*>(wemb + static_cast<size_t>(words[r]) * dim) : nullptr;
+  const float4* p4 = reinterpret_cast<const float4*>(pos + static_cast<size_t>(pos_mod ? r % pos_mod : 0) * dim);
+  float4* dst = reinterpret_cast<float4*>(out + static_cast<size_t>(r) * dim);
+  unsigned m = 0u;
+  for(int i = threadIdx.x; i < dim / 4; i += kRowThreads) {
+    float4 e = src ? __ldg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 p = __ldg(p4 + i);
+    float4 o;
+    o.x = __fadd_rn(__fmul_rn(e.x, scale), p.x);
+    o.y = __fadd_rn(__fmul_rn(e.y, scale), p.y);
+    o.z = __fadd_rn(__fmul_rn(e.z, scale), p.z);
+    o.w = __fadd_rn(__fmul_rn(e.w, scale), p.w);
+    dst[i] = o;
+    m = max4u(m, o);
+  }
+  m = block_max_u(m, red);
+  if(threadIdx.x == 0) {
+    if(rowmax)
+      rowmax[r] = __uint_as_float(m);
+    if(absmax_slot)
+      atomicMax(absmax_slot, m);
+  }
+}
+
+// out = LayerNorm(a + resid) * gamma + beta, one block of 256 threads per row; biased variance
+// (gamma * (x - mean) / sqrt(var + eps) + beta, src/tensors/cpu/tensor_operators.cpp:1087-1124).
+// Arithmetic order (all operations rounded to nearest, restated identically by the CPU checker):
+//   thread t owns the float4 chunks c = t + 256*j;  y = a + resid;
+//   s_t = sum_j ((y0 + y1) + (y2 + y3));  mean = block256_sum(s) / dim;
+//   q_t = sum_j fma(d0,d0, fma(d1,d1, fma(d2,d2, d3*d3))), d = y - mean;  var = block256_sum(q) / dim;
+//   out = ((y - mean) / sqrt(var + eps)) * gamma + beta.
+__global__ void __launch_bounds__(kRowThreads)
+add_layernorm_kernel(const float* __restrict__ a, const float* __restrict__ resid, const float* __restrict__ gamma,
+                     const float* __restrict__ beta, float eps, int dim, float* __restrict__ out, float* __restrict__ rowmax,
+                     unsigned* absmax_slot) {
+  __shared__ float redf[kRowThreads / 32];
+  __shared__ unsigned redu[kRowThreads / 32];
+  const int r = blockIdx.x;
+  const float4* a4 = reinterpret_cast<const float4*>(a + static_cast<size_t>(r) * dim);
+  const float4* r4 = resid ? reinterpret_cast<const float4*>(resid + static_cast<size_t>(r) * dim) : nullptr;
+  float4 v[kMaxVec];
+  float s = 0.f;
+#pragma unroll
+  for(int j = 0; j < kMaxVec; ++j) {
+    const int i = threadIdx.x + j * kRowThreads;
+    if(i < dim / 4) {
+      float4 x = a4[i];
+      if(r4) {
+        const float4 y = r4[i];
+        x.x = __fadd_rn(x.x, y.x); x.y = __fadd_rn(x.y, y.y); x.z = __fadd_rn(x.z, y.z); x.w = __fadd_rn(x.w, y.w);
+      }
+      v[j] = x;
+      s = __fadd_rn(s, __fadd_rn(__fadd_rn(x.x, x.y), __fadd_rn(x.z, x.w)));
+    }
+  }
+  const float mean = __fdiv_rn(block256_sum_det(s, redf), static_cast<float>(dim));
+  float q = 0.f;
+#pragma unroll
+  for(int j = 0; j < kMaxVec; ++j) {
+    const int i = threadIdx.x + j * kRowThreads;
+    if(i < dim / 4) {
+      const float dx = __fadd_rn(v[j].x, -mean), dy = __fadd_rn(v[j].y, -mean), dz = __fadd_rn(v[j].z, -mean), dw = __fadd_rn(v[j].w, -mean);
+      q = __fadd_rn(q, __fmaf_rn(dx, dx, __fmaf_rn(dy, dy, __fmaf_rn(dz, dz, __fmul_rn(dw, dw)))));
+    }
+  }
+  const float var = __fdiv_rn(block256_sum_det(q, redf), static_cast<float>(dim));
+  const float denom = __fsqrt_rn(__fadd_rn(var, eps));
+  const float4* g4 = reinterpret_cast<const float4*>(gamma);
+  const float4* b4 = reinterpret_cast<const float4*>(beta);
+  float4* o4 = reinterpret_cast<float4*>(out + static_cast<size_t>(r) * dim);
+  unsigned m = 0u;
+#pragma unroll
+  for(int j = 0; j < kMaxVec; ++j) {
+    const int i = threadIdx.x + j * kRowThreads;
+    if(i < dim / 4) {
+      const float4 g = __ldg(g4 + i), b = __ldg(b4 + i);
+      float4 o;
+      o.x = __fadd_rn(__fmul_rn(__fdiv_rn(__fadd_rn(v[j].x, -mean), denom), g.x), b.x);
+      o.y = __fadd_rn(__fmul_rn(__fdiv_rn(__fadd_rn(v[j].y, -mean), denom), g.y), b.y);
+      o.z = __fadd_rn(__fmul_rn(__fdiv_rn(__fadd_rn(v[j].z, -mean), denom), g.z), b.z);
+      o.w = __fadd_rn(__fmul_rn(__fdiv_rn(__fadd_rn(v[j].w, -mean), denom), g.w), b.w);
+      o4[i] = o;
+      m = max4u(m, o);
+    }
+  }
+  m = block_max_u(m, redu);
+  if(threadIdx.x == 0) {
+    if(rowmax)
+      rowmax[r] = __uint_as_float(m);
+    if(absmax_slot)
+      atomicMax(absmax_slot, m);
+  }
+}
+
+__device__ __forceinline__ int quantize_one(float v, float qm) {
+  int r = __float2int_rn(__fmul_rn(v, qm));
+  return max(-127, min(127, r));
+}
+__device__ __forceinline__ unsigned pack4(const float4& v, float qm) {
+  return (static_cast<unsigned>(quantize_one(v.x, qm)) & 0xffu) | ((static_cast<unsigned>(quantize_one(v.y, qm)) & 0xffu) << 8) |
+         ((static_cast<unsigned>(quantize_one(v.z, qm)) & 0xffu) << 16) | ((static_cast<unsigned>(quantize_one(v.w, qm)) & 0xffu) << 24);
+}
+__device__ __forceinline__ float quant_mult_from_bits(unsigned bits) {
+  return bits == 0u ? 1.0f : __fdiv_rn(127.0f, __uint_as_float(bits));
+}
+
+// Quantise with the multiplier derived from an abs-max slot that a producer kernel already reduced.
+// Optional row gather: source row of output row i is src_rows[i] (rows of `row_len` floats).
+__global__ void __launch_bounds__(256)
+quantize_slot_kernel(const float* __restrict__ x, size_t n, const unsigned* __restrict__ absmax_slot, int8_t* __restrict__ q,
+                     float* __restrict__ d_quant_mult, int* status) {
+  const unsigned bits = *absmax_slot;
+  const float qm = quant_mult_from_bits(bits);
+  if(blockIdx.x == 0 && threadIdx.x == 0) {
+    *d_quant_mult = qm;
+    if(bits >= 0x7f800000u)
+      atomicMax(status, static_cast<int>(kDevNonFinite));
+  }
+  const size_t n16 = n / 16;
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  uint4* q16 = reinterpret_cast<uint4*>(q);
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for(size_t i = tid; i < n16; i += stride) {
+    const float4 a = __ldg(x4 + 4 * i), b = __ldg(x4 + 4 * i + 1), c = __ldg(x4 + 4 * i + 2), d = __ldg(x4 + 4 * i + 3);
+    uint4 o;
+    o.x = pack4(a, qm); o.y = pack4(b, qm); o.z = pack4(c, qm); o.w = pack4(d, qm);
+    q16[i] = o;
+  }
+  for(size_t i = n16 * 16 + tid; i < n; i += stride)
+    q[i] = static_cast<int8_t>(quantize_one(x[i], qm));
+}
+
+// ---- self-attention history ------------------------------------------------------------------
+// The decoder re-projects keys/values from the whole history of layer inputs every step, quantised
+// with ONE multiplier over that history (src/models/transformer.h:401-417).  The history is kept as
+// per-step slabs slab[t'][row][dim] in the row order of step t', plus an ancestor table
+// anc[t'][r] = row of slab t' that current hypothesis r descends from, so a beam reorder only
+// rewrites the small table.  rowmax[t'][row] holds max|x| of each slab row.
+
+// anc_new[t'][r] = anc_old[t'][hyp[r]] (t' < t), anc_new[t][r] = r.
+__global__ void ancestors_update_kernel(const int* __restrict__ anc_old, int* __restrict__ anc_new, const int* __restrict__ hyp,
+                                        int t, int rows, int stride) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if(i >= (t + 1) * rows)
+    return;
+  const int tp = i / rows, r = i - tp * rows;
+  anc_new[tp * stride + r] = tp == t ? r : anc_old[tp * stride + hyp[r]];
+}
+
+// max over t' <= t, r < rows of rowmax[t'][anc[t'][r]] -> slot (single block).
+__global__ void __launch_bounds__(1024)
+history_absmax_kernel(const float* __restrict__ rowmax, const int* __restrict__ anc, int steps, int rows, int stride,
+                      unsigned* absmax_slot) {
+  __shared__ unsigned red[32];
+  unsigned m = 0u;
+  for(int i = threadIdx.x; i < steps * rows; i += blockDim.x) {
+    const int tp = i / rows, r = i - tp * rows;
+    m = max(m, abs_bits(rowmax[tp * stride + anc[tp * stride + r]]));
+  }
+  m = __reduce_max_sync(0xffffffffu, m);
+  if((threadIdx.x & 31) == 0)
+    red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if(threadIdx.x < 32) {
+    m = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0u;
+    m = __reduce_max_sync(0xffffffffu, m);
+    if(threadIdx.x == 0)
+      *absmax_slot = m;
+  }
+}
+
+// hq[(t' * rows + r), :] = quantise(slab[t'][anc[t'][r], :]) for t' < steps: one block per output row.
+__global__ void __launch_bounds__(128)
+history_quantize_kernel(const float* __restrict__ slabs, size_t slab_stride, const int* __restrict__ anc, int anc_stride, int rows,
+                        int dim, const unsigned* __restrict__ absmax_slot, int8_t* __restrict__ hq, float* __restrict__ d_quant_mult) {
+  const float qm = quant_mult_from_bits(*absmax_slot);
+  const int out_row = blockIdx.x;
+  const int tp = out_row / rows, r = out_row - tp * rows;
+  if(out_row == 0 && threadIdx.x == 0)
+    *d_quant_mult = qm;
+  const float4* src = reinterpret_cast<const float4*>(slabs + tp * slab_stride + static_cast<size_t>(anc[tp * anc_stride + r]) * dim);
+  uint4* dst = reinterpret_cast<uint4*>(hq + static_cast<size_t>(out_row) * dim);
+  for(int i = threadIdx.x; i < dim / 16; i += blockDim.x) {
+    const float4 a = __ldg(src + 4 * i), b = __ldg(src + 4 * i + 1), c = __ldg(src + 4 * i + 2), d = __ldg(src + 4 * i + 3);
+    uint4 o;
+    o.x = pack4(a, qm); o.y = pack4(b, qm); o.z = pack4(c, qm); o.w = pack4(d, qm);
+    dst[i] = o;
+  }
+}
+
+// ---- single-query attention --------------------------------------------------------------------
+// One block per query row, one warp per head (looping when there are more heads than warps).
+// Key/value row of position p for query row r is  kv_base(r) + p * kv_stride:
+//   mode 0, decoder self-attention over the time-major history:  base = r,              stride = rows
+//   mode 1, cross-attention over the context [batch, len, dim]:   base = (r % batch)*len, stride = 1, log mask row r % batch
+//   mode 2, encoder self-attention, rows ordered [batch, len]:    base = (r / len)*len,   stride = 1, log mask row r / len
+// softmax(q.k / sqrt(dh) + mask) . v in fp32 (src/models/transformer.h:240-277).
+// Arithmetic order per (row, head), restated identically by the CPU checker:
+//   s_p = fma-chain over i ascending of q_i * k_{p,i}, starting from 0;  s_p = s_p * scale;  s_p = s_p + mask_p
+//   mx = max_p s_p;  e_p = det_expf(s_p - mx)
+//   lane l accumulates e_p for p = l, l+32, ... in ascending order; sum = butterfly over the 32 lanes
+//   w_p = e_p / sum;  out_i = fma-chain over p ascending of w_p * v_{p,i}, starting from 0.
+template <int DH>
+__global__ void __launch_bounds__(256)
+attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                  const float* __restrict__ log_mask, int heads, int len, int rows, int batch, int mode, float scale,
+                  float* __restrict__ out, unsigned* absmax_slot) {
+  extern __shared__ float probs[];  // [warps][len]
+  const int r = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int dim = heads * DH;
+  const int group = mode == 1 ? r % batch : (mode == 2 ? r / len : 0);
+  const size_t base = mode == 0 ? static_cast<size_t>(r) : static_cast<size_t>(group) * len;
+  const size_t stride = mode == 0 ? static_cast<size_t>(rows) : 1;
+  const float* mask = (mode != 0 && log_mask) ? log_mask + static_cast<size_t>(group) * len : nullptr;
+  float* p = probs + warp * len;
+  unsigned m_abs = 0u;
+  constexpr int PER = DH / 32;
+  for(int h = warp; h < heads; h += warps) {
+    const float4* qh = reinterpret_cast<const float4*>(q + static_cast<size_t>(r) * dim + h * DH);
+    float4 qreg[DH / 4];
+#pragma unroll
+    for(int i = 0; i < DH / 4; ++i)
+      qreg[i] = __ldg(qh + i);
+    float mx = -FLT_MAX;
+    for(int pos = lane; pos < len; pos += 32) {
+      const float4* kr = reinterpret_cast<const float4*>(k + (base + pos * stride) * dim + h * DH);
+      float4 kk[DH / 4];
+#pragma unroll
+      for(int i = 0; i < DH / 4; ++i)
+        kk[i] = __ldg(kr + i);
+      float sc = 0.f;
+#pragma unroll
+      for(int i = 0; i < DH / 4; ++i) {
+        sc = __fmaf_rn(qreg[i].x, kk[i].x, sc);
+        sc = __fmaf_rn(qreg[i].y, kk[i].y, sc);
+        sc = __fmaf_rn(qreg[i].z, kk[i].z, sc);
+        sc = __fmaf_rn(qreg[i].w, kk[i].w, sc);
+      }
+      sc = __fmul_rn(sc, scale);
+      if(mask)
+        sc = __fadd_rn(sc, mask[pos]);
+      p[pos] = sc;
+      mx = fmaxf(mx, sc);
+    }
+#pragma unroll
+    for(int o = 16; o > 0; o >>= 1)
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float part = 0.f;
+    for(int pos = lane; pos < len; pos += 32) {
+      const float e = det_expf(__fadd_rn(p[pos], -mx));
+      p[pos] = e;
+      part = __fadd_rn(part, e);
+    }
+    const float sum = warp_sum_det(part);
+    for(int pos = lane; pos < len; pos += 32)
+      p[pos] = __fdiv_rn(p[pos], sum);
+    __syncwarp();
+    // weighted sum of values: a lane owns PER consecutive output elements; loads are issued eight
+    // positions ahead of the (strictly ordered) fma chain
+    float acc[PER];
+#pragma unroll
+    for(int i = 0; i < PER; ++i)
+      acc[i] = 0.f;
+    const float* vbase = v + base * dim + h * DH + lane * PER;
+    const size_t vstep = stride * dim;
+    int pos = 0;
+    for(; pos + 8 <= len; pos += 8) {
+      float vv[8][PER];
+#pragma unroll
+      for(int u = 0; u < 8; ++u)
+#pragma unroll
+        for(int i = 0; i < PER; ++i)
+          vv[u][i] = __ldg(vbase + (pos + u) * vstep + i);
+#pragma unroll
+      for(int u = 0; u < 8; ++u) {
+        const float w = p[pos + u];
+#pragma unroll
+        for(int i = 0; i < PER; ++i)
+          acc[i] = __fmaf_rn(w, vv[u][i], acc[i]);
+      }
+    }
+    for(; pos < len; ++pos) {
+      const float w = p[pos];
+#pragma unroll
+      for(int i = 0; i < PER; ++i)
+        acc[i] = __fmaf_rn(w, __ldg(vbase + pos * vstep + i), acc[i]);
+    }
+    float* o = out + static_cast<size_t>(r) * dim + h * DH + lane * PER;
+#pragma unroll
+    for(int i = 0; i < PER; ++i) {
+      o[i] = acc[i];
+      m_abs = max(m_abs, abs_bits(acc[i]));
+    }
+    __syncwarp();
+  }
+  if(absmax_slot) {
+    m_abs = __reduce_max_sync(0xffffffffu, m_abs);
+    if(lane == 0)
+      atomicMax(absmax_slot, m_abs);
+  }
+}
+
+// ---- output layer: log-softmax + per-row top-k --------------------------------------------------
+constexpr int kMaxK = 8;
+
+struct TopK {
+  float v[kMaxK];
+  int i[kMaxK];
+};
+
+// larger value first; ties: smaller index first
+__device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
+
+template <int K>
+__device__ __forceinline__ void topk_insert(TopK& t, float v, int idx) {
+  if(!better(v, idx, t.v[K - 1], t.i[K - 1]))
+    return;
+  t.v[K - 1] = v;
+  t.i[K - 1] = idx;
+  // bubble up with compile-time indices so the lists stay in registers
+#pragma unroll
+  for(int j = K - 1; j > 0; --j) {
+    if(better(t.v[j], t.i[j], t.v[j - 1], t.i[j - 1])) {
+      const float tv = t.v[j];
+      const int ti = t.i[j];
+      t.v[j] = t.v[j - 1];
+      t.i[j] = t.i[j - 1];
+      t.v[j - 1] = tv;
+      t.i[j - 1] = ti;
+    }
+  }
+}
+
+// One block per row: cand_score[r][j] = (j-th largest logit - logsumexp(row)) + prev_score[r], cand_word[r][j].
+template <int K>
+__global__ void __launch_bounds__(256)
+lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ prev_scores, float* __restrict__ cand_score,
+                int* __restrict__ cand_word) {
+  __shared__ float s_v[256 * K];
+  __shared__ int s_i[256 * K];
+  __shared__ float redf[8];
+  const int r = blockIdx.x;
+  const float* row = logits + static_cast<size_t>(r) * vocab;
+  TopK t;
+#pragma unroll
+  for(int j = 0; j < K; ++j) {
+    t.v[j] = -FLT_MAX;
+    t.i[j] = 0x7fffffff;
+  }
+  float mx = -FLT_MAX;
+  for(int i = threadIdx.x; i < vocab; i += 256) {
+    const float x = row[i];
+    mx = fmaxf(mx, x);
+    topk_insert<K>(t, x, i);
+  }
+  for(int o = 16; o > 0; o >>= 1)
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if((threadIdx.x & 31) == 0)
+    redf[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = redf[0];
+#pragma unroll
+  for(int w = 1; w < 8; ++w)
+    mx = fmaxf(mx, redf[w]);
+  // log-sum-exp in a fixed order: thread t adds det_expf(x_i - mx) for i = t, t+256, ... ascending,
+  // then the deterministic block sum; lse = mx + det_logf(sum)
+  float sum = 0.f;
+  for(int i = threadIdx.x; i < vocab; i += 256)
+    sum = __fadd_rn(sum, det_expf(__fadd_rn(row[i], -mx)));
+  sum = block256_sum_det(sum, redf);
+  const float lse = __fadd_rn(mx, det_logf(sum));
+#pragma unroll
+  for(int j = 0; j < K; ++j) {
+    s_v[threadIdx.x * K + j] = t.v[j];
+    s_i[threadIdx.x * K + j] = t.i[j];
+  }
+  __syncthreads();
+  // tree merge of the per-thread sorted lists
+  for(int active = 128; active >= 1; active >>= 1) {
+    if(threadIdx.x < active) {
+      TopK a;
+#pragma unroll
+      for(int j = 0; j < K; ++j) {
+        a.v[j] = s_v[threadIdx.x * K + j];
+        a.i[j] = s_i[threadIdx.x * K + j];
+      }
+#pragma unroll
+      for(int j = 0; j < K; ++j)
+        topk_insert<K>(a, s_v[(threadIdx.x + active) * K + j], s_i[(threadIdx.x + active) * K + j]);
+#pragma unroll
+      for(int j = 0; j < K; ++j) {
+        s_v[threadIdx.x * K + j] = a.v[j];
+        s_i[threadIdx.x * K + j] = a.i[j];
+      }
+    }
+    __syncthreads();
+  }
+  if(threadIdx.x < K) {
+    const float ps = prev_scores ? prev_scores[r] : 0.f;
+    cand_score[r * K + threadIdx.x] = __fadd_rn(__fadd_rn(s_v[threadIdx.x], -lse), ps);
+    cand_word[r * K + threadIdx.x] = s_i[threadIdx.x];
+  }
+}
+
+// Per sentence b: merge the beam x K row candidates (rows beam-major: row = j * batch + b) into the
+// K best, sorted; key order on ties = (beam j, rank) ascending, i.e. smaller flattened key first.
+// out_score[b][n], out_beam[b][n], out_word[b][n].
+template <int K>
+__global__ void nbest_merge_kernel(const float* __restrict__ cand_score, const int* __restrict__ cand_word, int beam, int batch,
+                                   int vocab, float* __restrict__ out_score, int* __restrict__ out_beam, int* __restrict__ out_word) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if(b >= batch)
+    return;
+  TopK t;
+#pragma unroll
+  for(int j = 0; j < K; ++j) {
+    t.v[j] = -FLT_MAX;
+    t.i[j] = 0x7fffffff;
+  }
+  for(int j = 0; j < beam; ++j) {
+    const int row = j * batch + b;
+    for(int c = 0; c < K; ++c) {
+      const float s = cand_score[row * K + c];
+      const int key = j * vocab + cand_word[row * K + c];  // the reference's flattened (beam, word) key
+      // -inf candidates (dummy hypotheses) must stay behind every real one but keep a defined order
+      topk_insert<K>(t, s == -INFINITY ? -FLT_MAX : s, key);
+    }
+  }
+#pragma unroll
+  for(int n = 0; n < K; ++n) {
+    const bool valid = t.i[n] != 0x7fffffff && t.v[n] > -FLT_MAX;
+    out_score[b * K + n] = valid ? t.v[n] : -INFINITY;
+    out_beam[b * K + n] = valid ? t.i[n] / vocab : 0;
+    out_word[b * K + n] = valid ? t.i[n] % vocab : 0;
+  }
+}
+
+// rows gather: out[i,:] = in[idx[i],:]  (16-byte copies when the row length allows it)
+__global__ void gather_rows_kernel(const float* __restrict__ in, const int* __restrict__ idx, int dim, float* __restrict__ out) {
+  const int r = blockIdx.x;
+  const float* src = in + static_cast<size_t>(idx[r]) * dim;
+  float* dst = out + static_cast<size_t>(r) * dim;
+  if((dim & 3) == 0) {
+    const float4* s4 = reinterpret_cast<const float4*>(src);
+    float4* d4 = reinterpret_cast<float4*>(dst);
+    for(int i = threadIdx.x; i < dim / 4; i += blockDim.x)
+      d4[i] = __ldg(s4 + i);
+  } else {
+    for(int i = threadIdx.x; i < dim; i += blockDim.x)
+      dst[i] = __ldg(src + i);
+  }
+}
+
+// SSRU cell (src/rnn/cells.h:1052-1066): c' = c[hyp] * sigmoid(f) + x * (1 - sigmoid(f)); h = relu(c').
+// Writes the new cell state and y = LayerNorm(h + resid) * gamma + beta is done by add_layernorm on h.
+__global__ void ssru_cell_kernel(const float* __restrict__ cell_old, const int* __restrict__ hyp, const float* __restrict__ xw,
+                                 const float* __restrict__ f, int dim, float* __restrict__ cell_new, float* __restrict__ h_out) {
+  const int r = blockIdx.x;
+  const float* c = cell_old + static_cast<size_t>(hyp ? hyp[r] : r) * dim;
+  for(int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const size_t o = static_cast<size_t>(r) * dim + i;
+    // sigmoid and highway with every rounding explicit: sig = 1 / (1 + det_expf(-f));
+    // c' = fma(x, 1 - sig, c * sig)
+    const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, det_expf(-f[o])));
+    const float cn = __fmaf_rn(xw[o], __fadd_rn(1.0f, -sig), __fmul_rn(c[i], sig));
+    cell_new[o] = cn;
+    h_out[o] = cn > 0.f ? cn : 0.f;
+  }
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------ launchers
+int launch_embed(const float* wemb, const int* words, const float* pos, int pos_mod, float scale, int rows, int dim, float* out,
+                 float* rowmax, unsigned* slot, cudaStream_t s) {
+  if(rows <= 0 || dim <= 0 || dim % 4 != 0 || dim > kRowThreads * 4 * kMaxVec || out == nullptr || pos == nullptr)
+    return MI8_ERR_BAD_ARG;
+  embed_kernel<<<rows, kRowThreads, 0, s>>>(wemb, words, pos, pos_mod, scale, dim, out, rowmax, slot);
+  count_launch();
+  return check_launch();
+}
+
+int launch_add_layernorm(const float* a, const float* resid, const float* gamma, const float* beta, float eps, int rows, int dim,
+                         float* out, float* rowmax, unsigned* slot, cudaStream_t s) {
+  if(rows <= 0 || dim <= 0 || dim % 4 != 0 || dim > kRowThreads * 4 * kMaxVec || a == nullptr || out == nullptr)
+    return MI8_ERR_BAD_ARG;
+  add_layernorm_kernel<<<rows, kRowThreads, 0, s>>>(a, resid, gamma, beta, eps, dim, out, rowmax, slot);
+  count_launch();
+  return check_launch();
+}
+
+int launch_quantize_slot(const float* x, size_t n, const unsigned* slot, int8_t* q, float* d_qm, cudaStream_t s) {
+  if(x == nullptr || q == nullptr || slot == nullptr || d_qm == nullptr || n == 0)
+    return MI8_ERR_BAD_ARG;
+  if((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(q) & 15u))
+    return MI8_ERR_MISALIGNED;
+  int* status = device_status_ptr();
+  if(status == nullptr)
+    return MI8_ERR_LAUNCH;
+  size_t blocks = (n / 16 + 255) / 256;
+  const size_t cap = static_cast<size_t>(sm_count()) * 8;
+  blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
+  quantize_slot_kernel<<<static_cast<int>(blocks), 256, 0, s>>>(x, n, slot, q, d_qm, status);
+  count_launch();
+  return check_launch();
+}
+
+int launch_ancestors_update(const int* anc_old, int* anc_new, const int* hyp, int t, int rows, int stride, cudaStream_t s) {
+  const int n = (t + 1) * rows;
+  ancestors_update_kernel<<<(n + 255) / 256, 256, 0, s>>>(anc_old, anc_new, hyp, t, rows, stride);
+  count_launch();
+  return check_launch();
+}
+
+int launch_history_absmax(const float* rowmax, const int* anc, int steps, int rows, int stride, unsigned* slot, cudaStream_t s) {
+  history_absmax_kernel<<<1, 1024, 0, s>>>(rowmax, anc, steps, rows, stride, slot);
+  count_launch();
+  return check_launch();
+}
+
+int launch_history_quantize(const float* slabs, size_t slab_stride, const int* anc, int anc_stride, int steps, int rows, int dim,
+                            const unsigned* slot, int8_t* hq, float* d_qm, cudaStream_t s) {
+  if(dim % 16 != 0)
+    return MI8_ERR_MISALIGNED;
+  history_quantize_kernel<<<steps * rows, 128, 0, s>>>(slabs, slab_stride, anc, anc_stride, rows, dim, slot, hq, d_qm);
+  count_launch();
+  return check_launch();
+}
+
+int launch_attention1(const float* q, const float* k, const float* v, const float* log_mask, int rows, int heads, int dim_head,
+                      int len, int batch, int mode, float* out, unsigned* slot, cudaStream_t s) {
+  if(rows <= 0 || heads <= 0 || len <= 0)
+    return MI8_ERR_BAD_ARG;
+  if(mode < 0 || mode > 2)
+    return MI8_ERR_BAD_ARG;
+  const float scale = 1.0f / sqrtf(static_cast<float>(dim_head));
+  const int warps = heads < 8 ? heads : 8;
+  const size_t smem = static_cast<size_t>(warps) * len * sizeof(float);
+  if(smem > 48 * 1024)
+    return MI8_ERR_UNSUPPORTED;
+  if(dim_head == 64)
+    attention1_kernel<64><<<rows, warps * 32, smem, s>>>(q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
+  else if(dim_head == 32)
+    attention1_kernel<32><<<rows, warps * 32, smem, s>>>(q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
+  else
+    return MI8_ERR_UNSUPPORTED;
+  count_launch();
+  return check_launch();
+}
+
+int launch_lse_topk(const float* logits, int rows, int vocab, int k, const float* prev_scores, float* cand_score, int* cand_word,
+                    cudaStream_t s) {
+  if(rows <= 0 || vocab <= 0 || k < 1 || k > kMaxK)
+    return MI8_ERR_BAD_ARG;
+  switch(k) {
+    case 1: lse_topk_kernel<1><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 2: lse_topk_kernel<2><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 3: lse_topk_kernel<3><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 4: lse_topk_kernel<4><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 5: lse_topk_kernel<5><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 6: lse_topk_kernel<6><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 7: lse_topk_kernel<7><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
+    default: lse_topk_kernel<8><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
+  }
+  count_launch();
+  return check_launch();
+}
+
+int launch_nbest_merge(const float* cand_score, const int* cand_word, int beam, int batch, int vocab, int k, float* out_score,
+                       int* out_beam, int* out_word, cudaStream_t s) {
+  if(k < 1 || k > kMaxK || beam < 1 || batch < 1)
+    return MI8_ERR_BAD_ARG;
+  const int blocks = (batch + 127) / 128;
+  switch(k) {
+    case 1: nbest_merge_kernel<1><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 2: nbest_merge_kernel<2><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 3: nbest_merge_kernel<3><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 4: nbest_merge_kernel<4><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 5: nbest_merge_kernel<5><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 6: nbest_merge_kernel<6><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 7: nbest_merge_kernel<7><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    default: nbest_merge_kernel<8><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+  }
+  count_launch();
+  return check_launch();
+}
+
+int launch_gather_rows(const float* in, const int* idx, int rows, int dim, float* out, cudaStream_t s) {
+  if(rows <= 0 || dim <= 0)
+    return MI8_ERR_BAD_ARG;
+  gather_rows_kernel<<<rows, 128, 0, s>>>(in, idx, dim, out);
+  count_launch();
+  return check_launch();
+}
+
+int launch_ssru_cell(const float* cell_old, const int* hyp, const float* xw, const float* f, int rows, int dim, float* cell_new,
+                     float* h_out, cudaStream_t s) {
+  ssru_cell_kernel<<<rows, 256, 0, s>>>(cell_old, hyp, xw, f, dim, cell_new, h_out);
+  count_launch();
+  return check_launch();
+}
+
+}  // namespace mi8

@@ -49,6 +49,9 @@ struct GemmPlan {
 };
 int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, GemmPlan* plan);
 
+int profile_begin(int max_records);
+int profile_end(mi8_gemm_record* out, int capacity, int* count);
+
 // quantisation kernels (mi8_quant.cu)
 int launch_max_absolute(const float* x, size_t n, float* d_absmax, float* d_quant_mult, void* ws, size_t ws_bytes,
                         cudaStream_t stream);
@@ -56,9 +59,31 @@ int launch_quantize(const float* x, size_t n, const float* d_quant_mult, int8_t*
 int launch_transpose_quantize(const float* w, int K, int N, const float* d_quant_mult, int8_t* bt, cudaStream_t stream);
 
 // GEMM (mi8_gemm.cu)
+// absmax_out (optional): 4-byte slot that receives max|C| (unsigned bit pattern, atomicMax) for the
+// quantisation of C as the next affine's input.
 int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb, float scale,
                 const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* ws, size_t ws_bytes,
-                cudaStream_t stream, int force_tile_m, int force_splits);
+                cudaStream_t stream, int force_tile_m, int force_splits, unsigned* absmax_out = nullptr);
+
+// decode-step glue (mi8_glue.cu)
+int launch_embed(const float* wemb, const int* words, const float* pos, int pos_mod, float scale, int rows, int dim, float* out,
+                 float* rowmax, unsigned* slot, cudaStream_t s);
+int launch_add_layernorm(const float* a, const float* resid, const float* gamma, const float* beta, float eps, int rows, int dim,
+                         float* out, float* rowmax, unsigned* slot, cudaStream_t s);
+int launch_quantize_slot(const float* x, size_t n, const unsigned* slot, int8_t* q, float* d_qm, cudaStream_t s);
+int launch_ancestors_update(const int* anc_old, int* anc_new, const int* hyp, int t, int rows, int stride, cudaStream_t s);
+int launch_history_absmax(const float* rowmax, const int* anc, int steps, int rows, int stride, unsigned* slot, cudaStream_t s);
+int launch_history_quantize(const float* slabs, size_t slab_stride, const int* anc, int anc_stride, int steps, int rows, int dim,
+                            const unsigned* slot, int8_t* hq, float* d_qm, cudaStream_t s);
+int launch_attention1(const float* q, const float* k, const float* v, const float* log_mask, int rows, int heads, int dim_head,
+                      int len, int batch, int mode, float* out, unsigned* slot, cudaStream_t s);
+int launch_lse_topk(const float* logits, int rows, int vocab, int k, const float* prev_scores, float* cand_score, int* cand_word,
+                    cudaStream_t s);
+int launch_nbest_merge(const float* cand_score, const int* cand_word, int beam, int batch, int vocab, int k, float* out_score,
+                       int* out_beam, int* out_word, cudaStream_t s);
+int launch_gather_rows(const float* in, const int* idx, int rows, int dim, float* out, cudaStream_t s);
+int launch_ssru_cell(const float* cell_old, const int* hyp, const float* xw, const float* f, int rows, int dim, float* cell_new,
+                     float* h_out, cudaStream_t s);
 
 inline cudaStream_t as_stream(void* s) { return s ? reinterpret_cast<cudaStream_t>(s) : cudaStreamPerThread; }
 

@@ -19,7 +19,7 @@ import torch
 import torch.nn.functional as F
 
 from . import ops
-from .model import TransformerConfig, is_intgemm_param
+from .model import TransformerConfig, is_intgemm_param, sinusoidal_table
 
 NEG_MASK = -99999999.0  # transposedLogMask (transformer.h:138-143)
 
@@ -203,12 +203,99 @@ class Int8Transformer:
         return torch.addmm(out_b, x, self.wemb.t())
 
 
+class NativeStepper:
+    """The decoder time step as ONE call into the C++ driver (include/marian_i8_decode.h): all glue
+    kernels and affines of a step are launched from native code, the caller only exchanges the small
+    per-step index / n-best arrays.  Device memory (arena, outputs) is allocated here, once."""
+
+    def __init__(self, model: "Int8Transformer", max_batch: int = 128, beam: int = 4, max_src: int = 136, max_steps: int = 208):
+        import ctypes
+        from .binding import Mi8dConfig, check, lib
+        if not model.output_int8:
+            raise ops.Mi8Error(3, "the native step driver runs the tied output layer in int8")
+        self.m, self.L, self.check = model, lib(), check
+        cfg = model.cfg
+        max_steps = max(max_steps, max_src)        # the position table also serves the encoder
+        self.cfg = Mi8dConfig(cfg.dim_emb, cfg.dim_ffn, cfg.heads, cfg.enc_depth, cfg.dec_depth, cfg.vocab,
+                              int(cfg.decoder_autoreg == "rnn"), max_batch * beam, max_batch, max_steps, max_src)
+        dev = model.device
+        nbytes = int(self.L.mi8d_arena_bytes(ctypes.byref(self.cfg)))
+        self.arena = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        handle = ctypes.c_void_p()
+        check(self.L.mi8d_create(ctypes.byref(self.cfg), self.arena.data_ptr(), nbytes, model.ws.ptr, model.ws.nbytes,
+                                 ctypes.byref(handle)))
+        self.h = handle
+        for name, w in model.w.items():
+            check(self.L.mi8d_set_weight(self.h, name.encode(), w.data.data_ptr(), w.cols, w.rows))
+        check(self.L.mi8d_set_weight(self.h, b"Wemb_intgemm8", model.wemb_q.data.data_ptr(), model.wemb_q.cols, model.wemb_q.rows))
+        for name, p in model.p.items():
+            check(self.L.mi8d_set_param(self.h, name.encode(), p.data_ptr()))
+        self.pos = torch.from_numpy(sinusoidal_table(max_steps, cfg.dim_emb)).to(dev)
+        check(self.L.mi8d_set_positions(self.h, self.pos.data_ptr()))
+        self.max_batch, self.max_steps, self.max_src = max_batch, max_steps, max_src
+        self.out = torch.empty(3, max_batch * 8, dtype=torch.int32, device=dev)       # score bits, beam, word
+        self.host_out = torch.empty(3, max_batch * 8, dtype=torch.int32).pin_memory()
+        self.ctrl = torch.empty(3 * max_batch * beam + max_batch, dtype=torch.int32, device=dev)
+        self.host_ctrl = torch.empty(3 * max_batch * beam + max_batch, dtype=torch.int32).pin_memory()
+
+    def __del__(self):
+        try:
+            self.L.mi8d_destroy(self.h)
+        except Exception:
+            pass
+
+    def encode(self, ids_t: torch.Tensor, mask_t: torch.Tensor):
+        """Encoder forward on the device (ids int64/int32 [B,S], mask float [B,S]) and start of the mini-batch."""
+        B, S = ids_t.shape
+        if B > self.max_batch or S > self.max_src:
+            raise ops.Mi8Error(3, f"mini-batch {B}x{S} exceeds the driver's limits {self.max_batch}x{self.max_src}")
+        ids32 = ids_t.to(torch.int32).contiguous()
+        log_mask = ((1.0 - mask_t) * NEG_MASK).contiguous()     # exactly 0 or -99999999
+        self.check(self.L.mi8d_encode(self.h, ids32.data_ptr(), log_mask.data_ptr(), B, S, torch.cuda.current_stream().cuda_stream))
+
+    def start(self, ctx: torch.Tensor, log_mask: torch.Tensor):
+        B, S = ctx.shape[0], ctx.shape[1]
+        if B > self.max_batch or S > self.max_src:
+            raise ops.Mi8Error(3, f"mini-batch {B}x{S} exceeds the driver's limits {self.max_batch}x{self.max_src}")
+        self.check(self.L.mi8d_start(self.h, ctx.contiguous().data_ptr(), log_mask.contiguous().data_ptr(), B, S,
+                                     torch.cuda.current_stream().cuda_stream))
+
+    def step(self, hyp_idx, prev_words, batch_idx, prev_scores, beam: int, batch: int, n_best: int):
+        """hyp_idx / prev_words / prev_scores: NumPy arrays of beam*batch entries (None at the first
+        step); batch_idx: NumPy array of `batch` entries.  Returns NumPy (score, beam, word) [batch, n_best]."""
+        stream = torch.cuda.current_stream().cuda_stream
+        R = beam * batch
+        if hyp_idx is None:
+            ptrs = (None, None, None, None)
+            up = 0
+        else:
+            hc = self.host_ctrl.numpy()
+            hc[0:R] = hyp_idx
+            hc[R:2 * R] = prev_words
+            hc[2 * R:3 * R] = prev_scores.astype(np.float32).view(np.int32)
+            hc[3 * R:3 * R + batch] = batch_idx
+            up = 3 * R + batch
+            self.ctrl[:up].copy_(self.host_ctrl[:up], non_blocking=True)
+            base = self.ctrl.data_ptr()
+            ptrs = (base, base + 4 * R, base + 12 * R, base + 8 * R)
+        n = batch * n_best
+        o = self.out
+        self.check(self.L.mi8d_step(self.h, ptrs[0], ptrs[1], ptrs[2], ptrs[3], beam, batch, n_best,
+                                    o[0].data_ptr(), o[1].data_ptr(), o[2].data_ptr(), stream))
+        self.host_out[:, :n].copy_(o[:, :n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()                       # the step's one host sync
+        ho = self.host_out.numpy()
+        nv = ho[0, :n].view(np.float32).reshape(batch, n_best).copy()
+        return nv, ho[1, :n].astype(np.int64).reshape(batch, n_best), ho[2, :n].astype(np.int64).reshape(batch, n_best), up * 4, 3 * n * 4
+
+
 class BeamSearch:
     """Host-side bookkeeping of BeamSearch::search with batch purging (beam_search.cpp:249-538)."""
 
     def __init__(self, model: Int8Transformer, beam: int = 4, max_length_factor: float = 1.5, normalize: float = 1.0,
-                 word_penalty: float = 0.0):
+                 word_penalty: float = 0.0, native: "NativeStepper | None" = None):
         self.m = model
+        self.native = native      # None: torch glue ops per step; else the C++ step driver
         self.beam = beam
         self.factor = max_length_factor
         self.alpha = normalize
@@ -233,8 +320,12 @@ class BeamSearch:
         """Same with ids (int64) and mask (float32) already on the device."""
         m, dev, eos = self.m, self.m.device, self.m.cfg.eos_id
         B0, width = ids_t.shape
-        ctx, log_mask = m.encode(ids_t, mask_t)
-        st = m.start_state(ctx, log_mask)
+        if self.native is not None:
+            self.native.encode(ids_t, mask_t)
+            st = None
+        else:
+            ctx, log_mask = m.encode(ids_t, mask_t)
+            st = m.start_state(ctx, log_mask)
 
         beam = self.beam
         col = np.arange(beam)[None, :]
@@ -254,35 +345,22 @@ class BeamSearch:
                 break
             active = np.nonzero(W > 0)[0]
             nb = len(active)
+            n_best = max_beam
             if t == 0:
-                tensor_beam = 1
-                logits = m.step(st, None, None, None, 1)
-                prev_scores_t = torch.zeros(nb, device=dev)
+                tensor_beam, hyp_idx, pw, ps, batch_indices = 1, None, None, None, None
             else:
                 tensor_beam = max_beam
                 batch_indices = step_map[active]
                 valid = np.arange(max_beam)[:, None] < W[active][None, :]                  # [max_beam, nb]
-                hyp_idx = np.where(valid, prev_state[active].T[:max_beam] * prev_dim + batch_indices[None, :], 0)
-                pw = np.where(valid, words[active].T[:max_beam], eos)                       # dummy slots carry EOS
-                ps = np.where(valid, scores[active].T[:max_beam], -np.inf).astype(np.float32)
-                R = max_beam * nb
-                host = torch.from_numpy(np.concatenate([hyp_idx.reshape(-1), pw.reshape(-1), batch_indices])).to(dev)
-                prev_scores_t = torch.from_numpy(ps.reshape(-1)).to(dev)
-                self.h2d_bytes += host.numel() * 8 + ps.size * 4
-                logits = m.step(st, host[:R], host[R:2 * R], host[2 * R:], max_beam)
-            # n-best over beam x vocabulary per sentence: row-wise top-N of the logits, shifted by the
-            # row's log-sum-exp and previous path score, then merged across the rows of a sentence
-            # (the same set as top-N over the flattened [beam * V] log-softmax scores).
-            n_best = max_beam
-            lse = torch.logsumexp(logits, dim=-1)
-            top_v, top_i = torch.topk(logits, n_best, dim=-1)                              # [R, n_best]
-            cand = (top_v - lse[:, None]) + prev_scores_t[:, None]
-            cand = cand.view(tensor_beam, nb, n_best).permute(1, 0, 2).reshape(nb, tensor_beam * n_best)
-            best_v, best_c = torch.topk(cand, n_best, dim=-1)                              # sorted, descending
-            word_sel = top_i.view(tensor_beam, nb, n_best).permute(1, 0, 2).reshape(nb, -1).gather(1, best_c)
-            out = torch.stack([best_v.double(), (best_c // n_best).double(), word_sel.double()]).cpu().numpy()  # the step's one sync
-            nv, nbm, nw = out[0].astype(np.float32), out[1].astype(np.int64), out[2].astype(np.int64)
-            self.d2h_bytes += out.size * 8
+                hyp_idx = np.where(valid, prev_state[active].T[:max_beam] * prev_dim + batch_indices[None, :], 0).reshape(-1)
+                pw = np.where(valid, words[active].T[:max_beam], eos).reshape(-1)           # dummy slots carry EOS
+                ps = np.where(valid, scores[active].T[:max_beam], -np.inf).astype(np.float32).reshape(-1)
+            if self.native is not None:
+                nv, nbm, nw, up, down = self.native.step(hyp_idx, pw, batch_indices, ps, tensor_beam, nb, n_best)
+                self.h2d_bytes += up
+                self.d2h_bytes += down
+            else:
+                nv, nbm, nw = self._nbest_torch(st, hyp_idx, pw, batch_indices, ps, tensor_beam, nb, n_best)
 
             # toHyps: every sentence keeps its current number of hypotheses, skipping invalid scores
             ok = nv > -np.inf
@@ -332,6 +410,30 @@ class BeamSearch:
 
         return self._traceback(history, finals, B0)
 
+    def _nbest_torch(self, st, hyp_idx, pw, batch_indices, ps, tensor_beam, nb, n_best):
+        """One step through the torch-glue model, then n-best over beam x vocabulary per sentence:
+        row-wise top-N of the logits, shifted by the row's log-sum-exp and previous path score, merged
+        across the rows of a sentence (the same set as top-N over the flattened [beam * V] scores)."""
+        m, dev = self.m, self.m.device
+        if hyp_idx is None:
+            logits = m.step(st, None, None, None, 1)
+            prev_scores_t = torch.zeros(nb, device=dev)
+        else:
+            R = tensor_beam * nb
+            host = torch.from_numpy(np.concatenate([hyp_idx, pw, batch_indices]).astype(np.int64)).to(dev)
+            prev_scores_t = torch.from_numpy(ps).to(dev)
+            self.h2d_bytes += host.numel() * 8 + ps.size * 4
+            logits = m.step(st, host[:R], host[R:2 * R], host[2 * R:], tensor_beam)
+        lse = torch.logsumexp(logits, dim=-1)
+        top_v, top_i = torch.topk(logits, n_best, dim=-1)                              # [R, n_best]
+        cand = (top_v - lse[:, None]) + prev_scores_t[:, None]
+        cand = cand.view(tensor_beam, nb, n_best).permute(1, 0, 2).reshape(nb, tensor_beam * n_best)
+        best_v, best_c = torch.topk(cand, n_best, dim=-1)                              # sorted, descending
+        word_sel = top_i.view(tensor_beam, nb, n_best).permute(1, 0, 2).reshape(nb, -1).gather(1, best_c)
+        out = torch.stack([best_v.double(), (best_c // n_best).double(), word_sel.double()]).cpu().numpy()  # the step's one sync
+        self.d2h_bytes += out.size * 8
+        return out[0].astype(np.float32), out[1].astype(np.int64), out[2].astype(np.int64)
+
     @staticmethod
     def _traceback(history, finals, B0):
         results = []
@@ -354,9 +456,9 @@ class BeamSearch:
         return results
 
 
-def decode_corpus(model: Int8Transformer, batches, beam=4, max_length_factor=1.5, normalize=1.0):
+def decode_corpus(model: Int8Transformer, batches, beam=4, max_length_factor=1.5, normalize=1.0, native=None):
     """Translate all mini-batches on one replica; returns {sentence id: token list} and the token count."""
-    bs = BeamSearch(model, beam, max_length_factor, normalize)
+    bs = BeamSearch(model, beam, max_length_factor, normalize, native=native)
     out, n_tokens = {}, 0
     for sent_ids, ids, mask in batches:
         res = bs.search(ids, mask)

@@ -68,8 +68,8 @@ CONFIGS = {
     "base": TransformerConfig(512, 2048, 8, 6, 6, 32000),
     "big": TransformerConfig(1024, 4096, 16, 6, 6, 32000),
     "student": TransformerConfig(256, 1536, 8, 12, 2, 32000, decoder_autoreg="rnn"),
-    "tiny": TransformerConfig(64, 128, 4, 2, 2, 512),
-    "tiny-ssru": TransformerConfig(64, 128, 4, 2, 2, 512, decoder_autoreg="rnn"),
+    "tiny": TransformerConfig(64, 128, 2, 2, 2, 512),
+    "tiny-ssru": TransformerConfig(64, 128, 2, 2, 2, 512, decoder_autoreg="rnn"),
 }
 
 
@@ -161,3 +161,16 @@ def make_batches(corpus, mini_batch: int):
             mask[r, :n] = 1.0
         batches.append((np.array(idx, np.int64), ids, mask))
     return batches
+
+
+def sinusoidal_table(n: int, dim: int) -> np.ndarray:
+    """Position table [n, dim] of gSinusoidalPositionEmbeddings (src/tensors/gpu/tensor_operators.cu:793-817):
+    v = pos * exp(-(i mod dim/2) * ln(10000) / (dim/2 - 1)), sin for the first half, cos for the second.
+    Computed once on the host in float32 so that every consumer sees the same bits."""
+    half = dim // 2
+    inc = np.float32(math.log(10000.0) / (half - 1.0))
+    i = np.arange(dim)
+    freq = np.exp((i % half).astype(np.float32) * -inc).astype(np.float32)
+    pos = np.arange(n, dtype=np.float32)[:, None]
+    v = (pos * freq[None, :]).astype(np.float32)
+    return np.where(i[None, :] < half, np.sin(v), np.cos(v)).astype(np.float32)

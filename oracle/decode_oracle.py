@@ -36,23 +36,6 @@ def _positions(start, n, dim):
     return np.where(i[None, :] < half, np.sin(v), np.cos(v)).astype(np.float32)
 
 
-def _layer_norm(x, scale, bias, eps=1e-6):
-    mean = x.mean(axis=-1, keepdims=True, dtype=np.float32)
-    var = ((x - mean) ** 2).mean(axis=-1, keepdims=True, dtype=np.float32)
-    return ((x - mean) / np.sqrt(var + np.float32(eps)) * scale.reshape(-1) + bias.reshape(-1)).astype(np.float32)
-
-
-def _softmax(z):
-    z = z - z.max(axis=-1, keepdims=True)
-    e = np.exp(z, dtype=np.float32)
-    return (e / e.sum(axis=-1, keepdims=True, dtype=np.float32)).astype(np.float32)
-
-
-def _log_softmax(z):
-    m = z.max(axis=-1, keepdims=True)
-    return (z - m - np.log(np.exp(z - m, dtype=np.float32).sum(axis=-1, keepdims=True, dtype=np.float32))).astype(np.float32)
-
-
 class Hyp:
     __slots__ = ("prev", "word", "prev_state", "score")
 
@@ -68,6 +51,9 @@ class Hyp:
 
 
 class OracleTransformer:
+    """All float glue (embedding, LayerNorm, attention, SSRU cell, log-softmax/top-k) runs through the
+    fixed-order C functions of oracle_i8.c; all affines through its int8 path."""
+
     def __init__(self, cfg, params: dict, oracle: COracle | None = None, output_int8: bool = True, threads: int = 0):
         self.cfg = cfg
         self.o = oracle or COracle()
@@ -85,61 +71,63 @@ class OracleTransformer:
         self.wemb_q = self.o.prepare_b(self.wemb, w_is_nk=True) if output_int8 else None
         self.d, self.h = cfg.dim_emb, cfg.heads
         self.dh = self.d // self.h
+        self.pos = _positions(0, 512, self.d)
+        self.scale = float(np.sqrt(np.float32(self.d)))
 
     def affine(self, x, wname, bname=None, relu=False):
         bt, qb = self.w[wname]
         bias = self.p[bname].reshape(-1) if bname else None
         return self.o.affine(x.reshape(-1, x.shape[-1]), bt, qb, bias, 1.0, relu)
 
-    def ln(self, x, prefix):
-        return _layer_norm(x, self.p[prefix + "_ln_scale"], self.p[prefix + "_ln_bias"])
-
-    def heads(self, x, rows, steps):
-        return x.reshape(rows, steps, self.h, self.dh).transpose(0, 2, 1, 3)
-
-    def attention(self, q, k, v, log_mask):
-        z = np.matmul(q, np.swapaxes(k, -1, -2)) * np.float32(1.0 / math.sqrt(self.dh))
-        if log_mask is not None:
-            z = z + log_mask
-        return np.matmul(_softmax(z.astype(np.float32)), v).astype(np.float32)
+    def add_ln(self, a, resid, prefix):
+        return self.o.add_layernorm(a, resid, self.p[prefix + "_ln_scale"], self.p[prefix + "_ln_bias"], 1e-6)
 
     def ffn(self, x, prefix):
         h = self.affine(x, prefix + "_W1", prefix + "_b1", relu=True)
         out = self.affine(h, prefix + "_W2", prefix + "_b2")
-        return self.ln(out.reshape(x.shape) + x, prefix + "_ffn")
+        return self.add_ln(out, x, prefix + "_ffn")
 
     def encode(self, ids, mask):
         B, S = ids.shape
-        x = (self.wemb[ids] * np.float32(math.sqrt(self.d)) + _positions(0, S, self.d)[None]).astype(np.float32)
-        log_mask = ((1.0 - mask.astype(np.float32)) * NEG_MASK).reshape(B, 1, 1, S)
+        M = B * S
+        x = self.o.embed(self.wemb, ids.reshape(-1), self.pos, S, self.scale, M)
+        log_mask = ((np.float32(1.0) - mask.astype(np.float32)) * NEG_MASK).astype(np.float32)      # [B, S]
         for i in range(1, self.cfg.enc_depth + 1):
             pre = f"encoder_l{i}_self"
-            q = self.heads(self.affine(x, pre + "_Wq", pre + "_bq"), B, S)
-            k = self.heads(self.affine(x, pre + "_Wk", pre + "_bk"), B, S)
-            v = self.heads(self.affine(x, pre + "_Wv", pre + "_bv"), B, S)
-            a = self.attention(q, k, v, log_mask).transpose(0, 2, 1, 3).reshape(B * S, self.d)
-            out = self.affine(a, pre + "_Wo", pre + "_bo")
-            x = self.ln(out.reshape(B, S, self.d) + x, pre + "_Wo")
+            q = self.affine(x, pre + "_Wq", pre + "_bq")
+            k = self.affine(x, pre + "_Wk", pre + "_bk")
+            v = self.affine(x, pre + "_Wv", pre + "_bv")
+            a = self.o.attention1(q, k, v, log_mask, M, self.h, self.dh, S, B, 2)
+            x = self.add_ln(self.affine(a, pre + "_Wo", pre + "_bo"), x, pre + "_Wo")
             x = self.ffn(x, f"encoder_l{i}_ffn")
-        return x, log_mask
+        return x.reshape(B, S, self.d), log_mask
+
+    def start_state(self, ctx, mask):
+        B = ctx.shape[0]
+        layer = [np.zeros((B, self.d), np.float32) if self.cfg.decoder_autoreg == "rnn" else None
+                 for _ in range(self.cfg.dec_depth)]
+        return {"ctx": ctx, "mask": mask, "layer": layer, "cross_rows": -1, "pos": 0}
 
     def step(self, st, hyp_indices, prev_words, batch_indices, beam):
+        """Returns the logits [beam*batch, V] of one decoder step (rows beam-major)."""
         cfg, t = self.cfg, st["pos"]
         if t > 0:
             if len(batch_indices) != st["ctx"].shape[0]:
                 st["ctx"] = st["ctx"][batch_indices]
                 st["mask"] = st["mask"][batch_indices]
-            st["layer"] = [s[hyp_indices] for s in st["layer"]]
+            if cfg.decoder_autoreg == "rnn":
+                st["layer"] = [s[hyp_indices] for s in st["layer"]]
+            else:
+                st["layer"] = [s[:, hyp_indices] for s in st["layer"]]           # history is time-major [T, R, d]
         B, S = st["ctx"].shape[:2]
         R = beam * B
-        emb = np.zeros((R, self.d), np.float32) if t == 0 else self.wemb[prev_words]
-        x = (emb * np.float32(math.sqrt(self.d)) + _positions(t, 1, self.d)).astype(np.float32)
+        x = self.o.embed(self.wemb, None if t == 0 else prev_words, self.pos[t:t + 1], 0, self.scale, R)
         if st["cross_rows"] != B:
             st["ck"], st["cv"] = [], []
             for i in range(1, cfg.dec_depth + 1):
                 pre = f"decoder_l{i}_context"
-                st["ck"].append(self.heads(self.affine(st["ctx"], pre + "_Wk", pre + "_bk"), B, S))
-                st["cv"].append(self.heads(self.affine(st["ctx"], pre + "_Wv", pre + "_bv"), B, S))
+                st["ck"].append(self.affine(st["ctx"], pre + "_Wk", pre + "_bk"))      # [B*S, d]
+                st["cv"].append(self.affine(st["ctx"], pre + "_Wv", pre + "_bv"))
             st["cross_rows"] = B
         for i in range(1, cfg.dec_depth + 1):
             li = i - 1
@@ -147,26 +135,23 @@ class OracleTransformer:
                 pre = f"decoder_l{i}_rnn"
                 xw = self.affine(x, pre + "_W")
                 f = self.affine(x, pre + "_Wf", pre + "_bf")
-                sig = (1.0 / (1.0 + np.exp(-f, dtype=np.float32))).astype(np.float32)
-                cell = (st["layer"][li] * sig + xw * (1.0 - sig)).astype(np.float32)
+                cell, h = self.o.ssru_cell(st["layer"][li], xw, f)
                 st["layer"][li] = cell
-                x = self.ln(np.maximum(cell, 0) + x, pre + "_ffn")
+                x = self.add_ln(h, x, pre + "_ffn")
             else:
                 pre = f"decoder_l{i}_self"
-                hist = x.reshape(R, 1, self.d) if st["layer"][li] is None else np.concatenate(
-                    [st["layer"][li], x.reshape(R, 1, self.d)], axis=1)
+                hist = x[None] if st["layer"][li] is None else np.concatenate([st["layer"][li], x[None]], axis=0)
                 st["layer"][li] = hist
-                steps = hist.shape[1]
-                q = self.heads(self.affine(x, pre + "_Wq", pre + "_bq"), R, 1)
-                k = self.heads(self.affine(hist, pre + "_Wk", pre + "_bk"), R, steps)
-                v = self.heads(self.affine(hist, pre + "_Wv", pre + "_bv"), R, steps)
-                a = self.attention(q, k, v, None).transpose(0, 2, 1, 3).reshape(R, self.d)
-                x = self.ln(self.affine(a, pre + "_Wo", pre + "_bo") + x, pre + "_Wo")
+                steps = hist.shape[0]
+                q = self.affine(x, pre + "_Wq", pre + "_bq")
+                k = self.affine(hist, pre + "_Wk", pre + "_bk")                          # one multiplier over the history
+                v = self.affine(hist, pre + "_Wv", pre + "_bv")
+                a = self.o.attention1(q, k, v, None, R, self.h, self.dh, steps, B, 0)
+                x = self.add_ln(self.affine(a, pre + "_Wo", pre + "_bo"), x, pre + "_Wo")
             pre = f"decoder_l{i}_context"
-            q = self.heads(self.affine(x, pre + "_Wq", pre + "_bq"), R, 1).reshape(beam, B, self.h, 1, self.dh)
-            a = self.attention(q, st["ck"][li][None], st["cv"][li][None], st["mask"][None])
-            a = a.transpose(0, 1, 3, 2, 4).reshape(R, self.d)
-            x = self.ln(self.affine(a, pre + "_Wo", pre + "_bo") + x, pre + "_Wo")
+            q = self.affine(x, pre + "_Wq", pre + "_bq")
+            a = self.o.attention1(q, st["ck"][li], st["cv"][li], st["mask"], R, self.h, self.dh, S, B, 1)
+            x = self.add_ln(self.affine(a, pre + "_Wo", pre + "_bo"), x, pre + "_Wo")
             x = self.ffn(x, f"decoder_l{i}_ffn")
         st["pos"] = t + 1
         b = self.p["decoder_ff_logit_out_b"].reshape(-1)
@@ -174,12 +159,6 @@ class OracleTransformer:
             bt, qb = self.wemb_q
             return self.o.affine(x, bt, qb, b)
         return (x @ self.wemb.T + b).astype(np.float32)
-
-    def start_state(self, ctx, mask):
-        B = ctx.shape[0]
-        layer = [np.zeros((B, self.d), np.float32) if self.cfg.decoder_autoreg == "rnn" else None
-                 for _ in range(self.cfg.dec_depth)]
-        return {"ctx": ctx, "mask": mask, "layer": layer, "cross_rows": -1, "pos": 0}
 
 
 def beam_search(model: OracleTransformer, ids, mask, beam=4, max_length_factor=1.5, normalize=1.0, word_penalty=0.0):
@@ -223,22 +202,25 @@ def beam_search(model: OracleTransformer, ids, mask, beam=4, max_length_factor=1
             tensor_beam = max_beam
             prev_scores = np.array(ps, np.float32).reshape(max_beam, cur_dim)
         nb = len(active)
-        logp = _log_softmax(logits).reshape(tensor_beam, nb, V)
-        expanded = (prev_scores[:, :, None] + logp).transpose(1, 0, 2).reshape(nb, tensor_beam * V)
         n_best = max_beam
+        # log-softmax and top-N per row in the fixed order, then the N best of beam x N candidates per
+        # sentence; ties go to the smaller flattened (beam, word) key
+        cs, cw = model.o.lse_topk(logits, n_best, prev_scores.reshape(-1))
+        cs = cs.reshape(tensor_beam, nb, n_best)
+        cw = cw.reshape(tensor_beam, nb, n_best)
         new_beams = [[] for _ in range(B0)]
         for c, o in enumerate(active):
-            row = expanded[c]
-            keys = np.argpartition(-row, n_best)[:n_best] if row.size > n_best else np.arange(row.size)
-            keys = keys[np.argsort(-row[keys], kind="stable")]
-            for key in keys:
+            cands = []
+            for j in range(tensor_beam):
+                for r in range(n_best):
+                    if cs[j, c, r] != -np.inf:
+                        cands.append((-float(cs[j, c, r]), j * V + int(cw[j, c, r]), float(cs[j, c, r])))
+            cands.sort(key=lambda e: (e[0], e[1]))
+            for _neg, key, score in cands[:n_best]:
                 if len(new_beams[o]) >= len(beams[o]):
                     break
-                score = row[key]
-                if score == -np.inf:
-                    continue
-                j, word = int(key) // V, int(key) % V
-                new_beams[o].append(Hyp(beams[o][j], word, j, float(score)))
+                j, word = key // V, key % V
+                new_beams[o].append(Hyp(beams[o][j], word, j, score))
         prev_map = list(batch_map)
         # purge + history
         length = t + 1

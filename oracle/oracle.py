@@ -119,6 +119,20 @@ class COracle:
         L.mo_affine.restype = ctypes.c_int
         L.mo_affine.argtypes = [f32p, ctypes.c_int, ctypes.c_int, i8p, ctypes.c_float, ctypes.c_int, f32p,
                                 ctypes.c_float, ctypes.c_int, f32p, i8p, i32p, f32p]
+        L.mo_add_layernorm.restype = None
+        L.mo_add_layernorm.argtypes = [f32p, f32p, f32p, f32p, ctypes.c_float, ctypes.c_int, ctypes.c_int, f32p]
+        L.mo_attention1.restype = None
+        L.mo_attention1.argtypes = [f32p, f32p, f32p, f32p] + [ctypes.c_int] * 6 + [f32p]
+        L.mo_lse_topk.restype = None
+        L.mo_lse_topk.argtypes = [f32p, ctypes.c_int, ctypes.c_int, ctypes.c_int, f32p, f32p, i32p]
+        L.mo_embed.restype = None
+        L.mo_embed.argtypes = [f32p, i32p, f32p, ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int, f32p]
+        L.mo_ssru_cell.restype = None
+        L.mo_ssru_cell.argtypes = [f32p, f32p, f32p, ctypes.c_size_t, f32p, f32p]
+        L.mo_det_expf.restype = ctypes.c_float
+        L.mo_det_expf.argtypes = [ctypes.c_float]
+        L.mo_det_logf.restype = ctypes.c_float
+        L.mo_det_logf.argtypes = [ctypes.c_float]
         L.mo_max_threads.restype = ctypes.c_int
         L.mo_set_threads.argtypes = [ctypes.c_int]
         self.L = L
@@ -189,3 +203,54 @@ class COracle:
         if want_acc:
             return out, acc, aq, np.float32(qa.value)
         return out
+
+    # ---- float glue in the fixed operation order (see oracle_i8.c) -------------------------------
+    def add_layernorm(self, a, resid, gamma, beta, eps=1e-6):
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        rows, dim = int(np.prod(a.shape[:-1])), a.shape[-1]
+        r = None if resid is None else np.ascontiguousarray(resid, dtype=np.float32)
+        g = np.ascontiguousarray(gamma, dtype=np.float32).reshape(-1)
+        b = np.ascontiguousarray(beta, dtype=np.float32).reshape(-1)
+        out = np.empty_like(a)
+        self.L.mo_add_layernorm(_p(a, ctypes.c_float), _p(r, ctypes.c_float), _p(g, ctypes.c_float), _p(b, ctypes.c_float),
+                                ctypes.c_float(eps), rows, dim, _p(out, ctypes.c_float))
+        return out
+
+    def attention1(self, q, k, v, log_mask, rows, heads, dh, length, batch, mode):
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        k = np.ascontiguousarray(k, dtype=np.float32)
+        v = np.ascontiguousarray(v, dtype=np.float32)
+        m = None if log_mask is None else np.ascontiguousarray(log_mask, dtype=np.float32)
+        out = np.empty((rows, heads * dh), dtype=np.float32)
+        self.L.mo_attention1(_p(q, ctypes.c_float), _p(k, ctypes.c_float), _p(v, ctypes.c_float), _p(m, ctypes.c_float),
+                             rows, heads, dh, length, batch, mode, _p(out, ctypes.c_float))
+        return out
+
+    def lse_topk(self, logits, k, prev_scores=None):
+        logits = np.ascontiguousarray(logits, dtype=np.float32)
+        rows, vocab = logits.shape
+        ps = None if prev_scores is None else np.ascontiguousarray(prev_scores, dtype=np.float32)
+        cs = np.empty((rows, k), dtype=np.float32)
+        cw = np.empty((rows, k), dtype=np.int32)
+        self.L.mo_lse_topk(_p(logits, ctypes.c_float), rows, vocab, k, _p(ps, ctypes.c_float), _p(cs, ctypes.c_float),
+                           _p(cw, ctypes.c_int32))
+        return cs, cw
+
+    def embed(self, wemb, words, pos, pos_mod, scale, rows):
+        wemb = np.ascontiguousarray(wemb, dtype=np.float32)
+        dim = wemb.shape[1]
+        w = None if words is None else np.ascontiguousarray(words, dtype=np.int32)
+        pos = np.ascontiguousarray(pos, dtype=np.float32)
+        out = np.empty((rows, dim), dtype=np.float32)
+        self.L.mo_embed(_p(wemb, ctypes.c_float), _p(w, ctypes.c_int32), _p(pos, ctypes.c_float), pos_mod, ctypes.c_float(scale),
+                        rows, dim, _p(out, ctypes.c_float))
+        return out
+
+    def ssru_cell(self, cell, xw, f):
+        cell = np.ascontiguousarray(cell, dtype=np.float32)
+        xw = np.ascontiguousarray(xw, dtype=np.float32)
+        f = np.ascontiguousarray(f, dtype=np.float32)
+        cn, h = np.empty_like(cell), np.empty_like(cell)
+        self.L.mo_ssru_cell(_p(cell, ctypes.c_float), _p(xw, ctypes.c_float), _p(f, ctypes.c_float), cell.size,
+                            _p(cn, ctypes.c_float), _p(h, ctypes.c_float))
+        return cn, h

@@ -240,3 +240,214 @@ int mo_affine(const float* a, int m, int k, const int8_t* bt, float qb, int n, c
   if(!acc_out) free(acc);
   return MO_OK;
 }
+
+/* ===================================================================================================
+ * Float glue of the decode (LayerNorm, attention, log-softmax/top-k, embedding, SSRU cell).
+ *
+ * The reference leaves the order of its float reductions to whatever BLAS / SIMD kernels it is built
+ * with, so no particular order is "the" reference order.  An int8 pipeline amplifies a one-ulp
+ * difference in these ops to a full quantisation step within two affines, therefore the checker and
+ * the engine must round identically to be comparable at all.  The functions below fix one order
+ * (thread-strided partial sums, a 32-wide butterfly, eight partials added in ascending order; fma
+ * chains in ascending index order) and fixed polynomials for exp and log, built from correctly
+ * rounded IEEE operations only.
+ *   LayerNorm: gamma * (x - mean) / sqrt(var + eps) + beta, biased variance
+ *              (src/tensors/cpu/tensor_operators.cpp:1087-1124, eps 1e-6 src/layers/generic.h:248-253)
+ *   attention: softmax(q.k / sqrt(dh) + mask) . v   (src/models/transformer.h:240-277)
+ *   SSRU:      c' = c*sigmoid(f) + x*(1 - sigmoid(f)), h = relu(c')   (src/rnn/cells.h:1052-1066)
+ *   n-best:    log-softmax + top-N over beam x vocabulary (src/translator/beam_search.cpp:469-496)
+ * =================================================================================================== */
+#include <float.h>
+
+#define MO_FMA_CLONES __attribute__((target_clones("arch=haswell", "default")))
+
+static inline float mo_det_expf_i(float x) {
+  if(x < -87.0f) return 0.0f;
+  if(x > 88.0f) x = 88.0f;
+  const float n = rintf(x * 1.44269504f);
+  float r = fmaf(n, -0.693145752f, x);
+  r = fmaf(n, -1.42860677e-06f, r);
+  float p = 1.3888889e-3f;
+  p = fmaf(p, r, 8.3333338e-3f);
+  p = fmaf(p, r, 4.1666668e-2f);
+  p = fmaf(p, r, 1.6666667e-1f);
+  p = fmaf(p, r, 0.5f);
+  p = fmaf(p, r, 1.0f);
+  p = fmaf(p, r, 1.0f);
+  const int e = (int)n;
+  union { int32_t i; float f; } s;
+  s.i = (e + 127) << 23;
+  return p * s.f;
+}
+
+static inline float mo_det_logf_i(float x) {
+  union { int32_t i; float f; } u;
+  u.f = x;
+  int e = ((u.i >> 23) & 0xff) - 127;
+  u.i = (u.i & 0x007fffff) | 0x3f800000;
+  float m = u.f;
+  if(m > 1.41421354f) { m = m * 0.5f; e += 1; }
+  const float s = (m + -1.0f) / (m + 1.0f);
+  const float s2 = s * s;
+  float t = 0.181818187f;
+  t = fmaf(t, s2, 0.222222224f);
+  t = fmaf(t, s2, 0.285714298f);
+  t = fmaf(t, s2, 0.400000006f);
+  t = fmaf(t, s2, 0.666666687f);
+  t = t * s2;
+  const float lm = fmaf(s, t, 2.0f * s);
+  return fmaf((float)e, 0.693147182f, lm);
+}
+
+MO_FMA_CLONES float mo_det_expf(float x) { return mo_det_expf_i(x); }
+MO_FMA_CLONES float mo_det_logf(float x) { return mo_det_logf_i(x); }
+
+/* v[i] <- v[i] + v[i ^ o] for o = 16, 8, 4, 2, 1; every entry ends with the same bits */
+static inline float mo_warp_sum(const float* v32) {
+  float a[32], b[32];
+  memcpy(a, v32, sizeof(a));
+  for(int o = 16; o > 0; o >>= 1) {
+    for(int i = 0; i < 32; ++i) b[i] = a[i] + a[i ^ o];
+    memcpy(a, b, sizeof(a));
+  }
+  return a[0];
+}
+
+static inline float mo_block256_sum(const float* v256) {
+  float t = 0.0f;
+  for(int w = 0; w < 8; ++w) t = t + mo_warp_sum(v256 + 32 * w);
+  return t;
+}
+
+/* out = LayerNorm(a + resid) * gamma + beta per row (resid may be NULL) */
+MO_FMA_CLONES void mo_add_layernorm(const float* a, const float* resid, const float* gamma, const float* beta, float eps, int rows,
+                                    int dim, float* out) {
+  const int chunks = dim / 4;
+  float* y = (float*)malloc(sizeof(float) * (size_t)dim);
+  for(int r = 0; r < rows; ++r) {
+    const float* ar = a + (size_t)r * dim;
+    const float* rr = resid ? resid + (size_t)r * dim : NULL;
+    for(int i = 0; i < dim; ++i) y[i] = rr ? ar[i] + rr[i] : ar[i];
+    float part[256];
+    for(int t = 0; t < 256; ++t) {
+      float s = 0.0f;
+      for(int c = t; c < chunks; c += 256) s = s + ((y[4 * c] + y[4 * c + 1]) + (y[4 * c + 2] + y[4 * c + 3]));
+      part[t] = s;
+    }
+    const float mean = mo_block256_sum(part) / (float)dim;
+    for(int t = 0; t < 256; ++t) {
+      float q = 0.0f;
+      for(int c = t; c < chunks; c += 256) {
+        const float dx = y[4 * c] + -mean, dy = y[4 * c + 1] + -mean, dz = y[4 * c + 2] + -mean, dw = y[4 * c + 3] + -mean;
+        q = q + fmaf(dx, dx, fmaf(dy, dy, fmaf(dz, dz, dw * dw)));
+      }
+      part[t] = q;
+    }
+    const float var = mo_block256_sum(part) / (float)dim;
+    const float denom = sqrtf(var + eps);
+    float* o = out + (size_t)r * dim;
+    for(int i = 0; i < dim; ++i) o[i] = ((y[i] + -mean) / denom) * gamma[i] + beta[i];
+  }
+  free(y);
+}
+
+/* Single-query attention; key/value row of position p for query row r is base(r) + p*stride:
+ * mode 0: base = r, stride = rows (time-major history); mode 1: base = (r % batch)*len (cross-attention);
+ * mode 2: base = (r / len)*len (encoder self-attention, rows ordered [batch, len]). */
+MO_FMA_CLONES void mo_attention1(const float* q, const float* k, const float* v, const float* log_mask, int rows, int heads, int dh,
+                                 int len, int batch, int mode, float* out) {
+  const int dim = heads * dh;
+  const float scale = 1.0f / sqrtf((float)dh);
+  float* p = (float*)malloc(sizeof(float) * (size_t)len);
+  for(int r = 0; r < rows; ++r) {
+    const int group = mode == 1 ? r % batch : (mode == 2 ? r / len : 0);
+    const size_t base = mode == 0 ? (size_t)r : (size_t)group * len;
+    const size_t stride = mode == 0 ? (size_t)rows : 1;
+    const float* mask = (mode != 0 && log_mask) ? log_mask + (size_t)group * len : NULL;
+    for(int h = 0; h < heads; ++h) {
+      const float* qh = q + (size_t)r * dim + h * dh;
+      float mx = -FLT_MAX;
+      for(int pos = 0; pos < len; ++pos) {
+        const float* kr = k + (base + pos * stride) * dim + h * dh;
+        float s = 0.0f;
+        for(int i = 0; i < dh; ++i) s = fmaf(qh[i], kr[i], s);
+        s = s * scale;
+        if(mask) s = s + mask[pos];
+        p[pos] = s;
+        if(s > mx) mx = s;
+      }
+      float part[32];
+      for(int l = 0; l < 32; ++l) part[l] = 0.0f;
+      for(int pos = 0; pos < len; ++pos) {
+        const float e = mo_det_expf_i(p[pos] + -mx);
+        p[pos] = e;
+        part[pos & 31] = part[pos & 31] + e;
+      }
+      const float sum = mo_warp_sum(part);
+      for(int pos = 0; pos < len; ++pos) p[pos] = p[pos] / sum;
+      float* o = out + (size_t)r * dim + h * dh;
+      for(int i = 0; i < dh; ++i) {
+        float acc = 0.0f;
+        for(int pos = 0; pos < len; ++pos) acc = fmaf(p[pos], v[(base + pos * stride) * dim + h * dh + i], acc);
+        o[i] = acc;
+      }
+    }
+  }
+  free(p);
+}
+
+/* larger value first; ties: smaller index first */
+static inline int mo_better(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
+
+/* cand_score[r][j] = (j-th largest logit - lse(row)) + prev_score[r]; cand_word[r][j]; k <= 8 */
+MO_FMA_CLONES void mo_lse_topk(const float* logits, int rows, int vocab, int k, const float* prev_scores, float* cand_score,
+                               int32_t* cand_word) {
+  for(int r = 0; r < rows; ++r) {
+    const float* row = logits + (size_t)r * vocab;
+    float tv[8];
+    int ti[8];
+    for(int j = 0; j < k; ++j) { tv[j] = -FLT_MAX; ti[j] = 0x7fffffff; }
+    float mx = -FLT_MAX;
+    for(int i = 0; i < vocab; ++i) {
+      const float x = row[i];
+      if(x > mx) mx = x;
+      if(mo_better(x, i, tv[k - 1], ti[k - 1])) {
+        int pos = k - 1;
+        while(pos > 0 && mo_better(x, i, tv[pos - 1], ti[pos - 1])) { tv[pos] = tv[pos - 1]; ti[pos] = ti[pos - 1]; --pos; }
+        tv[pos] = x;
+        ti[pos] = i;
+      }
+    }
+    float part[256];
+    for(int t = 0; t < 256; ++t) {
+      float s = 0.0f;
+      for(int i = t; i < vocab; i += 256) s = s + mo_det_expf_i(row[i] + -mx);
+      part[t] = s;
+    }
+    const float lse = mx + mo_det_logf_i(mo_block256_sum(part));
+    const float ps = prev_scores ? prev_scores[r] : 0.0f;
+    for(int j = 0; j < k; ++j) {
+      cand_score[(size_t)r * k + j] = (tv[j] + -lse) + ps;
+      cand_word[(size_t)r * k + j] = ti[j];
+    }
+  }
+}
+
+/* out[r,:] = wemb[words[r],:] * scale + pos[(pos_mod ? r % pos_mod : 0),:]   (words NULL: zero embedding) */
+void mo_embed(const float* wemb, const int32_t* words, const float* pos, int pos_mod, float scale, int rows, int dim, float* out) {
+  for(int r = 0; r < rows; ++r) {
+    const float* e = words ? wemb + (size_t)words[r] * dim : NULL;
+    const float* p = pos + (size_t)(pos_mod ? r % pos_mod : 0) * dim;
+    for(int i = 0; i < dim; ++i) out[(size_t)r * dim + i] = (e ? e[i] : 0.0f) * scale + p[i];
+  }
+}
+
+/* SSRU cell on already gathered state: sig = 1/(1+exp(-f)); c' = fma(x, 1 - sig, c*sig); h = relu(c') */
+MO_FMA_CLONES void mo_ssru_cell(const float* cell, const float* xw, const float* f, size_t n, float* cell_new, float* h) {
+  for(size_t i = 0; i < n; ++i) {
+    const float sig = 1.0f / (1.0f + mo_det_expf_i(-f[i]));
+    const float cn = fmaf(xw[i], 1.0f + -sig, cell[i] * sig);
+    cell_new[i] = cn;
+    h[i] = cn > 0.0f ? cn : 0.0f;
+  }
+}

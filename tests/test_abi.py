@@ -9,10 +9,10 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _declared_symbols():
-    text = open(os.path.join(ROOT, "include", "marian_i8.h")).read()
+def _declared_symbols(header="marian_i8.h", prefix="mi8_"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(mi8_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(" + prefix + r"[a-z0-9_]+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():
@@ -25,6 +25,12 @@ def test_library_exports_every_declared_symbol():
     for sym in declared:
         assert hasattr(L, sym), f"{sym} declared in include/marian_i8.h but not exported"
     assert sorted(EXPORTS) == declared
+    from marian_dev_b200.binding import DECODE_EXPORTS
+    declared_decode = _declared_symbols("marian_i8_decode.h", "mi8[dg]_")
+    assert declared_decode
+    for sym in declared_decode:
+        assert hasattr(L, sym), f"{sym} declared in include/marian_i8_decode.h but not exported"
+    assert sorted(DECODE_EXPORTS) == declared_decode
 
 
 def test_strerror_and_version():
