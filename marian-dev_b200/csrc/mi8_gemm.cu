@@ -528,18 +528,27 @@ int profile_end(mi8_gemm_record* out, int capacity, int* count) {
 int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, GemmPlan* plan) {
   if(M <= 0 || N <= 0 || K <= 0)
     return MI8_ERR_BAD_ARG;
+  const int sms = sm_count();
   int tm = force_tile_m;
   if(tm == 0) {
-    tm = 256;
-    for(int cand : {16, 32, 64, 128, 256})
-      if(M <= cand) {
-        tm = cand;
-        break;
+    // Tile width along M.  Up to 64 rows: the smallest tile that holds them.  Above that, 256-row tiles
+    // only when they already give every SM a tile; otherwise narrower tiles (a quarter of M, 32..128
+    // rows) spread the weight stream over more SMs, which measured faster for the decode shapes.
+    if(M <= 64) {
+      tm = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    } else {
+      const long long tiles256 = static_cast<long long>((N + kTileN - 1) / kTileN) * ((M + 255) / 256);
+      if(tiles256 >= sms) {
+        tm = 256;
+      } else {
+        tm = 32;
+        while(tm < 128 && tm * 4 < M)
+          tm *= 2;
       }
+    }
   }
   if(tm != 16 && tm != 32 && tm != 64 && tm != 128 && tm != 256)
     return MI8_ERR_BAD_ARG;
-  const int sms = sm_count();
   plan->tile_m = tm;
   plan->stages = tm == 256 ? 4 : (tm == 128 ? 6 : 8);
   plan->n_tiles = (N + kTileN - 1) / kTileN;
@@ -552,11 +561,11 @@ int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, Gemm
   if(splits == 0) {
     splits = 1;
     if(tiles < sms) {
-      // Spread the weight stream over more SMs, but keep the partial-accumulator traffic
-      // (splits * M * N * 4 bytes) below about twice the weight bytes (K * N).
+      // Split K across idle SMs, but leave every split at least eight 128-byte K blocks: below that
+      // the fence + arrival counter of the split path costs more than the shorter stream saves.
       int by_sms = static_cast<int>(sms / tiles);
-      int by_traffic = K / (2 * M) > 1 ? K / (2 * M) : 1;
-      splits = by_sms < by_traffic ? by_sms : by_traffic;
+      int by_depth = plan->kb_total / 8 > 1 ? plan->kb_total / 8 : 1;
+      splits = by_sms < by_depth ? by_sms : by_depth;
       if(splits > plan->kb_total)
         splits = plan->kb_total;
       if(splits < 1)

@@ -195,26 +195,19 @@ __global__ void ancestors_update_kernel(const int* __restrict__ anc_old, int* __
   anc_new[tp * stride + r] = tp == t ? r : anc_old[tp * stride + hyp[r]];
 }
 
-// max over t' <= t, r < rows of rowmax[t'][anc[t'][r]] -> slot (single block).
-__global__ void __launch_bounds__(1024)
+// max over t' < steps, r < rows of rowmax[t'][anc[t'][r]], reduced into the (zeroed) slot with atomicMax.
+__global__ void __launch_bounds__(256)
 history_absmax_kernel(const float* __restrict__ rowmax, const int* __restrict__ anc, int steps, int rows, int stride,
                       unsigned* absmax_slot) {
-  __shared__ unsigned red[32];
   unsigned m = 0u;
-  for(int i = threadIdx.x; i < steps * rows; i += blockDim.x) {
+  const int n = steps * rows;
+  for(int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const int tp = i / rows, r = i - tp * rows;
     m = max(m, abs_bits(rowmax[tp * stride + anc[tp * stride + r]]));
   }
   m = __reduce_max_sync(0xffffffffu, m);
-  if((threadIdx.x & 31) == 0)
-    red[threadIdx.x >> 5] = m;
-  __syncthreads();
-  if(threadIdx.x < 32) {
-    m = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0u;
-    m = __reduce_max_sync(0xffffffffu, m);
-    if(threadIdx.x == 0)
-      *absmax_slot = m;
-  }
+  if((threadIdx.x & 31) == 0 && m != 0u)
+    atomicMax(absmax_slot, m);
 }
 
 // hq[(t' * rows + r), :] = quantise(slab[t'][anc[t'][r], :]) for t' < steps: one block per output row.
@@ -237,114 +230,114 @@ history_quantize_kernel(const float* __restrict__ slabs, size_t slab_stride, con
 }
 
 // ---- single-query attention --------------------------------------------------------------------
-// One block per query row, one warp per head (looping when there are more heads than warps).
+// One block per query row; thread i owns elements 4i..4i+3 of the model dimension, i.e. a quarter-row
+// slice of head i / G with G = DH/4 threads per head.  For every key position the block reads the whole
+// key row (all heads) with one 16-byte load per thread - fully coalesced whatever the layout of the
+// history - and the G threads of a head combine their partial dot products with a butterfly.
 // Key/value row of position p for query row r is  kv_base(r) + p * kv_stride:
 //   mode 0, decoder self-attention over the time-major history:  base = r,              stride = rows
 //   mode 1, cross-attention over the context [batch, len, dim]:   base = (r % batch)*len, stride = 1, log mask row r % batch
 //   mode 2, encoder self-attention, rows ordered [batch, len]:    base = (r / len)*len,   stride = 1, log mask row r / len
 // softmax(q.k / sqrt(dh) + mask) . v in fp32 (src/models/transformer.h:240-277).
 // Arithmetic order per (row, head), restated identically by the CPU checker:
-//   s_p = fma-chain over i ascending of q_i * k_{p,i}, starting from 0;  s_p = s_p * scale;  s_p = s_p + mask_p
+//   thread j of the head: d_j = fma(q3,k3, fma(q2,k2, fma(q1,k1, q0*k0))) over its four elements
+//   s_p = butterfly over the G threads (d_j + d_{j^o}, o = G/2 .. 1);  s_p = s_p * scale;  s_p = s_p + mask_p
 //   mx = max_p s_p;  e_p = det_expf(s_p - mx)
-//   lane l accumulates e_p for p = l, l+32, ... in ascending order; sum = butterfly over the 32 lanes
+//   thread j accumulates e_p for p = j, j+G, ... ascending; sum = butterfly over the G threads
 //   w_p = e_p / sum;  out_i = fma-chain over p ascending of w_p * v_{p,i}, starting from 0.
 template <int DH>
 __global__ void __launch_bounds__(256)
 attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ log_mask, int heads, int len, int rows, int batch, int mode, float scale,
                   float* __restrict__ out, unsigned* absmax_slot) {
-  extern __shared__ float probs[];  // [warps][len]
+  extern __shared__ float sc_smem[];  // [heads][len] scores, then probabilities
+  constexpr int G = DH / 4;
   const int r = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int tid = threadIdx.x;
   const int dim = heads * DH;
+  const bool active = tid < dim / 4;
+  const int head = tid / G, j = tid % G;
   const int group = mode == 1 ? r % batch : (mode == 2 ? r / len : 0);
   const size_t base = mode == 0 ? static_cast<size_t>(r) : static_cast<size_t>(group) * len;
-  const size_t stride = mode == 0 ? static_cast<size_t>(rows) : 1;
+  const size_t stride = (mode == 0 ? static_cast<size_t>(rows) : 1) * dim;
   const float* mask = (mode != 0 && log_mask) ? log_mask + static_cast<size_t>(group) * len : nullptr;
-  float* p = probs + warp * len;
-  unsigned m_abs = 0u;
-  constexpr int PER = DH / 32;
-  for(int h = warp; h < heads; h += warps) {
-    const float4* qh = reinterpret_cast<const float4*>(q + static_cast<size_t>(r) * dim + h * DH);
-    float4 qreg[DH / 4];
+  const float4 qv = active ? __ldg(reinterpret_cast<const float4*>(q + static_cast<size_t>(r) * dim) + tid) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const float* kbase = k + base * dim + 4 * tid;
+  const float* vbase = v + base * dim + 4 * tid;
+  float* srow = sc_smem + (active ? head : 0) * len;
+
+  // scores: eight key rows in flight per thread
+  for(int p0 = 0; p0 < len; p0 += 8) {
+    float4 kk[8];
 #pragma unroll
-    for(int i = 0; i < DH / 4; ++i)
-      qreg[i] = __ldg(qh + i);
-    float mx = -FLT_MAX;
-    for(int pos = lane; pos < len; pos += 32) {
-      const float4* kr = reinterpret_cast<const float4*>(k + (base + pos * stride) * dim + h * DH);
-      float4 kk[DH / 4];
+    for(int u = 0; u < 8; ++u)
+      kk[u] = (active && p0 + u < len) ? __ldg(reinterpret_cast<const float4*>(kbase + (p0 + u) * stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for(int i = 0; i < DH / 4; ++i)
-        kk[i] = __ldg(kr + i);
-      float sc = 0.f;
+    for(int u = 0; u < 8; ++u) {
+      float d = __fmul_rn(qv.x, kk[u].x);
+      d = __fmaf_rn(qv.y, kk[u].y, d);
+      d = __fmaf_rn(qv.z, kk[u].z, d);
+      d = __fmaf_rn(qv.w, kk[u].w, d);
 #pragma unroll
-      for(int i = 0; i < DH / 4; ++i) {
-        sc = __fmaf_rn(qreg[i].x, kk[i].x, sc);
-        sc = __fmaf_rn(qreg[i].y, kk[i].y, sc);
-        sc = __fmaf_rn(qreg[i].z, kk[i].z, sc);
-        sc = __fmaf_rn(qreg[i].w, kk[i].w, sc);
+      for(int o = G / 2; o > 0; o >>= 1)
+        d = __fadd_rn(d, __shfl_xor_sync(0xffffffffu, d, o));
+      if(active && j == 0 && p0 + u < len) {
+        d = __fmul_rn(d, scale);
+        if(mask)
+          d = __fadd_rn(d, mask[p0 + u]);
+        srow[p0 + u] = d;
       }
-      sc = __fmul_rn(sc, scale);
-      if(mask)
-        sc = __fadd_rn(sc, mask[pos]);
-      p[pos] = sc;
-      mx = fmaxf(mx, sc);
     }
+  }
+  __syncthreads();
+  // softmax over the positions of this thread's head (the G threads of a head work together)
+  float mx = -FLT_MAX;
+  if(active)
+    for(int p = j; p < len; p += G)
+      mx = fmaxf(mx, srow[p]);
 #pragma unroll
-    for(int o = 16; o > 0; o >>= 1)
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float part = 0.f;
-    for(int pos = lane; pos < len; pos += 32) {
-      const float e = det_expf(__fadd_rn(p[pos], -mx));
-      p[pos] = e;
+  for(int o = G / 2; o > 0; o >>= 1)
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float part = 0.f;
+  if(active)
+    for(int p = j; p < len; p += G) {
+      const float e = det_expf(__fadd_rn(srow[p], -mx));
+      srow[p] = e;
       part = __fadd_rn(part, e);
     }
-    const float sum = warp_sum_det(part);
-    for(int pos = lane; pos < len; pos += 32)
-      p[pos] = __fdiv_rn(p[pos], sum);
-    __syncwarp();
-    // weighted sum of values: a lane owns PER consecutive output elements; loads are issued eight
-    // positions ahead of the (strictly ordered) fma chain
-    float acc[PER];
 #pragma unroll
-    for(int i = 0; i < PER; ++i)
-      acc[i] = 0.f;
-    const float* vbase = v + base * dim + h * DH + lane * PER;
-    const size_t vstep = stride * dim;
-    int pos = 0;
-    for(; pos + 8 <= len; pos += 8) {
-      float vv[8][PER];
+  for(int o = G / 2; o > 0; o >>= 1)
+    part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
+  if(active)
+    for(int p = j; p < len; p += G)
+      srow[p] = __fdiv_rn(srow[p], part);
+  __syncthreads();
+  // weighted sum of the value rows, strictly in position order, loads eight rows ahead
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for(int p0 = 0; p0 < len; p0 += 8) {
+    float4 vv[8];
 #pragma unroll
-      for(int u = 0; u < 8; ++u)
+    for(int u = 0; u < 8; ++u)
+      vv[u] = (active && p0 + u < len) ? __ldg(reinterpret_cast<const float4*>(vbase + (p0 + u) * stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for(int i = 0; i < PER; ++i)
-          vv[u][i] = __ldg(vbase + (pos + u) * vstep + i);
-#pragma unroll
-      for(int u = 0; u < 8; ++u) {
-        const float w = p[pos + u];
-#pragma unroll
-        for(int i = 0; i < PER; ++i)
-          acc[i] = __fmaf_rn(w, vv[u][i], acc[i]);
+    for(int u = 0; u < 8; ++u) {
+      if(p0 + u < len) {
+        const float w = srow[p0 + u];
+        acc.x = __fmaf_rn(w, vv[u].x, acc.x);
+        acc.y = __fmaf_rn(w, vv[u].y, acc.y);
+        acc.z = __fmaf_rn(w, vv[u].z, acc.z);
+        acc.w = __fmaf_rn(w, vv[u].w, acc.w);
       }
     }
-    for(; pos < len; ++pos) {
-      const float w = p[pos];
-#pragma unroll
-      for(int i = 0; i < PER; ++i)
-        acc[i] = __fmaf_rn(w, __ldg(vbase + pos * vstep + i), acc[i]);
-    }
-    float* o = out + static_cast<size_t>(r) * dim + h * DH + lane * PER;
-#pragma unroll
-    for(int i = 0; i < PER; ++i) {
-      o[i] = acc[i];
-      m_abs = max(m_abs, abs_bits(acc[i]));
-    }
-    __syncwarp();
+  }
+  unsigned m_abs = 0u;
+  if(active) {
+    reinterpret_cast<float4*>(out + static_cast<size_t>(r) * dim)[tid] = acc;
+    m_abs = max4u(0u, acc);
   }
   if(absmax_slot) {
     m_abs = __reduce_max_sync(0xffffffffu, m_abs);
-    if(lane == 0)
+    if((tid & 31) == 0 && m_abs != 0u)
       atomicMax(absmax_slot, m_abs);
   }
 }
@@ -562,7 +555,9 @@ int launch_ancestors_update(const int* anc_old, int* anc_new, const int* hyp, in
 }
 
 int launch_history_absmax(const float* rowmax, const int* anc, int steps, int rows, int stride, unsigned* slot, cudaStream_t s) {
-  history_absmax_kernel<<<1, 1024, 0, s>>>(rowmax, anc, steps, rows, stride, slot);
+  int blocks = (steps * rows + 1023) / 1024;
+  blocks = blocks < 1 ? 1 : (blocks > 128 ? 128 : blocks);
+  history_absmax_kernel<<<blocks, 256, 0, s>>>(rowmax, anc, steps, rows, stride, slot);
   count_launch();
   return check_launch();
 }
@@ -583,14 +578,17 @@ int launch_attention1(const float* q, const float* k, const float* v, const floa
   if(mode < 0 || mode > 2)
     return MI8_ERR_BAD_ARG;
   const float scale = 1.0f / sqrtf(static_cast<float>(dim_head));
-  const int warps = heads < 8 ? heads : 8;
-  const size_t smem = static_cast<size_t>(warps) * len * sizeof(float);
+  const int dim = heads * dim_head;
+  if(dim > 1024)
+    return MI8_ERR_UNSUPPORTED;
+  const int threads = ((dim / 4 + 31) / 32) * 32;
+  const size_t smem = static_cast<size_t>(heads) * len * sizeof(float);
   if(smem > 48 * 1024)
     return MI8_ERR_UNSUPPORTED;
   if(dim_head == 64)
-    attention1_kernel<64><<<rows, warps * 32, smem, s>>>(q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
+    attention1_kernel<64><<<rows, threads, smem, s>>>(q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
   else if(dim_head == 32)
-    attention1_kernel<32><<<rows, warps * 32, smem, s>>>(q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
+    attention1_kernel<32><<<rows, threads, smem, s>>>(q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
   else
     return MI8_ERR_UNSUPPORTED;
   count_launch();

@@ -351,12 +351,25 @@ MO_FMA_CLONES void mo_add_layernorm(const float* a, const float* resid, const fl
   free(y);
 }
 
+/* v[j] <- v[j] + v[j ^ o] for o = g/2 .. 1 over a group of g entries (g a power of two <= 32) */
+static inline float mo_group_sum(const float* v, int g) {
+  float a[32], b[32];
+  memcpy(a, v, sizeof(float) * (size_t)g);
+  for(int o = g / 2; o > 0; o >>= 1) {
+    for(int i = 0; i < g; ++i) b[i] = a[i] + a[i ^ o];
+    memcpy(a, b, sizeof(float) * (size_t)g);
+  }
+  return a[0];
+}
+
 /* Single-query attention; key/value row of position p for query row r is base(r) + p*stride:
  * mode 0: base = r, stride = rows (time-major history); mode 1: base = (r % batch)*len (cross-attention);
- * mode 2: base = (r / len)*len (encoder self-attention, rows ordered [batch, len]). */
+ * mode 2: base = (r / len)*len (encoder self-attention, rows ordered [batch, len]).
+ * A head is handled by g = dh/4 workers, worker j owning elements 4j..4j+3 of the head. */
 MO_FMA_CLONES void mo_attention1(const float* q, const float* k, const float* v, const float* log_mask, int rows, int heads, int dh,
                                  int len, int batch, int mode, float* out) {
   const int dim = heads * dh;
+  const int g = dh / 4;
   const float scale = 1.0f / sqrtf((float)dh);
   float* p = (float*)malloc(sizeof(float) * (size_t)len);
   for(int r = 0; r < rows; ++r) {
@@ -369,21 +382,28 @@ MO_FMA_CLONES void mo_attention1(const float* q, const float* k, const float* v,
       float mx = -FLT_MAX;
       for(int pos = 0; pos < len; ++pos) {
         const float* kr = k + (base + pos * stride) * dim + h * dh;
-        float s = 0.0f;
-        for(int i = 0; i < dh; ++i) s = fmaf(qh[i], kr[i], s);
+        float d[32];
+        for(int j = 0; j < g; ++j) {
+          float t = qh[4 * j] * kr[4 * j];
+          t = fmaf(qh[4 * j + 1], kr[4 * j + 1], t);
+          t = fmaf(qh[4 * j + 2], kr[4 * j + 2], t);
+          t = fmaf(qh[4 * j + 3], kr[4 * j + 3], t);
+          d[j] = t;
+        }
+        float s = mo_group_sum(d, g);
         s = s * scale;
         if(mask) s = s + mask[pos];
         p[pos] = s;
         if(s > mx) mx = s;
       }
       float part[32];
-      for(int l = 0; l < 32; ++l) part[l] = 0.0f;
+      for(int j = 0; j < g; ++j) part[j] = 0.0f;
       for(int pos = 0; pos < len; ++pos) {
         const float e = mo_det_expf_i(p[pos] + -mx);
         p[pos] = e;
-        part[pos & 31] = part[pos & 31] + e;
+        part[pos % g] = part[pos % g] + e;
       }
-      const float sum = mo_warp_sum(part);
+      const float sum = mo_group_sum(part, g);
       for(int pos = 0; pos < len; ++pos) p[pos] = p[pos] / sum;
       float* o = out + (size_t)r * dim + h * dh;
       for(int i = 0; i < dh; ++i) {

@@ -43,7 +43,7 @@ def test_strerror_and_version():
     assert L.mi8_strerror(99) == b"unknown status"
 
 
-@pytest.mark.parametrize("m,expect_tile", [(1, 16), (16, 16), (17, 32), (64, 64), (65, 128), (200, 256), (512, 256)])
+@pytest.mark.parametrize("m,expect_tile", [(1, 16), (16, 16), (17, 32), (64, 64), (65, 32), (128, 32), (200, 64), (512, 128), (8192, 256)])
 def test_plan_tile_choice(m, expect_tile):
     from marian_dev_b200 import multiply_plan
     p = multiply_plan(m, 1024, 1024)
