@@ -151,6 +151,11 @@ int mi8_multiply_i8_static(const int8_t* aq, const int8_t* bt, int M, int N, int
  * out[5]=CTAs launched, out[6]=dynamic shared memory bytes, out[7]=SM count. */
 int mi8_multiply_plan(int M, int N, int K, int force_tile_m, int force_splits, int out[8]);
 
+/* Programmatic dependent launch: when enabled (the default) every kernel of the library is launched so
+ * that its set-up (and, in the GEMM, the first weight tiles) overlaps the tail of the previous kernel on
+ * the stream; each kernel waits for its predecessor before touching dependent data.  Process-wide switch. */
+void mi8_set_pdl(int enabled);
+
 /* Measurement aid: between mi8_profile_begin and mi8_profile_end every GEMM launch made by the calling
  * thread is bracketed by CUDA events on its stream; mi8_profile_end waits for them and returns one record
  * per launch (at most `capacity`).  Off by default; costs two cudaEventRecord calls per launch when on. */

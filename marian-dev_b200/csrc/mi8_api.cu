@@ -18,6 +18,12 @@ int* g_status_ptr[64] = {};
 int g_sm_count[64] = {};
 }  // namespace
 
+namespace {
+bool g_pdl = true;
+}
+bool pdl_enabled() { return g_pdl; }
+void set_pdl(bool on) { g_pdl = on; }
+
 void set_last_cuda_error(cudaError_t e) { t_last_error = e; }
 void count_launch() { ++t_launches; }
 
@@ -208,6 +214,8 @@ int mi8_affine_f32(const float* a, int M, int K, const int8_t* bt, const float* 
   return launch_gemm(aq_scratch, bt, M, N, K, d_qa, d_qb, scale, bias, relu, c, out_dtype, nullptr, workspace,
                      workspace_bytes, as_stream(stream), 0, 0);
 }
+
+void mi8_set_pdl(int enabled) { set_pdl(enabled != 0); }
 
 int mi8_profile_begin(int max_records) { return profile_begin(max_records); }
 int mi8_profile_end(mi8_gemm_record* records, int capacity, int* count) { return profile_end(records, capacity, count); }

@@ -119,6 +119,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  pdl_launch_dependents();  // the next kernel on the stream may begin its own set-up now
   if(threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_a);
@@ -148,21 +149,38 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 
   if(warp == 0) {
     // ------------------------------------------------------------ TMA producer
+    // The weights do not depend on the previous kernel: the weight tiles of the first pipeline fill
+    // are requested before waiting for it, the activation tiles (its output) after.
     uint32_t it = 0;
+    uint32_t prefetched = 0;  // stages whose weight tile is already in flight
+    if(lane == 0) {
+      const WorkItem w0 = decode_work(p, blockIdx.x);
+      const int n_pre = min(T::kStages, w0.kb_end - w0.kb_begin);
+      for(int i = 0; i < n_pre; ++i) {
+        uint8_t* st = tiles + i * T::kStageBytes;
+        mbar_arrive_expect_tx(&ctl->full[i], T::kStageBytes);
+        tma_load_2d(st, &tmap_w, (w0.kb_begin + i) * kTileKBytes, w0.n_tile * kTileN, &ctl->full[i]);
+      }
+      prefetched = n_pre;
+    }
+    pdl_wait();
     for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
       const WorkItem wi = decode_work(p, w);
       for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
         const uint32_t s = it % T::kStages;
         const uint32_t ph = (it / T::kStages) & 1u;
-        if(lane == 0)
+        const bool pre = lane == 0 && it < prefetched;
+        if(lane == 0 && !pre)
           ok = mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if(!ok)
           break;
         if(lane == 0) {
           uint8_t* st = tiles + s * T::kStageBytes;
-          mbar_arrive_expect_tx(&ctl->full[s], T::kStageBytes);
-          tma_load_2d(st, &tmap_w, kb * kTileKBytes, wi.n_tile * kTileN, &ctl->full[s]);
+          if(!pre) {
+            mbar_arrive_expect_tx(&ctl->full[s], T::kStageBytes);
+            tma_load_2d(st, &tmap_w, kb * kTileKBytes, wi.n_tile * kTileN, &ctl->full[s]);
+          }
           tma_load_2d(st + T::kWBytes, &tmap_a, kb * kTileKBytes, wi.m_tile * TM, &ctl->full[s]);
         }
         __syncwarp();
@@ -238,6 +256,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     constexpr int kChunks = TM / T::kChunk;
     constexpr int kChunkStep = kChunks > 1 ? 2 : 1;
     const bool has_chunks = kChunks > 1 || group == 0;
+    pdl_wait();  // the activation multiplier is written by the previous kernel
     const float unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(*p.d_qa, *p.d_qb)), p.scale);
     uint32_t acc_it = 0;
     for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++acc_it) {
@@ -479,7 +498,11 @@ int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p
     if(rec.start != nullptr && rec.stop != nullptr)
       cudaEventRecord(rec.start, stream);
   }
-  mi8_gemm_kernel<TM><<<plan.grid, kThreads, smem, stream>>>(tw, ta, p);
+  cudaError_t le = launch_kernel(mi8_gemm_kernel<TM>, dim3(plan.grid), dim3(kThreads), smem, stream, tw, ta, p);
+  if(le != cudaSuccess) {
+    set_last_cuda_error(le);
+    return MI8_ERR_LAUNCH;
+  }
   if(profiled && rec.start != nullptr && rec.stop != nullptr) {
     cudaEventRecord(rec.stop, stream);
     t_profile.records.push_back(rec);

@@ -43,6 +43,8 @@ __device__ __forceinline__ unsigned max4u(unsigned m, const float4& v) {
 __global__ void __launch_bounds__(kRowThreads)
 embed_kernel(const float* __restrict__ wemb, const int* __restrict__ words, const float* __restrict__ pos, int pos_mod, float scale,
              int dim, float* __restrict__ out, float* __restrict__ rowmax, unsigned* absmax_slot) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ unsigned red[kRowThreads / 32];
   const int r = blockIdx.x;
   const float4* src = words ? reinterpret_cast<const float4*>(wemb + static_cast<size_t>(words[r]) * dim) : nullptr;
@@ -80,6 +82,8 @@ __global__ void __launch_bounds__(kRowThreads)
 add_layernorm_kernel(const float* __restrict__ a, const float* __restrict__ resid, const float* __restrict__ gamma,
                      const float* __restrict__ beta, float eps, int dim, float* __restrict__ out, float* __restrict__ rowmax,
                      unsigned* absmax_slot) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float redf[kRowThreads / 32];
   __shared__ unsigned redu[kRowThreads / 32];
   const int r = blockIdx.x;
@@ -156,6 +160,8 @@ __device__ __forceinline__ float quant_mult_from_bits(unsigned bits) {
 __global__ void __launch_bounds__(256)
 quantize_slot_kernel(const float* __restrict__ x, size_t n, const unsigned* __restrict__ absmax_slot, int8_t* __restrict__ q,
                      float* __restrict__ d_quant_mult, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   const unsigned bits = *absmax_slot;
   const float qm = quant_mult_from_bits(bits);
   if(blockIdx.x == 0 && threadIdx.x == 0) {
@@ -188,6 +194,8 @@ quantize_slot_kernel(const float* __restrict__ x, size_t n, const unsigned* __re
 // anc_new[t'][r] = anc_old[t'][hyp[r]] (t' < t), anc_new[t][r] = r.
 __global__ void ancestors_update_kernel(const int* __restrict__ anc_old, int* __restrict__ anc_new, const int* __restrict__ hyp,
                                         int t, int rows, int stride) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if(i >= (t + 1) * rows)
     return;
@@ -199,6 +207,8 @@ __global__ void ancestors_update_kernel(const int* __restrict__ anc_old, int* __
 __global__ void __launch_bounds__(256)
 history_absmax_kernel(const float* __restrict__ rowmax, const int* __restrict__ anc, int steps, int rows, int stride,
                       unsigned* absmax_slot) {
+  pdl_launch_dependents();
+  pdl_wait();
   unsigned m = 0u;
   const int n = steps * rows;
   for(int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
@@ -214,6 +224,8 @@ history_absmax_kernel(const float* __restrict__ rowmax, const int* __restrict__ 
 __global__ void __launch_bounds__(128)
 history_quantize_kernel(const float* __restrict__ slabs, size_t slab_stride, const int* __restrict__ anc, int anc_stride, int rows,
                         int dim, const unsigned* __restrict__ absmax_slot, int8_t* __restrict__ hq, float* __restrict__ d_quant_mult) {
+  pdl_launch_dependents();
+  pdl_wait();
   const float qm = quant_mult_from_bits(*absmax_slot);
   const int out_row = blockIdx.x;
   const int tp = out_row / rows, r = out_row - tp * rows;
@@ -250,6 +262,8 @@ __global__ void __launch_bounds__(256)
 attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ log_mask, int heads, int len, int rows, int batch, int mode, float scale,
                   float* __restrict__ out, unsigned* absmax_slot) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float sc_smem[];  // [heads][len] scores, then probabilities
   constexpr int G = DH / 4;
   const int r = blockIdx.x;
@@ -378,6 +392,8 @@ template <int K>
 __global__ void __launch_bounds__(256)
 lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ prev_scores, float* __restrict__ cand_score,
                 int* __restrict__ cand_word) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float s_v[256 * K];
   __shared__ int s_i[256 * K];
   __shared__ float redf[8];
@@ -450,6 +466,8 @@ lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __rest
 template <int K>
 __global__ void nbest_merge_kernel(const float* __restrict__ cand_score, const int* __restrict__ cand_word, int beam, int batch,
                                    int vocab, float* __restrict__ out_score, int* __restrict__ out_beam, int* __restrict__ out_word) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if(b >= batch)
     return;
@@ -479,6 +497,8 @@ __global__ void nbest_merge_kernel(const float* __restrict__ cand_score, const i
 
 // rows gather: out[i,:] = in[idx[i],:]  (16-byte copies when the row length allows it)
 __global__ void gather_rows_kernel(const float* __restrict__ in, const int* __restrict__ idx, int dim, float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* src = in + static_cast<size_t>(idx[r]) * dim;
   float* dst = out + static_cast<size_t>(r) * dim;
@@ -497,6 +517,8 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const int* __re
 // Writes the new cell state and y = LayerNorm(h + resid) * gamma + beta is done by add_layernorm on h.
 __global__ void ssru_cell_kernel(const float* __restrict__ cell_old, const int* __restrict__ hyp, const float* __restrict__ xw,
                                  const float* __restrict__ f, int dim, float* __restrict__ cell_new, float* __restrict__ h_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* c = cell_old + static_cast<size_t>(hyp ? hyp[r] : r) * dim;
   for(int i = threadIdx.x; i < dim; i += blockDim.x) {
@@ -517,7 +539,7 @@ int launch_embed(const float* wemb, const int* words, const float* pos, int pos_
                  float* rowmax, unsigned* slot, cudaStream_t s) {
   if(rows <= 0 || dim <= 0 || dim % 4 != 0 || dim > kRowThreads * 4 * kMaxVec || out == nullptr || pos == nullptr)
     return MI8_ERR_BAD_ARG;
-  embed_kernel<<<rows, kRowThreads, 0, s>>>(wemb, words, pos, pos_mod, scale, dim, out, rowmax, slot);
+  launch_kernel(embed_kernel, dim3(rows), dim3(kRowThreads), 0, s, wemb, words, pos, pos_mod, scale, dim, out, rowmax, slot);
   count_launch();
   return check_launch();
 }
@@ -526,7 +548,7 @@ int launch_add_layernorm(const float* a, const float* resid, const float* gamma,
                          float* out, float* rowmax, unsigned* slot, cudaStream_t s) {
   if(rows <= 0 || dim <= 0 || dim % 4 != 0 || dim > kRowThreads * 4 * kMaxVec || a == nullptr || out == nullptr)
     return MI8_ERR_BAD_ARG;
-  add_layernorm_kernel<<<rows, kRowThreads, 0, s>>>(a, resid, gamma, beta, eps, dim, out, rowmax, slot);
+  launch_kernel(add_layernorm_kernel, dim3(rows), dim3(kRowThreads), 0, s, a, resid, gamma, beta, eps, dim, out, rowmax, slot);
   count_launch();
   return check_launch();
 }
@@ -542,14 +564,14 @@ int launch_quantize_slot(const float* x, size_t n, const unsigned* slot, int8_t*
   size_t blocks = (n / 16 + 255) / 256;
   const size_t cap = static_cast<size_t>(sm_count()) * 8;
   blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
-  quantize_slot_kernel<<<static_cast<int>(blocks), 256, 0, s>>>(x, n, slot, q, d_qm, status);
+  launch_kernel(quantize_slot_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, s, x, n, slot, q, d_qm, status);
   count_launch();
   return check_launch();
 }
 
 int launch_ancestors_update(const int* anc_old, int* anc_new, const int* hyp, int t, int rows, int stride, cudaStream_t s) {
   const int n = (t + 1) * rows;
-  ancestors_update_kernel<<<(n + 255) / 256, 256, 0, s>>>(anc_old, anc_new, hyp, t, rows, stride);
+  launch_kernel(ancestors_update_kernel, dim3((n + 255) / 256), dim3(256), 0, s, anc_old, anc_new, hyp, t, rows, stride);
   count_launch();
   return check_launch();
 }
@@ -557,7 +579,7 @@ int launch_ancestors_update(const int* anc_old, int* anc_new, const int* hyp, in
 int launch_history_absmax(const float* rowmax, const int* anc, int steps, int rows, int stride, unsigned* slot, cudaStream_t s) {
   int blocks = (steps * rows + 1023) / 1024;
   blocks = blocks < 1 ? 1 : (blocks > 128 ? 128 : blocks);
-  history_absmax_kernel<<<blocks, 256, 0, s>>>(rowmax, anc, steps, rows, stride, slot);
+  launch_kernel(history_absmax_kernel, dim3(blocks), dim3(256), 0, s, rowmax, anc, steps, rows, stride, slot);
   count_launch();
   return check_launch();
 }
@@ -566,7 +588,7 @@ int launch_history_quantize(const float* slabs, size_t slab_stride, const int* a
                             const unsigned* slot, int8_t* hq, float* d_qm, cudaStream_t s) {
   if(dim % 16 != 0)
     return MI8_ERR_MISALIGNED;
-  history_quantize_kernel<<<steps * rows, 128, 0, s>>>(slabs, slab_stride, anc, anc_stride, rows, dim, slot, hq, d_qm);
+  launch_kernel(history_quantize_kernel, dim3(steps * rows), dim3(128), 0, s, slabs, slab_stride, anc, anc_stride, rows, dim, slot, hq, d_qm);
   count_launch();
   return check_launch();
 }
@@ -586,9 +608,9 @@ int launch_attention1(const float* q, const float* k, const float* v, const floa
   if(smem > 48 * 1024)
     return MI8_ERR_UNSUPPORTED;
   if(dim_head == 64)
-    attention1_kernel<64><<<rows, threads, smem, s>>>(q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
+    launch_kernel(attention1_kernel<64>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
   else if(dim_head == 32)
-    attention1_kernel<32><<<rows, threads, smem, s>>>(q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
+    launch_kernel(attention1_kernel<32>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
   else
     return MI8_ERR_UNSUPPORTED;
   count_launch();
@@ -600,14 +622,14 @@ int launch_lse_topk(const float* logits, int rows, int vocab, int k, const float
   if(rows <= 0 || vocab <= 0 || k < 1 || k > kMaxK)
     return MI8_ERR_BAD_ARG;
   switch(k) {
-    case 1: lse_topk_kernel<1><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 2: lse_topk_kernel<2><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 3: lse_topk_kernel<3><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 4: lse_topk_kernel<4><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 5: lse_topk_kernel<5><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 6: lse_topk_kernel<6><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 7: lse_topk_kernel<7><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
-    default: lse_topk_kernel<8><<<rows, 256, 0, s>>>(logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 1: launch_kernel(lse_topk_kernel<1>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 2: launch_kernel(lse_topk_kernel<2>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 3: launch_kernel(lse_topk_kernel<3>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 4: launch_kernel(lse_topk_kernel<4>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 5: launch_kernel(lse_topk_kernel<5>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 6: launch_kernel(lse_topk_kernel<6>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 7: launch_kernel(lse_topk_kernel<7>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    default: launch_kernel(lse_topk_kernel<8>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
   }
   count_launch();
   return check_launch();
@@ -619,14 +641,14 @@ int launch_nbest_merge(const float* cand_score, const int* cand_word, int beam, 
     return MI8_ERR_BAD_ARG;
   const int blocks = (batch + 127) / 128;
   switch(k) {
-    case 1: nbest_merge_kernel<1><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
-    case 2: nbest_merge_kernel<2><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
-    case 3: nbest_merge_kernel<3><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
-    case 4: nbest_merge_kernel<4><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
-    case 5: nbest_merge_kernel<5><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
-    case 6: nbest_merge_kernel<6><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
-    case 7: nbest_merge_kernel<7><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
-    default: nbest_merge_kernel<8><<<blocks, 128, 0, s>>>(cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 1: launch_kernel(nbest_merge_kernel<1>, dim3(blocks), dim3(128), 0, s, cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 2: launch_kernel(nbest_merge_kernel<2>, dim3(blocks), dim3(128), 0, s, cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 3: launch_kernel(nbest_merge_kernel<3>, dim3(blocks), dim3(128), 0, s, cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 4: launch_kernel(nbest_merge_kernel<4>, dim3(blocks), dim3(128), 0, s, cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 5: launch_kernel(nbest_merge_kernel<5>, dim3(blocks), dim3(128), 0, s, cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 6: launch_kernel(nbest_merge_kernel<6>, dim3(blocks), dim3(128), 0, s, cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    case 7: launch_kernel(nbest_merge_kernel<7>, dim3(blocks), dim3(128), 0, s, cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
+    default: launch_kernel(nbest_merge_kernel<8>, dim3(blocks), dim3(128), 0, s, cand_score, cand_word, beam, batch, vocab, out_score, out_beam, out_word); break;
   }
   count_launch();
   return check_launch();
@@ -635,14 +657,14 @@ int launch_nbest_merge(const float* cand_score, const int* cand_word, int beam, 
 int launch_gather_rows(const float* in, const int* idx, int rows, int dim, float* out, cudaStream_t s) {
   if(rows <= 0 || dim <= 0)
     return MI8_ERR_BAD_ARG;
-  gather_rows_kernel<<<rows, 128, 0, s>>>(in, idx, dim, out);
+  launch_kernel(gather_rows_kernel, dim3(rows), dim3(128), 0, s, in, idx, dim, out);
   count_launch();
   return check_launch();
 }
 
 int launch_ssru_cell(const float* cell_old, const int* hyp, const float* xw, const float* f, int rows, int dim, float* cell_new,
                      float* h_out, cudaStream_t s) {
-  ssru_cell_kernel<<<rows, 256, 0, s>>>(cell_old, hyp, xw, f, dim, cell_new, h_out);
+  launch_kernel(ssru_cell_kernel, dim3(rows), dim3(256), 0, s, cell_old, hyp, xw, f, dim, cell_new, h_out);
   count_launch();
   return check_launch();
 }

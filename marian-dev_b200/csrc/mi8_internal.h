@@ -85,6 +85,26 @@ int launch_gather_rows(const float* in, const int* idx, int rows, int dim, float
 int launch_ssru_cell(const float* cell_old, const int* hyp, const float* xw, const float* f, int rows, int dim, float* cell_new,
                      float* h_out, cudaStream_t s);
 
+// Whether kernels are launched with programmatic dependent launch (mi8_set_pdl; on by default).
+bool pdl_enabled();
+void set_pdl(bool on);
+
+// Launches `kernel` with or without the programmatic-stream-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline cudaStream_t as_stream(void* s) { return s ? reinterpret_cast<cudaStream_t>(s) : cudaStreamPerThread; }
 
 }  // namespace mi8

@@ -41,6 +41,8 @@ __device__ __forceinline__ unsigned block_max(unsigned m, unsigned* smem) {
 __global__ void __launch_bounds__(kBlock)
 mi8_absmax_kernel(const float* __restrict__ x, size_t n, unsigned* partials, unsigned* counter, float* d_absmax,
                   float* d_quant_mult, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ unsigned red[kBlock / 32];
   __shared__ int is_last;
   unsigned m = 0u;
@@ -101,6 +103,8 @@ __device__ __forceinline__ unsigned pack4(const float4& v, float qm) {
 // 16 floats in (four 16-byte loads), 16 int8 out (one 16-byte store) per thread and iteration.
 __global__ void __launch_bounds__(kBlock)
 mi8_quantize_kernel(const float* __restrict__ x, size_t n, const float* __restrict__ d_quant_mult, int8_t* __restrict__ q) {
+  pdl_launch_dependents();
+  pdl_wait();
   const float qm = *d_quant_mult;
   const size_t n16 = n / 16;
   const float4* x4 = reinterpret_cast<const float4*>(x);
@@ -128,6 +132,8 @@ mi8_quantize_kernel(const float* __restrict__ x, size_t n, const float* __restri
 __global__ void __launch_bounds__(256)
 mi8_transpose_quantize_kernel(const float* __restrict__ w, int K, int N, const float* __restrict__ d_quant_mult,
                               int8_t* __restrict__ bt) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float tile[32][33];
   const float qm = *d_quant_mult;
   const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
@@ -174,7 +180,7 @@ int launch_max_absolute(const float* x, size_t n, float* d_absmax, float* d_quan
   int grid = stream_grid(n / 4 + 1);
   if(grid > kWsMaxAbsmaxBlocks)
     grid = kWsMaxAbsmaxBlocks;
-  mi8_absmax_kernel<<<grid, kBlock, 0, stream>>>(x, n, reinterpret_cast<unsigned*>(wsb + kWsOffAbsmaxPartials),
+  launch_kernel(mi8_absmax_kernel, dim3(grid), dim3(kBlock), 0, stream, x, n, reinterpret_cast<unsigned*>(wsb + kWsOffAbsmaxPartials),
                                                  reinterpret_cast<unsigned*>(wsb + kWsOffAbsmaxCounter), d_absmax,
                                                  d_quant_mult, status);
   count_launch();
@@ -187,7 +193,7 @@ int launch_quantize(const float* x, size_t n, const float* d_quant_mult, int8_t*
   if((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(q) & 15u))
     return MI8_ERR_MISALIGNED;
   const int grid = stream_grid(n / 16 + 1);
-  mi8_quantize_kernel<<<grid, kBlock, 0, stream>>>(x, n, d_quant_mult, q);
+  launch_kernel(mi8_quantize_kernel, dim3(grid), dim3(kBlock), 0, stream, x, n, d_quant_mult, q);
   count_launch();
   return check_launch();
 }
@@ -198,7 +204,7 @@ int launch_transpose_quantize(const float* w, int K, int N, const float* d_quant
   dim3 grid((N + 31) / 32, (K + 31) / 32);
   if(grid.y > 65535)
     return MI8_ERR_UNSUPPORTED;
-  mi8_transpose_quantize_kernel<<<grid, 256, 0, stream>>>(w, K, N, d_quant_mult, bt);
+  launch_kernel(mi8_transpose_quantize_kernel, dim3(grid), dim3(256), 0, stream, w, K, N, d_quant_mult, bt);
   count_launch();
   return check_launch();
 }
