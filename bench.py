@@ -43,6 +43,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="big", help="big (the benchmark), base, student, tiny (debugging)")
     ap.add_argument("--cpu-sentences", type=int, default=8, help="sentences in the CPU-baseline sample")
+    ap.add_argument("--affine", default=None, help="M,K,N: time one int8 affine (abs-max + quantise + GEMM with bias and ReLU) instead of the decode")
+    ap.add_argument("--sweep", action="store_true", help="time the affine shape sweep M x K x N instead of the decode")
     return ap.parse_args()
 
 
@@ -341,9 +343,71 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ----------------------------------------------------------------------------- single affines (parity-config shapes)
+def time_affine(m, k, n, iters=40):
+    """One affine = prepareA (abs-max + quantise) + GEMM with fused bias/ReLU, through the C ABI, on operand
+    sets rotated through more than the L2 capacity; returns a dict for one JSON line."""
+    import torch
+    from marian_dev_b200 import ops
+    dev = torch.device("cuda", torch.cuda.current_device())
+    per_copy = 4 * m * k + n * k + 4 * m * n
+    copies = max(2, min(32, int(300e6 // per_copy) + 1))
+    xs = [torch.randn(m, k, device=dev) for _ in range(copies)]
+    ws = [ops.prepareB(torch.randn(k, n, device=dev) * 0.02) for _ in range(copies)]
+    bias = torch.randn(n, device=dev) * 0.01
+    outs = [torch.empty(m, n, device=dev) for _ in range(copies)]
+    aq = [ops.IntgemmTensor(m, k, dev) for _ in range(copies)]
+
+    def run(i):
+        j = i % copies
+        ops.prepareA(xs[j], out=aq[j])
+        ops.multiply(aq[j], ws[j], bias, 1.0, True, out=outs[j])
+
+    for i in range(5):
+        run(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            for i in range(iters):
+                run(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        g.replay()
+        e1.record(s)
+        torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1000.0 / iters
+    by = 4 * m * k + k * n + 4 * n + 4 * m * n + 8
+    return {"M": m, "K": k, "N": n, "us_per_affine": round(us, 2), "GBps": round(by / us / 1e3, 1), "TOPS": round(2.0 * m * n * k / us / 1e6, 2),
+            "algorithmic_bytes": by, "launches_per_affine": 3, "operand_sets": copies}
+
+
+def run_affines(args):
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the int8 engine has no CPU path")
+    warm = torch.randn(8192, 8192, device="cuda", dtype=torch.bfloat16)
+    for _ in range(30):
+        warm @ warm                                   # bring the clocks up before timing microsecond kernels
+    torch.cuda.synchronize()
+    if args.affine:
+        shapes = [tuple(int(v) for v in args.affine.split(","))]
+    else:
+        shapes = [(m, k, n) for m in (1, 8, 64, 256, 1024, 4096) for k in (512, 1024, 4096) for n in (512, 2048, 4096, 32000)]
+    for (m, k, n) in shapes:
+        r = time_affine(m, k, n)
+        r.update({"metric": "int8_affine", "timing": "CUDA-graph replay of 40 affines, CUDA events, operand sets rotated through > L2"})
+        print(json.dumps(r), flush=True)
+
+
 if __name__ == "__main__":
     a = parse_args()
-    if a.impl == "reference":
+    if a.affine or a.sweep:
+        run_affines(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_ours(a)
