@@ -149,7 +149,7 @@ def run_ours(args):
     import numpy as np
     import torch
     import torch.distributed as dist
-    from marian_dev_b200 import decoder, model, ops
+    from marian_dev_b200 import decoder, model, ops, parallel
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -166,7 +166,7 @@ def run_ours(args):
     del params
     per_rank = args.warmup + args.steps                          # both timed legs decode the same mini-batches
     batches = build_corpus(model, cfg, per_rank * world)
-    mine = [batches[i] for i in range(rank, len(batches), world)][:per_rank]
+    mine = parallel.shard_batches(batches, rank, world)[:per_rank]
     stepper = decoder.NativeStepper(net, max_batch=MINI_BATCH, beam=BEAM, max_src=136, max_steps=208)
     search = decoder.BeamSearch(net, beam=BEAM, max_length_factor=1.5, normalize=1.0, native=stepper)
 
@@ -176,17 +176,10 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def gather_outputs(results):
-        """The path's one collective: every rank contributes its [sentences, max_len] token matrix."""
-        if world == 1:
-            return results
-        mat = torch.full((MINI_BATCH, 192), -1, dtype=torch.int32)       # 192 = 1.5 x the longest source
-        for r, (toks, _s) in enumerate(results):
-            mat[r, :len(toks)] = torch.tensor(toks, dtype=torch.int32)
-        g = mat.to(dev)
-        out = [torch.empty_like(g) for _ in range(world)]
-        dist.all_gather(out, g)
-        return out
+    def gather_outputs(sent_ids, results):
+        """The path's one collective: every rank contributes its {sentence id: tokens}; all receive the union."""
+        local = {int(sid): toks for sid, (toks, _s) in zip(sent_ids, results)}
+        return parallel.gather_outputs(local, max_len=192, device=dev)   # 192 = 1.5 x the longest source
 
     # warm-up
     for b in mine[:args.warmup]:
@@ -195,7 +188,7 @@ def run_ours(args):
 
     # ---- leg 1: inputs resident in HBM ------------------------------------------------------
     leg1 = mine[args.warmup:args.warmup + args.steps]
-    resident = [(torch.from_numpy(ids.astype(np.int64)).to(dev), torch.from_numpy(mask).to(dev)) for _, ids, mask in leg1]
+    resident = [(sid, torch.from_numpy(ids.astype(np.int64)).to(dev), torch.from_numpy(mask).to(dev)) for sid, ids, mask in leg1]
     sampler = ClockSampler(local_rank)
     ops.reset_launch_count()
     tokens = 0
@@ -204,9 +197,9 @@ def run_ours(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with GemmTimer() as gt:
         e0.record()
-        for ids_t, mask_t in resident:
+        for sid, ids_t, mask_t in resident:
             res = search.search_device(ids_t, mask_t)
-            gather_outputs(res)
+            gather_outputs(sid, res)
             tokens += sum(len(t) for t, _ in res)
         e1.record()
         barrier()
@@ -217,15 +210,15 @@ def run_ours(args):
 
     # ---- leg 2: end to end through the public call with host buffers --------------------------
     leg2 = leg1
-    pinned = [(torch.from_numpy(ids.astype(np.int64)).pin_memory(), torch.from_numpy(mask).pin_memory()) for _, ids, mask in leg2]
+    pinned = [(sid, torch.from_numpy(ids.astype(np.int64)).pin_memory(), torch.from_numpy(mask).pin_memory()) for sid, ids, mask in leg2]
     search.h2d_bytes = search.d2h_bytes = 0
     tokens2 = 0
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
-    for ids_p, mask_p in pinned:
+    for sid, ids_p, mask_p in pinned:
         res = search.search(ids_p, mask_p)
-        gather_outputs(res)
+        gather_outputs(sid, res)
         tokens2 += sum(len(t) for t, _ in res)
     f1.record()
     barrier()
