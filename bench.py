@@ -195,17 +195,27 @@ def run_ours(args):
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with GemmTimer() as gt:
-        e0.record()
-        for sid, ids_t, mask_t in resident:
-            res = search.search_device(ids_t, mask_t)
-            gather_outputs(sid, res)
-            tokens += sum(len(t) for t, _ in res)
-        e1.record()
-        barrier()
+    e0.record()
+    for sid, ids_t, mask_t in resident:
+        res = search.search_device(ids_t, mask_t)
+        gather_outputs(sid, res)
+        tokens += sum(len(t) for t, _ in res)
+    e1.record()
+    barrier()
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1)
     launches = ops.launch_count()
+
+    # ---- the same region once more with every GEMM launch bracketed by CUDA events (the events sit
+    # between kernels and so cost some overlap: this pass attributes time, the pass above is the value)
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with GemmTimer() as gt:
+        p0.record()
+        for sid, ids_t, mask_t in resident:
+            search.search_device(ids_t, mask_t)
+        p1.record()
+        barrier()
+    ms_profiled = p0.elapsed_time(p1)
     gemm_total, gemm_classes = gt.summary()
 
     # ---- leg 2: end to end through the public call with host buffers --------------------------
@@ -249,7 +259,8 @@ def run_ours(args):
             "frac": round(achieved / hbm_peak, 4), "peak_source": peak_src, "traffic": None,
             "launches": gemm_total["launches"], "avg_launch_us": round(gemm_total["us"] / max(1, gemm_total["launches"]), 2),
             "tops": round(gemm_total["ops"] / max(gemm_total["us"], 1e-9) / 1e6, 1),
-            "gemm_share_of_step_time": round(gemm_total["us"] / 1e3 / max(ms, 1e-9), 3),
+            "gemm_share_of_step_time": round(gemm_total["us"] / 1e3 / max(ms_profiled, 1e-9), 3),
+            "profiled_pass_ms": round(ms_profiled, 2),
             "by_shape": {k: {"launches": v["launches"], "us_total": round(v["us"], 1),
                              "GBps": round(v["bytes"] / max(v["us"], 1e-9) / 1e3, 1),
                              "TOPS": round(v["ops"] / max(v["us"], 1e-9) / 1e6, 1)} for k, v in sorted(gemm_classes.items(), key=lambda kv: -kv[1]["us"])},

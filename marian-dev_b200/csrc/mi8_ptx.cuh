@@ -1,4 +1,4 @@
-// Inline-PTX building blocks for the sm_100a int8 affine engine: mbarrier, TMA (no multicast),
+// Inline-PTX building blocks for the sm_100a int8 affine engine: mbarrier, TMA loads into this CTA only,
 // tcgen05 (TMEM allocation, kind::i8 MMA, commit, TMEM loads).  Every wait is bounded.
 #pragma once
 #include <cstdint>
