@@ -97,6 +97,11 @@ int mi8g_lse_topk(const float* logits, int rows, int vocab, int k, const float* 
 int mi8g_nbest_merge(const float* cand_score, const int* cand_word, int beam, int batch, int vocab, int k,
                      float* out_score, int* out_beam, int* out_word, void* stream);
 
+/* How often the stored self-attention keys/values could be kept: out[0] = (layer, step) pairs whose
+ * history abs-max was bit-identical to the previous step's, out[1] = all pairs; reset != 0 clears the
+ * counters.  Synchronises the device. */
+int mi8d_history_reuse(mi8d_decoder* d, unsigned out[2], int reset);
+
 /* Pointer to the last step's logits [beam*batch, vocab] (device), for tests. */
 const float* mi8d_last_logits(const mi8d_decoder* d);
 

@@ -28,7 +28,7 @@ class Mi8dConfig(ctypes.Structure):
 
 # Every symbol include/marian_i8_decode.h declares.
 DECODE_EXPORTS = ["mi8d_arena_bytes", "mi8d_create", "mi8d_destroy", "mi8d_set_weight", "mi8d_set_param", "mi8d_set_positions",
-                  "mi8d_start", "mi8d_encode", "mi8d_step", "mi8d_last_logits",
+                  "mi8d_start", "mi8d_encode", "mi8d_step", "mi8d_last_logits", "mi8d_history_reuse",
                   "mi8g_embed", "mi8g_add_layernorm", "mi8g_quantize_slot", "mi8g_attention1", "mi8g_lse_topk", "mi8g_nbest_merge"]
 
 # Every symbol include/marian_i8.h declares.
@@ -115,6 +115,8 @@ def lib() -> ctypes.CDLL:
     L.mi8d_encode.argtypes = [vp, vp, vp, ci, ci, vp]
     L.mi8d_encode.restype = ci
     L.mi8d_step.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, vp, vp, vp, vp]
+    L.mi8d_history_reuse.argtypes = [vp, ctypes.POINTER(ctypes.c_uint * 2), ci]
+    L.mi8d_history_reuse.restype = ci
     L.mi8d_last_logits.argtypes = [vp]
     L.mi8d_last_logits.restype = vp
     L.mi8g_embed.argtypes = [vp, vp, vp, ci, cf, ci, ci, vp, vp, vp, vp]

@@ -36,8 +36,11 @@ struct Arena {
 };
 
 struct LayerBufs {
-  float* slab = nullptr;     // [max_steps][max_rows][d]   layer inputs (self-attention decoders)
-  float* rowmax = nullptr;   // [max_steps][max_rows]
+  float* slab = nullptr;     // [max_steps][slab_rows][d]  layer inputs (self-attention decoders), row order of each step
+  float* rowmax = nullptr;   // [max_steps][slab_rows]     max|x| per slab row
+  float* kslab = nullptr;    // [max_steps][slab_rows][d]  projected keys / values of the slabs, valid for the
+  float* vslab = nullptr;    //                            history abs-max remembered in prev_bits
+  int8_t* hq = nullptr;      // [max_steps][slab_rows][d]  quantised slabs + multiplier behind the last slab
   float* cross_k = nullptr;  // [max_batch * max_src, d]
   float* cross_v = nullptr;
   float* cell[2] = {nullptr, nullptr};  // SSRU state, double-buffered [max_rows, d]
@@ -62,8 +65,10 @@ struct mi8d_decoder {
   float* x_final = nullptr;
   float *x1 = nullptr, *x2 = nullptr;    // after self / cross blocks
   float *qbuf = nullptr, *abuf = nullptr, *obuf = nullptr, *hbuf = nullptr, *fbuf = nullptr;
-  float *kbuf = nullptr, *vbuf = nullptr;
-  int8_t *aq = nullptr, *hq = nullptr, *cq = nullptr;
+  int8_t *aq = nullptr, *cq = nullptr;
+  unsigned* prev_bits = nullptr;   // per layer: history abs-max (bit pattern) the stored keys/values were computed with
+  unsigned* reuse_stats = nullptr; // [0] (layer, step) pairs that reused stored keys/values, [1] all pairs
+  int slab_rows = 0;               // rows reserved per history slab for the current mini-batch
   float* logits = nullptr;
   float* cand_score = nullptr;
   int* cand_word = nullptr;
@@ -89,6 +94,9 @@ struct mi8d_decoder {
       if(!c.ssru) {
         L.slab = arena.take<float>(T * R * d);
         L.rowmax = arena.take<float>(T * R);
+        L.kslab = arena.take<float>(T * R * d);
+        L.vslab = arena.take<float>(T * R * d);
+        L.hq = arena.take<int8_t>(T * R * d + 256);
       } else {
         L.cell[0] = arena.take<float>(R * d);
         L.cell[1] = arena.take<float>(R * d);
@@ -107,11 +115,10 @@ struct mi8d_decoder {
     hbuf = arena.take<float>(R * f);
     aq = arena.take<int8_t>(R * (f > d ? f : d) + 256);
     if(!c.ssru) {
-      kbuf = arena.take<float>(T * R * d);
-      vbuf = arena.take<float>(T * R * d);
-      hq = arena.take<int8_t>(T * R * d + 256);
       anc[0] = arena.take<int>(T * R);
       anc[1] = arena.take<int>(T * R);
+      prev_bits = arena.take<unsigned>(c.dec_depth);
+      reuse_stats = arena.take<unsigned>(2);
     }
     cq = arena.take<int8_t>(B * S * d + 256);
     logits = arena.take<float>(R * static_cast<size_t>(c.vocab));
@@ -218,6 +225,8 @@ int mi8d_create(const mi8d_config* cfg, void* arena, size_t arena_bytes, void* w
   d->layout();
   d->ws = workspace;
   d->ws_bytes = workspace_bytes;
+  if(d->reuse_stats != nullptr)
+    cudaMemset(d->reuse_stats, 0, 2 * sizeof(unsigned));
   *out = d;
   return MI8_OK;
 }
@@ -252,6 +261,24 @@ int mi8d_set_positions(mi8d_decoder* d, const float* table) {
 }
 
 const float* mi8d_last_logits(const mi8d_decoder* d) { return d ? d->logits : nullptr; }
+
+int mi8d_history_reuse(mi8d_decoder* d, unsigned out[2], int reset) {
+  if(d == nullptr || out == nullptr)
+    return MI8_ERR_BAD_ARG;
+  out[0] = out[1] = 0;
+  if(d->reuse_stats == nullptr)
+    return MI8_OK;
+  cudaError_t e = cudaDeviceSynchronize();
+  if(e == cudaSuccess)
+    e = cudaMemcpy(out, d->reuse_stats, 2 * sizeof(unsigned), cudaMemcpyDeviceToHost);
+  if(e == cudaSuccess && reset)
+    e = cudaMemset(d->reuse_stats, 0, 2 * sizeof(unsigned));
+  if(e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return MI8_ERR_LAUNCH;
+  }
+  return MI8_OK;
+}
 
 int mi8g_embed(const float* wemb, const int* words, const float* pos, int pos_mod, float scale, int rows, int dim, float* out,
                float* rowmax, unsigned* absmax_slot, void* stream) {
@@ -310,6 +337,7 @@ int mi8d_start(mi8d_decoder* d, const float* context, const float* log_mask, int
   d->anc_cur = 0;
   d->cell_cur = 0;
   d->cross_valid = false;
+  d->slab_rows = (d->cfg.max_rows / d->cfg.max_batch) * batch;
   return MI8_OK;
 }
 
@@ -377,6 +405,7 @@ int mi8d_encode(mi8d_decoder* d, const int* ids, const float* log_mask, int batc
   d->anc_cur = 0;
   d->cell_cur = 0;
   d->cross_valid = false;
+  d->slab_rows = (c.max_rows / c.max_batch) * batch;
   return MI8_OK;
 }
 
@@ -388,7 +417,7 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
   const mi8d_config& c = d->cfg;
   const int t = d->t;
   const int R = beam * batch;
-  if(R > c.max_rows || t >= c.max_steps || batch > d->batch)
+  if(R > c.max_rows || t >= c.max_steps || batch > d->batch || (!c.ssru && R > d->slab_rows))
     return MI8_ERR_UNSUPPORTED;
   if(t > 0 && (hyp_idx == nullptr || prev_words == nullptr))
     return MI8_ERR_BAD_ARG;
@@ -398,7 +427,8 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
     return MI8_ERR_BAD_ARG;
   cudaStream_t s = as_stream(stream);
   const int dm = c.dim_emb, S = d->src;
-  const size_t slab_stride = static_cast<size_t>(c.max_rows) * dm;
+  const int SR = d->slab_rows;
+  const size_t slab_stride = static_cast<size_t>(SR) * dm;
 
   cudaError_t e = cudaMemsetAsync(d->slots, 0, sizeof(unsigned) * d->n_slots, s);
   if(e != cudaSuccess) {
@@ -437,11 +467,11 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
 
   const int anc_new = d->anc_cur ^ 1;
   if(!c.ssru)
-    MI8D_TRY(launch_ancestors_update(d->anc[d->anc_cur], d->anc[anc_new], hyp_idx, t, R, c.max_rows, s));
+    MI8D_TRY(launch_ancestors_update(d->anc[d->anc_cur], d->anc[anc_new], hyp_idx, t, R, SR, s));
 
   // layer-0 input: scaled embedding of the previous word (zero at the first step) + position t
   float* x = c.ssru ? d->x_in : d->layers[0].slab + static_cast<size_t>(t) * slab_stride;
-  float* x_rowmax = c.ssru ? nullptr : d->layers[0].rowmax + static_cast<size_t>(t) * c.max_rows;
+  float* x_rowmax = c.ssru ? nullptr : d->layers[0].rowmax + static_cast<size_t>(t) * SR;
   unsigned* x_slot = next_slot();
   MI8D_TRY(launch_embed(d->P("Wemb"), t == 0 ? nullptr : prev_words, d->positions + static_cast<size_t>(t) * dm, 0,
                         sqrtf(static_cast<float>(dm)), R, dm, x, x_rowmax, x_slot, s));
@@ -464,14 +494,26 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
       unsigned* sa = next_slot();
       MI8D_TRY(quant(d, x, R, dm, x_slot, d->aq, s));
       MI8D_TRY(gemm(d, d->aq, R, pre + "_Wq", pre + "_bq", false, d->qbuf, s));
-      // keys and values: the whole history, re-quantised with one multiplier, re-projected
+      // Keys and values are projections of the WHOLE history of layer inputs, quantised with one
+      // multiplier over the live part of that history.  The projections of earlier steps are kept per slab
+      // and stay valid as long as that multiplier's abs-max does not change (compared bit for bit on the
+      // device); then only the newest slab is quantised and projected, otherwise everything is redone.
       const int steps = t + 1;
-      MI8D_TRY(launch_history_absmax(L.rowmax, d->anc[anc_new], steps, R, c.max_rows, sh, s));
-      MI8D_TRY(launch_history_quantize(L.slab, slab_stride, d->anc[anc_new], c.max_rows, steps, R, dm, sh, d->hq,
-                                       reinterpret_cast<float*>(d->hq + static_cast<size_t>(steps) * R * dm), s));
-      MI8D_TRY(gemm(d, d->hq, steps * R, pre + "_Wk", pre + "_bk", false, d->kbuf, s));
-      MI8D_TRY(gemm(d, d->hq, steps * R, pre + "_Wv", pre + "_bv", false, d->vbuf, s));
-      MI8D_TRY(launch_attention1(d->qbuf, d->kbuf, d->vbuf, nullptr, R, c.heads, dm / c.heads, steps, batch, 0, d->abuf, sa, s));
+      float* hq_tail = reinterpret_cast<float*>(L.hq + static_cast<size_t>(c.max_steps) * c.max_rows * dm);
+      MI8D_TRY(launch_history_absmax(L.rowmax, d->anc[anc_new], steps, R, SR, sh, s));
+      MI8D_TRY(launch_history_quantize(L.slab, SR, steps, dm, sh, d->prev_bits + l, L.hq, hq_tail, s));
+      const Weight* wk = d->W(pre + "_Wk");
+      const Weight* wv = d->W(pre + "_Wv");
+      const float* bk = d->P(pre + "_bk");
+      const float* bv = d->P(pre + "_bv");
+      if(wk == nullptr || wv == nullptr || bk == nullptr || bv == nullptr)
+        return MI8_ERR_BAD_ARG;
+      MI8D_TRY(launch_gemm(L.hq, wk->bt, steps * SR, wk->N, wk->K, hq_tail, wk->qm(), 1.0f, bk, 0, L.kslab, MI8_F32, nullptr, d->ws,
+                           d->ws_bytes, s, 0, 0, nullptr, d->prev_bits + l, sh, t * SR));
+      MI8D_TRY(launch_gemm(L.hq, wv->bt, steps * SR, wv->N, wv->K, hq_tail, wv->qm(), 1.0f, bv, 0, L.vslab, MI8_F32, nullptr, d->ws,
+                           d->ws_bytes, s, 0, 0, nullptr, d->prev_bits + l, sh, t * SR));
+      MI8D_TRY(launch_attention1(d->qbuf, L.kslab, L.vslab, nullptr, R, c.heads, dm / c.heads, steps, batch, 0, d->abuf, sa, s,
+                                 d->anc[anc_new], SR, SR));
       MI8D_TRY(quant(d, d->abuf, R, dm, sa, d->aq, s));
       MI8D_TRY(gemm(d, d->aq, R, pre + "_Wo", pre + "_bo", false, d->obuf, s));
       MI8D_TRY(add_ln(d, d->obuf, x, pre + "_Wo", R, d->x1, nullptr, s1, s));
@@ -496,7 +538,7 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
       // the block's output is the next layer's input: write it straight into that layer's history slab
       const bool last = l + 1 == c.dec_depth;
       float* nx = last ? d->x_final : (c.ssru ? d->x_in : d->layers[l + 1].slab + static_cast<size_t>(t) * slab_stride);
-      float* nx_rowmax = (last || c.ssru) ? nullptr : d->layers[l + 1].rowmax + static_cast<size_t>(t) * c.max_rows;
+      float* nx_rowmax = (last || c.ssru) ? nullptr : d->layers[l + 1].rowmax + static_cast<size_t>(t) * SR;
       x_slot = next_slot();
       MI8D_TRY(add_ln(d, d->obuf, d->x2, ffn + "_ffn", R, nx, nx_rowmax, x_slot, s));
       x = nx;
@@ -513,6 +555,8 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
   MI8D_TRY(launch_lse_topk(d->logits, R, c.vocab, n_best, prev_scores, d->cand_score, d->cand_word, s));
   MI8D_TRY(launch_nbest_merge(d->cand_score, d->cand_word, beam, batch, c.vocab, n_best, out_score, out_beam, out_word, s));
 
+  if(!c.ssru)   // remember which abs-max the stored keys/values of every layer now belong to (slot 2 + 7*layer)
+    MI8D_TRY(launch_history_commit(d->prev_bits, d->slots, 2, 7, c.dec_depth, d->reuse_stats, s));
   d->anc_cur = anc_new;
   d->cell_cur = cell_new;
   d->t = t + 1;

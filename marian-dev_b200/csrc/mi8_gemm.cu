@@ -76,6 +76,9 @@ struct GemmParams {
   int32_t* partials;
   unsigned* tile_counters;
   unsigned* absmax_out;
+  const unsigned* skip_a;   // when both are set and *skip_a == *skip_b, tiles that lie entirely below
+  const unsigned* skip_b;   // row skip_rows_below are not computed (their previous results still hold)
+  int skip_rows_below;
   int* status;
 };
 
@@ -153,7 +156,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     // are requested before waiting for it, the activation tiles (its output) after.
     uint32_t it = 0;
     uint32_t prefetched = 0;  // stages whose weight tile is already in flight
-    if(lane == 0) {
+    if(lane == 0 && p.skip_a == nullptr) {
       const WorkItem w0 = decode_work(p, blockIdx.x);
       const int n_pre = min(T::kStages, w0.kb_end - w0.kb_begin);
       for(int i = 0; i < n_pre; ++i) {
@@ -164,8 +167,11 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       prefetched = n_pre;
     }
     pdl_wait();
+    const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
     for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
       const WorkItem wi = decode_work(p, w);
+      if(skip_on && (wi.m_tile + 1) * TM <= p.skip_rows_below)
+        continue;
       for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
         const uint32_t s = it % T::kStages;
         const uint32_t ph = (it / T::kStages) & 1u;
@@ -202,8 +208,15 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     // ------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = make_idesc_i8(TM);
     uint32_t it = 0, acc_it = 0;
-    for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++acc_it) {
+    bool skip_on = false;
+    if(p.skip_a != nullptr) {
+      pdl_wait();  // the skip words are written by earlier kernels of the stream
+      skip_on = *p.skip_a == *p.skip_b;
+    }
+    for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
       const WorkItem wi = decode_work(p, w);
+      if(skip_on && (wi.m_tile + 1) * TM <= p.skip_rows_below)
+        continue;
       const uint32_t as = acc_it & 1u;
       const uint32_t aph = (acc_it >> 1) & 1u;
       if(lane == 0)
@@ -239,6 +252,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       if(lane == 0)
         tc_commit(&ctl->tmem_full[as]);  // accumulator complete
       __syncwarp();
+      ++acc_it;
     }
     if(!ok) {
       *abort_flag = 1;
@@ -259,8 +273,11 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     pdl_wait();  // the activation multiplier is written by the previous kernel
     const float unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(*p.d_qa, *p.d_qb)), p.scale);
     uint32_t acc_it = 0;
-    for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++acc_it) {
+    const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
+    for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
       const WorkItem wi = decode_work(p, w);
+      if(skip_on && (wi.m_tile + 1) * TM <= p.skip_rows_below)
+        continue;
       const uint32_t as = acc_it & 1u;
       const uint32_t aph = (acc_it >> 1) & 1u;
       if(lane == 0)
@@ -391,6 +408,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before_sync();
       mbar_arrive(&ctl->tmem_empty[as]);
+      ++acc_it;
     }
     if(!ok) {
       *abort_flag = 1;
@@ -613,7 +631,8 @@ int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, Gemm
 
 int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb, float scale,
                 const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* ws, size_t ws_bytes,
-                cudaStream_t stream, int force_tile_m, int force_splits, unsigned* absmax_out) {
+                cudaStream_t stream, int force_tile_m, int force_splits, unsigned* absmax_out, const unsigned* skip_a,
+                const unsigned* skip_b, int skip_rows_below) {
   if(M < 0 || N <= 0 || K <= 0)
     return MI8_ERR_BAD_ARG;
   if(M == 0)
@@ -662,6 +681,9 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
   p.partials = wsb ? reinterpret_cast<int32_t*>(wsb + kWsOffPartials) : nullptr;
   p.tile_counters = wsb ? reinterpret_cast<unsigned*>(wsb + kWsOffTileCounters) : nullptr;
   p.absmax_out = absmax_out;
+  p.skip_a = skip_a;
+  p.skip_b = skip_b;
+  p.skip_rows_below = skip_rows_below;
   p.status = device_status_ptr();
   if(p.status == nullptr)
     return MI8_ERR_LAUNCH;

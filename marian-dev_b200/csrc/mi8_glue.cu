@@ -220,24 +220,48 @@ history_absmax_kernel(const float* __restrict__ rowmax, const int* __restrict__ 
     atomicMax(absmax_slot, m);
 }
 
-// hq[(t' * rows + r), :] = quantise(slab[t'][anc[t'][r], :]) for t' < steps: one block per output row.
+// hq[t'][row] = quantise(slab[t'][row]) with the multiplier of the current history abs-max, one block per
+// slab row.  Keys/values of earlier steps only change when that abs-max changes: if it still equals the
+// value the stored keys/values were computed with (*prev_bits), the rows of the old slabs are left alone
+// and only the newest slab is quantised (the GEMM that follows skips the old tiles the same way).
 __global__ void __launch_bounds__(128)
-history_quantize_kernel(const float* __restrict__ slabs, size_t slab_stride, const int* __restrict__ anc, int anc_stride, int rows,
-                        int dim, const unsigned* __restrict__ absmax_slot, int8_t* __restrict__ hq, float* __restrict__ d_quant_mult) {
+history_quantize_kernel(const float* __restrict__ slabs, int slab_rows, int steps, int dim, const unsigned* __restrict__ absmax_slot,
+                        const unsigned* __restrict__ prev_bits, int8_t* __restrict__ hq, float* __restrict__ d_quant_mult) {
   pdl_launch_dependents();
   pdl_wait();
-  const float qm = quant_mult_from_bits(*absmax_slot);
-  const int out_row = blockIdx.x;
-  const int tp = out_row / rows, r = out_row - tp * rows;
-  if(out_row == 0 && threadIdx.x == 0)
-    *d_quant_mult = qm;
-  const float4* src = reinterpret_cast<const float4*>(slabs + tp * slab_stride + static_cast<size_t>(anc[tp * anc_stride + r]) * dim);
-  uint4* dst = reinterpret_cast<uint4*>(hq + static_cast<size_t>(out_row) * dim);
-  for(int i = threadIdx.x; i < dim / 16; i += blockDim.x) {
-    const float4 a = __ldg(src + 4 * i), b = __ldg(src + 4 * i + 1), c = __ldg(src + 4 * i + 2), d = __ldg(src + 4 * i + 3);
-    uint4 o;
-    o.x = pack4(a, qm); o.y = pack4(b, qm); o.z = pack4(c, qm); o.w = pack4(d, qm);
-    dst[i] = o;
+  const unsigned bits = *absmax_slot;
+  if(blockIdx.x == 0 && threadIdx.x == 0)
+    *d_quant_mult = quant_mult_from_bits(bits);
+  const float qm = quant_mult_from_bits(bits);
+  const int total = steps * slab_rows;
+  const int first = (*prev_bits == bits) ? (steps - 1) * slab_rows : 0;   // unchanged abs-max: only the newest slab
+  for(int out_row = first + blockIdx.x; out_row < total; out_row += gridDim.x) {
+    const float4* src = reinterpret_cast<const float4*>(slabs + static_cast<size_t>(out_row) * dim);
+    uint4* dst = reinterpret_cast<uint4*>(hq + static_cast<size_t>(out_row) * dim);
+    for(int i = threadIdx.x; i < dim / 16; i += blockDim.x) {
+      const float4 a = __ldg(src + 4 * i), b = __ldg(src + 4 * i + 1), c = __ldg(src + 4 * i + 2), d = __ldg(src + 4 * i + 3);
+      uint4 o;
+      o.x = pack4(a, qm); o.y = pack4(b, qm); o.z = pack4(c, qm); o.w = pack4(d, qm);
+      dst[i] = o;
+    }
+  }
+}
+
+// prev_bits[l] = slots[first + l * stride]: remembers, per layer, the abs-max the stored keys/values belong to.
+// stats[0] counts (layer, step) pairs whose abs-max was unchanged, stats[1] all pairs.
+__global__ void history_commit_kernel(unsigned* __restrict__ prev_bits, const unsigned* __restrict__ slots, int first, int stride, int layers,
+                                      unsigned* __restrict__ stats) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int l = threadIdx.x;
+  if(l < layers) {
+    const unsigned now = slots[first + l * stride];
+    if(stats) {
+      if(prev_bits[l] == now)
+        atomicAdd(stats, 1u);
+      atomicAdd(stats + 1, 1u);
+    }
+    prev_bits[l] = now;
   }
 }
 
@@ -261,7 +285,7 @@ template <int DH>
 __global__ void __launch_bounds__(256)
 attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ log_mask, int heads, int len, int rows, int batch, int mode, float scale,
-                  float* __restrict__ out, unsigned* absmax_slot) {
+                  float* __restrict__ out, unsigned* absmax_slot, const int* __restrict__ anc, int anc_stride, int kv_rows) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float sc_smem[];  // [heads][len] scores, then probabilities
@@ -276,16 +300,28 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   const size_t stride = (mode == 0 ? static_cast<size_t>(rows) : 1) * dim;
   const float* mask = (mode != 0 && log_mask) ? log_mask + static_cast<size_t>(group) * len : nullptr;
   const float4 qv = active ? __ldg(reinterpret_cast<const float4*>(q + static_cast<size_t>(r) * dim) + tid) : make_float4(0.f, 0.f, 0.f, 0.f);
-  const float* kbase = k + base * dim + 4 * tid;
-  const float* vbase = v + base * dim + 4 * tid;
   float* srow = sc_smem + (active ? head : 0) * len;
+  // mode 0 with an ancestor table: keys/values are stored per step in that step's row order, and the row
+  // of position p that query row r descends from is anc[p][r]
+  const bool indirect = mode == 0 && anc != nullptr;
+  int* anc_s = reinterpret_cast<int*>(sc_smem + heads * len);   // [len] ancestor rows of this query row
+  if(indirect) {
+    for(int p = tid; p < len; p += blockDim.x)
+      anc_s[p] = anc[static_cast<size_t>(p) * anc_stride + r];
+    __syncthreads();
+  }
+  auto row_offset = [&](int p) -> size_t {
+    if(indirect)
+      return (static_cast<size_t>(p) * kv_rows + anc_s[p]) * dim + 4 * tid;
+    return base * dim + 4 * tid + p * stride;
+  };
 
   // scores: eight key rows in flight per thread
   for(int p0 = 0; p0 < len; p0 += 8) {
     float4 kk[8];
 #pragma unroll
     for(int u = 0; u < 8; ++u)
-      kk[u] = (active && p0 + u < len) ? __ldg(reinterpret_cast<const float4*>(kbase + (p0 + u) * stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      kk[u] = (active && p0 + u < len) ? __ldg(reinterpret_cast<const float4*>(k + row_offset(p0 + u))) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for(int u = 0; u < 8; ++u) {
       float d = __fmul_rn(qv.x, kk[u].x);
@@ -332,7 +368,7 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     float4 vv[8];
 #pragma unroll
     for(int u = 0; u < 8; ++u)
-      vv[u] = (active && p0 + u < len) ? __ldg(reinterpret_cast<const float4*>(vbase + (p0 + u) * stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      vv[u] = (active && p0 + u < len) ? __ldg(reinterpret_cast<const float4*>(v + row_offset(p0 + u))) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for(int u = 0; u < 8; ++u) {
       if(p0 + u < len) {
@@ -405,8 +441,34 @@ lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __rest
     t.v[j] = -FLT_MAX;
     t.i[j] = 0x7fffffff;
   }
+  // Thread t owns the 4-element chunks c = t, t+256, ... of the row (16-byte loads when the row is
+  // aligned) and, of a ragged tail, the elements i with i % 256 == t.
+  const int chunks = vocab / 4;
+  const bool vec = (vocab & 3) == 0;
+  auto load4 = [&](int c) -> float4 {
+    if(vec)
+      return __ldg(reinterpret_cast<const float4*>(row) + c);
+    return make_float4(row[4 * c], row[4 * c + 1], row[4 * c + 2], row[4 * c + 3]);
+  };
   float mx = -FLT_MAX;
-  for(int i = threadIdx.x; i < vocab; i += 256) {
+  for(int c0 = threadIdx.x; c0 < chunks; c0 += 4 * 256) {
+    float4 x[4];
+#pragma unroll
+    for(int u = 0; u < 4; ++u)
+      x[u] = (c0 + u * 256 < chunks) ? load4(c0 + u * 256) : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+#pragma unroll
+    for(int u = 0; u < 4; ++u) {
+      const int i = 4 * (c0 + u * 256);
+      if(c0 + u * 256 < chunks) {
+        mx = fmaxf(mx, fmaxf(fmaxf(x[u].x, x[u].y), fmaxf(x[u].z, x[u].w)));
+        topk_insert<K>(t, x[u].x, i);
+        topk_insert<K>(t, x[u].y, i + 1);
+        topk_insert<K>(t, x[u].z, i + 2);
+        topk_insert<K>(t, x[u].w, i + 3);
+      }
+    }
+  }
+  for(int i = 4 * chunks + threadIdx.x; i < vocab; i += 256) {
     const float x = row[i];
     mx = fmaxf(mx, x);
     topk_insert<K>(t, x, i);
@@ -420,10 +482,26 @@ lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __rest
 #pragma unroll
   for(int w = 1; w < 8; ++w)
     mx = fmaxf(mx, redf[w]);
-  // log-sum-exp in a fixed order: thread t adds det_expf(x_i - mx) for i = t, t+256, ... ascending,
-  // then the deterministic block sum; lse = mx + det_logf(sum)
+  // log-sum-exp in a fixed order: thread t adds det_expf(x_i - mx) over its chunks in ascending order
+  // (the four elements of a chunk one after the other), then its tail elements; the 256 partial sums
+  // go through the deterministic block sum; lse = mx + det_logf(sum)
   float sum = 0.f;
-  for(int i = threadIdx.x; i < vocab; i += 256)
+  for(int c0 = threadIdx.x; c0 < chunks; c0 += 4 * 256) {
+    float4 x[4];
+#pragma unroll
+    for(int u = 0; u < 4; ++u)
+      x[u] = (c0 + u * 256 < chunks) ? load4(c0 + u * 256) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for(int u = 0; u < 4; ++u) {
+      if(c0 + u * 256 < chunks) {
+        sum = __fadd_rn(sum, det_expf(__fadd_rn(x[u].x, -mx)));
+        sum = __fadd_rn(sum, det_expf(__fadd_rn(x[u].y, -mx)));
+        sum = __fadd_rn(sum, det_expf(__fadd_rn(x[u].z, -mx)));
+        sum = __fadd_rn(sum, det_expf(__fadd_rn(x[u].w, -mx)));
+      }
+    }
+  }
+  for(int i = 4 * chunks + threadIdx.x; i < vocab; i += 256)
     sum = __fadd_rn(sum, det_expf(__fadd_rn(row[i], -mx)));
   sum = block256_sum_det(sum, redf);
   const float lse = __fadd_rn(mx, det_logf(sum));
@@ -584,17 +662,29 @@ int launch_history_absmax(const float* rowmax, const int* anc, int steps, int ro
   return check_launch();
 }
 
-int launch_history_quantize(const float* slabs, size_t slab_stride, const int* anc, int anc_stride, int steps, int rows, int dim,
-                            const unsigned* slot, int8_t* hq, float* d_qm, cudaStream_t s) {
+int launch_history_quantize(const float* slabs, int slab_rows, int steps, int dim, const unsigned* slot, const unsigned* prev_bits,
+                            int8_t* hq, float* d_qm, cudaStream_t s) {
   if(dim % 16 != 0)
     return MI8_ERR_MISALIGNED;
-  launch_kernel(history_quantize_kernel, dim3(steps * rows), dim3(128), 0, s, slabs, slab_stride, anc, anc_stride, rows, dim, slot, hq, d_qm);
+  int blocks = steps * slab_rows;
+  const int cap = sm_count() * 16;
+  blocks = blocks > cap ? cap : blocks;
+  launch_kernel(history_quantize_kernel, dim3(blocks), dim3(128), 0, s, slabs, slab_rows, steps, dim, slot, prev_bits, hq, d_qm);
+  count_launch();
+  return check_launch();
+}
+
+int launch_history_commit(unsigned* prev_bits, const unsigned* slots, int first, int stride, int layers, unsigned* stats, cudaStream_t s) {
+  if(layers > 64)
+    return MI8_ERR_UNSUPPORTED;
+  launch_kernel(history_commit_kernel, dim3(1), dim3(64), 0, s, prev_bits, slots, first, stride, layers, stats);
   count_launch();
   return check_launch();
 }
 
 int launch_attention1(const float* q, const float* k, const float* v, const float* log_mask, int rows, int heads, int dim_head,
-                      int len, int batch, int mode, float* out, unsigned* slot, cudaStream_t s) {
+                      int len, int batch, int mode, float* out, unsigned* slot, cudaStream_t s, const int* anc, int anc_stride,
+                      int kv_rows) {
   if(rows <= 0 || heads <= 0 || len <= 0)
     return MI8_ERR_BAD_ARG;
   if(mode < 0 || mode > 2)
@@ -604,13 +694,13 @@ int launch_attention1(const float* q, const float* k, const float* v, const floa
   if(dim > 1024)
     return MI8_ERR_UNSUPPORTED;
   const int threads = ((dim / 4 + 31) / 32) * 32;
-  const size_t smem = static_cast<size_t>(heads) * len * sizeof(float);
+  const size_t smem = (static_cast<size_t>(heads) + 1) * len * sizeof(float);
   if(smem > 48 * 1024)
     return MI8_ERR_UNSUPPORTED;
   if(dim_head == 64)
-    launch_kernel(attention1_kernel<64>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
+    launch_kernel(attention1_kernel<64>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
   else if(dim_head == 32)
-    launch_kernel(attention1_kernel<32>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot);
+    launch_kernel(attention1_kernel<32>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
   else
     return MI8_ERR_UNSUPPORTED;
   count_launch();

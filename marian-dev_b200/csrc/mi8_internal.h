@@ -63,7 +63,8 @@ int launch_transpose_quantize(const float* w, int K, int N, const float* d_quant
 // quantisation of C as the next affine's input.
 int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb, float scale,
                 const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* ws, size_t ws_bytes,
-                cudaStream_t stream, int force_tile_m, int force_splits, unsigned* absmax_out = nullptr);
+                cudaStream_t stream, int force_tile_m, int force_splits, unsigned* absmax_out = nullptr,
+                const unsigned* skip_a = nullptr, const unsigned* skip_b = nullptr, int skip_rows_below = 0);
 
 // decode-step glue (mi8_glue.cu)
 int launch_embed(const float* wemb, const int* words, const float* pos, int pos_mod, float scale, int rows, int dim, float* out,
@@ -73,10 +74,12 @@ int launch_add_layernorm(const float* a, const float* resid, const float* gamma,
 int launch_quantize_slot(const float* x, size_t n, const unsigned* slot, int8_t* q, float* d_qm, cudaStream_t s);
 int launch_ancestors_update(const int* anc_old, int* anc_new, const int* hyp, int t, int rows, int stride, cudaStream_t s);
 int launch_history_absmax(const float* rowmax, const int* anc, int steps, int rows, int stride, unsigned* slot, cudaStream_t s);
-int launch_history_quantize(const float* slabs, size_t slab_stride, const int* anc, int anc_stride, int steps, int rows, int dim,
-                            const unsigned* slot, int8_t* hq, float* d_qm, cudaStream_t s);
+int launch_history_quantize(const float* slabs, int slab_rows, int steps, int dim, const unsigned* slot, const unsigned* prev_bits,
+                            int8_t* hq, float* d_qm, cudaStream_t s);
+int launch_history_commit(unsigned* prev_bits, const unsigned* slots, int first, int stride, int layers, unsigned* stats, cudaStream_t s);
 int launch_attention1(const float* q, const float* k, const float* v, const float* log_mask, int rows, int heads, int dim_head,
-                      int len, int batch, int mode, float* out, unsigned* slot, cudaStream_t s);
+                      int len, int batch, int mode, float* out, unsigned* slot, cudaStream_t s, const int* anc = nullptr,
+                      int anc_stride = 0, int kv_rows = 0);
 int launch_lse_topk(const float* logits, int rows, int vocab, int k, const float* prev_scores, float* cand_score, int* cand_word,
                     cudaStream_t s);
 int launch_nbest_merge(const float* cand_score, const int* cand_word, int beam, int batch, int vocab, int k, float* out_score,

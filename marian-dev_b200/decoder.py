@@ -253,6 +253,13 @@ class NativeStepper:
         log_mask = ((1.0 - mask_t) * NEG_MASK).contiguous()     # exactly 0 or -99999999
         self.check(self.L.mi8d_encode(self.h, ids32.data_ptr(), log_mask.data_ptr(), B, S, torch.cuda.current_stream().cuda_stream))
 
+    def history_reuse(self, reset: bool = False):
+        """(reused, total) counts of (layer, step) pairs whose stored self-attention keys/values stayed valid."""
+        import ctypes
+        out = (ctypes.c_uint * 2)()
+        self.check(self.L.mi8d_history_reuse(self.h, ctypes.byref(out), int(reset)))
+        return int(out[0]), int(out[1])
+
     def start(self, ctx: torch.Tensor, log_mask: torch.Tensor):
         B, S = ctx.shape[0], ctx.shape[1]
         if B > self.max_batch or S > self.max_src:

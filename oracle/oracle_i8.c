@@ -438,10 +438,15 @@ MO_FMA_CLONES void mo_lse_topk(const float* logits, int rows, int vocab, int k, 
         ti[pos] = i;
       }
     }
+    /* worker t of 256 owns the 4-element chunks c = t, t+256, ... (elements added one after the other)
+     * and, of a ragged tail, the elements i with i % 256 == t */
     float part[256];
+    const int chunks = vocab / 4;
     for(int t = 0; t < 256; ++t) {
       float s = 0.0f;
-      for(int i = t; i < vocab; i += 256) s = s + mo_det_expf_i(row[i] + -mx);
+      for(int c = t; c < chunks; c += 256)
+        for(int e = 0; e < 4; ++e) s = s + mo_det_expf_i(row[4 * c + e] + -mx);
+      for(int i = 4 * chunks + t; i < vocab; i += 256) s = s + mo_det_expf_i(row[i] + -mx);
       part[t] = s;
     }
     const float lse = mx + mo_det_logf_i(mo_block256_sum(part));
