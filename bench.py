@@ -256,7 +256,10 @@ def run_ours(args):
         roofline = {
             "kernel": "mi8_gemm_kernel (all launches of the timed region)",
             "bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
-            "frac": round(achieved / hbm_peak, 4), "peak_source": peak_src, "traffic": None,
+            "frac": round(achieved / hbm_peak, 4), "peak_source": peak_src,
+            # DRAM read + write of one output-layer launch (M=512, K=1024, N=32000; algorithmic 98.9 MB, part of C stays in L2),
+            # from the ncu capture summarised in profiles/gemm_kernel_ncu_b200.md
+            "traffic": 44.7e6, "traffic_unit": "bytes per launch of the 512x1024x32000 shape",
             "launches": gemm_total["launches"], "avg_launch_us": round(gemm_total["us"] / max(1, gemm_total["launches"]), 2),
             "tops": round(gemm_total["ops"] / max(gemm_total["us"], 1e-9) / 1e6, 1),
             "gemm_share_of_step_time": round(gemm_total["us"] / 1e3 / max(ms_profiled, 1e-9), 3),
