@@ -33,6 +33,30 @@ UNIT = "tokens/s"
 WORKLOAD = "transformer-big decode (6+6 layers, d=1024, ffn=4096, 16 heads, tied 32000 vocab, all affines int8), beam 4, mini-batch 128, lengths clip(N(30,12),4,128), max length 1.5x source"
 MINI_BATCH = 128
 BEAM = 4
+# The benchmark line is the "big" workload; the others are the remaining named decode configurations,
+# runnable with --model for parity-sized measurements (their lines carry their own workload string).
+WORKLOADS = {
+    "big": dict(desc=WORKLOAD, mini_batch=128, beam=4, lengths=dict(length_dist="normal", lo=4, hi=128, mean=30.0, std=12.0)),
+    "base": dict(desc="transformer-base decode (6+6 layers, d=512, ffn=2048, 8 heads, tied 32000 vocab, all affines int8), beam 4, "
+                      "mini-batch 64, lengths U[8,64], max length 1.5x source",
+                 mini_batch=64, beam=4, lengths=dict(length_dist="uniform", lo=8, hi=64)),
+    "student": dict(desc="student decode (12 encoder layers d=256 ffn=1536 8 heads, 2-layer SSRU decoder, 32000 vocab, all affines int8), "
+                         "greedy, lengths U[5,40], max length 1.5x source",
+                    mini_batch=16, beam=1, lengths=dict(length_dist="uniform", lo=5, hi=40)),
+}
+
+
+def workload(args):
+    w = dict(WORKLOADS.get(args.model, WORKLOADS["big"]))
+    if args.model not in WORKLOADS:
+        w["desc"] = f"{args.model} (debug workload)"
+    if args.mini_batch:
+        w["mini_batch"] = args.mini_batch
+    if args.beam:
+        w["beam"] = args.beam
+    if args.model != "big" or args.mini_batch or args.beam:
+        w["desc"] += f" [mini-batch {w['mini_batch']}, beam {w['beam']}]"
+    return w
 
 
 def parse_args():
@@ -42,16 +66,18 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="big", help="big (the benchmark), base, student, tiny (debugging)")
+    ap.add_argument("--mini-batch", type=int, default=0, help="override the workload's mini-batch (sentences)")
+    ap.add_argument("--beam", type=int, default=0, help="override the workload's beam size")
     ap.add_argument("--cpu-sentences", type=int, default=8, help="sentences in the CPU-baseline sample")
     ap.add_argument("--affine", default=None, help="M,K,N: time one int8 affine (abs-max + quantise + GEMM with bias and ReLU) instead of the decode")
     ap.add_argument("--sweep", action="store_true", help="time the affine shape sweep M x K x N instead of the decode")
     return ap.parse_args()
 
 
-def build_corpus(model_mod, cfg, n_batches):
-    n = n_batches * MINI_BATCH
-    corpus = model_mod.synthetic_corpus(max(n, MINI_BATCH), cfg.vocab, seed=1, length_dist="normal", lo=4, hi=128, mean=30.0, std=12.0)
-    return model_mod.make_batches(corpus, MINI_BATCH)
+def build_corpus(model_mod, cfg, n_batches, wl):
+    n = n_batches * wl["mini_batch"]
+    corpus = model_mod.synthetic_corpus(n, cfg.vocab, seed=1, **wl["lengths"])
+    return model_mod.make_batches(corpus, wl["mini_batch"])
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -165,10 +191,11 @@ def run_ours(args):
     net = decoder.Int8Transformer(cfg, params, dev, output_int8=True)
     del params
     per_rank = args.warmup + args.steps                          # both timed legs decode the same mini-batches
-    batches = build_corpus(model, cfg, per_rank * world)
+    wl = workload(args)
+    batches = build_corpus(model, cfg, per_rank * world, wl)
     mine = parallel.shard_batches(batches, rank, world)[:per_rank]
-    stepper = decoder.NativeStepper(net, max_batch=MINI_BATCH, beam=BEAM, max_src=136, max_steps=208)
-    search = decoder.BeamSearch(net, beam=BEAM, max_length_factor=1.5, normalize=1.0, native=stepper)
+    stepper = decoder.NativeStepper(net, max_batch=wl["mini_batch"], beam=wl["beam"], max_src=136, max_steps=208)
+    search = decoder.BeamSearch(net, beam=wl["beam"], max_length_factor=1.5, normalize=1.0, native=stepper)
 
     def barrier():
         torch.cuda.synchronize()
@@ -274,7 +301,7 @@ def run_ours(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / max(1, args.steps), 2),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 (s8 x s8 -> s32), fp32 epilogue",
             "data": "synthetic (random-init weights, uniform token ids, seeded)",
-            "config": {"workload": WORKLOAD if args.model == "big" else f"{args.model} (debug workload)", "mini_batch": MINI_BATCH, "beam": BEAM,
+            "config": {"workload": wl["desc"], "mini_batch": wl["mini_batch"], "beam": wl["beam"],
                        "tokens_counted": "best hypothesis per sentence, EOS included", "parallelism": f"replicas x{world}",
                        "l2": "not flushed: one decode step streams ~0.2 GB of int8 weights plus fp32 logits and history, more than the 126 MB L2"},
             "e2e": {"value": round(tokens2 / (ms2 / 1e3), 1), "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
@@ -300,8 +327,9 @@ def cpu_decode_sample(args, cfg_name):
     cores = o.max_threads()
     net = OracleTransformer(cfg, params, oracle=o, output_int8=True, threads=cores)
     del params
-    corpus = model.synthetic_corpus(MINI_BATCH, cfg.vocab, seed=1, length_dist="normal", lo=4, hi=128, mean=30.0, std=12.0)
-    n = args.cpu_sentences
+    wl = workload(args)
+    corpus = model.synthetic_corpus(wl["mini_batch"], cfg.vocab, seed=1, **wl["lengths"])
+    n = min(args.cpu_sentences, len(corpus))
     # a typical slice of the length-sorted batch (around the median length)
     order = sorted(range(len(corpus)), key=lambda i: len(corpus[i]))
     pick = [corpus[i] for i in order[len(order) // 2 - n // 2: len(order) // 2 - n // 2 + n]]
@@ -309,10 +337,10 @@ def cpu_decode_sample(args, cfg_name):
     t0 = time.time()
     tokens = 0
     for _sid, ids, mask in batches:
-        for toks, _s in beam_search(net, ids, mask, beam=BEAM, max_length_factor=1.5, normalize=1.0):
+        for toks, _s in beam_search(net, ids, mask, beam=wl["beam"], max_length_factor=1.5, normalize=1.0):
             tokens += len(toks)
     dt = time.time() - t0
-    return tokens / dt, cores, f"{n} sentences of median length from one mini-batch, beam {BEAM}, {dt:.1f} s of CPU work"
+    return tokens / dt, cores, f"{n} sentences of median length from one mini-batch, beam {wl['beam']}, {dt:.1f} s of CPU work"
 
 
 def cpu_baseline(args, cfg_name):
@@ -342,7 +370,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": len(vals),
         "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8 (s8 x s8 -> s32), fp32 epilogue", "data": "synthetic (random-init weights, uniform token ids, seeded)",
-        "config": {"workload": WORKLOAD if args.model == "big" else f"{args.model} (debug workload)", "mini_batch": MINI_BATCH, "beam": BEAM,
+        "config": {"workload": workload(args)["desc"], "mini_batch": workload(args)["mini_batch"], "beam": workload(args)["beam"],
                    "note": "CPU restatement of the reference's intgemm8 path (the reference itself is unbuildable here: intgemm submodule absent)"},
         "cpu_baseline": {"value": round(value, 2), "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": round(value, 2), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -111,13 +111,27 @@ int mi8_multiply_i8(const int8_t* aq, const int8_t* bt, int M, int N, int K,
                     const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out,
                     void* workspace, size_t workspace_bytes, void* stream);
 
-/* Same, with the tile width along M (16/32/64/128/256, 0 = automatic) and the split-K factor
- * (0 = automatic) forced.  Any split factor gives bit-identical results. */
+/* Same, with the tile width along M (16/32/64/128/256, 0 = automatic; 512 = the two-CTA kernel: one
+ * tcgen05.mma.cta_group::2 tile of 256 weight rows x 256 activation rows per cluster of two CTAs, no
+ * split-K) and the split-K factor (0 = automatic) forced.  Any choice gives bit-identical results. */
 int mi8_multiply_i8_ex(const int8_t* aq, const int8_t* bt, int M, int N, int K,
                        const float* d_qa, const float* d_qb, float scale,
                        const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out,
                        void* workspace, size_t workspace_bytes, void* stream,
                        int force_tile_m, int force_splits);
+
+/* The multiply for an activation whose leading rows did not change since the previous call (no
+ * counterpart in the reference, which recomputes; used for the decoder's stored keys/values).  When the
+ * two device words *same_a and *same_b are equal at the time the kernel runs, tiles of activation rows
+ * that lie entirely below row `rows_unchanged_below` are left as they are in c (the caller guarantees
+ * they hold the result of the same operands); everything else is computed.  When the words differ
+ * the whole product is computed.  The decision is taken on the device, so no host synchronisation. */
+int mi8_multiply_i8_rows_from(const int8_t* aq, const int8_t* bt, int M, int N, int K,
+                              const float* d_qa, const float* d_qb, float scale,
+                              const float* bias, int relu, void* c, int out_dtype,
+                              void* workspace, size_t workspace_bytes, void* stream,
+                              const unsigned* same_a, const unsigned* same_b, int rows_unchanged_below,
+                              int force_tile_m);
 
 /*
  * affine / dot / affineWithReluDropout on a float A and a converted weight in one call

@@ -198,6 +198,16 @@ int mi8_multiply_i8_ex(const int8_t* aq, const int8_t* bt, int M, int N, int K, 
                      as_stream(stream), force_tile_m, force_splits);
 }
 
+int mi8_multiply_i8_rows_from(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb,
+                              float scale, const float* bias, int relu, void* c, int out_dtype, void* workspace,
+                              size_t workspace_bytes, void* stream, const unsigned* same_a, const unsigned* same_b,
+                              int rows_unchanged_below, int force_tile_m) {
+  if(force_tile_m < 0 || same_a == nullptr || same_b == nullptr || rows_unchanged_below < 0)
+    return MI8_ERR_BAD_ARG;
+  return launch_gemm(aq, bt, M, N, K, d_qa, d_qb, scale, bias, relu, c, out_dtype, nullptr, workspace, workspace_bytes,
+                     as_stream(stream), force_tile_m, 0, nullptr, same_a, same_b, rows_unchanged_below);
+}
+
 int mi8_affine_f32(const float* a, int M, int K, const int8_t* bt, const float* d_qb, int N, const float* bias, float scale,
                    int relu, void* c, int out_dtype, int8_t* aq_scratch, void* workspace, size_t workspace_bytes,
                    void* stream) {
@@ -227,7 +237,7 @@ int mi8_multiply_plan(int M, int N, int K, int force_tile_m, int force_splits, i
   int rc = make_gemm_plan(M, N, K, force_tile_m, force_splits, &plan);
   if(rc != MI8_OK)
     return rc;
-  out[0] = plan.tile_m;
+  out[0] = plan.pair ? 512 : plan.tile_m;
   out[1] = plan.stages;
   out[2] = plan.splits;
   out[3] = plan.n_tiles;

@@ -34,6 +34,7 @@ constexpr int kMmaK = 32;       // K per tcgen05.mma kind::i8
 constexpr int kThreads = 320;
 constexpr int kEpilogueThreads = 256;
 constexpr int kMaxStages = 8;
+constexpr int kPairTileCode = 512;  // force_tile_m value that selects the CTA-pair kernel
 
 template <int TM>
 struct TileCfg {
@@ -107,6 +108,62 @@ template <>
 __device__ __forceinline__ void tmem_ld_chunk<16>(uint32_t taddr, int32_t (&v)[16]) { tmem_ld_x16(taddr, v); }
 template <>
 __device__ __forceinline__ void tmem_ld_chunk<32>(uint32_t taddr, int32_t (&v)[32]) { tmem_ld_x32(taddr, v); }
+
+// Dequantises one register chunk of accumulators of output column n (CH consecutive rows m starting at
+// element `base` of C, of which `valid` exist; `valid` may exceed CH) and stores it:
+// float(acc) * unquant (+ bias) as two separately rounded operations, then ReLU.  Each stage runs over
+// the whole chunk so the columns overlap in the pipeline.  Returns the running max|C| bit pattern.
+template <int CH>
+__device__ __forceinline__ unsigned write_back_chunk(const GemmParams& p, const int32_t (&v)[CH], size_t base, int valid, float unquant,
+                                                     float bias_n, unsigned out_max) {
+  float f[CH];
+#pragma unroll
+  for(int j = 0; j < CH; ++j)
+    f[j] = __fmul_rn(__int2float_rn(v[j]), unquant);
+  if(p.bias != nullptr) {
+#pragma unroll
+    for(int j = 0; j < CH; ++j)
+      f[j] = __fadd_rn(f[j], bias_n);
+  }
+  if(p.relu) {
+#pragma unroll
+    for(int j = 0; j < CH; ++j)
+      f[j] = f[j] > 0.0f ? f[j] : 0.0f;
+  }
+  if(p.absmax_out != nullptr) {
+#pragma unroll
+    for(int j = 0; j < CH; ++j)
+      if(j < valid)
+        out_max = max(out_max, __float_as_uint(f[j]) & 0x7fffffffu);
+  }
+  if(p.acc_out != nullptr) {
+    int32_t* dst = p.acc_out + base;
+#pragma unroll
+    for(int j = 0; j < CH; ++j)
+      if(j < valid)
+        dst[static_cast<size_t>(j) * p.N] = v[j];
+  }
+  if(p.out_f16) {
+    __half* dst = reinterpret_cast<__half*>(p.c) + base;
+#pragma unroll
+    for(int j = 0; j < CH; ++j)
+      if(j < valid)
+        dst[static_cast<size_t>(j) * p.N] = __float2half_rn(f[j]);
+  } else {
+    float* dst = reinterpret_cast<float*>(p.c) + base;
+    if(valid >= CH) {
+#pragma unroll
+      for(int j = 0; j < CH; ++j)
+        dst[static_cast<size_t>(j) * p.N] = f[j];
+    } else {
+#pragma unroll
+      for(int j = 0; j < CH; ++j)
+        if(j < valid)
+          dst[static_cast<size_t>(j) * p.N] = f[j];
+    }
+  }
+  return out_max;
+}
 
 template <int TM>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -346,58 +403,9 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             tmem_ld_chunk<T::kChunk>(t_addr + col0, v);
             tc_wait_ld();
           }
-          if(n_ok) {
-            // float(acc) * unquant (+ bias): two separately rounded operations, then ReLU.  Each
-            // stage runs over the whole register chunk so the 32 columns overlap in the pipeline.
-            const size_t base = static_cast<size_t>(m0 + col0) * p.N + n;
-            const int valid = cols_valid - col0;  // columns of this chunk that exist (may exceed the chunk)
-            float f[T::kChunk];
-#pragma unroll
-            for(int j = 0; j < T::kChunk; ++j)
-              f[j] = __fmul_rn(__int2float_rn(v[j]), unquant);
-            if(p.bias != nullptr) {
-#pragma unroll
-              for(int j = 0; j < T::kChunk; ++j)
-                f[j] = __fadd_rn(f[j], bias_n);
-            }
-            if(p.relu) {
-#pragma unroll
-              for(int j = 0; j < T::kChunk; ++j)
-                f[j] = f[j] > 0.0f ? f[j] : 0.0f;
-            }
-            if(p.absmax_out != nullptr) {
-#pragma unroll
-              for(int j = 0; j < T::kChunk; ++j)
-                if(j < valid)
-                  out_max = max(out_max, __float_as_uint(f[j]) & 0x7fffffffu);
-            }
-            if(p.acc_out != nullptr) {
-              int32_t* dst = p.acc_out + base;
-#pragma unroll
-              for(int j = 0; j < T::kChunk; ++j)
-                if(j < valid)
-                  dst[static_cast<size_t>(j) * p.N] = v[j];
-            }
-            if(p.out_f16) {
-              __half* dst = reinterpret_cast<__half*>(p.c) + base;
-#pragma unroll
-              for(int j = 0; j < T::kChunk; ++j)
-                if(j < valid)
-                  dst[static_cast<size_t>(j) * p.N] = __float2half_rn(f[j]);
-            } else {
-              float* dst = reinterpret_cast<float*>(p.c) + base;
-              if(valid >= T::kChunk) {
-#pragma unroll
-                for(int j = 0; j < T::kChunk; ++j)
-                  dst[static_cast<size_t>(j) * p.N] = f[j];
-              } else {
-#pragma unroll
-                for(int j = 0; j < T::kChunk; ++j)
-                  if(j < valid)
-                    dst[static_cast<size_t>(j) * p.N] = f[j];
-              }
-            }
-          }
+          if(n_ok)
+            out_max = write_back_chunk<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * p.N + n, cols_valid - col0, unquant, bias_n,
+                                                  out_max);
         }
       }
       if(p.absmax_out != nullptr) {
@@ -435,6 +443,280 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     }
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, T::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ CTA-pair variant (large M)
+// A cluster of two CTAs computes a tile of 256 weight rows x 256 activation rows with one
+// tcgen05.mma.cta_group::2 per 32 bytes of K.  CTA `rank` of the pair loads weight rows
+// [256 * pair_n + 128 * rank, +128) and activation rows [256 * m_tile + 128 * rank, +128) into its own
+// shared memory (32 KB per stage instead of 48 KB for the same 128 x 256 outputs per CTA) and owns the
+// accumulators of its 128 weight rows x all 256 activation rows in its TMEM, so its epilogue is the
+// one of the single-CTA kernel.  Per CTA the tensor core reads 64 instead of 96 bytes of shared
+// memory per clock at full rate, which leaves the shared-memory port room for the TMA writes.
+//   * full[s] lives in the rank-0 CTA: its producer announces the bytes of both CTAs, both CTAs'
+//     copies are credited to it; empty[s] and tmem_full[b] exist in both CTAs and are signalled by
+//     commits of the rank-0 MMA thread addressed to both; tmem_empty[b] of rank 0 collects one
+//     arrival per CTA (after that CTA's epilogue warps met at a named barrier).
+//   * The cluster barrier brackets the kernel: no remote arrival before the barriers exist, no CTA
+//     leaves (or frees TMEM) while its peer may still read its shared memory.
+struct PairCfg {
+  static constexpr int kTM = 256;             // activation rows per pair tile (MMA N)
+  static constexpr int kHalfRows = 128;       // activation rows each CTA loads
+  static constexpr int kStages = 6;
+  static constexpr int kWBytes = kTileN * kTileKBytes;
+  static constexpr int kABytes = kHalfRows * kTileKBytes;
+  static constexpr int kStageBytes = kWBytes + kABytes;
+  static constexpr int kAccStride = 256;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kChunk = 32;
+};
+constexpr int smem_bytes_pair() { return PairCfg::kStages * PairCfg::kStageBytes + static_cast<int>(sizeof(Control)) + 1024; }
+
+__global__ void __launch_bounds__(kThreads, 1)
+mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
+  using T = PairCfg;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;  // same in both CTAs
+  uint8_t* tiles = smem_raw + pad;
+  Control* ctl = reinterpret_cast<Control*>(tiles + T::kStages * T::kStageBytes);
+  volatile int* abort_flag = &ctl->abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+  const uint32_t peer_abort = mapa_shared(smem_u32(&ctl->abort), rank ^ 1u);
+
+  pdl_launch_dependents();
+  if(threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_a);
+    for(int s = 0; s < T::kStages; ++s) {
+      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->empty[s], 1);
+    }
+    for(int b = 0; b < 2; ++b) {
+      mbar_init(&ctl->tmem_full[b], 1);
+      mbar_init(&ctl->tmem_empty[b], 2);  // one arrival per CTA of the pair
+    }
+    mbar_init(&ctl->drain, 1);
+    ctl->abort = 0;
+    ctl->is_last = 0;
+    fence_mbar_init();
+  }
+  if(warp == 1) {
+    tmem_alloc_pair(&ctl->tmem_base, T::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctl->tmem_base);
+
+  bool ok = true;
+
+  if(warp == 0) {
+    // ------------------------------------------------------------ TMA producer (one per CTA)
+    uint32_t it = 0;
+    uint32_t prefetched = 0;
+    // copies of both CTAs are credited to full[s] of the rank-0 CTA
+    auto full_addr = [&](uint32_t s) { return mapa_shared(smem_u32(&ctl->full[s]), 0u); };
+    if(lane == 0 && p.skip_a == nullptr && pair_id < p.total_work) {
+      // weights do not depend on the previous kernel: request the first pipeline fill before waiting for it
+      const WorkItem w0 = decode_work(p, pair_id);
+      const int n_pre = min(T::kStages, w0.kb_end - w0.kb_begin);
+      for(int i = 0; i < n_pre; ++i) {
+        uint8_t* st = tiles + i * T::kStageBytes;
+        if(leader)
+          mbar_arrive_expect_tx(&ctl->full[i], 2 * T::kStageBytes);
+        tma_load_2d_pair(st, &tmap_w, (w0.kb_begin + i) * kTileKBytes, (2 * w0.n_tile + static_cast<int>(rank)) * kTileN, full_addr(i));
+      }
+      prefetched = n_pre;
+    }
+    pdl_wait();
+    const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
+    for(int w = pair_id; w < p.total_work && ok; w += n_pairs) {
+      const WorkItem wi = decode_work(p, w);
+      if(skip_on && (wi.m_tile + 1) * T::kTM <= p.skip_rows_below)
+        continue;
+      for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
+        const uint32_t s = it % T::kStages;
+        const uint32_t ph = (it / T::kStages) & 1u;
+        const bool pre = lane == 0 && it < prefetched;
+        if(lane == 0 && !pre)
+          ok = mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if(!ok)
+          break;
+        if(lane == 0) {
+          uint8_t* st = tiles + s * T::kStageBytes;
+          if(!pre) {
+            if(leader)
+              mbar_arrive_expect_tx(&ctl->full[s], 2 * T::kStageBytes);
+            tma_load_2d_pair(st, &tmap_w, kb * kTileKBytes, (2 * wi.n_tile + static_cast<int>(rank)) * kTileN, full_addr(s));
+          }
+          tma_load_2d_pair(st + T::kWBytes, &tmap_a, kb * kTileKBytes, wi.m_tile * T::kTM + static_cast<int>(rank) * T::kHalfRows,
+                           full_addr(s));
+        }
+        __syncwarp();
+      }
+    }
+    if(!ok) {
+      *abort_flag = 1;
+      if(lane == 0) {
+        st_cluster_u32(peer_abort, 1u);
+        atomicMax(p.status, static_cast<int>(kDevTimeoutProducer));
+        if(leader) {
+          // Wait (bounded) for the copies of both CTAs already announced, so none lands after the pair has gone.
+          const uint32_t first = it > static_cast<uint32_t>(T::kStages) ? it - T::kStages : 0u;
+          int no_abort = 0;
+          for(uint32_t j = first; j < it; ++j)
+            mbar_wait_bounded(&ctl->full[j % T::kStages], (j / T::kStages) & 1u, &no_abort);
+        }
+      }
+      __syncwarp();
+    }
+  } else if(warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (rank 0 only; rank 1 owns its TMEM half)
+    if(leader) {
+      constexpr uint32_t idesc = make_idesc_i8(T::kTM, 256);
+      uint32_t it = 0, acc_it = 0;
+      bool skip_on = false;
+      if(p.skip_a != nullptr) {
+        pdl_wait();
+        skip_on = *p.skip_a == *p.skip_b;
+      }
+      for(int w = pair_id; w < p.total_work && ok; w += n_pairs) {
+        const WorkItem wi = decode_work(p, w);
+        if(skip_on && (wi.m_tile + 1) * T::kTM <= p.skip_rows_below)
+          continue;
+        const uint32_t as = acc_it & 1u;
+        const uint32_t aph = (acc_it >> 1) & 1u;
+        if(lane == 0)
+          ok = mbar_wait_bounded(&ctl->tmem_empty[as], aph ^ 1u, abort_flag);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if(!ok)
+          break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + as * T::kAccStride;
+        for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
+          const uint32_t s = it % T::kStages;
+          const uint32_t ph = (it / T::kStages) & 1u;
+          if(lane == 0)
+            ok = mbar_wait_bounded(&ctl->full[s], ph, abort_flag);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if(!ok)
+            break;
+          tc_fence_after_sync();
+          if(lane == 0) {
+            const uint32_t w_addr = smem_u32(tiles + s * T::kStageBytes);
+            const uint32_t a_addr = w_addr + T::kWBytes;
+#pragma unroll
+            for(int k = 0; k < kTileKBytes / kMmaK; ++k) {
+              tc_mma_i8_pair(d_tmem, make_kmajor_sw128_desc(w_addr + k * kMmaK), make_kmajor_sw128_desc(a_addr + k * kMmaK), idesc,
+                             (kb > wi.kb_begin || k > 0) ? 1u : 0u);
+            }
+            tc_commit_pair(&ctl->empty[s], 3);  // frees this slot in both CTAs once the MMAs have read it
+          }
+          __syncwarp();
+        }
+        if(!ok)
+          break;
+        if(lane == 0)
+          tc_commit_pair(&ctl->tmem_full[as], 3);  // accumulator complete in both CTAs
+        __syncwarp();
+        ++acc_it;
+      }
+      if(!ok) {
+        *abort_flag = 1;
+        if(lane == 0) {
+          st_cluster_u32(peer_abort, 1u);
+          atomicMax(p.status, static_cast<int>(kDevTimeoutMma));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9 of both CTAs)
+    const int quarter = warp & 3;
+    const int group = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;
+    const int epi_tid = threadIdx.x - 64;
+    constexpr int kChunks = T::kTM / T::kChunk;
+    pdl_wait();
+    const float unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(*p.d_qa, *p.d_qb)), p.scale);
+    uint32_t acc_it = 0;
+    const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
+    for(int w = pair_id; w < p.total_work && ok; w += n_pairs) {
+      const WorkItem wi = decode_work(p, w);
+      if(skip_on && (wi.m_tile + 1) * T::kTM <= p.skip_rows_below)
+        continue;
+      const uint32_t as = acc_it & 1u;
+      const uint32_t aph = (acc_it >> 1) & 1u;
+      if(lane == 0)
+        ok = mbar_wait_bounded(&ctl->tmem_full[as], aph, abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if(!ok)
+        break;
+      tc_fence_after_sync();
+
+      const uint32_t t_addr = tmem_base + as * T::kAccStride + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int n = (2 * wi.n_tile + static_cast<int>(rank)) * kTileN + row;
+      const bool n_ok = n < p.N;
+      const int m0 = wi.m_tile * T::kTM;
+      const int cols_valid = min(T::kTM, p.M - m0);
+      const float bias_n = (p.bias != nullptr && n_ok) ? __ldg(p.bias + n) : 0.0f;
+      unsigned out_max = 0u;
+#pragma unroll 1
+      for(int c = group; c < kChunks; c += 2) {
+        const int col0 = c * T::kChunk;
+        if(col0 >= cols_valid)
+          break;
+        int32_t v[T::kChunk];
+        tmem_ld_chunk<T::kChunk>(t_addr + col0, v);
+        tc_wait_ld();
+        if(n_ok)
+          out_max = write_back_chunk<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * p.N + n, cols_valid - col0, unquant, bias_n, out_max);
+      }
+      if(p.absmax_out != nullptr) {
+        out_max = __reduce_max_sync(0xffffffffu, out_max);
+        if(lane == 0 && out_max != 0u)
+          atomicMax(p.absmax_out, out_max);
+      }
+      // hand the accumulator buffer back: all epilogue warps of this CTA meet, then one arrival per CTA
+      tc_fence_before_sync();
+      named_bar_sync(1, kEpilogueThreads);
+      if(epi_tid == 0)
+        mbar_arrive_cluster(mapa_shared(smem_u32(&ctl->tmem_empty[as]), 0u));
+      ++acc_it;
+    }
+    if(!ok) {
+      *abort_flag = 1;
+      if(lane == 0) {
+        st_cluster_u32(peer_abort, 1u);
+        atomicMax(p.status, static_cast<int>(kDevTimeoutEpilogue));
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  if(warp == 1 && leader && *abort_flag) {
+    // Something gave up: make sure no MMA is still running in either CTA before the accumulators are released.
+    if(lane == 0) {
+      int no_abort = 0;
+      tc_commit_pair(&ctl->drain, 1);
+      if(!mbar_wait_bounded(&ctl->drain, 0u, &no_abort))
+        atomicMax(p.status, static_cast<int>(kDevTimeoutDrain));
+    }
+    __syncwarp();
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();
+  if(warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, T::kTmemCols);
   }
 }
 
@@ -529,6 +811,69 @@ int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p
   return check_launch();
 }
 
+// Launch of the CTA-pair kernel: clusters of two CTAs, as many as can be resident at once.
+int launch_pair(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, const GemmPlan& plan, cudaStream_t stream) {
+  static bool attr_set[64] = {};
+  static int max_clusters[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if(dev < 0 || dev >= 64)
+    return MI8_ERR_UNSUPPORTED;
+  constexpr int smem = smem_bytes_pair();
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  if(!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(mi8_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if(e != cudaSuccess) {
+      set_last_cuda_error(e);
+      return MI8_ERR_LAUNCH;
+    }
+    // how many CTA pairs the device can hold at once (bounds the persistent grid)
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, mi8_gemm_pair_kernel, &cfg);
+    if(e != cudaSuccess || n <= 0) {
+      set_last_cuda_error(e);
+      cudaGetLastError();
+      return MI8_ERR_LAUNCH;
+    }
+    max_clusters[dev] = n;
+    attr_set[dev] = true;
+  }
+  const int pairs = plan.grid / 2 < max_clusters[dev] ? plan.grid / 2 : max_clusters[dev];
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  ProfileRecord rec{};
+  const bool profiled = t_profile.on && t_profile.records.size() < t_profile.capacity;
+  if(profiled) {
+    rec = ProfileRecord{p.M, p.N, p.K, p.out_f16 ? 2 : 4, t_profile.take(), t_profile.take()};
+    if(rec.start != nullptr && rec.stop != nullptr)
+      cudaEventRecord(rec.start, stream);
+  }
+  cudaError_t le = cudaLaunchKernelEx(&cfg, mi8_gemm_pair_kernel, tw, ta, p);
+  if(le != cudaSuccess) {
+    set_last_cuda_error(le);
+    return MI8_ERR_LAUNCH;
+  }
+  if(profiled && rec.start != nullptr && rec.stop != nullptr) {
+    cudaEventRecord(rec.stop, stream);
+    t_profile.records.push_back(rec);
+  }
+  count_launch();
+  return check_launch();
+}
+
 }  // namespace
 
 int profile_begin(int max_records) {
@@ -571,6 +916,36 @@ int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, Gemm
     return MI8_ERR_BAD_ARG;
   const int sms = sm_count();
   int tm = force_tile_m;
+  plan->pair = 0;
+  if(tm == 0 && force_splits <= 1 && M > 64) {
+    // Enough 128 x 256 tiles for every SM and at least eight K blocks per tile: the CTA-pair kernel
+    // moves a third less operand data from L2 into shared memory per output and measured 10-20 % faster
+    // there; with shorter K its extra per-tile synchronisation costs more than that saves.
+    const long long tiles256 = static_cast<long long>((N + kTileN - 1) / kTileN) * ((M + 255) / 256);
+    if(tiles256 >= sms && (K + kTileKBytes - 1) / kTileKBytes >= 8 && N > kTileN)
+      tm = kPairTileCode;
+  }
+  if(tm == kPairTileCode) {
+    // CTA-pair variant: tiles of 256 weight rows x 256 activation rows, one per cluster of two CTAs.
+    if(force_splits > 1)
+      return MI8_ERR_BAD_ARG;
+    plan->pair = 1;
+    plan->tile_m = PairCfg::kTM;
+    plan->stages = PairCfg::kStages;
+    plan->n_tiles = (N + 2 * kTileN - 1) / (2 * kTileN);
+    plan->m_tiles = (M + PairCfg::kTM - 1) / PairCfg::kTM;
+    plan->kb_total = (K + kTileKBytes - 1) / kTileKBytes;
+    plan->kb_per_split = plan->kb_total;
+    plan->splits = 1;
+    const long long pair_tiles = static_cast<long long>(plan->n_tiles) * plan->m_tiles;
+    if(pair_tiles > 0x7fffffffLL / 64)
+      return MI8_ERR_UNSUPPORTED;
+    const long long pairs = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
+    plan->grid = static_cast<int>(2 * pairs);
+    plan->smem_bytes = smem_bytes_pair();
+    plan->partial_bytes = 0;
+    return MI8_OK;
+  }
   if(tm == 0) {
     // Tile width along M.  Up to 64 rows: the smallest tile that holds them.  Above that, 256-row tiles
     // only when they already give every SM a tile; otherwise narrower tiles (a quarter of M, 32..128
@@ -655,7 +1030,7 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
   rc = encode_kmajor_map(&tw, bt, N, K, kTileN);
   if(rc != MI8_OK)
     return rc;
-  rc = encode_kmajor_map(&ta, aq, M, K, plan.tile_m);
+  rc = encode_kmajor_map(&ta, aq, M, K, plan.pair ? PairCfg::kHalfRows : plan.tile_m);
   if(rc != MI8_OK)
     return rc;
 
@@ -688,6 +1063,8 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
   if(p.status == nullptr)
     return MI8_ERR_LAUNCH;
 
+  if(plan.pair)
+    return launch_pair(tw, ta, p, plan, stream);
   switch(plan.tile_m) {
     case 16: return launch_cfg<16>(tw, ta, p, plan, stream);
     case 32: return launch_cfg<32>(tw, ta, p, plan, stream);

@@ -37,6 +37,7 @@ int check_launch();
 // ------------------------------------------------------------------ GEMM plan
 struct GemmPlan {
   int tile_m;        // activation rows per tile (MMA N): 16, 32, 64, 128 or 256
+  int pair;          // 1: CTA-pair kernel (256 weight rows x 256 activation rows per cluster of two CTAs)
   int stages;        // shared-memory pipeline depth
   int splits;        // split-K factor
   int n_tiles;       // tiles of 128 weight rows

@@ -163,6 +163,22 @@ def multiply(aq: IntgemmTensor, b: IntgemmTensor, bias: torch.Tensor | None = No
     return out
 
 
+def multiply_rows_from(aq: IntgemmTensor, b: IntgemmTensor, bias: torch.Tensor | None, out: torch.Tensor, same_a: torch.Tensor,
+                       same_b: torch.Tensor, rows_unchanged_below: int, relu: bool = False, scale: float = 1.0,
+                       ws: Workspace | None = None, tile_m: int = 0) -> torch.Tensor:
+    """mi8_multiply_i8_rows_from: when the device words same_a[0] and same_b[0] (int32/uint32 tensors) are equal, whole
+    tiles of activation rows below `rows_unchanged_below` keep what `out` already holds."""
+    m, k, n = aq.rows, aq.cols, b.rows
+    if b.cols != k or out.dtype != torch.float32 or out.numel() != m * n or not out.is_contiguous():
+        raise Mi8Error(1, "operand shapes / output layout do not match")
+    ws = ws or default_workspace(aq.device)
+    check(lib().mi8_multiply_i8_rows_from(aq.data.data_ptr(), b.data.data_ptr(), m, n, k, aq.quant_mult.data_ptr(),
+                                          b.quant_mult.data_ptr(), float(scale), bias.data_ptr() if bias is not None else None,
+                                          int(relu), out.data_ptr(), MI8_F32, ws.ptr, ws.nbytes, _stream_ptr(),
+                                          same_a.data_ptr(), same_b.data_ptr(), int(rows_unchanged_below), tile_m))
+    return out
+
+
 def _affine_or_dot(a: torch.Tensor, b: IntgemmTensor, bias, transA: bool, transB: bool, scale: float, relu: bool,
                    out_dtype=torch.float32, ws: Workspace | None = None, aq: IntgemmTensor | None = None) -> torch.Tensor:
     if not isinstance(b, IntgemmTensor):

@@ -156,6 +156,53 @@ def test_persistent_schedule_many_tiles(cuda_device, oracle):
     _run_affine(cuda_device, oracle, 4096, 256, 4096, True, True, 11)
 
 
+@pytest.mark.parametrize("m,k,n", [(512, 1024, 1024), (300, 256, 384), (777, 208, 333), (129, 128, 130), (1, 64, 8)])
+def test_cta_pair_kernel(cuda_device, oracle, m, k, n):
+    """tile_m = 512 selects the two-CTA kernel (256 x 256 tile per cluster): ragged M, odd numbers of
+    128-row weight tiles (the second CTA of the last pair has no rows), K that is not a multiple of 128."""
+    _run_affine(cuda_device, oracle, m, k, n, True, True, m + k + n, tile_m=512)
+
+
+def test_cta_pair_kernel_many_tiles(cuda_device, oracle):
+    # 16 x 16 = 256 pair tiles on 74 clusters: every pair walks several tiles and both accumulator buffers
+    _run_affine(cuda_device, oracle, 4096, 256, 4096, False, True, 12, tile_m=512)
+    _run_affine(cuda_device, oracle, 2100, 1024, 1000, True, False, 13, out_dtype=torch.float16, tile_m=512)
+
+
+@pytest.mark.parametrize("tile_m", [0, 64, 128, 256, 512])
+def test_rows_from_keeps_whole_tiles_below(cuda_device, oracle, tile_m):
+    """Equal words: tiles wholly below the row limit keep the sentinel, every other row is computed; unequal
+    words: everything is computed.  Covers the single-CTA and the two-CTA kernel."""
+    ops = _ops()
+    m, k, n = 1100, 256, 520
+    rng = np.random.default_rng(tile_m + 5)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+    bias = (rng.standard_normal(n) * 0.01).astype(np.float32)
+    bt, qb = oracle.prepare_b(w)
+    want = oracle.affine(a, bt, qb, bias, 1.0, False, want_acc=True)[0]
+    b = ops.prepareB(torch.from_numpy(w).to(cuda_device))
+    aq = ops.prepareA(torch.from_numpy(a).to(cuda_device))
+    bias_t = torch.from_numpy(bias).to(cuda_device)
+    from marian_dev_b200 import multiply_plan
+    plan = multiply_plan(m, n, k, tile_m, 0)
+    tm = 256 if plan["tile_m"] == 512 else plan["tile_m"]
+    words = torch.tensor([7, 7, 8], dtype=torch.int32, device=cuda_device)
+    for limit in (0, 300, 777, m):
+        out = torch.full((m, n), 12345.0, dtype=torch.float32, device=cuda_device)
+        ops.multiply_rows_from(aq, b, bias_t, out, words[0:1], words[1:2], limit, tile_m=tile_m)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        kept = (limit // tm) * tm      # whole tiles below the limit
+        assert np.all(got[:kept] == 12345.0)
+        assert np.array_equal(got[kept:], want[kept:])
+        out.fill_(12345.0)
+        ops.multiply_rows_from(aq, b, bias_t, out, words[0:1], words[2:3], limit, tile_m=tile_m)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), want)
+    assert ops.poll_status() == 0
+
+
 def test_fp16_output_and_scale(cuda_device, oracle):
     _run_affine(cuda_device, oracle, 96, 512, 256, False, True, 5, out_dtype=torch.float16, scale=0.125)
     _run_affine(cuda_device, oracle, 96, 512, 256, True, False, 6, scale=2.0)
