@@ -217,6 +217,7 @@ def run_ours(args):
     leg1 = mine[args.warmup:args.warmup + args.steps]
     resident = [(sid, torch.from_numpy(ids.astype(np.int64)).to(dev), torch.from_numpy(mask).to(dev)) for sid, ids, mask in leg1]
     sampler = ClockSampler(local_rank)
+    launches_before = ops.launch_count()          # warm-up launches (lets a profiler skip them)
     ops.reset_launch_count()
     tokens = 0
     barrier()
@@ -305,7 +306,7 @@ def run_ours(args):
                        "tokens_counted": "best hypothesis per sentence, EOS included", "parallelism": f"replicas x{world}",
                        "l2": "not flushed: one decode step streams ~0.2 GB of int8 weights plus fp32 logits and history, more than the 126 MB L2"},
             "e2e": {"value": round(tokens2 / (ms2 / 1e3), 1), "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
-            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "device_status": status,
+            "gpu_launches": int(launches), "gpu_launches_before_timed_region": int(launches_before), "clocks": clocks, "roofline": roofline, "device_status": status,
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu

@@ -213,14 +213,17 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     // are requested before waiting for it, the activation tiles (its output) after.
     uint32_t it = 0;
     uint32_t prefetched = 0;  // stages whose weight tile is already in flight
-    if(lane == 0 && p.skip_a == nullptr) {
+    if(p.skip_a == nullptr) {
       const WorkItem w0 = decode_work(p, blockIdx.x);
       const int n_pre = min(T::kStages, w0.kb_end - w0.kb_begin);
-      for(int i = 0; i < n_pre; ++i) {
-        uint8_t* st = tiles + i * T::kStageBytes;
-        mbar_arrive_expect_tx(&ctl->full[i], T::kStageBytes);
-        tma_load_2d(st, &tmap_w, (w0.kb_begin + i) * kTileKBytes, w0.n_tile * kTileN, &ctl->full[i]);
+      if(elect_one()) {
+        for(int i = 0; i < n_pre; ++i) {
+          uint8_t* st = tiles + i * T::kStageBytes;
+          mbar_arrive_expect_tx(&ctl->full[i], T::kStageBytes);
+          tma_load_2d(st, &tmap_w, (w0.kb_begin + i) * kTileKBytes, w0.n_tile * kTileN, &ctl->full[i]);
+        }
       }
+      __syncwarp();
       prefetched = n_pre;
     }
     pdl_wait();
@@ -232,13 +235,13 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
         const uint32_t s = it % T::kStages;
         const uint32_t ph = (it / T::kStages) & 1u;
-        const bool pre = lane == 0 && it < prefetched;
-        if(lane == 0 && !pre)
-          ok = mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        const bool pre = it < prefetched;
+        if(!pre)
+          ok = mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag);   // every lane polls: the branch stays warp-uniform
+        ok = __all_sync(0xffffffffu, ok);
         if(!ok)
           break;
-        if(lane == 0) {
+        if(elect_one()) {
           uint8_t* st = tiles + s * T::kStageBytes;
           if(!pre) {
             mbar_arrive_expect_tx(&ctl->full[s], T::kStageBytes);
@@ -276,9 +279,9 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         continue;
       const uint32_t as = acc_it & 1u;
       const uint32_t aph = (acc_it >> 1) & 1u;
-      if(lane == 0)
-        ok = mbar_wait_bounded(&ctl->tmem_empty[as], aph ^ 1u, abort_flag);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
+      // The whole warp walks the loop and polls the barriers, so every value below is warp-uniform;
+      // one elected lane issues the MMAs and commits.
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->tmem_empty[as], aph ^ 1u, abort_flag));
       if(!ok)
         break;
       tc_fence_after_sync();
@@ -286,15 +289,13 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
         const uint32_t s = it % T::kStages;
         const uint32_t ph = (it / T::kStages) & 1u;
-        if(lane == 0)
-          ok = mbar_wait_bounded(&ctl->full[s], ph, abort_flag);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->full[s], ph, abort_flag));
         if(!ok)
           break;
         tc_fence_after_sync();
-        if(lane == 0) {
-          const uint32_t w_addr = smem_u32(tiles + s * T::kStageBytes);
-          const uint32_t a_addr = w_addr + T::kWBytes;
+        const uint32_t w_addr = smem_u32(tiles + s * T::kStageBytes);
+        const uint32_t a_addr = w_addr + T::kWBytes;
+        if(elect_one()) {
 #pragma unroll
           for(int k = 0; k < kTileKBytes / kMmaK; ++k) {
             tc_mma_i8(d_tmem, make_kmajor_sw128_desc(w_addr + k * kMmaK), make_kmajor_sw128_desc(a_addr + k * kMmaK), idesc,
@@ -306,7 +307,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       }
       if(!ok)
         break;
-      if(lane == 0)
+      if(elect_one())
         tc_commit(&ctl->tmem_full[as]);  // accumulator complete
       __syncwarp();
       ++acc_it;
@@ -524,16 +525,19 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     uint32_t prefetched = 0;
     // copies of both CTAs are credited to full[s] of the rank-0 CTA
     auto full_addr = [&](uint32_t s) { return mapa_shared(smem_u32(&ctl->full[s]), 0u); };
-    if(lane == 0 && p.skip_a == nullptr && pair_id < p.total_work) {
+    if(p.skip_a == nullptr && pair_id < p.total_work) {
       // weights do not depend on the previous kernel: request the first pipeline fill before waiting for it
       const WorkItem w0 = decode_work(p, pair_id);
       const int n_pre = min(T::kStages, w0.kb_end - w0.kb_begin);
-      for(int i = 0; i < n_pre; ++i) {
-        uint8_t* st = tiles + i * T::kStageBytes;
-        if(leader)
-          mbar_arrive_expect_tx(&ctl->full[i], 2 * T::kStageBytes);
-        tma_load_2d_pair(st, &tmap_w, (w0.kb_begin + i) * kTileKBytes, (2 * w0.n_tile + static_cast<int>(rank)) * kTileN, full_addr(i));
+      if(elect_one()) {
+        for(int i = 0; i < n_pre; ++i) {
+          uint8_t* st = tiles + i * T::kStageBytes;
+          if(leader)
+            mbar_arrive_expect_tx(&ctl->full[i], 2 * T::kStageBytes);
+          tma_load_2d_pair(st, &tmap_w, (w0.kb_begin + i) * kTileKBytes, (2 * w0.n_tile + static_cast<int>(rank)) * kTileN, full_addr(i));
+        }
       }
+      __syncwarp();
       prefetched = n_pre;
     }
     pdl_wait();
@@ -545,13 +549,13 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
         const uint32_t s = it % T::kStages;
         const uint32_t ph = (it / T::kStages) & 1u;
-        const bool pre = lane == 0 && it < prefetched;
-        if(lane == 0 && !pre)
+        const bool pre = it < prefetched;
+        if(!pre)
           ok = mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        ok = __all_sync(0xffffffffu, ok);
         if(!ok)
           break;
-        if(lane == 0) {
+        if(elect_one()) {
           uint8_t* st = tiles + s * T::kStageBytes;
           if(!pre) {
             if(leader)
@@ -595,9 +599,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
           continue;
         const uint32_t as = acc_it & 1u;
         const uint32_t aph = (acc_it >> 1) & 1u;
-        if(lane == 0)
-          ok = mbar_wait_bounded(&ctl->tmem_empty[as], aph ^ 1u, abort_flag);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->tmem_empty[as], aph ^ 1u, abort_flag));
         if(!ok)
           break;
         tc_fence_after_sync();
@@ -605,15 +607,13 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
           const uint32_t s = it % T::kStages;
           const uint32_t ph = (it / T::kStages) & 1u;
-          if(lane == 0)
-            ok = mbar_wait_bounded(&ctl->full[s], ph, abort_flag);
-          ok = __shfl_sync(0xffffffffu, ok, 0);
+          ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->full[s], ph, abort_flag));
           if(!ok)
             break;
           tc_fence_after_sync();
-          if(lane == 0) {
-            const uint32_t w_addr = smem_u32(tiles + s * T::kStageBytes);
-            const uint32_t a_addr = w_addr + T::kWBytes;
+          const uint32_t w_addr = smem_u32(tiles + s * T::kStageBytes);
+          const uint32_t a_addr = w_addr + T::kWBytes;
+          if(elect_one()) {
 #pragma unroll
             for(int k = 0; k < kTileKBytes / kMmaK; ++k) {
               tc_mma_i8_pair(d_tmem, make_kmajor_sw128_desc(w_addr + k * kMmaK), make_kmajor_sw128_desc(a_addr + k * kMmaK), idesc,
@@ -625,7 +625,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         }
         if(!ok)
           break;
-        if(lane == 0)
+        if(elect_one())
           tc_commit_pair(&ctl->tmem_full[as], 3);  // accumulator complete in both CTAs
         __syncwarp();
         ++acc_it;
