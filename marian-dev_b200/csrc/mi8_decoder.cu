@@ -80,6 +80,12 @@ struct mi8d_decoder {
   int* anc[2] = {nullptr, nullptr};
   unsigned* slots = nullptr;
   int n_slots = 0;
+  // The history chain of a self-attention block (abs-max -> quantise -> key GEMM, value GEMM) does not depend on
+  // the query projection, and the two GEMMs not on each other: they run on two internal streams, forked from
+  // and joined to the caller's stream with events.
+  cudaStream_t side[2] = {nullptr, nullptr};
+  cudaEvent_t ev_x = nullptr, ev_hq = nullptr, ev_k = nullptr, ev_v = nullptr;
+  bool overlap = false;
 
   int t = 0, batch = 0, src = 0, ctx_cur = 0, anc_cur = 0, cell_cur = 0;
   bool cross_valid = false;
@@ -156,7 +162,7 @@ namespace {
 
 // aq (already quantised, multiplier behind the data) x weight -> c
 int gemm(mi8d_decoder* d, const int8_t* a, int M, const std::string& wname, const std::string& bname, bool relu, float* c,
-         cudaStream_t s, unsigned* absmax_out = nullptr) {
+         cudaStream_t s, unsigned* absmax_out = nullptr, int force_splits = 0) {
   const Weight* w = d->W(wname);
   if(w == nullptr)
     return MI8_ERR_BAD_ARG;
@@ -167,8 +173,8 @@ int gemm(mi8d_decoder* d, const int8_t* a, int M, const std::string& wname, cons
       return MI8_ERR_BAD_ARG;
   }
   const float* qa = reinterpret_cast<const float*>(a + static_cast<size_t>(M) * w->K);
-  return launch_gemm(a, w->bt, M, w->N, w->K, qa, w->qm(), 1.0f, bias, relu ? 1 : 0, c, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0,
-                     absmax_out);
+  return launch_gemm(a, w->bt, M, w->N, w->K, qa, w->qm(), 1.0f, bias, relu ? 1 : 0, c, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0,
+                     force_splits, absmax_out);
 }
 
 int quant(mi8d_decoder* /*d*/, const float* x, size_t rows, size_t dim, const unsigned* slot, int8_t* q, cudaStream_t s) {
@@ -183,6 +189,15 @@ int add_ln(mi8d_decoder* d, const float* a, const float* resid, const std::strin
     return MI8_ERR_BAD_ARG;
   return launch_add_layernorm(a, resid, g, b, 1e-6f, rows, d->cfg.dim_emb, out, rowmax, slot, s);
 }
+
+#define MI8D_CUDA(expr)               \
+  do {                                \
+    cudaError_t ce_ = (expr);         \
+    if(ce_ != cudaSuccess) {          \
+      set_last_cuda_error(ce_);       \
+      return MI8_ERR_LAUNCH;          \
+    }                                 \
+  } while(0)
 
 #define MI8D_TRY(expr)      \
   do {                      \
@@ -227,11 +242,32 @@ int mi8d_create(const mi8d_config* cfg, void* arena, size_t arena_bytes, void* w
   d->ws_bytes = workspace_bytes;
   if(d->reuse_stats != nullptr)
     cudaMemset(d->reuse_stats, 0, 2 * sizeof(unsigned));
+  if(!cfg->ssru) {
+    bool ok = cudaStreamCreateWithFlags(&d->side[0], cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&d->side[1], cudaStreamNonBlocking) == cudaSuccess;
+    for(cudaEvent_t* e : {&d->ev_x, &d->ev_hq, &d->ev_k, &d->ev_v})
+      ok = ok && cudaEventCreateWithFlags(e, cudaEventDisableTiming) == cudaSuccess;
+    d->overlap = ok;   // without them the step simply runs on the caller's stream alone
+    if(!ok)
+      cudaGetLastError();
+  }
   *out = d;
   return MI8_OK;
 }
 
-void mi8d_destroy(mi8d_decoder* d) { delete d; }
+void mi8d_destroy(mi8d_decoder* d) {
+  if(d == nullptr)
+    return;
+  for(cudaStream_t st : d->side)
+    if(st != nullptr) {
+      cudaStreamSynchronize(st);
+      cudaStreamDestroy(st);
+    }
+  for(cudaEvent_t e : {d->ev_x, d->ev_hq, d->ev_k, d->ev_v})
+    if(e != nullptr)
+      cudaEventDestroy(e);
+  delete d;
+}
 
 int mi8d_set_weight(mi8d_decoder* d, const char* name, const int8_t* bt, int K, int N) {
   if(d == nullptr || name == nullptr || bt == nullptr || K <= 0 || N <= 0)
@@ -492,26 +528,45 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
       const std::string pre = li + "_self";
       unsigned* sh = next_slot();
       unsigned* sa = next_slot();
-      MI8D_TRY(quant(d, x, R, dm, x_slot, d->aq, s));
-      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wq", pre + "_bq", false, d->qbuf, s));
       // Keys and values are projections of the WHOLE history of layer inputs, quantised with one
       // multiplier over the live part of that history.  The projections of earlier steps are kept per slab
       // and stay valid as long as that multiplier's abs-max does not change (compared bit for bit on the
       // device); then only the newest slab is quantised and projected, otherwise everything is redone.
+      // This chain only needs x and the ancestor table, so it runs beside the query projection.
+      const bool ov = d->overlap;
+      cudaStream_t sk = ov ? d->side[0] : s;   // abs-max, quantise, key GEMM
+      cudaStream_t sv = ov ? d->side[1] : s;   // value GEMM
+      if(ov) {
+        MI8D_CUDA(cudaEventRecord(d->ev_x, s));
+        MI8D_CUDA(cudaStreamWaitEvent(sk, d->ev_x, 0));
+      }
       const int steps = t + 1;
       float* hq_tail = reinterpret_cast<float*>(L.hq + static_cast<size_t>(c.max_steps) * c.max_rows * dm);
-      MI8D_TRY(launch_history_absmax(L.rowmax, d->anc[anc_new], steps, R, SR, sh, s));
-      MI8D_TRY(launch_history_quantize(L.slab, SR, steps, dm, sh, d->prev_bits + l, L.hq, hq_tail, s));
+      MI8D_TRY(launch_history_absmax(L.rowmax, d->anc[anc_new], steps, R, SR, sh, sk));
+      MI8D_TRY(launch_history_quantize(L.slab, SR, steps, dm, sh, d->prev_bits + l, L.hq, hq_tail, sk));
+      if(ov) {
+        MI8D_CUDA(cudaEventRecord(d->ev_hq, sk));
+        MI8D_CUDA(cudaStreamWaitEvent(sv, d->ev_hq, 0));
+      }
       const Weight* wk = d->W(pre + "_Wk");
       const Weight* wv = d->W(pre + "_Wv");
       const float* bk = d->P(pre + "_bk");
       const float* bv = d->P(pre + "_bv");
       if(wk == nullptr || wv == nullptr || bk == nullptr || bv == nullptr)
         return MI8_ERR_BAD_ARG;
+      // no split-K here (force_splits = 1): the three streams must not share the workspace's counters
       MI8D_TRY(launch_gemm(L.hq, wk->bt, steps * SR, wk->N, wk->K, hq_tail, wk->qm(), 1.0f, bk, 0, L.kslab, MI8_F32, nullptr, d->ws,
-                           d->ws_bytes, s, 0, 0, nullptr, d->prev_bits + l, sh, t * SR));
+                           d->ws_bytes, sk, 0, 1, nullptr, d->prev_bits + l, sh, t * SR));
       MI8D_TRY(launch_gemm(L.hq, wv->bt, steps * SR, wv->N, wv->K, hq_tail, wv->qm(), 1.0f, bv, 0, L.vslab, MI8_F32, nullptr, d->ws,
-                           d->ws_bytes, s, 0, 0, nullptr, d->prev_bits + l, sh, t * SR));
+                           d->ws_bytes, sv, 0, 1, nullptr, d->prev_bits + l, sh, t * SR));
+      MI8D_TRY(quant(d, x, R, dm, x_slot, d->aq, s));
+      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wq", pre + "_bq", false, d->qbuf, s, nullptr, ov ? 1 : 0));
+      if(ov) {
+        MI8D_CUDA(cudaEventRecord(d->ev_k, sk));
+        MI8D_CUDA(cudaEventRecord(d->ev_v, sv));
+        MI8D_CUDA(cudaStreamWaitEvent(s, d->ev_k, 0));
+        MI8D_CUDA(cudaStreamWaitEvent(s, d->ev_v, 0));
+      }
       MI8D_TRY(launch_attention1(d->qbuf, L.kslab, L.vslab, nullptr, R, c.heads, dm / c.heads, steps, batch, 0, d->abuf, sa, s,
                                  d->anc[anc_new], SR, SR));
       MI8D_TRY(quant(d, d->abuf, R, dm, sa, d->aq, s));
