@@ -120,6 +120,21 @@ int mi8_multiply_i8_ex(const int8_t* aq, const int8_t* bt, int M, int N, int K,
                        void* workspace, size_t workspace_bytes, void* stream,
                        int force_tile_m, int force_splits);
 
+/* The multiply that performs Int8::PrepareA itself (src/tensors/cpu/intgemm_interface.h:17-32 followed by
+ * :97-147 in one launch): `a` is the fp32 activation [M,K], `absmax_slot` a device word holding the bit
+ * pattern of max|a| that the activation's producer (or mi8_max_absolute_f32) left there.  The kernel
+ * derives quantMult = 127 / max|a|, quantises the rows it needs on the fly into shared memory and runs the
+ * same tcgen05 GEMM and write-back; no int8 copy of the activation is written.  qa_out (optional) receives
+ * the multiplier.  Results are bit-identical to mi8_quantize_f32_i8 + mi8_multiply_i8.  Only shapes that
+ * give every CTA one tile qualify (M * N small enough: the decode shapes); others return
+ * MI8_ERR_UNSUPPORTED and the caller takes the two-call route.  Every CTA reads its rows of the fp32
+ * activation (four times the int8 bytes), so with back-to-back launches overlapped by programmatic
+ * dependent launch the two-call route measured slightly faster (8.3 vs 8.9 us for 512 x 1024 x 1024);
+ * this entry saves a launch and the int8 buffer where that matters more. */
+int mi8_multiply_f32_slot(const float* a, const unsigned* absmax_slot, float* qa_out, const int8_t* bt,
+                          int M, int N, int K, const float* d_qb, float scale,
+                          const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* stream);
+
 /* The multiply for an activation whose leading rows did not change since the previous call (no
  * counterpart in the reference, which recomputes; used for the decoder's stored keys/values).  When the
  * two device words *same_a and *same_b are equal at the time the kernel runs, tiles of activation rows

@@ -36,7 +36,7 @@ EXPORTS = [
     "mi8_version", "mi8_strerror", "mi8_last_cuda_error", "mi8_last_cuda_error_string",
     "mi8_workspace_bytes", "mi8_workspace_init", "mi8_poll_status", "mi8_clear_status",
     "mi8_max_absolute_f32", "mi8_quantize_f32_i8", "mi8_prepare_a_f32", "mi8_prepare_b_f32",
-    "mi8_multiply_i8", "mi8_multiply_i8_ex", "mi8_multiply_i8_rows_from", "mi8_multiply_i8_static", "mi8_affine_f32", "mi8_multiply_plan",
+    "mi8_multiply_i8", "mi8_multiply_i8_ex", "mi8_multiply_i8_rows_from", "mi8_multiply_f32_slot", "mi8_multiply_i8_static", "mi8_affine_f32", "mi8_multiply_plan",
     "mi8_launch_count", "mi8_launch_count_reset", "mi8_profile_begin", "mi8_profile_end", "mi8_set_pdl",
 ]
 
@@ -88,6 +88,8 @@ def lib() -> ctypes.CDLL:
     L.mi8_multiply_i8_ex.argtypes = [vp, vp, ci, ci, ci, vp, vp, cf, vp, ci, vp, ci, vp, vp, sz, vp, ci, ci]
     L.mi8_multiply_i8_rows_from.argtypes = [vp, vp, ci, ci, ci, vp, vp, cf, vp, ci, vp, ci, vp, sz, vp, vp, vp, ci, ci]
     L.mi8_multiply_i8_rows_from.restype = ci
+    L.mi8_multiply_f32_slot.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp, cf, vp, ci, vp, ci, vp, vp]
+    L.mi8_multiply_f32_slot.restype = ci
     L.mi8_multiply_i8_static.argtypes = [vp, vp, ci, ci, ci, vp, vp, cf, vp, ci, vp, ci, vp]
     L.mi8_multiply_i8_static.restype = ci
     L.mi8_affine_f32.argtypes = [vp, ci, ci, vp, vp, ci, vp, cf, ci, vp, ci, vp, vp, sz, vp]

@@ -198,6 +198,12 @@ int mi8_multiply_i8_ex(const int8_t* aq, const int8_t* bt, int M, int N, int K, 
                      as_stream(stream), force_tile_m, force_splits);
 }
 
+int mi8_multiply_f32_slot(const float* a, const unsigned* absmax_slot, float* qa_out, const int8_t* bt, int M, int N, int K,
+                          const float* d_qb, float scale, const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out,
+                          void* stream) {
+  return launch_gemm_quant_a(a, absmax_slot, qa_out, bt, M, N, K, d_qb, scale, bias, relu, c, out_dtype, acc_out, as_stream(stream));
+}
+
 int mi8_multiply_i8_rows_from(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb,
                               float scale, const float* bias, int relu, void* c, int out_dtype, void* workspace,
                               size_t workspace_bytes, void* stream, const unsigned* same_a, const unsigned* same_b,

@@ -77,6 +77,9 @@ struct GemmParams {
   int32_t* partials;
   unsigned* tile_counters;
   unsigned* absmax_out;
+  const float* a_f32;       // quantise-in-kernel variant: fp32 activation [M,K] and the 4-byte slot that
+  const unsigned* a_slot;   // holds the bit pattern of max|A| (then aq / d_qa / the activation tensor map are unused)
+  float* qa_out;            // optional: receives the activation multiplier 127 / max|A|
   const unsigned* skip_a;   // when both are set and *skip_a == *skip_b, tiles that lie entirely below
   const unsigned* skip_b;   // row skip_rows_below are not computed (their previous results still hold)
   int skip_rows_below;
@@ -108,6 +111,16 @@ template <>
 __device__ __forceinline__ void tmem_ld_chunk<16>(uint32_t taddr, int32_t (&v)[16]) { tmem_ld_x16(taddr, v); }
 template <>
 __device__ __forceinline__ void tmem_ld_chunk<32>(uint32_t taddr, int32_t (&v)[32]) { tmem_ld_x32(taddr, v); }
+
+// Int8::PrepareA on four values: round-to-nearest-even of x * qm, saturated to +-127, packed little-endian.
+__device__ __forceinline__ unsigned pack4_i8(const float4& v, float qm) {
+  const int a = max(-127, min(127, __float2int_rn(__fmul_rn(v.x, qm))));
+  const int b = max(-127, min(127, __float2int_rn(__fmul_rn(v.y, qm))));
+  const int c = max(-127, min(127, __float2int_rn(__fmul_rn(v.z, qm))));
+  const int d = max(-127, min(127, __float2int_rn(__fmul_rn(v.w, qm))));
+  return (static_cast<unsigned>(a) & 0xffu) | ((static_cast<unsigned>(b) & 0xffu) << 8) | ((static_cast<unsigned>(c) & 0xffu) << 16) |
+         ((static_cast<unsigned>(d) & 0xffu) << 24);
+}
 
 // Dequantises one register chunk of accumulators of output column n (CH consecutive rows m starting at
 // element `base` of C, of which `valid` exist; `valid` may exceed CH) and stores it:
@@ -165,10 +178,16 @@ __device__ __forceinline__ unsigned write_back_chunk(const GemmParams& p, const 
   return out_max;
 }
 
-template <int TM>
+// kQuantA: the activation arrives as fp32 plus the abs-max slot its producer reduced; the eight epilogue
+// warps quantise the tile's rows (Int8::PrepareA: round(x * 127/max) saturated to +-127) straight into the
+// shared-memory ring in the 128-byte-swizzled K-major layout the MMA reads, so no int8 copy of the
+// activation and no quantisation launch exist.  Used when every CTA has one tile (they quantise before
+// their write-back work begins).
+template <int TM, bool kQuantA>
 __global__ void __launch_bounds__(kThreads, 1)
 mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
   using T = TileCfg<TM>;
+  constexpr int kConvWarps = kEpilogueThreads / 32;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles must start on a 1024-byte boundary.
   const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
@@ -184,7 +203,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_a);
     for(int s = 0; s < T::kStages; ++s) {
-      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->full[s], kQuantA ? 1 + kConvWarps : 1);   // producer (+ one arrival per quantising warp)
       mbar_init(&ctl->empty[s], 1);
     }
     for(int b = 0; b < 2; ++b) {
@@ -219,7 +238,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       if(elect_one()) {
         for(int i = 0; i < n_pre; ++i) {
           uint8_t* st = tiles + i * T::kStageBytes;
-          mbar_arrive_expect_tx(&ctl->full[i], T::kStageBytes);
+          mbar_arrive_expect_tx(&ctl->full[i], kQuantA ? T::kWBytes : T::kStageBytes);
           tma_load_2d(st, &tmap_w, (w0.kb_begin + i) * kTileKBytes, w0.n_tile * kTileN, &ctl->full[i]);
         }
       }
@@ -244,10 +263,11 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         if(elect_one()) {
           uint8_t* st = tiles + s * T::kStageBytes;
           if(!pre) {
-            mbar_arrive_expect_tx(&ctl->full[s], T::kStageBytes);
+            mbar_arrive_expect_tx(&ctl->full[s], kQuantA ? T::kWBytes : T::kStageBytes);
             tma_load_2d(st, &tmap_w, kb * kTileKBytes, wi.n_tile * kTileN, &ctl->full[s]);
           }
-          tma_load_2d(st + T::kWBytes, &tmap_a, kb * kTileKBytes, wi.m_tile * TM, &ctl->full[s]);
+          if(!kQuantA)
+            tma_load_2d(st + T::kWBytes, &tmap_a, kb * kTileKBytes, wi.m_tile * TM, &ctl->full[s]);
         }
         __syncwarp();
       }
@@ -328,14 +348,85 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     constexpr int kChunks = TM / T::kChunk;
     constexpr int kChunkStep = kChunks > 1 ? 2 : 1;
     const bool has_chunks = kChunks > 1 || group == 0;
-    pdl_wait();  // the activation multiplier is written by the previous kernel
-    const float unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(*p.d_qa, *p.d_qb)), p.scale);
+    pdl_wait();  // the activation multiplier (or abs-max slot) is written by the previous kernel
+    float qa;
+    if(kQuantA) {
+      const unsigned bits = *p.a_slot;
+      qa = bits == 0u ? 1.0f : __fdiv_rn(127.0f, __uint_as_float(bits));
+      if(blockIdx.x == 0 && epi_tid == 0) {
+        if(p.qa_out != nullptr)
+          *p.qa_out = qa;
+        if(bits >= 0x7f800000u)
+          atomicMax(p.status, static_cast<int>(kDevNonFinite));
+      }
+    } else {
+      qa = *p.d_qa;
+    }
+    const float unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.d_qb)), p.scale);
     uint32_t acc_it = 0;
+    uint32_t conv_it = 0;
     const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
     for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
       const WorkItem wi = decode_work(p, w);
       if(skip_on && (wi.m_tile + 1) * TM <= p.skip_rows_below)
         continue;
+      if(kQuantA) {
+        // Quantise this tile's activation rows, one 128-byte K block per pipeline stage.  A thread
+        // converts 16 consecutive K values (four 16-byte loads) into one 16-byte chunk and stores it where
+        // the 128-byte swizzle puts chunk c of row r: byte r * 128 + ((c ^ (r & 7)) << 4) of the tile.
+        // The fp32 loads of several K blocks are issued together (they do not depend on the ring), so a
+        // tile costs about one L2 round trip per batch instead of one per K block.
+        constexpr int kCpt = (TM * 8 + kEpilogueThreads - 1) / kEpilogueThreads;   // chunks per thread and K block
+        constexpr int kBatch = kCpt == 1 ? 4 : 2;
+        for(int kb0 = wi.kb_begin; kb0 < wi.kb_end && ok; kb0 += kBatch) {
+          float4 f[kBatch][kCpt][4];
+#pragma unroll
+          for(int b = 0; b < kBatch; ++b) {
+#pragma unroll
+            for(int q = 0; q < kCpt; ++q) {
+              const int c = epi_tid + q * kEpilogueThreads;
+              const int gm = wi.m_tile * TM + (c >> 3);
+              const int gk = (kb0 + b) * kTileKBytes + (c & 7) * 16;
+              const bool in = c < TM * 8 && kb0 + b < wi.kb_end && gm < p.M && gk < p.K;   // K % 16 == 0: whole chunk in or out
+              const float4* src = reinterpret_cast<const float4*>(p.a_f32 + static_cast<size_t>(in ? gm : 0) * p.K + (in ? gk : 0));
+#pragma unroll
+              for(int e = 0; e < 4; ++e)
+                f[b][q][e] = in ? src[e] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+#pragma unroll
+          for(int b = 0; b < kBatch; ++b) {
+            if(kb0 + b < wi.kb_end && ok) {
+              const uint32_t s = conv_it % T::kStages;
+              const uint32_t ph = (conv_it / T::kStages) & 1u;
+              ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag));
+              if(ok) {
+                uint8_t* a_tile = tiles + s * T::kStageBytes + T::kWBytes;
+#pragma unroll
+                for(int q = 0; q < kCpt; ++q) {
+                  const int c = epi_tid + q * kEpilogueThreads;
+                  if(c < TM * 8) {
+                    const int r = c >> 3, ch = c & 7;
+                    uint4 o;
+                    o.x = pack4_i8(f[b][q][0], qa);
+                    o.y = pack4_i8(f[b][q][1], qa);
+                    o.z = pack4_i8(f[b][q][2], qa);
+                    o.w = pack4_i8(f[b][q][3], qa);
+                    *reinterpret_cast<uint4*>(a_tile + r * 128 + ((ch ^ (r & 7)) << 4)) = o;
+                  }
+                }
+                fence_proxy_async_smem();   // the tensor core reads these bytes through the async proxy
+                __syncwarp();
+                if(lane == 0)
+                  mbar_arrive(&ctl->full[s]);
+                ++conv_it;
+              }
+            }
+          }
+        }
+        if(!ok)
+          break;
+      }
       const uint32_t as = acc_it & 1u;
       const uint32_t aph = (acc_it >> 1) & 1u;
       if(lane == 0)
@@ -777,14 +868,14 @@ struct ProfileState {
 };
 thread_local ProfileState t_profile;
 
-template <int TM>
+template <int TM, bool kQuantA = false>
 int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, const GemmPlan& plan, cudaStream_t stream) {
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   constexpr int smem = smem_bytes_for<TM>();
   if(dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(mi8_gemm_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(mi8_gemm_kernel<TM, kQuantA>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if(e != cudaSuccess) {
       set_last_cuda_error(e);
       return MI8_ERR_LAUNCH;
@@ -798,7 +889,7 @@ int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p
     if(rec.start != nullptr && rec.stop != nullptr)
       cudaEventRecord(rec.start, stream);
   }
-  cudaError_t le = launch_kernel(mi8_gemm_kernel<TM>, dim3(plan.grid), dim3(kThreads), smem, stream, tw, ta, p);
+  cudaError_t le = launch_kernel(mi8_gemm_kernel<TM, kQuantA>, dim3(plan.grid), dim3(kThreads), smem, stream, tw, ta, p);
   if(le != cudaSuccess) {
     set_last_cuda_error(le);
     return MI8_ERR_LAUNCH;
@@ -1056,6 +1147,9 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
   p.partials = wsb ? reinterpret_cast<int32_t*>(wsb + kWsOffPartials) : nullptr;
   p.tile_counters = wsb ? reinterpret_cast<unsigned*>(wsb + kWsOffTileCounters) : nullptr;
   p.absmax_out = absmax_out;
+  p.a_f32 = nullptr;
+  p.a_slot = nullptr;
+  p.qa_out = nullptr;
   p.skip_a = skip_a;
   p.skip_b = skip_b;
   p.skip_rows_below = skip_rows_below;
@@ -1071,6 +1165,80 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
     case 64: return launch_cfg<64>(tw, ta, p, plan, stream);
     case 128: return launch_cfg<128>(tw, ta, p, plan, stream);
     default: return launch_cfg<256>(tw, ta, p, plan, stream);
+  }
+}
+
+// Tile width for the quantise-in-kernel variant: one tile per CTA, tiles as narrow as still fit on the
+// SMs (each CTA reads its rows of the fp32 activation, so narrow tiles keep that read short).  0 = none fits.
+int quant_a_tile(int M, int N) {
+  const int sms = sm_count();
+  const int n_tiles = (N + kTileN - 1) / kTileN;
+  if(M <= 64)
+    return n_tiles <= sms ? (M <= 16 ? 16 : (M <= 32 ? 32 : 64)) : 0;
+  for(int tm : {32, 64})
+    if(static_cast<long long>(n_tiles) * ((M + tm - 1) / tm) <= sms)
+      return tm;
+  return 0;
+}
+
+int launch_gemm_quant_a(const float* a_f32, const unsigned* a_slot, float* qa_out, const int8_t* bt, int M, int N, int K,
+                        const float* d_qb, float scale, const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out,
+                        cudaStream_t stream, unsigned* absmax_out) {
+  if(M < 0 || N <= 0 || K <= 0)
+    return MI8_ERR_BAD_ARG;
+  if(M == 0)
+    return MI8_OK;
+  if(a_f32 == nullptr || a_slot == nullptr || bt == nullptr || d_qb == nullptr || c == nullptr)
+    return MI8_ERR_BAD_ARG;
+  if(out_dtype != MI8_F32 && out_dtype != MI8_F16)
+    return MI8_ERR_BAD_ARG;
+  if(K % 16 != 0 || (reinterpret_cast<uintptr_t>(a_f32) & 15u) || (reinterpret_cast<uintptr_t>(bt) & 15u))
+    return MI8_ERR_MISALIGNED;
+  const int tm = quant_a_tile(M, N);
+  if(tm == 0)
+    return MI8_ERR_UNSUPPORTED;
+  GemmPlan plan;
+  int rc = make_gemm_plan(M, N, K, tm, 1, &plan);
+  if(rc != MI8_OK)
+    return rc;
+  CUtensorMap tw;
+  rc = encode_kmajor_map(&tw, bt, N, K, kTileN);
+  if(rc != MI8_OK)
+    return rc;
+  GemmParams p;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.n_tiles = plan.n_tiles;
+  p.m_tiles = plan.m_tiles;
+  p.splits = 1;
+  p.kb_total = plan.kb_total;
+  p.kb_per_split = plan.kb_per_split;
+  p.total_work = plan.n_tiles * plan.m_tiles;
+  p.d_qa = nullptr;
+  p.d_qb = d_qb;
+  p.scale = scale;
+  p.bias = bias;
+  p.relu = relu ? 1 : 0;
+  p.out_f16 = out_dtype == MI8_F16 ? 1 : 0;
+  p.c = c;
+  p.acc_out = acc_out;
+  p.partials = nullptr;
+  p.tile_counters = nullptr;
+  p.absmax_out = absmax_out;
+  p.a_f32 = a_f32;
+  p.a_slot = a_slot;
+  p.qa_out = qa_out;
+  p.skip_a = nullptr;
+  p.skip_b = nullptr;
+  p.skip_rows_below = 0;
+  p.status = device_status_ptr();
+  if(p.status == nullptr)
+    return MI8_ERR_LAUNCH;
+  switch(tm) {   // the weight map stands in for the unused activation map
+    case 16: return launch_cfg<16, true>(tw, tw, p, plan, stream);
+    case 32: return launch_cfg<32, true>(tw, tw, p, plan, stream);
+    default: return launch_cfg<64, true>(tw, tw, p, plan, stream);
   }
 }
 

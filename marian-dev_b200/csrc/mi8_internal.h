@@ -67,6 +67,14 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
                 cudaStream_t stream, int force_tile_m, int force_splits, unsigned* absmax_out = nullptr,
                 const unsigned* skip_a = nullptr, const unsigned* skip_b = nullptr, int skip_rows_below = 0);
 
+// The GEMM that quantises its activation itself: `a_f32` [M,K] fp32 and `a_slot`, the 4-byte slot its
+// producer reduced max|A| into.  MI8_ERR_UNSUPPORTED when the shape does not give every CTA exactly one
+// tile (quant_a_tile() == 0): the caller then quantises with a kernel of its own and calls launch_gemm.
+int quant_a_tile(int M, int N);
+int launch_gemm_quant_a(const float* a_f32, const unsigned* a_slot, float* qa_out, const int8_t* bt, int M, int N, int K,
+                        const float* d_qb, float scale, const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out,
+                        cudaStream_t stream, unsigned* absmax_out = nullptr);
+
 // decode-step glue (mi8_glue.cu)
 int launch_embed(const float* wemb, const int* words, const float* pos, int pos_mod, float scale, int rows, int dim, float* out,
                  float* rowmax, unsigned* slot, cudaStream_t s);

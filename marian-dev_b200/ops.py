@@ -163,6 +163,30 @@ def multiply(aq: IntgemmTensor, b: IntgemmTensor, bias: torch.Tensor | None = No
     return out
 
 
+def multiply_from_slot(a: torch.Tensor, absmax_slot: torch.Tensor, b: IntgemmTensor, bias: torch.Tensor | None = None,
+                       scale: float = 1.0, relu: bool = False, out_dtype=torch.float32, acc_out: torch.Tensor | None = None,
+                       qa_out: torch.Tensor | None = None) -> torch.Tensor | None:
+    """mi8_multiply_f32_slot: the affine with PrepareA inside the GEMM kernel.  `a` fp32 [M,K], `absmax_slot` a
+    4-byte device tensor holding the bit pattern of max|a|.  Returns None when the shape does not qualify."""
+    _require_cuda(a, "a")
+    if a.dtype != torch.float32 or a.dim() != 2 or not a.is_contiguous():
+        raise Mi8Error(1, "a must be a contiguous float32 matrix")
+    m, k = a.shape
+    n = b.rows
+    if b.cols != k:
+        raise Mi8Error(1, f"inner dimensions differ: A has {k} columns, B has {b.cols} rows")
+    out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    rc = lib().mi8_multiply_f32_slot(a.data_ptr(), absmax_slot.data_ptr(), qa_out.data_ptr() if qa_out is not None else None,
+                                     b.data.data_ptr(), m, n, k, b.quant_mult.data_ptr(), float(scale),
+                                     bias.data_ptr() if bias is not None else None, int(relu), out.data_ptr(),
+                                     MI8_F32 if out_dtype == torch.float32 else MI8_F16,
+                                     acc_out.data_ptr() if acc_out is not None else None, _stream_ptr())
+    if rc == 3:      # MI8_ERR_UNSUPPORTED: not a one-tile-per-CTA shape
+        return None
+    check(rc)
+    return out
+
+
 def multiply_rows_from(aq: IntgemmTensor, b: IntgemmTensor, bias: torch.Tensor | None, out: torch.Tensor, same_a: torch.Tensor,
                        same_b: torch.Tensor, rows_unchanged_below: int, relu: bool = False, scale: float = 1.0,
                        ws: Workspace | None = None, tile_m: int = 0) -> torch.Tensor:

@@ -203,6 +203,40 @@ def test_rows_from_keeps_whole_tiles_below(cuda_device, oracle, tile_m):
     assert ops.poll_status() == 0
 
 
+@pytest.mark.parametrize("m,k,n", [(512, 1024, 1024), (512, 4096, 1024), (1, 64, 8), (16, 512, 384), (33, 208, 333), (64, 1024, 4096),
+                                   (200, 256, 640), (77, 1040, 136), (512, 512, 1152)])
+def test_multiply_quantises_its_activation(cuda_device, oracle, m, k, n):
+    """mi8_multiply_f32_slot: PrepareA inside the GEMM kernel from a pre-reduced abs-max; accumulators and
+    outputs equal the oracle's (and so the two-call route's) bit for bit; ragged M, N and K."""
+    ops = _ops()
+    rng = np.random.default_rng(m * 3 + k + n)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+    bias = (rng.standard_normal(n) * 0.01).astype(np.float32)
+    bt, qb = oracle.prepare_b(w)
+    want, want_acc, _want_aq, want_qa = oracle.affine(a, bt, qb, bias, 1.0, True, want_acc=True)
+    b = ops.prepareB(torch.from_numpy(w).to(cuda_device))
+    a_t = torch.from_numpy(a).to(cuda_device)
+    slot = a_t.abs().max().reshape(1).view(torch.int32).clone()       # bit pattern of max|a|
+    acc = torch.full((m, n), -7, dtype=torch.int32, device=cuda_device)
+    qa = torch.zeros(1, device=cuda_device)
+    out = ops.multiply_from_slot(a_t, slot, b, torch.from_numpy(bias).to(cuda_device), 1.0, True, acc_out=acc, qa_out=qa)
+    assert out is not None
+    torch.cuda.synchronize()
+    assert ops.poll_status() == 0
+    assert np.float32(qa.item()) == want_qa
+    assert np.array_equal(acc.cpu().numpy(), want_acc)
+    assert np.array_equal(out.cpu().numpy(), want)
+
+
+def test_multiply_from_slot_declines_large_shapes(cuda_device):
+    ops = _ops()
+    a = torch.randn(4096, 256, device=cuda_device)
+    b = ops.prepareB(torch.randn(256, 4096, device=cuda_device) * 0.02)
+    slot = a.abs().max().reshape(1).view(torch.int32).clone()
+    assert ops.multiply_from_slot(a, slot, b) is None
+
+
 def test_fp16_output_and_scale(cuda_device, oracle):
     _run_affine(cuda_device, oracle, 96, 512, 256, False, True, 5, out_dtype=torch.float16, scale=0.125)
     _run_affine(cuda_device, oracle, 96, 512, 256, True, False, 6, scale=2.0)
