@@ -68,7 +68,7 @@ def parse_args():
     ap.add_argument("--model", default="big", help="big (the benchmark), base, student, tiny (debugging)")
     ap.add_argument("--mini-batch", type=int, default=0, help="override the workload's mini-batch (sentences)")
     ap.add_argument("--beam", type=int, default=0, help="override the workload's beam size")
-    ap.add_argument("--cpu-sentences", type=int, default=8, help="sentences in the CPU-baseline sample")
+    ap.add_argument("--cpu-sentences", type=int, default=16, help="sentences in the CPU-baseline sample")
     ap.add_argument("--affine", default=None, help="M,K,N: time one int8 affine (abs-max + quantise + GEMM with bias and ReLU) instead of the decode")
     ap.add_argument("--sweep", action="store_true", help="time the affine shape sweep M x K x N instead of the decode")
     return ap.parse_args()

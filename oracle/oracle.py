@@ -143,6 +143,13 @@ class COracle:
     def set_threads(self, n: int) -> None:
         self.L.mo_set_threads(int(n))
 
+    def set_isa(self, isa: int) -> int:
+        """Route of the int8 multiply: 0 portable C, 1 AVX2, 2 AVX512-VNNI, -1 the best the host has
+        (values above that are clamped).  Returns the route in effect; all routes give identical sums."""
+        self.L.mo_set_isa.restype = ctypes.c_int
+        self.L.mo_set_isa.argtypes = [ctypes.c_int]
+        return int(self.L.mo_set_isa(int(isa)))
+
     def quant_mult(self, x: np.ndarray) -> np.float32:
         x = np.ascontiguousarray(x, dtype=np.float32)
         return np.float32(self.L.mo_compute_quant_mult(_p(x, ctypes.c_float), x.size))

@@ -81,12 +81,66 @@ static void mo_parallel_rows(int m, mo_row_fn fn, void* ctx) {
 }
 
 /* intgemm::MaxAbsolute(begin, end) as used by computeQuantMult (integer_common.h:173). */
-float mo_max_absolute(const float* x, size_t n) {
+static float mo_max_absolute_portable(const float* x, size_t n) {
   float m = 0.0f;
   for(size_t i = 0; i < n; ++i) {
     float a = fabsf(x[i]);
-    if(a > m) m = a;
+    if(a > m) m = a;   /* NaN never wins the comparison */
   }
+  return m;
+}
+
+#if defined(__x86_64__)
+#include <immintrin.h>
+__attribute__((target("avx2")))
+static float mo_max_absolute_avx2(const float* x, size_t n) {
+  const __m256 sign = _mm256_set1_ps(-0.0f);
+  __m256 m = _mm256_setzero_ps();
+  size_t i = 0;
+  for(; i + 8 <= n; i += 8)
+    m = _mm256_max_ps(_mm256_andnot_ps(sign, _mm256_loadu_ps(x + i)), m);   /* a NaN operand yields m, as in the scalar loop */
+  float t[8];
+  _mm256_storeu_ps(t, m);
+  float r = 0.0f;
+  for(int j = 0; j < 8; ++j) if(t[j] > r) r = t[j];
+  for(; i < n; ++i) { float a = fabsf(x[i]); if(a > r) r = a; }
+  return r;
+}
+#endif
+
+static int mo_has_avx2(void) {
+#if defined(__x86_64__)
+  static int cached = -1;
+  if(cached < 0) { __builtin_cpu_init(); cached = __builtin_cpu_supports("avx2") ? 1 : 0; }
+  return cached;
+#else
+  return 0;
+#endif
+}
+
+typedef struct { const float* x; size_t n; size_t per; float part[64]; } mo_absmax_ctx;
+static void mo_absmax_chunk(int b, int e, void* p) {
+  mo_absmax_ctx* c = (mo_absmax_ctx*)p;
+  for(int u = b; u < e; ++u) {
+    const size_t lo = (size_t)u * c->per, hi = lo + c->per < c->n ? lo + c->per : c->n;
+#if defined(__x86_64__)
+    c->part[u] = mo_has_avx2() ? mo_max_absolute_avx2(c->x + lo, hi - lo) : mo_max_absolute_portable(c->x + lo, hi - lo);
+#else
+    c->part[u] = mo_max_absolute_portable(c->x + lo, hi - lo);
+#endif
+  }
+}
+
+/* intgemm::MaxAbsolute(begin, end) as used by computeQuantMult (integer_common.h:173).  A maximum does not
+ * depend on the order it is taken in, so large inputs are split over the worker threads. */
+float mo_max_absolute(const float* x, size_t n) {
+  mo_absmax_ctx c;
+  c.x = x; c.n = n;
+  int units = (g_threads > 1 && n >= ((size_t)1 << 18)) ? (g_threads < 64 ? g_threads : 64) : 1;
+  c.per = (n + (size_t)units - 1) / (size_t)units;
+  if(units == 1) mo_absmax_chunk(0, 1, &c); else mo_parallel_rows(units, mo_absmax_chunk, &c);
+  float m = 0.0f;
+  for(int u = 0; u < units; ++u) if(c.part[u] > m) m = c.part[u];
   return m;
 }
 
@@ -109,9 +163,47 @@ static inline int8_t mo_quantize_one(float x, float quant_mult) {
 /* Int8::PrepareA(in, out, quantMult, rows, cols): element-wise quantise, same layout
  * (intgemm_interface.h:23-27).  `tail`, when non-null, receives the multiplier the way
  * getQuantMult(out) = quantMult does (intgemm_interface.h:28). */
+#if defined(__x86_64__)
+/* Same arithmetic as mo_quantize_one on 32 values at a time: one rounded multiply, round to nearest even,
+ * clamp to +-127, NaN -> 0, convert (exact for integral values), pack to bytes in order. */
+__attribute__((target("avx2")))
+static void mo_quantize_avx2(const float* in, int8_t* out, float qm, size_t n) {
+  const __m256 vq = _mm256_set1_ps(qm), hi = _mm256_set1_ps(127.0f), lo = _mm256_set1_ps(-127.0f);
+  const __m256i order = _mm256_setr_epi32(0, 4, 1, 5, 2, 6, 3, 7);
+  size_t i = 0;
+  for(; i + 32 <= n; i += 32) {
+    __m256i v[4];
+    for(int j = 0; j < 4; ++j) {
+      const __m256 prod = _mm256_mul_ps(_mm256_loadu_ps(in + i + 8 * j), vq);
+      __m256 r = _mm256_round_ps(prod, _MM_FROUND_TO_NEAREST_INT | _MM_FROUND_NO_EXC);
+      r = _mm256_max_ps(_mm256_min_ps(r, hi), lo);
+      r = _mm256_and_ps(r, _mm256_cmp_ps(prod, prod, _CMP_ORD_Q));
+      v[j] = _mm256_cvtps_epi32(r);
+    }
+    const __m256i b = _mm256_packs_epi16(_mm256_packs_epi32(v[0], v[1]), _mm256_packs_epi32(v[2], v[3]));
+    _mm256_storeu_si256((__m256i*)(out + i), _mm256_permutevar8x32_epi32(b, order));
+  }
+  for(; i < n; ++i) out[i] = mo_quantize_one(in[i], qm);
+}
+#endif
+
+typedef struct { const float* in; int8_t* out; float qm; size_t n, per; } mo_quant_ctx;
+static void mo_quant_chunk(int b, int e, void* p) {
+  mo_quant_ctx* c = (mo_quant_ctx*)p;
+  for(int u = b; u < e; ++u) {
+    const size_t lo = (size_t)u * c->per, hi = lo + c->per < c->n ? lo + c->per : c->n;
+#if defined(__x86_64__)
+    if(mo_has_avx2()) { mo_quantize_avx2(c->in + lo, c->out + lo, c->qm, hi - lo); continue; }
+#endif
+    for(size_t i = lo; i < hi; ++i) c->out[i] = mo_quantize_one(c->in[i], c->qm);
+  }
+}
+
 void mo_prepare_a(const float* in, int8_t* out, float quant_mult, int rows, int cols, float* tail) {
-  size_t n = (size_t)rows * (size_t)cols;
-  for(size_t i = 0; i < n; ++i) out[i] = mo_quantize_one(in[i], quant_mult);
+  mo_quant_ctx c = {in, out, quant_mult, (size_t)rows * (size_t)cols, 0};
+  int units = (g_threads > 1 && c.n >= ((size_t)1 << 18)) ? g_threads : 1;
+  c.per = ((c.n + (size_t)units - 1) / (size_t)units + 31) & ~(size_t)31;
+  if(units == 1) mo_quant_chunk(0, 1, &c); else mo_parallel_rows(units, mo_quant_chunk, &c);
   if(tail) memcpy(tail, &quant_mult, sizeof(float));
 }
 
@@ -132,30 +224,156 @@ float mo_prepare_b(const float* w, int k, int n, int w_is_nk, int8_t* bt) {
   return qm;
 }
 
-/* One output row against all of Bt; cloned per ISA so the same shared object runs on any x86-64 host. */
-__attribute__((target_clones("arch=icelake-server", "arch=skylake-avx512", "avx2", "default")))
-static void mo_row_times_bt(const int8_t* a_row, const int8_t* bt, int k, int n, int32_t* acc_row) {
-  for(int j = 0; j < n; ++j) {
-    const int8_t* b = bt + (size_t)j * k;
-    int32_t s = 0;
-    for(int p = 0; p < k; ++p) s += (int32_t)a_row[p] * (int32_t)b[p];
-    acc_row[j] = s;
+/* Multiply(A, B, rowsA, colsA, colsB, callback) with exact 32-bit accumulation
+ * (intgemm_interface.h:74-87).  A is [M,K] row-major int8, Bt is [N,K] row-major int8, so every output is a
+ * dot product of two K-contiguous rows.  Three routes, chosen once at run time; all give the same exact sums:
+ *   AVX512-VNNI  vpdpbusd (u8 x s8 -> s32, no saturation) on A + 128, corrected by 128 * sum_k Bt[j][k]
+ *                (the unsigned-shift trick intgemm's "Shifted" kernels use); 4 x 4 register blocking
+ *   AVX2         sign-extend to 16 bits, vpmaddwd (exact, unlike the saturating vpmaddubsw)
+ *   portable C   */
+#if defined(__x86_64__)
+#include <immintrin.h>
+
+__attribute__((target("avx512f,avx512bw,avx512vnni")))
+static void mo_rows_vnni(const int8_t* a, const int8_t* bt, int k, int n, int32_t* acc, int row_b, int row_e, int col_b, int col_e,
+                         uint8_t* au /* 4 * kp bytes */) {
+  const int kp = (k + 63) & ~63;
+  for(int i0 = row_b; i0 < row_e; i0 += 4) {
+    const int mi = row_e - i0 < 4 ? row_e - i0 : 4;
+    for(int r = 0; r < 4; ++r) {              /* A + 128 as unsigned bytes, zero padded to a multiple of 64 */
+      uint8_t* d = au + (size_t)r * kp;
+      if(r < mi) {
+        const int8_t* sr = a + (size_t)(i0 + r) * k;
+        for(int p = 0; p < k; ++p) d[p] = (uint8_t)(sr[p] + 128);
+        for(int p = k; p < kp; ++p) d[p] = 0;
+      } else {
+        memset(d, 0, (size_t)kp);
+      }
+    }
+    for(int j0 = col_b; j0 < col_e; j0 += 4) {
+      const int nj = col_e - j0 < 4 ? col_e - j0 : 4;
+      __m512i c[4][4];
+      for(int r = 0; r < 4; ++r)
+        for(int q = 0; q < 4; ++q) c[r][q] = _mm512_setzero_si512();
+      for(int p = 0; p < k; p += 64) {
+        const __mmask64 mk = (k - p) >= 64 ? ~(__mmask64)0 : (((__mmask64)1 << (k - p)) - 1);
+        __m512i vb[4];
+        for(int q = 0; q < 4; ++q)
+          vb[q] = q < nj ? _mm512_maskz_loadu_epi8(mk, bt + (size_t)(j0 + q) * k + p) : _mm512_setzero_si512();
+        for(int r = 0; r < 4; ++r) {
+          const __m512i va = _mm512_loadu_si512((const void*)(au + (size_t)r * kp + p));
+          for(int q = 0; q < 4; ++q) c[r][q] = _mm512_dpbusd_epi32(c[r][q], va, vb[q]);
+        }
+      }
+      for(int q = 0; q < nj; ++q) {
+        /* 128 * sum_k Bt[j][k] undoes the shift of A; vpdpbusd of all-ones bytes against Bt gives that sum */
+        __m512i sb = _mm512_setzero_si512();
+        const __m512i ones = _mm512_set1_epi8(1);
+        for(int p = 0; p < k; p += 64) {
+          const __mmask64 mk = (k - p) >= 64 ? ~(__mmask64)0 : (((__mmask64)1 << (k - p)) - 1);
+          sb = _mm512_dpbusd_epi32(sb, ones, _mm512_maskz_loadu_epi8(mk, bt + (size_t)(j0 + q) * k + p));
+        }
+        const int32_t corr = 128 * _mm512_reduce_add_epi32(sb);
+        for(int r = 0; r < mi; ++r)
+          acc[(size_t)(i0 + r) * n + j0 + q] = _mm512_reduce_add_epi32(c[r][q]) - corr;
+      }
+    }
   }
 }
 
-/* Multiply(A, B, rowsA, colsA, colsB, callback) with exact 32-bit accumulation
- * (intgemm_interface.h:74-87).  A is [M,K] row-major int8, Bt is [N,K] row-major int8. */
-typedef struct { const int8_t* a; const int8_t* bt; int k, n; int32_t* acc; } mo_mul_ctx;
+__attribute__((target("avx2")))
+static void mo_rows_avx2(const int8_t* a, const int8_t* bt, int k, int n, int32_t* acc, int row_b, int row_e, int col_b, int col_e) {
+  const int k16 = k & ~15;
+  for(int i = row_b; i < row_e; ++i) {
+    const int8_t* ar = a + (size_t)i * k;
+    for(int j = col_b; j < col_e; ++j) {
+      const int8_t* br = bt + (size_t)j * k;
+      __m256i c = _mm256_setzero_si256();
+      for(int p = 0; p < k16; p += 16) {
+        const __m256i va = _mm256_cvtepi8_epi16(_mm_loadu_si128((const __m128i*)(ar + p)));
+        const __m256i vb = _mm256_cvtepi8_epi16(_mm_loadu_si128((const __m128i*)(br + p)));
+        c = _mm256_add_epi32(c, _mm256_madd_epi16(va, vb));
+      }
+      __m128i h = _mm_add_epi32(_mm256_castsi256_si128(c), _mm256_extracti128_si256(c, 1));
+      h = _mm_add_epi32(h, _mm_shuffle_epi32(h, 0x4e));
+      h = _mm_add_epi32(h, _mm_shuffle_epi32(h, 0xb1));
+      int32_t sum = _mm_cvtsi128_si32(h);
+      for(int p = k16; p < k; ++p) sum += (int32_t)ar[p] * (int32_t)br[p];
+      acc[(size_t)i * n + j] = sum;
+    }
+  }
+}
+#endif
 
-static void mo_mul_rows(int b, int e, void* p) {
-  mo_mul_ctx* c = (mo_mul_ctx*)p;
-  for(int i = b; i < e; ++i) mo_row_times_bt(c->a + (size_t)i * c->k, c->bt, c->k, c->n, c->acc + (size_t)i * c->n);
+static void mo_rows_portable(const int8_t* a, const int8_t* bt, int k, int n, int32_t* acc, int row_b, int row_e, int col_b, int col_e) {
+  for(int i = row_b; i < row_e; ++i)
+    for(int j = col_b; j < col_e; ++j) {
+      const int8_t* ar = a + (size_t)i * k;
+      const int8_t* b = bt + (size_t)j * k;
+      int32_t sum = 0;
+      for(int p = 0; p < k; ++p) sum += (int32_t)ar[p] * (int32_t)b[p];
+      acc[(size_t)i * n + j] = sum;
+    }
+}
+
+/* 0 portable, 1 AVX2, 2 AVX512-VNNI; mo_set_isa(-1) picks the best the host has (the default). */
+static int g_isa = -1;
+static int mo_best_isa(void) {
+#if defined(__x86_64__)
+  __builtin_cpu_init();
+  if(__builtin_cpu_supports("avx512vnni") && __builtin_cpu_supports("avx512bw")) return 2;
+  if(__builtin_cpu_supports("avx2")) return 1;
+#endif
+  return 0;
+}
+int mo_set_isa(int isa) {
+  const int best = mo_best_isa();
+  g_isa = (isa < 0 || isa > best) ? best : isa;
+  return g_isa;
+}
+
+/* Work is dealt to the threads in units of 4 rows when there are enough rows, otherwise (the skinny decode
+ * shapes) in units of 16 weight rows, every thread then walking all activation rows. */
+typedef struct { const int8_t* a; const int8_t* bt; int m, k, n; int32_t* acc; int isa; int by_cols; } mo_mul_ctx;
+
+static void mo_mul_range(const mo_mul_ctx* c, int rb, int re, int cb, int ce) {
+#if defined(__x86_64__)
+  if(c->isa == 2) {
+    const int kp = (c->k + 63) & ~63;
+    uint8_t* au = (uint8_t*)aligned_alloc(64, (size_t)4 * kp);
+    if(au != NULL) {
+      mo_rows_vnni(c->a, c->bt, c->k, c->n, c->acc, rb, re, cb, ce, au);
+      free(au);
+      return;
+    }
+  }
+  if(c->isa >= 1) {
+    mo_rows_avx2(c->a, c->bt, c->k, c->n, c->acc, rb, re, cb, ce);
+    return;
+  }
+#endif
+  mo_rows_portable(c->a, c->bt, c->k, c->n, c->acc, rb, re, cb, ce);
+}
+
+static void mo_mul_units(int b, int e, void* p) {
+  const mo_mul_ctx* c = (const mo_mul_ctx*)p;
+  if(c->by_cols) {
+    const int cb = b * 16, ce = e * 16 < c->n ? e * 16 : c->n;
+    mo_mul_range(c, 0, c->m, cb, ce);
+  } else {
+    const int rb = b * 4, re = e * 4 < c->m ? e * 4 : c->m;
+    mo_mul_range(c, rb, re, 0, c->n);
+  }
 }
 
 int mo_multiply_i32(const int8_t* a, const int8_t* bt, int m, int k, int n, int32_t* acc) {
   if(m < 0 || k <= 0 || n <= 0) return MO_BAD_ARG;
-  mo_mul_ctx c = {a, bt, k, n, acc};
-  mo_parallel_rows(m, mo_mul_rows, &c);
+  if(m == 0) return MO_OK;
+  if(g_isa < 0) mo_set_isa(-1);
+  mo_mul_ctx c = {a, bt, m, k, n, acc, g_isa, 0};
+  const int row_units = (m + 3) / 4, col_units = (n + 15) / 16;
+  c.by_cols = row_units < 2 * g_threads && col_units > row_units;
+  mo_parallel_rows(c.by_cols ? col_units : row_units, mo_mul_units, &c);
   return MO_OK;
 }
 
@@ -219,7 +437,10 @@ static void mo_wr_rows(int b, int e, void* p) {
 
 void mo_unquantize_write(const int32_t* acc, int m, int n, float unquant, const float* bias, int relu, float* out) {
   mo_wr_ctx c = {acc, n, unquant, bias, relu, out};
-  mo_parallel_rows(m, mo_wr_rows, &c);
+  if((size_t)m * n < ((size_t)1 << 17))
+    mo_wr_rows(0, m, &c);            /* too little work to pay for starting threads */
+  else
+    mo_parallel_rows(m, mo_wr_rows, &c);
 }
 
 /* The whole affineOrDotTyped sequence (intgemm_interface.h:46-99) for float A [M,K] and a converted
@@ -366,13 +587,18 @@ static inline float mo_group_sum(const float* v, int g) {
  * mode 0: base = r, stride = rows (time-major history); mode 1: base = (r % batch)*len (cross-attention);
  * mode 2: base = (r / len)*len (encoder self-attention, rows ordered [batch, len]).
  * A head is handled by g = dh/4 workers, worker j owning elements 4j..4j+3 of the head. */
-MO_FMA_CLONES void mo_attention1(const float* q, const float* k, const float* v, const float* log_mask, int rows, int heads, int dh,
-                                 int len, int batch, int mode, float* out) {
+typedef struct { const float *q, *k, *v, *log_mask; int rows, heads, dh, len, batch, mode; float* out; } mo_att_ctx;
+
+MO_FMA_CLONES static void mo_attention_rows(int rb, int re, void* ctx) {
+  const mo_att_ctx* c = (const mo_att_ctx*)ctx;
+  const float *q = c->q, *k = c->k, *v = c->v, *log_mask = c->log_mask;
+  const int rows = c->rows, heads = c->heads, dh = c->dh, len = c->len, batch = c->batch, mode = c->mode;
+  float* out = c->out;
   const int dim = heads * dh;
   const int g = dh / 4;
   const float scale = 1.0f / sqrtf((float)dh);
   float* p = (float*)malloc(sizeof(float) * (size_t)len);
-  for(int r = 0; r < rows; ++r) {
+  for(int r = rb; r < re; ++r) {
     const int group = mode == 1 ? r % batch : (mode == 2 ? r / len : 0);
     const size_t base = mode == 0 ? (size_t)r : (size_t)group * len;
     const size_t stride = mode == 0 ? (size_t)rows : 1;
@@ -405,24 +631,41 @@ MO_FMA_CLONES void mo_attention1(const float* q, const float* k, const float* v,
       }
       const float sum = mo_group_sum(part, g);
       for(int pos = 0; pos < len; ++pos) p[pos] = p[pos] / sum;
+      /* every output element is the fma chain over the positions in ascending order, starting from 0;
+       * walking position-major keeps that order per element and reads each value row contiguously */
       float* o = out + (size_t)r * dim + h * dh;
-      for(int i = 0; i < dh; ++i) {
-        float acc = 0.0f;
-        for(int pos = 0; pos < len; ++pos) acc = fmaf(p[pos], v[(base + pos * stride) * dim + h * dh + i], acc);
-        o[i] = acc;
+      float acc[128];
+      for(int i = 0; i < dh; ++i) acc[i] = 0.0f;
+      for(int pos = 0; pos < len; ++pos) {
+        const float w = p[pos];
+        const float* vr = v + (base + pos * stride) * dim + h * dh;
+        for(int i = 0; i < dh; ++i) acc[i] = fmaf(w, vr[i], acc[i]);
       }
+      for(int i = 0; i < dh; ++i) o[i] = acc[i];
     }
   }
   free(p);
 }
 
+void mo_attention1(const float* q, const float* k, const float* v, const float* log_mask, int rows, int heads, int dh, int len, int batch,
+                   int mode, float* out) {
+  mo_att_ctx c = {q, k, v, log_mask, rows, heads, dh, len, batch, mode, out};
+  mo_parallel_rows(rows, mo_attention_rows, &c);
+}
+
 /* larger value first; ties: smaller index first */
 static inline int mo_better(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
-
 /* cand_score[r][j] = (j-th largest logit - lse(row)) + prev_score[r]; cand_word[r][j]; k <= 8 */
-MO_FMA_CLONES void mo_lse_topk(const float* logits, int rows, int vocab, int k, const float* prev_scores, float* cand_score,
-                               int32_t* cand_word) {
-  for(int r = 0; r < rows; ++r) {
+typedef struct { const float* logits; int vocab, k; const float* prev_scores; float* cand_score; int32_t* cand_word; } mo_lse_ctx;
+
+MO_FMA_CLONES static void mo_lse_rows(int rb, int re, void* ctx) {
+  const mo_lse_ctx* c = (const mo_lse_ctx*)ctx;
+  const float* logits = c->logits;
+  const int vocab = c->vocab, k = c->k;
+  const float* prev_scores = c->prev_scores;
+  float* cand_score = c->cand_score;
+  int32_t* cand_word = c->cand_word;
+  for(int r = rb; r < re; ++r) {
     const float* row = logits + (size_t)r * vocab;
     float tv[8];
     int ti[8];
@@ -456,6 +699,11 @@ MO_FMA_CLONES void mo_lse_topk(const float* logits, int rows, int vocab, int k, 
       cand_word[(size_t)r * k + j] = ti[j];
     }
   }
+}
+
+void mo_lse_topk(const float* logits, int rows, int vocab, int k, const float* prev_scores, float* cand_score, int32_t* cand_word) {
+  mo_lse_ctx c = {logits, vocab, k, prev_scores, cand_score, cand_word};
+  mo_parallel_rows(rows, mo_lse_rows, &c);
 }
 
 /* out[r,:] = wemb[words[r],:] * scale + pos[(pos_mod ? r % pos_mod : 0),:]   (words NULL: zero embedding) */

@@ -48,6 +48,28 @@ def test_threads_do_not_change_results(oracle):
     assert np.array_equal(r1, a.astype(np.int64) @ b.astype(np.int64).T)
 
 
+def test_multiply_routes_agree_with_exact_integer_product(oracle):
+    """The vectorised routes of the checker's int8 multiply (AVX512-VNNI with the +128 shift, AVX2 with 16-bit
+    widening) and the portable loop all equal the exact integer product, extreme values and ragged K included."""
+    rng = np.random.default_rng(3)
+    best = oracle.set_isa(-1)
+    try:
+        for (m, k, n) in [(7, 208, 33), (33, 1040, 130), (5, 64, 1), (1, 16, 3), (9, 4096, 17)]:
+            a = rng.integers(-127, 128, size=(m, k), dtype=np.int8)
+            bt = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+            a[0, :] = 127
+            bt[0, :] = -127
+            want = a.astype(np.int64) @ bt.astype(np.int64).T
+            for isa in range(best + 1):
+                assert oracle.set_isa(isa) == isa
+                for threads in (1, 3):
+                    oracle.set_threads(threads)
+                    assert np.array_equal(oracle.multiply_i32(a, bt).astype(np.int64), want), (m, k, n, isa, threads)
+    finally:
+        oracle.set_isa(-1)
+        oracle.set_threads(1)
+
+
 def test_quantise_rounding_and_saturation(oracle):
     x = np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 126.5, 127.0, -127.0, 300.0, -300.0, 0.49999997], dtype=np.float32)
     want = np.array([0, 2, 2, 0, -2, -2, 126, 127, -127, 127, -127, 0], dtype=np.int8)
