@@ -85,3 +85,18 @@ def test_base_model_sample_identical(cuda_device):
     """Transformer-base dimensions (d=512, 8 heads, 32000 words), one small mini-batch: identical sequences."""
     same, total, got, want, _ = _decode_both("base", 12, 12, 4, seed=0, lo=8, hi=20, native=True)
     assert same == total, f"only {same}/{total} sentences identical"
+
+
+@pytest.mark.parametrize("mini_batch", [1, 16])
+def test_student_model_greedy_identical(cuda_device, mini_batch):
+    """The student's dimensions (12 encoder layers d=256 ffn=1536, 2-layer SSRU decoder, 32000 words), greedy,
+    mini-batch 1 and 16: the M = 1..16 weight-streaming shapes, identical sequences."""
+    n = 3 if mini_batch == 1 else 16
+    same, total, got, want, _ = _decode_both("student", n, mini_batch, 1, seed=2, lo=5, hi=18, native=True)
+    assert same == total, f"only {same}/{total} sentences identical"
+
+
+def test_big_model_sample_identical(cuda_device):
+    """Transformer-big dimensions (d=1024, ffn=4096, 16 heads, 32000 words), beam 4, one small mini-batch."""
+    same, total, got, want, _ = _decode_both("big", 8, 8, 4, seed=1, lo=6, hi=14, native=True)
+    assert same == total, f"only {same}/{total} sentences identical"
