@@ -212,6 +212,7 @@ def run_ours(args):
     for b in mine[:args.warmup]:
         search.search(b[1], b[2])
     torch.cuda.synchronize()
+    int8_peak = round(ops.measure_int8_peak(), 1) if rank == 0 else None
 
     # ---- leg 1: inputs resident in HBM ------------------------------------------------------
     leg1 = mine[args.warmup:args.warmup + args.steps]
@@ -290,6 +291,7 @@ def run_ours(args):
             "traffic": 44.7e6, "traffic_unit": "bytes per launch of the 512x1024x32000 shape",
             "launches": gemm_total["launches"], "avg_launch_us": round(gemm_total["us"] / max(1, gemm_total["launches"]), 2),
             "tops": round(gemm_total["ops"] / max(gemm_total["us"], 1e-9) / 1e6, 1),
+            "int8_mma_peak_tops": int8_peak,   # a loop of the kernel's MMAs alone, measured on this GPU just before the timed region
             "gemm_share_of_step_time": round(gemm_total["us"] / 1e3 / max(ms_profiled, 1e-9), 3),
             "profiled_pass_ms": round(ms_profiled, 2),
             "by_shape": {k: {"launches": v["launches"], "us_total": round(v["us"], 1),
@@ -428,6 +430,10 @@ def run_affines(args):
     warm = torch.randn(8192, 8192, device="cuda", dtype=torch.bfloat16)
     for _ in range(30):
         warm @ warm                                   # bring the clocks up before timing microsecond kernels
+    if args.sweep:
+        from marian_dev_b200 import ops
+        print(json.dumps({"metric": "int8_mma_peak", "TOPS": round(ops.measure_int8_peak(), 1),
+                          "how": "loop of tcgen05.mma kind::i8 128x256x32 on every SM, no loads or stores, CUDA events, best of 3"}), flush=True)
     torch.cuda.synchronize()
     if args.affine:
         shapes = [tuple(int(v) for v in args.affine.split(","))]

@@ -120,6 +120,13 @@ int mi8_multiply_i8_ex(const int8_t* aq, const int8_t* bt, int M, int N, int K,
                        void* workspace, size_t workspace_bytes, void* stream,
                        int force_tile_m, int force_splits);
 
+/* Measurement aid (no counterpart in the reference): runs, on every SM, a loop of `k_blocks` x 4
+ * tcgen05.mma kind::i8 instructions (128 x 256 x 32 each) on one resident shared-memory tile, without loads
+ * or write-back, times it with CUDA events (best of three) and returns the rate in TOPS (host float).
+ * This is the int8 tensor-pipe figure the roofline fractions of the large-M shapes are quoted against;
+ * synchronises the stream. */
+int mi8_measure_int8_peak(int k_blocks, float* tops_out, void* stream);
+
 /* The multiply that performs Int8::PrepareA itself (src/tensors/cpu/intgemm_interface.h:17-32 followed by
  * :97-147 in one launch): `a` is the fp32 activation [M,K], `absmax_slot` a device word holding the bit
  * pattern of max|a| that the activation's producer (or mi8_max_absolute_f32) left there.  The kernel

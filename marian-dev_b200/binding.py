@@ -37,7 +37,7 @@ EXPORTS = [
     "mi8_workspace_bytes", "mi8_workspace_init", "mi8_poll_status", "mi8_clear_status",
     "mi8_max_absolute_f32", "mi8_quantize_f32_i8", "mi8_prepare_a_f32", "mi8_prepare_b_f32",
     "mi8_multiply_i8", "mi8_multiply_i8_ex", "mi8_multiply_i8_rows_from", "mi8_multiply_f32_slot", "mi8_multiply_i8_static", "mi8_affine_f32", "mi8_multiply_plan",
-    "mi8_launch_count", "mi8_launch_count_reset", "mi8_profile_begin", "mi8_profile_end", "mi8_set_pdl",
+    "mi8_launch_count", "mi8_launch_count_reset", "mi8_measure_int8_peak", "mi8_profile_begin", "mi8_profile_end", "mi8_set_pdl",
 ]
 
 
@@ -94,6 +94,8 @@ def lib() -> ctypes.CDLL:
     L.mi8_multiply_i8_static.restype = ci
     L.mi8_affine_f32.argtypes = [vp, ci, ci, vp, vp, ci, vp, cf, ci, vp, ci, vp, vp, sz, vp]
     L.mi8_multiply_plan.argtypes = [ci, ci, ci, ci, ci, ctypes.POINTER(ci * 8)]
+    L.mi8_measure_int8_peak.argtypes = [ci, ctypes.POINTER(cf), vp]
+    L.mi8_measure_int8_peak.restype = ci
     L.mi8_set_pdl.argtypes = [ci]
     L.mi8_set_pdl.restype = None
     L.mi8_profile_begin.argtypes = [ci]

@@ -233,6 +233,8 @@ int mi8_affine_f32(const float* a, int M, int K, const int8_t* bt, const float* 
 
 void mi8_set_pdl(int enabled) { set_pdl(enabled != 0); }
 
+int mi8_measure_int8_peak(int k_blocks, float* tops_out, void* stream) { return measure_int8_mma_peak(k_blocks, tops_out, as_stream(stream)); }
+
 int mi8_profile_begin(int max_records) { return profile_begin(max_records); }
 int mi8_profile_end(mi8_gemm_record* records, int capacity, int* count) { return profile_end(records, capacity, count); }
 

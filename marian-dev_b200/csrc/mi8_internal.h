@@ -50,6 +50,9 @@ struct GemmPlan {
 };
 int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, GemmPlan* plan);
 
+// mi8_peak.cu: TOPS of a loop of this library's int8 MMAs alone (k_blocks 128-byte K blocks per SM).
+int measure_int8_mma_peak(int k_blocks, float* tops_out, cudaStream_t stream);
+
 int profile_begin(int max_records);
 int profile_end(mi8_gemm_record* out, int capacity, int* count);
 

@@ -14,6 +14,8 @@ torch is used for device memory and streams only; all arithmetic runs in libmari
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import binding
@@ -161,6 +163,13 @@ def multiply(aq: IntgemmTensor, b: IntgemmTensor, bias: torch.Tensor | None = No
     if out_shape is not None:
         out = out.view(out_shape)
     return out
+
+
+def measure_int8_peak(k_blocks: int = 8192) -> float:
+    """TOPS of a loop of the library's int8 MMAs alone on every SM (mi8_measure_int8_peak)."""
+    out = ctypes.c_float(0.0)
+    check(lib().mi8_measure_int8_peak(int(k_blocks), ctypes.byref(out), _stream_ptr()))
+    return float(out.value)
 
 
 def multiply_from_slot(a: torch.Tensor, absmax_slot: torch.Tensor, b: IntgemmTensor, bias: torch.Tensor | None = None,

@@ -237,6 +237,15 @@ def test_multiply_from_slot_declines_large_shapes(cuda_device):
     assert ops.multiply_from_slot(a, slot, b) is None
 
 
+def test_int8_mma_peak_measurement(cuda_device):
+    """The measurement aid runs, raises no device status and reports a plausible tensor-pipe rate (above what the
+    full GEMM reaches, below the nominal 4.5 POPS of the part)."""
+    ops = _ops()
+    tops = ops.measure_int8_peak(2048)
+    assert ops.poll_status() == 0
+    assert 500.0 < tops < 4600.0
+
+
 def test_fp16_output_and_scale(cuda_device, oracle):
     _run_affine(cuda_device, oracle, 96, 512, 256, False, True, 5, out_dtype=torch.float16, scale=0.125)
     _run_affine(cuda_device, oracle, 96, 512, 256, True, False, 6, scale=2.0)
