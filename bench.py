@@ -287,7 +287,7 @@ def run_ours(args):
             "bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
             "frac": round(achieved / hbm_peak, 4), "peak_source": peak_src,
             # DRAM read + write of one output-layer launch (M=512, K=1024, N=32000; algorithmic 98.9 MB, part of C stays in L2),
-            # from the ncu capture summarised in profiles/gemm_kernel_ncu_b200.md
+            # measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on one launch of that shape
             "traffic": 44.7e6, "traffic_unit": "bytes per launch of the 512x1024x32000 shape",
             "launches": gemm_total["launches"], "avg_launch_us": round(gemm_total["us"] / max(1, gemm_total["launches"]), 2),
             "tops": round(gemm_total["ops"] / max(gemm_total["us"], 1e-9) / 1e6, 1),
@@ -423,14 +423,61 @@ def time_affine(m, k, n, iters=40):
             "algorithmic_bytes": by, "launches_per_affine": 3, "operand_sets": copies}
 
 
+def time_affine_sharded(m, k, n, rank, world, iters=40):
+    """The same affine with the rows of A split over the ranks (one MAX all-reduce of a float between the
+    abs-max and the quantisation).  Launched eagerly (the collective sits between the kernels), timed with
+    CUDA events, maximum over the ranks; GB/s and TOPS are for the whole M x K x N problem."""
+    import torch
+    import torch.distributed as dist
+    from marian_dev_b200 import ops, parallel
+    dev = torch.device("cuda", torch.cuda.current_device())
+    b, e = parallel.shard_rows(m, rank, world)
+    ml = e - b
+    per_copy = 4 * ml * k + n * k + 4 * ml * n
+    copies = max(2, min(32, int(300e6 // max(per_copy, 1)) + 1))
+    g = torch.Generator(device=dev).manual_seed(1234)          # the same weights on every rank
+    ws = [ops.prepareB(torch.randn(k, n, device=dev, generator=g) * 0.02) for _ in range(copies)]
+    bias = torch.randn(n, device=dev, generator=g) * 0.01
+    xs = [torch.randn(max(ml, 1), k, device=dev)[:ml] for _ in range(copies)]
+    for i in range(5):
+        if ml > 0:
+            parallel.sharded_affine(xs[i % copies], ws[i % copies], bias, 1.0, True)
+        else:
+            parallel.global_abs_max(torch.zeros(1, device=dev))
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        if ml > 0:
+            parallel.sharded_affine(xs[i % copies], ws[i % copies], bias, 1.0, True)
+        else:                                                   # fewer rows than ranks: still take part in the exchange
+            parallel.global_abs_max(torch.zeros(1, device=dev))
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) * 1000.0 / iters], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t[0])
+    by = 4 * m * k + k * n + 4 * n + 4 * m * n + 8
+    return {"M": m, "K": k, "N": n, "us_per_affine": round(us, 2), "GBps": round(by / us / 1e3, 1), "TOPS": round(2.0 * m * n * k / us / 1e6, 2),
+            "algorithmic_bytes": by, "n_gpus": world, "rows_per_rank": (m + world - 1) // world, "operand_sets": copies}
+
+
 def run_affines(args):
     import torch
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the int8 engine has no CPU path")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     warm = torch.randn(8192, 8192, device="cuda", dtype=torch.bfloat16)
     for _ in range(30):
         warm @ warm                                   # bring the clocks up before timing microsecond kernels
-    if args.sweep:
+    if args.sweep and rank == 0:
         from marian_dev_b200 import ops
         print(json.dumps({"metric": "int8_mma_peak", "TOPS": round(ops.measure_int8_peak(), 1),
                           "how": "loop of tcgen05.mma kind::i8 128x256x32 on every SM, no loads or stores, CUDA events, best of 3"}), flush=True)
@@ -440,9 +487,17 @@ def run_affines(args):
     else:
         shapes = [(m, k, n) for m in (1, 8, 64, 256, 1024, 4096) for k in (512, 1024, 4096) for n in (512, 2048, 4096, 32000)]
     for (m, k, n) in shapes:
-        r = time_affine(m, k, n)
-        r.update({"metric": "int8_affine", "timing": "CUDA-graph replay of 40 affines, CUDA events, operand sets rotated through > L2"})
-        print(json.dumps(r), flush=True)
+        if world > 1:
+            r = time_affine_sharded(m, k, n, rank, world)
+            r.update({"metric": "int8_affine_rows_sharded",
+                      "timing": "40 eager affines per rank (abs-max, MAX all-reduce of one float, quantise, GEMM), CUDA events, max over ranks"})
+        else:
+            r = time_affine(m, k, n)
+            r.update({"metric": "int8_affine", "timing": "CUDA-graph replay of 40 affines, CUDA events, operand sets rotated through > L2"})
+        if rank == 0:
+            print(json.dumps(r), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

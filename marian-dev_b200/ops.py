@@ -114,6 +114,30 @@ def prepareA(a: torch.Tensor, out: IntgemmTensor | None = None, ws: Workspace | 
     return out
 
 
+def max_absolute(a: torch.Tensor, ws: Workspace | None = None) -> torch.Tensor:
+    """max|a| as a one-element float32 device tensor (intgemm::MaxAbsolute, integer_common.h:173)."""
+    _require_cuda(a, "a")
+    if a.dtype != torch.float32:
+        raise Mi8Error(1, "max_absolute expects float32")
+    a = a.contiguous()
+    ws = ws or default_workspace(a.device)
+    out = torch.empty(2, dtype=torch.float32, device=a.device)      # [max|a|, 127/max|a|]
+    check(lib().mi8_max_absolute_f32(a.data_ptr(), a.numel(), out.data_ptr(), out[1:].data_ptr(), ws.ptr, ws.nbytes, _stream_ptr()))
+    return out[:1]
+
+
+def quantize_with_absmax(a: torch.Tensor, absmax: torch.Tensor, out: IntgemmTensor | None = None) -> IntgemmTensor:
+    """Int8::PrepareA with quantMult = 127 / absmax[0] taken from a device tensor (for instance a maximum
+    that several ranks agreed on); the multiplier is stored behind the data as usual."""
+    _require_cuda(a, "a")
+    a = a.contiguous()
+    rows = a.numel() // a.shape[-1]
+    cols = a.shape[-1]
+    q = out if out is not None else IntgemmTensor(rows, cols, a.device)
+    check(lib().mi8g_quantize_slot(a.data_ptr(), a.numel(), absmax.data_ptr(), q.data.data_ptr(), q.quant_mult.data_ptr(), _stream_ptr()))
+    return q
+
+
 def prepareB(w: torch.Tensor, w_is_nk: bool = False, ws: Workspace | None = None) -> IntgemmTensor:
     """marian-conv's intgemm8 conversion of one weight: W[K,N] fp32 -> Bt[N,K] int8 + multiplier."""
     _require_cuda(w, "W")

@@ -2,7 +2,12 @@
 whole sentences dealt round-robin (src/translator/translator.h:154-167: ``graphs_[id % numDevices_]``).
 Activation multipliers depend only on the mini-batch, so a mini-batch decodes to the same tokens on
 any rank.  The only exchange is the gather of the outputs (the reference's OutputCollector orders them
-by line number on the host, src/translator/output_collector.h:47-60)."""
+by line number on the host, src/translator/output_collector.h:47-60).
+
+A single affine can also be split by rows of the activation.  Its multiplier 127 / max|A| is a property of
+the WHOLE tensor (src/tensors/cpu/integer_common.h:169-173), so the ranks exchange one float - the maximum
+of their local maxima - between the abs-max and the quantisation; everything else is local, and the rows
+a rank computes are bit-identical to the same rows of the unsharded affine."""
 from __future__ import annotations
 
 import torch
@@ -42,3 +47,29 @@ def gather_outputs(local: dict, max_len: int, device=None) -> dict:
             if sid >= 0:
                 merged[sid] = [int(t) for t in row[2:2 + int(row[1])]]
     return merged
+
+
+def shard_rows(m: int, rank: int, world: int):
+    """Contiguous, near-even split of m rows: rank r owns [begin, end)."""
+    per, extra = divmod(m, world)
+    begin = rank * per + min(rank, extra)
+    return begin, begin + per + (1 if rank < extra else 0)
+
+
+def global_abs_max(local_max: torch.Tensor, group=None) -> torch.Tensor:
+    """In-place MAX all-reduce of a one-element float32 tensor (4 bytes on the wire); a no-op without a
+    process group.  Works on CPU tensors (gloo) and CUDA tensors (NCCL)."""
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(local_max, op=dist.ReduceOp.MAX, group=group)
+    return local_max
+
+
+def sharded_affine(a_local: torch.Tensor, b, bias=None, scale: float = 1.0, relu: bool = False, out_dtype=torch.float32,
+                   group=None) -> torch.Tensor:
+    """The int8 affine on this rank's rows of A: local abs-max, one MAX all-reduce of a float, quantisation
+    with the agreed multiplier, GEMM with the fused write-back.  Returns this rank's rows of C."""
+    from . import ops
+    amax = ops.max_absolute(a_local)
+    global_abs_max(amax, group)
+    aq = ops.quantize_with_absmax(a_local, amax)
+    return ops.multiply(aq, b, bias, scale, relu, out_dtype=out_dtype)

@@ -60,3 +60,72 @@ def test_shard_batches_is_round_robin():
     assert parallel.shard_batches(batches, 0, 4) == [0, 4, 8]
     assert parallel.shard_batches(batches, 3, 4) == [3, 7]
     assert sum((parallel.shard_batches(batches, r, 3) for r in range(3)), []).__len__() == 10
+
+
+def _affine_worker(rank, world, port, out):
+    """One rank of the row-sharded affine, with the CPU checker standing in for the device kernels: local
+    abs-max, the MAX all-reduce of one float (the code under test), quantisation with the agreed multiplier."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from marian_dev_b200 import parallel
+    from oracle.oracle import COracle
+    o = COracle()
+    rng = np.random.default_rng(5)
+    m, k, n = 37, 64, 24
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    a[30, 3] = 9.5                                   # the global maximum lives on the last rank only
+    w = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+    bias = (rng.standard_normal(n) * 0.01).astype(np.float32)
+    bt, qb = o.prepare_b(w)
+    b, e = parallel.shard_rows(m, rank, world)
+    local_max = torch.tensor([np.abs(a[b:e]).max()], dtype=torch.float32)
+    parallel.global_abs_max(local_max)
+    qa = np.float32(127.0) / np.float32(local_max.item())
+    aq = o.quantize(a[b:e], qa)
+    acc = o.multiply_i32(aq, bt)
+    unquant = np.float32(np.float32(1.0) / np.float32(np.float32(qa) * np.float32(qb))) * np.float32(1.0)
+    c = o.unquantize(acc, unquant, bias, False)
+    out.put((rank, b, e, c))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_row_sharded_affine_matches_unsharded_with_two_gloo_ranks():
+    sys.path.insert(0, ROOT)
+    from oracle.oracle import COracle
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_affine_worker, args=(r, 2, 29733, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    parts = [q.get(timeout=120) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    o = COracle()
+    rng = np.random.default_rng(5)
+    m, k, n = 37, 64, 24
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    a[30, 3] = 9.5
+    w = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+    bias = (rng.standard_normal(n) * 0.01).astype(np.float32)
+    bt, qb = o.prepare_b(w)
+    want = o.affine(a, bt, qb, bias, 1.0, False)
+    want = want[0] if isinstance(want, tuple) else want
+    covered = np.zeros(m, dtype=bool)
+    for _rank, b, e, c in parts:
+        assert np.array_equal(c, want[b:e])           # bit-identical to the same rows of the unsharded affine
+        covered[b:e] = True
+    assert covered.all()
+
+
+def test_shard_rows_covers_all_rows_once():
+    sys.path.insert(0, ROOT)
+    from marian_dev_b200 import parallel
+    for m in (1, 7, 8, 37, 4096):
+        for world in (1, 2, 3, 8):
+            spans = [parallel.shard_rows(m, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == m
+            assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
+            assert max(e - b for b, e in spans) - min(e - b for b, e in spans) <= 1
