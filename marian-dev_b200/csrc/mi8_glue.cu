@@ -423,95 +423,9 @@ __device__ __forceinline__ void topk_insert(TopK& t, float v, int idx) {
   }
 }
 
-// One block per row: cand_score[r][j] = (j-th largest logit - logsumexp(row)) + prev_score[r], cand_word[r][j].
+// Tree merge of the 256 per-thread sorted candidate lists in shared memory; the result is in list 0.
 template <int K>
-__global__ void __launch_bounds__(256)
-lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ prev_scores, float* __restrict__ cand_score,
-                int* __restrict__ cand_word) {
-  pdl_launch_dependents();
-  pdl_wait();
-  __shared__ float s_v[256 * K];
-  __shared__ int s_i[256 * K];
-  __shared__ float redf[8];
-  const int r = blockIdx.x;
-  const float* row = logits + static_cast<size_t>(r) * vocab;
-  TopK t;
-#pragma unroll
-  for(int j = 0; j < K; ++j) {
-    t.v[j] = -FLT_MAX;
-    t.i[j] = 0x7fffffff;
-  }
-  // Thread t owns the 4-element chunks c = t, t+256, ... of the row (16-byte loads when the row is
-  // aligned) and, of a ragged tail, the elements i with i % 256 == t.
-  const int chunks = vocab / 4;
-  const bool vec = (vocab & 3) == 0;
-  auto load4 = [&](int c) -> float4 {
-    if(vec)
-      return __ldg(reinterpret_cast<const float4*>(row) + c);
-    return make_float4(row[4 * c], row[4 * c + 1], row[4 * c + 2], row[4 * c + 3]);
-  };
-  float mx = -FLT_MAX;
-  for(int c0 = threadIdx.x; c0 < chunks; c0 += 4 * 256) {
-    float4 x[4];
-#pragma unroll
-    for(int u = 0; u < 4; ++u)
-      x[u] = (c0 + u * 256 < chunks) ? load4(c0 + u * 256) : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
-#pragma unroll
-    for(int u = 0; u < 4; ++u) {
-      const int i = 4 * (c0 + u * 256);
-      if(c0 + u * 256 < chunks) {
-        mx = fmaxf(mx, fmaxf(fmaxf(x[u].x, x[u].y), fmaxf(x[u].z, x[u].w)));
-        topk_insert<K>(t, x[u].x, i);
-        topk_insert<K>(t, x[u].y, i + 1);
-        topk_insert<K>(t, x[u].z, i + 2);
-        topk_insert<K>(t, x[u].w, i + 3);
-      }
-    }
-  }
-  for(int i = 4 * chunks + threadIdx.x; i < vocab; i += 256) {
-    const float x = row[i];
-    mx = fmaxf(mx, x);
-    topk_insert<K>(t, x, i);
-  }
-  for(int o = 16; o > 0; o >>= 1)
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if((threadIdx.x & 31) == 0)
-    redf[threadIdx.x >> 5] = mx;
-  __syncthreads();
-  mx = redf[0];
-#pragma unroll
-  for(int w = 1; w < 8; ++w)
-    mx = fmaxf(mx, redf[w]);
-  // log-sum-exp in a fixed order: thread t adds det_expf(x_i - mx) over its chunks in ascending order
-  // (the four elements of a chunk one after the other), then its tail elements; the 256 partial sums
-  // go through the deterministic block sum; lse = mx + det_logf(sum)
-  float sum = 0.f;
-  for(int c0 = threadIdx.x; c0 < chunks; c0 += 4 * 256) {
-    float4 x[4];
-#pragma unroll
-    for(int u = 0; u < 4; ++u)
-      x[u] = (c0 + u * 256 < chunks) ? load4(c0 + u * 256) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for(int u = 0; u < 4; ++u) {
-      if(c0 + u * 256 < chunks) {
-        sum = __fadd_rn(sum, det_expf(__fadd_rn(x[u].x, -mx)));
-        sum = __fadd_rn(sum, det_expf(__fadd_rn(x[u].y, -mx)));
-        sum = __fadd_rn(sum, det_expf(__fadd_rn(x[u].z, -mx)));
-        sum = __fadd_rn(sum, det_expf(__fadd_rn(x[u].w, -mx)));
-      }
-    }
-  }
-  for(int i = 4 * chunks + threadIdx.x; i < vocab; i += 256)
-    sum = __fadd_rn(sum, det_expf(__fadd_rn(row[i], -mx)));
-  sum = block256_sum_det(sum, redf);
-  const float lse = __fadd_rn(mx, det_logf(sum));
-#pragma unroll
-  for(int j = 0; j < K; ++j) {
-    s_v[threadIdx.x * K + j] = t.v[j];
-    s_i[threadIdx.x * K + j] = t.i[j];
-  }
-  __syncthreads();
-  // tree merge of the per-thread sorted lists
+__device__ __forceinline__ void topk_block_merge(float* s_v, int* s_i) {
   for(int active = 128; active >= 1; active >>= 1) {
     if(threadIdx.x < active) {
       TopK a;
@@ -531,6 +445,107 @@ lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __rest
     }
     __syncthreads();
   }
+}
+
+// Combines the per-block pairs (m_b, s_b) of one row, held in shared memory, into the row's log-sum-exp:
+// M = max_b m_b;  S = sum over b ascending of s_b * exp(m_b - M), product and sum rounded separately;
+// lse = M + log(S).  bm/bs: nb entries each; red: 9 floats.  Every thread returns the same value.
+__device__ __forceinline__ float lse_from_blocks(float* bm, float* bs, int nb, float* red) {
+  float mx = -FLT_MAX;
+  for(int b = threadIdx.x; b < nb; b += blockDim.x)
+    mx = fmaxf(mx, bm[b]);
+  for(int o = 16; o > 0; o >>= 1)
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  __syncthreads();
+  if((threadIdx.x & 31) == 0)
+    red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+  for(int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w)
+    mx = fmaxf(mx, red[w]);
+  for(int b = threadIdx.x; b < nb; b += blockDim.x)
+    bs[b] = __fmul_rn(bs[b], det_expf(__fadd_rn(bm[b], -mx)));
+  __syncthreads();
+  if(threadIdx.x == 0) {
+    float total = 0.f;
+    for(int b = 0; b < nb; ++b)
+      total = __fadd_rn(total, bs[b]);
+    red[8] = __fadd_rn(mx, det_logf(total));
+  }
+  __syncthreads();
+  return red[8];
+}
+
+// One block per row: cand_score[r][j] = (j-th largest logit - logsumexp(row)) + prev_score[r], cand_word[r][j].
+// The log-sum-exp is defined over blocks of 128 consecutive entries (the unit the output GEMM's write-back
+// owns): per block its maximum m_b and s_b = sum of det_expf(x - m_b) with the entries added one after the
+// other in ascending order; the blocks are combined by lse_from_blocks.  Thread t takes blocks t, t + 256, ...
+template <int K>
+__global__ void __launch_bounds__(256)
+lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ prev_scores, float* __restrict__ cand_score,
+                int* __restrict__ cand_word) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float lse_blocks[];   // [nb] block maxima, [nb] block sums
+  __shared__ float s_v[256 * K];
+  __shared__ int s_i[256 * K];
+  __shared__ float red[9];
+  const int r = blockIdx.x;
+  const float* row = logits + static_cast<size_t>(r) * vocab;
+  const int nb = (vocab + 127) / 128;
+  float* bm = lse_blocks;
+  float* bs = lse_blocks + nb;
+  const bool vec = (vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15u) == 0;
+  TopK t;
+#pragma unroll
+  for(int j = 0; j < K; ++j) {
+    t.v[j] = -FLT_MAX;
+    t.i[j] = 0x7fffffff;
+  }
+  for(int b = threadIdx.x; b < nb; b += 256) {
+    const int lo = b * 128, cnt = min(128, vocab - lo);
+    float m = -FLT_MAX;
+    if(vec) {
+      const float4* p4 = reinterpret_cast<const float4*>(row + lo);
+      for(int c = 0; c < cnt / 4; ++c) {
+        const float4 x = __ldg(p4 + c);
+        const int i = lo + 4 * c;
+        m = fmaxf(m, fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w)));
+        topk_insert<K>(t, x.x, i);
+        topk_insert<K>(t, x.y, i + 1);
+        topk_insert<K>(t, x.z, i + 2);
+        topk_insert<K>(t, x.w, i + 3);
+      }
+      float sum = 0.f;
+      for(int c = 0; c < cnt / 4; ++c) {
+        const float4 x = __ldg(p4 + c);
+        sum = __fadd_rn(sum, det_expf(__fadd_rn(x.x, -m)));
+        sum = __fadd_rn(sum, det_expf(__fadd_rn(x.y, -m)));
+        sum = __fadd_rn(sum, det_expf(__fadd_rn(x.z, -m)));
+        sum = __fadd_rn(sum, det_expf(__fadd_rn(x.w, -m)));
+      }
+      bs[b] = sum;
+    } else {
+      for(int i = 0; i < cnt; ++i) {
+        const float x = row[lo + i];
+        m = fmaxf(m, x);
+        topk_insert<K>(t, x, lo + i);
+      }
+      float sum = 0.f;
+      for(int i = 0; i < cnt; ++i)
+        sum = __fadd_rn(sum, det_expf(__fadd_rn(row[lo + i], -m)));
+      bs[b] = sum;
+    }
+    bm[b] = m;
+  }
+#pragma unroll
+  for(int j = 0; j < K; ++j) {
+    s_v[threadIdx.x * K + j] = t.v[j];
+    s_i[threadIdx.x * K + j] = t.i[j];
+  }
+  __syncthreads();
+  const float lse = lse_from_blocks(bm, bs, nb, red);
+  topk_block_merge<K>(s_v, s_i);
   if(threadIdx.x < K) {
     const float ps = prev_scores ? prev_scores[r] : 0.f;
     cand_score[r * K + threadIdx.x] = __fadd_rn(__fadd_rn(s_v[threadIdx.x], -lse), ps);
@@ -711,15 +726,18 @@ int launch_lse_topk(const float* logits, int rows, int vocab, int k, const float
                     cudaStream_t s) {
   if(rows <= 0 || vocab <= 0 || k < 1 || k > kMaxK)
     return MI8_ERR_BAD_ARG;
+  const size_t smem = 2 * static_cast<size_t>((vocab + 127) / 128) * sizeof(float);
+  if(smem > 32 * 1024)
+    return MI8_ERR_UNSUPPORTED;
   switch(k) {
-    case 1: launch_kernel(lse_topk_kernel<1>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 2: launch_kernel(lse_topk_kernel<2>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 3: launch_kernel(lse_topk_kernel<3>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 4: launch_kernel(lse_topk_kernel<4>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 5: launch_kernel(lse_topk_kernel<5>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 6: launch_kernel(lse_topk_kernel<6>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
-    case 7: launch_kernel(lse_topk_kernel<7>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
-    default: launch_kernel(lse_topk_kernel<8>, dim3(rows), dim3(256), 0, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 1: launch_kernel(lse_topk_kernel<1>, dim3(rows), dim3(256), smem, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 2: launch_kernel(lse_topk_kernel<2>, dim3(rows), dim3(256), smem, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 3: launch_kernel(lse_topk_kernel<3>, dim3(rows), dim3(256), smem, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 4: launch_kernel(lse_topk_kernel<4>, dim3(rows), dim3(256), smem, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 5: launch_kernel(lse_topk_kernel<5>, dim3(rows), dim3(256), smem, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 6: launch_kernel(lse_topk_kernel<6>, dim3(rows), dim3(256), smem, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    case 7: launch_kernel(lse_topk_kernel<7>, dim3(rows), dim3(256), smem, s, logits, vocab, prev_scores, cand_score, cand_word); break;
+    default: launch_kernel(lse_topk_kernel<8>, dim3(rows), dim3(256), smem, s, logits, vocab, prev_scores, cand_score, cand_word); break;
   }
   count_launch();
   return check_launch();

@@ -670,10 +670,8 @@ MO_FMA_CLONES static void mo_lse_rows(int rb, int re, void* ctx) {
     float tv[8];
     int ti[8];
     for(int j = 0; j < k; ++j) { tv[j] = -FLT_MAX; ti[j] = 0x7fffffff; }
-    float mx = -FLT_MAX;
     for(int i = 0; i < vocab; ++i) {
       const float x = row[i];
-      if(x > mx) mx = x;
       if(mo_better(x, i, tv[k - 1], ti[k - 1])) {
         int pos = k - 1;
         while(pos > 0 && mo_better(x, i, tv[pos - 1], ti[pos - 1])) { tv[pos] = tv[pos - 1]; ti[pos] = ti[pos - 1]; --pos; }
@@ -681,18 +679,32 @@ MO_FMA_CLONES static void mo_lse_rows(int rb, int re, void* ctx) {
         ti[pos] = i;
       }
     }
-    /* worker t of 256 owns the 4-element chunks c = t, t+256, ... (elements added one after the other)
-     * and, of a ragged tail, the elements i with i % 256 == t */
-    float part[256];
-    const int chunks = vocab / 4;
-    for(int t = 0; t < 256; ++t) {
-      float s = 0.0f;
-      for(int c = t; c < chunks; c += 256)
-        for(int e = 0; e < 4; ++e) s = s + mo_det_expf_i(row[4 * c + e] + -mx);
-      for(int i = 4 * chunks + t; i < vocab; i += 256) s = s + mo_det_expf_i(row[i] + -mx);
-      part[t] = s;
+    /* log-sum-exp over blocks of 128 consecutive entries (the last one may be short): per block its maximum m_b
+     * and s_b = sum of exp(x - m_b), entries added one after the other in ascending order starting from 0;
+     * then M = max_b m_b, S = sum over the blocks in ascending order of s_b * exp(m_b - M) (product and sum
+     * rounded separately), lse = M + log(S).  A producer that owns one block of a row at a time (the output
+     * GEMM's write-back) can compute the per-block pairs without seeing the rest of the row. */
+    const int nb = (vocab + 127) / 128;
+    float big = -FLT_MAX;
+    float* bm = (float*)malloc(sizeof(float) * (size_t)nb * 2);
+    float* bs = bm + nb;
+    for(int b = 0; b < nb; ++b) {
+      const int lo = b * 128, hi = lo + 128 < vocab ? lo + 128 : vocab;
+      float m = -FLT_MAX;
+      for(int i = lo; i < hi; ++i) if(row[i] > m) m = row[i];
+      float sb = 0.0f;
+      for(int i = lo; i < hi; ++i) sb = sb + mo_det_expf_i(row[i] + -m);
+      bm[b] = m;
+      bs[b] = sb;
+      if(m > big) big = m;
     }
-    const float lse = mx + mo_det_logf_i(mo_block256_sum(part));
+    float total = 0.0f;
+    for(int b = 0; b < nb; ++b) {
+      const float term = bs[b] * mo_det_expf_i(bm[b] + -big);
+      total = total + term;
+    }
+    free(bm);
+    const float lse = big + mo_det_logf_i(total);
     const float ps = prev_scores ? prev_scores[r] : 0.0f;
     for(int j = 0; j < k; ++j) {
       cand_score[(size_t)r * k + j] = (tv[j] + -lse) + ps;
