@@ -93,6 +93,18 @@ int mi8g_attention1(const float* q, const float* k, const float* v, const float*
  * (LogSoftmax + per-row part of the n-best search, src/translator/nth_element.cu:366-413). */
 int mi8g_lse_topk(const float* logits, int rows, int vocab, int k, const float* prev_scores, float* cand_score,
                   int* cand_word, void* stream);
+/* The output layer in two launches without logits in memory: the int8 GEMM of the quantised activation aq
+ * [rows, K] (multiplier d_qa) with the quantised tied embedding matrix wq [vocab, K] (multiplier d_qw) reduces
+ * value = float(acc) / (qa * qw) + bias[word] inside its write-back to, per (row, block of 128 words), the
+ * block maximum, the block's sum of exponentials and its best entries; a second kernel combines the blocks.
+ * Output as mi8g_lse_topk on the materialised logits, bit for bit.  scratch: mi8g_output_scratch_bytes()
+ * bytes of device memory; logits_out (optional, [rows, vocab]) additionally receives the values (slow; for
+ * checks).  (LogSoftmax + n-best of src/translator/beam_search.cpp:431-496 fused into the output affine.) */
+size_t mi8g_output_scratch_bytes(int rows, int vocab);
+int mi8g_output_topk(const int8_t* aq, const float* d_qa, const int8_t* wq, const float* d_qw, int rows, int vocab, int K,
+                     const float* bias, int k, const float* prev_scores, void* scratch, size_t scratch_bytes, float* logits_out,
+                     float* cand_score, int* cand_word, void* stream);
+
 /* Per sentence: the k best of its beam x k row candidates, sorted; ties to the smaller (beam, word) key. */
 int mi8g_nbest_merge(const float* cand_score, const int* cand_word, int beam, int batch, int vocab, int k,
                      float* out_score, int* out_beam, int* out_word, void* stream);
@@ -102,7 +114,10 @@ int mi8g_nbest_merge(const float* cand_score, const int* cand_word, int beam, in
  * counters.  Synchronises the device. */
 int mi8d_history_reuse(mi8d_decoder* d, unsigned out[2], int reset);
 
-/* Pointer to the last step's logits [beam*batch, vocab] (device), for tests. */
+/* keep != 0: every step also writes its logits [beam*batch, vocab] (the output layer then runs unfused);
+ * mi8d_last_logits returns them.  Off by default: the fused output layer never materialises them. */
+int mi8d_keep_logits(mi8d_decoder* d, int keep);
+/* Pointer to the last step's logits [beam*batch, vocab] (device); meaningful only with mi8d_keep_logits. */
 const float* mi8d_last_logits(const mi8d_decoder* d);
 
 #ifdef __cplusplus

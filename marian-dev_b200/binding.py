@@ -29,7 +29,8 @@ class Mi8dConfig(ctypes.Structure):
 # Every symbol include/marian_i8_decode.h declares.
 DECODE_EXPORTS = ["mi8d_arena_bytes", "mi8d_create", "mi8d_destroy", "mi8d_set_weight", "mi8d_set_param", "mi8d_set_positions",
                   "mi8d_start", "mi8d_encode", "mi8d_step", "mi8d_last_logits", "mi8d_history_reuse",
-                  "mi8g_embed", "mi8g_add_layernorm", "mi8g_quantize_slot", "mi8g_attention1", "mi8g_lse_topk", "mi8g_nbest_merge"]
+                  "mi8g_embed", "mi8g_add_layernorm", "mi8g_quantize_slot", "mi8g_attention1", "mi8g_lse_topk", "mi8g_nbest_merge",
+                  "mi8g_output_scratch_bytes", "mi8g_output_topk", "mi8d_keep_logits"]
 
 # Every symbol include/marian_i8.h declares.
 EXPORTS = [
@@ -123,6 +124,12 @@ def lib() -> ctypes.CDLL:
     L.mi8d_step.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, vp, vp, vp, vp]
     L.mi8d_history_reuse.argtypes = [vp, ctypes.POINTER(ctypes.c_uint * 2), ci]
     L.mi8d_history_reuse.restype = ci
+    L.mi8d_keep_logits.argtypes = [vp, ci]
+    L.mi8d_keep_logits.restype = ci
+    L.mi8g_output_scratch_bytes.argtypes = [ci, ci]
+    L.mi8g_output_scratch_bytes.restype = sz
+    L.mi8g_output_topk.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp, ci, vp, vp, sz, vp, vp, vp, vp]
+    L.mi8g_output_topk.restype = ci
     L.mi8d_last_logits.argtypes = [vp]
     L.mi8d_last_logits.restype = vp
     L.mi8g_embed.argtypes = [vp, vp, vp, ci, cf, ci, ci, vp, vp, vp, vp]

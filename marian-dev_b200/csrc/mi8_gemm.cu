@@ -17,11 +17,13 @@
 // Roles inside a CTA of 320 threads: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2..9 = epilogue (two warps per TMEM lane quarter, alternating 32-column chunks).  Two TMEM accumulator buffers let the
 // epilogue of one tile overlap the MMAs of the next.  CTAs are persistent over a static schedule.
+#include <cfloat>
 #include <cuda_fp16.h>
 
 #include <vector>
 
 #include "mi8_internal.h"
+#include "mi8_math.cuh"
 #include "mi8_ptx.cuh"
 
 namespace mi8 {
@@ -77,6 +79,14 @@ struct GemmParams {
   int32_t* partials;
   unsigned* tile_counters;
   unsigned* absmax_out;
+  // output-layer variant (kTopK > 0): per (row, block of 128 columns) the block maximum, the block's sum of
+  // exponentials and its kTopK largest values with their column indices, instead of (or besides) C
+  float* lg_max;
+  float* lg_sum;
+  float* lg_topv;
+  int* lg_topi;
+  int lg_blocks;            // blocks of 128 columns per row
+  float* lg_logits;         // optional [rows, columns] row-major copy of the values
   const float* a_f32;       // quantise-in-kernel variant: fp32 activation [M,K] and the 4-byte slot that
   const unsigned* a_slot;   // holds the bit pattern of max|A| (then aq / d_qa / the activation tensor map are unused)
   float* qa_out;            // optional: receives the activation multiplier 127 / max|A|
@@ -183,7 +193,11 @@ __device__ __forceinline__ unsigned write_back_chunk(const GemmParams& p, const 
 // shared-memory ring in the 128-byte-swizzled K-major layout the MMA reads, so no int8 copy of the
 // activation and no quantisation launch exist.  Used when every CTA has one tile (they quantise before
 // their write-back work begins).
-template <int TM, bool kQuantA>
+// kTopK > 0 (the output layer, operands swapped by the host: the M-side tile holds 128 ACTIVATION rows, the
+// N-side tile 256 rows of the tied embedding matrix): a thread owns one query row and 128 consecutive
+// vocabulary entries of it per tile, so it can reduce them on its own - block maximum, sum of exponentials
+// in ascending order, the kTopK best entries - and the [rows, vocabulary] logits never reach memory.
+template <int TM, bool kQuantA, int kTopK = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
   using T = TileCfg<TM>;
@@ -232,7 +246,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     // are requested before waiting for it, the activation tiles (its output) after.
     uint32_t it = 0;
     uint32_t prefetched = 0;  // stages whose weight tile is already in flight
-    if(p.skip_a == nullptr) {
+    if(p.skip_a == nullptr && kTopK == 0) {   // (output-layer variant: the M-side operand is the activation, nothing to prefetch)
       const WorkItem w0 = decode_work(p, blockIdx.x);
       const int n_pre = min(T::kStages, w0.kb_end - w0.kb_begin);
       if(elect_one()) {
@@ -441,6 +455,120 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const bool n_ok = n < p.N;
       const int m0 = wi.m_tile * TM;
       const int cols_valid = min(TM, p.M - m0);  // activation rows of this tile that exist
+      if constexpr(kTopK > 0) {
+        // Output layer: lane = query row n, columns = vocabulary entries m0 .. m0 + TM - 1; warp group g takes
+        // the 128-column block g of the tile.  Value = float(acc) * unquant + bias[column], rounded as in the
+        // plain write-back.  Two sweeps over the block's accumulators (TMEM reads are cheap): maximum and best
+        // entries first, then the exponentials against that maximum, added in ascending column order.
+        static_assert(TM == 256, "the output-layer write-back assumes 256-column tiles");
+        const int blk_col0 = group * 128;
+        const int cnt = min(128, cols_valid - blk_col0);           // columns of this block that exist (may be <= 0)
+        const int v0 = m0 + blk_col0;
+        TopK best;
+#pragma unroll
+        for(int j = 0; j < kTopK; ++j) {
+          best.v[j] = -FLT_MAX;
+          best.i[j] = 0x7fffffff;
+        }
+        float bmax = -FLT_MAX;
+        float bsum = 0.f;
+        // Whole blocks (all but the vocabulary's last one) run without per-column tests, so the 32 columns of a
+        // chunk form one straight-line region and their conversions / exponentials overlap in the pipeline.
+        const bool whole = cnt == 128;
+#pragma unroll 1
+        for(int c = 0; c < 4; ++c) {
+          int32_t v[32];
+          tmem_ld_chunk<32>(t_addr + blk_col0 + c * 32, v);
+          const float4* b4 = reinterpret_cast<const float4*>(p.bias + v0 + c * 32);
+          float x[32];
+          if(whole) {
+            float bb[32];
+            if((reinterpret_cast<uintptr_t>(b4) & 15u) == 0) {
+#pragma unroll
+              for(int j = 0; j < 8; ++j) {
+                const float4 t4 = __ldg(b4 + j);
+                bb[4 * j] = t4.x; bb[4 * j + 1] = t4.y; bb[4 * j + 2] = t4.z; bb[4 * j + 3] = t4.w;
+              }
+            } else {
+#pragma unroll
+              for(int j = 0; j < 32; ++j)
+                bb[j] = __ldg(p.bias + v0 + c * 32 + j);
+            }
+            tc_wait_ld();
+#pragma unroll
+            for(int j = 0; j < 32; ++j)
+              x[j] = __fadd_rn(__fmul_rn(__int2float_rn(v[j]), unquant), bb[j]);
+            float cm = x[0];
+#pragma unroll
+            for(int j = 1; j < 32; ++j)
+              cm = fmaxf(cm, x[j]);
+            bmax = fmaxf(bmax, cm);
+            if(cm >= best.v[kTopK - 1]) {   // only chunks that can change the list are scanned for candidates
+#pragma unroll
+              for(int j = 0; j < 32; ++j)
+                topk_insert<kTopK>(best, x[j], v0 + c * 32 + j);
+            }
+          } else {
+            tc_wait_ld();
+#pragma unroll
+            for(int j = 0; j < 32; ++j) {
+              const int col = c * 32 + j;
+              x[j] = -FLT_MAX;
+              if(col < cnt) {
+                x[j] = __fadd_rn(__fmul_rn(__int2float_rn(v[j]), unquant), __ldg(p.bias + v0 + col));
+                bmax = fmaxf(bmax, x[j]);
+                topk_insert<kTopK>(best, x[j], v0 + col);
+              }
+            }
+          }
+          if(p.lg_logits != nullptr && n_ok) {
+#pragma unroll
+            for(int j = 0; j < 32; ++j)
+              if(c * 32 + j < cnt)
+                p.lg_logits[static_cast<size_t>(n) * p.M + v0 + c * 32 + j] = x[j];
+          }
+        }
+#pragma unroll 1
+        for(int c = 0; c < 4; ++c) {
+          int32_t v[32];
+          tmem_ld_chunk<32>(t_addr + blk_col0 + c * 32, v);
+          tc_wait_ld();
+          if(whole) {
+            float e[32];
+#pragma unroll
+            for(int j = 0; j < 32; ++j) {
+              const float x = __fadd_rn(__fmul_rn(__int2float_rn(v[j]), unquant), __ldg(p.bias + v0 + c * 32 + j));
+              e[j] = det_expf(__fadd_rn(x, -bmax));
+            }
+#pragma unroll
+            for(int j = 0; j < 32; ++j)
+              bsum = __fadd_rn(bsum, e[j]);
+          } else {
+#pragma unroll
+            for(int j = 0; j < 32; ++j) {
+              const int col = c * 32 + j;
+              if(col < cnt) {
+                const float x = __fadd_rn(__fmul_rn(__int2float_rn(v[j]), unquant), __ldg(p.bias + v0 + col));
+                bsum = __fadd_rn(bsum, det_expf(__fadd_rn(x, -bmax)));
+              }
+            }
+          }
+        }
+        if(n_ok && cnt > 0) {
+          const size_t slot = static_cast<size_t>(n) * p.lg_blocks + (v0 >> 7);
+          p.lg_max[slot] = bmax;
+          p.lg_sum[slot] = bsum;
+#pragma unroll
+          for(int j = 0; j < kTopK; ++j) {
+            p.lg_topv[slot * kTopK + j] = best.v[j];
+            p.lg_topi[slot * kTopK + j] = best.i[j];
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&ctl->tmem_empty[as]);
+        ++acc_it;
+        continue;
+      }
       const float bias_n = (p.bias != nullptr && n_ok) ? __ldg(p.bias + n) : 0.0f;
       // Split-K: every split adds its partial accumulators into one int32 buffer per tile with
       // fire-and-forget reductions (layout [column][128 rows], coalesced); the last split to arrive
@@ -868,14 +996,14 @@ struct ProfileState {
 };
 thread_local ProfileState t_profile;
 
-template <int TM, bool kQuantA = false>
+template <int TM, bool kQuantA = false, int kTopK = 0>
 int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, const GemmPlan& plan, cudaStream_t stream) {
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   constexpr int smem = smem_bytes_for<TM>();
   if(dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(mi8_gemm_kernel<TM, kQuantA>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(mi8_gemm_kernel<TM, kQuantA, kTopK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if(e != cudaSuccess) {
       set_last_cuda_error(e);
       return MI8_ERR_LAUNCH;
@@ -889,7 +1017,7 @@ int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p
     if(rec.start != nullptr && rec.stop != nullptr)
       cudaEventRecord(rec.start, stream);
   }
-  cudaError_t le = launch_kernel(mi8_gemm_kernel<TM, kQuantA>, dim3(plan.grid), dim3(kThreads), smem, stream, tw, ta, p);
+  cudaError_t le = launch_kernel(mi8_gemm_kernel<TM, kQuantA, kTopK>, dim3(plan.grid), dim3(kThreads), smem, stream, tw, ta, p);
   if(le != cudaSuccess) {
     set_last_cuda_error(le);
     return MI8_ERR_LAUNCH;
@@ -1147,6 +1275,10 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
   p.partials = wsb ? reinterpret_cast<int32_t*>(wsb + kWsOffPartials) : nullptr;
   p.tile_counters = wsb ? reinterpret_cast<unsigned*>(wsb + kWsOffTileCounters) : nullptr;
   p.absmax_out = absmax_out;
+  p.lg_max = p.lg_sum = p.lg_topv = nullptr;
+  p.lg_topi = nullptr;
+  p.lg_blocks = 0;
+  p.lg_logits = nullptr;
   p.a_f32 = nullptr;
   p.a_slot = nullptr;
   p.qa_out = nullptr;
@@ -1226,6 +1358,10 @@ int launch_gemm_quant_a(const float* a_f32, const unsigned* a_slot, float* qa_ou
   p.partials = nullptr;
   p.tile_counters = nullptr;
   p.absmax_out = absmax_out;
+  p.lg_max = p.lg_sum = p.lg_topv = nullptr;
+  p.lg_topi = nullptr;
+  p.lg_blocks = 0;
+  p.lg_logits = nullptr;
   p.a_f32 = a_f32;
   p.a_slot = a_slot;
   p.qa_out = qa_out;
@@ -1240,6 +1376,74 @@ int launch_gemm_quant_a(const float* a_f32, const unsigned* a_slot, float* qa_ou
     case 32: return launch_cfg<32, true>(tw, tw, p, plan, stream);
     default: return launch_cfg<64, true>(tw, tw, p, plan, stream);
   }
+}
+
+// Output layer without logits in memory: values[r][v] = float(acc) * unquant + bias[v] are reduced inside the
+// write-back to, per (row, block of 128 vocabulary entries), the block maximum, the block's sum of exponentials
+// and its k_top (4 or 8) best entries.  The host swaps the operands: the activation is the M-side operand of the
+// kernel (128 rows per tile, one TMEM lane per query row) and the weight matrix the N-side operand (256 rows
+// per tile), so a thread owns a row and walks 128 consecutive vocabulary entries.
+int launch_gemm_logits(const int8_t* aq, const float* d_qa, const int8_t* wq, const float* d_qw, int rows, int vocab, int K,
+                       const float* bias, float scale, int k_top, float* blk_max, float* blk_sum, float* blk_topv, int* blk_topi,
+                       float* logits_out, cudaStream_t stream) {
+  if(rows < 0 || vocab <= 0 || K <= 0 || (k_top != 4 && k_top != 8))
+    return MI8_ERR_BAD_ARG;
+  if(rows == 0)
+    return MI8_OK;
+  if(aq == nullptr || wq == nullptr || d_qa == nullptr || d_qw == nullptr || bias == nullptr || blk_max == nullptr || blk_sum == nullptr ||
+     blk_topv == nullptr || blk_topi == nullptr)
+    return MI8_ERR_BAD_ARG;
+  if(K % 16 != 0 || (reinterpret_cast<uintptr_t>(aq) & 15u) || (reinterpret_cast<uintptr_t>(wq) & 15u))
+    return MI8_ERR_MISALIGNED;
+  GemmPlan plan;
+  // in the kernel's terms: "weights" = the activation (N = rows), "activation" = the weight matrix (M = vocab)
+  int rc = make_gemm_plan(vocab, rows, K, 256, 1, &plan);
+  if(rc != MI8_OK)
+    return rc;
+  CUtensorMap tw, ta;
+  rc = encode_kmajor_map(&tw, aq, rows, K, kTileN);
+  if(rc != MI8_OK)
+    return rc;
+  rc = encode_kmajor_map(&ta, wq, vocab, K, 256);
+  if(rc != MI8_OK)
+    return rc;
+  GemmParams p;
+  p.M = vocab;
+  p.N = rows;
+  p.K = K;
+  p.n_tiles = plan.n_tiles;
+  p.m_tiles = plan.m_tiles;
+  p.splits = 1;
+  p.kb_total = plan.kb_total;
+  p.kb_per_split = plan.kb_per_split;
+  p.total_work = plan.n_tiles * plan.m_tiles;
+  p.d_qa = d_qw;
+  p.d_qb = d_qa;
+  p.scale = scale;
+  p.bias = bias;
+  p.relu = 0;
+  p.out_f16 = 0;
+  p.c = nullptr;
+  p.acc_out = nullptr;
+  p.partials = nullptr;
+  p.tile_counters = nullptr;
+  p.absmax_out = nullptr;
+  p.lg_max = blk_max;
+  p.lg_sum = blk_sum;
+  p.lg_topv = blk_topv;
+  p.lg_topi = blk_topi;
+  p.lg_blocks = (vocab + 127) / 128;
+  p.lg_logits = logits_out;
+  p.a_f32 = nullptr;
+  p.a_slot = nullptr;
+  p.qa_out = nullptr;
+  p.skip_a = nullptr;
+  p.skip_b = nullptr;
+  p.skip_rows_below = 0;
+  p.status = device_status_ptr();
+  if(p.status == nullptr)
+    return MI8_ERR_LAUNCH;
+  return k_top == 4 ? launch_cfg<256, false, 4>(tw, ta, p, plan, stream) : launch_cfg<256, false, 8>(tw, ta, p, plan, stream);
 }
 
 }  // namespace mi8

@@ -393,36 +393,6 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 }
 
 // ---- output layer: log-softmax + per-row top-k --------------------------------------------------
-constexpr int kMaxK = 8;
-
-struct TopK {
-  float v[kMaxK];
-  int i[kMaxK];
-};
-
-// larger value first; ties: smaller index first
-__device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
-
-template <int K>
-__device__ __forceinline__ void topk_insert(TopK& t, float v, int idx) {
-  if(!better(v, idx, t.v[K - 1], t.i[K - 1]))
-    return;
-  t.v[K - 1] = v;
-  t.i[K - 1] = idx;
-  // bubble up with compile-time indices so the lists stay in registers
-#pragma unroll
-  for(int j = K - 1; j > 0; --j) {
-    if(better(t.v[j], t.i[j], t.v[j - 1], t.i[j - 1])) {
-      const float tv = t.v[j];
-      const int ti = t.i[j];
-      t.v[j] = t.v[j - 1];
-      t.i[j] = t.i[j - 1];
-      t.v[j - 1] = tv;
-      t.i[j - 1] = ti;
-    }
-  }
-}
-
 // Tree merge of the 256 per-thread sorted candidate lists in shared memory; the result is in list 0.
 template <int K>
 __device__ __forceinline__ void topk_block_merge(float* s_v, int* s_i) {
@@ -550,6 +520,53 @@ lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __rest
     const float ps = prev_scores ? prev_scores[r] : 0.f;
     cand_score[r * K + threadIdx.x] = __fadd_rn(__fadd_rn(s_v[threadIdx.x], -lse), ps);
     cand_word[r * K + threadIdx.x] = s_i[threadIdx.x];
+  }
+}
+
+// Second half of the fused output layer: the GEMM's write-back left, per (row, block of 128 vocabulary entries),
+// the block maximum, the block's sum of exponentials and its KT best entries; one block per row combines them
+// into the row's log-sum-exp (lse_from_blocks) and its k best entries overall, exactly what lse_topk_kernel
+// computes from materialised logits.
+template <int KT>
+__global__ void __launch_bounds__(256)
+lse_merge_kernel(const float* __restrict__ blk_max, const float* __restrict__ blk_sum, const float* __restrict__ blk_topv,
+                 const int* __restrict__ blk_topi, int nb, int k, const float* __restrict__ prev_scores, float* __restrict__ cand_score,
+                 int* __restrict__ cand_word) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float lse_blocks[];
+  __shared__ float s_v[256 * KT];
+  __shared__ int s_i[256 * KT];
+  __shared__ float red[9];
+  const int r = blockIdx.x;
+  float* bm = lse_blocks;
+  float* bs = lse_blocks + nb;
+  TopK t;
+#pragma unroll
+  for(int j = 0; j < KT; ++j) {
+    t.v[j] = -FLT_MAX;
+    t.i[j] = 0x7fffffff;
+  }
+  for(int b = threadIdx.x; b < nb; b += 256) {
+    const size_t slot = static_cast<size_t>(r) * nb + b;
+    bm[b] = blk_max[slot];
+    bs[b] = blk_sum[slot];
+#pragma unroll
+    for(int j = 0; j < KT; ++j)
+      topk_insert<KT>(t, blk_topv[slot * KT + j], blk_topi[slot * KT + j]);
+  }
+#pragma unroll
+  for(int j = 0; j < KT; ++j) {
+    s_v[threadIdx.x * KT + j] = t.v[j];
+    s_i[threadIdx.x * KT + j] = t.i[j];
+  }
+  __syncthreads();
+  const float lse = lse_from_blocks(bm, bs, nb, red);
+  topk_block_merge<KT>(s_v, s_i);
+  if(threadIdx.x < k) {
+    const float ps = prev_scores ? prev_scores[r] : 0.f;
+    cand_score[r * k + threadIdx.x] = __fadd_rn(__fadd_rn(s_v[threadIdx.x], -lse), ps);
+    cand_word[r * k + threadIdx.x] = s_i[threadIdx.x];
   }
 }
 
@@ -739,6 +756,24 @@ int launch_lse_topk(const float* logits, int rows, int vocab, int k, const float
     case 7: launch_kernel(lse_topk_kernel<7>, dim3(rows), dim3(256), smem, s, logits, vocab, prev_scores, cand_score, cand_word); break;
     default: launch_kernel(lse_topk_kernel<8>, dim3(rows), dim3(256), smem, s, logits, vocab, prev_scores, cand_score, cand_word); break;
   }
+  count_launch();
+  return check_launch();
+}
+
+int launch_lse_merge(const float* blk_max, const float* blk_sum, const float* blk_topv, const int* blk_topi, int rows, int vocab,
+                     int k_top, int k, const float* prev_scores, float* cand_score, int* cand_word, cudaStream_t s) {
+  if(rows <= 0 || vocab <= 0 || k < 1 || k > k_top || (k_top != 4 && k_top != 8))
+    return MI8_ERR_BAD_ARG;
+  const int nb = (vocab + 127) / 128;
+  const size_t smem = 2 * static_cast<size_t>(nb) * sizeof(float);
+  if(smem > 32 * 1024)
+    return MI8_ERR_UNSUPPORTED;
+  if(k_top == 4)
+    launch_kernel(lse_merge_kernel<4>, dim3(rows), dim3(256), smem, s, blk_max, blk_sum, blk_topv, blk_topi, nb, k, prev_scores, cand_score,
+                  cand_word);
+  else
+    launch_kernel(lse_merge_kernel<8>, dim3(rows), dim3(256), smem, s, blk_max, blk_sum, blk_topv, blk_topi, nb, k, prev_scores, cand_score,
+                  cand_word);
   count_launch();
   return check_launch();
 }

@@ -78,6 +78,15 @@ int launch_gemm_quant_a(const float* a_f32, const unsigned* a_slot, float* qa_ou
                         const float* d_qb, float scale, const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out,
                         cudaStream_t stream, unsigned* absmax_out = nullptr);
 
+// Output layer: GEMM whose write-back reduces every (row, block of 128 vocabulary entries) to its maximum, its sum
+// of exponentials and its k_top (4 or 8) best entries (blk_* arrays: [rows][ceil(vocab/128)] (x k_top)); then
+// launch_lse_merge turns those into the per-row candidates launch_lse_topk would have produced from the logits.
+int launch_gemm_logits(const int8_t* aq, const float* d_qa, const int8_t* wq, const float* d_qw, int rows, int vocab, int K,
+                       const float* bias, float scale, int k_top, float* blk_max, float* blk_sum, float* blk_topv, int* blk_topi,
+                       float* logits_out, cudaStream_t stream);
+int launch_lse_merge(const float* blk_max, const float* blk_sum, const float* blk_topv, const int* blk_topi, int rows, int vocab,
+                     int k_top, int k, const float* prev_scores, float* cand_score, int* cand_word, cudaStream_t s);
+
 // decode-step glue (mi8_glue.cu)
 int launch_embed(const float* wemb, const int* words, const float* pos, int pos_mod, float scale, int rows, int dim, float* out,
                  float* rowmax, unsigned* slot, cudaStream_t s);

@@ -79,4 +79,35 @@ __device__ __forceinline__ float block256_sum_det(float v, float* red) {
   return t;
 }
 
+// ---- small sorted candidate lists (value descending, ties to the smaller index), kept in registers
+constexpr int kMaxK = 8;
+
+struct TopK {
+  float v[kMaxK];
+  int i[kMaxK];
+};
+
+// larger value first; ties: smaller index first
+__device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
+
+template <int K>
+__device__ __forceinline__ void topk_insert(TopK& t, float v, int idx) {
+  if(!better(v, idx, t.v[K - 1], t.i[K - 1]))
+    return;
+  t.v[K - 1] = v;
+  t.i[K - 1] = idx;
+  // bubble up with compile-time indices so the lists stay in registers
+#pragma unroll
+  for(int j = K - 1; j > 0; --j) {
+    if(better(t.v[j], t.i[j], t.v[j - 1], t.i[j - 1])) {
+      const float tv = t.v[j];
+      const int ti = t.i[j];
+      t.v[j] = t.v[j - 1];
+      t.i[j] = t.i[j - 1];
+      t.v[j - 1] = tv;
+      t.i[j - 1] = ti;
+    }
+  }
+}
+
 }  // namespace mi8

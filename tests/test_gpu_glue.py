@@ -157,3 +157,44 @@ def test_embed_and_quantize_slot(cuda_device, oracle):
     check(L.mi8g_embed(wd.data_ptr(), None, pd[3:].data_ptr(), 0, scale, rows, dim, out.data_ptr(), None, None, _stream()))
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), want0)
+
+
+@pytest.mark.parametrize("rows,vocab,k,dim", [(512, 32000, 4, 1024), (64, 1000, 4, 64), (5, 300, 1, 128), (130, 777 * 4, 8, 256), (33, 129, 3, 64)])
+def test_fused_output_layer_bit_exact(cuda_device, oracle, rows, vocab, k, dim):
+    """int8 GEMM with the log-sum-exp / top-k reduction inside its write-back + the block merge: candidates and the
+    (optional) logits equal the checker's affine followed by its log-softmax / top-k, bit for bit; ragged vocabularies,
+    row counts that are not a multiple of 128, k up to 8."""
+    L, check = _lib()
+    from marian_dev_b200 import ops
+    rng = np.random.default_rng(rows + vocab + k)
+    a = rng.standard_normal((rows, dim)).astype(np.float32)
+    wemb = (rng.standard_normal((vocab, dim)) * 0.05).astype(np.float32)       # [vocab, dim]: already N x K
+    bias = (rng.standard_normal(vocab) * 0.1).astype(np.float32)
+    prev = rng.standard_normal(rows).astype(np.float32)
+    bt, qb = oracle.prepare_b(wemb, w_is_nk=True)
+    logits_w = oracle.affine(a, bt, qb, bias, 1.0, False)
+    logits_w = logits_w[0] if isinstance(logits_w, tuple) else logits_w
+    cs_w, cw_w = oracle.lse_topk(logits_w, k, prev)
+    wq = ops.prepareB(torch.from_numpy(wemb).to(cuda_device), w_is_nk=True)
+    aq = ops.prepareA(torch.from_numpy(a).to(cuda_device))
+    nbytes = L.mi8g_output_scratch_bytes(rows, vocab)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=cuda_device)
+    logits = torch.full((rows, vocab), float("nan"), device=cuda_device)
+    cs = torch.empty(rows, k, device=cuda_device)
+    cw = torch.empty(rows, k, dtype=torch.int32, device=cuda_device)
+    bd, pd = _dev(bias, cuda_device), _dev(prev, cuda_device)
+    check(L.mi8g_output_topk(aq.data.data_ptr(), aq.quant_mult.data_ptr(), wq.data.data_ptr(), wq.quant_mult.data_ptr(), rows, vocab, dim,
+                             bd.data_ptr(), k, pd.data_ptr(), scratch.data_ptr(), nbytes, logits.data_ptr(), cs.data_ptr(), cw.data_ptr(),
+                             _stream()))
+    torch.cuda.synchronize()
+    assert ops.poll_status() == 0
+    assert np.array_equal(logits.cpu().numpy(), logits_w)
+    assert np.array_equal(cw.cpu().numpy(), cw_w)
+    assert np.array_equal(cs.cpu().numpy(), cs_w)
+    # without the logits copy: same candidates
+    cs2 = torch.empty_like(cs)
+    cw2 = torch.empty_like(cw)
+    check(L.mi8g_output_topk(aq.data.data_ptr(), aq.quant_mult.data_ptr(), wq.data.data_ptr(), wq.quant_mult.data_ptr(), rows, vocab, dim,
+                             bd.data_ptr(), k, pd.data_ptr(), scratch.data_ptr(), nbytes, None, cs2.data_ptr(), cw2.data_ptr(), _stream()))
+    torch.cuda.synchronize()
+    assert torch.equal(cs2, cs) and torch.equal(cw2, cw)
