@@ -203,10 +203,10 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def gather_outputs(sent_ids, results):
-        """The path's one collective: every rank contributes its {sentence id: tokens}; all receive the union."""
-        local = {int(sid): toks for sid, (toks, _s) in zip(sent_ids, results)}
-        return parallel.gather_outputs(local, max_len=192, device=dev)   # 192 = 1.5 x the longest source
+    def gather_outputs(collected):
+        """The path's one collective, once per timed leg (the reference's OutputCollector also runs beside the
+        decoding, not in lock-step with it): every rank contributes its {sentence id: tokens}; all receive the union."""
+        return parallel.gather_outputs(collected, max_len=192, device=dev)   # 192 = 1.5 x the longest source
 
     # warm-up
     for b in mine[:args.warmup]:
@@ -225,10 +225,12 @@ def run_ours(args):
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    collected = {}
     for sid, ids_t, mask_t in resident:
         res = search.search_device(ids_t, mask_t)
-        gather_outputs(sid, res)
+        collected.update({int(i): toks for i, (toks, _s) in zip(sid, res)})
         tokens += sum(len(t) for t, _ in res)
+    gather_outputs(collected)
     e1.record()
     barrier()
     clocks = sampler.stop()
@@ -255,10 +257,12 @@ def run_ours(args):
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
+    collected = {}
     for sid, ids_p, mask_p in pinned:
         res = search.search(ids_p, mask_p)
-        gather_outputs(sid, res)
+        collected.update({int(i): toks for i, (toks, _s) in zip(sid, res)})
         tokens2 += sum(len(t) for t, _ in res)
+    gather_outputs(collected)
     f1.record()
     barrier()
     ms2 = f0.elapsed_time(f1)

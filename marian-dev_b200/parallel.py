@@ -24,28 +24,27 @@ def gather_outputs(local: dict, max_len: int, device=None) -> dict:
     int32 matrix [sentences, 2 + max_len] per rank (id, length, tokens), padded to the largest count."""
     if not dist.is_available() or not dist.is_initialized() or dist.get_world_size() == 1:
         return dict(local)
+    import numpy as np
     world = dist.get_world_size()
     dev = device if device is not None else torch.device("cpu")
     n = torch.tensor([len(local)], dtype=torch.int64, device=dev)
     counts = [torch.zeros_like(n) for _ in range(world)]
     dist.all_gather(counts, n)
     rows = int(max(int(c.item()) for c in counts))
-    mat = torch.full((max(rows, 1), 2 + max_len), -1, dtype=torch.int32)
+    mat = np.full((max(rows, 1), 2 + max_len), -1, dtype=np.int32)     # built and decoded with NumPy: no per-element tensor access
     for r, (sid, toks) in enumerate(sorted(local.items())):
         toks = toks[:max_len]
         mat[r, 0], mat[r, 1] = sid, len(toks)
         if toks:
-            mat[r, 2:2 + len(toks)] = torch.tensor(toks, dtype=torch.int32)
-    mat = mat.to(dev)
-    out = [torch.empty_like(mat) for _ in range(world)]
-    dist.all_gather(out, mat)
+            mat[r, 2:2 + len(toks)] = toks
+    mat_t = torch.from_numpy(mat).to(dev)
+    out = [torch.empty_like(mat_t) for _ in range(world)]
+    dist.all_gather(out, mat_t)
     merged = {}
     for m in out:
-        m = m.cpu()
-        for row in m:
-            sid = int(row[0])
-            if sid >= 0:
-                merged[sid] = [int(t) for t in row[2:2 + int(row[1])]]
+        m = m.cpu().numpy()
+        for row in m[m[:, 0] >= 0]:
+            merged[int(row[0])] = row[2:2 + int(row[1])].tolist()
     return merged
 
 
