@@ -193,7 +193,7 @@ def run_ours(args):
     per_rank = args.warmup + args.steps                          # both timed legs decode the same mini-batches
     wl = workload(args)
     batches = build_corpus(model, cfg, per_rank * world, wl)
-    mine = parallel.shard_batches(batches, rank, world)[:per_rank]
+    mine = parallel.shard_batches(batches, rank, world, snake=True)[:per_rank]   # length-sorted list: snake order balances the ranks
     stepper = decoder.NativeStepper(net, max_batch=wl["mini_batch"], beam=wl["beam"], max_src=136, max_steps=208)
     search = decoder.BeamSearch(net, beam=wl["beam"], max_length_factor=1.5, normalize=1.0, native=stepper)
 

@@ -14,9 +14,18 @@ import torch
 import torch.distributed as dist
 
 
-def shard_batches(batches, rank: int, world: int):
-    """Mini-batch i goes to rank i % world."""
-    return [b for i, b in enumerate(batches) if i % world == rank]
+def shard_batches(batches, rank: int, world: int, snake: bool = False):
+    """Mini-batch i goes to rank i % world (the reference's rule).  With snake=True every second group of
+    `world` mini-batches is dealt in reverse: for a length-sorted list (the maxi-batch order) the ranks then
+    receive equally long work instead of rank 0 always getting the longest batch of each group."""
+    if not snake:
+        return [b for i, b in enumerate(batches) if i % world == rank]
+    out = []
+    for i, b in enumerate(batches):
+        group, pos = divmod(i, world)
+        if (pos if group % 2 == 0 else world - 1 - pos) == rank:
+            out.append(b)
+    return out
 
 
 def gather_outputs(local: dict, max_len: int, device=None) -> dict:

@@ -58,6 +58,9 @@ def test_shard_batches_is_round_robin():
     from marian_dev_b200 import parallel
     batches = list(range(10))
     assert parallel.shard_batches(batches, 0, 4) == [0, 4, 8]
+    assert parallel.shard_batches(batches, 0, 4, snake=True) == [0, 7, 8]
+    assert parallel.shard_batches(batches, 3, 4, snake=True) == [3, 4]
+    assert sorted(sum((parallel.shard_batches(batches, r, 4, snake=True) for r in range(4)), [])) == batches
     assert parallel.shard_batches(batches, 3, 4) == [3, 7]
     assert sum((parallel.shard_batches(batches, r, 3) for r in range(3)), []).__len__() == 10
 
