@@ -647,10 +647,10 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
   if(out_b == nullptr || wout == nullptr)
     return MI8_ERR_BAD_ARG;
   MI8D_TRY(quant(d, x, R, dm, x_slot, d->aq, s));
-  // Up to ~320 rows the GEMM whose write-back reduces the 128-word blocks is faster than writing the logits and
-  // reading them back (measured 74 vs 88 us at 256 rows, 47 vs 85 at 128); above that, and for greedy search, the
-  // plain GEMM followed by the log-softmax / top-k kernel wins (129 vs 99 us at 512 rows).
-  const bool fused_output = !d->keep_logits && R <= 320 && n_best >= 2;
+  // Below 512 rows the GEMM whose write-back reduces the 128-word blocks is faster than writing the logits and
+  // reading them back (measured 49 vs 67 us at 256 rows, 33 vs 64 at 128); at 512 rows the two are equal (80 vs 78 us)
+  // and for greedy search the plain GEMM followed by the log-softmax / top-k kernel wins.
+  const bool fused_output = !d->keep_logits && R <= 480 && n_best >= 2;
   if(!fused_output) {
     MI8D_TRY(gemm(d, d->aq, R, "Wemb_intgemm8", "decoder_ff_logit_out_b", false, d->logits, s));
     MI8D_TRY(launch_lse_topk(d->logits, R, c.vocab, n_best, prev_scores, d->cand_score, d->cand_word, s));

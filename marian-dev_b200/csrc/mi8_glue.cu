@@ -475,7 +475,47 @@ lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __rest
   for(int b = threadIdx.x; b < nb; b += 256) {
     const int lo = b * 128, cnt = min(128, vocab - lo);
     float m = -FLT_MAX;
-    if(vec) {
+    if(vec && cnt == 128) {
+      // whole block, 16-byte loads: 32 values at a time in registers, no per-value tests, so the conversions and
+      // exponentials of a chunk overlap; only chunks that can change the candidate list are scanned
+      const float4* p4 = reinterpret_cast<const float4*>(row + lo);
+#pragma unroll 1
+      for(int c = 0; c < 4; ++c) {
+        float x[32];
+#pragma unroll
+        for(int j = 0; j < 8; ++j) {
+          const float4 q = __ldg(p4 + c * 8 + j);
+          x[4 * j] = q.x; x[4 * j + 1] = q.y; x[4 * j + 2] = q.z; x[4 * j + 3] = q.w;
+        }
+        float cm = x[0];
+#pragma unroll
+        for(int j = 1; j < 32; ++j)
+          cm = fmaxf(cm, x[j]);
+        m = fmaxf(m, cm);
+        if(cm >= t.v[K - 1]) {
+#pragma unroll
+          for(int j = 0; j < 32; ++j)
+            topk_insert<K>(t, x[j], lo + c * 32 + j);
+        }
+      }
+      float sum = 0.f;
+#pragma unroll 1
+      for(int c = 0; c < 4; ++c) {
+        float e[32];
+#pragma unroll
+        for(int j = 0; j < 8; ++j) {
+          const float4 q = __ldg(p4 + c * 8 + j);
+          e[4 * j] = det_expf(__fadd_rn(q.x, -m));
+          e[4 * j + 1] = det_expf(__fadd_rn(q.y, -m));
+          e[4 * j + 2] = det_expf(__fadd_rn(q.z, -m));
+          e[4 * j + 3] = det_expf(__fadd_rn(q.w, -m));
+        }
+#pragma unroll
+        for(int j = 0; j < 32; ++j)
+          sum = __fadd_rn(sum, e[j]);
+      }
+      bs[b] = sum;
+    } else if(vec) {
       const float4* p4 = reinterpret_cast<const float4*>(row + lo);
       for(int c = 0; c < cnt / 4; ++c) {
         const float4 x = __ldg(p4 + c);

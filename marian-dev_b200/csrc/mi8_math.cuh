@@ -90,24 +90,23 @@ struct TopK {
 // larger value first; ties: smaller index first
 __device__ __forceinline__ bool better(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
 
+// Inserts (v, idx) into the sorted list without branches: the K comparisons against the current entries are
+// independent of one another (the list is sorted, so they form a prefix of false followed by true), then every
+// entry either stays, takes its predecessor or takes the new value.  The only chain from one insertion to the
+// next is a compare and a select, which keeps a scan over many values short on the critical path.
 template <int K>
 __device__ __forceinline__ void topk_insert(TopK& t, float v, int idx) {
-  if(!better(v, idx, t.v[K - 1], t.i[K - 1]))
-    return;
-  t.v[K - 1] = v;
-  t.i[K - 1] = idx;
-  // bubble up with compile-time indices so the lists stay in registers
+  bool c[K];
+#pragma unroll
+  for(int j = 0; j < K; ++j)
+    c[j] = better(v, idx, t.v[j], t.i[j]);
 #pragma unroll
   for(int j = K - 1; j > 0; --j) {
-    if(better(t.v[j], t.i[j], t.v[j - 1], t.i[j - 1])) {
-      const float tv = t.v[j];
-      const int ti = t.i[j];
-      t.v[j] = t.v[j - 1];
-      t.i[j] = t.i[j - 1];
-      t.v[j - 1] = tv;
-      t.i[j - 1] = ti;
-    }
+    t.v[j] = c[j - 1] ? t.v[j - 1] : (c[j] ? v : t.v[j]);
+    t.i[j] = c[j - 1] ? t.i[j - 1] : (c[j] ? idx : t.i[j]);
   }
+  t.v[0] = c[0] ? v : t.v[0];
+  t.i[0] = c[0] ? idx : t.i[0];
 }
 
 }  // namespace mi8
