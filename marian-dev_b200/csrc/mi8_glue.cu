@@ -392,6 +392,120 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   }
 }
 
+// Encoder self-attention (mode 2) with the keys and values of one (sentence, head) staged in shared memory: block
+// (b, h), thread = one query position (128 at a time).  attention1_kernel re-reads every key/value row once per
+// query; here they cross L2 -> SM once per sentence and head.  The arithmetic per (row, head) is that of
+// attention1_kernel restated for one thread: the G = DH/4 four-element partial dot products are combined in the
+// butterfly's order (pairs G/2 apart first), the softmax sum as G interleaved partial sums combined the same way,
+// the output as a fused-multiply-add chain over the positions in ascending order.
+template <int G>
+__device__ __forceinline__ float butterfly_order_sum(float (&a)[G]) {
+#pragma unroll
+  for(int o = G / 2; o > 0; o >>= 1) {
+#pragma unroll
+    for(int j = 0; j < o; ++j)
+      a[j] = __fadd_rn(a[j], a[j + o]);
+  }
+  return a[0];
+}
+
+template <int DH>
+__global__ void __launch_bounds__(128)
+attention_enc_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                     const float* __restrict__ log_mask, int heads, int len, float scale, float* __restrict__ out,
+                     unsigned* absmax_slot) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float enc_smem[];
+  constexpr int G = DH / 4;
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int dim = heads * DH;
+  float* ks = enc_smem;                     // [len][DH]
+  float* vs = ks + static_cast<size_t>(len) * DH;
+  float* sc = vs + static_cast<size_t>(len) * DH;   // [len][128] scores / probabilities, position-major
+  const size_t row0 = static_cast<size_t>(b) * len;
+  for(int i = threadIdx.x; i < len * (DH / 4); i += blockDim.x) {
+    const int p = i / (DH / 4), c = i % (DH / 4);
+    const size_t off = (row0 + p) * dim + h * DH + 4 * c;
+    reinterpret_cast<float4*>(ks)[i] = __ldg(reinterpret_cast<const float4*>(k + off));
+    reinterpret_cast<float4*>(vs)[i] = __ldg(reinterpret_cast<const float4*>(v + off));
+  }
+  __syncthreads();
+  const float* mask = log_mask ? log_mask + row0 : nullptr;
+  unsigned m_abs = 0u;
+  for(int q0 = 0; q0 < len; q0 += 128) {
+    const int qi = q0 + threadIdx.x;
+    const bool active = qi < len;
+    float qv[DH];
+    {
+      const float4* q4 = reinterpret_cast<const float4*>(q + (row0 + (active ? qi : 0)) * dim + h * DH);
+#pragma unroll
+      for(int c = 0; c < DH / 4; ++c) {
+        const float4 t = __ldg(q4 + c);
+        qv[4 * c] = t.x; qv[4 * c + 1] = t.y; qv[4 * c + 2] = t.z; qv[4 * c + 3] = t.w;
+      }
+    }
+    float mx = -FLT_MAX;
+    for(int p = 0; p < len; ++p) {
+      const float* kr = ks + p * DH;
+      float a[G];
+#pragma unroll
+      for(int j = 0; j < G; ++j) {
+        float d = __fmul_rn(qv[4 * j], kr[4 * j]);
+        d = __fmaf_rn(qv[4 * j + 1], kr[4 * j + 1], d);
+        d = __fmaf_rn(qv[4 * j + 2], kr[4 * j + 2], d);
+        d = __fmaf_rn(qv[4 * j + 3], kr[4 * j + 3], d);
+        a[j] = d;
+      }
+      float sv = __fmul_rn(butterfly_order_sum<G>(a), scale);
+      if(mask)
+        sv = __fadd_rn(sv, mask[p]);
+      sc[p * 128 + threadIdx.x] = sv;
+      mx = fmaxf(mx, sv);
+    }
+    float part[G];
+#pragma unroll
+    for(int j = 0; j < G; ++j)
+      part[j] = 0.f;
+    for(int p0 = 0; p0 < len; p0 += G) {
+#pragma unroll
+      for(int j = 0; j < G; ++j) {
+        if(p0 + j < len) {
+          const float e = det_expf(__fadd_rn(sc[(p0 + j) * 128 + threadIdx.x], -mx));
+          sc[(p0 + j) * 128 + threadIdx.x] = e;
+          part[j] = __fadd_rn(part[j], e);
+        }
+      }
+    }
+    const float total = butterfly_order_sum<G>(part);
+    float acc[DH];
+#pragma unroll
+    for(int e = 0; e < DH; ++e)
+      acc[e] = 0.f;
+    for(int p = 0; p < len; ++p) {
+      const float w = __fdiv_rn(sc[p * 128 + threadIdx.x], total);
+      const float* vr = vs + p * DH;
+#pragma unroll
+      for(int e = 0; e < DH; ++e)
+        acc[e] = __fmaf_rn(w, vr[e], acc[e]);
+    }
+    if(active) {
+      float4* o4 = reinterpret_cast<float4*>(out + (row0 + qi) * dim + h * DH);
+#pragma unroll
+      for(int c = 0; c < DH / 4; ++c) {
+        const float4 t = make_float4(acc[4 * c], acc[4 * c + 1], acc[4 * c + 2], acc[4 * c + 3]);
+        o4[c] = t;
+        m_abs = max4u(m_abs, t);
+      }
+    }
+  }
+  if(absmax_slot) {
+    m_abs = __reduce_max_sync(0xffffffffu, m_abs);
+    if((threadIdx.x & 31) == 0 && m_abs != 0u)
+      atomicMax(absmax_slot, m_abs);
+  }
+}
+
 // ---- output layer: log-softmax + per-row top-k --------------------------------------------------
 // Tree merge of the 256 per-thread sorted candidate lists in shared memory; the result is in list 0.
 template <int K>
@@ -765,6 +879,31 @@ int launch_attention1(const float* q, const float* k, const float* v, const floa
   const int dim = heads * dim_head;
   if(dim > 1024)
     return MI8_ERR_UNSUPPORTED;
+  if(mode == 2 && batch > 0 && rows == batch * len && anc == nullptr && (dim_head == 64 || dim_head == 32)) {
+    // encoder: keys/values of a (sentence, head) staged in shared memory, one thread per query position
+    const size_t esmem = (static_cast<size_t>(len) * dim_head * 2 + static_cast<size_t>(len) * 128) * sizeof(float);
+    if(esmem <= 200 * 1024) {
+      static bool attr_set[64][2] = {};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      const int which = dim_head == 64 ? 0 : 1;
+      if(dev >= 0 && dev < 64 && !attr_set[dev][which]) {
+        cudaError_t e = which == 0 ? cudaFuncSetAttribute(attention_enc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                                   : cudaFuncSetAttribute(attention_enc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if(e != cudaSuccess) {
+          set_last_cuda_error(e);
+          return MI8_ERR_LAUNCH;
+        }
+        attr_set[dev][which] = true;
+      }
+      if(which == 0)
+        launch_kernel(attention_enc_kernel<64>, dim3(batch, heads), dim3(128), esmem, s, q, k, v, log_mask, heads, len, scale, out, slot);
+      else
+        launch_kernel(attention_enc_kernel<32>, dim3(batch, heads), dim3(128), esmem, s, q, k, v, log_mask, heads, len, scale, out, slot);
+      count_launch();
+      return check_launch();
+    }
+  }
   const int threads = ((dim / 4 + 31) / 32) * 32;
   const size_t smem = (static_cast<size_t>(heads) + 1) * len * sizeof(float);
   if(smem > 48 * 1024)
