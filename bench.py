@@ -322,18 +322,22 @@ def run_ours(args):
 
 
 # ----------------------------------------------------------------------------- CPU baseline / reference arm
+_CPU_NET = {}
+
+
 def cpu_decode_sample(args, cfg_name):
     """Times the CPU restatement on a bounded sample of the same workload: one mini-batch of a few
-    sentences, beam 4, all host threads."""
+    sentences, same beam, all host threads.  The model is built once per process."""
     from marian_dev_b200 import model
     from oracle.decode_oracle import OracleTransformer, beam_search
     from oracle.oracle import COracle
     cfg = model.CONFIGS[cfg_name]
-    params = model.random_init(cfg, seed=0)
-    o = COracle()
-    cores = o.max_threads()
-    net = OracleTransformer(cfg, params, oracle=o, output_int8=True, threads=cores)
-    del params
+    if cfg_name not in _CPU_NET:
+        params = model.random_init(cfg, seed=0)
+        o = COracle()
+        _CPU_NET[cfg_name] = (OracleTransformer(cfg, params, oracle=o, output_int8=True, threads=o.max_threads()), o.max_threads())
+        del params
+    net, cores = _CPU_NET[cfg_name]
     wl = workload(args)
     corpus = model.synthetic_corpus(wl["mini_batch"], cfg.vocab, seed=1, **wl["lengths"])
     n = min(args.cpu_sentences, len(corpus))
