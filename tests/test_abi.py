@@ -110,3 +110,26 @@ def test_null_and_misaligned_arguments_are_rejected_before_any_launch():
     assert L.mi8_max_absolute_f32(16, 16, None, None, None, 0, None) == 4                                # no workspace
     assert L.mi8_workspace_init(None, 0, None) == 4
     assert L.mi8_prepare_a_f32(16, -1, 8, 32, 48, 64, 1 << 20, None) == 1
+
+
+def test_new_entry_points_reject_bad_arguments_before_any_launch():
+    """Argument checks of the entry points without a reference counterpart run on the host: no device is needed."""
+    from marian_dev_b200.binding import lib
+    L = lib()
+    # mi8_multiply_f32_slot: null pointers, K % 16, misaligned activation, bad dtype; M = 0 is a no-op
+    assert L.mi8_multiply_f32_slot(None, None, None, None, 4, 8, 64, None, 1.0, None, 0, None, 0, None, None) == 1
+    assert L.mi8_multiply_f32_slot(16, 32, None, 48, 4, 8, 40, 64, 1.0, None, 0, 80, 0, None, None) == 2
+    assert L.mi8_multiply_f32_slot(20, 32, None, 48, 4, 8, 64, 64, 1.0, None, 0, 80, 0, None, None) == 2
+    assert L.mi8_multiply_f32_slot(16, 32, None, 48, 4, 8, 64, 64, 1.0, None, 0, 80, 9, None, None) == 1
+    assert L.mi8_multiply_f32_slot(16, 32, None, 48, 0, 8, 64, 64, 1.0, None, 0, 80, 0, None, None) == 0
+    # a shape that does not give every CTA one tile is declined (MI8_ERR_UNSUPPORTED), not launched
+    assert L.mi8_multiply_f32_slot(16, 32, None, 48, 8192, 8192, 64, 64, 1.0, None, 0, 80, 0, None, None) == 3
+    # mi8_multiply_i8_rows_from: the two device words are mandatory, the row limit cannot be negative
+    assert L.mi8_multiply_i8_rows_from(16, 32, 4, 8, 64, 48, 64, 1.0, None, 0, 80, 0, None, 0, None, None, None, 0, 0) == 1
+    assert L.mi8_multiply_i8_rows_from(16, 32, 4, 8, 64, 48, 64, 1.0, None, 0, 80, 0, None, 0, None, 96, 112, -1, 0) == 1
+    # mi8_measure_int8_peak: iteration count and output pointer
+    assert L.mi8_measure_int8_peak(0, None, None) == 1
+    # fused output layer: scratch too small, k out of range
+    assert L.mi8g_output_scratch_bytes(512, 32000) == 512 * 250 * 18 * 4
+    assert L.mi8g_output_topk(16, 32, 48, 64, 8, 256, 64, 80, 4, None, 96, 16, None, 112, 128, None) == 4
+    assert L.mi8g_output_topk(16, 32, 48, 64, 8, 256, 64, 80, 9, None, 96, 1 << 20, None, 112, 128, None) == 1
