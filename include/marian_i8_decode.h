@@ -70,6 +70,24 @@ int mi8d_encode(mi8d_decoder* d, const int* ids, const float* log_mask, int batc
 int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const int* batch_idx, const float* prev_scores,
               int beam, int batch, int n_best, float* out_score, int* out_beam, int* out_word, void* stream);
 
+/* Beam search over one mini-batch: the bookkeeping of BeamSearch::search (src/translator/beam_search.cpp:249-538,
+ * hypothesis scoring src/translator/history.h:22-35) around mi8d_encode and mi8d_step, in C++ as in the reference.
+ *   ids [batch, width] int32 and log_mask [batch, width] float on the device (as for mi8d_encode)
+ *   out_tokens [batch, max_out] / out_len [batch] / out_score [batch] (optional) on the HOST: the best finished
+ *   hypothesis of every sentence, EOS included, and its normalised score
+ *   h2d_bytes / d2h_bytes (optional): bytes of per-step control words uploaded and n-best lists downloaded
+ * One stream synchronisation per decoder step.  MI8_ERR_WORKSPACE if max_out is too small for a result. */
+typedef struct mi8d_search_config {
+  int beam;                  /* <= 8 */
+  float max_length_factor;   /* stop at length >= factor * width */
+  float normalize;           /* score / length^normalize */
+  float word_penalty;
+  int eos_id;
+} mi8d_search_config;
+int mi8d_search(mi8d_decoder* d, const int* ids, const float* log_mask, int batch, int width, const mi8d_search_config* cfg,
+                int* out_tokens, int max_out, int* out_len, float* out_score, unsigned long long* h2d_bytes,
+                unsigned long long* d2h_bytes, void* stream);
+
 /* ---- the glue kernels on their own (what the driver sequences), exported for tests and for hosts that
  * build their own step.  All pointers are device pointers; `absmax_slot` is an optional 4-byte slot
  * (zeroed by the caller) into which the kernel reduces max|out| for a following mi8g_quantize_slot. ---- */

@@ -30,7 +30,7 @@ class Mi8dConfig(ctypes.Structure):
 DECODE_EXPORTS = ["mi8d_arena_bytes", "mi8d_create", "mi8d_destroy", "mi8d_set_weight", "mi8d_set_param", "mi8d_set_positions",
                   "mi8d_start", "mi8d_encode", "mi8d_step", "mi8d_last_logits", "mi8d_history_reuse",
                   "mi8g_embed", "mi8g_add_layernorm", "mi8g_quantize_slot", "mi8g_attention1", "mi8g_lse_topk", "mi8g_nbest_merge",
-                  "mi8g_output_scratch_bytes", "mi8g_output_topk", "mi8d_keep_logits"]
+                  "mi8g_output_scratch_bytes", "mi8g_output_topk", "mi8d_keep_logits", "mi8d_search"]
 
 # Every symbol include/marian_i8.h declares.
 EXPORTS = [
@@ -40,6 +40,11 @@ EXPORTS = [
     "mi8_multiply_i8", "mi8_multiply_i8_ex", "mi8_multiply_i8_rows_from", "mi8_multiply_f32_slot", "mi8_multiply_i8_static", "mi8_affine_f32", "mi8_multiply_plan",
     "mi8_launch_count", "mi8_launch_count_reset", "mi8_measure_int8_peak", "mi8_profile_begin", "mi8_profile_end", "mi8_set_pdl",
 ]
+
+
+class Mi8dSearchConfig(ctypes.Structure):
+    _fields_ = [("beam", ctypes.c_int), ("max_length_factor", ctypes.c_float), ("normalize", ctypes.c_float),
+                ("word_penalty", ctypes.c_float), ("eos_id", ctypes.c_int)]
 
 
 class Mi8Error(RuntimeError):
@@ -124,6 +129,9 @@ def lib() -> ctypes.CDLL:
     L.mi8d_step.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, vp, vp, vp, vp]
     L.mi8d_history_reuse.argtypes = [vp, ctypes.POINTER(ctypes.c_uint * 2), ci]
     L.mi8d_history_reuse.restype = ci
+    L.mi8d_search.argtypes = [vp, vp, vp, ci, ci, ctypes.POINTER(Mi8dSearchConfig), vp, ci, vp, vp, ctypes.POINTER(ctypes.c_ulonglong),
+                              ctypes.POINTER(ctypes.c_ulonglong), vp]
+    L.mi8d_search.restype = ci
     L.mi8d_keep_logits.argtypes = [vp, ci]
     L.mi8d_keep_logits.restype = ci
     L.mi8g_output_scratch_bytes.argtypes = [ci, ci]

@@ -5,6 +5,8 @@
 // encoder keys/values, the ReLU feed-forward block, each followed by residual add + LayerNorm
 // ("transformer-postprocess: dan"), then the tied output layer, log-softmax and n-best selection.
 #include <cstring>
+#include <cmath>
+#include <cstring>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -78,6 +80,11 @@ struct mi8d_decoder {
   float* context[2] = {nullptr, nullptr};
   float* log_mask[2] = {nullptr, nullptr};
   int* anc[2] = {nullptr, nullptr};
+  // beam-search bookkeeping (mi8d_search): per-step control words and n-best lists, device side and pinned host side
+  int* s_ctrl = nullptr;            // [3 * max_rows + max_batch]: hypothesis rows, previous words, path scores (as bits), batch rows
+  int* s_out = nullptr;             // [3][max_batch * 8]: scores (as bits), beams, words
+  int* h_ctrl = nullptr;
+  int* h_out = nullptr;
   float *blk_max = nullptr, *blk_sum = nullptr, *blk_topv = nullptr;   // per (row, 128-word block) partials of the output layer
   int* blk_topi = nullptr;
   bool keep_logits = false;
@@ -136,6 +143,8 @@ struct mi8d_decoder {
     blk_sum = arena.take<float>(R * nb);
     blk_topv = arena.take<float>(R * nb * 8);
     blk_topi = arena.take<int>(R * nb * 8);
+    s_ctrl = arena.take<int>(3 * R + B);
+    s_out = arena.take<int>(3 * B * 8);
     cand_score = arena.take<float>(R * 8);
     cand_word = arena.take<int>(R * 8);
     for(int i = 0; i < 2; ++i) {
@@ -250,6 +259,17 @@ int mi8d_create(const mi8d_config* cfg, void* arena, size_t arena_bytes, void* w
   d->ws_bytes = workspace_bytes;
   if(d->reuse_stats != nullptr)
     cudaMemset(d->reuse_stats, 0, 2 * sizeof(unsigned));
+  {
+    // pinned host staging for the beam search's per-step upload and download
+    const size_t nc = 3 * static_cast<size_t>(cfg->max_rows) + cfg->max_batch, no = 3 * static_cast<size_t>(cfg->max_batch) * 8;
+    if(cudaHostAlloc(reinterpret_cast<void**>(&d->h_ctrl), nc * sizeof(int), cudaHostAllocDefault) != cudaSuccess ||
+       cudaHostAlloc(reinterpret_cast<void**>(&d->h_out), no * sizeof(int), cudaHostAllocDefault) != cudaSuccess) {
+      cudaGetLastError();
+      if(d->h_ctrl)
+        cudaFreeHost(d->h_ctrl);
+      d->h_ctrl = d->h_out = nullptr;   // mi8d_search then reports MI8_ERR_WORKSPACE; stepping by hand still works
+    }
+  }
   if(!cfg->ssru) {
     bool ok = cudaStreamCreateWithFlags(&d->side[0], cudaStreamNonBlocking) == cudaSuccess &&
               cudaStreamCreateWithFlags(&d->side[1], cudaStreamNonBlocking) == cudaSuccess;
@@ -274,6 +294,10 @@ void mi8d_destroy(mi8d_decoder* d) {
   for(cudaEvent_t e : {d->ev_x, d->ev_hq, d->ev_k, d->ev_v})
     if(e != nullptr)
       cudaEventDestroy(e);
+  if(d->h_ctrl)
+    cudaFreeHost(d->h_ctrl);
+  if(d->h_out)
+    cudaFreeHost(d->h_out);
   delete d;
 }
 
@@ -670,6 +694,199 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
   d->anc_cur = anc_new;
   d->cell_cur = cell_new;
   d->t = t + 1;
+  return MI8_OK;
+}
+
+// Beam search over one mini-batch: the bookkeeping of BeamSearch::search (src/translator/beam_search.cpp:249-538)
+// around mi8d_encode / mi8d_step.  Per step: every sentence still in the batch contributes its surviving
+// hypotheses (beam-major rows, dummy slots with EOS and score -inf), the n-best lists come back, each sentence keeps
+// as many candidates as it had hypotheses (toHyps, :24-210), hypotheses that ended in EOS are scored
+// ((pathScore - wordPenalty * length) / length^normalize, src/translator/history.h:22-35) and leave the beam, a
+// sentence whose beam is empty leaves the batch (purgeBeams, :224-245), and everything stops at
+// length >= max_length_factor * width (:521-531).  The best finished hypothesis of every sentence is traced back
+// through the per-step parent links.  One stream synchronisation per step (the n-best download).
+int mi8d_search(mi8d_decoder* d, const int* ids, const float* log_mask, int batch, int width, const mi8d_search_config* sc,
+                int* out_tokens, int max_out, int* out_len, float* out_score, unsigned long long* h2d_bytes, unsigned long long* d2h_bytes,
+                void* stream) {
+  if(d == nullptr || ids == nullptr || log_mask == nullptr || sc == nullptr || out_tokens == nullptr || out_len == nullptr || batch <= 0 ||
+     width <= 0 || max_out <= 0 || sc->beam <= 0 || sc->beam > 8)
+    return MI8_ERR_BAD_ARG;
+  if(d->h_ctrl == nullptr || d->h_out == nullptr)
+    return MI8_ERR_WORKSPACE;
+  const mi8d_config& c = d->cfg;
+  const int beam = sc->beam, eos = sc->eos_id, B0 = batch;
+  if(beam * batch > c.max_rows || batch > c.max_batch)
+    return MI8_ERR_UNSUPPORTED;
+  cudaStream_t s = as_stream(stream);
+  int rc = mi8d_encode(d, ids, log_mask, batch, width, stream);
+  if(rc != MI8_OK)
+    return rc;
+
+  struct Final { double norm; int t, pos; };
+  struct StepRecord { std::vector<int> words, prev, unpurged; };   // [B0 * beam] each
+  std::vector<int> W(B0, beam), step_map(B0), new_n(B0), new_W(B0);
+  std::vector<int> words(B0 * beam, 0), prev_state(B0 * beam, 0), new_words(B0 * beam), new_prev(B0 * beam);
+  std::vector<float> scores(B0 * beam, 0.f), new_scores(B0 * beam);
+  std::vector<std::vector<Final>> finals(B0);
+  std::vector<StepRecord> history;
+  std::vector<int> active;
+  for(int o = 0; o < B0; ++o)
+    step_map[o] = o;
+  int prev_dim = B0;
+  unsigned long long up_bytes = 0, down_bytes = 0;
+
+  for(int t = 0;; ++t) {
+    int max_beam = 0;
+    active.clear();
+    for(int o = 0; o < B0; ++o) {
+      max_beam = W[o] > max_beam ? W[o] : max_beam;
+      if(W[o] > 0)
+        active.push_back(o);
+    }
+    if(max_beam == 0)
+      break;
+    const int nb = static_cast<int>(active.size());
+    const int n_best = max_beam;
+    const int tensor_beam = t == 0 ? 1 : max_beam;
+    const int R = tensor_beam * nb;
+    const int *hyp = nullptr, *pw = nullptr, *bidx = nullptr;
+    const float* ps = nullptr;
+    if(t > 0) {
+      int* hc = d->h_ctrl;
+      for(int j = 0; j < max_beam; ++j) {
+        for(int a = 0; a < nb; ++a) {
+          const int o = active[a];
+          const bool valid = j < W[o];
+          const int idx = j * nb + a;
+          hc[idx] = valid ? prev_state[o * beam + j] * prev_dim + step_map[o] : 0;
+          hc[R + idx] = valid ? words[o * beam + j] : eos;                       // dummy slots carry EOS
+          const float sv = valid ? scores[o * beam + j] : -INFINITY;
+          memcpy(&hc[2 * R + idx], &sv, sizeof(float));
+        }
+      }
+      for(int a = 0; a < nb; ++a)
+        hc[3 * R + a] = step_map[active[a]];
+      const size_t n_up = static_cast<size_t>(3 * R + nb) * sizeof(int);
+      MI8D_CUDA(cudaMemcpyAsync(d->s_ctrl, hc, n_up, cudaMemcpyHostToDevice, s));
+      up_bytes += n_up;
+      hyp = d->s_ctrl;
+      pw = d->s_ctrl + R;
+      ps = reinterpret_cast<const float*>(d->s_ctrl + 2 * R);
+      bidx = d->s_ctrl + 3 * R;
+    }
+    const int cells = nb * n_best;
+    float* o_score = reinterpret_cast<float*>(d->s_out);
+    int* o_beam = d->s_out + cells;
+    int* o_word = d->s_out + 2 * cells;
+    rc = mi8d_step(d, hyp, pw, bidx, ps, tensor_beam, nb, n_best, o_score, o_beam, o_word, stream);
+    if(rc != MI8_OK)
+      return rc;
+    MI8D_CUDA(cudaMemcpyAsync(d->h_out, d->s_out, static_cast<size_t>(3 * cells) * sizeof(int), cudaMemcpyDeviceToHost, s));
+    MI8D_CUDA(cudaStreamSynchronize(s));
+    down_bytes += static_cast<size_t>(3 * cells) * sizeof(int);
+    const float* nv = reinterpret_cast<const float*>(d->h_out);
+    const int* nbm = d->h_out + cells;
+    const int* nw = d->h_out + 2 * cells;
+
+    // toHyps: every sentence keeps its current number of hypotheses, skipping invalid scores
+    std::fill(new_n.begin(), new_n.end(), 0);
+    std::fill(new_words.begin(), new_words.end(), 0);
+    std::fill(new_prev.begin(), new_prev.end(), 0);
+    std::fill(new_scores.begin(), new_scores.end(), 0.f);
+    for(int a = 0; a < nb; ++a) {
+      const int o = active[a];
+      int cnt = 0;
+      for(int cidx = 0; cidx < n_best && cnt < W[o]; ++cidx) {
+        const float v = nv[a * n_best + cidx];
+        if(!(v > -INFINITY))
+          continue;
+        new_words[o * beam + cnt] = nw[a * n_best + cidx];
+        new_scores[o * beam + cnt] = v;
+        new_prev[o * beam + cnt] = nbm[a * n_best + cidx];
+        ++cnt;
+      }
+      new_n[o] = cnt;
+    }
+    // purgeBeams and History::add
+    const int length = t + 1;
+    const bool max_len_reached = static_cast<double>(length) >= static_cast<double>(sc->max_length_factor) * width;
+    StepRecord rec;
+    rec.words = new_words;
+    rec.prev = new_prev;
+    rec.unpurged.assign(B0 * beam, 0);
+    std::fill(new_W.begin(), new_W.end(), 0);
+    for(int o = 0; o < B0; ++o) {
+      int surv = 0;
+      for(int j = 0; j < new_n[o]; ++j)
+        if(new_words[o * beam + j] != eos)
+          ++surv;
+      new_W[o] = surv;
+      const bool last = surv == 0 || max_len_reached;
+      int rank = 0;
+      for(int j = 0; j < new_n[o]; ++j) {
+        const bool is_eos = new_words[o * beam + j] == eos;
+        if(is_eos || last) {
+          const double norm = (static_cast<double>(new_scores[o * beam + j]) - static_cast<double>(sc->word_penalty) * length) /
+                              std::pow(static_cast<double>(length), static_cast<double>(sc->normalize));
+          finals[o].push_back(Final{norm, t, j});
+        }
+        if(!is_eos)
+          rec.unpurged[o * beam + rank++] = j;
+      }
+    }
+    history.push_back(std::move(rec));
+    if(max_len_reached)
+      break;
+    const StepRecord& cur = history.back();
+    std::fill(words.begin(), words.end(), 0);
+    std::fill(scores.begin(), scores.end(), 0.f);
+    std::fill(prev_state.begin(), prev_state.end(), 0);
+    for(int o = 0; o < B0; ++o) {
+      for(int r2 = 0; r2 < new_W[o]; ++r2) {
+        const int j = cur.unpurged[o * beam + r2];
+        words[o * beam + r2] = new_words[o * beam + j];
+        scores[o * beam + r2] = new_scores[o * beam + j];
+        prev_state[o * beam + r2] = new_prev[o * beam + j];
+      }
+    }
+    W = new_W;
+    std::fill(step_map.begin(), step_map.end(), -1);
+    for(int a = 0; a < nb; ++a)
+      step_map[active[a]] = a;
+    prev_dim = nb;
+  }
+
+  // best finished hypothesis per sentence (highest score; ties to the earlier step, then the earlier position), traced back
+  for(int o = 0; o < B0; ++o) {
+    out_len[o] = 0;
+    if(out_score)
+      out_score[o] = -INFINITY;
+    if(finals[o].empty())
+      continue;
+    const Final* best = &finals[o][0];
+    for(const Final& f : finals[o])
+      if(f.norm > best->norm || (f.norm == best->norm && (f.t < best->t || (f.t == best->t && f.pos < best->pos))))
+        best = &f;
+    int t = best->t, pos = best->pos;
+    const int len = t + 1;
+    if(len > max_out)
+      return MI8_ERR_WORKSPACE;
+    for(;;) {
+      out_tokens[static_cast<size_t>(o) * max_out + t] = history[t].words[o * beam + pos];
+      if(t == 0)
+        break;
+      // the parent is addressed by its row in the previous step's purged beam: map it back to that step's unpurged list
+      pos = history[t - 1].unpurged[o * beam + history[t].prev[o * beam + pos]];
+      --t;
+    }
+    out_len[o] = len;
+    if(out_score)
+      out_score[o] = static_cast<float>(best->norm);
+  }
+  if(h2d_bytes)
+    *h2d_bytes = up_bytes;
+  if(d2h_bytes)
+    *d2h_bytes = down_bytes;
   return MI8_OK;
 }
 

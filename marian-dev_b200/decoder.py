@@ -253,6 +253,29 @@ class NativeStepper:
         log_mask = ((1.0 - mask_t) * NEG_MASK).contiguous()     # exactly 0 or -99999999
         self.check(self.L.mi8d_encode(self.h, ids32.data_ptr(), log_mask.data_ptr(), B, S, torch.cuda.current_stream().cuda_stream))
 
+    def search(self, ids_t: torch.Tensor, mask_t: torch.Tensor, beam: int, max_length_factor: float, normalize: float,
+               word_penalty: float = 0.0, eos_id: int = 0):
+        """mi8d_search: the whole beam search of one mini-batch (encoder, decoder steps, bookkeeping, traceback) in the
+        C++ driver.  Returns [(tokens, score)] per sentence and the bytes moved host <-> device by the step loop."""
+        import ctypes
+        from .binding import Mi8dSearchConfig
+        B, S = ids_t.shape
+        if B > self.max_batch or S > self.max_src:
+            raise ops.Mi8Error(3, f"mini-batch {B}x{S} exceeds the driver's limits {self.max_batch}x{self.max_src}")
+        ids32 = ids_t.to(torch.int32).contiguous()
+        log_mask = ((1.0 - mask_t) * NEG_MASK).contiguous()
+        max_out = int(math.ceil(max_length_factor * S)) + 2
+        toks = np.empty((B, max_out), np.int32)
+        lens = np.empty(B, np.int32)
+        scores = np.empty(B, np.float32)
+        up, down = ctypes.c_ulonglong(0), ctypes.c_ulonglong(0)
+        cfg = Mi8dSearchConfig(int(beam), float(max_length_factor), float(normalize), float(word_penalty), int(eos_id))
+        self.check(self.L.mi8d_search(self.h, ids32.data_ptr(), log_mask.data_ptr(), B, S, ctypes.byref(cfg), toks.ctypes.data, max_out,
+                                      lens.ctypes.data, scores.ctypes.data, ctypes.byref(up), ctypes.byref(down),
+                                      torch.cuda.current_stream().cuda_stream))
+        res = [(toks[b, :lens[b]].tolist(), float(scores[b])) for b in range(B)]
+        return res, int(up.value), int(down.value)
+
     def history_reuse(self, reset: bool = False):
         """(reused, total) counts of (layer, step) pairs whose stored self-attention keys/values stayed valid."""
         import ctypes
@@ -300,9 +323,10 @@ class BeamSearch:
     """Host-side bookkeeping of BeamSearch::search with batch purging (beam_search.cpp:249-538)."""
 
     def __init__(self, model: Int8Transformer, beam: int = 4, max_length_factor: float = 1.5, normalize: float = 1.0,
-                 word_penalty: float = 0.0, native: "NativeStepper | None" = None):
+                 word_penalty: float = 0.0, native: "NativeStepper | None" = None, native_search: bool = True):
         self.m = model
         self.native = native      # None: torch glue ops per step; else the C++ step driver
+        self.native_search = native_search   # with a native stepper: also run the bookkeeping in the C++ driver (mi8d_search)
         self.beam = beam
         self.factor = max_length_factor
         self.alpha = normalize
@@ -325,6 +349,11 @@ class BeamSearch:
     @torch.no_grad()
     def search_device(self, ids_t: torch.Tensor, mask_t: torch.Tensor):
         """Same with ids (int64) and mask (float32) already on the device."""
+        if self.native is not None and self.native_search:
+            res, up, down = self.native.search(ids_t, mask_t, self.beam, self.factor, self.alpha, self.wp, self.m.cfg.eos_id)
+            self.h2d_bytes += up
+            self.d2h_bytes += down
+            return res
         m, dev, eos = self.m, self.m.device, self.m.cfg.eos_id
         B0, width = ids_t.shape
         if self.native is not None:
@@ -463,9 +492,9 @@ class BeamSearch:
         return results
 
 
-def decode_corpus(model: Int8Transformer, batches, beam=4, max_length_factor=1.5, normalize=1.0, native=None):
+def decode_corpus(model: Int8Transformer, batches, beam=4, max_length_factor=1.5, normalize=1.0, native=None, native_search=True):
     """Translate all mini-batches on one replica; returns {sentence id: token list} and the token count."""
-    bs = BeamSearch(model, beam, max_length_factor, normalize, native=native)
+    bs = BeamSearch(model, beam, max_length_factor, normalize, native=native, native_search=native_search)
     out, n_tokens = {}, 0
     for sent_ids, ids, mask in batches:
         res = bs.search(ids, mask)

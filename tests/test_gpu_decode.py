@@ -14,7 +14,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _decode_both(cfg_name, n_sent, mini_batch, beam, seed, lo=3, hi=12, output_int8=True, native=False):
+def _decode_both(cfg_name, n_sent, mini_batch, beam, seed, lo=3, hi=12, output_int8=True, native=False, native_search=True):
     from marian_dev_b200 import decoder, model, ops
     from oracle.decode_oracle import OracleTransformer, beam_search
     cfg = model.CONFIGS[cfg_name]
@@ -23,7 +23,7 @@ def _decode_both(cfg_name, n_sent, mini_batch, beam, seed, lo=3, hi=12, output_i
     batches = model.make_batches(corpus, mini_batch)
     gpu = decoder.Int8Transformer(cfg, params, torch.device("cuda", 0), output_int8=output_int8)
     stepper = decoder.NativeStepper(gpu, max_batch=mini_batch, beam=max(beam, 1), max_src=hi + 2, max_steps=2 * hi + 8) if native else None
-    got, n_tok = decoder.decode_corpus(gpu, batches, beam=beam, native=stepper)
+    got, n_tok = decoder.decode_corpus(gpu, batches, beam=beam, native=stepper, native_search=native_search)
     assert ops.poll_status() == 0
     ref_model = OracleTransformer(cfg, params, output_int8=output_int8, threads=8)
     want = {}
@@ -100,3 +100,27 @@ def test_big_model_sample_identical(cuda_device):
     """Transformer-big dimensions (d=1024, ffn=4096, 16 heads, 32000 words), beam 4, one small mini-batch."""
     same, total, got, want, _ = _decode_both("big", 8, 8, 4, seed=1, lo=6, hi=14, native=True)
     assert same == total, f"only {same}/{total} sentences identical"
+
+
+@pytest.mark.parametrize("cfg_name,beam", [("tiny", 4), ("tiny", 1), ("tiny-ssru", 4)])
+def test_cpp_beam_search_equals_python_bookkeeping(cuda_device, cfg_name, beam):
+    """mi8d_search (bookkeeping in the C++ driver) and the NumPy bookkeeping around mi8d_step return the same token
+    sequences and scores, sentence by sentence, on a model whose EOS bias makes hypotheses finish at different steps."""
+    from marian_dev_b200 import decoder, model
+    cfg = model.CONFIGS[cfg_name]
+    params = model.random_init(cfg, 7)
+    params["decoder_ff_logit_out_b"][0, cfg.eos_id] += 4.0
+    corpus = model.synthetic_corpus(24, cfg.vocab, 8, "uniform", 3, 14)
+    batches = model.make_batches(corpus, 12)
+    gpu = decoder.Int8Transformer(cfg, params, torch.device("cuda", 0))
+    stepper = decoder.NativeStepper(gpu, max_batch=12, beam=beam, max_src=16, max_steps=40)
+    a = decoder.BeamSearch(gpu, beam=beam, native=stepper, native_search=True)
+    b = decoder.BeamSearch(gpu, beam=beam, native=stepper, native_search=False)
+    ended_early = 0
+    for _sid, ids, mask in batches:
+        ra, rb = a.search(ids, mask), b.search(ids, mask)
+        assert [t for t, _ in ra] == [t for t, _ in rb]
+        # the C++ search returns the score as float32, the NumPy bookkeeping as a Python float
+        assert np.allclose([s for _, s in ra], [s for _, s in rb], rtol=1e-6, atol=0)
+        ended_early += sum(1 for t, _ in ra if len(t) < int(1.5 * ids.shape[1]))
+    assert ended_early > 0      # the purge paths were exercised
