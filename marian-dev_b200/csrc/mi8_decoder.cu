@@ -4,7 +4,8 @@
 // self-attention over the re-projected history (or the SSRU cell), cross-attention over cached
 // encoder keys/values, the ReLU feed-forward block, each followed by residual add + LayerNorm
 // ("transformer-postprocess: dan"), then the tied output layer, log-softmax and n-best selection.
-#include <cstring>
+// mi8d_search adds the beam-search bookkeeping around the step (BeamSearch::search,
+// src/translator/beam_search.cpp:249-538), so a mini-batch is translated by one call.
 #include <cmath>
 #include <cstring>
 #include <string>

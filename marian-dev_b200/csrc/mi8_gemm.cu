@@ -15,8 +15,14 @@
 // associative, so every split factor gives bit-identical accumulators.
 //
 // Roles inside a CTA of 320 threads: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..9 = epilogue (two warps per TMEM lane quarter, alternating 32-column chunks).  Two TMEM accumulator buffers let the
-// epilogue of one tile overlap the MMAs of the next.  CTAs are persistent over a static schedule.
+// warps 2..9 = epilogue (two warps per TMEM lane quarter, alternating 32-column chunks).  Two TMEM
+// accumulator buffers let the epilogue of one tile overlap the MMAs of the next.  CTAs are persistent
+// over a static schedule.  The producer and MMA loops run warp-uniformly and issue from one elected lane.
+//
+// Variants in this file: the kernel that quantises its fp32 activation itself (kQuantA), the output-layer
+// kernel whose write-back reduces every 128-word block to its maximum, sum of exponentials and best
+// entries (kTopK), and the CTA-pair kernel (tcgen05.mma.cta_group::2, 256 x 256 tile per cluster of two
+// CTAs) that the plan picks for large M.
 #include <cfloat>
 #include <cuda_fp16.h>
 
