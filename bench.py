@@ -28,6 +28,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+KERNEL_NAMES = ["mi8_gemm_pair_kernel", "mi8_gemm_kernel", "quantize_slot_kernel", "attention1_kernel", "attention_enc_kernel",
+                "add_layernorm_kernel", "history_quantize_kernel", "history_absmax_kernel", "history_commit_kernel", "lse_topk_kernel",
+                "lse_merge_kernel", "nbest_merge_kernel", "embed_kernel", "ancestors_update_kernel", "gather_rows_kernel",
+                "ssru_cell_kernel", "mi8_absmax_kernel", "mi8_quantize_kernel", "mi8_transpose_quantize_kernel"]
 METRIC = "int8_decode_tgt_tokens_per_sec"
 UNIT = "tokens/s"
 WORKLOAD = "transformer-big decode (6+6 layers, d=1024, ffn=4096, 16 heads, tied 32000 vocab, all affines int8), beam 4, mini-batch 128, lengths clip(N(30,12),4,128), max length 1.5x source"
@@ -248,6 +252,34 @@ def run_ours(args):
     ms_profiled = p0.elapsed_time(p1)
     gemm_total, gemm_classes = gt.summary()
 
+    # ---- and once with every kernel bracketed (mi8_kernel_times_*): per kernel function its launches and device time
+    kernel_table = None
+    if rank == 0:
+        import ctypes
+        import re
+        from marian_dev_b200.binding import Mi8KernelTime, check, lib
+        check(lib().mi8_kernel_times_begin())
+        for sid, ids_t, mask_t in resident[:max(1, len(resident) // 2)]:
+            search.search_device(ids_t, mask_t)
+        buf = (Mi8KernelTime * 64)()
+        n = ctypes.c_int(0)
+        check(lib().mi8_kernel_times_end(buf, 64, ctypes.byref(n)))
+        rows = []
+        for r in buf[:n.value]:
+            nm = r.name.decode(errors="replace")
+            short = max((b for b in KERNEL_NAMES if b in nm), key=len, default=nm[:40])        # readable part of the mangled symbol
+            targs = re.findall(r"ILi(\d+)E|Li(\d+)E|Lb([01])E", nm[nm.find(short):])
+            rows.append((short + ("<" + ",".join(x or y or z for x, y, z in targs) + ">" if targs else ""), int(r.launches), float(r.total_us)))
+        tot = sum(us for _, _, us in rows) or 1.0
+        merged = {}
+        for nm, l, us in rows:
+            a = merged.setdefault(nm, [0, 0.0])
+            a[0] += l
+            a[1] += us
+        kernel_table = [{"kernel": k, "launches": v[0], "us": round(v[1], 1), "share": round(v[1] / tot, 4)}
+                        for k, v in sorted(merged.items(), key=lambda kv: -kv[1][1])]
+    barrier()
+
     # ---- leg 2: end to end through the public call with host buffers --------------------------
     leg2 = leg1
     pinned = [(sid, torch.from_numpy(ids.astype(np.int64)).pin_memory(), torch.from_numpy(mask).pin_memory()) for sid, ids, mask in leg2]
@@ -312,7 +344,10 @@ def run_ours(args):
                        "tokens_counted": "best hypothesis per sentence, EOS included", "parallelism": f"replicas x{world}",
                        "l2": "not flushed: one decode step streams ~0.2 GB of int8 weights plus fp32 logits and history, more than the 126 MB L2"},
             "e2e": {"value": round(tokens2 / (ms2 / 1e3), 1), "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
-            "gpu_launches": int(launches), "gpu_launches_before_timed_region": int(launches_before), "clocks": clocks, "roofline": roofline, "device_status": status,
+            "gpu_launches": int(launches), "gpu_launches_before_timed_region": int(launches_before), "clocks": clocks,
+            # per kernel: launches / device time / share, CUDA events around every launch of half the timed mini-batches;
+            # launches serialise while timed, so every launch carries its ~4 us launch latency: compare shares
+            "kernels": kernel_table, "roofline": roofline, "device_status": status,
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu

@@ -203,6 +203,18 @@ typedef struct mi8_gemm_record {
 int mi8_profile_begin(int max_records);
 int mi8_profile_end(mi8_gemm_record* records, int capacity, int* count);
 
+/* Measurement aid: between mi8_kernel_times_begin and mi8_kernel_times_end every kernel the calling thread
+ * launches through the library is bracketed by CUDA events on its stream (launch overlap is off meanwhile, so
+ * the launches serialise); _end waits for the device and returns, per kernel function, its launches and
+ * total device time.  `name` is the function's (mangled) symbol name, truncated. */
+typedef struct mi8_kernel_time {
+  char name[160];
+  long long launches;
+  double total_us;
+} mi8_kernel_time;
+int mi8_kernel_times_begin(void);
+int mi8_kernel_times_end(mi8_kernel_time* out, int capacity, int* count);
+
 /* Number of kernels this thread has launched through the library since the last reset. */
 unsigned long long mi8_launch_count(void);
 void mi8_launch_count_reset(void);

@@ -20,6 +20,11 @@ class Mi8GemmRecord(ctypes.Structure):
     _fields_ = [("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("out_bytes", ctypes.c_int), ("us", ctypes.c_float)]
 
 
+class Mi8KernelTime(ctypes.Structure):
+    """mi8_kernel_time of include/marian_i8.h."""
+    _fields_ = [("name", ctypes.c_char * 160), ("launches", ctypes.c_longlong), ("total_us", ctypes.c_double)]
+
+
 class Mi8dConfig(ctypes.Structure):
     """mi8d_config of include/marian_i8_decode.h."""
     _fields_ = [(n, ctypes.c_int) for n in ("dim_emb", "dim_ffn", "heads", "enc_depth", "dec_depth", "vocab", "ssru", "max_rows",
@@ -38,7 +43,7 @@ EXPORTS = [
     "mi8_workspace_bytes", "mi8_workspace_init", "mi8_poll_status", "mi8_clear_status",
     "mi8_max_absolute_f32", "mi8_quantize_f32_i8", "mi8_prepare_a_f32", "mi8_prepare_b_f32",
     "mi8_multiply_i8", "mi8_multiply_i8_ex", "mi8_multiply_i8_rows_from", "mi8_multiply_f32_slot", "mi8_multiply_i8_static", "mi8_affine_f32", "mi8_multiply_plan",
-    "mi8_launch_count", "mi8_launch_count_reset", "mi8_measure_int8_peak", "mi8_profile_begin", "mi8_profile_end", "mi8_set_pdl",
+    "mi8_launch_count", "mi8_launch_count_reset", "mi8_measure_int8_peak", "mi8_kernel_times_begin", "mi8_kernel_times_end", "mi8_profile_begin", "mi8_profile_end", "mi8_set_pdl",
 ]
 
 
@@ -102,6 +107,9 @@ def lib() -> ctypes.CDLL:
     L.mi8_multiply_plan.argtypes = [ci, ci, ci, ci, ci, ctypes.POINTER(ci * 8)]
     L.mi8_measure_int8_peak.argtypes = [ci, ctypes.POINTER(cf), vp]
     L.mi8_measure_int8_peak.restype = ci
+    L.mi8_kernel_times_begin.restype = ci
+    L.mi8_kernel_times_end.argtypes = [ctypes.POINTER(Mi8KernelTime), ci, ctypes.POINTER(ci)]
+    L.mi8_kernel_times_end.restype = ci
     L.mi8_set_pdl.argtypes = [ci]
     L.mi8_set_pdl.restype = None
     L.mi8_profile_begin.argtypes = [ci]

@@ -2,6 +2,7 @@
 // the kernels.  No call here allocates device memory or synchronises with the host, except
 // mi8_poll_status which exists to do exactly that.
 #include <cstring>
+#include <vector>
 
 #include "mi8_internal.h"
 #include "mi8_ptx.cuh"
@@ -23,6 +24,37 @@ bool g_pdl = true;
 }
 bool pdl_enabled() { return g_pdl; }
 void set_pdl(bool on) { g_pdl = on; }
+
+// ---- per-kernel device times -------------------------------------------------------------------------
+struct KernelTimeState {
+  bool on = false;
+  std::vector<const void*> funcs;
+  std::vector<cudaEvent_t> pool;     // two events per launch, created once and reused
+  size_t used = 0;
+  cudaEvent_t take() {
+    if(used == pool.size()) {
+      cudaEvent_t e = nullptr;
+      if(cudaEventCreate(&e) != cudaSuccess)
+        return nullptr;
+      pool.push_back(e);
+    }
+    return pool[used++];
+  }
+};
+thread_local KernelTimeState t_ktimes;
+
+bool kernel_times_on() { return t_ktimes.on; }
+void kernel_times_before(const void* func, cudaStream_t stream) {
+  cudaEvent_t e = t_ktimes.take();
+  t_ktimes.funcs.push_back(func);
+  if(e != nullptr)
+    cudaEventRecord(e, stream);
+}
+void kernel_times_after(cudaStream_t stream) {
+  cudaEvent_t e = t_ktimes.take();
+  if(e != nullptr)
+    cudaEventRecord(e, stream);
+}
 
 void set_last_cuda_error(cudaError_t e) { t_last_error = e; }
 void count_launch() { ++t_launches; }
@@ -232,6 +264,55 @@ int mi8_affine_f32(const float* a, int M, int K, const int8_t* bt, const float* 
 }
 
 void mi8_set_pdl(int enabled) { set_pdl(enabled != 0); }
+
+int mi8_kernel_times_begin(void) {
+  t_ktimes.on = true;
+  t_ktimes.funcs.clear();
+  t_ktimes.used = 0;
+  return MI8_OK;
+}
+
+int mi8_kernel_times_end(mi8_kernel_time* out, int capacity, int* count) {
+  t_ktimes.on = false;
+  int n = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  for(size_t i = 0; e == cudaSuccess && i < t_ktimes.funcs.size() && 2 * i + 1 < t_ktimes.used; ++i) {
+    float ms = 0.f;
+    if(cudaEventElapsedTime(&ms, t_ktimes.pool[2 * i], t_ktimes.pool[2 * i + 1]) != cudaSuccess) {
+      cudaGetLastError();
+      continue;
+    }
+    const char* name = nullptr;
+    if(cudaFuncGetName(&name, t_ktimes.funcs[i]) != cudaSuccess || name == nullptr) {
+      cudaGetLastError();
+      name = "?";
+    }
+    int slot = -1;
+    for(int j = 0; j < n; ++j)
+      if(strncmp(out[j].name, name, sizeof(out[j].name) - 1) == 0) {
+        slot = j;
+        break;
+      }
+    if(slot < 0) {
+      if(out == nullptr || n >= capacity)
+        continue;
+      slot = n++;
+      memset(&out[slot], 0, sizeof(out[slot]));
+      strncpy(out[slot].name, name, sizeof(out[slot].name) - 1);
+    }
+    out[slot].launches += 1;
+    out[slot].total_us += ms * 1000.0;
+  }
+  t_ktimes.funcs.clear();
+  t_ktimes.used = 0;
+  if(count != nullptr)
+    *count = n;
+  if(e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return MI8_ERR_LAUNCH;
+  }
+  return MI8_OK;
+}
 
 int mi8_measure_int8_peak(int k_blocks, float* tops_out, void* stream) { return measure_int8_mma_peak(k_blocks, tops_out, as_stream(stream)); }
 

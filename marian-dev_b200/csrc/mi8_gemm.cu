@@ -1086,7 +1086,14 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& 
     if(rec.start != nullptr && rec.stop != nullptr)
       cudaEventRecord(rec.start, stream);
   }
+  const bool timed = kernel_times_on();
+  if(timed) {
+    cfg.numAttrs = 1;   // no launch overlap while per-kernel times are taken
+    kernel_times_before(reinterpret_cast<const void*>(mi8_gemm_pair_kernel), stream);
+  }
   cudaError_t le = cudaLaunchKernelEx(&cfg, mi8_gemm_pair_kernel, tw, ta, p);
+  if(timed)
+    kernel_times_after(stream);
   if(le != cudaSuccess) {
     set_last_cuda_error(le);
     return MI8_ERR_LAUNCH;

@@ -113,9 +113,26 @@ int launch_ssru_cell(const float* cell_old, const int* hyp, const float* xw, con
 bool pdl_enabled();
 void set_pdl(bool on);
 
+// Per-kernel device times (mi8_kernel_times_begin / _end): when on, every launch made through launch_kernel by
+// the calling thread is bracketed by CUDA events on its stream and attributed to the kernel function.
+bool kernel_times_on();
+void kernel_times_before(const void* func, cudaStream_t stream);
+void kernel_times_after(cudaStream_t stream);
+
 // Launches `kernel` with or without the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  if(kernel_times_on()) {
+    kernel_times_before(reinterpret_cast<const void*>(kernel), stream);
+    cudaLaunchConfig_t tcfg = {};
+    tcfg.gridDim = grid;
+    tcfg.blockDim = block;
+    tcfg.dynamicSmemBytes = smem;
+    tcfg.stream = stream;
+    const cudaError_t te = cudaLaunchKernelEx(&tcfg, kernel, static_cast<KArgs>(args)...);   // no launch overlap while timing
+    kernel_times_after(stream);
+    return te;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

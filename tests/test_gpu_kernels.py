@@ -322,3 +322,28 @@ def test_against_committed_golden_vectors(cuda_device):
         for key, arr in got.items():
             assert digest(arr) == want[name]["sha256"][key], f"{name}: {key} differs from the committed fixture"
     _assert_healthy()
+
+
+def test_kernel_times_facility(cuda_device):
+    """mi8_kernel_times_begin / _end attribute device time to the kernels launched in between."""
+    import ctypes
+    from marian_dev_b200.binding import Mi8KernelTime, check, lib
+    ops = _ops()
+    L = lib()
+    a = torch.randn(64, 256, device=cuda_device)
+    b = ops.prepareB(torch.randn(256, 128, device=cuda_device) * 0.02)
+    check(L.mi8_kernel_times_begin())
+    for _ in range(3):
+        ops.affine(a, b, None)
+    buf = (Mi8KernelTime * 16)()
+    n = ctypes.c_int(0)
+    check(L.mi8_kernel_times_end(buf, 16, ctypes.byref(n)))
+    got = {r.name.decode(): (r.launches, r.total_us) for r in buf[:n.value]}
+    gemm = [v for k, v in got.items() if "mi8_gemm_kernel" in k]
+    assert gemm and gemm[0][0] == 3 and gemm[0][1] > 0
+    assert sum(v[0] for v in got.values()) == 9          # abs-max, quantise, GEMM per affine
+    # off again: nothing is recorded
+    ops.affine(a, b, None)
+    check(L.mi8_kernel_times_begin())
+    check(L.mi8_kernel_times_end(buf, 16, ctypes.byref(n)))
+    assert n.value == 0
