@@ -347,3 +347,29 @@ def test_kernel_times_facility(cuda_device):
     check(L.mi8_kernel_times_begin())
     check(L.mi8_kernel_times_end(buf, 16, ctypes.byref(n)))
     assert n.value == 0
+
+
+@pytest.mark.parametrize("m,k,n", [(4096, 4096, 32000), (1, 4096, 32000), (4096, 512, 512), (1024, 1024, 32000), (4096, 4096, 4096)])
+def test_sweep_corner_shapes_at_full_size(cuda_device, oracle, m, k, n):
+    """The largest and the skinniest shapes of the affine sweep at their real sizes (two-CTA kernel, split-K and
+    weight-streaming plans included): int32 accumulators and fp32 outputs equal the checker's, bit for bit."""
+    ops = _ops()
+    oracle.set_threads(oracle.max_threads())
+    try:
+        rng = np.random.default_rng(m + k + n)
+        a = rng.standard_normal((m, k)).astype(np.float32)
+        w = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+        bias = (rng.standard_normal(n) * 0.01).astype(np.float32)
+        bt, qb = oracle.prepare_b(w)
+        want, want_acc, _aq, want_qa = oracle.affine(a, bt, qb, bias, 1.0, True, want_acc=True)
+        b = ops.prepareB(torch.from_numpy(w).to(cuda_device))
+        aq = ops.prepareA(torch.from_numpy(a).to(cuda_device))
+        acc = torch.empty((m, n), dtype=torch.int32, device=cuda_device)
+        out = ops.multiply(aq, b, torch.from_numpy(bias).to(cuda_device), 1.0, True, acc_out=acc)
+        torch.cuda.synchronize()
+        assert ops.poll_status() == 0
+        assert np.float32(aq.quant_mult.item()) == want_qa
+        assert np.array_equal(acc.cpu().numpy(), want_acc)
+        assert np.array_equal(out.cpu().numpy(), want)
+    finally:
+        oracle.set_threads(1)
