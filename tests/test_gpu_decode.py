@@ -124,3 +124,11 @@ def test_cpp_beam_search_equals_python_bookkeeping(cuda_device, cfg_name, beam):
         assert np.allclose([s for _, s in ra], [s for _, s in rb], rtol=1e-6, atol=0)
         ended_early += sum(1 for t, _ in ra if len(t) < int(1.5 * ids.shape[1]))
     assert ended_early > 0      # the purge paths were exercised
+
+
+def test_big_model_realistic_batch_identical(cuda_device):
+    """Transformer-big, 32 sentences of 20-40 tokens, beam 4: long enough histories for the two-CTA GEMM with tile
+    skipping on the stored keys/values, the fused output layer (128 rows) and the C++ beam search to run as they do
+    in the benchmark; every sequence identical to the CPU checker's."""
+    same, total, got, want, _ = _decode_both("big", 32, 32, 4, seed=3, lo=20, hi=40, native=True)
+    assert same == total, f"only {same}/{total} sentences identical"
