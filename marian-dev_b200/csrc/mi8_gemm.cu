@@ -1180,8 +1180,7 @@ int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, Gemm
   }
   if(tm == 0) {
     // Tile width along M.  Up to 64 rows: the smallest tile that holds them.  Above that, 256-row tiles
-    // only when they already give every SM a tile; otherwise narrower tiles (a quarter of M, 32..128
-    // rows) spread the weight stream over more SMs, which measured faster for the decode shapes.
+    // only when they already give every SM a tile; otherwise narrower tiles spread the work over more SMs.
     if(M <= 64) {
       tm = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     } else {
@@ -1189,9 +1188,16 @@ int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, Gemm
       if(tiles256 >= sms) {
         tm = 256;
       } else {
-        tm = 32;
-        while(tm < 128 && tm * 4 < M)
-          tm *= 2;
+        // The main loop of a CTA is bound by what one SM can pull from L2 (~64 bytes per clock), so the
+        // narrowest tile that still gives every tile its own SM finishes first (512 x 1024 x 1024: 5.2 us
+        // with 32-row tiles on 128 CTAs, 6.1 us with 128-row tiles on 32 CTAs).
+        tm = 128;
+        for(int cand : {32, 64}) {
+          if(static_cast<long long>((N + kTileN - 1) / kTileN) * ((M + cand - 1) / cand) <= sms) {
+            tm = cand;
+            break;
+          }
+        }
       }
     }
   }

@@ -43,7 +43,7 @@ def test_strerror_and_version():
     assert L.mi8_strerror(99) == b"unknown status"
 
 
-@pytest.mark.parametrize("m,expect_tile", [(1, 16), (16, 16), (17, 32), (64, 64), (65, 32), (128, 32), (200, 64), (512, 128), (2048, 128)])
+@pytest.mark.parametrize("m,expect_tile", [(1, 16), (16, 16), (17, 32), (64, 64), (65, 32), (128, 32), (200, 32), (512, 32), (1024, 64), (2048, 128)])
 def test_plan_tile_choice(m, expect_tile):
     from marian_dev_b200 import multiply_plan
     p = multiply_plan(m, 1024, 1024)
@@ -62,7 +62,7 @@ def test_plan_cta_pair_choice():
     assert p["tile_m"] == 512 and p["splits"] == 1 and p["n_tiles"] == 16 and p["m_tiles"] == 32
     assert p["grid"] % 2 == 0 and p["grid"] <= p["sm_count"] and p["smem_bytes"] <= 227 * 1024
     assert multiply_plan(8192, 4096, 512)["tile_m"] == 256
-    assert multiply_plan(512, 1024, 1024)["tile_m"] == 128
+    assert multiply_plan(512, 4096, 1024)["tile_m"] == 128
     assert multiply_plan(300, 384, 256, 512)["tile_m"] == 512      # forced
     assert multiply_plan(300, 384, 256, 512)["n_tiles"] == 2
 

@@ -43,7 +43,7 @@ def test_static_scratch_matches_workspace_entry_point(cuda_device, m, k, n):
 
 def test_static_scratch_rejects_oversized_shapes(cuda_device):
     from marian_dev_b200.binding import MI8_F32, lib
-    m, k, n = 512, 4096, 2304                                        # split-K plan needs 4.5 MiB of accumulation buffers
+    m, k, n = 64, 4096, 8320                                         # split-K plan: 65 tiles x 32 KiB = 2.03 MiB of accumulation buffers
     aq = torch.zeros(m * k + 4, dtype=torch.int8, device=cuda_device)
     bt = torch.zeros(n * k + 4, dtype=torch.int8, device=cuda_device)
     q = torch.ones(2, device=cuda_device)
