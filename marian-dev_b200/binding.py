@@ -37,6 +37,10 @@ DECODE_EXPORTS = ["mi8d_arena_bytes", "mi8d_create", "mi8d_destroy", "mi8d_set_w
                   "mi8g_embed", "mi8g_add_layernorm", "mi8g_quantize_slot", "mi8g_attention1", "mi8g_lse_topk", "mi8g_nbest_merge",
                   "mi8g_output_scratch_bytes", "mi8g_output_topk", "mi8d_keep_logits", "mi8d_search"]
 
+# Every symbol include/marian_packed8.h declares.
+PACKED8_EXPORTS = ["mi8p_packed_bytes", "mi8p_unpack_b", "mi8p_quantize_rows", "mi8p_multiply", "mi8p_scratch_bytes",
+                   "mi8p_gemm_int8_packed"]
+
 # Every symbol include/marian_i8.h declares.
 EXPORTS = [
     "mi8_version", "mi8_strerror", "mi8_last_cuda_error", "mi8_last_cuda_error_string",
@@ -117,6 +121,14 @@ def lib() -> ctypes.CDLL:
     L.mi8_profile_end.argtypes = [ctypes.POINTER(Mi8GemmRecord), ci, ctypes.POINTER(ci)]
     L.mi8_profile_end.restype = ci
     L.mi8_launch_count.restype = ctypes.c_ulonglong
+    L.mi8p_packed_bytes.restype = sz
+    L.mi8p_packed_bytes.argtypes = [ci, ci]
+    L.mi8p_unpack_b.argtypes = [vp, ci, ci, vp, vp]
+    L.mi8p_quantize_rows.argtypes = [vp, ci, ci, vp, vp, vp, vp, vp]
+    L.mi8p_multiply.argtypes = [vp] * 8 + [ci, ci, ci, vp, ci, vp, vp, vp, sz, vp, ci, ci]
+    L.mi8p_scratch_bytes.restype = sz
+    L.mi8p_scratch_bytes.argtypes = [ci, ci]
+    L.mi8p_gemm_int8_packed.argtypes = [vp] * 7 + [ci, ci, ci, vp, sz, vp, sz, vp]
     L.mi8_launch_count_reset.restype = None
     for name in ("mi8_workspace_init", "mi8_poll_status", "mi8_clear_status", "mi8_max_absolute_f32",
                  "mi8_quantize_f32_i8", "mi8_prepare_a_f32", "mi8_prepare_b_f32", "mi8_multiply_i8",

@@ -4,6 +4,7 @@
 #include <cstring>
 #include <vector>
 
+#include "../../include/marian_packed8.h"
 #include "mi8_internal.h"
 #include "mi8_ptx.cuh"
 
@@ -335,6 +336,60 @@ int mi8_multiply_plan(int M, int N, int K, int force_tile_m, int force_splits, i
   out[6] = plan.smem_bytes;
   out[7] = sm_count();
   return MI8_OK;
+}
+
+// ------------------------------------------------------------------ packed8avx512 scheme (marian_packed8.h)
+size_t mi8p_packed_bytes(int K, int N) {
+  return K > 0 && N > 0 ? static_cast<size_t>(K) * N + static_cast<size_t>(N) * 12 : 0;
+}
+
+int mi8p_unpack_b(const int8_t* packed, int K, int N, int8_t* bt, void* stream) {
+  return launch_p8_unpack_bt(packed, K, N, bt, as_stream(stream));
+}
+
+int mi8p_quantize_rows(const float* a, int M, int K, uint8_t* aq, float* scale_a, int32_t* zp_a, int32_t* sum_a, void* stream) {
+  return launch_p8_quantize_rows(a, M, K, aq, scale_a, zp_a, sum_a, as_stream(stream));
+}
+
+int mi8p_multiply(const uint8_t* aq, const float* scale_a, const int32_t* zp_a, const int32_t* sum_a, const int8_t* bt,
+                  const float* scale_b, const int32_t* zp_b, const int32_t* off_b, int M, int N, int K, const float* bias, int relu,
+                  float* c, int32_t* acc_out, void* workspace, size_t workspace_bytes, void* stream, int force_tile_m,
+                  int force_splits) {
+  return launch_gemm_p8(aq, scale_a, zp_a, sum_a, bt, scale_b, zp_b, off_b, M, N, K, bias, relu, c, acc_out, workspace, workspace_bytes,
+                        as_stream(stream), force_tile_m, force_splits);
+}
+
+size_t mi8p_scratch_bytes(int M, int K) {
+  if(M <= 0 || K <= 0)
+    return 0;
+  const size_t aq = (static_cast<size_t>(M) * K + 255) / 256 * 256;
+  const size_t per_row = (static_cast<size_t>(M) * 4 + 255) / 256 * 256;
+  return aq + 3 * per_row;
+}
+
+int mi8p_gemm_int8_packed(const float* a, const int8_t* bt, const float* scale_b, const int32_t* zp_b, const int32_t* off_b,
+                          const float* bias, float* c, int M, int N, int K, void* scratch, size_t scratch_bytes, void* workspace,
+                          size_t workspace_bytes, void* stream) {
+  if(M < 0 || N <= 0 || K <= 0)
+    return MI8_ERR_BAD_ARG;
+  if(M == 0)
+    return MI8_OK;
+  if(scratch == nullptr || scratch_bytes < mi8p_scratch_bytes(M, K))
+    return MI8_ERR_WORKSPACE;
+  if(reinterpret_cast<uintptr_t>(scratch) & 255u)
+    return MI8_ERR_MISALIGNED;
+  uint8_t* base = static_cast<uint8_t*>(scratch);
+  const size_t aq_bytes = (static_cast<size_t>(M) * K + 255) / 256 * 256;
+  const size_t per_row = (static_cast<size_t>(M) * 4 + 255) / 256 * 256;
+  uint8_t* aq = base;
+  float* scale_a = reinterpret_cast<float*>(base + aq_bytes);
+  int32_t* zp_a = reinterpret_cast<int32_t*>(base + aq_bytes + per_row);
+  int32_t* sum_a = reinterpret_cast<int32_t*>(base + aq_bytes + 2 * per_row);
+  int rc = launch_p8_quantize_rows(a, M, K, aq, scale_a, zp_a, sum_a, as_stream(stream));
+  if(rc != MI8_OK)
+    return rc;
+  return launch_gemm_p8(aq, scale_a, zp_a, sum_a, bt, scale_b, zp_b, off_b, M, N, K, bias, 0, c, nullptr, workspace, workspace_bytes,
+                        as_stream(stream), 0, 0);
 }
 
 }  // extern "C"

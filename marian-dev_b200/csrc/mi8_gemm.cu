@@ -99,6 +99,14 @@ struct GemmParams {
   const unsigned* skip_a;   // when both are set and *skip_a == *skip_b, tiles that lie entirely below
   const unsigned* skip_b;   // row skip_rows_below are not computed (their previous results still hold)
   int skip_rows_below;
+  // packed8avx512 scheme (kP8): the activation is uint8 with a scale, zero point and row sum per ROW,
+  // the weights int8 with a scale, zero point and column offset per COLUMN (d_qa / d_qb / scale unused)
+  const float* p8_scale_a;
+  const int32_t* p8_zp_a;
+  const int32_t* p8_sum_a;
+  const float* p8_scale_b;
+  const int32_t* p8_zp_b;
+  const int32_t* p8_off_b;
   int* status;
 };
 
@@ -194,6 +202,35 @@ __device__ __forceinline__ unsigned write_back_chunk(const GemmParams& p, const 
   return out_max;
 }
 
+// Write-back of the packed8avx512 scheme (marian::cpu::mjdgemm dequantizeAndAdd, AVX-512 route,
+// src/tensors/cpu/mjdgemm/mjdgemm_avx512.cpp:290-322): the thread owns weight column n, v[j] is the
+// accumulator of activation row m_first + j.
+//   xv = acc - zeroPointA[m] * colOffsetsB[n] - zeroPointB[n] * sumA[m]      (int32, wrapping)
+//   out = (scaleA[m] * scaleB[n]) * float(xv), and with a bias one fused multiply-add of the same product,
+// which is what the reference computes once GCC has contracted its multiply and add.
+template <int CH>
+__device__ __forceinline__ void write_back_chunk_p8(const GemmParams& p, const int32_t (&v)[CH], size_t base, int valid, int m_first, float scale_b,
+                                                    int zp_b, int off_b, float bias_n) {
+  float* dst = reinterpret_cast<float*>(p.c) + base;
+  int32_t* acc_dst = p.acc_out != nullptr ? p.acc_out + base : nullptr;
+#pragma unroll
+  for(int j = 0; j < CH; ++j) {
+    if(j < valid) {
+      const int m = m_first + j;
+      const unsigned xv = static_cast<unsigned>(v[j]) - static_cast<unsigned>(__ldg(p.p8_zp_a + m)) * static_cast<unsigned>(off_b)
+                          - static_cast<unsigned>(zp_b) * static_cast<unsigned>(__ldg(p.p8_sum_a + m));
+      const float scale = __fmul_rn(__ldg(p.p8_scale_a + m), scale_b);
+      const float xf = __int2float_rn(static_cast<int>(xv));
+      float r = p.bias != nullptr ? __fmaf_rn(scale, xf, bias_n) : __fmul_rn(scale, xf);
+      if(p.relu)
+        r = r > 0.0f ? r : 0.0f;
+      dst[static_cast<size_t>(j) * p.N] = r;
+      if(acc_dst != nullptr)
+        acc_dst[static_cast<size_t>(j) * p.N] = v[j];
+    }
+  }
+}
+
 // kQuantA: the activation arrives as fp32 plus the abs-max slot its producer reduced; the eight epilogue
 // warps quantise the tile's rows (Int8::PrepareA: round(x * 127/max) saturated to +-127) straight into the
 // shared-memory ring in the 128-byte-swizzled K-major layout the MMA reads, so no int8 copy of the
@@ -203,7 +240,7 @@ __device__ __forceinline__ unsigned write_back_chunk(const GemmParams& p, const 
 // N-side tile 256 rows of the tied embedding matrix): a thread owns one query row and 128 consecutive
 // vocabulary entries of it per tile, so it can reduce them on its own - block maximum, sum of exponentials
 // in ascending order, the kTopK best entries - and the [rows, vocabulary] logits never reach memory.
-template <int TM, bool kQuantA, int kTopK = 0>
+template <int TM, bool kQuantA, int kTopK = 0, bool kP8 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
   using T = TileCfg<TM>;
@@ -306,7 +343,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     }
   } else if(warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc = make_idesc_i8(TM);
+    constexpr uint32_t idesc = kP8 ? make_idesc_i8_ub(TM) : make_idesc_i8(TM);
     uint32_t it = 0, acc_it = 0;
     bool skip_on = false;
     if(p.skip_a != nullptr) {
@@ -379,10 +416,12 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         if(bits >= 0x7f800000u)
           atomicMax(p.status, static_cast<int>(kDevNonFinite));
       }
+    } else if(kP8) {
+      qa = 1.0f;
     } else {
       qa = *p.d_qa;
     }
-    const float unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.d_qb)), p.scale);
+    const float unquant = kP8 ? 1.0f : __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.d_qb)), p.scale);
     uint32_t acc_it = 0;
     uint32_t conv_it = 0;
     const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
@@ -576,6 +615,15 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         continue;
       }
       const float bias_n = (p.bias != nullptr && n_ok) ? __ldg(p.bias + n) : 0.0f;
+      float p8_scale_b = 0.0f;
+      int p8_zp_b = 0, p8_off_b = 0;
+      if constexpr(kP8) {
+        if(n_ok) {
+          p8_scale_b = __ldg(p.p8_scale_b + n);
+          p8_zp_b = __ldg(p.p8_zp_b + n);
+          p8_off_b = __ldg(p.p8_off_b + n);
+        }
+      }
       // Split-K: every split adds its partial accumulators into one int32 buffer per tile with
       // fire-and-forget reductions (layout [column][128 rows], coalesced); the last split to arrive
       // reads the totals back, zeroes the buffer again and runs the write-back.
@@ -629,7 +677,11 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             tmem_ld_chunk<T::kChunk>(t_addr + col0, v);
             tc_wait_ld();
           }
-          if(n_ok)
+          if constexpr(kP8) {
+            if(n_ok)
+              write_back_chunk_p8<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * p.N + n, cols_valid - col0, m0 + col0, p8_scale_b, p8_zp_b,
+                                             p8_off_b, bias_n);
+          } else if(n_ok)
             out_max = write_back_chunk<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * p.N + n, cols_valid - col0, unquant, bias_n,
                                                   out_max);
         }
@@ -1002,14 +1054,14 @@ struct ProfileState {
 };
 thread_local ProfileState t_profile;
 
-template <int TM, bool kQuantA = false, int kTopK = 0>
+template <int TM, bool kQuantA = false, int kTopK = 0, bool kP8 = false>
 int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, const GemmPlan& plan, cudaStream_t stream) {
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   constexpr int smem = smem_bytes_for<TM>();
   if(dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(mi8_gemm_kernel<TM, kQuantA, kTopK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(mi8_gemm_kernel<TM, kQuantA, kTopK, kP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if(e != cudaSuccess) {
       set_last_cuda_error(e);
       return MI8_ERR_LAUNCH;
@@ -1023,7 +1075,7 @@ int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p
     if(rec.start != nullptr && rec.stop != nullptr)
       cudaEventRecord(rec.start, stream);
   }
-  cudaError_t le = launch_kernel(mi8_gemm_kernel<TM, kQuantA, kTopK>, dim3(plan.grid), dim3(kThreads), smem, stream, tw, ta, p);
+  cudaError_t le = launch_kernel(mi8_gemm_kernel<TM, kQuantA, kTopK, kP8>, dim3(plan.grid), dim3(kThreads), smem, stream, tw, ta, p);
   if(le != cudaSuccess) {
     set_last_cuda_error(le);
     return MI8_ERR_LAUNCH;
@@ -1316,6 +1368,71 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
     case 64: return launch_cfg<64>(tw, ta, p, plan, stream);
     case 128: return launch_cfg<128>(tw, ta, p, plan, stream);
     default: return launch_cfg<256>(tw, ta, p, plan, stream);
+  }
+}
+
+// The packed8avx512 multiply: the plan of launch_gemm without the CTA-pair kernel; the accumulators and the
+// split-K machinery are the same, only the operand signedness and the write-back differ.
+int launch_gemm_p8(const uint8_t* aq, const float* scale_a, const int32_t* zp_a, const int32_t* sum_a, const int8_t* bt,
+                   const float* scale_b, const int32_t* zp_b, const int32_t* off_b, int M, int N, int K, const float* bias, int relu,
+                   float* c, int32_t* acc_out, void* ws, size_t ws_bytes, cudaStream_t stream, int force_tile_m, int force_splits) {
+  if(M < 0 || N <= 0 || K <= 0 || force_tile_m < 0 || force_splits < 0 || force_tile_m == kPairTileCode)
+    return MI8_ERR_BAD_ARG;
+  if(M == 0)
+    return MI8_OK;
+  if(aq == nullptr || bt == nullptr || c == nullptr || scale_a == nullptr || zp_a == nullptr || sum_a == nullptr || scale_b == nullptr
+     || zp_b == nullptr || off_b == nullptr)
+    return MI8_ERR_BAD_ARG;
+  if(K % 16 != 0 || (reinterpret_cast<uintptr_t>(aq) & 15u) || (reinterpret_cast<uintptr_t>(bt) & 15u))
+    return MI8_ERR_MISALIGNED;
+  GemmPlan plan;
+  int rc = make_gemm_plan(M, N, K, force_tile_m, force_splits, &plan);
+  if(rc == MI8_OK && plan.pair)
+    rc = make_gemm_plan(M, N, K, 256, force_splits, &plan);
+  if(rc != MI8_OK)
+    return rc;
+  if(plan.splits > 1 && (ws == nullptr || ws_bytes < kWsHeaderBytes + plan.partial_bytes))
+    return MI8_ERR_WORKSPACE;
+  CUtensorMap tw, ta;
+  rc = encode_kmajor_map(&tw, bt, N, K, kTileN);
+  if(rc != MI8_OK)
+    return rc;
+  rc = encode_kmajor_map(&ta, reinterpret_cast<const int8_t*>(aq), M, K, plan.tile_m);
+  if(rc != MI8_OK)
+    return rc;
+  GemmParams p{};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.n_tiles = plan.n_tiles;
+  p.m_tiles = plan.m_tiles;
+  p.splits = plan.splits;
+  p.kb_total = plan.kb_total;
+  p.kb_per_split = plan.kb_per_split;
+  p.total_work = plan.n_tiles * plan.m_tiles * plan.splits;
+  p.scale = 1.0f;
+  p.bias = bias;
+  p.relu = relu ? 1 : 0;
+  p.c = c;
+  p.acc_out = acc_out;
+  uint8_t* wsb = static_cast<uint8_t*>(ws);
+  p.partials = wsb ? reinterpret_cast<int32_t*>(wsb + kWsOffPartials) : nullptr;
+  p.tile_counters = wsb ? reinterpret_cast<unsigned*>(wsb + kWsOffTileCounters) : nullptr;
+  p.p8_scale_a = scale_a;
+  p.p8_zp_a = zp_a;
+  p.p8_sum_a = sum_a;
+  p.p8_scale_b = scale_b;
+  p.p8_zp_b = zp_b;
+  p.p8_off_b = off_b;
+  p.status = device_status_ptr();
+  if(p.status == nullptr)
+    return MI8_ERR_LAUNCH;
+  switch(plan.tile_m) {
+    case 16: return launch_cfg<16, false, 0, true>(tw, ta, p, plan, stream);
+    case 32: return launch_cfg<32, false, 0, true>(tw, ta, p, plan, stream);
+    case 64: return launch_cfg<64, false, 0, true>(tw, ta, p, plan, stream);
+    case 128: return launch_cfg<128, false, 0, true>(tw, ta, p, plan, stream);
+    default: return launch_cfg<256, false, 0, true>(tw, ta, p, plan, stream);
   }
 }
 

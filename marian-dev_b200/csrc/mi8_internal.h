@@ -78,6 +78,14 @@ int launch_gemm_quant_a(const float* a_f32, const unsigned* a_slot, float* qa_ou
                         const float* d_qb, float scale, const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out,
                         cudaStream_t stream, unsigned* absmax_out = nullptr);
 
+// packed8avx512 scheme (mi8_packed8.cu, mi8_gemm.cu): weight item back to Bt[N,K]; per-row uint8 quantisation of
+// the activation; uint8 x int8 GEMM whose write-back applies the zero points, the scales and the bias.
+int launch_p8_unpack_bt(const int8_t* packed, int K, int N, int8_t* bt, cudaStream_t stream);
+int launch_p8_quantize_rows(const float* a, int M, int K, uint8_t* aq, float* scale_a, int32_t* zp_a, int32_t* sum_a, cudaStream_t stream);
+int launch_gemm_p8(const uint8_t* aq, const float* scale_a, const int32_t* zp_a, const int32_t* sum_a, const int8_t* bt,
+                   const float* scale_b, const int32_t* zp_b, const int32_t* off_b, int M, int N, int K, const float* bias, int relu,
+                   float* c, int32_t* acc_out, void* ws, size_t ws_bytes, cudaStream_t stream, int force_tile_m, int force_splits);
+
 // Output layer: GEMM whose write-back reduces every (row, block of 128 vocabulary entries) to its maximum, its sum
 // of exponentials and its k_top (4 or 8) best entries (blk_* arrays: [rows][ceil(vocab/128)] (x k_top)); then
 // launch_lse_merge turns those into the per-row candidates launch_lse_topk would have produced from the logits.

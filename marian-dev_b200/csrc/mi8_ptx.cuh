@@ -243,4 +243,9 @@ __host__ __device__ constexpr uint32_t make_idesc_i8(int n, int m = 128) {
   return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// The same with an UNSIGNED 8-bit B operand (bits [10,13) = 0): uint8 activations against int8 weights.
+__host__ __device__ constexpr uint32_t make_idesc_i8_ub(int n, int m = 128) {
+  return (2u << 4) | (1u << 7) | (0u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
 }  // namespace mi8

@@ -261,3 +261,152 @@ class COracle:
         self.L.mo_ssru_cell(_p(cell, ctypes.c_float), _p(xw, ctypes.c_float), _p(f, ctypes.c_float), cell.size,
                             _p(cn, ctypes.c_float), _p(h, ctypes.c_float))
         return cn, h
+
+
+# ---------------------------------------------------------------------------------------------
+# packed8avx512 (mjdgemm route): restatement in oracle_packed8.c, and the reference's own code
+# compiled into _ref/libref_mjdgemm.so by `make ref`.
+
+_REF_MJD = os.path.join(_HERE, "_ref", "libref_mjdgemm.so")
+
+
+def aligned_empty(shape, dtype, alignment: int = 64) -> np.ndarray:
+    """A C-contiguous array whose first byte sits on `alignment` (the reference's AVX-512 route uses
+    aligned loads on A, the bias, C and the per-column parameters)."""
+    nbytes = int(np.prod(shape)) * np.dtype(dtype).itemsize
+    raw = np.zeros(nbytes + alignment, np.uint8)
+    off = (-raw.ctypes.data) % alignment
+    return raw[off:off + nbytes].view(dtype).reshape(shape)
+
+
+def aligned_copy(a: np.ndarray, dtype=None) -> np.ndarray:
+    out = aligned_empty(a.shape, dtype or a.dtype)
+    out[...] = a
+    return out
+
+
+class Packed8Item:
+    """Views into one packed8avx512 item: block-ordered int8 weights, then scaleB, zeroPointB, colOffsetsB."""
+
+    def __init__(self, packed: np.ndarray, K: int, N: int):
+        assert packed.dtype == np.int8 and packed.size == K * N + 12 * N
+        self.packed, self.K, self.N = packed, K, N
+        self.scale_b = packed[K * N:K * N + 4 * N].view(np.float32)
+        self.zp_b = packed[K * N + 4 * N:K * N + 8 * N].view(np.int32)
+        self.off_b = packed[K * N + 8 * N:].view(np.int32)
+
+
+class Packed8Oracle:
+    """ctypes view of the mo_p8_* functions of liboracle_i8.so."""
+
+    def __init__(self, lib_path: str | None = None):
+        if lib_path is None:
+            lib_path = _LIB if os.path.exists(_LIB) else build()
+        L = ctypes.CDLL(lib_path)
+        if not hasattr(L, "mo_p8_gemm_packed"):
+            L = ctypes.CDLL(build(force=True))
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        L.mo_p8_packed_bytes.restype = ctypes.c_size_t
+        L.mo_p8_packed_bytes.argtypes = [ci, ci]
+        L.mo_p8_prepare_b.argtypes = [vp, ci, ci, vp]
+        L.mo_p8_pack_b.argtypes = [vp, ci, ci, vp]
+        L.mo_p8_unpack_bt.argtypes = [vp, ci, ci, vp]
+        L.mo_p8_quantize_rows.restype = None
+        L.mo_p8_quantize_rows.argtypes = [vp, ci, ci, vp, vp, vp, vp]
+        L.mo_p8_affine_bt.argtypes = [vp] * 6 + [ci, vp, vp, ci, ci, ci]
+        L.mo_p8_gemm_packed.argtypes = [vp, vp, vp, vp, ci, ci, ci]
+        L.mo_p8_set_threads.argtypes = [ci]
+        self.L = L
+
+    @staticmethod
+    def _v(a):
+        return a.ctypes.data_as(ctypes.c_void_p) if a is not None else None
+
+    def set_threads(self, n: int) -> None:
+        self.L.mo_p8_set_threads(int(n))
+
+    def prepare_b(self, w: np.ndarray) -> Packed8Item:
+        """fp32 W [K,N] -> packed item (fbgemmPacked8Pack restated, min/max range)."""
+        w = np.ascontiguousarray(w, np.float32)
+        K, N = w.shape
+        packed = aligned_empty((self.L.mo_p8_packed_bytes(K, N),), np.int8)
+        if self.L.mo_p8_prepare_b(self._v(w), K, N, self._v(packed)):
+            raise ValueError("packed8avx512 needs K % 256 == 0 and N % 32 == 0")
+        return Packed8Item(packed, K, N)
+
+    def pack_b(self, b: np.ndarray) -> np.ndarray:
+        b = np.ascontiguousarray(b, np.int8)
+        K, N = b.shape
+        out = np.zeros(K * N, np.int8)
+        if self.L.mo_p8_pack_b(self._v(b), K, N, self._v(out)):
+            raise ValueError("bad shape")
+        return out
+
+    def unpack_bt(self, item: Packed8Item) -> np.ndarray:
+        bt = np.zeros((item.N, item.K), np.int8)
+        if self.L.mo_p8_unpack_bt(self._v(item.packed), item.K, item.N, self._v(bt)):
+            raise ValueError("bad shape")
+        return bt
+
+    def quantize_rows(self, a: np.ndarray):
+        a = np.ascontiguousarray(a, np.float32)
+        M, K = a.shape
+        aq = np.zeros((M, K), np.uint8)
+        sa, za, su = np.zeros(M, np.float32), np.zeros(M, np.int32), np.zeros(M, np.int32)
+        self.L.mo_p8_quantize_rows(self._v(a), M, K, self._v(aq), self._v(sa), self._v(za), self._v(su))
+        return aq, sa, za, su
+
+    def affine(self, a: np.ndarray, item: Packed8Item, bias=None, relu: bool = False, want_acc: bool = False):
+        a = np.ascontiguousarray(a, np.float32)
+        M, K = a.shape
+        assert K == item.K
+        bt = self.unpack_bt(item)
+        c = np.zeros((M, item.N), np.float32)
+        acc = np.zeros((M, item.N), np.int32) if want_acc else None
+        b = np.ascontiguousarray(bias, np.float32) if bias is not None else None
+        rc = self.L.mo_p8_affine_bt(self._v(a), self._v(bt), self._v(item.scale_b), self._v(item.zp_b), self._v(item.off_b),
+                                    self._v(b), int(relu), self._v(c), self._v(acc), M, item.N, K)
+        if rc:
+            raise ValueError("bad arguments")
+        return (c, acc) if want_acc else c
+
+
+class RefMjdgemm:
+    """The reference's own gemmInt8Packed, when `make -C oracle ref` has built it (raises FileNotFoundError otherwise)."""
+
+    SHAPES_NK = [(512, 512), (1024, 1024), (4096, 1024), (3072, 1024), (1024, 4096), (8192, 512), (512, 8192), (1024, 512),
+                 (512, 1024), (32000, 512)]
+
+    def __init__(self, lib_path: str = _REF_MJD):
+        if not os.path.exists(lib_path):
+            raise FileNotFoundError(lib_path)
+        self.L = ctypes.CDLL(lib_path)
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        self.L.ref_mjd_gemm.argtypes = [vp, vp, vp, vp, ci, ci, ci]
+        self.L.ref_mjd_pack_b.argtypes = [vp, vp, ci, ci]
+
+    def isa(self) -> int:
+        """marian::cpu::InstructionSet the reference picks on this host (5 and 6 are the AVX-512 route)."""
+        return int(self.L.ref_mjd_isa())
+
+    def supported(self, N: int, K: int) -> bool:
+        return bool(self.L.ref_mjd_supported(N, K))
+
+    def gemm(self, a: np.ndarray, item: Packed8Item, bias=None) -> np.ndarray:
+        a = aligned_copy(np.asarray(a, np.float32))
+        M, K = a.shape
+        b = aligned_copy(np.asarray(bias, np.float32)) if bias is not None else None
+        packed = item.packed if item.packed.ctypes.data % 64 == 0 else aligned_copy(item.packed)
+        c = aligned_empty((M, item.N), np.float32)
+        v = Packed8Oracle._v
+        if self.L.ref_mjd_gemm(v(a), v(packed), v(b), v(c), M, item.N, K):
+            raise ValueError("the reference does not instantiate this weight shape")
+        return np.array(c)
+
+    def pack_b(self, b: np.ndarray) -> np.ndarray:
+        b = np.ascontiguousarray(b, np.int8)
+        K, N = b.shape
+        out = np.zeros(K * N, np.int8)
+        if self.L.ref_mjd_pack_b(Packed8Oracle._v(b), Packed8Oracle._v(out), N, K):
+            raise ValueError("the reference does not instantiate this weight shape")
+        return out

@@ -31,6 +31,12 @@ def test_library_exports_every_declared_symbol():
     for sym in declared_decode:
         assert hasattr(L, sym), f"{sym} declared in include/marian_i8_decode.h but not exported"
     assert sorted(DECODE_EXPORTS) == declared_decode
+    from marian_dev_b200.binding import PACKED8_EXPORTS
+    declared_p8 = _declared_symbols("marian_packed8.h", "mi8p_")
+    assert declared_p8
+    for sym in declared_p8:
+        assert hasattr(L, sym), f"{sym} declared in include/marian_packed8.h but not exported"
+    assert sorted(PACKED8_EXPORTS) == declared_p8
 
 
 def test_strerror_and_version():
