@@ -75,6 +75,8 @@ def parse_args():
     ap.add_argument("--cpu-sentences", type=int, default=16, help="sentences in the CPU-baseline sample")
     ap.add_argument("--affine", default=None, help="M,K,N: time one int8 affine (abs-max + quantise + GEMM with bias and ReLU) instead of the decode")
     ap.add_argument("--sweep", action="store_true", help="time the affine shape sweep M x K x N instead of the decode")
+    ap.add_argument("--packed8", action="store_true",
+                    help="time the packed8avx512 affine on the weight shapes the reference's mjdgemm instantiates, the reference's own CPU code beside it")
     return ap.parse_args()
 
 
@@ -507,6 +509,137 @@ def time_affine_sharded(m, k, n, rank, world, iters=40):
             "algorithmic_bytes": by, "n_gpus": world, "rows_per_rank": (m + world - 1) // world, "operand_sets": copies}
 
 
+def time_packed8(m, k, n, iters=40):
+    """One packed8avx512 affine = per-row uint8 quantisation + uint8 x int8 GEMM with the zero-point / scale / bias
+    write-back (2 launches), through the C ABI, CUDA-graph replay over operand sets larger than L2."""
+    import numpy as np
+    import torch
+    from marian_dev_b200 import ops, packed8
+    from marian_dev_b200.binding import check, lib
+    dev = torch.device("cuda", torch.cuda.current_device())
+    L = lib()
+    per_copy = 4 * m * k + n * k + 4 * m * n
+    copies = max(2, min(32, int(300e6 // per_copy) + 1))
+    rng = np.random.default_rng(0)
+    host_item = np.zeros(int(L.mi8p_packed_bytes(k, n)), np.int8)
+    host_item[:k * n] = rng.integers(-64, 64, size=k * n, dtype=np.int8)
+    tail = host_item[k * n:]
+    tail[:4 * n].view(np.float32)[:] = 0.001
+    tail[4 * n:8 * n].view(np.int32)[:] = 3
+    tail[8 * n:].view(np.int32)[:] = -7
+    ws = [packed8.Packed8Weight(host_item, k, n, device=dev) for _ in range(copies)]
+    xs = [torch.randn(m, k, device=dev) for _ in range(copies)]
+    bias = torch.randn(n, device=dev) * 0.01
+    outs = [torch.empty(m, n, device=dev) for _ in range(copies)]
+    scratch = [torch.empty(max(256, int(L.mi8p_scratch_bytes(m, k))), dtype=torch.uint8, device=dev) for _ in range(copies)]
+    wsp = ops.default_workspace(dev)
+
+    def run(i, stream):
+        j = i % copies
+        w = ws[j]
+        check(L.mi8p_gemm_int8_packed(xs[j].data_ptr(), w.bt.data_ptr(), w.scale_b.data_ptr(), w.zp_b.data_ptr(), w.off_b.data_ptr(),
+                                      bias.data_ptr(), outs[j].data_ptr(), m, n, k, scratch[j].data_ptr(), scratch[j].numel(),
+                                      wsp.ptr, wsp.nbytes, stream))
+
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for i in range(5):
+            run(i, s.cuda_stream)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for i in range(iters):
+                run(i, s.cuda_stream)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        g.replay()
+        e1.record(s)
+        torch.cuda.synchronize()
+    if ops.poll_status() != 0:
+        raise RuntimeError("device status set during the packed8 timing")
+    us = e0.elapsed_time(e1) * 1000.0 / iters
+    by = 4 * m * k + k * n + 12 * n + 4 * n + 4 * m * n
+    return {"M": m, "K": k, "N": n, "us_per_affine": round(us, 2), "GBps": round(by / us / 1e3, 1), "TOPS": round(2.0 * m * n * k / us / 1e6, 2),
+            "algorithmic_bytes": by, "launches_per_affine": 2, "operand_sets": copies}
+
+
+def time_packed8_reference(m, k, n, budget_s=0.6):
+    """The reference's own gemmInt8Packed (compiled from its tree into oracle/_ref) on the host: one call on one
+    thread, and one call per hardware thread at once (Marian runs one translation worker per core)."""
+    import threading
+    import numpy as np
+    from oracle.oracle import Packed8Item, RefMjdgemm, aligned_copy, aligned_empty
+    ref = RefMjdgemm()
+    rng = np.random.default_rng(1)
+    packed = aligned_empty((k * n + 12 * n,), np.int8)
+    packed[:k * n] = rng.integers(-64, 64, size=k * n, dtype=np.int8)
+    item = Packed8Item(packed, k, n)
+    item.scale_b[:] = 0.001
+    a = aligned_copy(rng.standard_normal((m, k)).astype(np.float32))
+    bias = aligned_copy(rng.standard_normal(n).astype(np.float32))
+    c = aligned_empty((m, n), np.float32)
+    import ctypes
+
+    def vp(x):
+        return x.ctypes.data_as(ctypes.c_void_p)
+
+    def call(out):
+        ref.L.ref_mjd_gemm(vp(a), vp(packed), vp(bias), vp(out), m, n, k)
+
+    call(c)
+    t0 = time.perf_counter()
+    reps = 0
+    while reps < 3 or time.perf_counter() - t0 < budget_s / 2:
+        call(c)
+        reps += 1
+    single_us = (time.perf_counter() - t0) / reps * 1e6
+    cores = os.cpu_count() or 1
+    outs = [aligned_empty((m, n), np.float32) for _ in range(cores)]
+    per_thread = max(2, int(budget_s / 2 / (single_us * 1e-6)))
+
+    def worker(o):
+        for _ in range(per_thread):
+            call(o)
+
+    threads = [threading.Thread(target=worker, args=(o,)) for o in outs]
+    t0 = time.perf_counter()
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    all_us = (time.perf_counter() - t0) / (per_thread * cores) * 1e6
+    return {"us_per_affine_1_thread": round(single_us, 1), "us_per_affine_all_cores": round(all_us, 2), "cores": cores, "isa": ref.isa()}
+
+
+def run_packed8(args):
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the int8 engine has no CPU path")
+    torch.cuda.set_device(0)
+    warm = torch.randn(8192, 8192, device="cuda", dtype=torch.bfloat16)
+    for _ in range(30):
+        warm @ warm
+    torch.cuda.synchronize()
+    shapes_nk = [(512, 512), (1024, 1024), (4096, 1024), (3072, 1024), (1024, 4096), (8192, 512), (512, 8192), (1024, 512), (512, 1024),
+                 (32000, 512)]
+    for (n, k) in shapes_nk:
+        for m in (1, 8, 64, 256, 1024):
+            r = time_packed8(m, k, n)
+            r.update({"metric": "packed8avx512_affine", "timing": "CUDA-graph replay of 40 affines, CUDA events, operand sets rotated through > L2"})
+            try:
+                cpu = time_packed8_reference(m, k, n)
+                best_all = cpu["us_per_affine_all_cores"] < cpu["us_per_affine_1_thread"]
+                r["cpu_baseline"] = {"value": cpu["us_per_affine_all_cores"] if best_all else cpu["us_per_affine_1_thread"], "unit": "us/affine",
+                                     "cores": cpu["cores"] if best_all else 1, "kind": "reference",
+                                     "sample": f"gemmInt8Packed of oracle/_ref (ISA {cpu['isa']}): single thread {cpu['us_per_affine_1_thread']} us, "
+                                               f"one call per hardware thread at once {cpu['us_per_affine_all_cores']} us per affine"}
+            except FileNotFoundError:
+                r["cpu_baseline"] = None
+            print(json.dumps(r), flush=True)
+
+
 def run_affines(args):
     import torch
     if not torch.cuda.is_available():
@@ -545,7 +678,9 @@ def run_affines(args):
 
 if __name__ == "__main__":
     a = parse_args()
-    if a.affine or a.sweep:
+    if a.packed8:
+        run_packed8(a)
+    elif a.affine or a.sweep:
         run_affines(a)
     elif a.impl == "reference":
         run_reference(a)

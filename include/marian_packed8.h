@@ -45,6 +45,7 @@ int mi8p_quantize_rows(const float* a, int M, int K, uint8_t* aq, float* scale_a
 /* computeBlock + dequantizeAndAdd (mjdgemm_avx512.cpp:21-170, 290-322) on the tcgen05 GEMM: c fp32 [M,N];
  * bias fp32 [N] or NULL; relu != 0 applies max(0, .) (affineWithReluDropout, src/graph/expression_operators.cpp:721-731);
  * acc_out int32 [M,N] or NULL receives the raw uint8 x int8 sums.  workspace as for mi8_multiply_i8.
+ * aq, bt and the three per-row arrays must be 16-byte aligned, K % 16 == 0.
  * force_tile_m / force_splits: 0 = automatic (test hooks, as in mi8_multiply_i8_ex). */
 int mi8p_multiply(const uint8_t* aq, const float* scale_a, const int32_t* zp_a, const int32_t* sum_a,
                   const int8_t* bt, const float* scale_b, const int32_t* zp_b, const int32_t* off_b,

@@ -208,26 +208,52 @@ __device__ __forceinline__ unsigned write_back_chunk(const GemmParams& p, const 
 //   xv = acc - zeroPointA[m] * colOffsetsB[n] - zeroPointB[n] * sumA[m]      (int32, wrapping)
 //   out = (scaleA[m] * scaleB[n]) * float(xv), and with a bias one fused multiply-add of the same product,
 // which is what the reference computes once GCC has contracted its multiply and add.
+__device__ __forceinline__ float p8_value(int acc, int zp_a, int sum_a, float scale_a, float scale_b, int zp_b, int off_b, bool has_bias,
+                                          float bias_n, int relu) {
+  const unsigned xv = static_cast<unsigned>(acc) - static_cast<unsigned>(zp_a) * static_cast<unsigned>(off_b)
+                      - static_cast<unsigned>(zp_b) * static_cast<unsigned>(sum_a);
+  const float scale = __fmul_rn(scale_a, scale_b);
+  const float xf = __int2float_rn(static_cast<int>(xv));
+  float r = has_bias ? __fmaf_rn(scale, xf, bias_n) : __fmul_rn(scale, xf);
+  if(relu)
+    r = r > 0.0f ? r : 0.0f;
+  return r;
+}
+
+// The per-row parameters of four consecutive activation rows come in with one 16-byte load per array
+// (m_first is a multiple of 16 and the arrays are 16-byte aligned; a warp reads the same address, so each
+// load is one broadcast transaction); the ragged last chunk of a tile takes the element-wise path.
 template <int CH>
 __device__ __forceinline__ void write_back_chunk_p8(const GemmParams& p, const int32_t (&v)[CH], size_t base, int valid, int m_first, float scale_b,
                                                     int zp_b, int off_b, float bias_n) {
   float* dst = reinterpret_cast<float*>(p.c) + base;
   int32_t* acc_dst = p.acc_out != nullptr ? p.acc_out + base : nullptr;
+  const bool has_bias = p.bias != nullptr;
+  if(valid >= CH) {
 #pragma unroll
-  for(int j = 0; j < CH; ++j) {
-    if(j < valid) {
-      const int m = m_first + j;
-      const unsigned xv = static_cast<unsigned>(v[j]) - static_cast<unsigned>(__ldg(p.p8_zp_a + m)) * static_cast<unsigned>(off_b)
-                          - static_cast<unsigned>(zp_b) * static_cast<unsigned>(__ldg(p.p8_sum_a + m));
-      const float scale = __fmul_rn(__ldg(p.p8_scale_a + m), scale_b);
-      const float xf = __int2float_rn(static_cast<int>(xv));
-      float r = p.bias != nullptr ? __fmaf_rn(scale, xf, bias_n) : __fmul_rn(scale, xf);
-      if(p.relu)
-        r = r > 0.0f ? r : 0.0f;
-      dst[static_cast<size_t>(j) * p.N] = r;
-      if(acc_dst != nullptr)
-        acc_dst[static_cast<size_t>(j) * p.N] = v[j];
+    for(int j = 0; j < CH; j += 4) {
+      const int4 za = __ldg(reinterpret_cast<const int4*>(p.p8_zp_a + m_first + j));
+      const int4 su = __ldg(reinterpret_cast<const int4*>(p.p8_sum_a + m_first + j));
+      const float4 sa = __ldg(reinterpret_cast<const float4*>(p.p8_scale_a + m_first + j));
+      dst[static_cast<size_t>(j + 0) * p.N] = p8_value(v[j + 0], za.x, su.x, sa.x, scale_b, zp_b, off_b, has_bias, bias_n, p.relu);
+      dst[static_cast<size_t>(j + 1) * p.N] = p8_value(v[j + 1], za.y, su.y, sa.y, scale_b, zp_b, off_b, has_bias, bias_n, p.relu);
+      dst[static_cast<size_t>(j + 2) * p.N] = p8_value(v[j + 2], za.z, su.z, sa.z, scale_b, zp_b, off_b, has_bias, bias_n, p.relu);
+      dst[static_cast<size_t>(j + 3) * p.N] = p8_value(v[j + 3], za.w, su.w, sa.w, scale_b, zp_b, off_b, has_bias, bias_n, p.relu);
     }
+  } else {
+#pragma unroll
+    for(int j = 0; j < CH; ++j)
+      if(j < valid) {
+        const int m = m_first + j;
+        dst[static_cast<size_t>(j) * p.N] = p8_value(v[j], __ldg(p.p8_zp_a + m), __ldg(p.p8_sum_a + m), __ldg(p.p8_scale_a + m), scale_b, zp_b,
+                                                     off_b, has_bias, bias_n, p.relu);
+      }
+  }
+  if(acc_dst != nullptr) {
+#pragma unroll
+    for(int j = 0; j < CH; ++j)
+      if(j < valid)
+        acc_dst[static_cast<size_t>(j) * p.N] = v[j];
   }
 }
 
@@ -1385,6 +1411,8 @@ int launch_gemm_p8(const uint8_t* aq, const float* scale_a, const int32_t* zp_a,
     return MI8_ERR_BAD_ARG;
   if(K % 16 != 0 || (reinterpret_cast<uintptr_t>(aq) & 15u) || (reinterpret_cast<uintptr_t>(bt) & 15u))
     return MI8_ERR_MISALIGNED;
+  if((reinterpret_cast<uintptr_t>(scale_a) & 15u) || (reinterpret_cast<uintptr_t>(zp_a) & 15u) || (reinterpret_cast<uintptr_t>(sum_a) & 15u))
+    return MI8_ERR_MISALIGNED;   // the write-back reads the per-row arrays four rows at a time
   GemmPlan plan;
   int rc = make_gemm_plan(M, N, K, force_tile_m, force_splits, &plan);
   if(rc == MI8_OK && plan.pair)
