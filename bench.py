@@ -624,6 +624,12 @@ def run_packed8(args):
     torch.cuda.synchronize()
     shapes_nk = [(512, 512), (1024, 1024), (4096, 1024), (3072, 1024), (1024, 4096), (8192, 512), (512, 8192), (1024, 512), (512, 1024),
                  (32000, 512)]
+    if args.affine:                                     # one shape, GPU only (the form the ncu captures use)
+        m, k, n = (int(v) for v in args.affine.split(","))
+        r = time_packed8(m, k, n, iters=10)
+        r.update({"metric": "packed8avx512_affine", "timing": "CUDA-graph replay of 10 affines, CUDA events"})
+        print(json.dumps(r), flush=True)
+        return
     for (n, k) in shapes_nk:
         for m in (1, 8, 64, 256, 1024):
             r = time_packed8(m, k, n)
