@@ -31,6 +31,13 @@ extern "C" {
 /* Bytes of a packed8avx512 item for a [K,N] weight: K*N + 12*N. */
 size_t mi8p_packed_bytes(int K, int N);
 
+/* Offline conversion, the packed8avx512 branch of marian-conv (ExpressionGraphPackable::pack,
+ * src/tensors/cpu/expression_graph_packable.h:49-95 -> fbgemmPacked8Pack, src/tensors/cpu/fbgemm/packed_gemm.cpp:372-480,
+ * min/max ranges): w fp32 [K,N] row-major -> item of mi8p_packed_bytes(K, N) bytes.  Per column
+ * scaleB = (max - min) / 127, zeroPointB = (int32)(63 - max / scaleB), q = nearest_even(clamp(zeroPointB + x / scaleB, -64, 63)),
+ * colOffsetsB = sum(q) - zeroPointB * K.  K % 256 == 0 and N % 32 == 0, else MI8_ERR_UNSUPPORTED. */
+int mi8p_prepare_b_f32(const float* w, int K, int N, int8_t* packed, void* stream);
+
 /* Load-time step: the block order of packB (src/tensors/cpu/mjdgemm/mjdgemm_utils.h:136-165:
  * [K/256][N/32][64][32 columns][4 rows]) back to bt[N,K] row-major, the K-major layout the GEMM reads.
  * Requires K % 256 == 0 and N % 32 == 0 (the reference pads neither); MI8_ERR_UNSUPPORTED otherwise.

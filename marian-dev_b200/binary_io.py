@@ -24,8 +24,10 @@ TYPE_INT8 = 0x0100 + 1
 TYPE_FLOAT32 = 0x0400 + 4
 TYPE_INTGEMM8 = 0x10000 + 1
 TYPE_INTGEMM16 = 0x10000 + 2
+TYPE_PACKED8AVX512 = 0x0800 + 1 + 0x2000               # Type::packed8avx512 (src/common/types.h:315)
 _HW_BITS = 0x1000 | 0x2000 | 0x4000 | 0x8000          # avx2 / avx512 / sse2 / ssse3 layouts
-TYPE_NAMES = {TYPE_INT8: "int8", TYPE_FLOAT32: "float32", TYPE_INTGEMM8: "intgemm8", TYPE_INTGEMM16: "intgemm16"}
+TYPE_NAMES = {TYPE_INT8: "int8", TYPE_FLOAT32: "float32", TYPE_INTGEMM8: "intgemm8", TYPE_INTGEMM16: "intgemm16",
+              TYPE_PACKED8AVX512: "packed8avx512"}
 
 
 class Item:
@@ -60,6 +62,12 @@ def intgemm8_item(name: str, bt: np.ndarray, quant_mult: float, logical_shape) -
     """Payload = int8 Bt[N,K] then the fp32 multiplier (requiredBytes: elements + 4), padded to 256."""
     raw = np.ascontiguousarray(bt, dtype=np.int8).tobytes() + struct.pack("<f", float(quant_mult))
     return Item(name, logical_shape, TYPE_INTGEMM8, _pad256(raw))
+
+
+def packed8_item(name: str, packed: np.ndarray, logical_shape) -> Item:
+    """A packed8avx512 item: block-ordered int8 weights + scaleB + zeroPointB + colOffsetsB, logical shape [K,N]
+    (src/tensors/cpu/expression_graph_packable.h:82-92; the payload is padded to the allocation's 256-byte multiple)."""
+    return Item(name, logical_shape, TYPE_PACKED8AVX512, _pad256(np.ascontiguousarray(packed).view(np.uint8).tobytes()))
 
 
 def save_items(path: str, items) -> None:
@@ -123,8 +131,8 @@ def convert(params: dict, yaml_text: str, gemm_type: str = "intgemm8", device="c
     import torch
 
     from . import ops
-    if gemm_type not in ("float32", "intgemm8"):
-        raise ValueError(f"gemm-type {gemm_type} is not supported by this engine (float32 or intgemm8)")
+    if gemm_type not in ("float32", "intgemm8", "packed8avx512"):
+        raise ValueError(f"gemm-type {gemm_type} is not supported by this engine (float32, intgemm8 or packed8avx512)")
     items = []
     for name, val in params.items():
         val = np.asarray(val, dtype=np.float32)
@@ -132,6 +140,14 @@ def convert(params: dict, yaml_text: str, gemm_type: str = "intgemm8", device="c
             t = ops.prepareB(torch.from_numpy(np.ascontiguousarray(val)).to(device))
             torch.cuda.synchronize()
             items.append(intgemm8_item(name, t.data.cpu().numpy(), float(t.quant_mult.item()), val.shape))
+        elif gemm_type == "packed8avx512" and val.ndim == 2 and is_intgemm_param(name):
+            # the same parameter selection as the intgemm branch (expression_graph_packable.h:52-53); the blocks have no padding
+            from . import packed8
+            if val.shape[0] % 256 or val.shape[1] % 32:
+                raise ValueError(f"{name}: packed8avx512 needs K % 256 == 0 and N % 32 == 0, got {val.shape}")
+            t = packed8.prepareB(torch.from_numpy(np.ascontiguousarray(val)).to(device))
+            torch.cuda.synchronize()
+            items.append(packed8_item(name, t.item.cpu().numpy(), val.shape))
         else:
             items.append(float_item(name, val))
     items.append(meta_item(yaml_text))
@@ -139,7 +155,7 @@ def convert(params: dict, yaml_text: str, gemm_type: str = "intgemm8", device="c
 
 
 def items_to_params(items, device="cuda"):
-    """Items -> (yaml text, {name: float32 ndarray | ops.IntgemmTensor on the device})."""
+    """Items -> (yaml text, {name: float32 ndarray | ops.IntgemmTensor | packed8.Packed8Weight on the device})."""
     import torch
 
     from . import ops
@@ -155,6 +171,11 @@ def items_to_params(items, device="cuda"):
             need = n * k + 4
             t.storage[:need].copy_(torch.frombuffer(bytearray(it.bytes[:need]), dtype=torch.uint8))
             params[it.name] = t
+        elif it.type == TYPE_PACKED8AVX512:
+            from . import packed8
+            k, n = it.shape[-2], it.shape[-1]
+            need = k * n + 12 * n
+            params[it.name] = packed8.Packed8Weight(np.frombuffer(it.bytes, dtype=np.int8, count=need), k, n, device=device)
         elif (it.type & 0x10000) and (it.type & _HW_BITS):
             raise ValueError(f"{it.name}: hardware-specific intgemm layout (type {it.type:#x}) cannot be used on the GPU; "
                              "convert the model with --gemm-type intgemm8")

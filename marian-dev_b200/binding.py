@@ -38,7 +38,7 @@ DECODE_EXPORTS = ["mi8d_arena_bytes", "mi8d_create", "mi8d_destroy", "mi8d_set_w
                   "mi8g_output_scratch_bytes", "mi8g_output_topk", "mi8d_keep_logits", "mi8d_search"]
 
 # Every symbol include/marian_packed8.h declares.
-PACKED8_EXPORTS = ["mi8p_packed_bytes", "mi8p_unpack_b", "mi8p_quantize_rows", "mi8p_multiply", "mi8p_scratch_bytes",
+PACKED8_EXPORTS = ["mi8p_packed_bytes", "mi8p_prepare_b_f32", "mi8p_unpack_b", "mi8p_quantize_rows", "mi8p_multiply", "mi8p_scratch_bytes",
                    "mi8p_gemm_int8_packed"]
 
 # Every symbol include/marian_i8.h declares.
@@ -124,6 +124,7 @@ def lib() -> ctypes.CDLL:
     L.mi8p_packed_bytes.restype = sz
     L.mi8p_packed_bytes.argtypes = [ci, ci]
     L.mi8p_unpack_b.argtypes = [vp, ci, ci, vp, vp]
+    L.mi8p_prepare_b_f32.argtypes = [vp, ci, ci, vp, vp]
     L.mi8p_quantize_rows.argtypes = [vp, ci, ci, vp, vp, vp, vp, vp]
     L.mi8p_multiply.argtypes = [vp] * 8 + [ci, ci, ci, vp, ci, vp, vp, vp, sz, vp, ci, ci]
     L.mi8p_scratch_bytes.restype = sz

@@ -343,6 +343,10 @@ size_t mi8p_packed_bytes(int K, int N) {
   return K > 0 && N > 0 ? static_cast<size_t>(K) * N + static_cast<size_t>(N) * 12 : 0;
 }
 
+int mi8p_prepare_b_f32(const float* w, int K, int N, int8_t* packed, void* stream) {
+  return launch_p8_prepare_b(w, K, N, packed, as_stream(stream));
+}
+
 int mi8p_unpack_b(const int8_t* packed, int K, int N, int8_t* bt, void* stream) {
   return launch_p8_unpack_bt(packed, K, N, bt, as_stream(stream));
 }

@@ -80,6 +80,7 @@ int launch_gemm_quant_a(const float* a_f32, const unsigned* a_slot, float* qa_ou
 
 // packed8avx512 scheme (mi8_packed8.cu, mi8_gemm.cu): weight item back to Bt[N,K]; per-row uint8 quantisation of
 // the activation; uint8 x int8 GEMM whose write-back applies the zero points, the scales and the bias.
+int launch_p8_prepare_b(const float* w, int K, int N, int8_t* packed, cudaStream_t stream);
 int launch_p8_unpack_bt(const int8_t* packed, int K, int N, int8_t* bt, cudaStream_t stream);
 int launch_p8_quantize_rows(const float* a, int M, int K, uint8_t* aq, float* scale_a, int32_t* zp_a, int32_t* sum_a, cudaStream_t stream);
 int launch_gemm_p8(const uint8_t* aq, const float* scale_a, const int32_t* zp_a, const int32_t* sum_a, const int8_t* bt,

@@ -40,6 +40,67 @@ p8_unpack_bt_kernel(const uint32_t* __restrict__ packed, int K, int N, uint32_t*
   }
 }
 
+// Offline conversion of one fp32 weight [K,N] into a packed8avx512 item (fbgemmPacked8Pack with min/max ranges,
+// src/tensors/cpu/fbgemm/packed_gemm.cpp:372-480): per column scaleB = (max - min) / 127,
+// zeroPointB = trunc(63 - max / scaleB), q = nearest_even(clamp(zeroPointB + x / scaleB, -64, 63)) (7-bit range),
+// colOffsetsB = sum of the column's q - zeroPointB * K; weights in the block order of the item, the three arrays behind them.
+// One block converts the 32 columns of one block column: warp w takes the row groups w, w + 8, ... (four
+// consecutive rows each), lane = column, so every load is one 128-byte line and every store one 128-byte run.
+__global__ void __launch_bounds__(kBlock)
+p8_prepare_b_kernel(const float* __restrict__ w, int K, int N, uint32_t* __restrict__ packed, float* __restrict__ scale_b,
+                    int32_t* __restrict__ zp_b, int32_t* __restrict__ off_b) {
+  pdl_wait();
+  __shared__ float s_min[kBlock / 32][kNcb], s_max[kBlock / 32][kNcb];
+  __shared__ int s_sum[kBlock / 32][kNcb];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nb = blockIdx.x, n = nb * kNcb + lane;
+  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+  for(int k = warp; k < K; k += kBlock / 32) {
+    const float v = __ldg(w + static_cast<size_t>(k) * N + n);
+    mn = fminf(mn, v);
+    mx = fmaxf(mx, v);
+  }
+  s_min[warp][lane] = mn;
+  s_max[warp][lane] = mx;
+  __syncthreads();
+#pragma unroll
+  for(int i = 0; i < kBlock / 32; ++i) {
+    mn = fminf(mn, s_min[i][lane]);
+    mx = fmaxf(mx, s_max[i][lane]);
+  }
+  float s = __fdiv_rn(__fsub_rn(mx, mn), 127.0f);
+  if(!(s > 0.0f))
+    s = 1.0f;   // constant column
+  const int z = __float2int_rz(__fsub_rn(63.0f, __fdiv_rn(mx, s)));
+  const float zf = __int2float_rn(z);
+  int sum = 0;
+  const int n_blocks = N / kNcb;
+  for(int g = warp; g < K / kRi; g += kBlock / 32) {
+    uint32_t word = 0;
+#pragma unroll
+    for(int r = 0; r < kRi; ++r) {
+      const float x = __ldg(w + static_cast<size_t>(g * kRi + r) * N + n);
+      const float t = fminf(fmaxf(__fadd_rn(zf, __fdiv_rn(x, s)), -64.0f), 63.0f);
+      const int q = __float2int_rn(t);
+      sum += q;
+      word |= (static_cast<uint32_t>(q) & 0xffu) << (8 * r);
+    }
+    const int kb = (g * kRi) / kKcb, group = (g * kRi % kKcb) / kRi;
+    packed[(static_cast<size_t>(kb) * n_blocks + nb) * (kKcb * kNcb / kRi) + group * kNcb + lane] = word;
+  }
+  s_sum[warp][lane] = sum;
+  __syncthreads();
+  if(warp == 0) {
+    int total = 0;
+#pragma unroll
+    for(int i = 0; i < kBlock / 32; ++i)
+      total += s_sum[i][lane];
+    scale_b[n] = s;
+    zp_b[n] = z;
+    off_b[n] = total - z * K;
+  }
+}
+
 __device__ __forceinline__ float block_reduce(float v, float* smem, bool is_max) {
 #pragma unroll
   for(int o = 16; o > 0; o >>= 1) {
@@ -135,6 +196,25 @@ int launch_p8_unpack_bt(const int8_t* packed, int K, int N, int8_t* bt, cudaStre
   const int grid = static_cast<int>(std::min<size_t>((words + kBlock - 1) / kBlock, static_cast<size_t>(sm_count()) * 16));
   cudaError_t e = launch_kernel(p8_unpack_bt_kernel, dim3(grid), dim3(kBlock), 0, stream, reinterpret_cast<const uint32_t*>(packed), K, N,
                                 reinterpret_cast<uint32_t*>(bt));
+  if(e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return MI8_ERR_LAUNCH;
+  }
+  count_launch();
+  return check_launch();
+}
+
+int launch_p8_prepare_b(const float* w, int K, int N, int8_t* packed, cudaStream_t stream) {
+  if(w == nullptr || packed == nullptr || K <= 0 || N <= 0)
+    return MI8_ERR_BAD_ARG;
+  if(K % kKcb != 0 || N % kNcb != 0)
+    return MI8_ERR_UNSUPPORTED;
+  if(reinterpret_cast<uintptr_t>(packed) & 3u)
+    return MI8_ERR_MISALIGNED;
+  int8_t* tail = packed + static_cast<size_t>(K) * N;
+  cudaError_t e = launch_kernel(p8_prepare_b_kernel, dim3(N / kNcb), dim3(kBlock), 0, stream, w, K, N, reinterpret_cast<uint32_t*>(packed),
+                                reinterpret_cast<float*>(tail), reinterpret_cast<int32_t*>(tail + static_cast<size_t>(N) * 4),
+                                reinterpret_cast<int32_t*>(tail + static_cast<size_t>(N) * 8));
   if(e != cudaSuccess) {
     set_last_cuda_error(e);
     return MI8_ERR_LAUNCH;

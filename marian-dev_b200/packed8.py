@@ -18,7 +18,7 @@ class Packed8Weight:
     def __init__(self, packed, K: int, N: int, device="cuda"):
         L = lib()
         nbytes = int(L.mi8p_packed_bytes(K, N))
-        host = torch.as_tensor(np.ascontiguousarray(packed).view(np.int8)) if not isinstance(packed, torch.Tensor) else packed
+        host = torch.from_numpy(np.array(packed, copy=True).view(np.int8)) if not isinstance(packed, torch.Tensor) else packed
         if host.numel() != nbytes or host.dtype != torch.int8:
             raise ValueError(f"a packed8avx512 item of a [{K},{N}] weight has {nbytes} bytes")
         self.K, self.N = K, N
@@ -29,6 +29,17 @@ class Packed8Weight:
         self.scale_b = tail[:4 * N].view(torch.float32)
         self.zp_b = tail[4 * N:8 * N].view(torch.int32)
         self.off_b = tail[8 * N:].view(torch.int32)
+
+
+def prepareB(w: torch.Tensor) -> Packed8Weight:
+    """marian-conv --gemm-type packed8avx512 for one weight: fp32 [K,N] on the device -> Packed8Weight (item + Bt)."""
+    _require_cuda(w, "W")
+    w = w.contiguous().float()
+    K, N = w.shape
+    L = lib()
+    item = torch.empty(int(L.mi8p_packed_bytes(K, N)), dtype=torch.int8, device=w.device)
+    check(L.mi8p_prepare_b_f32(w.data_ptr(), K, N, item.data_ptr(), _stream_ptr()))
+    return Packed8Weight(item, K, N, device=w.device)
 
 
 def quantize_rows(a: torch.Tensor):

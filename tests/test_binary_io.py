@@ -51,6 +51,19 @@ def test_intgemm8_item_layout_and_meta():
         assert bio.is_intgemm_param(name) == want
 
 
+def test_packed8avx512_item_layout(tmp_path):
+    k, n = 256, 32
+    packed = (np.arange(k * n + 12 * n) % 251 - 125).astype(np.int8)
+    it = bio.packed8_item("encoder_l1_ffn_W1", packed, (k, n))
+    assert it.type == 0x2801 and it.shape == [k, n]                            # Type::packed8avx512, logical [K,N]
+    assert it.bytes[:packed.size] == packed.tobytes() and len(it.bytes) % 256 == 0
+    path = str(tmp_path / "m.bin")
+    bio.save_items(path, [it, bio.meta_item("type: transformer\n")])
+    back = bio.load_items(path)[0]
+    assert back.type == 0x2801 and back.shape == [k, n] and back.bytes[:packed.size] == packed.tobytes()
+    assert bio.TYPE_NAMES[back.type] == "packed8avx512"
+
+
 def test_hardware_specific_intgemm_items_are_refused():
     it = bio.Item("x_W", [16, 8], 0x10001 + 0x2000, b"\0" * 256)               # intgemm8avx512
     with pytest.raises(ValueError, match="hardware-specific"):

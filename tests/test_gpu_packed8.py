@@ -134,3 +134,33 @@ def test_one_call_entry_and_argument_checks(cuda_device, chk):
     assert L.mi8p_gemm_int8_packed(at.data_ptr(), wt.bt.data_ptr(), wt.scale_b.data_ptr(), wt.zp_b.data_ptr(), wt.off_b.data_ptr(),
                                    None, c.data_ptr(), 8, 64, 256, None, 0, None, 0, None) != 0   # no scratch
     _healthy()
+
+
+@pytest.mark.parametrize("K,N", [(256, 32), (512, 512), (1024, 96), (1536, 256)])
+def test_weight_conversion_bit_exact_and_container_round_trip(cuda_device, chk, tmp_path, K, N):
+    from marian_dev_b200 import binary_io as bio
+    p8 = _p8()
+    rng = np.random.default_rng(K + N)
+    w = (rng.standard_normal((K, N)) * 0.05).astype(np.float32)
+    w[:, 3] = 0.25                                            # a constant column
+    w[:, 5] = np.abs(w[:, 5])                                 # a one-sided column
+    want = chk.prepare_b(w)
+    got = p8.prepareB(torch.from_numpy(w).to(cuda_device))
+    torch.cuda.synchronize()
+    _healthy()
+    assert np.array_equal(got.item.cpu().numpy(), want.packed)          # weights, scales, zero points, column offsets
+    assert np.array_equal(got.bt.cpu().numpy(), chk.unpack_bt(want))
+    # marian-conv --gemm-type packed8avx512, then load: the affine on the loaded item equals the checker's
+    items = bio.convert({"encoder_l1_ffn_W1": w, "encoder_l1_ffn_b1": np.zeros((1, N), np.float32)}, "type: transformer\n",
+                        gemm_type="packed8avx512", device=cuda_device)
+    path = str(tmp_path / "model.bin")
+    bio.save_items(path, items)
+    _, params = bio.items_to_params(bio.load_items(path), device=cuda_device)
+    wt = params["encoder_l1_ffn_W1"]
+    assert isinstance(wt, p8.Packed8Weight) and params["encoder_l1_ffn_b1"].dtype == np.float32
+    a = rng.standard_normal((9, K)).astype(np.float32)
+    c = p8.gemmInt8Packed(torch.from_numpy(a).to(cuda_device), wt)
+    torch.cuda.synchronize()
+    assert _same_bits(c.cpu().numpy(), chk.affine(a, want, None))
+    L = __import__("marian_dev_b200.binding", fromlist=["lib"]).lib()
+    assert L.mi8p_prepare_b_f32(got.item.data_ptr(), 100, 32, got.item.data_ptr(), None) == 3
