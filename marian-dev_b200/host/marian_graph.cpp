@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/marian_i8.h"
+#include "../../include/marian_packed8.h"
 
 namespace marian {
 
@@ -25,11 +26,19 @@ std::string typeName(Type t) {
     case Type::float32: return "float32";
     case Type::intgemm8: return "intgemm8";
     case Type::intgemm16: return "intgemm16";
+    case Type::packed8avx2: return "packed8avx2";
+    case Type::packed8avx512: return "packed8avx512";
   }
   return "unknown";
 }
 
+namespace {
+size_t packed8ItemBytes(const Shape& shape) { return (mi8p_packed_bytes(shape[-2], shape[-1]) + 255) / 256 * 256; }
+}  // namespace
+
 size_t requiredBytes(const Shape& shape, Type type) {
+  if(isPacked(type))
+    return packed8ItemBytes(shape) + shape.elements();
   if(isIntgemm(type))
     return shape.elements() * sizeOf(type) + sizeOf(Type::float32);
   return shape.elements() * sizeOf(type);
@@ -82,6 +91,38 @@ Expr ExpressionGraph::intgemm8Param(const std::string& name, Expr w, bool wIsNK)
   check(mi8_prepare_b_f32(w->val()->data<float>(), k, n, wIsNK ? 1 : 0, q->value->data<int8_t>(), quantMultPtr(q->value), ws_, wsBytes_,
                           stream_),
         "weight conversion");
+  return q;
+}
+
+Expr ExpressionGraph::packed8Item(const std::string& name, const Shape& shape, const void* hostItem) {
+  MI8_ABORT_IF(shape.size() != 2, "A packed8avx512 parameter is a matrix");
+  const int k = shape[0], n = shape[1];
+  Expr q = std::make_shared<Node>();
+  q->graph = this;
+  q->name = name;
+  q->shapeValue = shape;
+  q->typeValue = Type::packed8avx512;
+  q->value = allocate(shape, Type::packed8avx512);
+  int8_t* item = q->value->data<int8_t>();
+  if(hostItem != nullptr)
+    checkCuda(cudaMemcpyAsync(item, hostItem, mi8p_packed_bytes(k, n), cudaMemcpyHostToDevice, streamOf(this)), "parameter upload");
+  check(mi8p_unpack_b(item, k, n, item + packed8ItemBytes(shape), stream_), "packed8avx512 load");
+  checkCuda(cudaStreamSynchronize(streamOf(this)), "parameter upload");
+  return q;
+}
+
+Expr ExpressionGraph::packed8Param(const std::string& name, Expr w) {
+  MI8_ABORT_IF(!isFloat(w->value_type()) || w->shape().size() != 2, "Only 2-D float32 parameters can be packed");
+  const int k = w->shape()[0], n = w->shape()[1];
+  Expr q = std::make_shared<Node>();
+  q->graph = this;
+  q->name = name;
+  q->shapeValue = w->shape();
+  q->typeValue = Type::packed8avx512;
+  q->value = allocate(q->shapeValue, Type::packed8avx512);
+  int8_t* item = q->value->data<int8_t>();
+  check(mi8p_prepare_b_f32(w->val()->data<float>(), k, n, item, stream_), "packed8avx512 conversion");
+  check(mi8p_unpack_b(item, k, n, item + packed8ItemBytes(q->shapeValue), stream_), "packed8avx512 load");
   return q;
 }
 
@@ -168,17 +209,62 @@ Expr affineOrDot(Expr a, Expr bQuant, Expr bias, bool transA, bool /*transB*/, f
 }
 
 }  // namespace integer
+
+namespace variant {
+
+Expr affine(Type packType, Expr a, Expr bPacked, const Shape& bShape, Expr bias, bool transA, bool transB, float scale) {
+  MI8_ABORT_IF(packType != Type::packed8avx512, "Only avx512 packed matrix format is supported, not " + typeName(packType));
+  MI8_ABORT_IF(transA || transB, "Transposition is currently not supported");
+  MI8_ABORT_IF(scale != 1.f, "The packed int8 product has no scalar factor");
+  MI8_ABORT_IF(!isFloat(a->value_type()), "Packed GEMM expects type of A to be float32 not " + typeName(a->value_type()));
+  MI8_ABORT_IF(a->shape()[-1] != bShape[-2], "Inner dimensions of A and B do not match");
+  Shape outShape = a->shape();
+  outShape.set(-1, bShape[-1]);
+  const int k = bShape[-2], n = bShape[-1];
+  auto nodeOp = [=](Expr out, const std::vector<Expr>& ch) {
+    Tensor A = ch[0]->val(), B = ch[1]->val();
+    const float* b = ch.size() > 2 ? ch[2]->val()->data<float>() : nullptr;
+    ExpressionGraph* g = out->graph;
+    const int m = rows(A);
+    const int8_t* item = B->data<int8_t>();
+    const int8_t* tail = item + static_cast<size_t>(k) * n;   // scaleB, zeroPointB, colOffsetsB (mjdgemm_avx512.cpp:222-227)
+    const int8_t* bt = item + packed8ItemBytes(B->shape);
+    Shape scratchShape({static_cast<int>(mi8p_scratch_bytes(m, k))});
+    Tensor scratch = g->allocate(scratchShape, Type::int8);
+    check(mi8p_gemm_int8_packed(A->data<float>(), bt, reinterpret_cast<const float*>(tail), reinterpret_cast<const int32_t*>(tail + 4 * n),
+                                reinterpret_cast<const int32_t*>(tail + 8 * n), b, out->val()->data<float>(), m, n, k, scratch->memory,
+                                scratchShape.elements(), g->workspace(), g->workspaceBytes(), g->stream()),
+          "packed multiply");
+  };
+  std::vector<Expr> children = {a, bPacked};
+  if(bias) {
+    MI8_ABORT_IF(!isFloat(bias->value_type()) || static_cast<int>(bias->shape().elements()) != n,
+                 "Bias must be float32 with one value per output column");
+    children.push_back(bias);
+  }
+  return lambda(children, outShape, Type::float32, nodeOp);
+}
+
+Expr dot(Type packType, Expr a, Expr bPacked, const Shape& bShape, bool transA, bool transB, float scale) {
+  return affine(packType, a, bPacked, bShape, nullptr, transA, transB, scale);
+}
+
+}  // namespace variant
 }  // namespace gpu
 
 Expr dot(Expr a, Expr b, bool transA, bool transB, float scale) {
   if(isFloat(a->value_type()) && isIntgemm(b->value_type()))
     return gpu::integer::affineOrDot(a, b, nullptr, transA, transB, scale);
+  if(isFloat(a->value_type()) && isPacked(b->value_type()))
+    return gpu::variant::dot(b->value_type(), a, b, b->shape(), transA, transB, scale);
   MI8_ABORT("GPU only supports float for A and intgemm8 for B on this path; float x float products belong to Marian's cuBLAS path");
 }
 
 Expr affine(Expr a, Expr b, Expr bias, bool transA, bool transB, float scale) {
   if(isFloat(a->value_type()) && isIntgemm(b->value_type()))
     return gpu::integer::affineOrDot(a, b, bias, transA, transB, scale);
+  if(isFloat(a->value_type()) && isPacked(b->value_type()))   // expression_operators.cpp:697-700
+    return gpu::variant::affine(b->value_type(), a, b, b->shape(), bias, transA, transB, scale);
   MI8_ABORT("GPU only supports float for A and intgemm8 for B on this path; float x float products belong to Marian's cuBLAS path");
 }
 

@@ -37,9 +37,12 @@ enum class Type : size_t {
   float32 = 0x0400 + 4,
   intgemm8 = 0x10000 + 1,
   intgemm16 = 0x10000 + 2,
+  packed8avx2 = 0x0800 + 1 + 0x1000,     // FBGEMM int8 items (types.h:313-315); only the avx512 blocking is served
+  packed8avx512 = 0x0800 + 1 + 0x2000,
 };
 inline bool isFloat(Type t) { return (static_cast<size_t>(t) & 0x0400) != 0; }
 inline bool isIntgemm(Type t) { return (static_cast<size_t>(t) & 0x10000) != 0; }
+inline bool isPacked(Type t) { return (static_cast<size_t>(t) & 0x0800) != 0; }
 inline size_t sizeOf(Type t) { return static_cast<size_t>(t) & 0xff; }
 std::string typeName(Type t);
 
@@ -59,7 +62,9 @@ struct Shape {
   bool operator==(const Shape& o) const { return dims == o.dims; }
 };
 
-// bytes a tensor needs: intgemm tensors carry one extra float, the quantisation multiplier (types.cpp:32-37)
+// bytes a tensor needs: intgemm tensors carry one extra float, the quantisation multiplier (types.cpp:32-37);
+// a packed8avx512 tensor of logical shape [K,N] holds the item (K*N + 12*N bytes, rounded up to 256) followed by
+// the row-major Bt[N,K] copy the GPU multiply reads (made when the parameter is created)
 size_t requiredBytes(const Shape& shape, Type type);
 
 struct TensorBase {
@@ -108,6 +113,11 @@ public:
   // (expression_graph_packable.h:160-201); wIsNK: W already is [N,K] (tied embedding used with transB)
   Expr intgemm8Param(const std::string& name, Expr floatParam, bool wIsNK = false);
 
+  // marian-conv --gemm-type packed8avx512 for one parameter (expression_graph_packable.h:49-95): float W[K,N] ->
+  // packed8avx512 node, logical shape [K,N]; packed8Item takes the bytes of an item read from a model file instead
+  Expr packed8Param(const std::string& name, Expr floatParam);
+  Expr packed8Item(const std::string& name, const Shape& shape, const void* hostItem);
+
   Expr add(Expr node);    // appends a computed node to the tape
   void forward();         // allocate -> forward() per node in tape order, then waits for the stream
   void get(Expr e, std::vector<float>& host);       // copies a float32 value back
@@ -142,6 +152,13 @@ namespace integer {
 Expr prepareA(Expr a);
 Expr affineOrDot(Expr a, Expr bQuant, Expr bias, bool transA, bool transB, float scale, bool relu = false);
 }  // namespace integer
+namespace variant {
+// GPU twin of cpu::variant::affine / dot for packed int8 weights (src/tensors/cpu/fbgemm/expanded_gemm.h, reached from
+// expression_operators.cpp:697-700 when isPacked(b)); the arithmetic is that of mjdgemm::gemmInt8Packed
+// (src/tensors/cpu/fbgemm/packed_gemm.cpp:18-31).  `scale` must be 1 and no transposition, as there.
+Expr affine(Type packType, Expr a, Expr bPacked, const Shape& bShape, Expr bias, bool transA, bool transB, float scale);
+Expr dot(Type packType, Expr a, Expr bPacked, const Shape& bShape, bool transA, bool transB, float scale);
+}  // namespace variant
 }  // namespace gpu
 
 }  // namespace marian

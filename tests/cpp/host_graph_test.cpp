@@ -18,6 +18,9 @@ extern "C" {
 float mo_prepare_b(const float* w, int k, int n, int w_is_nk, int8_t* bt);
 int mo_affine(const float* a, int m, int k, const int8_t* bt, float qb, int n, const float* bias, float scale, int relu, float* out,
               int8_t* aq_out, int32_t* acc_out, float* qa_out);
+size_t mo_p8_packed_bytes(int K, int N);
+int mo_p8_prepare_b(const float* w, int K, int N, int8_t* packed);
+int mo_p8_gemm_packed(const float* a, const int8_t* packed, const float* bias, float* c, int M, int N, int K);
 }
 
 using namespace marian;
@@ -113,6 +116,44 @@ int main() {
     float gotQb = 0;
     graph.get(W, gotBt, &gotQb);
     CHECK(gotQb == qb && gotBt == bt);
+  }
+
+  {  // packed8avx512 weights: converted in the graph and uploaded as a ready item; affine and dot dispatch on isPacked(B)
+    ExpressionGraph graph(arena, arenaBytes, ws, wsBytes);
+    const int M = 10, K = 512, N = 96;
+    std::mt19937 rng(9);
+    std::normal_distribution<float> nd(0.f, 1.f);
+    std::vector<float> vA(M * K), vB(K * N), vBias(N);
+    for(auto& v : vA) v = nd(rng) * 2.f;
+    for(auto& v : vB) v = nd(rng) * 0.05f;
+    for(auto& v : vBias) v = nd(rng) * 0.1f;
+    std::vector<int8_t> item(mo_p8_packed_bytes(K, N));
+    CHECK(mo_p8_prepare_b(vB.data(), K, N, item.data()) == 0);
+    std::vector<float> want(M * N), wantDot(M * N);
+    mo_p8_gemm_packed(vA.data(), item.data(), vBias.data(), want.data(), M, N, K);
+    mo_p8_gemm_packed(vA.data(), item.data(), nullptr, wantDot.data(), M, N, K);
+    Expr A = graph.param("A", {2, 5, K}, Type::float32, vA.data());
+    Expr Bf = graph.param("encoder_l1_ffn_W1", {K, N}, Type::float32, vB.data());
+    Expr bias = graph.param("encoder_l1_ffn_b1", {1, N}, Type::float32, vBias.data());
+    Expr W = graph.packed8Param("encoder_l1_ffn_W1", Bf);                       // converted on the device
+    Expr W2 = graph.packed8Item("encoder_l1_ffn_W1", {K, N}, item.data());      // as read from a model file
+    CHECK(W->value_type() == Type::packed8avx512 && isPacked(W->value_type()) && W->shape() == Shape({K, N}));
+    Expr Y = affine(A, W, bias), Y2 = affine(A, W2, bias), D = dot(A, W2);
+    CHECK(Y->shape() == Shape({2, 5, N}));
+    graph.forward();
+    std::vector<float> got, got2, gotDot;
+    graph.get(Y, got);
+    graph.get(Y2, got2);
+    graph.get(D, gotDot);
+    bool same = true;
+    for(int i = 0; i < M * N; ++i)
+      same = same && got[i] == want[i] && got2[i] == want[i] && gotDot[i] == wantDot[i];
+    CHECK(same);
+    CHECK(aborts_with([&] { affine(A, W, bias, false, true); }, "Transposition is currently not supported"));
+    CHECK(aborts_with([&] { gpu::variant::affine(Type::packed8avx2, A, W, W->shape(), bias, false, false, 1.f); }, "Only avx512 packed matrix format"));
+    std::vector<float> v8(4 * 256, 1.f);
+    Expr A8 = graph.param("A8", {4, 256}, Type::float32, v8.data());
+    CHECK(aborts_with([&] { affine(A8, W, nullptr); }, "Inner dimensions"));
   }
 
   {  // error behaviour: the reference's messages for wrongly typed operands
