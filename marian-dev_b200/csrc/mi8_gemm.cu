@@ -777,6 +777,7 @@ struct PairCfg {
 };
 constexpr int smem_bytes_pair() { return PairCfg::kStages * PairCfg::kStageBytes + static_cast<int>(sizeof(Control)) + 1024; }
 
+template <bool kP8>
 __global__ void __launch_bounds__(kThreads, 1)
 mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
   using T = PairCfg;
@@ -889,7 +890,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   } else if(warp == 1) {
     // ------------------------------------------------------------ MMA issuer (rank 0 only; rank 1 owns its TMEM half)
     if(leader) {
-      constexpr uint32_t idesc = make_idesc_i8(T::kTM, 256);
+      constexpr uint32_t idesc = kP8 ? make_idesc_i8_ub(T::kTM, 256) : make_idesc_i8(T::kTM, 256);
       uint32_t it = 0, acc_it = 0;
       bool skip_on = false;
       if(p.skip_a != nullptr) {
@@ -949,7 +950,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     const int epi_tid = threadIdx.x - 64;
     constexpr int kChunks = T::kTM / T::kChunk;
     pdl_wait();
-    const float unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(*p.d_qa, *p.d_qb)), p.scale);
+    const float unquant = kP8 ? 1.0f : __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(*p.d_qa, *p.d_qb)), p.scale);
     uint32_t acc_it = 0;
     const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
     for(int w = pair_id; w < p.total_work && ok; w += n_pairs) {
@@ -971,6 +972,15 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       const int m0 = wi.m_tile * T::kTM;
       const int cols_valid = min(T::kTM, p.M - m0);
       const float bias_n = (p.bias != nullptr && n_ok) ? __ldg(p.bias + n) : 0.0f;
+      float p8_scale_b = 0.0f;
+      int p8_zp_b = 0, p8_off_b = 0;
+      if constexpr(kP8) {
+        if(n_ok) {
+          p8_scale_b = __ldg(p.p8_scale_b + n);
+          p8_zp_b = __ldg(p.p8_zp_b + n);
+          p8_off_b = __ldg(p.p8_off_b + n);
+        }
+      }
       unsigned out_max = 0u;
 #pragma unroll 1
       for(int c = group; c < kChunks; c += 2) {
@@ -980,7 +990,11 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         int32_t v[T::kChunk];
         tmem_ld_chunk<T::kChunk>(t_addr + col0, v);
         tc_wait_ld();
-        if(n_ok)
+        if constexpr(kP8) {
+          if(n_ok)
+            write_back_chunk_p8<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * p.N + n, cols_valid - col0, m0 + col0, p8_scale_b, p8_zp_b,
+                                           p8_off_b, bias_n);
+        } else if(n_ok)
           out_max = write_back_chunk<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * p.N + n, cols_valid - col0, unquant, bias_n, out_max);
       }
       if(p.absmax_out != nullptr) {
@@ -1115,6 +1129,7 @@ int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p
 }
 
 // Launch of the CTA-pair kernel: clusters of two CTAs, as many as can be resident at once.
+template <bool kP8 = false>
 int launch_pair(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, const GemmPlan& plan, cudaStream_t stream) {
   static bool attr_set[64] = {};
   static int max_clusters[64] = {};
@@ -1136,7 +1151,7 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& 
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   if(!attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(mi8_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(mi8_gemm_pair_kernel<kP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if(e != cudaSuccess) {
       set_last_cuda_error(e);
       return MI8_ERR_LAUNCH;
@@ -1145,7 +1160,7 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& 
     cfg.gridDim = dim3(2 * (sm_count() / 2));
     cfg.numAttrs = 1;
     int n = 0;
-    e = cudaOccupancyMaxActiveClusters(&n, mi8_gemm_pair_kernel, &cfg);
+    e = cudaOccupancyMaxActiveClusters(&n, mi8_gemm_pair_kernel<kP8>, &cfg);
     if(e != cudaSuccess || n <= 0) {
       set_last_cuda_error(e);
       cudaGetLastError();
@@ -1167,9 +1182,9 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& 
   const bool timed = kernel_times_on();
   if(timed) {
     cfg.numAttrs = 1;   // no launch overlap while per-kernel times are taken
-    kernel_times_before(reinterpret_cast<const void*>(mi8_gemm_pair_kernel), stream);
+    kernel_times_before(reinterpret_cast<const void*>(mi8_gemm_pair_kernel<kP8>), stream);
   }
-  cudaError_t le = cudaLaunchKernelEx(&cfg, mi8_gemm_pair_kernel, tw, ta, p);
+  cudaError_t le = cudaLaunchKernelEx(&cfg, mi8_gemm_pair_kernel<kP8>, tw, ta, p);
   if(timed)
     kernel_times_after(stream);
   if(le != cudaSuccess) {
@@ -1397,12 +1412,12 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
   }
 }
 
-// The packed8avx512 multiply: the plan of launch_gemm without the CTA-pair kernel; the accumulators and the
+// The packed8avx512 multiply: the plan of launch_gemm (CTA-pair kernel included); the accumulators and the
 // split-K machinery are the same, only the operand signedness and the write-back differ.
 int launch_gemm_p8(const uint8_t* aq, const float* scale_a, const int32_t* zp_a, const int32_t* sum_a, const int8_t* bt,
                    const float* scale_b, const int32_t* zp_b, const int32_t* off_b, int M, int N, int K, const float* bias, int relu,
                    float* c, int32_t* acc_out, void* ws, size_t ws_bytes, cudaStream_t stream, int force_tile_m, int force_splits) {
-  if(M < 0 || N <= 0 || K <= 0 || force_tile_m < 0 || force_splits < 0 || force_tile_m == kPairTileCode)
+  if(M < 0 || N <= 0 || K <= 0 || force_tile_m < 0 || force_splits < 0)
     return MI8_ERR_BAD_ARG;
   if(M == 0)
     return MI8_OK;
@@ -1415,8 +1430,6 @@ int launch_gemm_p8(const uint8_t* aq, const float* scale_a, const int32_t* zp_a,
     return MI8_ERR_MISALIGNED;   // the write-back reads the per-row arrays four rows at a time
   GemmPlan plan;
   int rc = make_gemm_plan(M, N, K, force_tile_m, force_splits, &plan);
-  if(rc == MI8_OK && plan.pair)
-    rc = make_gemm_plan(M, N, K, 256, force_splits, &plan);
   if(rc != MI8_OK)
     return rc;
   if(plan.splits > 1 && (ws == nullptr || ws_bytes < kWsHeaderBytes + plan.partial_bytes))
@@ -1425,7 +1438,7 @@ int launch_gemm_p8(const uint8_t* aq, const float* scale_a, const int32_t* zp_a,
   rc = encode_kmajor_map(&tw, bt, N, K, kTileN);
   if(rc != MI8_OK)
     return rc;
-  rc = encode_kmajor_map(&ta, reinterpret_cast<const int8_t*>(aq), M, K, plan.tile_m);
+  rc = encode_kmajor_map(&ta, reinterpret_cast<const int8_t*>(aq), M, K, plan.pair ? PairCfg::kHalfRows : plan.tile_m);
   if(rc != MI8_OK)
     return rc;
   GemmParams p{};
@@ -1455,6 +1468,8 @@ int launch_gemm_p8(const uint8_t* aq, const float* scale_a, const int32_t* zp_a,
   p.status = device_status_ptr();
   if(p.status == nullptr)
     return MI8_ERR_LAUNCH;
+  if(plan.pair)
+    return launch_pair<true>(tw, ta, p, plan, stream);
   switch(plan.tile_m) {
     case 16: return launch_cfg<16, false, 0, true>(tw, ta, p, plan, stream);
     case 32: return launch_cfg<32, false, 0, true>(tw, ta, p, plan, stream);

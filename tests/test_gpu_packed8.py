@@ -106,8 +106,9 @@ def test_against_checker_on_reference_shapes(cuda_device, chk, M, N, K, relu):
         assert _same_bits(c, ref.gemm(a, item, bias))
 
 
-@pytest.mark.parametrize("tile_m,splits", [(16, 0), (32, 0), (64, 0), (128, 0), (256, 0), (0, 2), (0, 4), (64, 8)])
+@pytest.mark.parametrize("tile_m,splits", [(16, 0), (32, 0), (64, 0), (128, 0), (256, 0), (512, 0), (0, 2), (0, 4), (64, 8)])
 def test_every_tile_width_and_split(cuda_device, chk, tile_m, splits):
+    # tile_m 512 = the two-CTA kernel (tcgen05.mma.cta_group::2 with an unsigned activation operand)
     w, a, bias = _gen.inputs(77, 130, 1024, 288)
     item = chk.prepare_b(w)
     c, acc, _, _ = _gpu_affine(cuda_device, a, item, None, tile_m=tile_m, splits=splits)
