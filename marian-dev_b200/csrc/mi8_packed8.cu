@@ -183,6 +183,76 @@ p8_quantize_rows_kernel(const float* __restrict__ a, int K, uint8_t* __restrict_
   }
 }
 
+__device__ __forceinline__ int p8_q(float x, float inv, float zf) {
+  return __float2int_rn(fminf(fmaxf(__fmaf_rn(x, inv, zf), 0.0f), 255.0f));
+}
+
+// The same for rows of at most 128 * kVec values: one WARP per row, the row held in registers (kVec 16-byte loads per
+// lane, all issued before the first use), statistics by shuffles - one pass over global memory and no block barrier.
+template <int kVec>
+__global__ void __launch_bounds__(kBlock)
+p8_quantize_rows_warp_kernel(const float* __restrict__ a, int M, int K, uint8_t* __restrict__ aq, float* __restrict__ scale_a,
+                             int32_t* __restrict__ zp_a, int32_t* __restrict__ sum_a, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int m = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5);
+  if(m >= M)
+    return;
+  const float4* row = reinterpret_cast<const float4*>(a + static_cast<size_t>(m) * K);
+  const int k4 = K / 4;
+  float4 v[kVec];
+#pragma unroll
+  for(int i = 0; i < kVec; ++i) {
+    const int idx = lane + 32 * i;
+    v[i] = idx < k4 ? __ldg(row + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float mn = 3.402823466e+38f, mx = -3.402823466e+38f;
+  unsigned bits = 0u;
+#pragma unroll
+  for(int i = 0; i < kVec; ++i) {
+    if(lane + 32 * i < k4) {
+      mn = fminf(fminf(mn, v[i].x), fminf(v[i].y, fminf(v[i].z, v[i].w)));
+      mx = fmaxf(fmaxf(mx, v[i].x), fmaxf(v[i].y, fmaxf(v[i].z, v[i].w)));
+      bits = max(max(bits, __float_as_uint(v[i].x) & 0x7fffffffu), max(__float_as_uint(v[i].y) & 0x7fffffffu,
+                 max(__float_as_uint(v[i].z) & 0x7fffffffu, __float_as_uint(v[i].w) & 0x7fffffffu)));
+    }
+  }
+#pragma unroll
+  for(int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if(bits >= 0x7f800000u)
+    atomicMax(status, static_cast<int>(kDevNonFinite));
+  if(mn == mx) {
+    mn = fminf(mn, 0.0f);
+    mx = fmaxf(mx, 0.0f);
+  }
+  float s = __fdiv_rn(__fsub_rn(mx, mn), 255.0f);
+  if(mn == mx)
+    s = 1.0f;
+  const int z = __float2int_rz(__fsub_rn(255.0f, __fdiv_rn(mx, s)));
+  const float inv = __fdiv_rn(1.0f, s), zf = __int2float_rn(z);
+  int sum = 0;
+  uint32_t* out = reinterpret_cast<uint32_t*>(aq + static_cast<size_t>(m) * K);
+#pragma unroll
+  for(int i = 0; i < kVec; ++i) {
+    const int idx = lane + 32 * i;
+    if(idx < k4) {
+      const int q0 = p8_q(v[i].x, inv, zf), q1 = p8_q(v[i].y, inv, zf), q2 = p8_q(v[i].z, inv, zf), q3 = p8_q(v[i].w, inv, zf);
+      sum += q0 + q1 + q2 + q3;
+      out[idx] = static_cast<uint32_t>(q0) | (static_cast<uint32_t>(q1) << 8) | (static_cast<uint32_t>(q2) << 16) | (static_cast<uint32_t>(q3) << 24);
+    }
+  }
+  sum = __reduce_add_sync(0xffffffffu, sum);
+  if(lane == 0) {
+    scale_a[m] = s;
+    zp_a[m] = z;
+    sum_a[m] = sum;
+  }
+}
+
 }  // namespace
 
 int launch_p8_unpack_bt(const int8_t* packed, int K, int N, int8_t* bt, cudaStream_t stream) {
@@ -235,7 +305,16 @@ int launch_p8_quantize_rows(const float* a, int M, int K, uint8_t* aq, float* sc
   int* status = device_status_ptr();
   if(status == nullptr)
     return MI8_ERR_LAUNCH;
-  cudaError_t e = launch_kernel(p8_quantize_rows_kernel, dim3(M), dim3(kBlock), 0, stream, a, K, aq, scale_a, zp_a, sum_a, status);
+  const int warp_grid = (M + kBlock / 32 - 1) / (kBlock / 32);
+  cudaError_t e;
+  if(K <= 512)
+    e = launch_kernel(p8_quantize_rows_warp_kernel<4>, dim3(warp_grid), dim3(kBlock), 0, stream, a, M, K, aq, scale_a, zp_a, sum_a, status);
+  else if(K <= 1024)
+    e = launch_kernel(p8_quantize_rows_warp_kernel<8>, dim3(warp_grid), dim3(kBlock), 0, stream, a, M, K, aq, scale_a, zp_a, sum_a, status);
+  else if(K <= 2048)
+    e = launch_kernel(p8_quantize_rows_warp_kernel<16>, dim3(warp_grid), dim3(kBlock), 0, stream, a, M, K, aq, scale_a, zp_a, sum_a, status);
+  else
+    e = launch_kernel(p8_quantize_rows_kernel, dim3(M), dim3(kBlock), 0, stream, a, K, aq, scale_a, zp_a, sum_a, status);
   if(e != cudaSuccess) {
     set_last_cuda_error(e);
     return MI8_ERR_LAUNCH;

@@ -81,3 +81,12 @@ def sharded_affine(a_local: torch.Tensor, b, bias=None, scale: float = 1.0, relu
     global_abs_max(amax, group)
     aq = ops.quantize_with_absmax(a_local, amax)
     return ops.multiply(aq, b, bias, scale, relu, out_dtype=out_dtype)
+
+
+def sharded_packed8_affine(a_local: torch.Tensor, w, bias=None) -> torch.Tensor:
+    """The packed8avx512 affine on this rank's rows of A.  That scheme quantises every ROW of A with its own scale
+    and zero point (src/tensors/cpu/mjdgemm/mjdgemm_avx512.cpp:195-228), so rows shard with no exchange at all:
+    this rank's rows of C equal the same rows of the unsharded product bit for bit.  `w` is a packed8.Packed8Weight
+    replicated on every rank."""
+    from . import packed8
+    return packed8.gemmInt8Packed(a_local, w, bias)

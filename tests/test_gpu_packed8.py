@@ -165,3 +165,20 @@ def test_weight_conversion_bit_exact_and_container_round_trip(cuda_device, chk, 
     assert _same_bits(c.cpu().numpy(), chk.affine(a, want, None))
     L = __import__("marian_dev_b200.binding", fromlist=["lib"]).lib()
     assert L.mi8p_prepare_b_f32(got.item.data_ptr(), 100, 32, got.item.data_ptr(), None) == 3
+
+
+def test_row_shards_need_no_exchange(cuda_device, chk):
+    from marian_dev_b200 import parallel
+    p8 = _p8()
+    w, a, bias = _gen.inputs(123, 301, 512, 256)
+    item = chk.prepare_b(w)
+    wt = p8.Packed8Weight(item.packed, 512, 256, device=cuda_device)
+    bt = torch.from_numpy(bias).to(cuda_device)
+    whole = p8.gemmInt8Packed(torch.from_numpy(a).to(cuda_device), wt, bt).cpu().numpy()
+    for world in (2, 3, 8):
+        parts = []
+        for rank in range(world):
+            r0, r1 = parallel.shard_rows(301, rank, world)
+            parts.append(parallel.sharded_packed8_affine(torch.from_numpy(a[r0:r1]).to(cuda_device), wt, bt).cpu().numpy())
+        assert _same_bits(np.concatenate(parts), whole)
+    _healthy()
