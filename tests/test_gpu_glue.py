@@ -65,7 +65,9 @@ def test_add_layernorm_bit_exact(cuda_device, oracle, rows, dim, with_resid):
 @pytest.mark.parametrize("mode,rows,batch,length,heads,dh", [
     (0, 12, 3, 1, 2, 32), (0, 12, 3, 9, 2, 32), (0, 64, 16, 45, 16, 64), (0, 8, 2, 70, 8, 64),
     (1, 12, 3, 7, 2, 32), (1, 64, 16, 33, 16, 64), (2, 3 * 11, 3, 11, 4, 64), (2, 2 * 40, 2, 40, 8, 32),
-    (2, 2 * 136, 2, 136, 16, 64), (2, 5 * 3, 5, 3, 2, 32), (2, 1, 1, 1, 2, 64)])
+    (2, 2 * 136, 2, 136, 16, 64), (2, 5 * 3, 5, 3, 2, 32), (2, 1, 1, 1, 2, 64),
+    # cross-attention with several beams per sentence, at the decode benchmark's size among them
+    (1, 8 * 5, 5, 40, 8, 32), (1, 2 * 7, 7, 130, 16, 64), (1, 4 * 128, 128, 36, 16, 64), (1, 3 * 9, 9, 1, 4, 64)])
 def test_attention_bit_exact(cuda_device, oracle, mode, rows, batch, length, heads, dh):
     L, check = _lib()
     rng = np.random.default_rng(rows * length + mode)
