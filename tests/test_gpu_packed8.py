@@ -73,7 +73,6 @@ def test_hashed_reference_outputs(cuda_device, chk):
 
 
 def test_unpack_and_row_quantisation_bit_exact(cuda_device, chk):
-    rng = np.random.default_rng(11)
     w, a, bias = _gen.inputs(11, 37, 768, 160)
     a[5] = 0.0
     a[6] = -2.5
@@ -85,7 +84,6 @@ def test_unpack_and_row_quantisation_bit_exact(cuda_device, chk):
     oc, oacc = chk.affine(a, item, bias, want_acc=True)
     assert np.array_equal(acc, oacc)
     assert _same_bits(c, oc)
-    del rng
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 512, 512), (4, 1024, 1024), (57, 4096, 1024), (200, 1024, 4096), (300, 3072, 1024),
@@ -163,8 +161,8 @@ def test_weight_conversion_bit_exact_and_container_round_trip(cuda_device, chk, 
     c = p8.gemmInt8Packed(torch.from_numpy(a).to(cuda_device), wt)
     torch.cuda.synchronize()
     assert _same_bits(c.cpu().numpy(), chk.affine(a, want, None))
-    L = __import__("marian_dev_b200.binding", fromlist=["lib"]).lib()
-    assert L.mi8p_prepare_b_f32(got.item.data_ptr(), 100, 32, got.item.data_ptr(), None) == 3
+    from marian_dev_b200.binding import lib
+    assert lib().mi8p_prepare_b_f32(got.item.data_ptr(), 100, 32, got.item.data_ptr(), None) == 3
 
 
 def test_row_shards_need_no_exchange(cuda_device, chk):
