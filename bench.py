@@ -5,9 +5,15 @@
 
 One "step" is the decode of one mini-batch (128 synthetic sentences, beam 4) on one GPU: encoder,
 then decoder steps until every hypothesis ended or 1.5 x the source width is reached, with every
-weight multiplication on the int8 engine.  With N GPUs every rank holds a full model replica and
-decodes its own K mini-batches (mini-batches are dealt round-robin, as the reference's translator
-does); the only collective is the gather of the output token matrix.  Rank 0 prints one JSON line.
+weight multiplication on the int8 engine.  The workload's corpus is fixed (8192 sentences = 64
+length-sorted mini-batches, whatever N is); the timed mini-batches are the first N x K of one fixed
+shuffled order of them, so a run times a length-representative sample and `--steps 64` at N = 1 times
+the whole corpus.  With N GPUs every rank holds a full model replica and decodes K of those
+mini-batches (dealt so that the ranks get equally long work; the reference's translator hands the
+next mini-batch to the next free device); the only collective is the gather of the output token
+matrix.  Every decoded mini-batch is hashed and compared with the digest committed under
+tests/golden/ (which the GPU tests tie to the CPU checker): a run whose output differs prints no
+number.  Rank 0 prints one JSON line.
 
 `value` is measured with the mini-batch's token ids and mask already resident in HBM; `e2e` is the
 same decode called with host buffers (pinned host -> device copy of ids/mask inside the timed
@@ -40,13 +46,13 @@ BEAM = 4
 # The benchmark line is the "big" workload; the others are the remaining named decode configurations,
 # runnable with --model for parity-sized measurements (their lines carry their own workload string).
 WORKLOADS = {
-    "big": dict(desc=WORKLOAD, mini_batch=128, beam=4, lengths=dict(length_dist="normal", lo=4, hi=128, mean=30.0, std=12.0)),
+    "big": dict(desc=WORKLOAD, mini_batch=128, beam=4, sentences=8192, lengths=dict(length_dist="normal", lo=4, hi=128, mean=30.0, std=12.0)),
     "base": dict(desc="transformer-base decode (6+6 layers, d=512, ffn=2048, 8 heads, tied 32000 vocab, all affines int8), beam 4, "
                       "mini-batch 64, lengths U[8,64], max length 1.5x source",
-                 mini_batch=64, beam=4, lengths=dict(length_dist="uniform", lo=8, hi=64)),
+                 mini_batch=64, beam=4, sentences=2048, lengths=dict(length_dist="uniform", lo=8, hi=64)),
     "student": dict(desc="student decode (12 encoder layers d=256 ffn=1536 8 heads, 2-layer SSRU decoder, 32000 vocab, all affines int8), "
                          "greedy, lengths U[5,40], max length 1.5x source",
-                    mini_batch=16, beam=1, lengths=dict(length_dist="uniform", lo=5, hi=40)),
+                    mini_batch=16, beam=1, sentences=1024, lengths=dict(length_dist="uniform", lo=5, hi=40)),
 }
 
 
@@ -54,6 +60,7 @@ def workload(args):
     w = dict(WORKLOADS.get(args.model, WORKLOADS["big"]))
     if args.model not in WORKLOADS:
         w["desc"] = f"{args.model} (debug workload)"
+        w["sentences"] = 8 * w["mini_batch"]
     if args.mini_batch:
         w["mini_batch"] = args.mini_batch
     if args.beam:
@@ -75,15 +82,69 @@ def parse_args():
     ap.add_argument("--cpu-sentences", type=int, default=16, help="sentences in the CPU-baseline sample")
     ap.add_argument("--affine", default=None, help="M,K,N: time one int8 affine (abs-max + quantise + GEMM with bias and ReLU) instead of the decode")
     ap.add_argument("--sweep", action="store_true", help="time the affine shape sweep M x K x N instead of the decode")
+    ap.add_argument("--write-digests", default=None, metavar="PATH",
+                    help="decode the whole corpus of the big and base workloads and write the per-mini-batch output digests (the "
+                         "file committed as tests/golden/decode_digests.json) instead of timing")
+    ap.add_argument("--trace", default=None, metavar="PATH",
+                    help="decode one mini-batch with the in-situ kernel timeline on and write its per-kernel summary to PATH")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="step-driver tuning switch (fuse_weights, quant_in_gemm, fused_output_max_rows, side_stream, attention_unroll)")
+    ap.add_argument("--strong", action="store_true",
+                    help="strong scaling: the whole fixed corpus, mini-batches taken from a shared counter by whichever rank is free")
+    ap.add_argument("--glue", default=None, metavar="KERNEL",
+                    help="time one glue kernel at the benchmark's decode shapes (attention1_self, attention1_cross, quantize_slot, "
+                         "add_layernorm, lse_topk), the form the ncu captures use")
     ap.add_argument("--packed8", action="store_true",
                     help="time the packed8avx512 affine on the weight shapes the reference's mjdgemm instantiates, the reference's own CPU code beside it")
     return ap.parse_args()
 
 
-def build_corpus(model_mod, cfg, n_batches, wl):
-    n = n_batches * wl["mini_batch"]
-    corpus = model_mod.synthetic_corpus(n, cfg.vocab, seed=1, **wl["lengths"])
+def corpus_batches(model_mod, cfg, wl):
+    """The workload's whole corpus as length-sorted mini-batches (maxi-batch style): the same list for every N."""
+    if wl.get("mini_batch") not in (None, 0) and wl.get("sentences", 0) % wl["mini_batch"] != 0:
+        wl = dict(wl, sentences=(wl["sentences"] // wl["mini_batch"] + 1) * wl["mini_batch"])
+    corpus = model_mod.synthetic_corpus(wl["sentences"], cfg.vocab, seed=1, **wl["lengths"])
     return model_mod.make_batches(corpus, wl["mini_batch"])
+
+
+def batch_order(n_batches):
+    """One fixed shuffled order of the corpus' mini-batches; the timed set is a prefix of it (cyclic when N x K exceeds it)."""
+    import numpy as np
+    return [int(i) for i in np.random.default_rng(7).permutation(n_batches)]
+
+
+def deal_batches(picked, widths, rank, world):
+    """The reference gives the next mini-batch to the next free device (src/translator/translator.h:154-167); for a
+    pre-dealt list the equivalent is equally long work per rank: widest first, dealt in snake order."""
+    ranked = sorted(picked, key=lambda b: -widths[b])
+    mine = []
+    for i, b in enumerate(ranked):
+        group, pos = divmod(i, world)
+        if (pos if group % 2 == 0 else world - 1 - pos) == rank:
+            mine.append(b)
+    return mine
+
+
+def tokens_digest(sent_ids, results):
+    """sha256 over (sentence id, length, tokens) of one mini-batch in sentence-id order."""
+    import hashlib
+    import numpy as np
+    h = hashlib.sha256()
+    for sid, toks in sorted(zip((int(x) for x in sent_ids), (list(t) for t in results))):
+        h.update(np.asarray([sid, len(toks)] + toks, dtype=np.int32).tobytes())
+    return h.hexdigest()
+
+
+def load_digests(name):
+    try:
+        return json.load(open(os.path.join(ROOT, "tests", "golden", "decode_digests.json"))).get(name, {}).get("batches", {})
+    except OSError:
+        return {}
+
+
+# DRAM read + write bytes of ONE launch of the decode's dominant GEMM shape (dram__bytes_read.sum + dram__bytes_write.sum),
+# from the ncu captures summarised in profiles/decode_gemm_ncu_b200.md (key: M, N, K).
+NCU_DRAM_BYTES_PER_LAUNCH = {}
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -157,17 +218,22 @@ class GemmTimer:
         buf = (Mi8GemmRecord * self.capacity)()
         n = ctypes.c_int(0)
         check(lib().mi8_profile_end(buf, self.capacity, ctypes.byref(n)))
-        self.records = [(r.M, r.N, r.K, r.out_bytes, r.us) for r in buf[:n.value]]
+        self.records = [(r.M, r.N, r.K, r.out_bytes, r.us, r.rows_computed) for r in buf[:n.value]]
 
     def summary(self):
-        """Aggregate per shape class."""
+        """Aggregate per shape class.  Bytes and operations are those of the rows a launch really computed
+        (`rows_computed`, written by the kernel: launches over stored keys/values skip what is unchanged)."""
         total = {"launches": 0, "us": 0.0, "bytes": 0.0, "ops": 0.0}
         classes = {}
-        for (m, n, k, ob, us) in self.records:
-            by = m * k + n * k + 4 * n + ob * m * n + 8          # int8 A in, weights, bias, C out, two multipliers
-            op = 2.0 * m * n * k
-            key = ("history K/V re-projection (M = rows x steps)" if m > 1024 and n == k else f"N={n},K={k}")
-            c = classes.setdefault(key, {"launches": 0, "us": 0.0, "bytes": 0.0, "ops": 0.0})
+        for (m, n, k, ob, us, rows) in self.records:
+            if rows > 0:
+                by = rows * k + n * k + 4 * n + ob * rows * n + 8          # int8 A in, weights, bias, C out, two multipliers
+                op = 2.0 * rows * n * k
+                key = f"M={m if m <= 512 else '>512'},N={n},K={k}"
+            else:
+                by, op = 0.0, 0.0
+                key = f"N={n},K={k}: earlier history slabs, nothing to recompute (launch exits)"
+            c = classes.setdefault(key, {"launches": 0, "us": 0.0, "bytes": 0.0, "ops": 0.0, "m": m, "n": n, "k": k})
             for d in (c, total):
                 d["launches"] += 1
                 d["us"] += us
@@ -177,12 +243,16 @@ class GemmTimer:
 
 
 # ----------------------------------------------------------------------------- our arm
-def run_ours(args):
-    import numpy as np
+def _apply_options(stepper, args):
+    for item in args.option:
+        name, _, value = item.partition("=")
+        stepper.set_option(name.strip(), int(value))
+
+
+def _setup(args):
     import torch
     import torch.distributed as dist
-    from marian_dev_b200 import decoder, model, ops, parallel
-
+    from marian_dev_b200 import decoder, model
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -190,18 +260,35 @@ def run_ours(args):
         raise RuntimeError("bench.py needs a CUDA device: the int8 engine has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
     cfg = model.CONFIGS[args.model]
     params = model.random_init(cfg, seed=0)
     net = decoder.Int8Transformer(cfg, params, dev, output_int8=True)
     del params
-    per_rank = args.warmup + args.steps                          # both timed legs decode the same mini-batches
     wl = workload(args)
-    batches = build_corpus(model, cfg, per_rank * world, wl)
-    mine = parallel.shard_batches(batches, rank, world, snake=True)[:per_rank]   # length-sorted list: snake order balances the ranks
+    batches = corpus_batches(model, cfg, wl)
     stepper = decoder.NativeStepper(net, max_batch=wl["mini_batch"], beam=wl["beam"], max_src=136, max_steps=208)
+    _apply_options(stepper, args)
     search = decoder.BeamSearch(net, beam=wl["beam"], max_length_factor=1.5, normalize=1.0, native=stepper)
+    return world, rank, local_rank, dev, cfg, wl, batches, stepper, search
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from marian_dev_b200 import ops, parallel
+
+    world, rank, local_rank, dev, cfg, wl, batches, stepper, search = _setup(args)
+    widths = [b[1].shape[1] for b in batches]
+    order = batch_order(len(batches))
+    need = world * args.steps
+    picked = [order[i % len(order)] for i in range(need)]
+    mine = deal_batches(picked, widths, rank, world)[:args.steps]
+    warm = [order[(need + i) % len(order)] for i in range(args.warmup)]          # other mini-batches than the timed ones
+    golden = load_digests(args.model) if not (args.mini_batch or args.beam) else {}
+    max_len = int(np.ceil(1.5 * max(widths))) + 2
 
     def barrier():
         torch.cuda.synchronize()
@@ -212,20 +299,22 @@ def run_ours(args):
     def gather_outputs(collected):
         """The path's one collective, once per timed leg (the reference's OutputCollector also runs beside the
         decoding, not in lock-step with it): every rank contributes its {sentence id: tokens}; all receive the union."""
-        return parallel.gather_outputs(collected, max_len=192, device=dev)   # 192 = 1.5 x the longest source
+        return parallel.gather_outputs(collected, max_len=max_len, device=dev)
 
     # warm-up
-    for b in mine[:args.warmup]:
-        search.search(b[1], b[2])
+    for b in warm:
+        search.search(batches[b][1], batches[b][2])
     torch.cuda.synchronize()
 
     # ---- leg 1: inputs resident in HBM ------------------------------------------------------
-    leg1 = mine[args.warmup:args.warmup + args.steps]
+    leg1 = [batches[b] for b in mine]
     resident = [(sid, torch.from_numpy(ids.astype(np.int64)).to(dev), torch.from_numpy(mask).to(dev)) for sid, ids, mask in leg1]
     sampler = ClockSampler(local_rank)
     launches_before = ops.launch_count()          # warm-up launches (lets a profiler skip them)
     ops.reset_launch_count()
+    stepper.search_stats(reset=True)
     tokens = 0
+    digests1 = []
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -235,12 +324,25 @@ def run_ours(args):
         res = search.search_device(ids_t, mask_t)
         collected.update({int(i): toks for i, (toks, _s) in zip(sid, res)})
         tokens += sum(len(t) for t, _ in res)
+        digests1.append(tokens_digest(sid, [t for t, _ in res]))
     gather_outputs(collected)
     e1.record()
     barrier()
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1)
     launches = ops.launch_count()
+    host = stepper.search_stats(reset=True)
+
+    # the output of the timed leg against the committed digests (tests/golden/decode_digests.json)
+    checked = mismatched = 0
+    for b, dg in zip(mine, digests1):
+        want = golden.get(str(b))
+        if want is not None:
+            checked += 1
+            mismatched += int(want != dg)
+    if mismatched:
+        raise RuntimeError(f"rank {rank}: the decoded tokens of {mismatched} of {checked} timed mini-batches differ from "
+                           "tests/golden/decode_digests.json: no number is reported for a wrong output")
 
     # ---- the same region once more with every GEMM launch bracketed by CUDA events (the events sit
     # between kernels and so cost some overlap: this pass attributes time, the pass above is the value)
@@ -261,7 +363,7 @@ def run_ours(args):
         import re
         from marian_dev_b200.binding import Mi8KernelTime, check, lib
         check(lib().mi8_kernel_times_begin())
-        for sid, ids_t, mask_t in resident[:max(1, len(resident) // 2)]:
+        for sid, ids_t, mask_t in resident[:max(1, min(3, len(resident) // 2))]:
             search.search_device(ids_t, mask_t)
         buf = (Mi8KernelTime * 64)()
         n = ctypes.c_int(0)
@@ -283,10 +385,10 @@ def run_ours(args):
     barrier()
 
     # ---- leg 2: end to end through the public call with host buffers --------------------------
-    leg2 = leg1
-    pinned = [(sid, torch.from_numpy(ids.astype(np.int64)).pin_memory(), torch.from_numpy(mask).pin_memory()) for sid, ids, mask in leg2]
+    pinned = [(sid, torch.from_numpy(ids.astype(np.int64)).pin_memory(), torch.from_numpy(mask).pin_memory()) for sid, ids, mask in leg1]
     search.h2d_bytes = search.d2h_bytes = 0
     tokens2 = 0
+    digests2 = []
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
@@ -295,23 +397,30 @@ def run_ours(args):
         res = search.search(ids_p, mask_p)
         collected.update({int(i): toks for i, (toks, _s) in zip(sid, res)})
         tokens2 += sum(len(t) for t, _ in res)
+        digests2.append(tokens_digest(sid, [t for t, _ in res]))
     gather_outputs(collected)
     f1.record()
     barrier()
     ms2 = f0.elapsed_time(f1)
+    if digests2 != digests1:
+        raise RuntimeError(f"rank {rank}: the end-to-end leg decoded different tokens than the device-resident leg")
     h2d, d2h = search.h2d_bytes / max(1, len(pinned)), search.d2h_bytes / max(1, len(pinned))
     status = ops.poll_status()
     int8_peak = round(ops.measure_int8_peak(), 1) if rank == 0 else None   # after the timed legs: it must not disturb them
 
+    per_rank = None
     if world > 1:
-        t = torch.tensor([ms, ms2], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms2 = float(t[0]), float(t[1])
-        c = torch.tensor([tokens, tokens2, launches], device=dev, dtype=torch.float64)
+        mine_ms = torch.tensor([ms, ms2], device=dev, dtype=torch.float64)
+        every = [torch.zeros_like(mine_ms) for _ in range(world)]
+        dist.all_gather(every, mine_ms)
+        per_rank = [round(float(x[0]), 2) for x in every]
+        ms, ms2 = max(float(x[0]) for x in every), max(float(x[1]) for x in every)
+        c = torch.tensor([tokens, tokens2, launches, checked], device=dev, dtype=torch.float64)
         dist.all_reduce(c, op=dist.ReduceOp.SUM)
-        tokens, tokens2, launches = int(c[0]), int(c[1]), int(c[2])
+        tokens, tokens2, launches, checked = int(c[0]), int(c[1]), int(c[2]), int(c[3])
 
     if rank == 0:
+        import hashlib
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -319,23 +428,31 @@ def run_ours(args):
             pass
         hbm_peak = peaks.get("hbm_gbs", 6650.0)
         peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
-        achieved = gemm_total["bytes"] / max(gemm_total["us"], 1e-9) / 1e3          # GB/s
+
+        def rates(v):
+            return {"launches": v["launches"], "us_total": round(v["us"], 1), "avg_us": round(v["us"] / max(1, v["launches"]), 2),
+                    "GBps": round(v["bytes"] / max(v["us"], 1e-9) / 1e3, 1), "TOPS": round(v["ops"] / max(v["us"], 1e-9) / 1e6, 1)}
+
+        by_shape = {k: rates(v) for k, v in sorted(gemm_classes.items(), key=lambda kv: -kv[1]["us"])}
+        dom_key, dom = max(gemm_classes.items(), key=lambda kv: kv[1]["us"])       # the shape class the GEMM kernel spends most time in
+        dom_rate = rates(dom)
+        all_rate = rates(gemm_total)
         roofline = {
-            "kernel": "mi8_gemm_kernel (all launches of the timed region)",
-            "bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
-            "frac": round(achieved / hbm_peak, 4), "peak_source": peak_src,
-            # DRAM read + write of one output-layer launch (M=512, K=1024, N=32000; algorithmic 98.9 MB, part of C stays in L2),
-            # measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on one launch of that shape
-            "traffic": 44.7e6, "traffic_unit": "bytes per launch of the 512x1024x32000 shape",
-            "launches": gemm_total["launches"], "avg_launch_us": round(gemm_total["us"] / max(1, gemm_total["launches"]), 2),
-            "tops": round(gemm_total["ops"] / max(gemm_total["us"], 1e-9) / 1e6, 1),
+            "kernel": f"mi8_gemm_kernel, the decode's dominant shape class {dom_key} ({dom['launches']} launches, "
+                      f"{round(100.0 * dom['us'] / max(gemm_total['us'], 1e-9), 1)} % of the GEMM time)",
+            "bound": "hbm", "achieved": dom_rate["GBps"], "peak": hbm_peak, "unit": "GB/s",
+            "frac": round(dom_rate["GBps"] / hbm_peak, 4), "peak_source": peak_src,
+            "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((dom["m"], dom["n"], dom["k"])),
+            "avg_launch_us": dom_rate["avg_us"], "tops": dom_rate["TOPS"],
+            "timing": "CUDA events around every GEMM launch of a repeat of the timed region (launch overlap off for that pass); "
+                      "bytes and operations count the rows each launch really computed",
+            "all_gemm_launches": dict(all_rate, frac=round(all_rate["GBps"] / hbm_peak, 4)),
             "int8_mma_peak_tops": int8_peak,   # a loop of the kernel's MMAs alone, measured on this GPU right after the timed legs
             "gemm_share_of_step_time": round(gemm_total["us"] / 1e3 / max(ms_profiled, 1e-9), 3),
             "profiled_pass_ms": round(ms_profiled, 2),
-            "by_shape": {k: {"launches": v["launches"], "us_total": round(v["us"], 1),
-                             "GBps": round(v["bytes"] / max(v["us"], 1e-9) / 1e3, 1),
-                             "TOPS": round(v["ops"] / max(v["us"], 1e-9) / 1e6, 1)} for k, v in sorted(gemm_classes.items(), key=lambda kv: -kv[1]["us"])},
+            "by_shape": by_shape,
         }
+        steps_done = max(1, host["steps"])
         cpu = cpu_baseline(args, cfg_name=args.model) if world == 1 else None
         line = {
             "metric": METRIC, "value": round(tokens / (ms / 1e3), 1), "unit": UNIT, "n_gpus": world,
@@ -343,19 +460,308 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 (s8 x s8 -> s32), fp32 epilogue",
             "data": "synthetic (random-init weights, uniform token ids, seeded)",
             "config": {"workload": wl["desc"], "mini_batch": wl["mini_batch"], "beam": wl["beam"],
+                       "corpus": f"{wl['sentences']} sentences = {len(batches)} length-sorted mini-batches; timed: the first {need} of a fixed "
+                                 f"shuffled order (widths {sorted(widths[b] for b in picked)[0]}..{sorted(widths[b] for b in picked)[-1]}, "
+                                 f"mean {round(sum(widths[b] for b in picked) / len(picked), 1)}; corpus mean {round(sum(widths) / len(widths), 1)}), "
+                                 "warm-up on other mini-batches",
                        "tokens_counted": "best hypothesis per sentence, EOS included", "parallelism": f"replicas x{world}",
+                       "options": args.option,
                        "l2": "not flushed: one decode step streams ~0.2 GB of int8 weights plus fp32 logits and history, more than the 126 MB L2"},
             "e2e": {"value": round(tokens2 / (ms2 / 1e3), 1), "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches), "gpu_launches_before_timed_region": int(launches_before), "clocks": clocks,
-            # per kernel: launches / device time / share, CUDA events around every launch of half the timed mini-batches;
+            "outputs": {"digest": hashlib.sha256("".join(digests1).encode()).hexdigest()[:16], "mini_batches_checked_against_golden": checked,
+                        "mismatches": 0, "e2e_leg_identical": True},
+            # where the host thread of rank 0 spent the timed leg, per decoder step: issuing launches, waiting for the device
+            # (the step's one synchronisation), beam bookkeeping
+            "host_per_decoder_step_us": {"issue": round(1e6 * host["issue_s"] / steps_done, 1), "wait_for_device": round(1e6 * host["wait_s"] / steps_done, 1),
+                                         "bookkeeping": round(1e6 * host["host_s"] / steps_done, 1), "decoder_steps": host["steps"],
+                                         "launches_per_decoder_step": round(launches / world / steps_done, 1)},
+            # per kernel: launches / device time / share, CUDA events around every launch of a few of the timed mini-batches;
             # launches serialise while timed, so every launch carries its ~4 us launch latency: compare shares
             "kernels": kernel_table, "roofline": roofline, "device_status": status,
         }
+        if per_rank is not None:
+            line["per_rank_ms"] = per_rank
+            line["rank_spread"] = round(max(per_rank) / max(min(per_rank), 1e-9), 4)
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_write_digests(args):
+    """Decodes the whole corpus of the big and base workloads on cuda:0 and writes the digest of every mini-batch."""
+    import numpy as np
+    import torch
+    out = {"made_by": "python bench.py --write-digests PATH (on a B200); tests/test_gpu_decode_bench_config.py compares entries with the CPU checker",
+           "digest": "sha256 over int32 (sentence id, length, tokens...) of the mini-batch's sentences in sentence-id order"}
+    for name in ("big", "base"):
+        a = argparse.Namespace(**vars(args))
+        a.model, a.mini_batch, a.beam = name, 0, 0
+        world, rank, local_rank, dev, cfg, wl, batches, stepper, search = _setup(a)
+        d = {}
+        tokens = 0
+        for i, (sid, ids, mask) in enumerate(batches):
+            res = search.search(ids, mask)
+            d[str(i)] = tokens_digest(sid, [t for t, _ in res])
+            tokens += sum(len(t) for t, _ in res)
+        out[name] = {"sentences": wl["sentences"], "mini_batch": wl["mini_batch"], "beam": wl["beam"], "tokens": tokens, "batches": d}
+        del stepper, search
+        torch.cuda.empty_cache()
+    with open(args.write_digests, "w") as f:
+        json.dump(out, f, indent=1)
+    print(json.dumps({"wrote": args.write_digests, "big_tokens": out["big"]["tokens"], "base_tokens": out["base"]["tokens"]}), flush=True)
+
+
+TRACE_KERNELS = {1: "mi8_gemm_kernel", 2: "mi8_gemm_pair_kernel", 3: "quantize_slot_kernel", 4: "quantize_dual_kernel", 5: "add_layernorm_kernel",
+                 6: "attention1_kernel", 7: "attention_enc_kernel", 8: "lse_topk_kernel", 9: "lse_merge_kernel", 10: "nbest_merge_kernel",
+                 11: "embed_kernel", 12: "ancestors_update_kernel", 13: "history_commit_kernel", 14: "gather_rows_kernel", 15: "ssru_cell_kernel",
+                 16: "mi8_absmax_kernel", 17: "mi8_quantize_kernel", 18: "mi8_gemm_kernel (output layer, reducing write-back)",
+                 19: "mi8_gemm_kernel (quantising its activation)"}
+
+
+def run_trace(args):
+    """One mini-batch (of median width) decoded with the in-situ timeline on: every kernel stamps the GPU's nanosecond timer at
+    its entry, when its wait for the preceding kernel returns and when its block 0 ends, with launch overlap left on.  Written
+    to PATH: per kernel (and GEMM shape) the launches, the time from `wait returned` to `end` (the kernel's own work), the time
+    from the previous kernel's end to this kernel's `wait returned` (the hand-over gap) and their shares of the decoder steps."""
+    import ctypes
+    import numpy as np
+    import torch
+    from marian_dev_b200.binding import check, lib
+    world, rank, local_rank, dev, cfg, wl, batches, stepper, search = _setup(args)
+    widths = [b[1].shape[1] for b in batches]
+    b = sorted(range(len(batches)), key=lambda i: widths[i])[len(batches) // 2]
+    sid, ids, mask = batches[b]
+    for _ in range(2):
+        search.search(ids, mask)
+    torch.cuda.synchronize()
+    cap = 400000
+    buf = torch.zeros(2 + 2 * cap, dtype=torch.int64, device=dev)
+    check(lib().mi8_trace_begin(buf.data_ptr(), cap))
+    stepper.search_stats(reset=True)
+    t0 = time.perf_counter()
+    res = search.search(ids, mask)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    check(lib().mi8_trace_end())
+    host = stepper.search_stats(reset=True)
+    raw = buf.cpu().numpy()
+    n = int(min(raw[0], cap))
+    t = raw[2:2 + 2 * n:2].astype(np.int64)
+    tag = raw[3:3 + 2 * n:2].astype(np.uint64)
+    phase = (tag & np.uint64(0xff)).astype(np.int64)
+    kern = ((tag >> np.uint64(8)) & np.uint64(0xff)).astype(np.int64)
+    extra = (tag >> np.uint64(16)).astype(np.uint64)
+    # pair the stamps of each launch: per kernel id the phases arrive in order 0, 1, 2
+    launches = []
+    open_launch = {}
+    for i in range(n):
+        key = (int(kern[i]), int(extra[i]))
+        if phase[i] == 0:
+            open_launch.setdefault(key, []).append([int(t[i]), None, None])
+        elif phase[i] == 1:
+            for rec in open_launch.get(key, []):
+                if rec[1] is None:
+                    rec[1] = int(t[i])
+                    break
+        else:
+            q = open_launch.get(key, [])
+            for j, rec in enumerate(q):
+                if rec[1] is not None and rec[2] is None:
+                    rec[2] = int(t[i])
+                    launches.append((key, rec[0], rec[1], rec[2]))
+                    q.pop(j)
+                    break
+    launches.sort(key=lambda r: r[2])
+    agg = {}
+    prev_end = None
+    for key, t_in, t_wait, t_end in launches:
+        k, ex = key
+        name = TRACE_KERNELS.get(k, str(k))
+        if k in (1, 2, 18, 19):
+            name += f" N={ex & 0xfffff},K={(ex >> 20) & 0xfffff},M={'<=512' if (ex >> 40) <= 512 else '>512'}"
+        a = agg.setdefault(name, {"launches": 0, "work_ns": 0, "gap_ns": 0})
+        a["launches"] += 1
+        a["work_ns"] += t_end - t_wait
+        if prev_end is not None:
+            a["gap_ns"] += max(0, t_wait - prev_end)
+        prev_end = max(prev_end or 0, t_end)
+    span = (launches[-1][3] - launches[0][1]) if launches else 1
+    rows = [{"kernel": k, "launches": v["launches"], "work_us": round(v["work_ns"] / 1e3, 1), "avg_work_us": round(v["work_ns"] / 1e3 / v["launches"], 2),
+             "gap_before_us": round(v["gap_ns"] / 1e3, 1), "avg_gap_us": round(v["gap_ns"] / 1e3 / v["launches"], 2),
+             "share_of_span": round((v["work_ns"] + v["gap_ns"]) / span, 4)} for k, v in sorted(agg.items(), key=lambda kv: -(kv[1]["work_ns"] + kv[1]["gap_ns"]))]
+    out = {"workload": wl["desc"], "mini_batch_index": b, "width": widths[b], "tokens": sum(len(x) for x, _ in res), "decoder_steps": host["steps"],
+           "wall_ms": round(wall * 1e3, 2), "device_span_ms": round(span / 1e6, 2), "stamps": n, "launches_paired": len(launches),
+           "host_per_decoder_step_us": {"issue": round(1e6 * host["issue_s"] / max(1, host["steps"]), 1),
+                                        "wait_for_device": round(1e6 * host["wait_s"] / max(1, host["steps"]), 1),
+                                        "bookkeeping": round(1e6 * host["host_s"] / max(1, host["steps"]), 1)},
+           "options": args.option, "kernels": rows,
+           "note": "work = block 0's time from the return of its wait for the preceding kernel to its end; gap = from the end of the "
+                   "preceding kernel's block 0 to that return (launch hand-over, memory flush, waiting for slower blocks of the predecessor)"}
+    with open(args.trace, "w") as f:
+        json.dump(out, f, indent=1)
+    print(json.dumps({k: out[k] for k in ("wall_ms", "device_span_ms", "decoder_steps", "tokens", "host_per_decoder_step_us")}), flush=True)
+    for r in rows[:24]:
+        print(json.dumps(r), flush=True)
+
+
+def run_strong(args):
+    """Strong scaling as the reference's translator does it (src/translator/translator.h:154-167: a thread pool in which the
+    next free device takes the next mini-batch): the whole fixed corpus, longest mini-batches first, dealt from one shared
+    counter (the process group's key-value store) to whichever rank asks next.  Prints one JSON line with "scaling": "strong",
+    the per-rank busy times and their spread."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from marian_dev_b200 import ops, parallel
+    world, rank, local_rank, dev, cfg, wl, batches, stepper, search = _setup(args)
+    widths = [b[1].shape[1] for b in batches]
+    by_cost = sorted(range(len(batches)), key=lambda i: -widths[i])
+    golden = load_digests(args.model)
+    max_len = int(np.ceil(1.5 * max(widths))) + 2
+    store = dist.distributed_c10d._get_default_store() if world > 1 else None
+    order = batch_order(len(batches))
+    for i in range(args.warmup):
+        search.search(batches[order[i]][1], batches[order[i]][2])
+    torch.cuda.synchronize()
+    pinned = [(sid, torch.from_numpy(ids.astype(np.int64)).pin_memory(), torch.from_numpy(mask).pin_memory()) for sid, ids, mask in batches]
+    taken = [0]
+
+    def next_batch():
+        if store is None:
+            taken[0] += 1
+            return taken[0] - 1
+        return int(store.add("mi8_next_mini_batch", 1)) - 1
+
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    e0.record()
+    tokens, mine, bad = 0, [], 0
+    collected = {}
+    while True:
+        i = next_batch()
+        if i >= len(by_cost):
+            break
+        b = by_cost[i]
+        sid, ids_p, mask_p = pinned[b]
+        res = search.search(ids_p, mask_p)
+        collected.update({int(x): toks for x, (toks, _s) in zip(sid, res)})
+        tokens += sum(len(t) for t, _ in res)
+        mine.append(b)
+        want = golden.get(str(b))
+        bad += int(want is not None and want != tokens_digest(sid, [t for t, _ in res]))
+    e1.record()
+    merged = parallel.gather_outputs(collected, max_len=max_len, device=dev)
+    e2.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    busy, total = e0.elapsed_time(e1), e0.elapsed_time(e2)
+    if bad:
+        raise RuntimeError(f"rank {rank}: {bad} mini-batches decoded to tokens that differ from tests/golden/decode_digests.json")
+    per_rank, counts = [busy], [len(mine)]
+    if world > 1:
+        v = torch.tensor([busy, total, tokens, len(mine)], device=dev, dtype=torch.float64)
+        every = [torch.zeros_like(v) for _ in range(world)]
+        dist.all_gather(every, v)
+        per_rank = [round(float(x[0]), 2) for x in every]
+        counts = [int(x[3]) for x in every]
+        total = max(float(x[1]) for x in every)
+        tokens = int(sum(float(x[2]) for x in every))
+    if rank == 0:
+        assert len(merged) == wl["sentences"]
+        print(json.dumps({"metric": METRIC, "value": round(tokens / (total / 1e3), 1), "unit": UNIT, "n_gpus": world, "scaling": "strong",
+                          "steps": len(batches), "ms_total": round(total, 2), "higher_is_better": True,
+                          "config": {"workload": wl["desc"], "corpus": f"{wl['sentences']} sentences, {len(batches)} mini-batches, longest first, "
+                                     "taken from a shared counter by the next free rank"},
+                          "per_rank_busy_ms": per_rank, "per_rank_mini_batches": counts,
+                          "rank_spread": round(max(per_rank) / max(min(per_rank), 1e-9), 4), "tokens": tokens, "clocks": clocks,
+                          "device_status": ops.poll_status()}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_glue(args):
+    """One glue kernel of the decoder step at the benchmark's shapes (512 hypothesis rows, d = 1024, 16 heads, 32000 words), called
+    through the C ABI on operand sets rotated through more than the L2 capacity, launch overlap on, CUDA events around 200 launches."""
+    import torch
+    from marian_dev_b200.binding import check, lib
+    L = lib()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    st = torch.cuda.current_stream().cuda_stream
+    R, d, heads, dh, V = 512, 1024, 16, 64, 32000
+    kind = args.glue
+    slot = torch.zeros(64, dtype=torch.int32, device=dev)
+    if kind in ("attention1_self", "attention1_cross"):
+        length, batch, mode = (24, 128, 0) if kind == "attention1_self" else (32, 128, 1)
+        kv_rows = length * R if mode == 0 else batch * length
+        sets = max(2, int(200e6 // (2 * kv_rows * d * 4)) + 1)
+        q = [torch.randn(R, d, device=dev) for _ in range(sets)]
+        k = [torch.randn(kv_rows, d, device=dev) for _ in range(sets)]
+        v = [torch.randn(kv_rows, d, device=dev) for _ in range(sets)]
+        out = torch.empty(R, d, device=dev)
+        mask = torch.zeros(batch, length, device=dev)
+        by = 2 * kv_rows * d * 4 + 2 * R * d * 4
+
+        def run(i):
+            j = i % sets
+            check(L.mi8g_attention1(q[j].data_ptr(), k[j].data_ptr(), v[j].data_ptr(), mask.data_ptr() if mode == 1 else None, R, heads, dh, length,
+                                    batch, mode, out.data_ptr(), slot.data_ptr(), st))
+        shape = f"{R} rows x {heads} heads x {dh}, {length} positions, mode {mode}"
+    elif kind == "quantize_slot":
+        sets = 64
+        x = [torch.randn(R, d, device=dev) for _ in range(sets)]
+        qo = torch.empty(R * d + 256, dtype=torch.int8, device=dev)
+        slot.view(torch.float32)[0] = 5.0
+        by = R * d * 5
+
+        def run(i):
+            check(L.mi8g_quantize_slot(x[i % sets].data_ptr(), R * d, slot.data_ptr(), qo.data_ptr(), qo[R * d:].data_ptr(), st))
+        shape = f"{R} x {d} fp32 -> int8"
+    elif kind == "add_layernorm":
+        sets = 32
+        a = [torch.randn(R, d, device=dev) for _ in range(sets)]
+        r = [torch.randn(R, d, device=dev) for _ in range(sets)]
+        g, b = torch.ones(d, device=dev), torch.zeros(d, device=dev)
+        out = torch.empty(R, d, device=dev)
+        by = R * d * 12
+
+        def run(i):
+            j = i % sets
+            check(L.mi8g_add_layernorm(a[j].data_ptr(), r[j].data_ptr(), g.data_ptr(), b.data_ptr(), 1e-6, R, d, out.data_ptr(), None, slot.data_ptr(), st))
+        shape = f"{R} rows x {d}"
+    elif kind == "lse_topk":
+        sets = 4
+        lg = [torch.randn(R, V, device=dev) for _ in range(sets)]
+        cs = torch.empty(R * 8, device=dev)
+        cw = torch.empty(R * 8, dtype=torch.int32, device=dev)
+        by = R * V * 4
+
+        def run(i):
+            check(L.mi8g_lse_topk(lg[i % sets].data_ptr(), R, V, 4, None, cs.data_ptr(), cw.data_ptr(), st))
+        shape = f"{R} rows x {V} words, k = 4"
+    else:
+        raise SystemExit(f"unknown kernel {kind}")
+    iters = 200
+    for i in range(10):
+        run(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        run(i)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1000.0 / iters
+    print(json.dumps({"metric": "glue_kernel", "kernel": kind, "shape": shape, "us_per_launch": round(us, 2), "algorithmic_bytes": by,
+                      "GBps": round(by / us / 1e3, 1), "operand_sets": sets,
+                      "timing": f"{iters} back-to-back launches (programmatic dependent launch on), CUDA events"}), flush=True)
 
 
 # ----------------------------------------------------------------------------- CPU baseline / reference arm
@@ -440,11 +846,12 @@ def time_affine(m, k, n, iters=40):
     bias = torch.randn(n, device=dev) * 0.01
     outs = [torch.empty(m, n, device=dev) for _ in range(copies)]
     aq = [ops.IntgemmTensor(m, k, dev) for _ in range(copies)]
+    wsp = ops.Workspace(device=dev)          # one workspace for the warm-up and the captured stream alike
 
     def run(i):
         j = i % copies
-        ops.prepareA(xs[j], out=aq[j])
-        ops.multiply(aq[j], ws[j], bias, 1.0, True, out=outs[j])
+        ops.prepareA(xs[j], out=aq[j], ws=wsp)
+        ops.multiply(aq[j], ws[j], bias, 1.0, True, out=outs[j], ws=wsp)
 
     for i in range(5):
         run(i)
@@ -684,7 +1091,15 @@ def run_affines(args):
 
 if __name__ == "__main__":
     a = parse_args()
-    if a.packed8:
+    if a.write_digests:
+        run_write_digests(a)
+    elif a.trace:
+        run_trace(a)
+    elif a.glue:
+        run_glue(a)
+    elif a.strong:
+        run_strong(a)
+    elif a.packed8:
         run_packed8(a)
     elif a.affine or a.sweep:
         run_affines(a)

@@ -19,6 +19,9 @@
  * split-K accumulation buffers and put every word they need zeroed back to zero before they finish,
  * so one workspace serves every later call on the same stream.  Calls that share a workspace must
  * not overlap on the device.
+ *
+ * Measurement and test aids (launch counters, per-kernel timers, the MMA-rate probe, the wait-fault hook)
+ * are declared separately in marian_i8_measure.h; nothing of this header needs them.
  */
 #ifndef MARIAN_I8_H_
 #define MARIAN_I8_H_
@@ -97,6 +100,13 @@ int mi8_prepare_b_f32(const float* w, int K, int N, int w_is_nk, int8_t* bt, flo
                       void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * out[b][c][r] = in[b][r][c] for `batch` matrices [rows, cols] of fp32: the transpose the reference puts in front of
+ * prepareA when affine / dot are called with transA (src/tensors/cpu/intgemm_interface.h:52,
+ * `transpose(a)` of src/graph/expression_operators.cpp).
+ */
+int mi8_transpose_f32(const float* in, int batch, int rows, int cols, float* out, void* stream);
+
+/*
  * C[M,N] = relu?( float(Aq . Bt^T) * (1/(qa*qb) * scale) + bias ), the forward step of the
  * multiply node of affineOrDotTyped (src/tensors/cpu/intgemm_interface.h:60-88: Multiply with
  * callbacks::UnquantizeAndAddBiasAndWrite / UnquantizeAndWrite) with the ReLU of
@@ -120,12 +130,17 @@ int mi8_multiply_i8_ex(const int8_t* aq, const int8_t* bt, int M, int N, int K,
                        void* workspace, size_t workspace_bytes, void* stream,
                        int force_tile_m, int force_splits);
 
-/* Measurement aid (no counterpart in the reference): runs, on every SM, a loop of `k_blocks` x 4
- * tcgen05.mma kind::i8 instructions (128 x 256 x 32 each) on one resident shared-memory tile, without loads
- * or write-back, times it with CUDA events (best of three) and returns the rate in TOPS (host float).
- * This is the int8 tensor-pipe figure the roofline fractions of the large-M shapes are quoted against;
- * synchronises the stream. */
-int mi8_measure_int8_peak(int k_blocks, float* tops_out, void* stream);
+/* One quantised activation against `count` (1..3) converted weights of the same shape in ONE launch: what
+ * MultiHead builds as separate affines over the same input - kh = affine(keys, Wk, bk) and vh = affine(values, Wv, bv)
+ * with keys == values (src/models/transformer.h:305-327), or q / k / v of encoder self-attention (:290-327) - and the
+ * SSRU's dot(input, W) and affine(input, Wf, bf) (src/rnn/cells.h:1029-1050).  bt_all holds the `count` matrices
+ * Bt[n_each, K] one behind the other; matrix i has its own multiplier *d_qb[i], bias bias[i] (bias or bias[i] NULL =
+ * dot) and output c[i] [M, n_each] row-major.  d_qb / bias / c are HOST arrays of device pointers.  n_each must be a
+ * multiple of 128 for count > 1 (MI8_ERR_UNSUPPORTED otherwise: the caller then multiplies one by one).  Each
+ * output is bit-identical to the mi8_multiply_i8 call it replaces. */
+int mi8_multiply_i8_multi(const int8_t* aq, const int8_t* bt_all, int M, int n_each, int K, int count, const float* d_qa,
+                          const float* const* d_qb, float scale, const float* const* bias, int relu, void* const* c, int out_dtype,
+                          void* workspace, size_t workspace_bytes, void* stream);
 
 /* The multiply that performs Int8::PrepareA itself (src/tensors/cpu/intgemm_interface.h:17-32 followed by
  * :97-147 in one launch): `a` is the fp32 activation [M,K], `absmax_slot` a device word holding the bit
@@ -191,33 +206,6 @@ int mi8_multiply_plan(int M, int N, int K, int force_tile_m, int force_splits, i
  * that its set-up (and, in the GEMM, the first weight tiles) overlaps the tail of the previous kernel on
  * the stream; each kernel waits for its predecessor before touching dependent data.  Process-wide switch. */
 void mi8_set_pdl(int enabled);
-
-/* Measurement aid: between mi8_profile_begin and mi8_profile_end every GEMM launch made by the calling
- * thread is bracketed by CUDA events on its stream; mi8_profile_end waits for them and returns one record
- * per launch (at most `capacity`).  Off by default; costs two cudaEventRecord calls per launch when on. */
-typedef struct mi8_gemm_record {
-  int M, N, K;       /* problem size of the launch */
-  int out_bytes;     /* bytes per output element (4 or 2) */
-  float us;          /* device time between the two events, microseconds */
-} mi8_gemm_record;
-int mi8_profile_begin(int max_records);
-int mi8_profile_end(mi8_gemm_record* records, int capacity, int* count);
-
-/* Measurement aid: between mi8_kernel_times_begin and mi8_kernel_times_end every kernel the calling thread
- * launches through the library is bracketed by CUDA events on its stream (launch overlap is off meanwhile, so
- * the launches serialise); _end waits for the device and returns, per kernel function, its launches and
- * total device time.  `name` is the function's (mangled) symbol name, truncated. */
-typedef struct mi8_kernel_time {
-  char name[160];
-  long long launches;
-  double total_us;
-} mi8_kernel_time;
-int mi8_kernel_times_begin(void);
-int mi8_kernel_times_end(mi8_kernel_time* out, int capacity, int* count);
-
-/* Number of kernels this thread has launched through the library since the last reset. */
-unsigned long long mi8_launch_count(void);
-void mi8_launch_count_reset(void);
 
 #ifdef __cplusplus
 }

@@ -132,6 +132,24 @@ int mi8g_nbest_merge(const float* cand_score, const int* cand_word, int beam, in
  * counters.  Synchronises the device. */
 int mi8d_history_reuse(mi8d_decoder* d, unsigned out[2], int reset);
 
+/* Tuning switches of the step driver; every setting computes the same values, bit for bit.
+ *   MI8D_OPT_FUSE_WEIGHTS (default 1): matrices that multiply the same activation (Wk|Wv of an attention block,
+ *     Wq|Wk|Wv of an encoder layer, the SSRU's W|Wf) run as ONE GEMM launch over copies stored one behind the other;
+ *   MI8D_OPT_QUANT_IN_GEMM (default 0): affines with K <= 1024 whose tiles fit one wave of CTAs quantise their
+ *     activation while loading it (mi8_multiply_f32_slot) instead of through a quantisation launch;
+ *   MI8D_OPT_FUSED_OUTPUT_MAX_ROWS (default 480): up to this many rows the output layer reduces its logits inside
+ *     the GEMM's write-back, above it the logits are written and read back by the log-softmax / top-k kernel;
+ *   MI8D_OPT_SIDE_STREAM (default 1): the re-projection of the earlier history slabs runs on an internal stream;
+ *   MI8D_OPT_ATTENTION_UNROLL (8 or 16, default 16; process-wide): key/value rows a thread keeps in flight. */
+enum mi8d_option {
+  MI8D_OPT_FUSE_WEIGHTS = 1,
+  MI8D_OPT_QUANT_IN_GEMM = 2,
+  MI8D_OPT_FUSED_OUTPUT_MAX_ROWS = 3,
+  MI8D_OPT_SIDE_STREAM = 4,
+  MI8D_OPT_ATTENTION_UNROLL = 5
+};
+int mi8d_set_option(mi8d_decoder* d, int option, int value);
+
 /* keep != 0: every step also writes its logits [beam*batch, vocab] (the output layer then runs unfused);
  * mi8d_last_logits returns them.  Off by default: the fused output layer never materialises them. */
 int mi8d_keep_logits(mi8d_decoder* d, int keep);

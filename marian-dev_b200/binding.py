@@ -16,12 +16,13 @@ LIB_PATH = os.path.join(_HERE, "libmarian_i8.so")
 MI8_F32, MI8_F16 = 0, 1
 
 class Mi8GemmRecord(ctypes.Structure):
-    """mi8_gemm_record of include/marian_i8.h."""
-    _fields_ = [("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("out_bytes", ctypes.c_int), ("us", ctypes.c_float)]
+    """mi8_gemm_record of include/marian_i8_measure.h."""
+    _fields_ = [("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("out_bytes", ctypes.c_int), ("us", ctypes.c_float),
+                ("rows_computed", ctypes.c_int)]
 
 
 class Mi8KernelTime(ctypes.Structure):
-    """mi8_kernel_time of include/marian_i8.h."""
+    """mi8_kernel_time of include/marian_i8_measure.h."""
     _fields_ = [("name", ctypes.c_char * 160), ("launches", ctypes.c_longlong), ("total_us", ctypes.c_double)]
 
 
@@ -35,7 +36,7 @@ class Mi8dConfig(ctypes.Structure):
 DECODE_EXPORTS = ["mi8d_arena_bytes", "mi8d_create", "mi8d_destroy", "mi8d_set_weight", "mi8d_set_param", "mi8d_set_positions",
                   "mi8d_start", "mi8d_encode", "mi8d_step", "mi8d_last_logits", "mi8d_history_reuse",
                   "mi8g_embed", "mi8g_add_layernorm", "mi8g_quantize_slot", "mi8g_attention1", "mi8g_lse_topk", "mi8g_nbest_merge",
-                  "mi8g_output_scratch_bytes", "mi8g_output_topk", "mi8d_keep_logits", "mi8d_search"]
+                  "mi8g_output_scratch_bytes", "mi8g_output_topk", "mi8d_keep_logits", "mi8d_search", "mi8d_set_option"]
 
 # Every symbol include/marian_packed8.h declares.
 PACKED8_EXPORTS = ["mi8p_packed_bytes", "mi8p_prepare_b_f32", "mi8p_unpack_b", "mi8p_quantize_rows", "mi8p_multiply", "mi8p_scratch_bytes",
@@ -47,8 +48,12 @@ EXPORTS = [
     "mi8_workspace_bytes", "mi8_workspace_init", "mi8_poll_status", "mi8_clear_status",
     "mi8_max_absolute_f32", "mi8_quantize_f32_i8", "mi8_prepare_a_f32", "mi8_prepare_b_f32",
     "mi8_multiply_i8", "mi8_multiply_i8_ex", "mi8_multiply_i8_rows_from", "mi8_multiply_f32_slot", "mi8_multiply_i8_static", "mi8_affine_f32", "mi8_multiply_plan",
-    "mi8_launch_count", "mi8_launch_count_reset", "mi8_measure_int8_peak", "mi8_kernel_times_begin", "mi8_kernel_times_end", "mi8_profile_begin", "mi8_profile_end", "mi8_set_pdl",
+    "mi8_set_pdl", "mi8_multiply_i8_multi", "mi8_transpose_f32",
 ]
+
+# Every symbol include/marian_i8_measure.h declares (measurement and test aids, not part of the drop-in surface).
+MEASURE_EXPORTS = ["mi8_launch_count", "mi8_launch_count_reset", "mi8_measure_int8_peak", "mi8_kernel_times_begin", "mi8_kernel_times_end",
+                   "mi8_profile_begin", "mi8_profile_end", "mi8_test_wait_fault", "mi8d_search_stats", "mi8_trace_begin", "mi8_trace_end"]
 
 
 class Mi8dSearchConfig(ctypes.Structure):
@@ -105,6 +110,10 @@ def lib() -> ctypes.CDLL:
     L.mi8_multiply_i8_rows_from.restype = ci
     L.mi8_multiply_f32_slot.argtypes = [vp, vp, vp, vp, ci, ci, ci, vp, cf, vp, ci, vp, ci, vp, vp]
     L.mi8_multiply_f32_slot.restype = ci
+    L.mi8_transpose_f32.argtypes = [vp, ci, ci, ci, vp, vp]
+    L.mi8_transpose_f32.restype = ci
+    L.mi8_multiply_i8_multi.argtypes = [vp, vp, ci, ci, ci, ci, vp, ctypes.POINTER(vp), cf, ctypes.POINTER(vp), ci, ctypes.POINTER(vp), ci, vp, sz, vp]
+    L.mi8_multiply_i8_multi.restype = ci
     L.mi8_multiply_i8_static.argtypes = [vp, vp, ci, ci, ci, vp, vp, cf, vp, ci, vp, ci, vp]
     L.mi8_multiply_i8_static.restype = ci
     L.mi8_affine_f32.argtypes = [vp, ci, ci, vp, vp, ci, vp, cf, ci, vp, ci, vp, vp, sz, vp]
@@ -121,6 +130,13 @@ def lib() -> ctypes.CDLL:
     L.mi8_profile_end.argtypes = [ctypes.POINTER(Mi8GemmRecord), ci, ctypes.POINTER(ci)]
     L.mi8_profile_end.restype = ci
     L.mi8_launch_count.restype = ctypes.c_ulonglong
+    L.mi8_trace_begin.argtypes = [vp, ci]
+    L.mi8_trace_begin.restype = ci
+    L.mi8_trace_end.restype = ci
+    L.mi8_test_wait_fault.argtypes = [ci, ctypes.c_uint]
+    L.mi8_test_wait_fault.restype = None
+    L.mi8d_search_stats.argtypes = [vp, ctypes.POINTER(ctypes.c_double * 4), ci]
+    L.mi8d_search_stats.restype = ci
     L.mi8p_packed_bytes.restype = sz
     L.mi8p_packed_bytes.argtypes = [ci, ci]
     L.mi8p_unpack_b.argtypes = [vp, ci, ci, vp, vp]
@@ -153,6 +169,8 @@ def lib() -> ctypes.CDLL:
     L.mi8d_search.argtypes = [vp, vp, vp, ci, ci, ctypes.POINTER(Mi8dSearchConfig), vp, ci, vp, vp, ctypes.POINTER(ctypes.c_ulonglong),
                               ctypes.POINTER(ctypes.c_ulonglong), vp]
     L.mi8d_search.restype = ci
+    L.mi8d_set_option.argtypes = [vp, ci, ci]
+    L.mi8d_set_option.restype = ci
     L.mi8d_keep_logits.argtypes = [vp, ci]
     L.mi8d_keep_logits.restype = ci
     L.mi8g_output_scratch_bytes.argtypes = [ci, ci]

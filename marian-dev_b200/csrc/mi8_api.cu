@@ -106,7 +106,7 @@ using namespace mi8;
 
 extern "C" {
 
-int mi8_version(void) { return 100; }
+int mi8_version(void) { return 10100; }
 
 const char* mi8_strerror(int status) {
   switch(status) {
@@ -215,6 +215,10 @@ int mi8_prepare_b_f32(const float* w, int K, int N, int w_is_nk, int8_t* bt, flo
   return launch_transpose_quantize(w, K, N, d_quant_mult, bt, as_stream(stream));
 }
 
+int mi8_transpose_f32(const float* in, int batch, int rows, int cols, float* out, void* stream) {
+  return launch_transpose_f32(in, batch, rows, cols, out, as_stream(stream));
+}
+
 int mi8_multiply_i8(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb,
                     float scale, const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* workspace,
                     size_t workspace_bytes, void* stream) {
@@ -229,6 +233,33 @@ int mi8_multiply_i8_ex(const int8_t* aq, const int8_t* bt, int M, int N, int K, 
     return MI8_ERR_BAD_ARG;
   return launch_gemm(aq, bt, M, N, K, d_qa, d_qb, scale, bias, relu, c, out_dtype, acc_out, workspace, workspace_bytes,
                      as_stream(stream), force_tile_m, force_splits);
+}
+
+int mi8_multiply_i8_multi(const int8_t* aq, const int8_t* bt_all, int M, int n_each, int K, int count, const float* d_qa,
+                          const float* const* d_qb, float scale, const float* const* bias, int relu, void* const* c, int out_dtype,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  if(count < 1 || count > 3 || n_each <= 0 || d_qb == nullptr || c == nullptr)
+    return MI8_ERR_BAD_ARG;
+  GemmCall g;
+  g.aq = aq;
+  g.bt = bt_all;
+  g.M = M;
+  g.N = n_each * count;
+  g.K = K;
+  g.d_qa = d_qa;
+  g.scale = scale;
+  g.relu = relu;
+  g.out_dtype = out_dtype;
+  g.nseg = count;
+  for(int i = 0; i < count; ++i) {
+    g.seg_qb[i] = d_qb[i];
+    g.seg_bias[i] = bias != nullptr ? bias[i] : nullptr;
+    g.seg_c[i] = c[i];
+  }
+  g.ws = workspace;
+  g.ws_bytes = workspace_bytes;
+  g.stream = as_stream(stream);
+  return launch_gemm_call(g);
 }
 
 int mi8_multiply_f32_slot(const float* a, const unsigned* absmax_slot, float* qa_out, const int8_t* bt, int M, int N, int K,
@@ -266,6 +297,36 @@ int mi8_affine_f32(const float* a, int M, int K, const int8_t* bt, const float* 
 
 void mi8_set_pdl(int enabled) { set_pdl(enabled != 0); }
 
+void mi8_test_wait_fault(int withhold_item, unsigned spin_limit) { test_wait_fault(withhold_item, spin_limit); }
+
+int mi8_trace_begin(unsigned long long* device_buf, int capacity) {
+  if(device_buf == nullptr || capacity <= 0)
+    return MI8_ERR_BAD_ARG;
+  const unsigned long long head[2] = {0ull, static_cast<unsigned long long>(capacity)};
+  cudaError_t e = cudaDeviceSynchronize();
+  if(e == cudaSuccess)
+    e = cudaMemcpy(device_buf, head, sizeof(head), cudaMemcpyHostToDevice);
+  if(e != cudaSuccess) {
+    set_last_cuda_error(e);
+    return MI8_ERR_LAUNCH;
+  }
+  if(trace_set_glue(device_buf) != 0 || trace_set_gemm(device_buf) != 0 || trace_set_quant(device_buf) != 0) {
+    set_last_cuda_error(cudaGetLastError());
+    return MI8_ERR_LAUNCH;
+  }
+  return MI8_OK;
+}
+
+int mi8_trace_end(void) {
+  cudaError_t e = cudaDeviceSynchronize();
+  const int rc = trace_set_glue(nullptr) | trace_set_gemm(nullptr) | trace_set_quant(nullptr);
+  if(e != cudaSuccess || rc != 0) {
+    set_last_cuda_error(e != cudaSuccess ? e : cudaGetLastError());
+    return MI8_ERR_LAUNCH;
+  }
+  return MI8_OK;
+}
+
 int mi8_kernel_times_begin(void) {
   t_ktimes.on = true;
   t_ktimes.funcs.clear();
@@ -277,27 +338,29 @@ int mi8_kernel_times_end(mi8_kernel_time* out, int capacity, int* count) {
   t_ktimes.on = false;
   int n = 0;
   cudaError_t e = cudaDeviceSynchronize();
+  std::vector<const void*> slot_func;   // launches are merged per kernel FUNCTION (names are only labels and may be truncated)
   for(size_t i = 0; e == cudaSuccess && i < t_ktimes.funcs.size() && 2 * i + 1 < t_ktimes.used; ++i) {
     float ms = 0.f;
     if(cudaEventElapsedTime(&ms, t_ktimes.pool[2 * i], t_ktimes.pool[2 * i + 1]) != cudaSuccess) {
       cudaGetLastError();
       continue;
     }
-    const char* name = nullptr;
-    if(cudaFuncGetName(&name, t_ktimes.funcs[i]) != cudaSuccess || name == nullptr) {
-      cudaGetLastError();
-      name = "?";
-    }
     int slot = -1;
     for(int j = 0; j < n; ++j)
-      if(strncmp(out[j].name, name, sizeof(out[j].name) - 1) == 0) {
+      if(slot_func[j] == t_ktimes.funcs[i]) {
         slot = j;
         break;
       }
     if(slot < 0) {
       if(out == nullptr || n >= capacity)
         continue;
+      const char* name = nullptr;
+      if(cudaFuncGetName(&name, t_ktimes.funcs[i]) != cudaSuccess || name == nullptr) {
+        cudaGetLastError();
+        name = "?";
+      }
       slot = n++;
+      slot_func.push_back(t_ktimes.funcs[i]);
       memset(&out[slot], 0, sizeof(out[slot]));
       strncpy(out[slot].name, name, sizeof(out[slot].name) - 1);
     }

@@ -6,6 +6,7 @@
 // ("transformer-postprocess: dan"), then the tied output layer, log-softmax and n-best selection.
 // mi8d_search adds the beam-search bookkeeping around the step (BeamSearch::search,
 // src/translator/beam_search.cpp:249-538), so a mini-batch is translated by one call.
+#include <chrono>
 #include <cmath>
 #include <cstring>
 #include <string>
@@ -22,6 +23,37 @@ struct Weight {
   const int8_t* bt = nullptr;
   int K = 0, N = 0;
   const float* qm() const { return reinterpret_cast<const float*>(bt + static_cast<size_t>(K) * N); }
+};
+
+// One affine as the step loop uses it: everything resolved to pointers once (no name lookups per step).
+struct Aff {
+  const int8_t* bt = nullptr;
+  const float* qm = nullptr;
+  const float* bias = nullptr;
+  int K = 0, N = 0;
+};
+// Several weights of the same shape multiplied with the same activation in one launch (Wk|Wv, Wq|Wk|Wv,
+// the SSRU's W|Wf): their int8 matrices copied one behind the other into the arena.
+struct Fused {
+  int8_t* bt = nullptr;   // [nseg * n, K] in the arena
+  int nseg = 0, n = 0, K = 0;
+  const float* qm[3] = {nullptr, nullptr, nullptr};
+  const float* bias[3] = {nullptr, nullptr, nullptr};
+  bool ready = false;
+};
+struct Norm {
+  const float* g = nullptr;
+  const float* b = nullptr;
+};
+struct EncLayerW {
+  Aff q, k, v, o, w1, w2;
+  Fused qkv;
+  Norm ln_att, ln_ffn;
+};
+struct DecLayerW {
+  Aff self_q, self_k, self_v, self_o, rnn_w, rnn_wf, ctx_q, ctx_k, ctx_v, ctx_o, w1, w2;
+  Fused self_kv, rnn, ctx_kv;
+  Norm ln_self, ln_ctx, ln_ffn;
 };
 
 size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
@@ -49,6 +81,9 @@ struct LayerBufs {
   float* cell[2] = {nullptr, nullptr};  // SSRU state, double-buffered [max_rows, d]
 };
 
+// Slots of the per-step abs-max array: slot 0 belongs to the embedding (input of layer 0), then eight per layer.
+enum LayerSlot { kSlotSelfLn = 0, kSlotHistory, kSlotSelfAtt, kSlotCtxAtt, kSlotCtxLn, kSlotRelu, kSlotOut, kSlotsPerLayer = 8 };
+
 }  // namespace
 }  // namespace mi8
 
@@ -62,6 +97,15 @@ struct mi8d_decoder {
   std::unordered_map<std::string, Weight> weights;
   std::unordered_map<std::string, const float*> params;
   const float* positions = nullptr;
+  // resolved model (rebuilt by resolve() after a parameter was registered)
+  bool dirty = true;
+  bool can_fuse = false;              // dim_emb is a multiple of 128: a weight tile never straddles two fused matrices
+  std::vector<EncLayerW> enc_w;
+  std::vector<DecLayerW> dec_w;
+  const float* wemb = nullptr;
+  const float* out_bias = nullptr;
+  Aff out_w;
+  std::vector<int8_t*> fused_enc, fused_self, fused_ctx;   // arena storage of the fused matrices
 
   std::vector<LayerBufs> layers;
   float* x_in = nullptr;                 // layer-0 input when there are no slabs (SSRU) and the final layer output
@@ -91,12 +135,16 @@ struct mi8d_decoder {
   bool keep_logits = false;
   unsigned* slots = nullptr;
   int n_slots = 0;
-  // The history chain of a self-attention block (abs-max -> quantise -> key GEMM, value GEMM) does not depend on
-  // the query projection, and the two GEMMs not on each other: they run on two internal streams, forked from
-  // and joined to the caller's stream with events.
-  cudaStream_t side[2] = {nullptr, nullptr};
-  cudaEvent_t ev_x = nullptr, ev_hq = nullptr, ev_k = nullptr, ev_v = nullptr;
+  // Re-projecting the keys/values of the EARLIER history slabs (needed only when the history's abs-max changed) does
+  // not depend on the query projection: it runs on an internal stream, forked from and joined to the caller's
+  // stream with events, beside the query projection and the newest slab's keys/values.
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   bool overlap = false;
+  // tuning switches (mi8d_set_option)
+  int opt_fuse = 1, opt_quant_in_gemm = 0, opt_fused_out_rows = 480, opt_side_stream = 1;
+  // host-side timing of mi8d_search
+  double t_issue = 0, t_wait = 0, t_host = 0, n_steps = 0;
 
   int t = 0, batch = 0, src = 0, ctx_cur = 0, anc_cur = 0, cell_cur = 0;
   bool cross_valid = false;
@@ -162,9 +210,26 @@ struct mi8d_decoder {
       enc_h = arena.take<float>(M * f);
       enc_aq = arena.take<int8_t>(M * (f > d ? f : d) + 256);
     }
-    n_slots = 8 * c.dec_depth + 8 + 4 * c.enc_depth;
+    n_slots = kSlotsPerLayer * c.dec_depth + 8 + 4 * c.enc_depth;
     slots = arena.take<unsigned>(n_slots);
+    // storage of the fused weight matrices (copies of the registered int8 matrices, made once by resolve())
+    can_fuse = d % 128 == 0;
+    fused_enc.assign(c.enc_depth, nullptr);
+    fused_self.assign(c.dec_depth, nullptr);
+    fused_ctx.assign(c.dec_depth, nullptr);
+    if(can_fuse) {
+      for(auto& p : fused_enc)
+        p = arena.take<int8_t>(3 * d * d);
+      for(auto& p : fused_self)
+        p = arena.take<int8_t>(2 * d * d);
+      for(auto& p : fused_ctx)
+        p = arena.take<int8_t>(2 * d * d);
+    }
   }
+
+  unsigned* layer_slot(int l, int which) const { return slots + 1 + kSlotsPerLayer * l + which; }
+  unsigned* input_slot(int l) const { return l == 0 ? slots : layer_slot(l - 1, kSlotOut); }
+  unsigned* enc_slot(int l, int which) const { return slots + 1 + kSlotsPerLayer * cfg.dec_depth + 4 * l + which; }
 
   const Weight* W(const std::string& name) const {
     auto it = weights.find(name);
@@ -174,39 +239,105 @@ struct mi8d_decoder {
     auto it = params.find(name);
     return it == params.end() ? nullptr : it->second;
   }
+  bool aff(Aff& a, const std::string& wname, const std::string& bname) const {
+    const Weight* w = W(wname);
+    if(w == nullptr)
+      return false;
+    a.bt = w->bt;
+    a.qm = w->qm();
+    a.K = w->K;
+    a.N = w->N;
+    a.bias = nullptr;
+    if(!bname.empty()) {
+      a.bias = P(bname);
+      if(a.bias == nullptr)
+        return false;
+    }
+    return true;
+  }
+  bool norm(Norm& n, const std::string& prefix) const {
+    n.g = P(prefix + "_ln_scale");
+    n.b = P(prefix + "_ln_bias");
+    return n.g != nullptr && n.b != nullptr;
+  }
+  // copies the matrices of `parts` one behind the other into `store` (stream-ordered on s)
+  bool fuse(Fused& f, int8_t* store, std::initializer_list<const Aff*> parts, cudaStream_t s) {
+    f = Fused();
+    if(store == nullptr)
+      return true;   // not fusable for this model: the step falls back to one launch per matrix
+    int i = 0;
+    for(const Aff* a : parts) {
+      if(i == 0) {
+        f.n = a->N;
+        f.K = a->K;
+      } else if(a->N != f.n || a->K != f.K) {
+        return true;
+      }
+      if(cudaMemcpyAsync(store + static_cast<size_t>(i) * f.n * f.K, a->bt, static_cast<size_t>(f.n) * f.K, cudaMemcpyDeviceToDevice, s) !=
+         cudaSuccess)
+        return false;
+      f.qm[i] = a->qm;
+      f.bias[i] = a->bias;
+      ++i;
+    }
+    f.bt = store;
+    f.nseg = i;
+    f.ready = f.n % 128 == 0;
+    return true;
+  }
+
+  // Looks every parameter up once and builds the fused matrices.  MI8_ERR_BAD_ARG names a missing parameter.
+  int resolve(cudaStream_t s) {
+    const mi8d_config& c = cfg;
+    enc_w.assign(c.enc_depth, EncLayerW());
+    dec_w.assign(c.dec_depth, DecLayerW());
+    bool ok = true, copies = true;
+    for(int l = 0; l < c.enc_depth; ++l) {
+      EncLayerW& e = enc_w[l];
+      const std::string pre = "encoder_l" + std::to_string(l + 1) + "_self", ffn = "encoder_l" + std::to_string(l + 1) + "_ffn";
+      ok = ok && aff(e.q, pre + "_Wq", pre + "_bq") && aff(e.k, pre + "_Wk", pre + "_bk") && aff(e.v, pre + "_Wv", pre + "_bv") &&
+           aff(e.o, pre + "_Wo", pre + "_bo") && aff(e.w1, ffn + "_W1", ffn + "_b1") && aff(e.w2, ffn + "_W2", ffn + "_b2") &&
+           norm(e.ln_att, pre + "_Wo") && norm(e.ln_ffn, ffn + "_ffn");
+      if(ok)
+        copies = copies && fuse(e.qkv, fused_enc[l], {&e.q, &e.k, &e.v}, s);
+    }
+    for(int l = 0; l < c.dec_depth && ok; ++l) {
+      DecLayerW& w = dec_w[l];
+      const std::string li = "decoder_l" + std::to_string(l + 1);
+      if(c.ssru) {
+        const std::string pre = li + "_rnn";
+        ok = ok && aff(w.rnn_w, pre + "_W", "") && aff(w.rnn_wf, pre + "_Wf", pre + "_bf") && norm(w.ln_self, pre + "_ffn");
+        if(ok)
+          copies = copies && fuse(w.rnn, fused_self[l], {&w.rnn_w, &w.rnn_wf}, s);
+      } else {
+        const std::string pre = li + "_self";
+        ok = ok && aff(w.self_q, pre + "_Wq", pre + "_bq") && aff(w.self_k, pre + "_Wk", pre + "_bk") &&
+             aff(w.self_v, pre + "_Wv", pre + "_bv") && aff(w.self_o, pre + "_Wo", pre + "_bo") && norm(w.ln_self, pre + "_Wo");
+        if(ok)
+          copies = copies && fuse(w.self_kv, fused_self[l], {&w.self_k, &w.self_v}, s);
+      }
+      const std::string pre = li + "_context", ffn = li + "_ffn";
+      ok = ok && aff(w.ctx_q, pre + "_Wq", pre + "_bq") && aff(w.ctx_k, pre + "_Wk", pre + "_bk") && aff(w.ctx_v, pre + "_Wv", pre + "_bv") &&
+           aff(w.ctx_o, pre + "_Wo", pre + "_bo") && norm(w.ln_ctx, pre + "_Wo") && aff(w.w1, ffn + "_W1", ffn + "_b1") &&
+           aff(w.w2, ffn + "_W2", ffn + "_b2") && norm(w.ln_ffn, ffn + "_ffn");
+      if(ok)
+        copies = copies && fuse(w.ctx_kv, fused_ctx[l], {&w.ctx_k, &w.ctx_v}, s);
+    }
+    wemb = P("Wemb");
+    ok = ok && wemb != nullptr && aff(out_w, "Wemb_intgemm8", "decoder_ff_logit_out_b");
+    out_bias = out_w.bias;
+    if(!ok)
+      return MI8_ERR_BAD_ARG;
+    if(!copies) {
+      set_last_cuda_error(cudaGetLastError());
+      return MI8_ERR_LAUNCH;
+    }
+    dirty = false;
+    return MI8_OK;
+  }
 };
 
 namespace {
-
-// aq (already quantised, multiplier behind the data) x weight -> c
-int gemm(mi8d_decoder* d, const int8_t* a, int M, const std::string& wname, const std::string& bname, bool relu, float* c,
-         cudaStream_t s, unsigned* absmax_out = nullptr, int force_splits = 0) {
-  const Weight* w = d->W(wname);
-  if(w == nullptr)
-    return MI8_ERR_BAD_ARG;
-  const float* bias = nullptr;
-  if(!bname.empty()) {
-    bias = d->P(bname);
-    if(bias == nullptr)
-      return MI8_ERR_BAD_ARG;
-  }
-  const float* qa = reinterpret_cast<const float*>(a + static_cast<size_t>(M) * w->K);
-  return launch_gemm(a, w->bt, M, w->N, w->K, qa, w->qm(), 1.0f, bias, relu ? 1 : 0, c, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0,
-                     force_splits, absmax_out);
-}
-
-int quant(mi8d_decoder* /*d*/, const float* x, size_t rows, size_t dim, const unsigned* slot, int8_t* q, cudaStream_t s) {
-  return launch_quantize_slot(x, rows * dim, slot, q, reinterpret_cast<float*>(q + rows * dim), s);
-}
-
-int add_ln(mi8d_decoder* d, const float* a, const float* resid, const std::string& prefix, int rows, float* out, float* rowmax,
-           unsigned* slot, cudaStream_t s) {
-  const float* g = d->P(prefix + "_ln_scale");
-  const float* b = d->P(prefix + "_ln_bias");
-  if(g == nullptr || b == nullptr)
-    return MI8_ERR_BAD_ARG;
-  return launch_add_layernorm(a, resid, g, b, 1e-6f, rows, d->cfg.dim_emb, out, rowmax, slot, s);
-}
 
 #define MI8D_CUDA(expr)               \
   do {                                \
@@ -223,6 +354,60 @@ int add_ln(mi8d_decoder* d, const float* a, const float* resid, const std::strin
     if(rc_ != MI8_OK)       \
       return rc_;           \
   } while(0)
+
+// aq (already quantised, multiplier behind the data) x weight -> c
+int gemm(mi8d_decoder* d, const int8_t* a, int M, const Aff& w, bool relu, float* c, cudaStream_t s, unsigned* absmax_out = nullptr,
+         int force_splits = 0) {
+  const float* qa = reinterpret_cast<const float*>(a + static_cast<size_t>(M) * w.K);
+  return launch_gemm(a, w.bt, M, w.N, w.K, qa, w.qm, 1.0f, w.bias, relu ? 1 : 0, c, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, force_splits,
+                     absmax_out);
+}
+
+// the same activation against the matrices of a fused group, one launch; outs[i] receives [M, f.n]
+int gemm_fused(mi8d_decoder* d, const int8_t* a, const float* qa, int M, const Fused& f, float* const* outs, cudaStream_t s,
+               int force_splits = 0, int a_rows_cap = 0, int a_row0 = 0, const unsigned* skip_a = nullptr,
+               const unsigned* skip_b = nullptr, int skip_rows_below = 0) {
+  GemmCall g;
+  g.aq = a;
+  g.bt = f.bt;
+  g.M = M;
+  g.N = f.nseg * f.n;
+  g.K = f.K;
+  g.d_qa = qa;
+  g.nseg = f.nseg;
+  for(int i = 0; i < f.nseg; ++i) {
+    g.seg_qb[i] = f.qm[i];
+    g.seg_bias[i] = f.bias[i];
+    g.seg_c[i] = outs[i];
+  }
+  g.ws = d->ws;
+  g.ws_bytes = d->ws_bytes;
+  g.stream = s;
+  g.force_splits = force_splits;
+  g.a_rows_cap = a_rows_cap;
+  g.a_row0 = a_row0;
+  g.skip_a = skip_a;
+  g.skip_b = skip_b;
+  g.skip_rows_below = skip_rows_below;
+  return launch_gemm_call(g);
+}
+
+// Int8::PrepareA of x (multiplier from the slot its producer reduced) followed by the affine: either the
+// quantisation kernel and the GEMM, or - with the option set and a shape that gives every CTA one tile - the GEMM
+// that quantises its operand while loading it.
+int quant_gemm(mi8d_decoder* d, const float* x, int M, const unsigned* slot, const Aff& w, bool relu, float* c, cudaStream_t s,
+               unsigned* absmax_out = nullptr) {
+  float* qa = reinterpret_cast<float*>(d->aq + static_cast<size_t>(M) * w.K);
+  if(d->opt_quant_in_gemm && w.K <= 1024 && quant_a_tile(M, w.N) != 0)
+    return launch_gemm_quant_a(x, slot, qa, w.bt, M, w.N, w.K, w.qm, 1.0f, w.bias, relu ? 1 : 0, c, MI8_F32, nullptr, s, absmax_out);
+  MI8D_TRY(launch_quantize_slot(x, static_cast<size_t>(M) * w.K, slot, d->aq, qa, s));
+  return gemm(d, d->aq, M, w, relu, c, s, absmax_out);
+}
+
+int add_ln(mi8d_decoder* d, const float* a, const float* resid, const Norm& n, int rows, float* out, float* rowmax, unsigned* slot,
+           cudaStream_t s, unsigned* slot2 = nullptr) {
+  return launch_add_layernorm(a, resid, n.g, n.b, 1e-6f, rows, d->cfg.dim_emb, out, rowmax, slot, s, slot2);
+}
 
 }  // namespace
 
@@ -244,6 +429,8 @@ int mi8d_create(const mi8d_config* cfg, void* arena, size_t arena_bytes, void* w
   if(cfg->enc_depth < 0 || cfg->dim_emb % 16 != 0 || cfg->dim_ffn % 16 != 0 || cfg->heads <= 0 || cfg->dim_emb % cfg->heads != 0 || cfg->dec_depth <= 0 ||
      cfg->max_rows <= 0 || cfg->max_steps <= 0 || cfg->max_batch <= 0 || cfg->max_src <= 0 || cfg->vocab <= 0)
     return MI8_ERR_BAD_ARG;
+  if(cfg->dec_depth > 16)
+    return MI8_ERR_UNSUPPORTED;
   const int dh = cfg->dim_emb / cfg->heads;
   if(dh != 64 && dh != 32)
     return MI8_ERR_UNSUPPORTED;
@@ -272,9 +459,8 @@ int mi8d_create(const mi8d_config* cfg, void* arena, size_t arena_bytes, void* w
     }
   }
   if(!cfg->ssru) {
-    bool ok = cudaStreamCreateWithFlags(&d->side[0], cudaStreamNonBlocking) == cudaSuccess &&
-              cudaStreamCreateWithFlags(&d->side[1], cudaStreamNonBlocking) == cudaSuccess;
-    for(cudaEvent_t* e : {&d->ev_x, &d->ev_hq, &d->ev_k, &d->ev_v})
+    bool ok = cudaStreamCreateWithFlags(&d->side, cudaStreamNonBlocking) == cudaSuccess;
+    for(cudaEvent_t* e : {&d->ev_fork, &d->ev_join})
       ok = ok && cudaEventCreateWithFlags(e, cudaEventDisableTiming) == cudaSuccess;
     d->overlap = ok;   // without them the step simply runs on the caller's stream alone
     if(!ok)
@@ -287,12 +473,11 @@ int mi8d_create(const mi8d_config* cfg, void* arena, size_t arena_bytes, void* w
 void mi8d_destroy(mi8d_decoder* d) {
   if(d == nullptr)
     return;
-  for(cudaStream_t st : d->side)
-    if(st != nullptr) {
-      cudaStreamSynchronize(st);
-      cudaStreamDestroy(st);
-    }
-  for(cudaEvent_t e : {d->ev_x, d->ev_hq, d->ev_k, d->ev_v})
+  if(d->side != nullptr) {
+    cudaStreamSynchronize(d->side);
+    cudaStreamDestroy(d->side);
+  }
+  for(cudaEvent_t e : {d->ev_fork, d->ev_join})
     if(e != nullptr)
       cudaEventDestroy(e);
   if(d->h_ctrl)
@@ -312,6 +497,7 @@ int mi8d_set_weight(mi8d_decoder* d, const char* name, const int8_t* bt, int K, 
   w.K = K;
   w.N = N;
   d->weights[name] = w;
+  d->dirty = true;
   return MI8_OK;
 }
 
@@ -319,6 +505,7 @@ int mi8d_set_param(mi8d_decoder* d, const char* name, const float* p) {
   if(d == nullptr || name == nullptr || p == nullptr)
     return MI8_ERR_BAD_ARG;
   d->params[name] = p;
+  d->dirty = true;
   return MI8_OK;
 }
 
@@ -326,6 +513,36 @@ int mi8d_set_positions(mi8d_decoder* d, const float* table) {
   if(d == nullptr || table == nullptr)
     return MI8_ERR_BAD_ARG;
   d->positions = table;
+  return MI8_OK;
+}
+
+int mi8d_set_option(mi8d_decoder* d, int option, int value) {
+  if(d == nullptr)
+    return MI8_ERR_BAD_ARG;
+  switch(option) {
+    case MI8D_OPT_FUSE_WEIGHTS: d->opt_fuse = value != 0; break;
+    case MI8D_OPT_QUANT_IN_GEMM: d->opt_quant_in_gemm = value != 0; break;
+    case MI8D_OPT_FUSED_OUTPUT_MAX_ROWS: d->opt_fused_out_rows = value; break;
+    case MI8D_OPT_SIDE_STREAM: d->opt_side_stream = value != 0; break;
+    case MI8D_OPT_ATTENTION_UNROLL:
+      if(value != 8 && value != 16)
+        return MI8_ERR_BAD_ARG;
+      set_attention_unroll(value);
+      break;
+    default: return MI8_ERR_BAD_ARG;
+  }
+  return MI8_OK;
+}
+
+int mi8d_search_stats(mi8d_decoder* d, double out[4], int reset) {
+  if(d == nullptr || out == nullptr)
+    return MI8_ERR_BAD_ARG;
+  out[0] = d->t_issue;
+  out[1] = d->t_wait;
+  out[2] = d->t_host;
+  out[3] = d->n_steps;
+  if(reset)
+    d->t_issue = d->t_wait = d->t_host = d->n_steps = 0;
   return MI8_OK;
 }
 
@@ -449,10 +666,13 @@ int mi8d_encode(mi8d_decoder* d, const int* ids, const float* log_mask, int batc
   const mi8d_config& c = d->cfg;
   if(c.enc_depth <= 0 || batch > c.max_batch || src > c.max_src || src > c.max_steps)
     return MI8_ERR_UNSUPPORTED;
-  if(d->positions == nullptr || d->P("Wemb") == nullptr)
+  if(d->positions == nullptr)
     return MI8_ERR_BAD_ARG;
   cudaStream_t s = as_stream(stream);
+  if(d->dirty)
+    MI8D_TRY(d->resolve(s));
   const int dm = c.dim_emb, M = batch * src;
+  const size_t n_d = static_cast<size_t>(M) * dm;
   cudaError_t e = cudaMemsetAsync(d->slots, 0, sizeof(unsigned) * d->n_slots, s);
   if(e == cudaSuccess)
     e = cudaMemcpyAsync(d->log_mask[0], log_mask, sizeof(float) * batch * src, cudaMemcpyDeviceToDevice, s);
@@ -460,35 +680,39 @@ int mi8d_encode(mi8d_decoder* d, const int* ids, const float* log_mask, int batc
     set_last_cuda_error(e);
     return MI8_ERR_LAUNCH;
   }
-  unsigned* slot = d->slots;
-  auto next_slot = [&]() { return slot++; };
+  float* aq_tail = reinterpret_cast<float*>(d->enc_aq + n_d);
   // embeddings * sqrt(d) + positions 0..src-1 (src/models/transformer.h:93,110-114)
   float* x = d->enc_x[0];
-  unsigned* x_slot = next_slot();
-  MI8D_TRY(launch_embed(d->P("Wemb"), ids, d->positions, src, sqrtf(static_cast<float>(dm)), M, dm, x, nullptr, x_slot, s));
+  unsigned* x_slot = d->slots;
+  MI8D_TRY(launch_embed(d->wemb, ids, d->positions, src, sqrtf(static_cast<float>(dm)), M, dm, x, nullptr, x_slot, s));
   for(int l = 0; l < c.enc_depth; ++l) {
-    const std::string li = "encoder_l" + std::to_string(l + 1);
-    const std::string pre = li + "_self", ffn = li + "_ffn";
-    unsigned *sa = next_slot(), *s1 = next_slot(), *s3 = next_slot();
-    // q, keys and values are the same tensor: one quantisation serves the three projections
-    MI8D_TRY(launch_quantize_slot(x, static_cast<size_t>(M) * dm, x_slot, d->enc_aq, reinterpret_cast<float*>(d->enc_aq + static_cast<size_t>(M) * dm), s));
-    MI8D_TRY(gemm(d, d->enc_aq, M, pre + "_Wq", pre + "_bq", false, d->enc_q, s));
-    MI8D_TRY(gemm(d, d->enc_aq, M, pre + "_Wk", pre + "_bk", false, d->enc_k, s));
-    MI8D_TRY(gemm(d, d->enc_aq, M, pre + "_Wv", pre + "_bv", false, d->enc_v, s));
+    const EncLayerW& w = d->enc_w[l];
+    unsigned *sa = d->enc_slot(l, 0), *s1 = d->enc_slot(l, 1), *s3 = d->enc_slot(l, 2);
+    // q, keys and values are the same tensor: one quantisation serves the three projections, and with fused
+    // weights one launch computes all three
+    MI8D_TRY(launch_quantize_slot(x, n_d, x_slot, d->enc_aq, aq_tail, s));
+    if(d->opt_fuse && w.qkv.ready) {
+      float* outs[3] = {d->enc_q, d->enc_k, d->enc_v};
+      MI8D_TRY(gemm_fused(d, d->enc_aq, aq_tail, M, w.qkv, outs, s));
+    } else {
+      MI8D_TRY(launch_gemm(d->enc_aq, w.q.bt, M, w.q.N, w.q.K, aq_tail, w.q.qm, 1.0f, w.q.bias, 0, d->enc_q, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
+      MI8D_TRY(launch_gemm(d->enc_aq, w.k.bt, M, w.k.N, w.k.K, aq_tail, w.k.qm, 1.0f, w.k.bias, 0, d->enc_k, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
+      MI8D_TRY(launch_gemm(d->enc_aq, w.v.bt, M, w.v.N, w.v.K, aq_tail, w.v.qm, 1.0f, w.v.bias, 0, d->enc_v, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
+    }
     float* a = d->enc_x[1];   // attention output, then reused as x1
     MI8D_TRY(launch_attention1(d->enc_q, d->enc_k, d->enc_v, d->log_mask[0], M, c.heads, dm / c.heads, src, batch, 2, a, sa, s));
-    MI8D_TRY(launch_quantize_slot(a, static_cast<size_t>(M) * dm, sa, d->enc_aq, reinterpret_cast<float*>(d->enc_aq + static_cast<size_t>(M) * dm), s));
-    MI8D_TRY(gemm(d, d->enc_aq, M, pre + "_Wo", pre + "_bo", false, d->enc_q, s));
-    MI8D_TRY(add_ln(d, d->enc_q, x, pre + "_Wo", M, a, nullptr, s1, s));                       // x1 = LN(Wo(a) + x)
-    MI8D_TRY(launch_quantize_slot(a, static_cast<size_t>(M) * dm, s1, d->enc_aq, reinterpret_cast<float*>(d->enc_aq + static_cast<size_t>(M) * dm), s));
-    MI8D_TRY(gemm(d, d->enc_aq, M, ffn + "_W1", ffn + "_b1", true, d->enc_h, s, s3));
-    MI8D_TRY(launch_quantize_slot(d->enc_h, static_cast<size_t>(M) * c.dim_ffn, s3, d->enc_aq,
-                                  reinterpret_cast<float*>(d->enc_aq + static_cast<size_t>(M) * c.dim_ffn), s));
-    MI8D_TRY(gemm(d, d->enc_aq, M, ffn + "_W2", ffn + "_b2", false, d->enc_q, s));
+    MI8D_TRY(launch_quantize_slot(a, n_d, sa, d->enc_aq, aq_tail, s));
+    MI8D_TRY(launch_gemm(d->enc_aq, w.o.bt, M, w.o.N, w.o.K, aq_tail, w.o.qm, 1.0f, w.o.bias, 0, d->enc_q, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
+    MI8D_TRY(add_ln(d, d->enc_q, x, w.ln_att, M, a, nullptr, s1, s));                       // x1 = LN(Wo(a) + x)
+    MI8D_TRY(launch_quantize_slot(a, n_d, s1, d->enc_aq, aq_tail, s));
+    MI8D_TRY(launch_gemm(d->enc_aq, w.w1.bt, M, w.w1.N, w.w1.K, aq_tail, w.w1.qm, 1.0f, w.w1.bias, 1, d->enc_h, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0, s3));
+    float* h_tail = reinterpret_cast<float*>(d->enc_aq + static_cast<size_t>(M) * c.dim_ffn);
+    MI8D_TRY(launch_quantize_slot(d->enc_h, static_cast<size_t>(M) * c.dim_ffn, s3, d->enc_aq, h_tail, s));
+    MI8D_TRY(launch_gemm(d->enc_aq, w.w2.bt, M, w.w2.N, w.w2.K, h_tail, w.w2.qm, 1.0f, w.w2.bias, 0, d->enc_q, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
     const bool last = l + 1 == c.enc_depth;
     float* nx = last ? d->context[0] : x;                                                     // the last layer writes the context
-    x_slot = next_slot();
-    MI8D_TRY(add_ln(d, d->enc_q, a, ffn + "_ffn", M, nx, nullptr, x_slot, s));
+    x_slot = d->enc_slot(l, 3);
+    MI8D_TRY(add_ln(d, d->enc_q, a, w.ln_ffn, M, nx, nullptr, x_slot, s));
     x = nx;
   }
   if(c.ssru) {
@@ -525,20 +749,17 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
     return MI8_ERR_BAD_ARG;
   if(t == 0 && beam != 1)
     return MI8_ERR_BAD_ARG;
-  if(d->positions == nullptr || d->P("Wemb") == nullptr)
+  if(d->positions == nullptr)
     return MI8_ERR_BAD_ARG;
   cudaStream_t s = as_stream(stream);
+  if(d->dirty)
+    MI8D_TRY(d->resolve(s));
   const int dm = c.dim_emb, S = d->src;
   const int SR = d->slab_rows;
   const size_t slab_stride = static_cast<size_t>(SR) * dm;
+  const size_t n_d = static_cast<size_t>(R) * dm;
 
-  cudaError_t e = cudaMemsetAsync(d->slots, 0, sizeof(unsigned) * d->n_slots, s);
-  if(e != cudaSuccess) {
-    set_last_cuda_error(e);
-    return MI8_ERR_LAUNCH;
-  }
-  unsigned* slot = d->slots;
-  auto next_slot = [&]() { return slot++; };
+  MI8D_CUDA(cudaMemsetAsync(d->slots, 0, sizeof(unsigned) * d->n_slots, s));
 
   // sentences that finished leave the batch: compact the encoder context, recompute cross K/V
   if(batch != d->batch) {
@@ -560,138 +781,155 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
     MI8D_TRY(launch_max_absolute(ctx, n, nullptr, cq_tail, d->ws, d->ws_bytes, s));
     MI8D_TRY(launch_quantize(ctx, n, cq_tail, d->cq, s));
     for(int l = 0; l < c.dec_depth; ++l) {
-      const std::string pre = "decoder_l" + std::to_string(l + 1) + "_context";
-      MI8D_TRY(gemm(d, d->cq, batch * S, pre + "_Wk", pre + "_bk", false, d->layers[l].cross_k, s));
-      MI8D_TRY(gemm(d, d->cq, batch * S, pre + "_Wv", pre + "_bv", false, d->layers[l].cross_v, s));
+      const DecLayerW& w = d->dec_w[l];
+      if(d->opt_fuse && w.ctx_kv.ready) {
+        float* outs[2] = {d->layers[l].cross_k, d->layers[l].cross_v};
+        MI8D_TRY(gemm_fused(d, d->cq, cq_tail, batch * S, w.ctx_kv, outs, s));
+      } else {
+        MI8D_TRY(launch_gemm(d->cq, w.ctx_k.bt, batch * S, w.ctx_k.N, w.ctx_k.K, cq_tail, w.ctx_k.qm, 1.0f, w.ctx_k.bias, 0, d->layers[l].cross_k,
+                             MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
+        MI8D_TRY(launch_gemm(d->cq, w.ctx_v.bt, batch * S, w.ctx_v.N, w.ctx_v.K, cq_tail, w.ctx_v.qm, 1.0f, w.ctx_v.bias, 0, d->layers[l].cross_v,
+                             MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
+      }
     }
     d->cross_valid = true;
   }
 
+  // Ancestor table of this step and, in the same launch, every layer's history abs-max over the earlier slabs; the
+  // producer of a layer's newest slab (embedding / the previous layer's last LayerNorm) adds that slab's maximum.
   const int anc_new = d->anc_cur ^ 1;
-  if(!c.ssru)
-    MI8D_TRY(launch_ancestors_update(d->anc[d->anc_cur], d->anc[anc_new], hyp_idx, t, R, SR, s));
+  if(!c.ssru) {
+    const float* rowmax[16];
+    unsigned* hslot[16];
+    for(int l = 0; l < c.dec_depth; ++l) {
+      rowmax[l] = d->layers[l].rowmax;
+      hslot[l] = d->layer_slot(l, kSlotHistory);
+    }
+    MI8D_TRY(launch_ancestors_update(d->anc[d->anc_cur], d->anc[anc_new], hyp_idx, t, R, SR, s, c.dec_depth, rowmax, hslot));
+  }
 
   // layer-0 input: scaled embedding of the previous word (zero at the first step) + position t
   float* x = c.ssru ? d->x_in : d->layers[0].slab + static_cast<size_t>(t) * slab_stride;
   float* x_rowmax = c.ssru ? nullptr : d->layers[0].rowmax + static_cast<size_t>(t) * SR;
-  unsigned* x_slot = next_slot();
-  MI8D_TRY(launch_embed(d->P("Wemb"), t == 0 ? nullptr : prev_words, d->positions + static_cast<size_t>(t) * dm, 0,
-                        sqrtf(static_cast<float>(dm)), R, dm, x, x_rowmax, x_slot, s));
+  MI8D_TRY(launch_embed(d->wemb, t == 0 ? nullptr : prev_words, d->positions + static_cast<size_t>(t) * dm, 0, sqrtf(static_cast<float>(dm)), R,
+                        dm, x, x_rowmax, d->input_slot(0), s, c.ssru ? nullptr : d->layer_slot(0, kSlotHistory)));
 
   const int cell_new = d->cell_cur ^ 1;
+  float* aq_tail = reinterpret_cast<float*>(d->aq + n_d);
   for(int l = 0; l < c.dec_depth; ++l) {
     LayerBufs& L = d->layers[l];
-    const std::string li = "decoder_l" + std::to_string(l + 1);
-    unsigned* s1 = next_slot();
+    const DecLayerW& w = d->dec_w[l];
+    unsigned* x_slot = d->input_slot(l);
+    unsigned* s1 = d->layer_slot(l, kSlotSelfLn);
     if(c.ssru) {
-      const std::string pre = li + "_rnn";
-      MI8D_TRY(quant(d, x, R, dm, x_slot, d->aq, s));
-      MI8D_TRY(gemm(d, d->aq, R, pre + "_W", "", false, d->qbuf, s));        // dot(input, W)
-      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wf", pre + "_bf", false, d->fbuf, s));  // affine(input, Wf, bf)
+      MI8D_TRY(launch_quantize_slot(x, n_d, x_slot, d->aq, aq_tail, s));
+      if(d->opt_fuse && w.rnn.ready) {
+        float* outs[2] = {d->qbuf, d->fbuf};
+        MI8D_TRY(gemm_fused(d, d->aq, aq_tail, R, w.rnn, outs, s));            // dot(input, W) and affine(input, Wf, bf)
+      } else {
+        MI8D_TRY(gemm(d, d->aq, R, w.rnn_w, false, d->qbuf, s));
+        MI8D_TRY(gemm(d, d->aq, R, w.rnn_wf, false, d->fbuf, s));
+      }
       MI8D_TRY(launch_ssru_cell(L.cell[d->cell_cur], t == 0 ? nullptr : hyp_idx, d->qbuf, d->fbuf, R, dm, L.cell[cell_new], d->abuf, s));
-      MI8D_TRY(add_ln(d, d->abuf, x, pre + "_ffn", R, d->x1, nullptr, s1, s));
+      MI8D_TRY(add_ln(d, d->abuf, x, w.ln_self, R, d->x1, nullptr, s1, s));
     } else {
-      const std::string pre = li + "_self";
-      unsigned* sh = next_slot();
-      unsigned* sa = next_slot();
-      // Keys and values are projections of the WHOLE history of layer inputs, quantised with one
-      // multiplier over the live part of that history.  The projections of earlier steps are kept per slab
-      // and stay valid as long as that multiplier's abs-max does not change (compared bit for bit on the
-      // device); then only the newest slab is quantised and projected, otherwise everything is redone.
-      // This chain only needs x and the ancestor table, so it runs beside the query projection.
-      const bool ov = d->overlap;
-      cudaStream_t sk = ov ? d->side[0] : s;   // abs-max, quantise, key GEMM
-      cudaStream_t sv = ov ? d->side[1] : s;   // value GEMM
-      if(ov) {
-        MI8D_CUDA(cudaEventRecord(d->ev_x, s));
-        MI8D_CUDA(cudaStreamWaitEvent(sk, d->ev_x, 0));
-      }
+      unsigned* sh = d->layer_slot(l, kSlotHistory);
+      unsigned* sa = d->layer_slot(l, kSlotSelfAtt);
+      // Keys and values are projections of the WHOLE history of layer inputs, quantised with one multiplier over the
+      // live part of that history.  The projections of earlier steps are kept per slab and stay valid as long as that
+      // multiplier's abs-max does not change (compared bit for bit on the device): then only the newest slab is
+      // quantised and projected, otherwise everything is.  One launch quantises the layer input twice - with its own
+      // multiplier for the query projection and, as the newest history slab, with the history's.
       const int steps = t + 1;
-      float* hq_tail = reinterpret_cast<float*>(L.hq + static_cast<size_t>(c.max_steps) * c.max_rows * dm);
-      MI8D_TRY(launch_history_absmax(L.rowmax, d->anc[anc_new], steps, R, SR, sh, sk));
-      MI8D_TRY(launch_history_quantize(L.slab, SR, steps, dm, sh, d->prev_bits + l, L.hq, hq_tail, sk));
-      if(ov) {
-        MI8D_CUDA(cudaEventRecord(d->ev_hq, sk));
-        MI8D_CUDA(cudaStreamWaitEvent(sv, d->ev_hq, 0));
+      const int cap_rows = c.max_steps * c.max_rows;
+      float* hq_tail = reinterpret_cast<float*>(L.hq + static_cast<size_t>(cap_rows) * dm);
+      MI8D_TRY(launch_quantize_dual(x, n_d, x_slot, d->aq, aq_tail, L.slab, SR, steps, R, dm, sh, d->prev_bits + l, L.hq, hq_tail, s));
+      const bool fused = d->opt_fuse && w.self_kv.ready;
+      float* kv_new[2] = {L.kslab + static_cast<size_t>(t) * slab_stride, L.vslab + static_cast<size_t>(t) * slab_stride};
+      float* kv_all[2] = {L.kslab, L.vslab};
+      const bool side = t > 0 && d->overlap && d->opt_side_stream;
+      cudaStream_t so = side ? d->side : s;
+      if(t > 0) {
+        // earlier slabs: recomputed only when the abs-max changed (all tiles skipped otherwise); no split-K, the two
+        // streams must not share the workspace's counters
+        if(side) {
+          MI8D_CUDA(cudaEventRecord(d->ev_fork, s));
+          MI8D_CUDA(cudaStreamWaitEvent(so, d->ev_fork, 0));
+        }
+        if(fused) {
+          MI8D_TRY(gemm_fused(d, L.hq, hq_tail, t * SR, w.self_kv, kv_all, so, 1, cap_rows, 0, d->prev_bits + l, sh, t * SR));
+        } else {
+          MI8D_TRY(launch_gemm(L.hq, w.self_k.bt, t * SR, w.self_k.N, w.self_k.K, hq_tail, w.self_k.qm, 1.0f, w.self_k.bias, 0, L.kslab, MI8_F32,
+                               nullptr, d->ws, d->ws_bytes, so, 0, 1, nullptr, d->prev_bits + l, sh, t * SR));
+          MI8D_TRY(launch_gemm(L.hq, w.self_v.bt, t * SR, w.self_v.N, w.self_v.K, hq_tail, w.self_v.qm, 1.0f, w.self_v.bias, 0, L.vslab, MI8_F32,
+                               nullptr, d->ws, d->ws_bytes, so, 0, 1, nullptr, d->prev_bits + l, sh, t * SR));
+        }
+        if(side)
+          MI8D_CUDA(cudaEventRecord(d->ev_join, so));
       }
-      const Weight* wk = d->W(pre + "_Wk");
-      const Weight* wv = d->W(pre + "_Wv");
-      const float* bk = d->P(pre + "_bk");
-      const float* bv = d->P(pre + "_bv");
-      if(wk == nullptr || wv == nullptr || bk == nullptr || bv == nullptr)
-        return MI8_ERR_BAD_ARG;
-      // no split-K here (force_splits = 1): the three streams must not share the workspace's counters
-      MI8D_TRY(launch_gemm(L.hq, wk->bt, steps * SR, wk->N, wk->K, hq_tail, wk->qm(), 1.0f, bk, 0, L.kslab, MI8_F32, nullptr, d->ws,
-                           d->ws_bytes, sk, 0, 1, nullptr, d->prev_bits + l, sh, t * SR));
-      MI8D_TRY(launch_gemm(L.hq, wv->bt, steps * SR, wv->N, wv->K, hq_tail, wv->qm(), 1.0f, bv, 0, L.vslab, MI8_F32, nullptr, d->ws,
-                           d->ws_bytes, sv, 0, 1, nullptr, d->prev_bits + l, sh, t * SR));
-      MI8D_TRY(quant(d, x, R, dm, x_slot, d->aq, s));
-      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wq", pre + "_bq", false, d->qbuf, s, nullptr, ov ? 1 : 0));
-      if(ov) {
-        MI8D_CUDA(cudaEventRecord(d->ev_k, sk));
-        MI8D_CUDA(cudaEventRecord(d->ev_v, sv));
-        MI8D_CUDA(cudaStreamWaitEvent(s, d->ev_k, 0));
-        MI8D_CUDA(cudaStreamWaitEvent(s, d->ev_v, 0));
+      MI8D_TRY(gemm(d, d->aq, R, w.self_q, false, d->qbuf, s, nullptr, side ? 1 : 0));
+      // newest slab: always projected, as a problem of its own (R live rows on narrow tiles)
+      if(fused) {
+        MI8D_TRY(gemm_fused(d, L.hq, hq_tail, R, w.self_kv, kv_new, s, 1, cap_rows, t * SR));
+      } else {
+        const int8_t* a_new = L.hq + static_cast<size_t>(t) * slab_stride;
+        MI8D_TRY(launch_gemm(a_new, w.self_k.bt, R, w.self_k.N, w.self_k.K, hq_tail, w.self_k.qm, 1.0f, w.self_k.bias, 0, kv_new[0], MI8_F32,
+                             nullptr, d->ws, d->ws_bytes, s, 0, 1));
+        MI8D_TRY(launch_gemm(a_new, w.self_v.bt, R, w.self_v.N, w.self_v.K, hq_tail, w.self_v.qm, 1.0f, w.self_v.bias, 0, kv_new[1], MI8_F32,
+                             nullptr, d->ws, d->ws_bytes, s, 0, 1));
       }
+      if(side)
+        MI8D_CUDA(cudaStreamWaitEvent(s, d->ev_join, 0));
       MI8D_TRY(launch_attention1(d->qbuf, L.kslab, L.vslab, nullptr, R, c.heads, dm / c.heads, steps, batch, 0, d->abuf, sa, s,
                                  d->anc[anc_new], SR, SR));
-      MI8D_TRY(quant(d, d->abuf, R, dm, sa, d->aq, s));
-      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wo", pre + "_bo", false, d->obuf, s));
-      MI8D_TRY(add_ln(d, d->obuf, x, pre + "_Wo", R, d->x1, nullptr, s1, s));
+      MI8D_TRY(quant_gemm(d, d->abuf, R, sa, w.self_o, false, d->obuf, s));
+      MI8D_TRY(add_ln(d, d->obuf, x, w.ln_self, R, d->x1, nullptr, s1, s));
     }
     {
-      const std::string pre = li + "_context";
-      unsigned* sa = next_slot();
-      unsigned* s2 = next_slot();
-      MI8D_TRY(quant(d, d->x1, R, dm, s1, d->aq, s));
-      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wq", pre + "_bq", false, d->qbuf, s));
+      unsigned* sa = d->layer_slot(l, kSlotCtxAtt);
+      unsigned* s2 = d->layer_slot(l, kSlotCtxLn);
+      MI8D_TRY(quant_gemm(d, d->x1, R, s1, w.ctx_q, false, d->qbuf, s));
       MI8D_TRY(launch_attention1(d->qbuf, L.cross_k, L.cross_v, lmask, R, c.heads, dm / c.heads, S, batch, 1, d->abuf, sa, s));
-      MI8D_TRY(quant(d, d->abuf, R, dm, sa, d->aq, s));
-      MI8D_TRY(gemm(d, d->aq, R, pre + "_Wo", pre + "_bo", false, d->obuf, s));
-      MI8D_TRY(add_ln(d, d->obuf, d->x1, pre + "_Wo", R, d->x2, nullptr, s2, s));
+      MI8D_TRY(quant_gemm(d, d->abuf, R, sa, w.ctx_o, false, d->obuf, s));
+      MI8D_TRY(add_ln(d, d->obuf, d->x1, w.ln_ctx, R, d->x2, nullptr, s2, s));
 
-      const std::string ffn = li + "_ffn";
-      unsigned* s3 = next_slot();
-      MI8D_TRY(quant(d, d->x2, R, dm, s2, d->aq, s));
-      MI8D_TRY(gemm(d, d->aq, R, ffn + "_W1", ffn + "_b1", true, d->hbuf, s, s3));   // ReLU and max|h| fused in the write-back
-      MI8D_TRY(quant(d, d->hbuf, R, c.dim_ffn, s3, d->aq, s));
-      MI8D_TRY(gemm(d, d->aq, R, ffn + "_W2", ffn + "_b2", false, d->obuf, s));
-      // the block's output is the next layer's input: write it straight into that layer's history slab
+      unsigned* s3 = d->layer_slot(l, kSlotRelu);
+      MI8D_TRY(quant_gemm(d, d->x2, R, s2, w.w1, true, d->hbuf, s, s3));   // ReLU and max|h| fused in the write-back
+      float* h_tail = reinterpret_cast<float*>(d->aq + static_cast<size_t>(R) * c.dim_ffn);
+      MI8D_TRY(launch_quantize_slot(d->hbuf, static_cast<size_t>(R) * c.dim_ffn, s3, d->aq, h_tail, s));
+      MI8D_TRY(gemm(d, d->aq, R, w.w2, false, d->obuf, s));
+      // the block's output is the next layer's input: write it straight into that layer's history slab, and its
+      // maximum into that layer's history abs-max as well
       const bool last = l + 1 == c.dec_depth;
       float* nx = last ? d->x_final : (c.ssru ? d->x_in : d->layers[l + 1].slab + static_cast<size_t>(t) * slab_stride);
       float* nx_rowmax = (last || c.ssru) ? nullptr : d->layers[l + 1].rowmax + static_cast<size_t>(t) * SR;
-      x_slot = next_slot();
-      MI8D_TRY(add_ln(d, d->obuf, d->x2, ffn + "_ffn", R, nx, nx_rowmax, x_slot, s));
+      unsigned* nx_hist = (last || c.ssru) ? nullptr : d->layer_slot(l + 1, kSlotHistory);
+      MI8D_TRY(add_ln(d, d->obuf, d->x2, w.ln_ffn, R, nx, nx_rowmax, d->layer_slot(l, kSlotOut), s, nx_hist));
       x = nx;
     }
   }
 
   // tied output layer, then log-softmax + n-best per sentence over beam x vocabulary
-  const float* out_b = d->P("decoder_ff_logit_out_b");
-  const Weight* wout = d->W("Wemb_intgemm8");
-  if(out_b == nullptr || wout == nullptr)
-    return MI8_ERR_BAD_ARG;
-  MI8D_TRY(quant(d, x, R, dm, x_slot, d->aq, s));
-  // Below 512 rows the GEMM whose write-back reduces the 128-word blocks is faster than writing the logits and
-  // reading them back (measured 49 vs 67 us at 256 rows, 33 vs 64 at 128); at 512 rows the two are equal (80 vs 78 us)
-  // and for greedy search the plain GEMM followed by the log-softmax / top-k kernel wins.
-  const bool fused_output = !d->keep_logits && R <= 480 && n_best >= 2;
+  unsigned* x_slot = d->input_slot(c.dec_depth);
+  MI8D_TRY(launch_quantize_slot(x, n_d, x_slot, d->aq, aq_tail, s));
+  // Up to opt_fused_out_rows rows the GEMM whose write-back reduces the 128-word blocks is faster than writing the logits
+  // and reading them back; for greedy search the plain GEMM followed by the log-softmax / top-k kernel wins.
+  const bool fused_output = !d->keep_logits && R <= d->opt_fused_out_rows && n_best >= 2;
   if(!fused_output) {
-    MI8D_TRY(gemm(d, d->aq, R, "Wemb_intgemm8", "decoder_ff_logit_out_b", false, d->logits, s));
+    MI8D_TRY(gemm(d, d->aq, R, d->out_w, false, d->logits, s));
     MI8D_TRY(launch_lse_topk(d->logits, R, c.vocab, n_best, prev_scores, d->cand_score, d->cand_word, s));
   } else {
     // the GEMM's write-back reduces every 128-word block of a row; the logits never reach memory
     const int k_top = n_best <= 4 ? 4 : 8;
-    const float* qa = reinterpret_cast<const float*>(d->aq + static_cast<size_t>(R) * dm);
-    MI8D_TRY(launch_gemm_logits(d->aq, qa, wout->bt, wout->qm(), R, c.vocab, dm, out_b, 1.0f, k_top, d->blk_max, d->blk_sum, d->blk_topv,
-                                d->blk_topi, nullptr, s));
+    MI8D_TRY(launch_gemm_logits(d->aq, aq_tail, d->out_w.bt, d->out_w.qm, R, c.vocab, dm, d->out_bias, 1.0f, k_top, d->blk_max, d->blk_sum,
+                                d->blk_topv, d->blk_topi, nullptr, s));
     MI8D_TRY(launch_lse_merge(d->blk_max, d->blk_sum, d->blk_topv, d->blk_topi, R, c.vocab, k_top, n_best, prev_scores, d->cand_score,
                               d->cand_word, s));
   }
   MI8D_TRY(launch_nbest_merge(d->cand_score, d->cand_word, beam, batch, c.vocab, n_best, out_score, out_beam, out_word, s));
 
-  if(!c.ssru)   // remember which abs-max the stored keys/values of every layer now belong to (slot 2 + 7*layer)
-    MI8D_TRY(launch_history_commit(d->prev_bits, d->slots, 2, 7, c.dec_depth, d->reuse_stats, s));
+  if(!c.ssru)   // remember which abs-max the stored keys/values of every layer now belong to
+    MI8D_TRY(launch_history_commit(d->prev_bits, d->slots, 1 + kSlotHistory, kSlotsPerLayer, c.dec_depth, d->reuse_stats, s));
   d->anc_cur = anc_new;
   d->cell_cur = cell_new;
   d->t = t + 1;
@@ -736,6 +974,9 @@ int mi8d_search(mi8d_decoder* d, const int* ids, const float* log_mask, int batc
   int prev_dim = B0;
   unsigned long long up_bytes = 0, down_bytes = 0;
 
+  using clk = std::chrono::steady_clock;
+  auto secs = [](clk::time_point a, clk::time_point b) { return std::chrono::duration<double>(b - a).count(); };
+  clk::time_point mark = clk::now();
   for(int t = 0;; ++t) {
     int max_beam = 0;
     active.clear();
@@ -779,11 +1020,19 @@ int mi8d_search(mi8d_decoder* d, const int* ids, const float* log_mask, int batc
     float* o_score = reinterpret_cast<float*>(d->s_out);
     int* o_beam = d->s_out + cells;
     int* o_word = d->s_out + 2 * cells;
+    const clk::time_point t_a = clk::now();
     rc = mi8d_step(d, hyp, pw, bidx, ps, tensor_beam, nb, n_best, o_score, o_beam, o_word, stream);
     if(rc != MI8_OK)
       return rc;
     MI8D_CUDA(cudaMemcpyAsync(d->h_out, d->s_out, static_cast<size_t>(3 * cells) * sizeof(int), cudaMemcpyDeviceToHost, s));
+    const clk::time_point t_b = clk::now();
     MI8D_CUDA(cudaStreamSynchronize(s));
+    const clk::time_point t_c = clk::now();
+    d->t_host += secs(mark, t_a);
+    d->t_issue += secs(t_a, t_b);
+    d->t_wait += secs(t_b, t_c);
+    d->n_steps += 1;
+    mark = t_c;
     down_bytes += static_cast<size_t>(3 * cells) * sizeof(int);
     const float* nv = reinterpret_cast<const float*>(d->h_out);
     const int* nbm = d->h_out + cells;

@@ -43,6 +43,7 @@ constexpr int kThreads = 320;
 constexpr int kEpilogueThreads = 256;
 constexpr int kMaxStages = 8;
 constexpr int kPairTileCode = 512;  // force_tile_m value that selects the CTA-pair kernel
+constexpr int kMaxSegments = 3;
 
 template <int TM>
 struct TileCfg {
@@ -108,6 +109,19 @@ struct GemmParams {
   const int32_t* p8_zp_b;
   const int32_t* p8_off_b;
   int* status;
+  // Several weight matrices of the same shape [seg_n, K] stored one behind the other and multiplied with the
+  // same activation in one launch (Wk|Wv of an attention block, Wq|Wk|Wv of the encoder): segment s covers
+  // weight rows [s * seg_n, (s + 1) * seg_n), has its own multiplier, bias and output matrix [M, seg_n].
+  // seg_n is a multiple of 128, so a tile never straddles two segments.  nseg == 1: the plain call
+  // (seg_n = N, seg_qb[0] = d_qb, seg_bias[0] = bias, seg_c[0] = c).
+  int nseg, seg_n;
+  const float* seg_qb[kMaxSegments];
+  const float* seg_bias[kMaxSegments];
+  void* seg_c[kMaxSegments];
+  int a_row0;               // first row of the activation inside its tensor map (a slab of a larger buffer)
+  int* rows_computed;       // optional (measurement): receives the number of activation rows this launch really computed
+  int withhold_item;        // test hook: the producer leaves out the loads of this pipeline item (-1 = none)
+  uint32_t spin_limit;      // bound of every barrier wait of this launch
 };
 
 struct WorkItem {
@@ -152,12 +166,12 @@ __device__ __forceinline__ unsigned pack4_i8(const float4& v, float qm) {
 // the whole chunk so the columns overlap in the pipeline.  Returns the running max|C| bit pattern.
 template <int CH>
 __device__ __forceinline__ unsigned write_back_chunk(const GemmParams& p, const int32_t (&v)[CH], size_t base, int valid, float unquant,
-                                                     float bias_n, unsigned out_max) {
+                                                     float bias_n, unsigned out_max, void* c, int ldc, bool has_bias) {
   float f[CH];
 #pragma unroll
   for(int j = 0; j < CH; ++j)
     f[j] = __fmul_rn(__int2float_rn(v[j]), unquant);
-  if(p.bias != nullptr) {
+  if(has_bias) {
 #pragma unroll
     for(int j = 0; j < CH; ++j)
       f[j] = __fadd_rn(f[j], bias_n);
@@ -173,30 +187,30 @@ __device__ __forceinline__ unsigned write_back_chunk(const GemmParams& p, const 
       if(j < valid)
         out_max = max(out_max, __float_as_uint(f[j]) & 0x7fffffffu);
   }
-  if(p.acc_out != nullptr) {
+  if(p.acc_out != nullptr) {   // (single-segment launches only: ldc == N)
     int32_t* dst = p.acc_out + base;
 #pragma unroll
     for(int j = 0; j < CH; ++j)
       if(j < valid)
-        dst[static_cast<size_t>(j) * p.N] = v[j];
+        dst[static_cast<size_t>(j) * ldc] = v[j];
   }
   if(p.out_f16) {
-    __half* dst = reinterpret_cast<__half*>(p.c) + base;
+    __half* dst = reinterpret_cast<__half*>(c) + base;
 #pragma unroll
     for(int j = 0; j < CH; ++j)
       if(j < valid)
-        dst[static_cast<size_t>(j) * p.N] = __float2half_rn(f[j]);
+        dst[static_cast<size_t>(j) * ldc] = __float2half_rn(f[j]);
   } else {
-    float* dst = reinterpret_cast<float*>(p.c) + base;
+    float* dst = reinterpret_cast<float*>(c) + base;
     if(valid >= CH) {
 #pragma unroll
       for(int j = 0; j < CH; ++j)
-        dst[static_cast<size_t>(j) * p.N] = f[j];
+        dst[static_cast<size_t>(j) * ldc] = f[j];
     } else {
 #pragma unroll
       for(int j = 0; j < CH; ++j)
         if(j < valid)
-          dst[static_cast<size_t>(j) * p.N] = f[j];
+          dst[static_cast<size_t>(j) * ldc] = f[j];
     }
   }
   return out_max;
@@ -282,6 +296,11 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   const int lane = threadIdx.x & 31;
 
   pdl_launch_dependents();  // the next kernel on the stream may begin its own set-up now
+  unsigned long long* tb = trace_open();
+  constexpr int kTraceId = kTopK > 0 ? kTrGemmLogits : (kQuantA ? kTrGemmQuantA : kTrGemm);
+  const unsigned long long trace_extra = static_cast<unsigned long long>(p.N) | (static_cast<unsigned long long>(p.K) << 20) |
+                                         (static_cast<unsigned long long>(p.M) << 40);
+  trace_stamp(tb, kTraceId, 0, trace_extra);
   if(threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_a);
@@ -315,7 +334,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     // are requested before waiting for it, the activation tiles (its output) after.
     uint32_t it = 0;
     uint32_t prefetched = 0;  // stages whose weight tile is already in flight
-    if(p.skip_a == nullptr && kTopK == 0) {   // (output-layer variant: the M-side operand is the activation, nothing to prefetch)
+    if(p.skip_a == nullptr && kTopK == 0 && p.withhold_item < 0) {   // (output-layer variant: the M-side operand is the activation, nothing to prefetch)
       const WorkItem w0 = decode_work(p, blockIdx.x);
       const int n_pre = min(T::kStages, w0.kb_end - w0.kb_begin);
       if(elect_one()) {
@@ -330,6 +349,8 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     }
     pdl_wait();
     const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
+    if(p.rows_computed != nullptr && blockIdx.x == 0 && lane == 0)
+      *p.rows_computed = p.M - (skip_on ? min(p.M, (p.skip_rows_below / TM) * TM) : 0);
     for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
       const WorkItem wi = decode_work(p, w);
       if(skip_on && (wi.m_tile + 1) * TM <= p.skip_rows_below)
@@ -339,10 +360,12 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const uint32_t ph = (it / T::kStages) & 1u;
         const bool pre = it < prefetched;
         if(!pre)
-          ok = mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag);   // every lane polls: the branch stays warp-uniform
+          ok = mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag, p.spin_limit);   // every lane polls: the branch stays warp-uniform
         ok = __all_sync(0xffffffffu, ok);
         if(!ok)
           break;
+        if(static_cast<int>(it) == p.withhold_item)
+          continue;   // test hook: this item's operands never arrive, so the roles that wait for them run out of patience
         if(elect_one()) {
           uint8_t* st = tiles + s * T::kStageBytes;
           if(!pre) {
@@ -350,7 +373,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             tma_load_2d(st, &tmap_w, kb * kTileKBytes, wi.n_tile * kTileN, &ctl->full[s]);
           }
           if(!kQuantA)
-            tma_load_2d(st + T::kWBytes, &tmap_a, kb * kTileKBytes, wi.m_tile * TM, &ctl->full[s]);
+            tma_load_2d(st + T::kWBytes, &tmap_a, kb * kTileKBytes, p.a_row0 + wi.m_tile * TM, &ctl->full[s]);
         }
         __syncwarp();
       }
@@ -363,7 +386,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const uint32_t first = it > static_cast<uint32_t>(T::kStages) ? it - T::kStages : 0u;
         int no_abort = 0;
         for(uint32_t j = first; j < it; ++j)
-          mbar_wait_bounded(&ctl->full[j % T::kStages], (j / T::kStages) & 1u, &no_abort);
+          mbar_wait_bounded(&ctl->full[j % T::kStages], (j / T::kStages) & 1u, &no_abort, p.spin_limit);
       }
       __syncwarp();
     }
@@ -371,11 +394,11 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     // ------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = kP8 ? make_idesc_i8_ub(TM) : make_idesc_i8(TM);
     uint32_t it = 0, acc_it = 0;
-    bool skip_on = false;
-    if(p.skip_a != nullptr) {
-      pdl_wait();  // the skip words are written by earlier kernels of the stream
-      skip_on = *p.skip_a == *p.skip_b;
-    }
+    // No MMA can be issued before the activation tiles arrive, and those are requested after the producer's
+    // pdl_wait(): waiting here as well costs nothing and keeps the predecessor's run time out of the bounded
+    // waits below (it also orders the read of the skip words, which earlier kernels of the stream write).
+    pdl_wait();
+    const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
     for(int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
       const WorkItem wi = decode_work(p, w);
       if(skip_on && (wi.m_tile + 1) * TM <= p.skip_rows_below)
@@ -384,7 +407,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const uint32_t aph = (acc_it >> 1) & 1u;
       // The whole warp walks the loop and polls the barriers, so every value below is warp-uniform;
       // one elected lane issues the MMAs and commits.
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->tmem_empty[as], aph ^ 1u, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->tmem_empty[as], aph ^ 1u, abort_flag, p.spin_limit));
       if(!ok)
         break;
       tc_fence_after_sync();
@@ -392,7 +415,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
         const uint32_t s = it % T::kStages;
         const uint32_t ph = (it / T::kStages) & 1u;
-        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->full[s], ph, abort_flag));
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->full[s], ph, abort_flag, p.spin_limit));
         if(!ok)
           break;
         tc_fence_after_sync();
@@ -432,6 +455,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     constexpr int kChunkStep = kChunks > 1 ? 2 : 1;
     const bool has_chunks = kChunks > 1 || group == 0;
     pdl_wait();  // the activation multiplier (or abs-max slot) is written by the previous kernel
+    trace_stamp(tb, kTraceId, 1, trace_extra);
     float qa;
     if(kQuantA) {
       const unsigned bits = *p.a_slot;
@@ -447,7 +471,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     } else {
       qa = *p.d_qa;
     }
-    const float unquant = kP8 ? 1.0f : __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.d_qb)), p.scale);
+    float unquant = kP8 ? 1.0f : __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.seg_qb[0])), p.scale);
     uint32_t acc_it = 0;
     uint32_t conv_it = 0;
     const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
@@ -484,7 +508,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             if(kb0 + b < wi.kb_end && ok) {
               const uint32_t s = conv_it % T::kStages;
               const uint32_t ph = (conv_it / T::kStages) & 1u;
-              ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag));
+              ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag, p.spin_limit));
               if(ok) {
                 uint8_t* a_tile = tiles + s * T::kStageBytes + T::kWBytes;
 #pragma unroll
@@ -515,7 +539,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const uint32_t as = acc_it & 1u;
       const uint32_t aph = (acc_it >> 1) & 1u;
       if(lane == 0)
-        ok = mbar_wait_bounded(&ctl->tmem_full[as], aph, abort_flag);
+        ok = mbar_wait_bounded(&ctl->tmem_full[as], aph, abort_flag, p.spin_limit);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if(!ok)
         break;
@@ -526,6 +550,16 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const bool n_ok = n < p.N;
       const int m0 = wi.m_tile * TM;
       const int cols_valid = min(TM, p.M - m0);  // activation rows of this tile that exist
+      // the weight segment this tile belongs to: its multiplier, bias, output matrix and the column inside it
+      int seg = 0, n_loc = n;
+      if(!kP8 && kTopK == 0 && p.nseg > 1) {
+        seg = (wi.n_tile * kTileN) / p.seg_n;
+        n_loc = n - seg * p.seg_n;
+        unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.seg_qb[seg])), p.scale);
+      }
+      const float* seg_bias = p.seg_bias[seg];
+      void* seg_c = p.seg_c[seg];
+      const int ldc = p.seg_n;
       if constexpr(kTopK > 0) {
         // Output layer: lane = query row n, columns = vocabulary entries m0 .. m0 + TM - 1; warp group g takes
         // the 128-column block g of the tile.  Value = float(acc) * unquant + bias[column], rounded as in the
@@ -640,7 +674,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         ++acc_it;
         continue;
       }
-      const float bias_n = (p.bias != nullptr && n_ok) ? __ldg(p.bias + n) : 0.0f;
+      const float bias_n = (seg_bias != nullptr && n_ok) ? __ldg(seg_bias + n_loc) : 0.0f;
       float p8_scale_b = 0.0f;
       int p8_zp_b = 0, p8_off_b = 0;
       if constexpr(kP8) {
@@ -708,8 +742,8 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
               write_back_chunk_p8<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * p.N + n, cols_valid - col0, m0 + col0, p8_scale_b, p8_zp_b,
                                              p8_off_b, bias_n);
           } else if(n_ok)
-            out_max = write_back_chunk<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * p.N + n, cols_valid - col0, unquant, bias_n,
-                                                  out_max);
+            out_max = write_back_chunk<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * ldc + n_loc, cols_valid - col0, unquant, bias_n,
+                                                  out_max, seg_c, ldc, seg_bias != nullptr);
         }
       }
       if(p.absmax_out != nullptr) {
@@ -739,7 +773,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       if(lane == 0) {
         int no_abort = 0;
         tc_commit(&ctl->drain);
-        drained = mbar_wait_bounded(&ctl->drain, 0u, &no_abort);
+        drained = mbar_wait_bounded(&ctl->drain, 0u, &no_abort, p.spin_limit);
         if(!drained)
           atomicMax(p.status, static_cast<int>(kDevTimeoutDrain));
       }
@@ -748,6 +782,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, T::kTmemCols);
   }
+  trace_stamp(tb, kTraceId, 2, trace_extra);
 }
 
 // ------------------------------------------------------------------ CTA-pair variant (large M)
@@ -796,6 +831,10 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   const uint32_t peer_abort = mapa_shared(smem_u32(&ctl->abort), rank ^ 1u);
 
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  const unsigned long long trace_extra = static_cast<unsigned long long>(p.N) | (static_cast<unsigned long long>(p.K) << 20) |
+                                         (static_cast<unsigned long long>(p.M) << 40);
+  trace_stamp(tb, kTrGemmPair, 0, trace_extra);
   if(threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_a);
@@ -829,7 +868,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     uint32_t prefetched = 0;
     // copies of both CTAs are credited to full[s] of the rank-0 CTA
     auto full_addr = [&](uint32_t s) { return mapa_shared(smem_u32(&ctl->full[s]), 0u); };
-    if(p.skip_a == nullptr && pair_id < p.total_work) {
+    if(p.skip_a == nullptr && pair_id < p.total_work && p.withhold_item < 0) {
       // weights do not depend on the previous kernel: request the first pipeline fill before waiting for it
       const WorkItem w0 = decode_work(p, pair_id);
       const int n_pre = min(T::kStages, w0.kb_end - w0.kb_begin);
@@ -846,6 +885,8 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     }
     pdl_wait();
     const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
+    if(p.rows_computed != nullptr && blockIdx.x == 0 && lane == 0)
+      *p.rows_computed = p.M - (skip_on ? min(p.M, (p.skip_rows_below / T::kTM) * T::kTM) : 0);
     for(int w = pair_id; w < p.total_work && ok; w += n_pairs) {
       const WorkItem wi = decode_work(p, w);
       if(skip_on && (wi.m_tile + 1) * T::kTM <= p.skip_rows_below)
@@ -855,10 +896,12 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         const uint32_t ph = (it / T::kStages) & 1u;
         const bool pre = it < prefetched;
         if(!pre)
-          ok = mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag);
+          ok = mbar_wait_bounded(&ctl->empty[s], ph ^ 1u, abort_flag, p.spin_limit);
         ok = __all_sync(0xffffffffu, ok);
         if(!ok)
           break;
+        if(static_cast<int>(it) == p.withhold_item)
+          continue;   // test hook (both CTAs of the pair leave the item out)
         if(elect_one()) {
           uint8_t* st = tiles + s * T::kStageBytes;
           if(!pre) {
@@ -866,8 +909,8 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
               mbar_arrive_expect_tx(&ctl->full[s], 2 * T::kStageBytes);
             tma_load_2d_pair(st, &tmap_w, kb * kTileKBytes, (2 * wi.n_tile + static_cast<int>(rank)) * kTileN, full_addr(s));
           }
-          tma_load_2d_pair(st + T::kWBytes, &tmap_a, kb * kTileKBytes, wi.m_tile * T::kTM + static_cast<int>(rank) * T::kHalfRows,
-                           full_addr(s));
+          tma_load_2d_pair(st + T::kWBytes, &tmap_a, kb * kTileKBytes,
+                           p.a_row0 + wi.m_tile * T::kTM + static_cast<int>(rank) * T::kHalfRows, full_addr(s));
         }
         __syncwarp();
       }
@@ -882,7 +925,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
           const uint32_t first = it > static_cast<uint32_t>(T::kStages) ? it - T::kStages : 0u;
           int no_abort = 0;
           for(uint32_t j = first; j < it; ++j)
-            mbar_wait_bounded(&ctl->full[j % T::kStages], (j / T::kStages) & 1u, &no_abort);
+            mbar_wait_bounded(&ctl->full[j % T::kStages], (j / T::kStages) & 1u, &no_abort, p.spin_limit);
         }
       }
       __syncwarp();
@@ -892,18 +935,15 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     if(leader) {
       constexpr uint32_t idesc = kP8 ? make_idesc_i8_ub(T::kTM, 256) : make_idesc_i8(T::kTM, 256);
       uint32_t it = 0, acc_it = 0;
-      bool skip_on = false;
-      if(p.skip_a != nullptr) {
-        pdl_wait();
-        skip_on = *p.skip_a == *p.skip_b;
-      }
+      pdl_wait();   // as in the single-CTA kernel: keeps the predecessor's run time out of the bounded waits
+      const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
       for(int w = pair_id; w < p.total_work && ok; w += n_pairs) {
         const WorkItem wi = decode_work(p, w);
         if(skip_on && (wi.m_tile + 1) * T::kTM <= p.skip_rows_below)
           continue;
         const uint32_t as = acc_it & 1u;
         const uint32_t aph = (acc_it >> 1) & 1u;
-        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->tmem_empty[as], aph ^ 1u, abort_flag));
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->tmem_empty[as], aph ^ 1u, abort_flag, p.spin_limit));
         if(!ok)
           break;
         tc_fence_after_sync();
@@ -911,7 +951,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         for(int kb = wi.kb_begin; kb < wi.kb_end; ++kb, ++it) {
           const uint32_t s = it % T::kStages;
           const uint32_t ph = (it / T::kStages) & 1u;
-          ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->full[s], ph, abort_flag));
+          ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->full[s], ph, abort_flag, p.spin_limit));
           if(!ok)
             break;
           tc_fence_after_sync();
@@ -950,7 +990,9 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     const int epi_tid = threadIdx.x - 64;
     constexpr int kChunks = T::kTM / T::kChunk;
     pdl_wait();
-    const float unquant = kP8 ? 1.0f : __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(*p.d_qa, *p.d_qb)), p.scale);
+    trace_stamp(tb, kTrGemmPair, 1, trace_extra);
+    const float qa = kP8 ? 1.0f : *p.d_qa;
+    float unquant = kP8 ? 1.0f : __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.seg_qb[0])), p.scale);
     uint32_t acc_it = 0;
     const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
     for(int w = pair_id; w < p.total_work && ok; w += n_pairs) {
@@ -960,7 +1002,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       const uint32_t as = acc_it & 1u;
       const uint32_t aph = (acc_it >> 1) & 1u;
       if(lane == 0)
-        ok = mbar_wait_bounded(&ctl->tmem_full[as], aph, abort_flag);
+        ok = mbar_wait_bounded(&ctl->tmem_full[as], aph, abort_flag, p.spin_limit);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if(!ok)
         break;
@@ -971,7 +1013,16 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
       const bool n_ok = n < p.N;
       const int m0 = wi.m_tile * T::kTM;
       const int cols_valid = min(T::kTM, p.M - m0);
-      const float bias_n = (p.bias != nullptr && n_ok) ? __ldg(p.bias + n) : 0.0f;
+      int seg = 0, n_loc = n;
+      if(!kP8 && p.nseg > 1) {
+        seg = ((2 * wi.n_tile + static_cast<int>(rank)) * kTileN) / p.seg_n;
+        n_loc = n - seg * p.seg_n;
+        unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.seg_qb[seg])), p.scale);
+      }
+      const float* seg_bias = p.seg_bias[seg];
+      void* seg_c = p.seg_c[seg];
+      const int ldc = p.seg_n;
+      const float bias_n = (seg_bias != nullptr && n_ok) ? __ldg(seg_bias + n_loc) : 0.0f;
       float p8_scale_b = 0.0f;
       int p8_zp_b = 0, p8_off_b = 0;
       if constexpr(kP8) {
@@ -995,7 +1046,8 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
             write_back_chunk_p8<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * p.N + n, cols_valid - col0, m0 + col0, p8_scale_b, p8_zp_b,
                                            p8_off_b, bias_n);
         } else if(n_ok)
-          out_max = write_back_chunk<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * p.N + n, cols_valid - col0, unquant, bias_n, out_max);
+          out_max = write_back_chunk<T::kChunk>(p, v, static_cast<size_t>(m0 + col0) * ldc + n_loc, cols_valid - col0, unquant, bias_n, out_max,
+                                                seg_c, ldc, seg_bias != nullptr);
       }
       if(p.absmax_out != nullptr) {
         out_max = __reduce_max_sync(0xffffffffu, out_max);
@@ -1024,7 +1076,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     if(lane == 0) {
       int no_abort = 0;
       tc_commit_pair(&ctl->drain, 1);
-      if(!mbar_wait_bounded(&ctl->drain, 0u, &no_abort))
+      if(!mbar_wait_bounded(&ctl->drain, 0u, &no_abort, p.spin_limit))
         atomicMax(p.status, static_cast<int>(kDevTimeoutDrain));
     }
     __syncwarp();
@@ -1035,6 +1087,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, T::kTmemCols);
   }
+  trace_stamp(tb, kTrGemmPair, 2, trace_extra);
 }
 
 // ------------------------------------------------------------------ host side
@@ -1070,8 +1123,76 @@ int encode_kmajor_map(CUtensorMap* map, const int8_t* base, int rows, int K, int
   return r == CUDA_SUCCESS ? MI8_OK : MI8_ERR_DRIVER;
 }
 
+// A tensor map only describes an address range and a box shape, so it can be reused for as long as the same
+// (pointer, rows, K, box) comes back - which a decoder that multiplies the same weights and the same activation
+// buffers every step does about a hundred times per step.  Per-thread table, open addressing; when it fills up
+// it is emptied and rebuilt (descriptors never go stale: they hold no data).
+struct MapCache {
+  static constexpr int kSlots = 2048;   // power of two
+  struct Entry {
+    const void* base;
+    int rows, K, box;
+    bool used;
+  };
+  Entry keys[kSlots];
+  alignas(64) CUtensorMap maps[kSlots];
+  int count = 0;
+  MapCache() { clear(); }
+  void clear() {
+    for(int i = 0; i < kSlots; ++i)
+      keys[i].used = false;
+    count = 0;
+  }
+};
+thread_local MapCache* t_map_cache = nullptr;
+
+int get_kmajor_map(CUtensorMap* out, const int8_t* base, int rows, int K, int box_rows) {
+  if(t_map_cache == nullptr)
+    t_map_cache = new MapCache();
+  MapCache& mc = *t_map_cache;
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+  h ^= static_cast<uint64_t>(rows) * 0x9E3779B97F4A7C15ull;
+  h ^= (static_cast<uint64_t>(K) << 21) ^ (static_cast<uint64_t>(box_rows) << 45);
+  h ^= h >> 29;
+  int slot = static_cast<int>(h & (MapCache::kSlots - 1));
+  for(int probe = 0; probe < 16; ++probe, slot = (slot + 1) & (MapCache::kSlots - 1)) {
+    MapCache::Entry& e = mc.keys[slot];
+    if(!e.used)
+      break;
+    if(e.base == base && e.rows == rows && e.K == K && e.box == box_rows) {
+      *out = mc.maps[slot];
+      return MI8_OK;
+    }
+  }
+  int rc = encode_kmajor_map(out, base, rows, K, box_rows);
+  if(rc != MI8_OK)
+    return rc;
+  if(mc.count > MapCache::kSlots / 2)
+    mc.clear();
+  slot = static_cast<int>(h & (MapCache::kSlots - 1));
+  for(int probe = 0; probe < 16; ++probe, slot = (slot + 1) & (MapCache::kSlots - 1)) {
+    MapCache::Entry& e = mc.keys[slot];
+    if(!e.used) {
+      e.base = base;
+      e.rows = rows;
+      e.K = K;
+      e.box = box_rows;
+      e.used = true;
+      mc.maps[slot] = *out;
+      ++mc.count;
+      break;
+    }
+  }
+  return MI8_OK;
+}
+
+// Test hook (mi8_test_wait_fault): the next launches withhold one pipeline item and wait with a short limit.
+int g_test_withhold_item = -1;
+uint32_t g_test_spin_limit = 0;
+
 // Optional bracketing of every GEMM launch with CUDA events on the launching stream (mi8_profile_begin /
-// mi8_profile_end), so a benchmark can attribute device time to this kernel inside its timed region.
+// mi8_profile_end), so a benchmark can attribute device time to this kernel inside its timed region.  The
+// kernel itself reports how many activation rows it computed (launches that reuse stored rows skip most).
 struct ProfileRecord {
   int M, N, K, out_bytes;
   cudaEvent_t start, stop;
@@ -1082,6 +1203,7 @@ struct ProfileState {
   std::vector<ProfileRecord> records;
   std::vector<cudaEvent_t> pool;   // events are created once and reused
   size_t pool_used = 0;
+  int* d_rows = nullptr;           // [capacity] rows computed per recorded launch (device memory held while profiling)
   cudaEvent_t take() {
     if(pool_used == pool.size()) {
       cudaEvent_t e;
@@ -1093,6 +1215,25 @@ struct ProfileState {
   }
 };
 thread_local ProfileState t_profile;
+
+// Fields every launcher sets the same way.
+void finish_params(GemmParams& p) {
+  p.withhold_item = g_test_withhold_item;
+  p.spin_limit = g_test_spin_limit != 0 ? g_test_spin_limit : kSpinLimit;
+  p.rows_computed = nullptr;
+  if(t_profile.on && t_profile.d_rows != nullptr && t_profile.records.size() < t_profile.capacity)
+    p.rows_computed = t_profile.d_rows + t_profile.records.size();
+}
+void single_segment(GemmParams& p) {
+  p.a_row0 = 0;
+  p.nseg = 1;
+  p.seg_n = p.N;
+  for(int i = 0; i < kMaxSegments; ++i) {
+    p.seg_qb[i] = p.d_qb;
+    p.seg_bias[i] = p.bias;
+    p.seg_c[i] = p.c;
+  }
+}
 
 template <int TM, bool kQuantA = false, int kTopK = 0, bool kP8 = false>
 int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p, const GemmPlan& plan, cudaStream_t stream) {
@@ -1201,9 +1342,25 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& 
 
 }  // namespace
 
+MI8_DEFINE_TRACE_SETTER(trace_set_gemm)
+
+void test_wait_fault(int withhold_item, unsigned spin_limit) {
+  g_test_withhold_item = withhold_item;
+  g_test_spin_limit = spin_limit;
+}
+
 int profile_begin(int max_records) {
   if(max_records <= 0)
     return MI8_ERR_BAD_ARG;
+  if(t_profile.d_rows != nullptr) {
+    cudaFree(t_profile.d_rows);
+    t_profile.d_rows = nullptr;
+  }
+  // the one allocation of the library, made by this measurement aid for the time profiling is on
+  if(cudaMalloc(reinterpret_cast<void**>(&t_profile.d_rows), sizeof(int) * static_cast<size_t>(max_records)) != cudaSuccess) {
+    cudaGetLastError();
+    t_profile.d_rows = nullptr;
+  }
   t_profile.on = true;
   t_profile.capacity = static_cast<size_t>(max_records);
   t_profile.records.clear();
@@ -1214,7 +1371,16 @@ int profile_begin(int max_records) {
 int profile_end(mi8_gemm_record* out, int capacity, int* count) {
   t_profile.on = false;
   int n = 0;
-  for(const ProfileRecord& r : t_profile.records) {
+  std::vector<int> rows(t_profile.records.size(), -1);
+  if(t_profile.d_rows != nullptr && !rows.empty()) {
+    if(cudaDeviceSynchronize() != cudaSuccess ||
+       cudaMemcpy(rows.data(), t_profile.d_rows, sizeof(int) * rows.size(), cudaMemcpyDeviceToHost) != cudaSuccess) {
+      cudaGetLastError();
+      std::fill(rows.begin(), rows.end(), -1);
+    }
+  }
+  for(size_t i = 0; i < t_profile.records.size(); ++i) {
+    const ProfileRecord& r = t_profile.records[i];
     if(n >= capacity || out == nullptr)
       break;
     float ms = 0.f;
@@ -1227,12 +1393,17 @@ int profile_end(mi8_gemm_record* out, int capacity, int* count) {
     out[n].K = r.K;
     out[n].out_bytes = r.out_bytes;
     out[n].us = ms * 1000.f;
+    out[n].rows_computed = rows[i] >= 0 ? rows[i] : r.M;
     ++n;
   }
   if(count != nullptr)
     *count = n;
   t_profile.records.clear();
   t_profile.pool_used = 0;
+  if(t_profile.d_rows != nullptr) {
+    cudaFree(t_profile.d_rows);
+    t_profile.d_rows = nullptr;
+  }
   return MI8_OK;
 }
 
@@ -1335,33 +1506,40 @@ int make_gemm_plan(int M, int N, int K, int force_tile_m, int force_splits, Gemm
   return MI8_OK;
 }
 
-int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb, float scale,
-                const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* ws, size_t ws_bytes,
-                cudaStream_t stream, int force_tile_m, int force_splits, unsigned* absmax_out, const unsigned* skip_a,
-                const unsigned* skip_b, int skip_rows_below) {
+int launch_gemm_call(const GemmCall& g) {
+  const int M = g.M, N = g.N, K = g.K;
   if(M < 0 || N <= 0 || K <= 0)
     return MI8_ERR_BAD_ARG;
   if(M == 0)
     return MI8_OK;
-  if(aq == nullptr || bt == nullptr || d_qa == nullptr || d_qb == nullptr || c == nullptr)
+  if(g.aq == nullptr || g.bt == nullptr || g.d_qa == nullptr || g.nseg < 1 || g.nseg > kMaxSegments)
     return MI8_ERR_BAD_ARG;
-  if(out_dtype != MI8_F32 && out_dtype != MI8_F16)
+  for(int i = 0; i < g.nseg; ++i)
+    if(g.seg_qb[i] == nullptr || g.seg_c[i] == nullptr)
+      return MI8_ERR_BAD_ARG;
+  if(g.nseg > 1 && (N % g.nseg != 0 || (N / g.nseg) % kTileN != 0 || g.acc_out != nullptr))
+    return MI8_ERR_UNSUPPORTED;   // a tile of 128 weight rows must not straddle two segments
+  if(g.out_dtype != MI8_F32 && g.out_dtype != MI8_F16)
     return MI8_ERR_BAD_ARG;
-  if(K % 16 != 0 || (reinterpret_cast<uintptr_t>(aq) & 15u) || (reinterpret_cast<uintptr_t>(bt) & 15u))
+  if(K % 16 != 0 || (reinterpret_cast<uintptr_t>(g.aq) & 15u) || (reinterpret_cast<uintptr_t>(g.bt) & 15u))
     return MI8_ERR_MISALIGNED;
   GemmPlan plan;
-  int rc = make_gemm_plan(M, N, K, force_tile_m, force_splits, &plan);
+  int rc = make_gemm_plan(M, N, K, g.force_tile_m, g.force_splits, &plan);
   if(rc != MI8_OK)
     return rc;
   if(plan.splits > 1) {
-    if(ws == nullptr || ws_bytes < kWsHeaderBytes + plan.partial_bytes)
+    if(g.ws == nullptr || g.ws_bytes < kWsHeaderBytes + plan.partial_bytes)
       return MI8_ERR_WORKSPACE;
   }
   CUtensorMap tw, ta;
-  rc = encode_kmajor_map(&tw, bt, N, K, kTileN);
+  rc = get_kmajor_map(&tw, g.bt, N, K, kTileN);
   if(rc != MI8_OK)
     return rc;
-  rc = encode_kmajor_map(&ta, aq, M, K, plan.pair ? PairCfg::kHalfRows : plan.tile_m);
+  // a_rows_cap: the activation buffer is known to hold that many rows, so one descriptor serves every M up to
+  // it (rows past M inside the last tile are then real bytes instead of zero fill; their products are never stored)
+  if(g.a_row0 < 0 || (g.a_row0 > 0 && g.a_rows_cap < g.a_row0 + M))
+    return MI8_ERR_BAD_ARG;
+  rc = get_kmajor_map(&ta, g.aq, g.a_rows_cap > M ? g.a_rows_cap : M, K, plan.pair ? PairCfg::kHalfRows : plan.tile_m);
   if(rc != MI8_OK)
     return rc;
 
@@ -1375,18 +1553,18 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
   p.kb_total = plan.kb_total;
   p.kb_per_split = plan.kb_per_split;
   p.total_work = plan.n_tiles * plan.m_tiles * plan.splits;
-  p.d_qa = d_qa;
-  p.d_qb = d_qb;
-  p.scale = scale;
-  p.bias = bias;
-  p.relu = relu ? 1 : 0;
-  p.out_f16 = out_dtype == MI8_F16 ? 1 : 0;
-  p.c = c;
-  p.acc_out = acc_out;
-  uint8_t* wsb = static_cast<uint8_t*>(ws);
+  p.d_qa = g.d_qa;
+  p.d_qb = g.seg_qb[0];
+  p.scale = g.scale;
+  p.bias = g.seg_bias[0];
+  p.relu = g.relu ? 1 : 0;
+  p.out_f16 = g.out_dtype == MI8_F16 ? 1 : 0;
+  p.c = g.seg_c[0];
+  p.acc_out = g.acc_out;
+  uint8_t* wsb = static_cast<uint8_t*>(g.ws);
   p.partials = wsb ? reinterpret_cast<int32_t*>(wsb + kWsOffPartials) : nullptr;
   p.tile_counters = wsb ? reinterpret_cast<unsigned*>(wsb + kWsOffTileCounters) : nullptr;
-  p.absmax_out = absmax_out;
+  p.absmax_out = g.absmax_out;
   p.lg_max = p.lg_sum = p.lg_topv = nullptr;
   p.lg_topi = nullptr;
   p.lg_blocks = 0;
@@ -1394,22 +1572,67 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
   p.a_f32 = nullptr;
   p.a_slot = nullptr;
   p.qa_out = nullptr;
-  p.skip_a = skip_a;
-  p.skip_b = skip_b;
-  p.skip_rows_below = skip_rows_below;
+  p.skip_a = g.skip_a;
+  p.skip_b = g.skip_b;
+  p.skip_rows_below = g.skip_rows_below;
+  p.p8_scale_a = p.p8_scale_b = nullptr;
+  p.p8_zp_a = p.p8_sum_a = p.p8_zp_b = p.p8_off_b = nullptr;
   p.status = device_status_ptr();
   if(p.status == nullptr)
     return MI8_ERR_LAUNCH;
+  single_segment(p);
+  p.nseg = g.nseg;
+  p.seg_n = N / g.nseg;
+  for(int i = 0; i < g.nseg; ++i) {
+    p.seg_qb[i] = g.seg_qb[i];
+    p.seg_bias[i] = g.seg_bias[i];
+    p.seg_c[i] = g.seg_c[i];
+  }
+  p.a_row0 = g.a_row0;
+  finish_params(p);
 
   if(plan.pair)
-    return launch_pair(tw, ta, p, plan, stream);
+    return launch_pair(tw, ta, p, plan, g.stream);
   switch(plan.tile_m) {
-    case 16: return launch_cfg<16>(tw, ta, p, plan, stream);
-    case 32: return launch_cfg<32>(tw, ta, p, plan, stream);
-    case 64: return launch_cfg<64>(tw, ta, p, plan, stream);
-    case 128: return launch_cfg<128>(tw, ta, p, plan, stream);
-    default: return launch_cfg<256>(tw, ta, p, plan, stream);
+    case 16: return launch_cfg<16>(tw, ta, p, plan, g.stream);
+    case 32: return launch_cfg<32>(tw, ta, p, plan, g.stream);
+    case 64: return launch_cfg<64>(tw, ta, p, plan, g.stream);
+    case 128: return launch_cfg<128>(tw, ta, p, plan, g.stream);
+    default: return launch_cfg<256>(tw, ta, p, plan, g.stream);
   }
+}
+
+int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const float* d_qa, const float* d_qb, float scale,
+                const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* ws, size_t ws_bytes,
+                cudaStream_t stream, int force_tile_m, int force_splits, unsigned* absmax_out, const unsigned* skip_a,
+                const unsigned* skip_b, int skip_rows_below) {
+  if(M > 0 && (d_qb == nullptr || c == nullptr))
+    return MI8_ERR_BAD_ARG;
+  GemmCall g;
+  g.aq = aq;
+  g.bt = bt;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.d_qa = d_qa;
+  g.scale = scale;
+  g.relu = relu;
+  g.out_dtype = out_dtype;
+  g.acc_out = acc_out;
+  g.nseg = 1;
+  g.seg_qb[0] = d_qb;
+  g.seg_bias[0] = bias;
+  g.seg_c[0] = c;
+  g.ws = ws;
+  g.ws_bytes = ws_bytes;
+  g.stream = stream;
+  g.force_tile_m = force_tile_m;
+  g.force_splits = force_splits;
+  g.absmax_out = absmax_out;
+  g.skip_a = skip_a;
+  g.skip_b = skip_b;
+  g.skip_rows_below = skip_rows_below;
+  return launch_gemm_call(g);
 }
 
 // The packed8avx512 multiply: the plan of launch_gemm (CTA-pair kernel included); the accumulators and the
@@ -1435,10 +1658,10 @@ int launch_gemm_p8(const uint8_t* aq, const float* scale_a, const int32_t* zp_a,
   if(plan.splits > 1 && (ws == nullptr || ws_bytes < kWsHeaderBytes + plan.partial_bytes))
     return MI8_ERR_WORKSPACE;
   CUtensorMap tw, ta;
-  rc = encode_kmajor_map(&tw, bt, N, K, kTileN);
+  rc = get_kmajor_map(&tw, bt, N, K, kTileN);
   if(rc != MI8_OK)
     return rc;
-  rc = encode_kmajor_map(&ta, reinterpret_cast<const int8_t*>(aq), M, K, plan.pair ? PairCfg::kHalfRows : plan.tile_m);
+  rc = get_kmajor_map(&ta, reinterpret_cast<const int8_t*>(aq), M, K, plan.pair ? PairCfg::kHalfRows : plan.tile_m);
   if(rc != MI8_OK)
     return rc;
   GemmParams p{};
@@ -1468,6 +1691,8 @@ int launch_gemm_p8(const uint8_t* aq, const float* scale_a, const int32_t* zp_a,
   p.status = device_status_ptr();
   if(p.status == nullptr)
     return MI8_ERR_LAUNCH;
+  single_segment(p);
+  finish_params(p);
   if(plan.pair)
     return launch_pair<true>(tw, ta, p, plan, stream);
   switch(plan.tile_m) {
@@ -1513,7 +1738,7 @@ int launch_gemm_quant_a(const float* a_f32, const unsigned* a_slot, float* qa_ou
   if(rc != MI8_OK)
     return rc;
   CUtensorMap tw;
-  rc = encode_kmajor_map(&tw, bt, N, K, kTileN);
+  rc = get_kmajor_map(&tw, bt, N, K, kTileN);
   if(rc != MI8_OK)
     return rc;
   GemmParams p;
@@ -1550,6 +1775,8 @@ int launch_gemm_quant_a(const float* a_f32, const unsigned* a_slot, float* qa_ou
   p.status = device_status_ptr();
   if(p.status == nullptr)
     return MI8_ERR_LAUNCH;
+  single_segment(p);
+  finish_params(p);
   switch(tm) {   // the weight map stands in for the unused activation map
     case 16: return launch_cfg<16, true>(tw, tw, p, plan, stream);
     case 32: return launch_cfg<32, true>(tw, tw, p, plan, stream);
@@ -1580,10 +1807,10 @@ int launch_gemm_logits(const int8_t* aq, const float* d_qa, const int8_t* wq, co
   if(rc != MI8_OK)
     return rc;
   CUtensorMap tw, ta;
-  rc = encode_kmajor_map(&tw, aq, rows, K, kTileN);
+  rc = get_kmajor_map(&tw, aq, rows, K, kTileN);
   if(rc != MI8_OK)
     return rc;
-  rc = encode_kmajor_map(&ta, wq, vocab, K, 256);
+  rc = get_kmajor_map(&ta, wq, vocab, K, 256);
   if(rc != MI8_OK)
     return rc;
   GemmParams p;
@@ -1622,6 +1849,8 @@ int launch_gemm_logits(const int8_t* aq, const float* d_qa, const int8_t* wq, co
   p.status = device_status_ptr();
   if(p.status == nullptr)
     return MI8_ERR_LAUNCH;
+  single_segment(p);
+  finish_params(p);
   return k_top == 4 ? launch_cfg<256, false, 4>(tw, ta, p, plan, stream) : launch_cfg<256, false, 8>(tw, ta, p, plan, stream);
 }
 

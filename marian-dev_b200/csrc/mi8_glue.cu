@@ -17,6 +17,7 @@ namespace {
 
 constexpr int kRowThreads = 256;
 constexpr int kMaxVec = 4;  // float4 per thread: rows of up to 4096 floats
+constexpr int kMaxHistLayers = 16;
 
 __device__ __forceinline__ unsigned abs_bits(float v) { return __float_as_uint(v) & 0x7fffffffu; }
 
@@ -42,9 +43,12 @@ __device__ __forceinline__ unsigned max4u(unsigned m, const float4& v) {
 // (words == nullptr: zero embedding, the start symbol; pos_mod = source width for the encoder, 0 for a decoder step)
 __global__ void __launch_bounds__(kRowThreads)
 embed_kernel(const float* __restrict__ wemb, const int* __restrict__ words, const float* __restrict__ pos, int pos_mod, float scale,
-             int dim, float* __restrict__ out, float* __restrict__ rowmax, unsigned* absmax_slot) {
+             int dim, float* __restrict__ out, float* __restrict__ rowmax, unsigned* absmax_slot, unsigned* absmax_slot2) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrEmbed, 0);
   pdl_wait();
+  trace_stamp(tb, kTrEmbed, 1);
   __shared__ unsigned red[kRowThreads / 32];
   const int r = blockIdx.x;
   const float4* src = words ? reinterpret_cast<const float4*>(wemb + static_cast<size_t>(words[r]) * dim) : nullptr;
@@ -68,7 +72,10 @@ embed_kernel(const float* __restrict__ wemb, const int* __restrict__ words, cons
       rowmax[r] = __uint_as_float(m);
     if(absmax_slot)
       atomicMax(absmax_slot, m);
+    if(absmax_slot2)
+      atomicMax(absmax_slot2, m);
   }
+  trace_stamp(tb, kTrEmbed, 2);
 }
 
 // out = LayerNorm(a + resid) * gamma + beta, one block of 256 threads per row; biased variance
@@ -81,9 +88,12 @@ embed_kernel(const float* __restrict__ wemb, const int* __restrict__ words, cons
 __global__ void __launch_bounds__(kRowThreads)
 add_layernorm_kernel(const float* __restrict__ a, const float* __restrict__ resid, const float* __restrict__ gamma,
                      const float* __restrict__ beta, float eps, int dim, float* __restrict__ out, float* __restrict__ rowmax,
-                     unsigned* absmax_slot) {
+                     unsigned* absmax_slot, unsigned* absmax_slot2) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrAddLn, 0);
   pdl_wait();
+  trace_stamp(tb, kTrAddLn, 1);
   __shared__ float redf[kRowThreads / 32];
   __shared__ unsigned redu[kRowThreads / 32];
   const int r = blockIdx.x;
@@ -140,7 +150,10 @@ add_layernorm_kernel(const float* __restrict__ a, const float* __restrict__ resi
       rowmax[r] = __uint_as_float(m);
     if(absmax_slot)
       atomicMax(absmax_slot, m);
+    if(absmax_slot2)
+      atomicMax(absmax_slot2, m);
   }
+  trace_stamp(tb, kTrAddLn, 2);
 }
 
 __device__ __forceinline__ int quantize_one(float v, float qm) {
@@ -161,7 +174,10 @@ __global__ void __launch_bounds__(256)
 quantize_slot_kernel(const float* __restrict__ x, size_t n, const unsigned* __restrict__ absmax_slot, int8_t* __restrict__ q,
                      float* __restrict__ d_quant_mult, int* status) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrQuantSlot, 0);
   pdl_wait();
+  trace_stamp(tb, kTrQuantSlot, 1);
   const unsigned bits = *absmax_slot;
   const float qm = quant_mult_from_bits(bits);
   if(blockIdx.x == 0 && threadIdx.x == 0) {
@@ -182,6 +198,62 @@ quantize_slot_kernel(const float* __restrict__ x, size_t n, const unsigned* __re
   }
   for(size_t i = n16 * 16 + tid; i < n; i += stride)
     q[i] = static_cast<int8_t>(quantize_one(x[i], qm));
+  trace_stamp(tb, kTrQuantSlot, 2);
+}
+
+// Two quantisations in one launch, for the start of a decoder self-attention block: blocks [0, blocks_x)
+// quantise the layer input x with its own multiplier (the query projection's operand), the others the
+// self-attention history with the multiplier of the whole live history (the key/value projections' operand):
+// one slab row per block and iteration, only the newest slab (`rows_new` live rows) when the history's abs-max
+// still has the bits the stored keys/values were computed with (*prev_bits), everything otherwise.
+__global__ void __launch_bounds__(256)
+quantize_dual_kernel(const float* __restrict__ x, size_t n, const unsigned* __restrict__ slot_x, int8_t* __restrict__ q,
+                     float* __restrict__ qm_x, int* status, int blocks_x, const float* __restrict__ slabs, int slab_rows, int steps,
+                     int rows_new, int dim, const unsigned* __restrict__ slot_h, const unsigned* __restrict__ prev_bits,
+                     int8_t* __restrict__ hq, float* __restrict__ qm_h) {
+  pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrQuantDual, 0);
+  pdl_wait();
+  trace_stamp(tb, kTrQuantDual, 1);
+  if(static_cast<int>(blockIdx.x) < blocks_x) {
+    const unsigned bits = *slot_x;
+    const float qm = quant_mult_from_bits(bits);
+    if(blockIdx.x == 0 && threadIdx.x == 0) {
+      *qm_x = qm;
+      if(bits >= 0x7f800000u)
+        atomicMax(status, static_cast<int>(kDevNonFinite));
+    }
+    const size_t n16 = n / 16;   // (rows * dim with dim % 16 == 0: no tail)
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    uint4* q16 = reinterpret_cast<uint4*>(q);
+    const size_t stride = static_cast<size_t>(blocks_x) * blockDim.x;
+    for(size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride) {
+      const float4 a = __ldg(x4 + 4 * i), b = __ldg(x4 + 4 * i + 1), c = __ldg(x4 + 4 * i + 2), d = __ldg(x4 + 4 * i + 3);
+      uint4 o;
+      o.x = pack4(a, qm); o.y = pack4(b, qm); o.z = pack4(c, qm); o.w = pack4(d, qm);
+      q16[i] = o;
+    }
+  } else {
+    const int hb = static_cast<int>(blockIdx.x) - blocks_x, nhb = static_cast<int>(gridDim.x) - blocks_x;
+    const unsigned bits = *slot_h;
+    const float qm = quant_mult_from_bits(bits);
+    if(hb == 0 && threadIdx.x == 0)
+      *qm_h = qm;
+    const int total = (steps - 1) * slab_rows + rows_new;
+    const int first = (*prev_bits == bits) ? (steps - 1) * slab_rows : 0;   // unchanged abs-max: only the newest slab
+    for(int out_row = first + hb; out_row < total; out_row += nhb) {
+      const float4* src = reinterpret_cast<const float4*>(slabs + static_cast<size_t>(out_row) * dim);
+      uint4* dst = reinterpret_cast<uint4*>(hq + static_cast<size_t>(out_row) * dim);
+      for(int i = threadIdx.x; i < dim / 16; i += blockDim.x) {
+        const float4 a = __ldg(src + 4 * i), b = __ldg(src + 4 * i + 1), c = __ldg(src + 4 * i + 2), d = __ldg(src + 4 * i + 3);
+        uint4 o;
+        o.x = pack4(a, qm); o.y = pack4(b, qm); o.z = pack4(c, qm); o.w = pack4(d, qm);
+        dst[i] = o;
+      }
+    }
+  }
+  trace_stamp(tb, kTrQuantDual, 2);
 }
 
 // ---- self-attention history ------------------------------------------------------------------
@@ -192,15 +264,39 @@ quantize_slot_kernel(const float* __restrict__ x, size_t n, const unsigned* __re
 // rewrites the small table.  rowmax[t'][row] holds max|x| of each slab row.
 
 // anc_new[t'][r] = anc_old[t'][hyp[r]] (t' < t), anc_new[t][r] = r.
-__global__ void ancestors_update_kernel(const int* __restrict__ anc_old, int* __restrict__ anc_new, const int* __restrict__ hyp,
-                                        int t, int rows, int stride) {
+// With hist.layers > 0 the kernel also starts every layer's history abs-max of this step: for each layer l the
+// maximum of rowmax_l[t'][anc_new[t'][r]] over the EARLIER slabs t' < t is reduced into hist.slot[l]; the producer
+// of the layer's newest slab adds that slab's maximum to the same slot, which then holds what
+// history_absmax_kernel computes in a launch of its own.
+struct HistMaxArgs {
+  int layers;
+  const float* rowmax[kMaxHistLayers];
+  unsigned* slot[kMaxHistLayers];
+};
+__global__ void __launch_bounds__(256)
+ancestors_update_kernel(const int* __restrict__ anc_old, int* __restrict__ anc_new, const int* __restrict__ hyp,
+                        int t, int rows, int stride, const HistMaxArgs hist) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrAncestors, 0);
   pdl_wait();
+  trace_stamp(tb, kTrAncestors, 1);
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if(i >= (t + 1) * rows)
-    return;
-  const int tp = i / rows, r = i - tp * rows;
-  anc_new[tp * stride + r] = tp == t ? r : anc_old[tp * stride + hyp[r]];
+  const bool in = i < (t + 1) * rows;
+  int tp = 0, src = 0;
+  if(in) {
+    tp = i / rows;
+    const int r = i - tp * rows;
+    src = tp == t ? r : anc_old[tp * stride + hyp[r]];
+    anc_new[tp * stride + r] = src;
+  }
+  for(int l = 0; l < hist.layers; ++l) {
+    unsigned m = (in && tp < t) ? abs_bits(hist.rowmax[l][tp * stride + src]) : 0u;
+    m = __reduce_max_sync(0xffffffffu, m);
+    if((threadIdx.x & 31) == 0 && m != 0u)
+      atomicMax(hist.slot[l], m);
+  }
+  trace_stamp(tb, kTrAncestors, 2);
 }
 
 // max over t' < steps, r < rows of rowmax[t'][anc[t'][r]], reduced into the (zeroed) slot with atomicMax.
@@ -252,7 +348,10 @@ history_quantize_kernel(const float* __restrict__ slabs, int slab_rows, int step
 __global__ void history_commit_kernel(unsigned* __restrict__ prev_bits, const unsigned* __restrict__ slots, int first, int stride, int layers,
                                       unsigned* __restrict__ stats) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrCommit, 0);
   pdl_wait();
+  trace_stamp(tb, kTrCommit, 1);
   const int l = threadIdx.x;
   if(l < layers) {
     const unsigned now = slots[first + l * stride];
@@ -263,6 +362,7 @@ __global__ void history_commit_kernel(unsigned* __restrict__ prev_bits, const un
     }
     prev_bits[l] = now;
   }
+  trace_stamp(tb, kTrCommit, 2);
 }
 
 // ---- single-query attention --------------------------------------------------------------------
@@ -281,13 +381,16 @@ __global__ void history_commit_kernel(unsigned* __restrict__ prev_bits, const un
 //   mx = max_p s_p;  e_p = det_expf(s_p - mx)
 //   thread j accumulates e_p for p = j, j+G, ... ascending; sum = butterfly over the G threads
 //   w_p = e_p / sum;  out_i = fma-chain over p ascending of w_p * v_{p,i}, starting from 0.
-template <int DH>
+template <int DH, int U>
 __global__ void __launch_bounds__(256)
 attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ log_mask, int heads, int len, int rows, int batch, int mode, float scale,
                   float* __restrict__ out, unsigned* absmax_slot, const int* __restrict__ anc, int anc_stride, int kv_rows) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrAttention1, 0);
   pdl_wait();
+  trace_stamp(tb, kTrAttention1, 1);
   extern __shared__ float sc_smem[];  // [heads][len] scores, then probabilities
   constexpr int G = DH / 4;
   const int r = blockIdx.x;
@@ -316,14 +419,15 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     return base * dim + 4 * tid + p * stride;
   };
 
-  // scores: eight key rows in flight per thread
-  for(int p0 = 0; p0 < len; p0 += 8) {
-    float4 kk[8];
+  // scores: U key rows in flight per thread (the loads do not depend on one another; the arithmetic per
+  // position is the same whatever U is)
+  for(int p0 = 0; p0 < len; p0 += U) {
+    float4 kk[U];
 #pragma unroll
-    for(int u = 0; u < 8; ++u)
+    for(int u = 0; u < U; ++u)
       kk[u] = (active && p0 + u < len) ? __ldg(reinterpret_cast<const float4*>(k + row_offset(p0 + u))) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for(int u = 0; u < 8; ++u) {
+    for(int u = 0; u < U; ++u) {
       float d = __fmul_rn(qv.x, kk[u].x);
       d = __fmaf_rn(qv.y, kk[u].y, d);
       d = __fmaf_rn(qv.z, kk[u].z, d);
@@ -362,15 +466,15 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     for(int p = j; p < len; p += G)
       srow[p] = __fdiv_rn(srow[p], part);
   __syncthreads();
-  // weighted sum of the value rows, strictly in position order, loads eight rows ahead
+  // weighted sum of the value rows, strictly in position order, loads U rows ahead
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for(int p0 = 0; p0 < len; p0 += 8) {
-    float4 vv[8];
+  for(int p0 = 0; p0 < len; p0 += U) {
+    float4 vv[U];
 #pragma unroll
-    for(int u = 0; u < 8; ++u)
+    for(int u = 0; u < U; ++u)
       vv[u] = (active && p0 + u < len) ? __ldg(reinterpret_cast<const float4*>(v + row_offset(p0 + u))) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for(int u = 0; u < 8; ++u) {
+    for(int u = 0; u < U; ++u) {
       if(p0 + u < len) {
         const float w = srow[p0 + u];
         acc.x = __fmaf_rn(w, vv[u].x, acc.x);
@@ -390,6 +494,7 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     if((tid & 31) == 0 && m_abs != 0u)
       atomicMax(absmax_slot, m_abs);
   }
+  trace_stamp(tb, kTrAttention1, 2);
 }
 
 // Encoder self-attention (mode 2) with the keys and values of one (sentence, head) staged in shared memory: block
@@ -415,7 +520,10 @@ attention_enc_kernel(const float* __restrict__ q, const float* __restrict__ k, c
                      const float* __restrict__ log_mask, int heads, int len, float scale, float* __restrict__ out,
                      unsigned* absmax_slot) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrAttentionEnc, 0);
   pdl_wait();
+  trace_stamp(tb, kTrAttentionEnc, 1);
   extern __shared__ float enc_smem[];
   constexpr int G = DH / 4;
   const int b = blockIdx.x, h = blockIdx.y;
@@ -504,6 +612,7 @@ attention_enc_kernel(const float* __restrict__ q, const float* __restrict__ k, c
     if((threadIdx.x & 31) == 0 && m_abs != 0u)
       atomicMax(absmax_slot, m_abs);
   }
+  trace_stamp(tb, kTrAttentionEnc, 2);
 }
 
 // ---- output layer: log-softmax + per-row top-k --------------------------------------------------
@@ -569,7 +678,10 @@ __global__ void __launch_bounds__(256)
 lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ prev_scores, float* __restrict__ cand_score,
                 int* __restrict__ cand_word) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrLseTopk, 0);
   pdl_wait();
+  trace_stamp(tb, kTrLseTopk, 1);
   extern __shared__ float lse_blocks[];   // [nb] block maxima, [nb] block sums
   __shared__ float s_v[256 * K];
   __shared__ int s_i[256 * K];
@@ -675,6 +787,7 @@ lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __rest
     cand_score[r * K + threadIdx.x] = __fadd_rn(__fadd_rn(s_v[threadIdx.x], -lse), ps);
     cand_word[r * K + threadIdx.x] = s_i[threadIdx.x];
   }
+  trace_stamp(tb, kTrLseTopk, 2);
 }
 
 // Second half of the fused output layer: the GEMM's write-back left, per (row, block of 128 vocabulary entries),
@@ -687,7 +800,10 @@ lse_merge_kernel(const float* __restrict__ blk_max, const float* __restrict__ bl
                  const int* __restrict__ blk_topi, int nb, int k, const float* __restrict__ prev_scores, float* __restrict__ cand_score,
                  int* __restrict__ cand_word) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrLseMerge, 0);
   pdl_wait();
+  trace_stamp(tb, kTrLseMerge, 1);
   extern __shared__ float lse_blocks[];
   __shared__ float s_v[256 * KT];
   __shared__ int s_i[256 * KT];
@@ -722,6 +838,7 @@ lse_merge_kernel(const float* __restrict__ blk_max, const float* __restrict__ bl
     cand_score[r * k + threadIdx.x] = __fadd_rn(__fadd_rn(s_v[threadIdx.x], -lse), ps);
     cand_word[r * k + threadIdx.x] = s_i[threadIdx.x];
   }
+  trace_stamp(tb, kTrLseMerge, 2);
 }
 
 // Per sentence b: merge the beam x K row candidates (rows beam-major: row = j * batch + b) into the
@@ -731,10 +848,15 @@ template <int K>
 __global__ void nbest_merge_kernel(const float* __restrict__ cand_score, const int* __restrict__ cand_word, int beam, int batch,
                                    int vocab, float* __restrict__ out_score, int* __restrict__ out_beam, int* __restrict__ out_word) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrNbest, 0);
   pdl_wait();
+  trace_stamp(tb, kTrNbest, 1);
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
-  if(b >= batch)
+  if(b >= batch) {
+    trace_stamp(tb, kTrNbest, 2);
     return;
+  }
   TopK t;
 #pragma unroll
   for(int j = 0; j < K; ++j) {
@@ -757,12 +879,16 @@ __global__ void nbest_merge_kernel(const float* __restrict__ cand_score, const i
     out_beam[b * K + n] = valid ? t.i[n] / vocab : 0;
     out_word[b * K + n] = valid ? t.i[n] % vocab : 0;
   }
+  trace_stamp(tb, kTrNbest, 2);
 }
 
 // rows gather: out[i,:] = in[idx[i],:]  (16-byte copies when the row length allows it)
 __global__ void gather_rows_kernel(const float* __restrict__ in, const int* __restrict__ idx, int dim, float* __restrict__ out) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrGather, 0);
   pdl_wait();
+  trace_stamp(tb, kTrGather, 1);
   const int r = blockIdx.x;
   const float* src = in + static_cast<size_t>(idx[r]) * dim;
   float* dst = out + static_cast<size_t>(r) * dim;
@@ -775,6 +901,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const int* __re
     for(int i = threadIdx.x; i < dim; i += blockDim.x)
       dst[i] = __ldg(src + i);
   }
+  trace_stamp(tb, kTrGather, 2);
 }
 
 // SSRU cell (src/rnn/cells.h:1052-1066): c' = c[hyp] * sigmoid(f) + x * (1 - sigmoid(f)); h = relu(c').
@@ -782,7 +909,10 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const int* __re
 __global__ void ssru_cell_kernel(const float* __restrict__ cell_old, const int* __restrict__ hyp, const float* __restrict__ xw,
                                  const float* __restrict__ f, int dim, float* __restrict__ cell_new, float* __restrict__ h_out) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrSsru, 0);
   pdl_wait();
+  trace_stamp(tb, kTrSsru, 1);
   const int r = blockIdx.x;
   const float* c = cell_old + static_cast<size_t>(hyp ? hyp[r] : r) * dim;
   for(int i = threadIdx.x; i < dim; i += blockDim.x) {
@@ -794,25 +924,31 @@ __global__ void ssru_cell_kernel(const float* __restrict__ cell_old, const int* 
     cell_new[o] = cn;
     h_out[o] = cn > 0.f ? cn : 0.f;
   }
+  trace_stamp(tb, kTrSsru, 2);
 }
+
+int g_attention_unroll = 16;   // key/value rows a thread of attention1_kernel keeps in flight (8 or 16)
 
 }  // namespace
 
+MI8_DEFINE_TRACE_SETTER(trace_set_glue)
+void set_attention_unroll(int u) { g_attention_unroll = u; }
+
 // ------------------------------------------------------------------------------------------------ launchers
 int launch_embed(const float* wemb, const int* words, const float* pos, int pos_mod, float scale, int rows, int dim, float* out,
-                 float* rowmax, unsigned* slot, cudaStream_t s) {
+                 float* rowmax, unsigned* slot, cudaStream_t s, unsigned* slot2) {
   if(rows <= 0 || dim <= 0 || dim % 4 != 0 || dim > kRowThreads * 4 * kMaxVec || out == nullptr || pos == nullptr)
     return MI8_ERR_BAD_ARG;
-  launch_kernel(embed_kernel, dim3(rows), dim3(kRowThreads), 0, s, wemb, words, pos, pos_mod, scale, dim, out, rowmax, slot);
+  launch_kernel(embed_kernel, dim3(rows), dim3(kRowThreads), 0, s, wemb, words, pos, pos_mod, scale, dim, out, rowmax, slot, slot2);
   count_launch();
   return check_launch();
 }
 
 int launch_add_layernorm(const float* a, const float* resid, const float* gamma, const float* beta, float eps, int rows, int dim,
-                         float* out, float* rowmax, unsigned* slot, cudaStream_t s) {
+                         float* out, float* rowmax, unsigned* slot, cudaStream_t s, unsigned* slot2) {
   if(rows <= 0 || dim <= 0 || dim % 4 != 0 || dim > kRowThreads * 4 * kMaxVec || a == nullptr || out == nullptr)
     return MI8_ERR_BAD_ARG;
-  launch_kernel(add_layernorm_kernel, dim3(rows), dim3(kRowThreads), 0, s, a, resid, gamma, beta, eps, dim, out, rowmax, slot);
+  launch_kernel(add_layernorm_kernel, dim3(rows), dim3(kRowThreads), 0, s, a, resid, gamma, beta, eps, dim, out, rowmax, slot, slot2);
   count_launch();
   return check_launch();
 }
@@ -833,9 +969,42 @@ int launch_quantize_slot(const float* x, size_t n, const unsigned* slot, int8_t*
   return check_launch();
 }
 
-int launch_ancestors_update(const int* anc_old, int* anc_new, const int* hyp, int t, int rows, int stride, cudaStream_t s) {
+int launch_ancestors_update(const int* anc_old, int* anc_new, const int* hyp, int t, int rows, int stride, cudaStream_t s,
+                            int hist_layers, const float* const* hist_rowmax, unsigned* const* hist_slot) {
+  if(hist_layers < 0 || hist_layers > kMaxHistLayers)
+    return MI8_ERR_UNSUPPORTED;
+  HistMaxArgs hist;
+  hist.layers = hist_layers;
+  for(int l = 0; l < kMaxHistLayers; ++l) {
+    hist.rowmax[l] = l < hist_layers ? hist_rowmax[l] : nullptr;
+    hist.slot[l] = l < hist_layers ? hist_slot[l] : nullptr;
+  }
   const int n = (t + 1) * rows;
-  launch_kernel(ancestors_update_kernel, dim3((n + 255) / 256), dim3(256), 0, s, anc_old, anc_new, hyp, t, rows, stride);
+  launch_kernel(ancestors_update_kernel, dim3((n + 255) / 256), dim3(256), 0, s, anc_old, anc_new, hyp, t, rows, stride, hist);
+  count_launch();
+  return check_launch();
+}
+
+int launch_quantize_dual(const float* x, size_t n, const unsigned* slot_x, int8_t* q, float* qm_x, const float* slabs, int slab_rows,
+                         int steps, int rows_new, int dim, const unsigned* slot_h, const unsigned* prev_bits, int8_t* hq, float* qm_h,
+                         cudaStream_t s) {
+  if(x == nullptr || q == nullptr || slot_x == nullptr || qm_x == nullptr || slabs == nullptr || slot_h == nullptr || prev_bits == nullptr ||
+     hq == nullptr || qm_h == nullptr || n == 0 || steps <= 0 || rows_new <= 0 || rows_new > slab_rows)
+    return MI8_ERR_BAD_ARG;
+  if(dim % 16 != 0 || n % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(q) & 15u))
+    return MI8_ERR_MISALIGNED;
+  int* status = device_status_ptr();
+  if(status == nullptr)
+    return MI8_ERR_LAUNCH;
+  size_t bx = (n / 16 + 255) / 256;
+  const size_t cap = static_cast<size_t>(sm_count()) * 4;
+  bx = bx < 1 ? 1 : (bx > cap ? cap : bx);
+  // history part: one block per row of the newest slab (the common case); a full requantisation strides over the rest
+  int bh = rows_new;
+  const int hcap = sm_count() * 8;
+  bh = bh > hcap ? hcap : bh;
+  launch_kernel(quantize_dual_kernel, dim3(static_cast<unsigned>(bx) + bh), dim3(256), 0, s, x, n, slot_x, q, qm_x, status,
+                static_cast<int>(bx), slabs, slab_rows, steps, rows_new, dim, slot_h, prev_bits, hq, qm_h);
   count_launch();
   return check_launch();
 }
@@ -908,10 +1077,15 @@ int launch_attention1(const float* q, const float* k, const float* v, const floa
   const size_t smem = (static_cast<size_t>(heads) + 1) * len * sizeof(float);
   if(smem > 48 * 1024)
     return MI8_ERR_UNSUPPORTED;
-  if(dim_head == 64)
-    launch_kernel(attention1_kernel<64>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
+  const bool wide = g_attention_unroll >= 16;
+  if(dim_head == 64 && wide)
+    launch_kernel(attention1_kernel<64, 16>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
+  else if(dim_head == 64)
+    launch_kernel(attention1_kernel<64, 8>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
+  else if(dim_head == 32 && wide)
+    launch_kernel(attention1_kernel<32, 16>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
   else if(dim_head == 32)
-    launch_kernel(attention1_kernel<32>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
+    launch_kernel(attention1_kernel<32, 8>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
   else
     return MI8_ERR_UNSUPPORTED;
   count_launch();

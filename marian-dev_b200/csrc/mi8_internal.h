@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/marian_i8.h"
+#include "../../include/marian_i8_measure.h"
 
 namespace mi8 {
 
@@ -61,6 +62,7 @@ int launch_max_absolute(const float* x, size_t n, float* d_absmax, float* d_quan
                         cudaStream_t stream);
 int launch_quantize(const float* x, size_t n, const float* d_quant_mult, int8_t* q, cudaStream_t stream);
 int launch_transpose_quantize(const float* w, int K, int N, const float* d_quant_mult, int8_t* bt, cudaStream_t stream);
+int launch_transpose_f32(const float* in, int batch, int rows, int cols, float* out, cudaStream_t stream);
 
 // GEMM (mi8_gemm.cu)
 // absmax_out (optional): 4-byte slot that receives max|C| (unsigned bit pattern, atomicMax) for the
@@ -69,6 +71,37 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
                 const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out, void* ws, size_t ws_bytes,
                 cudaStream_t stream, int force_tile_m, int force_splits, unsigned* absmax_out = nullptr,
                 const unsigned* skip_a = nullptr, const unsigned* skip_b = nullptr, int skip_rows_below = 0);
+
+// The general form: one activation against up to three weight matrices of the same shape stored one behind the
+// other (N = nseg * rows of one of them), each with its own multiplier, bias and output matrix [M, N / nseg].
+struct GemmCall {
+  const int8_t* aq = nullptr;
+  const int8_t* bt = nullptr;
+  int M = 0, N = 0, K = 0;
+  const float* d_qa = nullptr;
+  float scale = 1.0f;
+  int relu = 0;
+  int out_dtype = MI8_F32;
+  int32_t* acc_out = nullptr;
+  int nseg = 1;
+  const float* seg_qb[3] = {nullptr, nullptr, nullptr};
+  const float* seg_bias[3] = {nullptr, nullptr, nullptr};
+  void* seg_c[3] = {nullptr, nullptr, nullptr};
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  cudaStream_t stream = nullptr;
+  int force_tile_m = 0, force_splits = 0;
+  unsigned* absmax_out = nullptr;
+  const unsigned* skip_a = nullptr;
+  const unsigned* skip_b = nullptr;
+  int skip_rows_below = 0;
+  int a_rows_cap = 0;   // rows the activation buffer holds (extent of its tensor map); 0 = M
+  int a_row0 = 0;       // the M rows start at this row of the buffer `aq` points to (needs a_rows_cap >= a_row0 + M)
+};
+int launch_gemm_call(const GemmCall& g);
+
+// Test hook behind mi8_test_wait_fault (marian_i8_measure.h).
+void test_wait_fault(int withhold_item, unsigned spin_limit);
 
 // The GEMM that quantises its activation itself: `a_f32` [M,K] fp32 and `a_slot`, the 4-byte slot its
 // producer reduced max|A| into.  MI8_ERR_UNSUPPORTED when the shape does not give every CTA exactly one
@@ -97,12 +130,24 @@ int launch_lse_merge(const float* blk_max, const float* blk_sum, const float* bl
                      int k_top, int k, const float* prev_scores, float* cand_score, int* cand_word, cudaStream_t s);
 
 // decode-step glue (mi8_glue.cu)
+// slot2 (optional): a second 4-byte slot that receives the same maximum (the self-attention history's abs-max)
 int launch_embed(const float* wemb, const int* words, const float* pos, int pos_mod, float scale, int rows, int dim, float* out,
-                 float* rowmax, unsigned* slot, cudaStream_t s);
+                 float* rowmax, unsigned* slot, cudaStream_t s, unsigned* slot2 = nullptr);
 int launch_add_layernorm(const float* a, const float* resid, const float* gamma, const float* beta, float eps, int rows, int dim,
-                         float* out, float* rowmax, unsigned* slot, cudaStream_t s);
+                         float* out, float* rowmax, unsigned* slot, cudaStream_t s, unsigned* slot2 = nullptr);
 int launch_quantize_slot(const float* x, size_t n, const unsigned* slot, int8_t* q, float* d_qm, cudaStream_t s);
-int launch_ancestors_update(const int* anc_old, int* anc_new, const int* hyp, int t, int rows, int stride, cudaStream_t s);
+// hist_layers > 0: also reduces, per layer, the maximum of rowmax over the earlier slabs' ancestor rows into hist_slot[l]
+int launch_ancestors_update(const int* anc_old, int* anc_new, const int* hyp, int t, int rows, int stride, cudaStream_t s,
+                            int hist_layers = 0, const float* const* hist_rowmax = nullptr, unsigned* const* hist_slot = nullptr);
+// layer input x and the self-attention history quantised by one launch (see quantize_dual_kernel)
+int launch_quantize_dual(const float* x, size_t n, const unsigned* slot_x, int8_t* q, float* qm_x, const float* slabs, int slab_rows,
+                         int steps, int rows_new, int dim, const unsigned* slot_h, const unsigned* prev_bits, int8_t* hq, float* qm_h,
+                         cudaStream_t s);
+void set_attention_unroll(int u);
+// in-situ timeline: each translation unit with kernels installs the buffer in its own copy of the pointer
+int trace_set_glue(unsigned long long* buf);
+int trace_set_gemm(unsigned long long* buf);
+int trace_set_quant(unsigned long long* buf);
 int launch_history_absmax(const float* rowmax, const int* anc, int steps, int rows, int stride, unsigned* slot, cudaStream_t s);
 int launch_history_quantize(const float* slabs, int slab_rows, int steps, int dim, const unsigned* slot, const unsigned* prev_bits,
                             int8_t* hq, float* d_qm, cudaStream_t s);

@@ -15,7 +15,6 @@ enum DeviceStatus : int {
   kDevTimeoutEpilogue = 103,  // epilogue gave up waiting for a finished accumulator
   kDevTimeoutDrain = 104,     // teardown gave up waiting for copies / MMAs still in flight
   kDevNonFinite = 110,        // abs-max saw Inf or NaN
-  kDevTimeoutGridSync = 120,  // fused quantise kernel gave up at its grid-wide barrier
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -30,6 +29,38 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 // barrier/TMEM set-up and loads of constant weights qualify.  Without the launch attribute both are no-ops.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------- in-situ timeline (measurement aid)
+// While a trace buffer is installed (mi8_trace_begin), one thread of block 0 of every kernel stamps the
+// global nanosecond timer at kernel entry, after pdl_wait() and at its exit into the buffer
+// ([0] = entries used, [1] = capacity, then pairs (time, extra << 16 | kernel << 8 | phase); the GEMMs put
+// N | K << 20 | M << 40 into `extra`).  Unlike events between
+// launches this leaves programmatic dependent launch undisturbed, so it shows what a kernel costs inside the
+// running decoder step.  Every translation unit holds its own copy of the pointer (set by its
+// MI8_DEFINE_TRACE_SETTER function); it is null outside a trace, which costs one load per kernel.
+static __device__ unsigned long long* s_trace_buf = nullptr;
+enum TraceKernel : int {
+  kTrGemm = 1, kTrGemmPair, kTrQuantSlot, kTrQuantDual, kTrAddLn, kTrAttention1, kTrAttentionEnc, kTrLseTopk, kTrLseMerge,
+  kTrNbest, kTrEmbed, kTrAncestors, kTrCommit, kTrGather, kTrSsru, kTrAbsmax, kTrQuantize, kTrGemmLogits, kTrGemmQuantA
+};
+__device__ __forceinline__ unsigned long long* trace_open() {
+  return (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == blockDim.x - 1) ? s_trace_buf : nullptr;
+}
+__device__ __forceinline__ void trace_stamp(unsigned long long* tb, int kernel, int phase, unsigned long long extra = 0ull) {
+  if(tb != nullptr) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const unsigned long long idx = atomicAdd(tb, 1ull);
+    if(idx < tb[1]) {
+      tb[2 + 2 * idx] = t;
+      tb[3 + 2 * idx] = (extra << 16) | (static_cast<unsigned long long>(kernel) << 8) | static_cast<unsigned long long>(phase);
+    }
+  }
+}
+#define MI8_DEFINE_TRACE_SETTER(name)                                                         \
+  int name(unsigned long long* buf) {                                                         \
+    return cudaMemcpyToSymbol(s_trace_buf, &buf, sizeof(buf)) == cudaSuccess ? 0 : 5;         \
+  }
 
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -59,13 +90,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Spin limit for every barrier wait.  A healthy pipeline completes a wait in well under a
-// microsecond; the limit only exists so that a broken one returns an error instead of hanging.
+// Default spin limit of a barrier wait.  A healthy pipeline completes a wait in well under a
+// microsecond (every role first waits for the preceding kernel with pdl_wait(), so the limit only
+// measures this kernel's own pipeline); it exists so that a broken one returns an error instead of hanging.
 constexpr uint32_t kSpinLimit = 1u << 20;
 
 // Bounded wait.  `abort_flag` (shared memory) lets the other roles leave early once one gave up.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for(uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t limit = kSpinLimit) {
+  for(uint32_t i = 0; i < limit; ++i) {
     if(mbar_try_wait(bar, parity))
       return true;
     if((i & 0xff) == 0xff && *abort_flag)

@@ -42,7 +42,10 @@ __global__ void __launch_bounds__(kBlock)
 mi8_absmax_kernel(const float* __restrict__ x, size_t n, unsigned* partials, unsigned* counter, float* d_absmax,
                   float* d_quant_mult, int* status) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrAbsmax, 0);
   pdl_wait();
+  trace_stamp(tb, kTrAbsmax, 1);
   __shared__ unsigned red[kBlock / 32];
   __shared__ int is_last;
   unsigned m = 0u;
@@ -70,8 +73,10 @@ mi8_absmax_kernel(const float* __restrict__ x, size_t n, unsigned* partials, uns
     is_last = (old == gridDim.x - 1) ? 1 : 0;
   }
   __syncthreads();
-  if(!is_last)
+  if(!is_last) {
+    trace_stamp(tb, kTrAbsmax, 2);
     return;
+  }
   __threadfence();
   m = 0u;
   for(unsigned b = threadIdx.x; b < gridDim.x; b += kBlock)
@@ -88,6 +93,7 @@ mi8_absmax_kernel(const float* __restrict__ x, size_t n, unsigned* partials, uns
     if(d_quant_mult != nullptr)
       *d_quant_mult = (m == 0u) ? 1.0f : __fdiv_rn(127.0f, mx);
   }
+  trace_stamp(tb, kTrAbsmax, 2);
 }
 
 __device__ __forceinline__ int quantize_one(float v, float qm) {
@@ -104,7 +110,10 @@ __device__ __forceinline__ unsigned pack4(const float4& v, float qm) {
 __global__ void __launch_bounds__(kBlock)
 mi8_quantize_kernel(const float* __restrict__ x, size_t n, const float* __restrict__ d_quant_mult, int8_t* __restrict__ q) {
   pdl_launch_dependents();
+  unsigned long long* tb = trace_open();
+  trace_stamp(tb, kTrQuantize, 0);
   pdl_wait();
+  trace_stamp(tb, kTrQuantize, 1);
   const float qm = *d_quant_mult;
   const size_t n16 = n / 16;
   const float4* x4 = reinterpret_cast<const float4*>(x);
@@ -125,6 +134,7 @@ mi8_quantize_kernel(const float* __restrict__ x, size_t n, const float* __restri
   }
   for(size_t i = n16 * 16 + tid; i < n; i += stride)
     q[i] = static_cast<int8_t>(quantize_one(x[i], qm));
+  trace_stamp(tb, kTrQuantize, 2);
 }
 
 // W fp32 [K,N] row-major -> Bt int8 [N,K] row-major.  A block moves a 32(k) x 32(n) tile through
@@ -152,6 +162,33 @@ mi8_transpose_quantize_kernel(const float* __restrict__ w, int K, int N, const f
   }
 }
 
+// out[b][c][r] = in[b][r][c]: the last two axes of a float tensor swapped, 32 x 32 tiles through shared memory so that
+// reads and writes are both contiguous.  (Serves affine / dot with transA, which the reference resolves by a transpose
+// node in front of the quantisation, src/tensors/cpu/intgemm_interface.h:52.)
+__global__ void __launch_bounds__(256)
+mi8_transpose_f32_kernel(const float* __restrict__ in, int rows, int cols, float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float tile[32][33];
+  const size_t plane = static_cast<size_t>(rows) * cols;
+  const float* src = in + blockIdx.z * plane;
+  float* dst = out + blockIdx.z * plane;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for(int i = 0; i < 32; i += 8) {
+    const int r = r0 + ty + i, c = c0 + tx;
+    tile[ty + i][tx] = (r < rows && c < cols) ? src[static_cast<size_t>(r) * cols + c] : 0.0f;
+  }
+  __syncthreads();
+#pragma unroll
+  for(int i = 0; i < 32; i += 8) {
+    const int c = c0 + ty + i, r = r0 + tx;
+    if(c < cols && r < rows)
+      dst[static_cast<size_t>(c) * rows + r] = tile[tx][ty + i];
+  }
+}
+
 int stream_grid(size_t work_items) {
   const size_t per_block = static_cast<size_t>(kBlock) * 4;
   size_t blocks = (work_items + per_block - 1) / per_block;
@@ -164,6 +201,8 @@ int stream_grid(size_t work_items) {
 }
 
 }  // namespace
+
+MI8_DEFINE_TRACE_SETTER(trace_set_quant)
 
 int launch_max_absolute(const float* x, size_t n, float* d_absmax, float* d_quant_mult, void* ws, size_t ws_bytes,
                         cudaStream_t stream) {
@@ -205,6 +244,17 @@ int launch_transpose_quantize(const float* w, int K, int N, const float* d_quant
   if(grid.y > 65535)
     return MI8_ERR_UNSUPPORTED;
   launch_kernel(mi8_transpose_quantize_kernel, dim3(grid), dim3(256), 0, stream, w, K, N, d_quant_mult, bt);
+  count_launch();
+  return check_launch();
+}
+
+int launch_transpose_f32(const float* in, int batch, int rows, int cols, float* out, cudaStream_t stream) {
+  if(in == nullptr || out == nullptr || batch <= 0 || rows <= 0 || cols <= 0)
+    return MI8_ERR_BAD_ARG;
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch);
+  if(grid.y > 65535 || grid.z > 65535)
+    return MI8_ERR_UNSUPPORTED;
+  launch_kernel(mi8_transpose_f32_kernel, grid, dim3(256), 0, stream, in, rows, cols, out);
   count_launch();
   return check_launch();
 }

@@ -17,8 +17,9 @@
 // First call on a device.  Host code cannot use the array's name as a pointer: on the host it is
 // only a handle for the device symbol.  The first call made while a device is current asks the
 // runtime for that device's address of the array (cudaGetSymbolAddress) and remembers it; make that
-// first call outside of any stream capture.  Nothing here calls cudaMalloc, cudaFree or any
-// allocating library routine.
+// first call outside of any stream capture.  Two host threads that make the first call on the same device
+// at the same time both store the same address, which is harmless.  Nothing here calls cudaMalloc,
+// cudaFree or any allocating library routine.
 #include "mi8_internal.h"
 
 namespace mi8 {
@@ -64,6 +65,11 @@ extern "C" int mi8_multiply_i8_static(const int8_t* aq, const int8_t* bt, int M,
     return MI8_ERR_BAD_ARG;
   if(M == 0)
     return MI8_OK;
+  // every argument is checked before anything is queued on the stream, so a refused call leaves the array untouched
+  if(aq == nullptr || bt == nullptr || d_qa == nullptr || d_qb == nullptr || c == nullptr || (out_dtype != MI8_F32 && out_dtype != MI8_F16))
+    return MI8_ERR_BAD_ARG;
+  if(K % 16 != 0 || (reinterpret_cast<uintptr_t>(aq) & 15u) || (reinterpret_cast<uintptr_t>(bt) & 15u))
+    return MI8_ERR_MISALIGNED;
   GemmPlan plan;
   int rc = make_gemm_plan(M, N, K, 0, 0, &plan);
   if(rc != MI8_OK)

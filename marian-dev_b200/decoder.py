@@ -1,11 +1,12 @@
-"""Transformer / SSRU decode on the GPU with every affine running through the int8 engine.
+"""Transformer / SSRU decode on the GPU through the C++ step driver of libmarian_i8.so.
 
-This is the caller that drives the hot path for the tokens/sec metric; it restates
-``DecoderTransformer::step`` (src/models/transformer.h:713-896), the encoder (:581-637),
-``MultiHead`` / ``LayerAttention`` / ``LayerFFN`` (:279-454), the SSRU cell (src/rnn/cells.h:983-1067)
-and ``BeamSearch::search`` (src/translator/beam_search.cpp:249-538).  Attention, softmax, LayerNorm
-and the beam bookkeeping stay fp32 (torch ops and host code); all weight multiplications go through
-``ops.prepareA`` + ``ops.multiply`` (libmarian_i8.so).
+This is the caller that drives the hot path for the tokens/sec metric.  ``Int8Transformer`` holds one model
+replica (converted intgemm8 weights, fp32 biases / LayerNorm / embeddings), ``NativeStepper`` owns the driver
+object (include/marian_i8_decode.h) that runs the encoder (src/models/transformer.h:581-637) and
+``DecoderTransformer::step`` (:713-896) as sm_100a kernels, and ``BeamSearch`` is ``BeamSearch::search``
+(src/translator/beam_search.cpp:249-538): by default the whole search of a mini-batch is one call into the driver
+(``mi8d_search``); with ``native_search=False`` the bookkeeping runs here in NumPy around ``mi8d_step``.
+There is no other implementation behind these classes: without the library nothing runs.
 
 Row layout follows Marian: decoder tensors are ``[beam, batch, ...]`` flattened beam-major, so a
 hypothesis lives in row ``beamHypIdx * batch + batchIdx`` (beam_search.cpp:398).
@@ -16,34 +17,11 @@ import math
 
 import numpy as np
 import torch
-import torch.nn.functional as F
 
 from . import ops
 from .model import TransformerConfig, is_intgemm_param, sinusoidal_table
 
 NEG_MASK = -99999999.0  # transposedLogMask (transformer.h:138-143)
-
-
-def sinusoidal_positions(start: int, n: int, dim: int, device) -> torch.Tensor:
-    """gSinusoidalPositionEmbeddings (src/tensors/gpu/tensor_operators.cu:793-817)."""
-    half = dim // 2
-    inc = math.log(10000.0) / (half - 1.0)
-    i = torch.arange(dim, device=device)
-    freq = torch.exp((i % half).float() * -inc)
-    pos = torch.arange(start, start + n, device=device, dtype=torch.float32)[:, None]
-    v = pos * freq[None, :]
-    return torch.where(i[None, :] < half, torch.sin(v), torch.cos(v))
-
-
-class DecoderState:
-    def __init__(self):
-        self.layer = []          # per layer: self-attention history [R, t, d] or SSRU cell [R, d]
-        self.cross_k = []        # per layer [B, h, S, dh]
-        self.cross_v = []
-        self.cross_rows = -1     # batch size the cross K/V were computed for
-        self.context = None      # [B, S, d]
-        self.log_mask = None     # [B, 1, 1, S]
-        self.position = 0
 
 
 class Int8Transformer:
@@ -73,134 +51,6 @@ class Int8Transformer:
         self.d = cfg.dim_emb
         self.h = cfg.heads
         self.dh = cfg.dim_emb // cfg.heads
-
-    # ------------------------------------------------------------------ building blocks
-    def quant(self, x: torch.Tensor) -> ops.IntgemmTensor:
-        return ops.prepareA(x.reshape(-1, x.shape[-1]), ws=self.ws)
-
-    def mul(self, aq, wname, bname=None, relu=False):
-        bias = self.p[bname].view(-1) if bname else None
-        return ops.multiply(aq, self.w[wname], bias, 1.0, relu, ws=self.ws)
-
-    def layer_norm(self, x, prefix):
-        return F.layer_norm(x, (self.d,), self.p[prefix + "_ln_scale"].view(-1), self.p[prefix + "_ln_bias"].view(-1), 1e-6)
-
-    def split_heads(self, x, rows, steps):
-        return x.view(rows, steps, self.h, self.dh).permute(0, 2, 1, 3)      # [rows, h, steps, dh]
-
-    def attention(self, q, k, v, log_mask):
-        """softmax(q k^T / sqrt(dh) + mask) v, all fp32 (transformer.h:240-277)."""
-        z = torch.matmul(q, k.transpose(-1, -2)) * (1.0 / math.sqrt(self.dh))
-        if log_mask is not None:
-            z = z + log_mask
-        return torch.matmul(torch.softmax(z, dim=-1), v)
-
-    def ffn(self, x, prefix):
-        """LayerFFN with relu: W1 + ReLU fused in the GEMM write-back, W2, then add & norm."""
-        hq = self.quant(self.mul(self.quant(x), prefix + "_W1", prefix + "_b1", relu=True))
-        out = self.mul(hq, prefix + "_W2", prefix + "_b2")
-        return self.layer_norm(out.view_as(x) + x, prefix + "_ffn")
-
-    # ------------------------------------------------------------------ encoder
-    def encode(self, ids: torch.Tensor, mask: torch.Tensor):
-        """ids [B,S] int64, mask [B,S] float 0/1 -> context [B,S,d], log_mask [B,1,1,S]."""
-        B, S = ids.shape
-        x = self.wemb[ids] * math.sqrt(self.d) + sinusoidal_positions(0, S, self.d, self.device)[None]
-        log_mask = ((1.0 - mask) * NEG_MASK).view(B, 1, 1, S)
-        for i in range(1, self.cfg.enc_depth + 1):
-            pre = f"encoder_l{i}_self"
-            xq = self.quant(x)  # q, keys and values are the same tensor: one quantisation serves all three
-            q = self.split_heads(self.mul(xq, pre + "_Wq", pre + "_bq"), B, S)
-            k = self.split_heads(self.mul(xq, pre + "_Wk", pre + "_bk"), B, S)
-            v = self.split_heads(self.mul(xq, pre + "_Wv", pre + "_bv"), B, S)
-            a = self.attention(q, k, v, log_mask).permute(0, 2, 1, 3).reshape(B * S, self.d)
-            out = self.mul(self.quant(a), pre + "_Wo", pre + "_bo")
-            x = self.layer_norm(out.view(B, S, self.d) + x, pre + "_Wo")
-            x = self.ffn(x, f"encoder_l{i}_ffn")
-        return x, log_mask
-
-    def start_state(self, context, log_mask) -> DecoderState:
-        st = DecoderState()
-        st.context, st.log_mask = context, log_mask
-        B = context.shape[0]
-        for _ in range(self.cfg.dec_depth):
-            if self.cfg.decoder_autoreg == "rnn":
-                st.layer.append(torch.zeros(B, self.d, device=self.device))
-            else:
-                st.layer.append(None)
-        return st
-
-    # ------------------------------------------------------------------ one decoder step
-    def step(self, st: DecoderState, hyp_indices, prev_words, batch_indices, beam: int) -> torch.Tensor:
-        """Returns logits [beam * batch, V] (beam-major rows) and advances the state in place.
-
-        hyp_indices / prev_words are None at t = 0 (one start hypothesis per sentence, zero embedding);
-        batch_indices selects the sentences still active out of the previous step's batch."""
-        t = st.position
-        cfg = self.cfg
-        if t > 0:
-            if len(batch_indices) != st.context.shape[0]:
-                st.context = st.context.index_select(0, batch_indices)
-                st.log_mask = st.log_mask.index_select(0, batch_indices)
-            st.layer = [s.index_select(0, hyp_indices) for s in st.layer]
-        B, S = st.context.shape[0], st.context.shape[1]
-        R = beam * B
-        if t == 0:
-            emb = torch.zeros(R, self.d, device=self.device)
-        else:
-            emb = self.wemb[prev_words]
-        x = emb * math.sqrt(self.d) + sinusoidal_positions(t, 1, self.d, self.device)
-
-        # cross-attention keys/values are cached per batch and recomputed when the batch shrinks
-        if st.cross_rows != B:
-            st.cross_k, st.cross_v = [], []
-            cq = self.quant(st.context)
-            for i in range(1, cfg.dec_depth + 1):
-                pre = f"decoder_l{i}_context"
-                st.cross_k.append(self.split_heads(self.mul(cq, pre + "_Wk", pre + "_bk"), B, S))
-                st.cross_v.append(self.split_heads(self.mul(cq, pre + "_Wv", pre + "_bv"), B, S))
-            st.cross_rows = B
-
-        for i in range(1, cfg.dec_depth + 1):
-            li = i - 1
-            if cfg.decoder_autoreg == "rnn":
-                pre = f"decoder_l{i}_rnn"
-                xq = self.quant(x)
-                xw = self.mul(xq, pre + "_W")                       # dot(input, W)
-                f = self.mul(xq, pre + "_Wf", pre + "_bf")          # affine(input, Wf, bf)
-                sig = torch.sigmoid(f)
-                cell = st.layer[li] * sig + xw * (1.0 - sig)        # highway(cell, x, f)
-                st.layer[li] = cell
-                x = self.layer_norm(torch.relu(cell) + x, pre + "_ffn")
-            else:
-                pre = f"decoder_l{i}_self"
-                hist = x.view(R, 1, self.d) if st.layer[li] is None else torch.cat([st.layer[li], x.view(R, 1, self.d)], dim=1)
-                st.layer[li] = hist
-                steps = hist.shape[1]
-                q = self.split_heads(self.mul(self.quant(x), pre + "_Wq", pre + "_bq"), R, 1)
-                # keys and values are re-projected from the whole history every step, with one
-                # quantisation multiplier over all of it (transformer.h:401-417)
-                hq = self.quant(hist)
-                k = self.split_heads(self.mul(hq, pre + "_Wk", pre + "_bk"), R, steps)
-                v = self.split_heads(self.mul(hq, pre + "_Wv", pre + "_bv"), R, steps)
-                a = self.attention(q, k, v, None).permute(0, 2, 1, 3).reshape(R, self.d)
-                out = self.mul(self.quant(a), pre + "_Wo", pre + "_bo")
-                x = self.layer_norm(out + x, pre + "_Wo")
-
-            pre = f"decoder_l{i}_context"
-            q = self.split_heads(self.mul(self.quant(x), pre + "_Wq", pre + "_bq"), R, 1)   # [R, h, 1, dh]
-            q = q.reshape(beam, B, self.h, 1, self.dh)
-            a = self.attention(q, st.cross_k[li][None], st.cross_v[li][None], st.log_mask[None])
-            a = a.permute(0, 1, 3, 2, 4).reshape(R, self.d)
-            out = self.mul(self.quant(a), pre + "_Wo", pre + "_bo")
-            x = self.layer_norm(out + x, pre + "_Wo")
-            x = self.ffn(x, f"decoder_l{i}_ffn")
-
-        st.position = t + 1
-        out_b = self.p["decoder_ff_logit_out_b"].view(-1)
-        if self.output_int8:
-            return ops.multiply(self.quant(x), self.wemb_q, out_b, ws=self.ws)
-        return torch.addmm(out_b, x, self.wemb.t())
 
 
 class NativeStepper:
@@ -276,6 +126,20 @@ class NativeStepper:
         res = [(toks[b, :lens[b]].tolist(), float(scores[b])) for b in range(B)]
         return res, int(up.value), int(down.value)
 
+    OPTIONS = {"fuse_weights": 1, "quant_in_gemm": 2, "fused_output_max_rows": 3, "side_stream": 4, "attention_unroll": 5}
+
+    def set_option(self, name: str, value: int):
+        """mi8d_set_option: tuning switches of the step driver (every setting computes the same bits)."""
+        self.check(self.L.mi8d_set_option(self.h, self.OPTIONS[name], int(value)))
+
+    def search_stats(self, reset: bool = False):
+        """Host-side timing of mi8d_search since the last reset: seconds issuing kernels, seconds waiting for the
+        device, seconds of bookkeeping, decoder steps."""
+        import ctypes
+        out = (ctypes.c_double * 4)()
+        self.check(self.L.mi8d_search_stats(self.h, ctypes.byref(out), int(reset)))
+        return {"issue_s": out[0], "wait_s": out[1], "host_s": out[2], "steps": int(out[3])}
+
     def history_reuse(self, reset: bool = False):
         """(reused, total) counts of (layer, step) pairs whose stored self-attention keys/values stayed valid."""
         import ctypes
@@ -325,8 +189,8 @@ class BeamSearch:
     def __init__(self, model: Int8Transformer, beam: int = 4, max_length_factor: float = 1.5, normalize: float = 1.0,
                  word_penalty: float = 0.0, native: "NativeStepper | None" = None, native_search: bool = True):
         self.m = model
-        self.native = native      # None: torch glue ops per step; else the C++ step driver
-        self.native_search = native_search   # with a native stepper: also run the bookkeeping in the C++ driver (mi8d_search)
+        self.native = native      # the C++ step driver
+        self.native_search = native_search   # also run the bookkeeping in the C++ driver (mi8d_search)
         self.beam = beam
         self.factor = max_length_factor
         self.alpha = normalize
@@ -349,19 +213,14 @@ class BeamSearch:
     @torch.no_grad()
     def search_device(self, ids_t: torch.Tensor, mask_t: torch.Tensor):
         """Same with ids (int64) and mask (float32) already on the device."""
-        if self.native is not None and self.native_search:
+        if self.native is not None and self.native_search and type(self)._nbest is BeamSearch._nbest:
             res, up, down = self.native.search(ids_t, mask_t, self.beam, self.factor, self.alpha, self.wp, self.m.cfg.eos_id)
             self.h2d_bytes += up
             self.d2h_bytes += down
             return res
-        m, dev, eos = self.m, self.m.device, self.m.cfg.eos_id
+        eos = self.m.cfg.eos_id
         B0, width = ids_t.shape
-        if self.native is not None:
-            self.native.encode(ids_t, mask_t)
-            st = None
-        else:
-            ctx, log_mask = m.encode(ids_t, mask_t)
-            st = m.start_state(ctx, log_mask)
+        st = self._begin(ids_t, mask_t)
 
         beam = self.beam
         col = np.arange(beam)[None, :]
@@ -391,12 +250,7 @@ class BeamSearch:
                 hyp_idx = np.where(valid, prev_state[active].T[:max_beam] * prev_dim + batch_indices[None, :], 0).reshape(-1)
                 pw = np.where(valid, words[active].T[:max_beam], eos).reshape(-1)           # dummy slots carry EOS
                 ps = np.where(valid, scores[active].T[:max_beam], -np.inf).astype(np.float32).reshape(-1)
-            if self.native is not None:
-                nv, nbm, nw, up, down = self.native.step(hyp_idx, pw, batch_indices, ps, tensor_beam, nb, n_best)
-                self.h2d_bytes += up
-                self.d2h_bytes += down
-            else:
-                nv, nbm, nw = self._nbest_torch(st, hyp_idx, pw, batch_indices, ps, tensor_beam, nb, n_best)
+            nv, nbm, nw = self._nbest(st, hyp_idx, pw, batch_indices, ps, tensor_beam, nb, n_best)
 
             # toHyps: every sentence keeps its current number of hypotheses, skipping invalid scores
             ok = nv > -np.inf
@@ -446,29 +300,19 @@ class BeamSearch:
 
         return self._traceback(history, finals, B0)
 
-    def _nbest_torch(self, st, hyp_idx, pw, batch_indices, ps, tensor_beam, nb, n_best):
-        """One step through the torch-glue model, then n-best over beam x vocabulary per sentence:
-        row-wise top-N of the logits, shifted by the row's log-sum-exp and previous path score, merged
-        across the rows of a sentence (the same set as top-N over the flattened [beam * V] scores)."""
-        m, dev = self.m, self.m.device
-        if hyp_idx is None:
-            logits = m.step(st, None, None, None, 1)
-            prev_scores_t = torch.zeros(nb, device=dev)
-        else:
-            R = tensor_beam * nb
-            host = torch.from_numpy(np.concatenate([hyp_idx, pw, batch_indices]).astype(np.int64)).to(dev)
-            prev_scores_t = torch.from_numpy(ps).to(dev)
-            self.h2d_bytes += host.numel() * 8 + ps.size * 4
-            logits = m.step(st, host[:R], host[R:2 * R], host[2 * R:], tensor_beam)
-        lse = torch.logsumexp(logits, dim=-1)
-        top_v, top_i = torch.topk(logits, n_best, dim=-1)                              # [R, n_best]
-        cand = (top_v - lse[:, None]) + prev_scores_t[:, None]
-        cand = cand.view(tensor_beam, nb, n_best).permute(1, 0, 2).reshape(nb, tensor_beam * n_best)
-        best_v, best_c = torch.topk(cand, n_best, dim=-1)                              # sorted, descending
-        word_sel = top_i.view(tensor_beam, nb, n_best).permute(1, 0, 2).reshape(nb, -1).gather(1, best_c)
-        out = torch.stack([best_v.double(), (best_c // n_best).double(), word_sel.double()]).cpu().numpy()  # the step's one sync
-        self.d2h_bytes += out.size * 8
-        return out[0].astype(np.float32), out[1].astype(np.int64), out[2].astype(np.int64)
+    def _begin(self, ids_t, mask_t):
+        """Encoder forward and start of the mini-batch; returns the per-search state the step hook receives."""
+        if self.native is None:
+            raise ops.Mi8Error(1, "BeamSearch needs a NativeStepper: the decode has no implementation outside libmarian_i8.so")
+        self.native.encode(ids_t, mask_t)
+        return None
+
+    def _nbest(self, st, hyp_idx, pw, batch_indices, ps, tensor_beam, nb, n_best):
+        """One decoder step: (scores, parent beams, words), each [batch, n_best], from mi8d_step."""
+        nv, nbm, nw, up, down = self.native.step(hyp_idx, pw, batch_indices, ps, tensor_beam, nb, n_best)
+        self.h2d_bytes += up
+        self.d2h_bytes += down
+        return nv, nbm, nw
 
     @staticmethod
     def _traceback(history, finals, B0):
@@ -492,9 +336,10 @@ class BeamSearch:
         return results
 
 
-def decode_corpus(model: Int8Transformer, batches, beam=4, max_length_factor=1.5, normalize=1.0, native=None, native_search=True):
+def decode_corpus(model: Int8Transformer, batches, beam=4, max_length_factor=1.5, normalize=1.0, native=None, native_search=True,
+                  search_cls=None):
     """Translate all mini-batches on one replica; returns {sentence id: token list} and the token count."""
-    bs = BeamSearch(model, beam, max_length_factor, normalize, native=native, native_search=native_search)
+    bs = (search_cls or BeamSearch)(model, beam, max_length_factor, normalize, native=native, native_search=native_search)
     out, n_tokens = {}, 0
     for sent_ids, ids, mask in batches:
         res = bs.search(ids, mask)

@@ -167,6 +167,22 @@ Expr lambda(const std::vector<Expr>& children, Shape shape, Type type, LambdaNod
   return children[0]->graph->add(n);
 }
 
+// swaps the last two axes (the reference's transpose(a) with the default axes)
+Expr transpose(Expr a) {
+  MI8_ABORT_IF(!isFloat(a->value_type()), "transpose expects a float32 tensor, not " + typeName(a->value_type()));
+  MI8_ABORT_IF(a->shape().size() < 2, "transpose needs at least two axes");
+  Shape outShape = a->shape();
+  const int r = a->shape()[-2], c = a->shape()[-1];
+  outShape.set(-2, c);
+  outShape.set(-1, r);
+  auto nodeOp = [=](Expr out, const std::vector<Expr>& ch) {
+    Tensor in = ch[0]->val();
+    const int batch = static_cast<int>(in->shape.elements() / (static_cast<size_t>(r) * c));
+    check(mi8_transpose_f32(in->data<float>(), batch, r, c, out->val()->data<float>(), out->graph->stream()), "transpose");
+  };
+  return lambda({a}, outShape, Type::float32, nodeOp);
+}
+
 namespace gpu {
 namespace integer {
 
@@ -186,7 +202,8 @@ Expr affineOrDot(Expr a, Expr bQuant, Expr bias, bool transA, bool /*transB*/, f
   MI8_ABORT_IF(!isIntgemm(bQuant->value_type()),
                "Intgemm expects type of B to be a variant of intgemm not " + typeName(bQuant->value_type()));
   MI8_ABORT_IF(bQuant->value_type() != Type::intgemm8, "Only intgemm8 is supported on the GPU, not " + typeName(bQuant->value_type()));
-  MI8_ABORT_IF(transA, "transA needs a transpose node, which this mirror does not carry");
+  if(transA)   // as the reference: A is transposed by a node of its own in front of the quantisation (intgemm_interface.h:52)
+    a = transpose(a);
   MI8_ABORT_IF(a->shape()[-1] != bQuant->shape()[-2], "Inner dimensions of A and B do not match");
   Expr aQuant = prepareA(a);
   Shape outShape = aQuant->shape();

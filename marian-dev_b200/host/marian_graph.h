@@ -142,6 +142,7 @@ private:
 Expr lambda(const std::vector<Expr>& children, Shape shape, Type type, LambdaNodeFunctor fn);
 
 // the operator surface of the path (expression_operators.h:489-493,523-528,533-536)
+Expr transpose(Expr a);   // last two axes swapped (float32)
 Expr dot(Expr a, Expr b, bool transA = false, bool transB = false, float scale = 1.f);
 Expr affine(Expr a, Expr b, Expr bias, bool transA = false, bool transB = false, float scale = 1.f);
 Expr affineWithReluDropout(Expr x, Expr W, Expr bias, float dropProb = 0.f);

@@ -57,15 +57,19 @@ class Workspace:
         return self.buf.data_ptr()
 
 
-_default_ws: dict[int, Workspace] = {}
+_default_ws: dict[tuple, Workspace] = {}
 
 
 def default_workspace(device: torch.device) -> Workspace:
+    """The workspace ops.* calls use when none is passed: one per (device, current stream), because calls that
+    share a workspace must not overlap on the device and two streams give no such ordering."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    ws = _default_ws.get(idx)
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    ws = _default_ws.get(key)
     if ws is None:
-        ws = Workspace(device=torch.device("cuda", idx))
-        _default_ws[idx] = ws
+        with torch.cuda.stream(torch.cuda.current_stream(idx)):
+            ws = Workspace(device=torch.device("cuda", idx))
+        _default_ws[key] = ws
     return ws
 
 
@@ -236,13 +240,26 @@ def multiply_rows_from(aq: IntgemmTensor, b: IntgemmTensor, bias: torch.Tensor |
     return out
 
 
+def transpose(a: torch.Tensor) -> torch.Tensor:
+    """The last two axes of a float32 tensor swapped by the library's transpose kernel (the node the reference puts in front
+    of prepareA for transA, src/tensors/cpu/intgemm_interface.h:52)."""
+    _require_cuda(a, "a")
+    if a.dtype != torch.float32 or a.dim() < 2:
+        raise Mi8Error(1, "transpose expects a float32 tensor with at least two axes")
+    a = a.contiguous()
+    r, c = a.shape[-2], a.shape[-1]
+    out = torch.empty(a.shape[:-2] + (c, r), dtype=torch.float32, device=a.device)
+    check(lib().mi8_transpose_f32(a.data_ptr(), a.numel() // (r * c), r, c, out.data_ptr(), _stream_ptr()))
+    return out
+
+
 def _affine_or_dot(a: torch.Tensor, b: IntgemmTensor, bias, transA: bool, transB: bool, scale: float, relu: bool,
                    out_dtype=torch.float32, ws: Workspace | None = None, aq: IntgemmTensor | None = None) -> torch.Tensor:
     if not isinstance(b, IntgemmTensor):
         raise Mi8Error(1, f"Intgemm expects type of B to be a variant of intgemm not {type(b).__name__}")
     if aq is None:
         if transA:
-            a = a.transpose(-1, -2)
+            a = transpose(a)
         aq = prepareA(a, ws=ws)
         lead = tuple(a.shape[:-1])
     else:

@@ -42,7 +42,9 @@ def gather_outputs(local: dict, max_len: int, device=None) -> dict:
     rows = int(max(int(c.item()) for c in counts))
     mat = np.full((max(rows, 1), 2 + max_len), -1, dtype=np.int32)     # built and decoded with NumPy: no per-element tensor access
     for r, (sid, toks) in enumerate(sorted(local.items())):
-        toks = toks[:max_len]
+        if len(toks) > max_len:
+            raise ValueError(f"sentence {sid} has {len(toks)} tokens but the gather matrix holds {max_len}: "
+                             "size max_len from the search's length limit (max_length_factor x the widest source)")
         mat[r, 0], mat[r, 1] = sid, len(toks)
         if toks:
             mat[r, 2:2 + len(toks)] = toks

@@ -118,6 +118,40 @@ int main() {
     CHECK(gotQb == qb && gotBt == bt);
   }
 
+  {  // transA: A arrives as [K, M] and is transposed by a node of its own before the quantisation, as the reference does
+     // (intgemm_interface.h:52); values equal the product with the pre-transposed operand, bit for bit
+    ExpressionGraph graph(arena, arenaBytes, ws, wsBytes);
+    std::mt19937 rng(11);
+    std::normal_distribution<float> nd(0.f, 1.f);
+    const int M = 37, K = 48, N = 24;
+    std::vector<float> vA(M * K), vAt(K * M), vB(K * N), vBias(N);
+    for(auto& v : vA) v = nd(rng);
+    for(int i = 0; i < M; ++i)
+      for(int j = 0; j < K; ++j)
+        vAt[j * M + i] = vA[i * K + j];
+    for(auto& v : vB) v = 0.02f * nd(rng);
+    for(auto& v : vBias) v = 0.01f * nd(rng);
+    Expr At = graph.param("At", {K, M}, Type::float32, vAt.data());
+    Expr W = graph.intgemm8Param("W", graph.param("W_f", {K, N}, Type::float32, vB.data()));
+    Expr b = graph.param("b", {1, N}, Type::float32, vBias.data());
+    Expr Y = affine(At, W, b, /*transA=*/true);
+    Expr D = dot(At, W, true, false, 2.f);
+    CHECK(Y->shape() == Shape({M, N}) && D->shape() == Shape({M, N}));
+    graph.forward();
+    std::vector<float> got, gotD;
+    graph.get(Y, got);
+    graph.get(D, gotD);
+    std::vector<int8_t> bt(N * K);
+    const float qb = mo_prepare_b(vB.data(), K, N, 0, bt.data());
+    std::vector<float> want(M * N), wantD(M * N);
+    mo_affine(vA.data(), M, K, bt.data(), qb, N, vBias.data(), 1.f, 0, want.data(), nullptr, nullptr, nullptr);
+    mo_affine(vA.data(), M, K, bt.data(), qb, N, nullptr, 2.f, 0, wantD.data(), nullptr, nullptr, nullptr);
+    bool same = true;
+    for(int i = 0; i < M * N; ++i)
+      same = same && got[i] == want[i] && gotD[i] == wantD[i];
+    CHECK(same);
+  }
+
   {  // packed8avx512 weights: converted in the graph and uploaded as a ready item; affine and dot dispatch on isPacked(B)
     ExpressionGraph graph(arena, arenaBytes, ws, wsBytes);
     const int M = 10, K = 512, N = 96;

@@ -37,6 +37,12 @@ def test_library_exports_every_declared_symbol():
     for sym in declared_p8:
         assert hasattr(L, sym), f"{sym} declared in include/marian_packed8.h but not exported"
     assert sorted(PACKED8_EXPORTS) == declared_p8
+    from marian_dev_b200.binding import MEASURE_EXPORTS
+    declared_measure = _declared_symbols("marian_i8_measure.h", "mi8d?_")
+    assert declared_measure
+    for sym in declared_measure:
+        assert hasattr(L, sym), f"{sym} declared in include/marian_i8_measure.h but not exported"
+    assert sorted(MEASURE_EXPORTS) == declared_measure
 
 
 def test_strerror_and_version():

@@ -3,7 +3,7 @@ sentences.
 
 native-step: the product path (C++ step driver, fixed-order glue kernels).  Its float glue rounds
 exactly like the checker's, so every sequence must be identical (the requirement is >= 99 %).
-torch-glue: the same model with torch ops as glue.  Its softmax / LayerNorm round differently, and an
+torch-glue (tests/torch_glue.py, test infrastructure): the same model with torch ops as glue.  Its softmax / LayerNorm round differently, and an
 int8 pipeline amplifies one-ulp differences to quantisation-step differences, so random-init models
 (whose logits are nearly flat) occasionally pick another word; that path is only a cross-check of the
 driver and is held to a looser bar."""
@@ -21,9 +21,11 @@ def _decode_both(cfg_name, n_sent, mini_batch, beam, seed, lo=3, hi=12, output_i
     params = model.random_init(cfg, seed)
     corpus = model.synthetic_corpus(n_sent, cfg.vocab, seed + 1, "uniform", lo, hi)
     batches = model.make_batches(corpus, mini_batch)
-    gpu = decoder.Int8Transformer(cfg, params, torch.device("cuda", 0), output_int8=output_int8)
+    from tests.torch_glue import TorchGlueSearch, TorchGlueTransformer
+    gpu = (decoder.Int8Transformer if native else TorchGlueTransformer)(cfg, params, torch.device("cuda", 0), output_int8=output_int8)
     stepper = decoder.NativeStepper(gpu, max_batch=mini_batch, beam=max(beam, 1), max_src=hi + 2, max_steps=2 * hi + 8) if native else None
-    got, n_tok = decoder.decode_corpus(gpu, batches, beam=beam, native=stepper, native_search=native_search)
+    got, n_tok = decoder.decode_corpus(gpu, batches, beam=beam, native=stepper, native_search=native_search,
+                                       search_cls=None if native else TorchGlueSearch)
     assert ops.poll_status() == 0
     ref_model = OracleTransformer(cfg, params, output_int8=output_int8, threads=8)
     want = {}
@@ -65,9 +67,10 @@ def test_batch_purging_path(cuda_device, native):
     params["decoder_ff_logit_out_b"][0, cfg.eos_id] += 4.0
     corpus = model.synthetic_corpus(40, cfg.vocab, 4, "uniform", 4, 14)
     batches = model.make_batches(corpus, 20)
-    gpu = decoder.Int8Transformer(cfg, params, torch.device("cuda", 0))
+    from tests.torch_glue import TorchGlueSearch, TorchGlueTransformer
+    gpu = (decoder.Int8Transformer if native else TorchGlueTransformer)(cfg, params, torch.device("cuda", 0))
     stepper = decoder.NativeStepper(gpu, max_batch=20, beam=4, max_src=16, max_steps=40) if native else None
-    got, _ = decoder.decode_corpus(gpu, batches, beam=4, native=stepper)
+    got, _ = decoder.decode_corpus(gpu, batches, beam=4, native=stepper, search_cls=None if native else TorchGlueSearch)
     assert ops.poll_status() == 0
     ref_model = OracleTransformer(cfg, params, threads=8)
     want = {}
