@@ -35,7 +35,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 KERNEL_NAMES = ["mi8_gemm_pair_kernel", "mi8_gemm_kernel", "quantize_slot_kernel", "attention1_kernel", "attention_enc_kernel",
-                "add_layernorm_kernel", "history_quantize_kernel", "history_absmax_kernel", "history_commit_kernel", "lse_topk_kernel",
+                "add_layernorm_kernel", "quantize_dual_kernel", "history_commit_kernel", "lse_topk_kernel",
                 "lse_merge_kernel", "nbest_merge_kernel", "embed_kernel", "ancestors_update_kernel", "gather_rows_kernel",
                 "ssru_cell_kernel", "mi8_absmax_kernel", "mi8_quantize_kernel", "mi8_transpose_quantize_kernel"]
 METRIC = "int8_decode_tgt_tokens_per_sec"
@@ -89,11 +89,14 @@ def parse_args():
                     help="decode one mini-batch with the in-situ kernel timeline on and write its per-kernel summary to PATH")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="step-driver tuning switch (fuse_weights, quant_in_gemm, fused_output_max_rows, side_stream, attention_unroll)")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline sample (for quick A/B runs)")
     ap.add_argument("--strong", action="store_true",
                     help="strong scaling: the whole fixed corpus, mini-batches taken from a shared counter by whichever rank is free")
     ap.add_argument("--glue", default=None, metavar="KERNEL",
                     help="time one glue kernel at the benchmark's decode shapes (attention1_self, attention1_cross, quantize_slot, "
                          "add_layernorm, lse_topk), the form the ncu captures use")
+    ap.add_argument("--tile-sweep", default=None, metavar="M,K,N",
+                    help="time the GEMM alone (operands already quantised) for every tile width and split-K factor the kernel offers")
     ap.add_argument("--packed8", action="store_true",
                     help="time the packed8avx512 affine on the weight shapes the reference's mjdgemm instantiates, the reference's own CPU code beside it")
     return ap.parse_args()
@@ -453,7 +456,7 @@ def run_ours(args):
             "by_shape": by_shape,
         }
         steps_done = max(1, host["steps"])
-        cpu = cpu_baseline(args, cfg_name=args.model) if world == 1 else None
+        cpu = cpu_baseline(args, cfg_name=args.model) if world == 1 and not args.no_cpu_baseline else None
         line = {
             "metric": METRIC, "value": round(tokens / (ms / 1e3), 1), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / max(1, args.steps), 2),
@@ -537,7 +540,7 @@ def run_trace(args):
     for _ in range(2):
         search.search(ids, mask)
     torch.cuda.synchronize()
-    cap = 400000
+    cap = 1000000
     buf = torch.zeros(2 + 2 * cap, dtype=torch.int64, device=dev)
     check(lib().mi8_trace_begin(buf.data_ptr(), cap))
     stepper.search_stats(reset=True)
@@ -554,52 +557,61 @@ def run_trace(args):
     phase = (tag & np.uint64(0xff)).astype(np.int64)
     kern = ((tag >> np.uint64(8)) & np.uint64(0xff)).astype(np.int64)
     extra = (tag >> np.uint64(16)).astype(np.uint64)
-    # pair the stamps of each launch: per kernel id the phases arrive in order 0, 1, 2
-    launches = []
-    open_launch = {}
+    # pair the stamps of each launch: launches of one kernel (and GEMM shape) follow one another on the stream, so the n-th
+    # stamp of a phase belongs to the n-th launch.  Phases: 0 entry, 1 wait returned, 2 end of block 0, 3 end of the last block;
+    # GEMMs also 4 first operands landed, 5 first accumulator complete, 6 its write-back issued.
+    per_key = {}
     for i in range(n):
         key = (int(kern[i]), int(extra[i]))
-        if phase[i] == 0:
-            open_launch.setdefault(key, []).append([int(t[i]), None, None])
-        elif phase[i] == 1:
-            for rec in open_launch.get(key, []):
-                if rec[1] is None:
-                    rec[1] = int(t[i])
-                    break
-        else:
-            q = open_launch.get(key, [])
-            for j, rec in enumerate(q):
-                if rec[1] is not None and rec[2] is None:
-                    rec[2] = int(t[i])
-                    launches.append((key, rec[0], rec[1], rec[2]))
-                    q.pop(j)
-                    break
+        per_key.setdefault(key, {}).setdefault(int(phase[i]), []).append(int(t[i]))
+    launches = []
+    for key, ph in per_key.items():
+        for idx, t_in in enumerate(ph.get(0, [])):
+            if idx >= len(ph.get(1, [])) or idx >= len(ph.get(2, [])):
+                continue
+            t_end = ph[2][idx]
+            if idx < len(ph.get(3, [])) and len(ph[3]) == len(ph[0]):
+                t_end = max(t_end, ph[3][idx])
+            inner = tuple(ph[k][idx] if idx < len(ph.get(k, [])) and len(ph[k]) == len(ph[0]) else None for k in (4, 5, 6))
+            launches.append((key, t_in, ph[1][idx], t_end, inner))
     launches.sort(key=lambda r: r[2])
     agg = {}
     prev_end = None
-    for key, t_in, t_wait, t_end in launches:
+    for key, t_in, t_wait, t_end, inner in launches:
         k, ex = key
         name = TRACE_KERNELS.get(k, str(k))
         if k in (1, 2, 18, 19):
             name += f" N={ex & 0xfffff},K={(ex >> 20) & 0xfffff},M={'<=512' if (ex >> 40) <= 512 else '>512'}"
-        a = agg.setdefault(name, {"launches": 0, "work_ns": 0, "gap_ns": 0})
+        a = agg.setdefault(name, {"launches": 0, "work_ns": 0, "gap_ns": 0, "pre_ns": 0, "inner": [0, 0, 0, 0], "inner_n": 0})
         a["launches"] += 1
         a["work_ns"] += t_end - t_wait
+        a["pre_ns"] += t_wait - t_in                      # how long the kernel was resident before its predecessor finished
         if prev_end is not None:
             a["gap_ns"] += max(0, t_wait - prev_end)
+        if all(x is not None for x in inner):
+            a["inner"][0] += inner[0] - t_wait            # wait returned -> first operands in shared memory
+            a["inner"][1] += inner[1] - inner[0]          # -> first accumulator complete (main loop)
+            a["inner"][2] += inner[2] - inner[1]          # -> its write-back issued
+            a["inner"][3] += t_end - inner[2]             # -> kernel end (remaining tiles, teardown)
+            a["inner_n"] += 1
         prev_end = max(prev_end or 0, t_end)
     span = (launches[-1][3] - launches[0][1]) if launches else 1
     rows = [{"kernel": k, "launches": v["launches"], "work_us": round(v["work_ns"] / 1e3, 1), "avg_work_us": round(v["work_ns"] / 1e3 / v["launches"], 2),
              "gap_before_us": round(v["gap_ns"] / 1e3, 1), "avg_gap_us": round(v["gap_ns"] / 1e3 / v["launches"], 2),
-             "share_of_span": round((v["work_ns"] + v["gap_ns"]) / span, 4)} for k, v in sorted(agg.items(), key=lambda kv: -(kv[1]["work_ns"] + kv[1]["gap_ns"]))]
+             "avg_resident_before_wait_us": round(v["pre_ns"] / 1e3 / v["launches"], 2),
+             "share_of_span": round((v["work_ns"] + v["gap_ns"]) / span, 4),
+             **({"gemm_phases_avg_us": {"operands_landed": round(v["inner"][0] / 1e3 / v["inner_n"], 2), "main_loop": round(v["inner"][1] / 1e3 / v["inner_n"], 2),
+                                        "write_back": round(v["inner"][2] / 1e3 / v["inner_n"], 2), "rest": round(v["inner"][3] / 1e3 / v["inner_n"], 2)}}
+                if v["inner_n"] else {})}
+            for k, v in sorted(agg.items(), key=lambda kv: -(kv[1]["work_ns"] + kv[1]["gap_ns"]))]
     out = {"workload": wl["desc"], "mini_batch_index": b, "width": widths[b], "tokens": sum(len(x) for x, _ in res), "decoder_steps": host["steps"],
            "wall_ms": round(wall * 1e3, 2), "device_span_ms": round(span / 1e6, 2), "stamps": n, "launches_paired": len(launches),
            "host_per_decoder_step_us": {"issue": round(1e6 * host["issue_s"] / max(1, host["steps"]), 1),
                                         "wait_for_device": round(1e6 * host["wait_s"] / max(1, host["steps"]), 1),
                                         "bookkeeping": round(1e6 * host["host_s"] / max(1, host["steps"]), 1)},
            "options": args.option, "kernels": rows,
-           "note": "work = block 0's time from the return of its wait for the preceding kernel to its end; gap = from the end of the "
-                   "preceding kernel's block 0 to that return (launch hand-over, memory flush, waiting for slower blocks of the predecessor)"}
+           "note": "work = from the return of block 0's wait for the preceding kernel to the later of block 0's and the last block's end; "
+                   "gap = from the end of the preceding kernels to that return (launch hand-over and memory flush)"}
     with open(args.trace, "w") as f:
         json.dump(out, f, indent=1)
     print(json.dumps({k: out[k] for k in ("wall_ms", "device_span_ms", "decoder_steps", "tokens", "host_per_decoder_step_us")}), flush=True)
@@ -621,20 +633,12 @@ def run_strong(args):
     by_cost = sorted(range(len(batches)), key=lambda i: -widths[i])
     golden = load_digests(args.model)
     max_len = int(np.ceil(1.5 * max(widths))) + 2
-    store = dist.distributed_c10d._get_default_store() if world > 1 else None
+    next_batch = parallel.shared_counter()
     order = batch_order(len(batches))
     for i in range(args.warmup):
         search.search(batches[order[i]][1], batches[order[i]][2])
     torch.cuda.synchronize()
     pinned = [(sid, torch.from_numpy(ids.astype(np.int64)).pin_memory(), torch.from_numpy(mask).pin_memory()) for sid, ids, mask in batches]
-    taken = [0]
-
-    def next_batch():
-        if store is None:
-            taken[0] += 1
-            return taken[0] - 1
-        return int(store.add("mi8_next_mini_batch", 1)) - 1
-
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -697,6 +701,10 @@ def run_glue(args):
     st = torch.cuda.current_stream().cuda_stream
     R, d, heads, dh, V = 512, 1024, 16, 64, 32000
     kind = args.glue
+    for item in args.option:                                   # process-wide kernel switches (attention_unroll, attention_block_heads)
+        name, _, value = item.partition("=")
+        from marian_dev_b200.decoder import NativeStepper
+        check(L.mi8d_set_option(None, NativeStepper.OPTIONS[name.strip()], int(value)))
     slot = torch.zeros(64, dtype=torch.int32, device=dev)
     if kind in ("attention1_self", "attention1_cross"):
         length, batch, mode = (24, 128, 0) if kind == "attention1_self" else (32, 128, 1)
@@ -760,7 +768,7 @@ def run_glue(args):
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1000.0 / iters
     print(json.dumps({"metric": "glue_kernel", "kernel": kind, "shape": shape, "us_per_launch": round(us, 2), "algorithmic_bytes": by,
-                      "GBps": round(by / us / 1e3, 1), "operand_sets": sets,
+                      "GBps": round(by / us / 1e3, 1), "operand_sets": sets, "options": args.option,
                       "timing": f"{iters} back-to-back launches (programmatic dependent launch on), CUDA events"}), flush=True)
 
 
@@ -1053,6 +1061,64 @@ def run_packed8(args):
             print(json.dumps(r), flush=True)
 
 
+def run_tile_sweep(args):
+    """The int8 GEMM alone on one shape under every plan the kernel accepts: tile widths 32..256 (and the two-CTA kernel) x split-K
+    1..8, CUDA-graph replay of 40 launches over operand sets rotated through more than the L2 capacity.  The plan the library
+    would pick by itself is marked."""
+    import torch
+    from marian_dev_b200 import multiply_plan, ops
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    m, k, n = (int(v) for v in args.tile_sweep.split(","))
+    per_copy = m * k + n * k + 4 * m * n
+    copies = max(2, min(32, int(300e6 // per_copy) + 1))
+    aqs = [ops.prepareA(torch.randn(m, k, device=dev)) for _ in range(copies)]
+    ws = [ops.prepareB(torch.randn(k, n, device=dev) * 0.02) for _ in range(copies)]
+    bias = torch.randn(n, device=dev) * 0.01
+    outs = [torch.empty(m, n, device=dev) for _ in range(copies)]
+    wsp = ops.Workspace(device=dev)
+    auto = multiply_plan(m, n, k)
+    warm = torch.randn(8192, 8192, device=dev, dtype=torch.bfloat16)
+    for _ in range(20):
+        warm @ warm
+    for tile in (0, 16, 32, 64, 128, 256, 512):
+        for splits in (0, 1, 2, 4, 8):
+            if (tile == 0) != (splits == 0) or (tile == 512 and splits > 1) or (tile == 16 and m > 16):
+                continue
+            try:
+                plan = multiply_plan(m, n, k, tile, splits)
+
+                def run(i):
+                    j = i % copies
+                    ops.multiply(aqs[j], ws[j], bias, 1.0, False, out=outs[j], ws=wsp, tile_m=tile, splits=splits)
+                for i in range(3):
+                    run(i)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                st = torch.cuda.Stream()
+                with torch.cuda.stream(st):
+                    with torch.cuda.graph(g, stream=st):
+                        for i in range(40):
+                            run(i)
+                    g.replay()
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(st)
+                    g.replay()
+                    e1.record(st)
+                    torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1000.0 / 40
+            except Exception as e:                      # a plan the kernel refuses for this shape
+                print(json.dumps({"M": m, "K": k, "N": n, "tile": tile, "splits": splits, "refused": str(e)[:80]}), flush=True)
+                continue
+            by = m * k + k * n + 4 * n + 4 * m * n + 8
+            print(json.dumps({"M": m, "K": k, "N": n, "tile": plan["tile_m"], "splits": plan["splits"], "ctas": plan["grid"],
+                              "automatic": tile == 0, "us": round(us, 2), "GBps": round(by / us / 1e3, 1),
+                              "TOPS": round(2.0 * m * n * k / us / 1e6, 1)}), flush=True)
+    if ops.poll_status() != 0:
+        raise RuntimeError("device status set during the tile sweep")
+
+
 def run_affines(args):
     import torch
     if not torch.cuda.is_available():
@@ -1099,6 +1165,8 @@ if __name__ == "__main__":
         run_glue(a)
     elif a.strong:
         run_strong(a)
+    elif a.tile_sweep:
+        run_tile_sweep(a)
     elif a.packed8:
         run_packed8(a)
     elif a.affine or a.sweep:

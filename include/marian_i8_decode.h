@@ -140,15 +140,18 @@ int mi8d_history_reuse(mi8d_decoder* d, unsigned out[2], int reset);
  *   MI8D_OPT_FUSED_OUTPUT_MAX_ROWS (default 480): up to this many rows the output layer reduces its logits inside
  *     the GEMM's write-back, above it the logits are written and read back by the log-softmax / top-k kernel;
  *   MI8D_OPT_SIDE_STREAM (default 1): the re-projection of the earlier history slabs runs on an internal stream;
- *   MI8D_OPT_ATTENTION_UNROLL (8 or 16, default 16; process-wide): key/value rows a thread keeps in flight. */
+ *   MI8D_OPT_ATTENTION_UNROLL (8 or 16, default 8; process-wide): key/value rows a thread keeps in flight;
+ *   MI8D_OPT_ATTENTION_BLOCK_HEADS (default 8, 0 = all; process-wide): heads one block of the decoder attention serves;
+ *     a divisor of the head count splits every query row over several smaller blocks. */
 enum mi8d_option {
   MI8D_OPT_FUSE_WEIGHTS = 1,
   MI8D_OPT_QUANT_IN_GEMM = 2,
   MI8D_OPT_FUSED_OUTPUT_MAX_ROWS = 3,
   MI8D_OPT_SIDE_STREAM = 4,
-  MI8D_OPT_ATTENTION_UNROLL = 5
+  MI8D_OPT_ATTENTION_UNROLL = 5,
+  MI8D_OPT_ATTENTION_BLOCK_HEADS = 6
 };
-int mi8d_set_option(mi8d_decoder* d, int option, int value);
+int mi8d_set_option(mi8d_decoder* d, int option, int value);   /* d may be NULL for the process-wide switches */
 
 /* keep != 0: every step also writes its logits [beam*batch, vocab] (the output layer then runs unfused);
  * mi8d_last_logits returns them.  Off by default: the fused output layer never materialises them. */

@@ -517,8 +517,8 @@ int mi8d_set_positions(mi8d_decoder* d, const float* table) {
 }
 
 int mi8d_set_option(mi8d_decoder* d, int option, int value) {
-  if(d == nullptr)
-    return MI8_ERR_BAD_ARG;
+  if(d == nullptr && option != MI8D_OPT_ATTENTION_UNROLL && option != MI8D_OPT_ATTENTION_BLOCK_HEADS)
+    return MI8_ERR_BAD_ARG;   // (the process-wide switches need no decoder)
   switch(option) {
     case MI8D_OPT_FUSE_WEIGHTS: d->opt_fuse = value != 0; break;
     case MI8D_OPT_QUANT_IN_GEMM: d->opt_quant_in_gemm = value != 0; break;
@@ -529,6 +529,7 @@ int mi8d_set_option(mi8d_decoder* d, int option, int value) {
         return MI8_ERR_BAD_ARG;
       set_attention_unroll(value);
       break;
+    case MI8D_OPT_ATTENTION_BLOCK_HEADS: set_attention_block_heads(value); break;
     default: return MI8_ERR_BAD_ARG;
   }
   return MI8_OK;

@@ -418,6 +418,8 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->full[s], ph, abort_flag, p.spin_limit));
         if(!ok)
           break;
+        if(it == 0)
+          trace_stamp(trace_open_thread(32), kTraceId, 4, trace_extra);   // the first operands have landed
         tc_fence_after_sync();
         const uint32_t w_addr = smem_u32(tiles + s * T::kStageBytes);
         const uint32_t a_addr = w_addr + T::kWBytes;
@@ -456,22 +458,13 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const bool has_chunks = kChunks > 1 || group == 0;
     pdl_wait();  // the activation multiplier (or abs-max slot) is written by the previous kernel
     trace_stamp(tb, kTraceId, 1, trace_extra);
-    float qa;
-    if(kQuantA) {
-      const unsigned bits = *p.a_slot;
-      qa = bits == 0u ? 1.0f : __fdiv_rn(127.0f, __uint_as_float(bits));
-      if(blockIdx.x == 0 && epi_tid == 0) {
-        if(p.qa_out != nullptr)
-          *p.qa_out = qa;
-        if(bits >= 0x7f800000u)
-          atomicMax(p.status, static_cast<int>(kDevNonFinite));
-      }
-    } else if(kP8) {
-      qa = 1.0f;
-    } else {
+    // kQuantA: the multiplier comes from the abs-max slot, which is read only after the first fp32 loads of the
+    // activation have been issued (below), so the two round trips to L2 overlap instead of following one another.
+    float qa = 1.0f;
+    bool qa_ready = !kQuantA;
+    if(!kQuantA && !kP8)
       qa = *p.d_qa;
-    }
-    float unquant = kP8 ? 1.0f : __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.seg_qb[0])), p.scale);
+    float unquant = (kP8 || kQuantA) ? 1.0f : __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.seg_qb[0])), p.scale);
     uint32_t acc_it = 0;
     uint32_t conv_it = 0;
     const bool skip_on = p.skip_a != nullptr && *p.skip_a == *p.skip_b;
@@ -486,7 +479,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         // The fp32 loads of several K blocks are issued together (they do not depend on the ring), so a
         // tile costs about one L2 round trip per batch instead of one per K block.
         constexpr int kCpt = (TM * 8 + kEpilogueThreads - 1) / kEpilogueThreads;   // chunks per thread and K block
-        constexpr int kBatch = kCpt == 1 ? 4 : 2;
+        constexpr int kBatch = 8 / kCpt;   // 32 16-byte loads in flight per thread: all of K = 1024 in one round trip
         for(int kb0 = wi.kb_begin; kb0 < wi.kb_end && ok; kb0 += kBatch) {
           float4 f[kBatch][kCpt][4];
 #pragma unroll
@@ -502,6 +495,18 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
               for(int e = 0; e < 4; ++e)
                 f[b][q][e] = in ? src[e] : make_float4(0.f, 0.f, 0.f, 0.f);
             }
+          }
+          if(!qa_ready) {
+            const unsigned bits = *p.a_slot;
+            qa = bits == 0u ? 1.0f : __fdiv_rn(127.0f, __uint_as_float(bits));
+            unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.seg_qb[0])), p.scale);
+            if(blockIdx.x == 0 && epi_tid == 0) {
+              if(p.qa_out != nullptr)
+                *p.qa_out = qa;
+              if(bits >= 0x7f800000u)
+                atomicMax(p.status, static_cast<int>(kDevNonFinite));
+            }
+            qa_ready = true;
           }
 #pragma unroll
           for(int b = 0; b < kBatch; ++b) {
@@ -544,6 +549,8 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       if(!ok)
         break;
       tc_fence_after_sync();
+      if(acc_it == 0)
+        trace_stamp(tb, kTraceId, 5, trace_extra);   // the first accumulator is complete
 
       const uint32_t t_addr = tmem_base + as * T::kAccStride + (static_cast<uint32_t>(quarter * 32) << 16);
       const int n = wi.n_tile * kTileN + row;
@@ -754,6 +761,8 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before_sync();
       mbar_arrive(&ctl->tmem_empty[as]);
+      if(acc_it == 0)
+        trace_stamp(tb, kTraceId, 6, trace_extra);   // its write-back is issued
       ++acc_it;
     }
     if(!ok) {
@@ -783,6 +792,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     tmem_dealloc(tmem_base, T::kTmemCols);
   }
   trace_stamp(tb, kTraceId, 2, trace_extra);
+  trace_last_block_end(kTraceId, trace_extra);
 }
 
 // ------------------------------------------------------------------ CTA-pair variant (large M)
@@ -1088,6 +1098,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     tmem_dealloc_pair(tmem_base, T::kTmemCols);
   }
   trace_stamp(tb, kTrGemmPair, 2, trace_extra);
+  trace_last_block_end(kTrGemmPair, trace_extra);
 }
 
 // ------------------------------------------------------------------ host side
@@ -1252,7 +1263,8 @@ int launch_cfg(const CUtensorMap& tw, const CUtensorMap& ta, const GemmParams& p
   ProfileRecord rec{};
   const bool profiled = t_profile.on && t_profile.records.size() < t_profile.capacity;
   if(profiled) {
-    rec = ProfileRecord{p.M, p.N, p.K, p.out_f16 ? 2 : 4, t_profile.take(), t_profile.take()};
+    // (the output-layer variant runs with swapped operands: report the problem as the caller sees it)
+    rec = ProfileRecord{kTopK > 0 ? p.N : p.M, kTopK > 0 ? p.M : p.N, p.K, p.out_f16 ? 2 : 4, t_profile.take(), t_profile.take()};
     if(rec.start != nullptr && rec.stop != nullptr)
       cudaEventRecord(rec.start, stream);
   }
@@ -1360,6 +1372,8 @@ int profile_begin(int max_records) {
   if(cudaMalloc(reinterpret_cast<void**>(&t_profile.d_rows), sizeof(int) * static_cast<size_t>(max_records)) != cudaSuccess) {
     cudaGetLastError();
     t_profile.d_rows = nullptr;
+  } else {
+    cudaMemset(t_profile.d_rows, 0xff, sizeof(int) * static_cast<size_t>(max_records));   // -1: "not reported"
   }
   t_profile.on = true;
   t_profile.capacity = static_cast<size_t>(max_records);
@@ -1851,6 +1865,7 @@ int launch_gemm_logits(const int8_t* aq, const float* d_qa, const int8_t* wq, co
     return MI8_ERR_LAUNCH;
   single_segment(p);
   finish_params(p);
+  p.rows_computed = nullptr;   // (in this launch p.M counts vocabulary entries, not activation rows)
   return k_top == 4 ? launch_cfg<256, false, 4>(tw, ta, p, plan, stream) : launch_cfg<256, false, 8>(tw, ta, p, plan, stream);
 }
 

@@ -76,6 +76,7 @@ embed_kernel(const float* __restrict__ wemb, const int* __restrict__ words, cons
       atomicMax(absmax_slot2, m);
   }
   trace_stamp(tb, kTrEmbed, 2);
+  trace_last_block_end(kTrEmbed);
 }
 
 // out = LayerNorm(a + resid) * gamma + beta, one block of 256 threads per row; biased variance
@@ -154,6 +155,7 @@ add_layernorm_kernel(const float* __restrict__ a, const float* __restrict__ resi
       atomicMax(absmax_slot2, m);
   }
   trace_stamp(tb, kTrAddLn, 2);
+  trace_last_block_end(kTrAddLn);
 }
 
 __device__ __forceinline__ int quantize_one(float v, float qm) {
@@ -199,6 +201,7 @@ quantize_slot_kernel(const float* __restrict__ x, size_t n, const unsigned* __re
   for(size_t i = n16 * 16 + tid; i < n; i += stride)
     q[i] = static_cast<int8_t>(quantize_one(x[i], qm));
   trace_stamp(tb, kTrQuantSlot, 2);
+  trace_last_block_end(kTrQuantSlot);
 }
 
 // Two quantisations in one launch, for the start of a decoder self-attention block: blocks [0, blocks_x)
@@ -254,6 +257,7 @@ quantize_dual_kernel(const float* __restrict__ x, size_t n, const unsigned* __re
     }
   }
   trace_stamp(tb, kTrQuantDual, 2);
+  trace_last_block_end(kTrQuantDual);
 }
 
 // ---- self-attention history ------------------------------------------------------------------
@@ -297,50 +301,7 @@ ancestors_update_kernel(const int* __restrict__ anc_old, int* __restrict__ anc_n
       atomicMax(hist.slot[l], m);
   }
   trace_stamp(tb, kTrAncestors, 2);
-}
-
-// max over t' < steps, r < rows of rowmax[t'][anc[t'][r]], reduced into the (zeroed) slot with atomicMax.
-__global__ void __launch_bounds__(256)
-history_absmax_kernel(const float* __restrict__ rowmax, const int* __restrict__ anc, int steps, int rows, int stride,
-                      unsigned* absmax_slot) {
-  pdl_launch_dependents();
-  pdl_wait();
-  unsigned m = 0u;
-  const int n = steps * rows;
-  for(int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-    const int tp = i / rows, r = i - tp * rows;
-    m = max(m, abs_bits(rowmax[tp * stride + anc[tp * stride + r]]));
-  }
-  m = __reduce_max_sync(0xffffffffu, m);
-  if((threadIdx.x & 31) == 0 && m != 0u)
-    atomicMax(absmax_slot, m);
-}
-
-// hq[t'][row] = quantise(slab[t'][row]) with the multiplier of the current history abs-max, one block per
-// slab row.  Keys/values of earlier steps only change when that abs-max changes: if it still equals the
-// value the stored keys/values were computed with (*prev_bits), the rows of the old slabs are left alone
-// and only the newest slab is quantised (the GEMM that follows skips the old tiles the same way).
-__global__ void __launch_bounds__(128)
-history_quantize_kernel(const float* __restrict__ slabs, int slab_rows, int steps, int dim, const unsigned* __restrict__ absmax_slot,
-                        const unsigned* __restrict__ prev_bits, int8_t* __restrict__ hq, float* __restrict__ d_quant_mult) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const unsigned bits = *absmax_slot;
-  if(blockIdx.x == 0 && threadIdx.x == 0)
-    *d_quant_mult = quant_mult_from_bits(bits);
-  const float qm = quant_mult_from_bits(bits);
-  const int total = steps * slab_rows;
-  const int first = (*prev_bits == bits) ? (steps - 1) * slab_rows : 0;   // unchanged abs-max: only the newest slab
-  for(int out_row = first + blockIdx.x; out_row < total; out_row += gridDim.x) {
-    const float4* src = reinterpret_cast<const float4*>(slabs + static_cast<size_t>(out_row) * dim);
-    uint4* dst = reinterpret_cast<uint4*>(hq + static_cast<size_t>(out_row) * dim);
-    for(int i = threadIdx.x; i < dim / 16; i += blockDim.x) {
-      const float4 a = __ldg(src + 4 * i), b = __ldg(src + 4 * i + 1), c = __ldg(src + 4 * i + 2), d = __ldg(src + 4 * i + 3);
-      uint4 o;
-      o.x = pack4(a, qm); o.y = pack4(b, qm); o.z = pack4(c, qm); o.w = pack4(d, qm);
-      dst[i] = o;
-    }
-  }
+  trace_last_block_end(kTrAncestors);
 }
 
 // prev_bits[l] = slots[first + l * stride]: remembers, per layer, the abs-max the stored keys/values belong to.
@@ -363,6 +324,7 @@ __global__ void history_commit_kernel(unsigned* __restrict__ prev_bits, const un
     prev_bits[l] = now;
   }
   trace_stamp(tb, kTrCommit, 2);
+  trace_last_block_end(kTrCommit);
 }
 
 // ---- single-query attention --------------------------------------------------------------------
@@ -394,10 +356,13 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   extern __shared__ float sc_smem[];  // [heads][len] scores, then probabilities
   constexpr int G = DH / 4;
   const int r = blockIdx.x;
-  const int tid = threadIdx.x;
+  // blockIdx.y selects the group of heads this block serves (blockDim.x / G heads, all of them when gridDim.y == 1);
+  // `tid` is the thread's position in the row (quarter-row slice tid of the model dimension)
+  const int hb = gridDim.y == 1 ? heads : static_cast<int>(blockDim.x) / G;
+  const int tid = blockIdx.y * hb * G + threadIdx.x;
   const int dim = heads * DH;
   const bool active = tid < dim / 4;
-  const int head = tid / G, j = tid % G;
+  const int head = threadIdx.x / G, j = threadIdx.x % G;   // head inside the block's group
   const int group = mode == 1 ? r % batch : (mode == 2 ? r / len : 0);
   const size_t base = mode == 0 ? static_cast<size_t>(r) : static_cast<size_t>(group) * len;
   const size_t stride = (mode == 0 ? static_cast<size_t>(rows) : 1) * dim;
@@ -407,9 +372,9 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   // mode 0 with an ancestor table: keys/values are stored per step in that step's row order, and the row
   // of position p that query row r descends from is anc[p][r]
   const bool indirect = mode == 0 && anc != nullptr;
-  int* anc_s = reinterpret_cast<int*>(sc_smem + heads * len);   // [len] ancestor rows of this query row
+  int* anc_s = reinterpret_cast<int*>(sc_smem + hb * len);   // [len] ancestor rows of this query row
   if(indirect) {
-    for(int p = tid; p < len; p += blockDim.x)
+    for(int p = threadIdx.x; p < len; p += blockDim.x)
       anc_s[p] = anc[static_cast<size_t>(p) * anc_stride + r];
     __syncthreads();
   }
@@ -491,10 +456,11 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   }
   if(absmax_slot) {
     m_abs = __reduce_max_sync(0xffffffffu, m_abs);
-    if((tid & 31) == 0 && m_abs != 0u)
+    if((threadIdx.x & 31) == 0 && m_abs != 0u)
       atomicMax(absmax_slot, m_abs);
   }
   trace_stamp(tb, kTrAttention1, 2);
+  trace_last_block_end(kTrAttention1);
 }
 
 // Encoder self-attention (mode 2) with the keys and values of one (sentence, head) staged in shared memory: block
@@ -613,6 +579,7 @@ attention_enc_kernel(const float* __restrict__ q, const float* __restrict__ k, c
       atomicMax(absmax_slot, m_abs);
   }
   trace_stamp(tb, kTrAttentionEnc, 2);
+  trace_last_block_end(kTrAttentionEnc);
 }
 
 // ---- output layer: log-softmax + per-row top-k --------------------------------------------------
@@ -788,6 +755,7 @@ lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __rest
     cand_word[r * K + threadIdx.x] = s_i[threadIdx.x];
   }
   trace_stamp(tb, kTrLseTopk, 2);
+  trace_last_block_end(kTrLseTopk);
 }
 
 // Second half of the fused output layer: the GEMM's write-back left, per (row, block of 128 vocabulary entries),
@@ -839,6 +807,7 @@ lse_merge_kernel(const float* __restrict__ blk_max, const float* __restrict__ bl
     cand_word[r * k + threadIdx.x] = s_i[threadIdx.x];
   }
   trace_stamp(tb, kTrLseMerge, 2);
+  trace_last_block_end(kTrLseMerge);
 }
 
 // Per sentence b: merge the beam x K row candidates (rows beam-major: row = j * batch + b) into the
@@ -855,6 +824,7 @@ __global__ void nbest_merge_kernel(const float* __restrict__ cand_score, const i
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if(b >= batch) {
     trace_stamp(tb, kTrNbest, 2);
+    trace_last_block_end(kTrNbest);
     return;
   }
   TopK t;
@@ -880,6 +850,7 @@ __global__ void nbest_merge_kernel(const float* __restrict__ cand_score, const i
     out_word[b * K + n] = valid ? t.i[n] % vocab : 0;
   }
   trace_stamp(tb, kTrNbest, 2);
+  trace_last_block_end(kTrNbest);
 }
 
 // rows gather: out[i,:] = in[idx[i],:]  (16-byte copies when the row length allows it)
@@ -902,6 +873,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const int* __re
       dst[i] = __ldg(src + i);
   }
   trace_stamp(tb, kTrGather, 2);
+  trace_last_block_end(kTrGather);
 }
 
 // SSRU cell (src/rnn/cells.h:1052-1066): c' = c[hyp] * sigmoid(f) + x * (1 - sigmoid(f)); h = relu(c').
@@ -925,14 +897,17 @@ __global__ void ssru_cell_kernel(const float* __restrict__ cell_old, const int* 
     h_out[o] = cn > 0.f ? cn : 0.f;
   }
   trace_stamp(tb, kTrSsru, 2);
+  trace_last_block_end(kTrSsru);
 }
 
-int g_attention_unroll = 16;   // key/value rows a thread of attention1_kernel keeps in flight (8 or 16)
+int g_attention_block_heads = 8;   // heads one block of attention1_kernel serves (0 = all heads of the row)
+int g_attention_unroll = 8;   // key/value rows a thread of attention1_kernel keeps in flight (8 or 16; 16 costs a block per SM and measured 7 % slower)
 
 }  // namespace
 
 MI8_DEFINE_TRACE_SETTER(trace_set_glue)
 void set_attention_unroll(int u) { g_attention_unroll = u; }
+void set_attention_block_heads(int h) { g_attention_block_heads = h; }
 
 // ------------------------------------------------------------------------------------------------ launchers
 int launch_embed(const float* wemb, const int* words, const float* pos, int pos_mod, float scale, int rows, int dim, float* out,
@@ -1009,26 +984,6 @@ int launch_quantize_dual(const float* x, size_t n, const unsigned* slot_x, int8_
   return check_launch();
 }
 
-int launch_history_absmax(const float* rowmax, const int* anc, int steps, int rows, int stride, unsigned* slot, cudaStream_t s) {
-  int blocks = (steps * rows + 1023) / 1024;
-  blocks = blocks < 1 ? 1 : (blocks > 128 ? 128 : blocks);
-  launch_kernel(history_absmax_kernel, dim3(blocks), dim3(256), 0, s, rowmax, anc, steps, rows, stride, slot);
-  count_launch();
-  return check_launch();
-}
-
-int launch_history_quantize(const float* slabs, int slab_rows, int steps, int dim, const unsigned* slot, const unsigned* prev_bits,
-                            int8_t* hq, float* d_qm, cudaStream_t s) {
-  if(dim % 16 != 0)
-    return MI8_ERR_MISALIGNED;
-  int blocks = steps * slab_rows;
-  const int cap = sm_count() * 16;
-  blocks = blocks > cap ? cap : blocks;
-  launch_kernel(history_quantize_kernel, dim3(blocks), dim3(128), 0, s, slabs, slab_rows, steps, dim, slot, prev_bits, hq, d_qm);
-  count_launch();
-  return check_launch();
-}
-
 int launch_history_commit(unsigned* prev_bits, const unsigned* slots, int first, int stride, int layers, unsigned* stats, cudaStream_t s) {
   if(layers > 64)
     return MI8_ERR_UNSUPPORTED;
@@ -1073,19 +1028,27 @@ int launch_attention1(const float* q, const float* k, const float* v, const floa
       return check_launch();
     }
   }
-  const int threads = ((dim / 4 + 31) / 32) * 32;
-  const size_t smem = (static_cast<size_t>(heads) + 1) * len * sizeof(float);
+  // A block serves `hb` heads of one query row.  Splitting a row over several smaller blocks changes nothing in the
+  // arithmetic (heads are independent) and lets the SMs share the rows out evenly: 512 rows of 256 threads are 3.46
+  // blocks per SM - some SMs get four, the others three - while halves or quarters of rows balance to within a few per cent.
+  const int G = dim_head / 4;
+  int hb = heads;
+  if(g_attention_block_heads > 0 && heads % g_attention_block_heads == 0 && (g_attention_block_heads * G) % 32 == 0)
+    hb = g_attention_block_heads;
+  const int threads = ((hb * G + 31) / 32) * 32;
+  const dim3 agrid(rows, heads / hb);
+  const size_t smem = (static_cast<size_t>(hb) + 1) * len * sizeof(float);
   if(smem > 48 * 1024)
     return MI8_ERR_UNSUPPORTED;
   const bool wide = g_attention_unroll >= 16;
   if(dim_head == 64 && wide)
-    launch_kernel(attention1_kernel<64, 16>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
+    launch_kernel(attention1_kernel<64, 16>, agrid, dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
   else if(dim_head == 64)
-    launch_kernel(attention1_kernel<64, 8>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
+    launch_kernel(attention1_kernel<64, 8>, agrid, dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
   else if(dim_head == 32 && wide)
-    launch_kernel(attention1_kernel<32, 16>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
+    launch_kernel(attention1_kernel<32, 16>, agrid, dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
   else if(dim_head == 32)
-    launch_kernel(attention1_kernel<32, 8>, dim3(rows), dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
+    launch_kernel(attention1_kernel<32, 8>, agrid, dim3(threads), smem, s, q, k, v, log_mask, heads, len, rows, batch, mode, scale, out, slot, anc, anc_stride, kv_rows);
   else
     return MI8_ERR_UNSUPPORTED;
   count_launch();

@@ -144,13 +144,11 @@ int launch_quantize_dual(const float* x, size_t n, const unsigned* slot_x, int8_
                          int steps, int rows_new, int dim, const unsigned* slot_h, const unsigned* prev_bits, int8_t* hq, float* qm_h,
                          cudaStream_t s);
 void set_attention_unroll(int u);
+void set_attention_block_heads(int h);
 // in-situ timeline: each translation unit with kernels installs the buffer in its own copy of the pointer
 int trace_set_glue(unsigned long long* buf);
 int trace_set_gemm(unsigned long long* buf);
 int trace_set_quant(unsigned long long* buf);
-int launch_history_absmax(const float* rowmax, const int* anc, int steps, int rows, int stride, unsigned* slot, cudaStream_t s);
-int launch_history_quantize(const float* slabs, int slab_rows, int steps, int dim, const unsigned* slot, const unsigned* prev_bits,
-                            int8_t* hq, float* d_qm, cudaStream_t s);
 int launch_history_commit(unsigned* prev_bits, const unsigned* slots, int first, int stride, int layers, unsigned* stats, cudaStream_t s);
 int launch_attention1(const float* q, const float* k, const float* v, const float* log_mask, int rows, int heads, int dim_head,
                       int len, int batch, int mode, float* out, unsigned* slot, cudaStream_t s, const int* anc = nullptr,

@@ -32,7 +32,7 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 
 // ---------------------------------------------------------------- in-situ timeline (measurement aid)
 // While a trace buffer is installed (mi8_trace_begin), one thread of block 0 of every kernel stamps the
-// global nanosecond timer at kernel entry, after pdl_wait() and at its exit into the buffer
+// global nanosecond timer at kernel entry (phase 0), after pdl_wait() (1) and at its exit (2; 3 = the last block's exit) into the buffer
 // ([0] = entries used, [1] = capacity, then pairs (time, extra << 16 | kernel << 8 | phase); the GEMMs put
 // N | K << 20 | M << 40 into `extra`).  Unlike events between
 // launches this leaves programmatic dependent launch undisturbed, so it shows what a kernel costs inside the
@@ -46,6 +46,13 @@ enum TraceKernel : int {
 __device__ __forceinline__ unsigned long long* trace_open() {
   return (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == blockDim.x - 1) ? s_trace_buf : nullptr;
 }
+// The same for another thread of block 0 (a kernel whose roles live in different warps stamps from several).
+__device__ __forceinline__ unsigned long long* trace_open_thread(unsigned thread) {
+  return (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == thread) ? s_trace_buf : nullptr;
+}
+// ... and for the last block of the grid, whose end (phase 3) bounds the kernel's duration from the other side:
+// blocks are dispatched in index order, so it is among the last to finish.
+__device__ __forceinline__ void trace_last_block_end(int kernel, unsigned long long extra = 0ull);
 __device__ __forceinline__ void trace_stamp(unsigned long long* tb, int kernel, int phase, unsigned long long extra = 0ull) {
   if(tb != nullptr) {
     unsigned long long t;
@@ -56,6 +63,10 @@ __device__ __forceinline__ void trace_stamp(unsigned long long* tb, int kernel, 
       tb[3 + 2 * idx] = (extra << 16) | (static_cast<unsigned long long>(kernel) << 8) | static_cast<unsigned long long>(phase);
     }
   }
+}
+__device__ __forceinline__ void trace_last_block_end(int kernel, unsigned long long extra) {
+  if(blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1 && threadIdx.x == blockDim.x - 1 && (gridDim.x > 1 || gridDim.y > 1))
+    trace_stamp(s_trace_buf, kernel, 3, extra);
 }
 #define MI8_DEFINE_TRACE_SETTER(name)                                                         \
   int name(unsigned long long* buf) {                                                         \

@@ -75,6 +75,7 @@ mi8_absmax_kernel(const float* __restrict__ x, size_t n, unsigned* partials, uns
   __syncthreads();
   if(!is_last) {
     trace_stamp(tb, kTrAbsmax, 2);
+    trace_last_block_end(kTrAbsmax);
     return;
   }
   __threadfence();
@@ -94,6 +95,7 @@ mi8_absmax_kernel(const float* __restrict__ x, size_t n, unsigned* partials, uns
       *d_quant_mult = (m == 0u) ? 1.0f : __fdiv_rn(127.0f, mx);
   }
   trace_stamp(tb, kTrAbsmax, 2);
+  trace_last_block_end(kTrAbsmax);
 }
 
 __device__ __forceinline__ int quantize_one(float v, float qm) {
@@ -135,6 +137,7 @@ mi8_quantize_kernel(const float* __restrict__ x, size_t n, const float* __restri
   for(size_t i = n16 * 16 + tid; i < n; i += stride)
     q[i] = static_cast<int8_t>(quantize_one(x[i], qm));
   trace_stamp(tb, kTrQuantize, 2);
+  trace_last_block_end(kTrQuantize);
 }
 
 // W fp32 [K,N] row-major -> Bt int8 [N,K] row-major.  A block moves a 32(k) x 32(n) tile through

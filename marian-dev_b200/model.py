@@ -70,9 +70,10 @@ CONFIGS = {
     "student": TransformerConfig(256, 1536, 8, 12, 2, 32000, decoder_autoreg="rnn"),
     "tiny": TransformerConfig(64, 128, 2, 2, 2, 512),
     "tiny-ssru": TransformerConfig(64, 128, 2, 2, 2, 512, decoder_autoreg="rnn"),
-    # small models whose width is a multiple of 128, the condition for multiplying Wk|Wv (Wq|Wk|Wv, W|Wf) in one launch
-    "small": TransformerConfig(128, 256, 4, 2, 2, 512),
-    "small-ssru": TransformerConfig(128, 256, 4, 2, 2, 512, decoder_autoreg="rnn"),
+    # small models whose width is a multiple of 128 (the condition for multiplying Wk|Wv, Wq|Wk|Wv, W|Wf in one launch) and
+    # whose heads are 64 wide and come in fours (the condition for the decoder attention that serves all beams per block)
+    "small": TransformerConfig(256, 512, 4, 2, 2, 512),
+    "small-ssru": TransformerConfig(256, 512, 4, 2, 2, 512, decoder_autoreg="rnn"),
 }
 
 

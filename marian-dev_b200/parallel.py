@@ -28,6 +28,40 @@ def shard_batches(batches, rank: int, world: int, snake: bool = False):
     return out
 
 
+def shared_counter(key: str = "mi8_next_mini_batch"):
+    """A counter shared by all ranks: the returned callable hands out 0, 1, 2, ... with every value going to exactly one
+    rank (an atomic add on the process group's key-value store; a local counter without a process group).  It is how the
+    reference's translator deals mini-batches - its thread pool gives the next one to whichever device is free
+    (src/translator/translator.h:154-167) - when the ranks are processes instead of threads."""
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size() == 1:
+        state = [0]
+
+        def take_local() -> int:
+            state[0] += 1
+            return state[0] - 1
+        return take_local
+    store = dist.distributed_c10d._get_default_store()
+
+    def take() -> int:
+        return int(store.add(key, 1)) - 1
+    return take
+
+
+def pack_outputs(local: dict, rows: int, max_len: int):
+    """{sentence id: tokens} as one int32 matrix [max(rows, 1), 2 + max_len] of (id, length, tokens), unused cells -1.
+    A hypothesis longer than max_len is an error, never cut: outputs must not depend on the number of ranks."""
+    import numpy as np
+    mat = np.full((max(rows, 1), 2 + max_len), -1, dtype=np.int32)     # built and decoded with NumPy: no per-element tensor access
+    for r, (sid, toks) in enumerate(sorted(local.items())):
+        if len(toks) > max_len:
+            raise ValueError(f"sentence {sid} has {len(toks)} tokens but the gather matrix holds {max_len}: "
+                             "size max_len from the search's length limit (max_length_factor x the widest source)")
+        mat[r, 0], mat[r, 1] = sid, len(toks)
+        if toks:
+            mat[r, 2:2 + len(toks)] = toks
+    return mat
+
+
 def gather_outputs(local: dict, max_len: int, device=None) -> dict:
     """All ranks contribute {sentence id: tokens}; every rank receives the union.  The payload is one
     int32 matrix [sentences, 2 + max_len] per rank (id, length, tokens), padded to the largest count."""
@@ -40,15 +74,7 @@ def gather_outputs(local: dict, max_len: int, device=None) -> dict:
     counts = [torch.zeros_like(n) for _ in range(world)]
     dist.all_gather(counts, n)
     rows = int(max(int(c.item()) for c in counts))
-    mat = np.full((max(rows, 1), 2 + max_len), -1, dtype=np.int32)     # built and decoded with NumPy: no per-element tensor access
-    for r, (sid, toks) in enumerate(sorted(local.items())):
-        if len(toks) > max_len:
-            raise ValueError(f"sentence {sid} has {len(toks)} tokens but the gather matrix holds {max_len}: "
-                             "size max_len from the search's length limit (max_length_factor x the widest source)")
-        mat[r, 0], mat[r, 1] = sid, len(toks)
-        if toks:
-            mat[r, 2:2 + len(toks)] = toks
-    mat_t = torch.from_numpy(mat).to(dev)
+    mat_t = torch.from_numpy(pack_outputs(local, rows, max_len)).to(dev)
     out = [torch.empty_like(mat_t) for _ in range(world)]
     dist.all_gather(out, mat_t)
     merged = {}

@@ -70,13 +70,14 @@ def test_options_do_not_change_the_output(cuda_device):
                 want[int(s)] = toks
         gpu = decoder.Int8Transformer(cfg, params, cuda_device)
         settings = [{}, {"fuse_weights": 0}, {"quant_in_gemm": 1}, {"fused_output_max_rows": 0}, {"fused_output_max_rows": 4096},
-                    {"side_stream": 0}, {"attention_unroll": 8}]
+                    {"side_stream": 0}, {"attention_unroll": 16}, {"attention_block_heads": 2}, {"attention_block_heads": 0}]
         for opts in settings:
             stepper = decoder.NativeStepper(gpu, max_batch=20, beam=beam, max_src=24, max_steps=48)
             for k, v in opts.items():
                 stepper.set_option(k, v)
             got, _ = decoder.decode_corpus(gpu, batches, beam=beam, native=stepper)
-            stepper.set_option("attention_unroll", 16)
+            stepper.set_option("attention_unroll", 8)                    # (these switches are process-wide: back to the defaults)
+            stepper.set_option("attention_block_heads", 8)
             assert ops.poll_status() == 0
             diff = [k for k in want if want[k] != got[k]]
             assert not diff, f"{cfg_name} beam {beam} with {opts}: {len(diff)} of {len(want)} sentences differ"

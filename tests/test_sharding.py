@@ -132,3 +132,58 @@ def test_shard_rows_covers_all_rows_once():
             assert spans[0][0] == 0 and spans[-1][1] == m
             assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
             assert max(e - b for b, e in spans) - min(e - b for b, e in spans) <= 1
+
+
+def _counter_worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from marian_dev_b200 import parallel
+    take = parallel.shared_counter("test_counter")
+    dist.barrier()
+    mine = []
+    while True:
+        i = take()
+        if i >= 23:
+            break
+        mine.append(i)
+        if rank == 0:                            # a slow rank simply takes fewer
+            import time
+            time.sleep(0.01)
+    merged = parallel.gather_outputs({i: [i, rank] for i in mine}, max_len=4)
+    if rank == 0:
+        out.put((mine, merged))
+    dist.destroy_process_group()
+
+
+def test_shared_counter_deals_every_mini_batch_to_exactly_one_rank():
+    """Strong scaling deals from one counter: two gloo ranks draw until it runs out; together they hold every value once."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_counter_worker, args=(r, 2, 29741, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    mine0, merged = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(merged) == list(range(23))
+    owners = {i: v[1] for i, v in merged.items()}
+    assert sorted(i for i, r in owners.items() if r == 0) == sorted(mine0)
+    assert 0 < len(mine0) < 23                                   # both ranks took part
+
+
+def test_shared_counter_without_a_process_group():
+    from marian_dev_b200 import parallel
+    take = parallel.shared_counter()
+    assert [take() for _ in range(4)] == [0, 1, 2, 3]
+
+
+def test_gather_refuses_to_truncate():
+    import pytest
+    from marian_dev_b200 import parallel
+    assert parallel.gather_outputs({1: [1, 2, 3]}, max_len=2) == {1: [1, 2, 3]}      # single process: nothing to pack
+    m = parallel.pack_outputs({4: [9, 8], 2: []}, rows=3, max_len=2)
+    assert m.tolist() == [[2, 0, -1, -1], [4, 2, 9, 8], [-1, -1, -1, -1]]
+    with pytest.raises(ValueError, match="3 tokens"):
+        parallel.pack_outputs({1: [1, 2, 3]}, rows=1, max_len=2)
