@@ -44,6 +44,15 @@ void mi8d_destroy(mi8d_decoder* d);
 /* Registers an intgemm8 parameter (Bt[N,K] int8 followed by its fp32 multiplier) under Marian's name,
  * e.g. "decoder_l1_self_Wq"; "Wemb_intgemm8" is the quantised tied output matrix [vocab, dim_emb]. */
 int mi8d_set_weight(mi8d_decoder* d, const char* name, const int8_t* bt, int K, int N);
+/* Registers a packed8avx512 parameter under Marian's name: the row-major Bt[N,K] copy of its int8 matrix (mi8p_unpack_b)
+ * and the per-column scale, zero point and column offset of the item's tail (src/tensors/cpu/fbgemm/packed_gemm.cpp:372-480).
+ * A decoder that received one packed8avx512 weight runs EVERY affine through that scheme, as the reference does for a model
+ * converted with marian-conv --gemm-type packed8avx512 (fbgemmPacked8Gemm -> mjdgemm::gemmInt8Packed,
+ * src/tensors/cpu/fbgemm/packed_gemm.cpp:566-592): activations are quantised per row, so earlier keys/values of the decoder's
+ * self-attention never change and are kept as a plain cache; the tied output matrix is registered as "Wemb_packed8"
+ * (the conversion of Wemb^T [dim_emb, vocab]).  Mixing both kinds of weights is an error at the first step (MI8_ERR_BAD_ARG). */
+int mi8d_set_packed8_weight(mi8d_decoder* d, const char* name, const int8_t* bt, const float* scale_b, const int32_t* zp_b,
+                            const int32_t* off_b, int K, int N);
 /* Registers a float32 parameter (biases, LayerNorm scale/bias, "Wemb", "decoder_ff_logit_out_b"). */
 int mi8d_set_param(mi8d_decoder* d, const char* name, const float* p);
 /* Sinusoidal position table [max_steps, dim_emb] (src/tensors/gpu/tensor_operators.cu:793-817). */

@@ -28,8 +28,20 @@ struct Weight {
 // One affine as the step loop uses it: everything resolved to pointers once (no name lookups per step).
 struct Aff {
   const int8_t* bt = nullptr;
-  const float* qm = nullptr;
+  const float* qm = nullptr;       // intgemm8: the weight's multiplier
   const float* bias = nullptr;
+  int K = 0, N = 0;
+  // packed8avx512: per-column scale, zero point and column offset instead of one multiplier
+  bool p8 = false;
+  const float* scale_b = nullptr;
+  const int32_t* zp_b = nullptr;
+  const int32_t* off_b = nullptr;
+};
+struct P8Weight {
+  const int8_t* bt = nullptr;
+  const float* scale_b = nullptr;
+  const int32_t* zp_b = nullptr;
+  const int32_t* off_b = nullptr;
   int K = 0, N = 0;
 };
 // Several weights of the same shape multiplied with the same activation in one launch (Wk|Wv, Wq|Wk|Wv,
@@ -95,6 +107,8 @@ struct mi8d_decoder {
   void* ws = nullptr;
   size_t ws_bytes = 0;
   std::unordered_map<std::string, Weight> weights;
+  std::unordered_map<std::string, P8Weight> p8_weights;   // packed8avx512 model: every affine's weight is registered here instead
+  bool p8 = false;
   std::unordered_map<std::string, const float*> params;
   const float* positions = nullptr;
   // resolved model (rebuilt by resolve() after a parameter was registered)
@@ -135,6 +149,9 @@ struct mi8d_decoder {
   bool keep_logits = false;
   unsigned* slots = nullptr;
   int n_slots = 0;
+  // packed8avx512: scale, zero point and sum of every row of the activation quantised last
+  float* p8_scale_a = nullptr;
+  int32_t *p8_zp_a = nullptr, *p8_sum_a = nullptr;
   // Re-projecting the keys/values of the EARLIER history slabs (needed only when the history's abs-max changed) does
   // not depend on the query projection: it runs on an internal stream, forked from and joined to the caller's
   // stream with events, beside the query projection and the newest slab's keys/values.
@@ -212,6 +229,10 @@ struct mi8d_decoder {
     }
     n_slots = kSlotsPerLayer * c.dec_depth + 8 + 4 * c.enc_depth;
     slots = arena.take<unsigned>(n_slots);
+    const size_t max_act_rows = R > B * S ? R : B * S;
+    p8_scale_a = arena.take<float>(max_act_rows);
+    p8_zp_a = arena.take<int32_t>(max_act_rows);
+    p8_sum_a = arena.take<int32_t>(max_act_rows);
     // storage of the fused weight matrices (copies of the registered int8 matrices, made once by resolve())
     can_fuse = d % 128 == 0;
     fused_enc.assign(c.enc_depth, nullptr);
@@ -240,13 +261,27 @@ struct mi8d_decoder {
     return it == params.end() ? nullptr : it->second;
   }
   bool aff(Aff& a, const std::string& wname, const std::string& bname) const {
-    const Weight* w = W(wname);
-    if(w == nullptr)
-      return false;
-    a.bt = w->bt;
-    a.qm = w->qm();
-    a.K = w->K;
-    a.N = w->N;
+    a = Aff();
+    if(p8) {
+      auto it = p8_weights.find(wname);
+      if(it == p8_weights.end())
+        return false;
+      a.p8 = true;
+      a.bt = it->second.bt;
+      a.scale_b = it->second.scale_b;
+      a.zp_b = it->second.zp_b;
+      a.off_b = it->second.off_b;
+      a.K = it->second.K;
+      a.N = it->second.N;
+    } else {
+      const Weight* w = W(wname);
+      if(w == nullptr)
+        return false;
+      a.bt = w->bt;
+      a.qm = w->qm();
+      a.K = w->K;
+      a.N = w->N;
+    }
     a.bias = nullptr;
     if(!bname.empty()) {
       a.bias = P(bname);
@@ -263,7 +298,7 @@ struct mi8d_decoder {
   // copies the matrices of `parts` one behind the other into `store` (stream-ordered on s)
   bool fuse(Fused& f, int8_t* store, std::initializer_list<const Aff*> parts, cudaStream_t s) {
     f = Fused();
-    if(store == nullptr)
+    if(store == nullptr || p8)
       return true;   // not fusable for this model: the step falls back to one launch per matrix
     int i = 0;
     for(const Aff* a : parts) {
@@ -324,7 +359,7 @@ struct mi8d_decoder {
         copies = copies && fuse(w.ctx_kv, fused_ctx[l], {&w.ctx_k, &w.ctx_v}, s);
     }
     wemb = P("Wemb");
-    ok = ok && wemb != nullptr && aff(out_w, "Wemb_intgemm8", "decoder_ff_logit_out_b");
+    ok = ok && wemb != nullptr && aff(out_w, p8 ? "Wemb_packed8" : "Wemb_intgemm8", "decoder_ff_logit_out_b");
     out_bias = out_w.bias;
     if(!ok)
       return MI8_ERR_BAD_ARG;
@@ -392,16 +427,34 @@ int gemm_fused(mi8d_decoder* d, const int8_t* a, const float* qa, int M, const F
   return launch_gemm_call(g);
 }
 
+// The activation quantisation of either scheme into `q`: intgemm8 - Int8::PrepareA with the multiplier 127 / max|x| from the
+// slot the producer reduced (stored behind the data); packed8avx512 - uint8 per row with its own scale, zero point and sum
+// (src/tensors/cpu/mjdgemm/mjdgemm_avx512.cpp:195-276), kept in the decoder's per-row arrays until the next quantisation.
+int quantize_act(mi8d_decoder* d, const float* x, int M, int K, const unsigned* slot, int8_t* q, cudaStream_t s) {
+  if(d->p8)
+    return launch_p8_quantize_rows(x, M, K, reinterpret_cast<uint8_t*>(q), d->p8_scale_a, d->p8_zp_a, d->p8_sum_a, s);
+  return launch_quantize_slot(x, static_cast<size_t>(M) * K, slot, q, reinterpret_cast<float*>(q + static_cast<size_t>(M) * K), s);
+}
+
+// ... and the product of that quantised activation with one weight
+int gemm_act(mi8d_decoder* d, const int8_t* q, int M, const Aff& w, bool relu, float* c, cudaStream_t s, unsigned* absmax_out = nullptr,
+             int force_splits = 0) {
+  if(w.p8)
+    return launch_gemm_p8(reinterpret_cast<const uint8_t*>(q), d->p8_scale_a, d->p8_zp_a, d->p8_sum_a, w.bt, w.scale_b, w.zp_b, w.off_b, M, w.N,
+                          w.K, w.bias, relu ? 1 : 0, c, nullptr, d->ws, d->ws_bytes, s, 0, force_splits);
+  return gemm(d, q, M, w, relu, c, s, absmax_out, force_splits);
+}
+
 // Int8::PrepareA of x (multiplier from the slot its producer reduced) followed by the affine: either the
 // quantisation kernel and the GEMM, or - with the option set and a shape that gives every CTA one tile - the GEMM
 // that quantises its operand while loading it.
 int quant_gemm(mi8d_decoder* d, const float* x, int M, const unsigned* slot, const Aff& w, bool relu, float* c, cudaStream_t s,
                unsigned* absmax_out = nullptr) {
   float* qa = reinterpret_cast<float*>(d->aq + static_cast<size_t>(M) * w.K);
-  if(d->opt_quant_in_gemm && w.K <= 1024 && quant_a_tile(M, w.N) != 0)
+  if(!w.p8 && d->opt_quant_in_gemm && w.K <= 1024 && quant_a_tile(M, w.N) != 0)
     return launch_gemm_quant_a(x, slot, qa, w.bt, M, w.N, w.K, w.qm, 1.0f, w.bias, relu ? 1 : 0, c, MI8_F32, nullptr, s, absmax_out);
-  MI8D_TRY(launch_quantize_slot(x, static_cast<size_t>(M) * w.K, slot, d->aq, qa, s));
-  return gemm(d, d->aq, M, w, relu, c, s, absmax_out);
+  MI8D_TRY(quantize_act(d, x, M, w.K, slot, d->aq, s));
+  return gemm_act(d, d->aq, M, w, relu, c, s, absmax_out);
 }
 
 int add_ln(mi8d_decoder* d, const float* a, const float* resid, const Norm& n, int rows, float* out, float* rowmax, unsigned* slot,
@@ -497,6 +550,25 @@ int mi8d_set_weight(mi8d_decoder* d, const char* name, const int8_t* bt, int K, 
   w.K = K;
   w.N = N;
   d->weights[name] = w;
+  d->dirty = true;
+  return MI8_OK;
+}
+
+int mi8d_set_packed8_weight(mi8d_decoder* d, const char* name, const int8_t* bt, const float* scale_b, const int32_t* zp_b, const int32_t* off_b,
+                            int K, int N) {
+  if(d == nullptr || name == nullptr || bt == nullptr || scale_b == nullptr || zp_b == nullptr || off_b == nullptr || K <= 0 || N <= 0)
+    return MI8_ERR_BAD_ARG;
+  if(K % 16 != 0 || (reinterpret_cast<uintptr_t>(bt) & 15u))
+    return MI8_ERR_MISALIGNED;
+  P8Weight w;
+  w.bt = bt;
+  w.scale_b = scale_b;
+  w.zp_b = zp_b;
+  w.off_b = off_b;
+  w.K = K;
+  w.N = N;
+  d->p8_weights[name] = w;
+  d->p8 = true;
   d->dirty = true;
   return MI8_OK;
 }
@@ -691,25 +763,24 @@ int mi8d_encode(mi8d_decoder* d, const int* ids, const float* log_mask, int batc
     unsigned *sa = d->enc_slot(l, 0), *s1 = d->enc_slot(l, 1), *s3 = d->enc_slot(l, 2);
     // q, keys and values are the same tensor: one quantisation serves the three projections, and with fused
     // weights one launch computes all three
-    MI8D_TRY(launch_quantize_slot(x, n_d, x_slot, d->enc_aq, aq_tail, s));
+    MI8D_TRY(quantize_act(d, x, M, dm, x_slot, d->enc_aq, s));
     if(d->opt_fuse && w.qkv.ready) {
       float* outs[3] = {d->enc_q, d->enc_k, d->enc_v};
       MI8D_TRY(gemm_fused(d, d->enc_aq, aq_tail, M, w.qkv, outs, s));
     } else {
-      MI8D_TRY(launch_gemm(d->enc_aq, w.q.bt, M, w.q.N, w.q.K, aq_tail, w.q.qm, 1.0f, w.q.bias, 0, d->enc_q, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
-      MI8D_TRY(launch_gemm(d->enc_aq, w.k.bt, M, w.k.N, w.k.K, aq_tail, w.k.qm, 1.0f, w.k.bias, 0, d->enc_k, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
-      MI8D_TRY(launch_gemm(d->enc_aq, w.v.bt, M, w.v.N, w.v.K, aq_tail, w.v.qm, 1.0f, w.v.bias, 0, d->enc_v, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
+      MI8D_TRY(gemm_act(d, d->enc_aq, M, w.q, false, d->enc_q, s));
+      MI8D_TRY(gemm_act(d, d->enc_aq, M, w.k, false, d->enc_k, s));
+      MI8D_TRY(gemm_act(d, d->enc_aq, M, w.v, false, d->enc_v, s));
     }
     float* a = d->enc_x[1];   // attention output, then reused as x1
     MI8D_TRY(launch_attention1(d->enc_q, d->enc_k, d->enc_v, d->log_mask[0], M, c.heads, dm / c.heads, src, batch, 2, a, sa, s));
-    MI8D_TRY(launch_quantize_slot(a, n_d, sa, d->enc_aq, aq_tail, s));
-    MI8D_TRY(launch_gemm(d->enc_aq, w.o.bt, M, w.o.N, w.o.K, aq_tail, w.o.qm, 1.0f, w.o.bias, 0, d->enc_q, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
+    MI8D_TRY(quantize_act(d, a, M, dm, sa, d->enc_aq, s));
+    MI8D_TRY(gemm_act(d, d->enc_aq, M, w.o, false, d->enc_q, s));
     MI8D_TRY(add_ln(d, d->enc_q, x, w.ln_att, M, a, nullptr, s1, s));                       // x1 = LN(Wo(a) + x)
-    MI8D_TRY(launch_quantize_slot(a, n_d, s1, d->enc_aq, aq_tail, s));
-    MI8D_TRY(launch_gemm(d->enc_aq, w.w1.bt, M, w.w1.N, w.w1.K, aq_tail, w.w1.qm, 1.0f, w.w1.bias, 1, d->enc_h, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0, s3));
-    float* h_tail = reinterpret_cast<float*>(d->enc_aq + static_cast<size_t>(M) * c.dim_ffn);
-    MI8D_TRY(launch_quantize_slot(d->enc_h, static_cast<size_t>(M) * c.dim_ffn, s3, d->enc_aq, h_tail, s));
-    MI8D_TRY(launch_gemm(d->enc_aq, w.w2.bt, M, w.w2.N, w.w2.K, h_tail, w.w2.qm, 1.0f, w.w2.bias, 0, d->enc_q, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
+    MI8D_TRY(quantize_act(d, a, M, dm, s1, d->enc_aq, s));
+    MI8D_TRY(gemm_act(d, d->enc_aq, M, w.w1, true, d->enc_h, s, s3));                        // ReLU (and max|h|) in the write-back
+    MI8D_TRY(quantize_act(d, d->enc_h, M, c.dim_ffn, s3, d->enc_aq, s));
+    MI8D_TRY(gemm_act(d, d->enc_aq, M, w.w2, false, d->enc_q, s));
     const bool last = l + 1 == c.enc_depth;
     float* nx = last ? d->context[0] : x;                                                     // the last layer writes the context
     x_slot = d->enc_slot(l, 3);
@@ -779,18 +850,20 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
     // one quantisation of the context serves the key and value projections of every layer
     const size_t n = static_cast<size_t>(batch) * S * dm;
     float* cq_tail = reinterpret_cast<float*>(d->cq + n);
-    MI8D_TRY(launch_max_absolute(ctx, n, nullptr, cq_tail, d->ws, d->ws_bytes, s));
-    MI8D_TRY(launch_quantize(ctx, n, cq_tail, d->cq, s));
+    if(d->p8) {
+      MI8D_TRY(quantize_act(d, ctx, batch * S, dm, nullptr, d->cq, s));
+    } else {
+      MI8D_TRY(launch_max_absolute(ctx, n, nullptr, cq_tail, d->ws, d->ws_bytes, s));
+      MI8D_TRY(launch_quantize(ctx, n, cq_tail, d->cq, s));
+    }
     for(int l = 0; l < c.dec_depth; ++l) {
       const DecLayerW& w = d->dec_w[l];
       if(d->opt_fuse && w.ctx_kv.ready) {
         float* outs[2] = {d->layers[l].cross_k, d->layers[l].cross_v};
         MI8D_TRY(gemm_fused(d, d->cq, cq_tail, batch * S, w.ctx_kv, outs, s));
       } else {
-        MI8D_TRY(launch_gemm(d->cq, w.ctx_k.bt, batch * S, w.ctx_k.N, w.ctx_k.K, cq_tail, w.ctx_k.qm, 1.0f, w.ctx_k.bias, 0, d->layers[l].cross_k,
-                             MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
-        MI8D_TRY(launch_gemm(d->cq, w.ctx_v.bt, batch * S, w.ctx_v.N, w.ctx_v.K, cq_tail, w.ctx_v.qm, 1.0f, w.ctx_v.bias, 0, d->layers[l].cross_v,
-                             MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, 0));
+        MI8D_TRY(gemm_act(d, d->cq, batch * S, w.ctx_k, false, d->layers[l].cross_k, s));
+        MI8D_TRY(gemm_act(d, d->cq, batch * S, w.ctx_v, false, d->layers[l].cross_v, s));
       }
     }
     d->cross_valid = true;
@@ -806,7 +879,7 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
       rowmax[l] = d->layers[l].rowmax;
       hslot[l] = d->layer_slot(l, kSlotHistory);
     }
-    MI8D_TRY(launch_ancestors_update(d->anc[d->anc_cur], d->anc[anc_new], hyp_idx, t, R, SR, s, c.dec_depth, rowmax, hslot));
+    MI8D_TRY(launch_ancestors_update(d->anc[d->anc_cur], d->anc[anc_new], hyp_idx, t, R, SR, s, d->p8 ? 0 : c.dec_depth, rowmax, hslot));
   }
 
   // layer-0 input: scaled embedding of the previous word (zero at the first step) + position t
@@ -823,16 +896,29 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
     unsigned* x_slot = d->input_slot(l);
     unsigned* s1 = d->layer_slot(l, kSlotSelfLn);
     if(c.ssru) {
-      MI8D_TRY(launch_quantize_slot(x, n_d, x_slot, d->aq, aq_tail, s));
+      MI8D_TRY(quantize_act(d, x, R, dm, x_slot, d->aq, s));
       if(d->opt_fuse && w.rnn.ready) {
         float* outs[2] = {d->qbuf, d->fbuf};
         MI8D_TRY(gemm_fused(d, d->aq, aq_tail, R, w.rnn, outs, s));            // dot(input, W) and affine(input, Wf, bf)
       } else {
-        MI8D_TRY(gemm(d, d->aq, R, w.rnn_w, false, d->qbuf, s));
-        MI8D_TRY(gemm(d, d->aq, R, w.rnn_wf, false, d->fbuf, s));
+        MI8D_TRY(gemm_act(d, d->aq, R, w.rnn_w, false, d->qbuf, s));
+        MI8D_TRY(gemm_act(d, d->aq, R, w.rnn_wf, false, d->fbuf, s));
       }
       MI8D_TRY(launch_ssru_cell(L.cell[d->cell_cur], t == 0 ? nullptr : hyp_idx, d->qbuf, d->fbuf, R, dm, L.cell[cell_new], d->abuf, s));
       MI8D_TRY(add_ln(d, d->abuf, x, w.ln_self, R, d->x1, nullptr, s1, s));
+    } else if(d->p8) {
+      // packed8avx512 quantises every ROW of an activation on its own, so the keys/values of earlier steps never change:
+      // the newest slab is projected and stored, the rest is a plain key/value cache (what the reference recomputes from the
+      // concatenated history, src/models/transformer.h:401-417, comes out identical row by row)
+      unsigned* sa = d->layer_slot(l, kSlotSelfAtt);
+      MI8D_TRY(quantize_act(d, x, R, dm, nullptr, d->aq, s));
+      MI8D_TRY(gemm_act(d, d->aq, R, w.self_q, false, d->qbuf, s));
+      MI8D_TRY(gemm_act(d, d->aq, R, w.self_k, false, L.kslab + static_cast<size_t>(t) * slab_stride, s));
+      MI8D_TRY(gemm_act(d, d->aq, R, w.self_v, false, L.vslab + static_cast<size_t>(t) * slab_stride, s));
+      MI8D_TRY(launch_attention1(d->qbuf, L.kslab, L.vslab, nullptr, R, c.heads, dm / c.heads, t + 1, batch, 0, d->abuf, sa, s, d->anc[anc_new],
+                                 SR, SR));
+      MI8D_TRY(quant_gemm(d, d->abuf, R, sa, w.self_o, false, d->obuf, s));
+      MI8D_TRY(add_ln(d, d->obuf, x, w.ln_self, R, d->x1, nullptr, s1, s));
     } else {
       unsigned* sh = d->layer_slot(l, kSlotHistory);
       unsigned* sa = d->layer_slot(l, kSlotSelfAtt);
@@ -896,9 +982,8 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
 
       unsigned* s3 = d->layer_slot(l, kSlotRelu);
       MI8D_TRY(quant_gemm(d, d->x2, R, s2, w.w1, true, d->hbuf, s, s3));   // ReLU and max|h| fused in the write-back
-      float* h_tail = reinterpret_cast<float*>(d->aq + static_cast<size_t>(R) * c.dim_ffn);
-      MI8D_TRY(launch_quantize_slot(d->hbuf, static_cast<size_t>(R) * c.dim_ffn, s3, d->aq, h_tail, s));
-      MI8D_TRY(gemm(d, d->aq, R, w.w2, false, d->obuf, s));
+      MI8D_TRY(quantize_act(d, d->hbuf, R, c.dim_ffn, s3, d->aq, s));
+      MI8D_TRY(gemm_act(d, d->aq, R, w.w2, false, d->obuf, s));
       // the block's output is the next layer's input: write it straight into that layer's history slab, and its
       // maximum into that layer's history abs-max as well
       const bool last = l + 1 == c.dec_depth;
@@ -912,12 +997,12 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
 
   // tied output layer, then log-softmax + n-best per sentence over beam x vocabulary
   unsigned* x_slot = d->input_slot(c.dec_depth);
-  MI8D_TRY(launch_quantize_slot(x, n_d, x_slot, d->aq, aq_tail, s));
+  MI8D_TRY(quantize_act(d, x, R, dm, x_slot, d->aq, s));
   // Up to opt_fused_out_rows rows the GEMM whose write-back reduces the 128-word blocks is faster than writing the logits
   // and reading them back; for greedy search the plain GEMM followed by the log-softmax / top-k kernel wins.
-  const bool fused_output = !d->keep_logits && R <= d->opt_fused_out_rows && n_best >= 2;
+  const bool fused_output = !d->p8 && !d->keep_logits && R <= d->opt_fused_out_rows && n_best >= 2;
   if(!fused_output) {
-    MI8D_TRY(gemm(d, d->aq, R, d->out_w, false, d->logits, s));
+    MI8D_TRY(gemm_act(d, d->aq, R, d->out_w, false, d->logits, s));
     MI8D_TRY(launch_lse_topk(d->logits, R, c.vocab, n_best, prev_scores, d->cand_score, d->cand_word, s));
   } else {
     // the GEMM's write-back reduces every 128-word block of a row; the logits never reach memory
@@ -929,7 +1014,7 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
   }
   MI8D_TRY(launch_nbest_merge(d->cand_score, d->cand_word, beam, batch, c.vocab, n_best, out_score, out_beam, out_word, s));
 
-  if(!c.ssru)   // remember which abs-max the stored keys/values of every layer now belong to
+  if(!c.ssru && !d->p8)   // remember which abs-max the stored keys/values of every layer now belong to
     MI8D_TRY(launch_history_commit(d->prev_bits, d->slots, 1 + kSlotHistory, kSlotsPerLayer, c.dec_depth, d->reuse_stats, s));
   d->anc_cur = anc_new;
   d->cell_cur = cell_new;

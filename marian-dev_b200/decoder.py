@@ -27,27 +27,39 @@ NEG_MASK = -99999999.0  # transposedLogMask (transformer.h:138-143)
 class Int8Transformer:
     """Model replica on one GPU: converted (intgemm8) weights, fp32 biases / LayerNorm / embeddings."""
 
-    def __init__(self, cfg: TransformerConfig, params: dict, device, output_int8: bool = True, ws=None):
+    def __init__(self, cfg: TransformerConfig, params: dict, device, output_int8: bool = True, ws=None, scheme: str = "intgemm8"):
+        """scheme: "intgemm8" (per-tensor multipliers) or "packed8avx512" (per-column weight and per-row activation
+        quantisation, the FBGEMM / mjdgemm format).  params may hold float arrays (converted here, as marian-conv would),
+        ready IntgemmTensor objects or, for packed8avx512, packed8.Packed8Weight objects / their item bytes."""
+        from . import packed8
+        if scheme not in ("intgemm8", "packed8avx512"):
+            raise ops.Mi8Error(1, f"unknown weight scheme {scheme}")
         self.cfg = cfg
+        self.scheme = scheme
         self.device = torch.device(device)
         self.ws = ws or ops.default_workspace(self.device)
         self.output_int8 = output_int8
-        self.w = {}   # name -> IntgemmTensor
+        self.w = {}   # name -> IntgemmTensor or Packed8Weight
         self.p = {}   # name -> fp32 tensor
         for name, val in params.items():
-            if isinstance(val, ops.IntgemmTensor):
+            if isinstance(val, (ops.IntgemmTensor, packed8.Packed8Weight)):
                 self.w[name] = val
             else:
                 t = torch.as_tensor(np.ascontiguousarray(val), dtype=torch.float32).to(self.device)
-                if is_intgemm_param(name):
-                    self.w[name] = ops.prepareB(t, ws=self.ws)   # on-line conversion of a float model
+                if is_intgemm_param(name):     # on-line conversion of a float model
+                    self.w[name] = ops.prepareB(t, ws=self.ws) if scheme == "intgemm8" else packed8.prepareB(t)
                 else:
                     self.p[name] = t
         self.wemb = self.p["Wemb"]                                 # [V, d] fp32, for the lookup
         # Tied output layer: affine(x, Wemb, b, transB=true).  The reference leaves Wemb in fp32
         # (its name test skips it); the int8 mode quantises the [V,d] matrix, which already is the
-        # K-major Bt[N,K] layout.
-        self.wemb_q = ops.prepareB(self.wemb, w_is_nk=True, ws=self.ws) if output_int8 else None
+        # K-major Bt[N,K] layout (for packed8avx512: the conversion of Wemb^T, unless the caller supplied "Wemb_packed8").
+        if not output_int8:
+            self.wemb_q = None
+        elif scheme == "intgemm8":
+            self.wemb_q = ops.prepareB(self.wemb, w_is_nk=True, ws=self.ws)
+        else:
+            self.wemb_q = self.w.pop("Wemb_packed8", None) or packed8.prepareB(self.wemb.t().contiguous())
         self.d = cfg.dim_emb
         self.h = cfg.heads
         self.dh = cfg.dim_emb // cfg.heads
@@ -75,9 +87,17 @@ class NativeStepper:
         check(self.L.mi8d_create(ctypes.byref(self.cfg), self.arena.data_ptr(), nbytes, model.ws.ptr, model.ws.nbytes,
                                  ctypes.byref(handle)))
         self.h = handle
-        for name, w in model.w.items():
-            check(self.L.mi8d_set_weight(self.h, name.encode(), w.data.data_ptr(), w.cols, w.rows))
-        check(self.L.mi8d_set_weight(self.h, b"Wemb_intgemm8", model.wemb_q.data.data_ptr(), model.wemb_q.cols, model.wemb_q.rows))
+        if model.scheme == "packed8avx512":
+            def reg(name, w):
+                check(self.L.mi8d_set_packed8_weight(self.h, name.encode(), w.bt.data_ptr(), w.scale_b.data_ptr(), w.zp_b.data_ptr(),
+                                                     w.off_b.data_ptr(), w.K, w.N))
+            for name, w in model.w.items():
+                reg(name, w)
+            reg("Wemb_packed8", model.wemb_q)
+        else:
+            for name, w in model.w.items():
+                check(self.L.mi8d_set_weight(self.h, name.encode(), w.data.data_ptr(), w.cols, w.rows))
+            check(self.L.mi8d_set_weight(self.h, b"Wemb_intgemm8", model.wemb_q.data.data_ptr(), model.wemb_q.cols, model.wemb_q.rows))
         for name, p in model.p.items():
             check(self.L.mi8d_set_param(self.h, name.encode(), p.data_ptr()))
         self.pos = torch.from_numpy(sinusoidal_table(max_steps, cfg.dim_emb)).to(dev)

@@ -54,29 +54,49 @@ class OracleTransformer:
     """All float glue (embedding, LayerNorm, attention, SSRU cell, log-softmax/top-k) runs through the
     fixed-order C functions of oracle_i8.c; all affines through its int8 path."""
 
-    def __init__(self, cfg, params: dict, oracle: COracle | None = None, output_int8: bool = True, threads: int = 0):
+    def __init__(self, cfg, params: dict, oracle: COracle | None = None, output_int8: bool = True, threads: int = 0,
+                 scheme: str = "intgemm8", packed_items: dict | None = None):
+        """scheme "packed8avx512": every affine goes through the restatement of the reference's mjdgemm route
+        (oracle_packed8.c: per-row uint8 activations, per-column int8 weights) instead of the intgemm8 one; packed_items
+        optionally supplies ready items (name -> Packed8Item, "Wemb_packed8" for the tied output matrix) so that a test can
+        hand both sides the same bytes."""
         self.cfg = cfg
         self.o = oracle or COracle()
+        self.scheme = scheme
+        self.p8 = None
+        if scheme == "packed8avx512":
+            from .oracle import Packed8Oracle
+            self.p8 = Packed8Oracle()
         if threads:
             self.o.set_threads(threads)
         self.w, self.p = {}, {}
         for name, val in params.items():
             val = np.ascontiguousarray(val, dtype=np.float32)
             if _is_intgemm_param(name):
-                self.w[name] = self.o.prepare_b(val)          # (Bt int8 [N,K], quantMult)
+                if self.p8 is not None:
+                    self.w[name] = (packed_items or {}).get(name) or self.p8.prepare_b(val)
+                else:
+                    self.w[name] = self.o.prepare_b(val)          # (Bt int8 [N,K], quantMult)
             else:
                 self.p[name] = val
         self.output_int8 = output_int8
         self.wemb = self.p["Wemb"]
-        self.wemb_q = self.o.prepare_b(self.wemb, w_is_nk=True) if output_int8 else None
+        if not output_int8:
+            self.wemb_q = None
+        elif self.p8 is not None:
+            self.wemb_q = (packed_items or {}).get("Wemb_packed8") or self.p8.prepare_b(np.ascontiguousarray(self.wemb.T))
+        else:
+            self.wemb_q = self.o.prepare_b(self.wemb, w_is_nk=True)
         self.d, self.h = cfg.dim_emb, cfg.heads
         self.dh = self.d // self.h
         self.pos = _positions(0, 512, self.d)
         self.scale = float(np.sqrt(np.float32(self.d)))
 
     def affine(self, x, wname, bname=None, relu=False):
-        bt, qb = self.w[wname]
         bias = self.p[bname].reshape(-1) if bname else None
+        if self.p8 is not None:
+            return self.p8.affine(np.ascontiguousarray(x.reshape(-1, x.shape[-1]), dtype=np.float32), self.w[wname], bias, relu)
+        bt, qb = self.w[wname]
         return self.o.affine(x.reshape(-1, x.shape[-1]), bt, qb, bias, 1.0, relu)
 
     def add_ln(self, a, resid, prefix):
@@ -155,6 +175,8 @@ class OracleTransformer:
             x = self.ffn(x, f"decoder_l{i}_ffn")
         st["pos"] = t + 1
         b = self.p["decoder_ff_logit_out_b"].reshape(-1)
+        if self.output_int8 and self.p8 is not None:
+            return self.p8.affine(np.ascontiguousarray(x, dtype=np.float32), self.wemb_q, b)
         if self.output_int8:
             bt, qb = self.wemb_q
             return self.o.affine(x, bt, qb, b)

@@ -360,7 +360,13 @@ class Packed8Oracle:
         a = np.ascontiguousarray(a, np.float32)
         M, K = a.shape
         assert K == item.K
-        bt = self.unpack_bt(item)
+        bt = getattr(item, "_bt_cache", None)        # the row-major copy is made once per item
+        if bt is None:
+            bt = self.unpack_bt(item)
+            try:
+                item._bt_cache = bt
+            except AttributeError:
+                pass
         c = np.zeros((M, item.N), np.float32)
         acc = np.zeros((M, item.N), np.int32) if want_acc else None
         b = np.ascontiguousarray(bias, np.float32) if bias is not None else None
