@@ -89,6 +89,9 @@ def parse_args():
                     help="decode one mini-batch with the in-situ kernel timeline on and write its per-kernel summary to PATH")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="step-driver tuning switch (fuse_weights, quant_in_gemm, fused_output_max_rows, side_stream, attention_unroll)")
+    ap.add_argument("--legacy-sample", action="store_true",
+                    help="time what earlier versions of this benchmark timed (a corpus of (warmup + steps) mini-batches sorted longest first, "
+                         "warm-up on the longest, the rest timed), for comparisons with their numbers; no digest check")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline sample (for quick A/B runs)")
     ap.add_argument("--strong", action="store_true",
                     help="strong scaling: the whole fixed corpus, mini-batches taken from a shared counter by whichever rank is free")
@@ -146,8 +149,9 @@ def load_digests(name):
 
 
 # DRAM read + write bytes of ONE launch of the decode's dominant GEMM shape (dram__bytes_read.sum + dram__bytes_write.sum),
-# from the ncu captures summarised in profiles/decode_gemm_ncu_b200.md (key: M, N, K).
-NCU_DRAM_BYTES_PER_LAUNCH = {}
+# from the ncu captures summarised in profiles/decode_kernels_ncu_b200.md (key: M, N, K).  They are BELOW the algorithmic bytes:
+# the fp32 output of these launches is still in the 126 MB L2 when the kernel ends, and part of the operands never left it.
+NCU_DRAM_BYTES_PER_LAUNCH = {(512, 1024, 1024): 1.63e6, (512, 4096, 1024): 4.79e6, (512, 1024, 4096): 6.35e6, (512, 32000, 1024): 44.0e6}
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -284,13 +288,23 @@ def run_ours(args):
     from marian_dev_b200 import ops, parallel
 
     world, rank, local_rank, dev, cfg, wl, batches, stepper, search = _setup(args)
+    if args.legacy_sample:
+        from marian_dev_b200 import model as model_mod
+        per_rank = args.warmup + args.steps
+        corpus = model_mod.synthetic_corpus(per_rank * world * wl["mini_batch"], cfg.vocab, seed=1, **wl["lengths"])
+        batches = model_mod.make_batches(corpus, wl["mini_batch"])
     widths = [b[1].shape[1] for b in batches]
     order = batch_order(len(batches))
     need = world * args.steps
-    picked = [order[i % len(order)] for i in range(need)]
-    mine = deal_batches(picked, widths, rank, world)[:args.steps]
-    warm = [order[(need + i) % len(order)] for i in range(args.warmup)]          # other mini-batches than the timed ones
-    golden = load_digests(args.model) if not (args.mini_batch or args.beam) else {}
+    if args.legacy_sample:
+        own = parallel.shard_batches(list(range(len(batches))), rank, world, snake=True)
+        warm, mine, picked = own[:args.warmup], own[args.warmup:args.warmup + args.steps], list(range(len(batches)))
+        golden = {}
+    else:
+        picked = [order[i % len(order)] for i in range(need)]
+        mine = deal_batches(picked, widths, rank, world)[:args.steps]
+        warm = [order[(need + i) % len(order)] for i in range(args.warmup)]          # other mini-batches than the timed ones
+        golden = load_digests(args.model) if not (args.mini_batch or args.beam) else {}
     max_len = int(np.ceil(1.5 * max(widths))) + 2
 
     def barrier():
@@ -317,20 +331,21 @@ def run_ours(args):
     ops.reset_launch_count()
     stepper.search_stats(reset=True)
     tokens = 0
-    digests1 = []
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     collected = {}
+    results1 = []
     for sid, ids_t, mask_t in resident:
         res = search.search_device(ids_t, mask_t)
         collected.update({int(i): toks for i, (toks, _s) in zip(sid, res)})
         tokens += sum(len(t) for t, _ in res)
-        digests1.append(tokens_digest(sid, [t for t, _ in res]))
+        results1.append(res)
     gather_outputs(collected)
     e1.record()
     barrier()
+    digests1 = [tokens_digest(sid, [t for t, _ in res]) for (sid, _i, _m), res in zip(resident, results1)]    # (hashed outside the timed region)
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1)
     launches = ops.launch_count()
@@ -391,19 +406,20 @@ def run_ours(args):
     pinned = [(sid, torch.from_numpy(ids.astype(np.int64)).pin_memory(), torch.from_numpy(mask).pin_memory()) for sid, ids, mask in leg1]
     search.h2d_bytes = search.d2h_bytes = 0
     tokens2 = 0
-    digests2 = []
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
     collected = {}
+    results2 = []
     for sid, ids_p, mask_p in pinned:
         res = search.search(ids_p, mask_p)
         collected.update({int(i): toks for i, (toks, _s) in zip(sid, res)})
         tokens2 += sum(len(t) for t, _ in res)
-        digests2.append(tokens_digest(sid, [t for t, _ in res]))
+        results2.append(res)
     gather_outputs(collected)
     f1.record()
     barrier()
+    digests2 = [tokens_digest(sid, [t for t, _ in res]) for (sid, _i, _m), res in zip(pinned, results2)]
     ms2 = f0.elapsed_time(f1)
     if digests2 != digests1:
         raise RuntimeError(f"rank {rank}: the end-to-end leg decoded different tokens than the device-resident leg")
@@ -468,7 +484,7 @@ def run_ours(args):
                                  f"mean {round(sum(widths[b] for b in picked) / len(picked), 1)}; corpus mean {round(sum(widths) / len(widths), 1)}), "
                                  "warm-up on other mini-batches",
                        "tokens_counted": "best hypothesis per sentence, EOS included", "parallelism": f"replicas x{world}",
-                       "options": args.option,
+                       "options": args.option, "legacy_sample": bool(args.legacy_sample),
                        "l2": "not flushed: one decode step streams ~0.2 GB of int8 weights plus fp32 logits and history, more than the 126 MB L2"},
             "e2e": {"value": round(tokens2 / (ms2 / 1e3), 1), "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches), "gpu_launches_before_timed_region": int(launches_before), "clocks": clocks,
@@ -581,7 +597,7 @@ def run_trace(args):
         k, ex = key
         name = TRACE_KERNELS.get(k, str(k))
         if k in (1, 2, 18, 19):
-            name += f" N={ex & 0xfffff},K={(ex >> 20) & 0xfffff},M={'<=512' if (ex >> 40) <= 512 else '>512'}"
+            name += f" N={ex & 0xfffff},K={(ex >> 20) & 0xfffff}"
         a = agg.setdefault(name, {"launches": 0, "work_ns": 0, "gap_ns": 0, "pre_ns": 0, "inner": [0, 0, 0, 0], "inner_n": 0})
         a["launches"] += 1
         a["work_ns"] += t_end - t_wait
@@ -1157,6 +1173,8 @@ def run_affines(args):
 
 if __name__ == "__main__":
     a = parse_args()
+    if a.trace:      # the build of the library that carries the timeline stamps (the product library is built without them)
+        os.environ["MARIAN_I8_LIBRARY"] = os.path.join(ROOT, "marian-dev_b200", "libmarian_i8_trace.so")
     if a.write_digests:
         run_write_digests(a)
     elif a.trace:

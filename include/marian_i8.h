@@ -207,6 +207,7 @@ int mi8_multiply_plan(int M, int N, int K, int force_tile_m, int force_splits, i
  * the stream; each kernel waits for its predecessor before touching dependent data.  Process-wide switch. */
 void mi8_set_pdl(int enabled);
 
+
 #ifdef __cplusplus
 }
 #endif

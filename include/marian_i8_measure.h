@@ -53,14 +53,16 @@ void mi8_launch_count_reset(void);
 
 /* In-situ timeline of the kernels of this library.  Between mi8_trace_begin and mi8_trace_end one thread of block 0
  * of every kernel writes the GPU's global nanosecond timer into `device_buf` at three points: phase 0 at kernel entry,
- * phase 1 when its wait for the preceding kernel returns, phase 2 at the end of block 0.  Unlike events placed between
+ * phase 1 when its wait for the preceding kernel returns, phase 2 at the end of block 0 (phase 3: the end of the last block).  Unlike events placed between
  * launches this leaves programmatic dependent launch as it is, so the stamps show what each kernel costs inside a
  * running decoder step.  device_buf: caller-owned device memory of 2 + 2 * capacity 64-bit words; on return from
  * mi8_trace_end word 0 holds the number of stamps taken (those beyond `capacity` are dropped), followed by pairs
  * (time in ns, extra << 16 | kernel << 8 | phase) in arrival order.  kernel: 1 GEMM, 2 CTA-pair GEMM, 3 quantize_slot,
  * 4 quantize_dual, 5 add_layernorm, 6 attention1, 7 attention_enc, 8 lse_topk, 9 lse_merge, 10 nbest_merge, 11 embed,
  * 12 ancestors_update, 13 history_commit, 14 gather_rows, 15 ssru_cell, 16 absmax, 17 quantize, 18 output-layer GEMM,
- * 19 quantising GEMM; the GEMMs put N | K << 20 | M << 40 into `extra`.  Both calls synchronise the device. */
+ * 19 quantising GEMM; the GEMMs put N | K << 20 into `extra`.  Both calls synchronise the device.
+ * The stamps cost about 2 % of a decode even while no buffer is installed, so the product library is built without them
+ * (mi8_trace_begin then returns MI8_ERR_UNSUPPORTED); libmarian_i8_trace.so, built from the same sources, carries them. */
 int mi8_trace_begin(unsigned long long* device_buf, int capacity);
 int mi8_trace_end(void);
 

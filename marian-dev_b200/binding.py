@@ -11,7 +11,7 @@ import os
 import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmarian_i8.so")
+LIB_PATH = os.environ.get("MARIAN_I8_LIBRARY") or os.path.join(_HERE, "libmarian_i8.so")   # (the variable selects another build of the same ABI)
 
 MI8_F32, MI8_F16 = 0, 1
 

@@ -302,6 +302,9 @@ void mi8_test_wait_fault(int withhold_item, unsigned spin_limit) { test_wait_fau
 int mi8_trace_begin(unsigned long long* device_buf, int capacity) {
   if(device_buf == nullptr || capacity <= 0)
     return MI8_ERR_BAD_ARG;
+#ifdef MI8_NO_TRACE
+  return MI8_ERR_UNSUPPORTED;   // this build carries no timeline code (libmarian_i8_trace.so does)
+#endif
   const unsigned long long head[2] = {0ull, static_cast<unsigned long long>(capacity)};
   cudaError_t e = cudaDeviceSynchronize();
   if(e == cudaSuccess)

@@ -392,16 +392,27 @@ namespace {
 
 // aq (already quantised, multiplier behind the data) x weight -> c
 int gemm(mi8d_decoder* d, const int8_t* a, int M, const Aff& w, bool relu, float* c, cudaStream_t s, unsigned* absmax_out = nullptr,
-         int force_splits = 0) {
+         int force_splits = 0, int force_tile_m = 0) {
   const float* qa = reinterpret_cast<const float*>(a + static_cast<size_t>(M) * w.K);
-  return launch_gemm(a, w.bt, M, w.N, w.K, qa, w.qm, 1.0f, w.bias, relu ? 1 : 0, c, MI8_F32, nullptr, d->ws, d->ws_bytes, s, 0, force_splits,
-                     absmax_out);
+  return launch_gemm(a, w.bt, M, w.N, w.K, qa, w.qm, 1.0f, w.bias, relu ? 1 : 0, c, MI8_F32, nullptr, d->ws, d->ws_bytes, s, force_tile_m,
+                     force_splits, absmax_out);
+}
+
+// The narrowest tile (activation rows) that covers an M x N product with at most `budget` CTAs; 0 = leave it to the plan.
+// Two GEMMs that run side by side on two streams each take half of the SMs this way (a CTA of this kernel fills an SM).
+int tile_within(int M, int N, int budget) {
+  if(M <= 64)
+    return 0;
+  for(int tm : {32, 64, 128, 256})
+    if(((N + 127) / 128) * ((M + tm - 1) / tm) <= budget)
+      return tm;
+  return 0;
 }
 
 // the same activation against the matrices of a fused group, one launch; outs[i] receives [M, f.n]
 int gemm_fused(mi8d_decoder* d, const int8_t* a, const float* qa, int M, const Fused& f, float* const* outs, cudaStream_t s,
                int force_splits = 0, int a_rows_cap = 0, int a_row0 = 0, const unsigned* skip_a = nullptr,
-               const unsigned* skip_b = nullptr, int skip_rows_below = 0) {
+               const unsigned* skip_b = nullptr, int skip_rows_below = 0, int force_tile_m = 0) {
   GemmCall g;
   g.aq = a;
   g.bt = f.bt;
@@ -419,6 +430,7 @@ int gemm_fused(mi8d_decoder* d, const int8_t* a, const float* qa, int M, const F
   g.ws_bytes = d->ws_bytes;
   g.stream = s;
   g.force_splits = force_splits;
+  g.force_tile_m = force_tile_m;
   g.a_rows_cap = a_rows_cap;
   g.a_row0 = a_row0;
   g.skip_a = skip_a;
@@ -934,15 +946,20 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
       const bool fused = d->opt_fuse && w.self_kv.ready;
       float* kv_new[2] = {L.kslab + static_cast<size_t>(t) * slab_stride, L.vslab + static_cast<size_t>(t) * slab_stride};
       float* kv_all[2] = {L.kslab, L.vslab};
-      const bool side = t > 0 && d->overlap && d->opt_side_stream;
+      // The key/value projections do not depend on the query projection: they run on the internal stream beside it.  Both
+      // sides then use tiles wide enough to fit half of the SMs each (a CTA of the GEMM fills an SM), so they really run
+      // at the same time; no split-K on either side, the two streams must not share the workspace's counters.
+      const bool side = d->overlap && d->opt_side_stream;
       cudaStream_t so = side ? d->side : s;
+      const int half = sm_count() / 2;
+      const int tile_q = side ? tile_within(R, w.self_q.N, half) : 0;
+      const int tile_kv = side ? tile_within(R, 2 * w.self_k.N, half) : 0;
+      if(side) {
+        MI8D_CUDA(cudaEventRecord(d->ev_fork, s));
+        MI8D_CUDA(cudaStreamWaitEvent(so, d->ev_fork, 0));
+      }
       if(t > 0) {
-        // earlier slabs: recomputed only when the abs-max changed (all tiles skipped otherwise); no split-K, the two
-        // streams must not share the workspace's counters
-        if(side) {
-          MI8D_CUDA(cudaEventRecord(d->ev_fork, s));
-          MI8D_CUDA(cudaStreamWaitEvent(so, d->ev_fork, 0));
-        }
+        // earlier slabs: recomputed only when the abs-max changed (all tiles skipped otherwise)
         if(fused) {
           MI8D_TRY(gemm_fused(d, L.hq, hq_tail, t * SR, w.self_kv, kv_all, so, 1, cap_rows, 0, d->prev_bits + l, sh, t * SR));
         } else {
@@ -951,20 +968,20 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
           MI8D_TRY(launch_gemm(L.hq, w.self_v.bt, t * SR, w.self_v.N, w.self_v.K, hq_tail, w.self_v.qm, 1.0f, w.self_v.bias, 0, L.vslab, MI8_F32,
                                nullptr, d->ws, d->ws_bytes, so, 0, 1, nullptr, d->prev_bits + l, sh, t * SR));
         }
-        if(side)
-          MI8D_CUDA(cudaEventRecord(d->ev_join, so));
       }
-      MI8D_TRY(gemm(d, d->aq, R, w.self_q, false, d->qbuf, s, nullptr, side ? 1 : 0));
-      // newest slab: always projected, as a problem of its own (R live rows on narrow tiles)
+      // newest slab: always projected, as a problem of its own (R live rows)
       if(fused) {
-        MI8D_TRY(gemm_fused(d, L.hq, hq_tail, R, w.self_kv, kv_new, s, 1, cap_rows, t * SR));
+        MI8D_TRY(gemm_fused(d, L.hq, hq_tail, R, w.self_kv, kv_new, so, 1, cap_rows, t * SR, nullptr, nullptr, 0, tile_kv));
       } else {
         const int8_t* a_new = L.hq + static_cast<size_t>(t) * slab_stride;
         MI8D_TRY(launch_gemm(a_new, w.self_k.bt, R, w.self_k.N, w.self_k.K, hq_tail, w.self_k.qm, 1.0f, w.self_k.bias, 0, kv_new[0], MI8_F32,
-                             nullptr, d->ws, d->ws_bytes, s, 0, 1));
+                             nullptr, d->ws, d->ws_bytes, so, 0, 1));
         MI8D_TRY(launch_gemm(a_new, w.self_v.bt, R, w.self_v.N, w.self_v.K, hq_tail, w.self_v.qm, 1.0f, w.self_v.bias, 0, kv_new[1], MI8_F32,
-                             nullptr, d->ws, d->ws_bytes, s, 0, 1));
+                             nullptr, d->ws, d->ws_bytes, so, 0, 1));
       }
+      if(side)
+        MI8D_CUDA(cudaEventRecord(d->ev_join, so));
+      MI8D_TRY(gemm(d, d->aq, R, w.self_q, false, d->qbuf, s, nullptr, side ? 1 : 0, tile_q));
       if(side)
         MI8D_CUDA(cudaStreamWaitEvent(s, d->ev_join, 0));
       MI8D_TRY(launch_attention1(d->qbuf, L.kslab, L.vslab, nullptr, R, c.heads, dm / c.heads, steps, batch, 0, d->abuf, sa, s,

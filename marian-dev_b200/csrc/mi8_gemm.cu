@@ -296,11 +296,11 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   const int lane = threadIdx.x & 31;
 
   pdl_launch_dependents();  // the next kernel on the stream may begin its own set-up now
-  unsigned long long* tb = trace_open();
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   constexpr int kTraceId = kTopK > 0 ? kTrGemmLogits : (kQuantA ? kTrGemmQuantA : kTrGemm);
   const unsigned long long trace_extra = static_cast<unsigned long long>(p.N) | (static_cast<unsigned long long>(p.K) << 20) |
                                          (static_cast<unsigned long long>(p.M) << 40);
-  trace_stamp(tb, kTraceId, 0, trace_extra);
   if(threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_a);
@@ -418,8 +418,6 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->full[s], ph, abort_flag, p.spin_limit));
         if(!ok)
           break;
-        if(it == 0)
-          trace_stamp(trace_open_thread(32), kTraceId, 4, trace_extra);   // the first operands have landed
         tc_fence_after_sync();
         const uint32_t w_addr = smem_u32(tiles + s * T::kStageBytes);
         const uint32_t a_addr = w_addr + T::kWBytes;
@@ -457,7 +455,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     constexpr int kChunkStep = kChunks > 1 ? 2 : 1;
     const bool has_chunks = kChunks > 1 || group == 0;
     pdl_wait();  // the activation multiplier (or abs-max slot) is written by the previous kernel
-    trace_stamp(tb, kTraceId, 1, trace_extra);
+    trace_stamp_start(th, kTraceId, trace_extra);
     // kQuantA: the multiplier comes from the abs-max slot, which is read only after the first fp32 loads of the
     // activation have been issued (below), so the two round trips to L2 overlap instead of following one another.
     float qa = 1.0f;
@@ -549,8 +547,6 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       if(!ok)
         break;
       tc_fence_after_sync();
-      if(acc_it == 0)
-        trace_stamp(tb, kTraceId, 5, trace_extra);   // the first accumulator is complete
 
       const uint32_t t_addr = tmem_base + as * T::kAccStride + (static_cast<uint32_t>(quarter * 32) << 16);
       const int n = wi.n_tile * kTileN + row;
@@ -761,8 +757,6 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before_sync();
       mbar_arrive(&ctl->tmem_empty[as]);
-      if(acc_it == 0)
-        trace_stamp(tb, kTraceId, 6, trace_extra);   // its write-back is issued
       ++acc_it;
     }
     if(!ok) {
@@ -792,7 +786,7 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     tmem_dealloc(tmem_base, T::kTmemCols);
   }
   trace_stamp(tb, kTraceId, 2, trace_extra);
-  trace_last_block_end(kTraceId, trace_extra);
+  trace_stamp(th.last, kTraceId, 3, trace_extra);
 }
 
 // ------------------------------------------------------------------ CTA-pair variant (large M)
@@ -841,10 +835,10 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   const uint32_t peer_abort = mapa_shared(smem_u32(&ctl->abort), rank ^ 1u);
 
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   const unsigned long long trace_extra = static_cast<unsigned long long>(p.N) | (static_cast<unsigned long long>(p.K) << 20) |
                                          (static_cast<unsigned long long>(p.M) << 40);
-  trace_stamp(tb, kTrGemmPair, 0, trace_extra);
   if(threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_a);
@@ -1000,7 +994,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     const int epi_tid = threadIdx.x - 64;
     constexpr int kChunks = T::kTM / T::kChunk;
     pdl_wait();
-    trace_stamp(tb, kTrGemmPair, 1, trace_extra);
+    trace_stamp_start(th, kTrGemmPair, trace_extra);
     const float qa = kP8 ? 1.0f : *p.d_qa;
     float unquant = kP8 ? 1.0f : __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.seg_qb[0])), p.scale);
     uint32_t acc_it = 0;
@@ -1098,7 +1092,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
     tmem_dealloc_pair(tmem_base, T::kTmemCols);
   }
   trace_stamp(tb, kTrGemmPair, 2, trace_extra);
-  trace_last_block_end(kTrGemmPair, trace_extra);
+  trace_stamp(th.last, kTrGemmPair, 3, trace_extra);
 }
 
 // ------------------------------------------------------------------ host side
@@ -1163,7 +1157,7 @@ int get_kmajor_map(CUtensorMap* out, const int8_t* base, int rows, int K, int bo
   MapCache& mc = *t_map_cache;
   uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
   h ^= static_cast<uint64_t>(rows) * 0x9E3779B97F4A7C15ull;
-  h ^= (static_cast<uint64_t>(K) << 21) ^ (static_cast<uint64_t>(box_rows) << 45);
+  h ^= (static_cast<uint64_t>(K) << 21) ^ (static_cast<uint64_t>(static_cast<uint32_t>(box_rows)) << 40);
   h ^= h >> 29;
   int slot = static_cast<int>(h & (MapCache::kSlots - 1));
   for(int probe = 0; probe < 16; ++probe, slot = (slot + 1) & (MapCache::kSlots - 1)) {

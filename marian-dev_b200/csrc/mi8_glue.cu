@@ -45,10 +45,10 @@ __global__ void __launch_bounds__(kRowThreads)
 embed_kernel(const float* __restrict__ wemb, const int* __restrict__ words, const float* __restrict__ pos, int pos_mod, float scale,
              int dim, float* __restrict__ out, float* __restrict__ rowmax, unsigned* absmax_slot, unsigned* absmax_slot2) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrEmbed, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrEmbed, 1);
+  trace_stamp_start(th, kTrEmbed);
   __shared__ unsigned red[kRowThreads / 32];
   const int r = blockIdx.x;
   const float4* src = words ? reinterpret_cast<const float4*>(wemb + static_cast<size_t>(words[r]) * dim) : nullptr;
@@ -76,7 +76,7 @@ embed_kernel(const float* __restrict__ wemb, const int* __restrict__ words, cons
       atomicMax(absmax_slot2, m);
   }
   trace_stamp(tb, kTrEmbed, 2);
-  trace_last_block_end(kTrEmbed);
+  trace_stamp(th.last, kTrEmbed, 3);
 }
 
 // out = LayerNorm(a + resid) * gamma + beta, one block of 256 threads per row; biased variance
@@ -91,10 +91,10 @@ add_layernorm_kernel(const float* __restrict__ a, const float* __restrict__ resi
                      const float* __restrict__ beta, float eps, int dim, float* __restrict__ out, float* __restrict__ rowmax,
                      unsigned* absmax_slot, unsigned* absmax_slot2) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrAddLn, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrAddLn, 1);
+  trace_stamp_start(th, kTrAddLn);
   __shared__ float redf[kRowThreads / 32];
   __shared__ unsigned redu[kRowThreads / 32];
   const int r = blockIdx.x;
@@ -155,7 +155,7 @@ add_layernorm_kernel(const float* __restrict__ a, const float* __restrict__ resi
       atomicMax(absmax_slot2, m);
   }
   trace_stamp(tb, kTrAddLn, 2);
-  trace_last_block_end(kTrAddLn);
+  trace_stamp(th.last, kTrAddLn, 3);
 }
 
 __device__ __forceinline__ int quantize_one(float v, float qm) {
@@ -176,10 +176,10 @@ __global__ void __launch_bounds__(256)
 quantize_slot_kernel(const float* __restrict__ x, size_t n, const unsigned* __restrict__ absmax_slot, int8_t* __restrict__ q,
                      float* __restrict__ d_quant_mult, int* status) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrQuantSlot, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrQuantSlot, 1);
+  trace_stamp_start(th, kTrQuantSlot);
   const unsigned bits = *absmax_slot;
   const float qm = quant_mult_from_bits(bits);
   if(blockIdx.x == 0 && threadIdx.x == 0) {
@@ -201,7 +201,7 @@ quantize_slot_kernel(const float* __restrict__ x, size_t n, const unsigned* __re
   for(size_t i = n16 * 16 + tid; i < n; i += stride)
     q[i] = static_cast<int8_t>(quantize_one(x[i], qm));
   trace_stamp(tb, kTrQuantSlot, 2);
-  trace_last_block_end(kTrQuantSlot);
+  trace_stamp(th.last, kTrQuantSlot, 3);
 }
 
 // Two quantisations in one launch, for the start of a decoder self-attention block: blocks [0, blocks_x)
@@ -215,10 +215,10 @@ quantize_dual_kernel(const float* __restrict__ x, size_t n, const unsigned* __re
                      int rows_new, int dim, const unsigned* __restrict__ slot_h, const unsigned* __restrict__ prev_bits,
                      int8_t* __restrict__ hq, float* __restrict__ qm_h) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrQuantDual, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrQuantDual, 1);
+  trace_stamp_start(th, kTrQuantDual);
   if(static_cast<int>(blockIdx.x) < blocks_x) {
     const unsigned bits = *slot_x;
     const float qm = quant_mult_from_bits(bits);
@@ -257,7 +257,7 @@ quantize_dual_kernel(const float* __restrict__ x, size_t n, const unsigned* __re
     }
   }
   trace_stamp(tb, kTrQuantDual, 2);
-  trace_last_block_end(kTrQuantDual);
+  trace_stamp(th.last, kTrQuantDual, 3);
 }
 
 // ---- self-attention history ------------------------------------------------------------------
@@ -281,10 +281,10 @@ __global__ void __launch_bounds__(256)
 ancestors_update_kernel(const int* __restrict__ anc_old, int* __restrict__ anc_new, const int* __restrict__ hyp,
                         int t, int rows, int stride, const HistMaxArgs hist) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrAncestors, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrAncestors, 1);
+  trace_stamp_start(th, kTrAncestors);
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   const bool in = i < (t + 1) * rows;
   int tp = 0, src = 0;
@@ -301,7 +301,7 @@ ancestors_update_kernel(const int* __restrict__ anc_old, int* __restrict__ anc_n
       atomicMax(hist.slot[l], m);
   }
   trace_stamp(tb, kTrAncestors, 2);
-  trace_last_block_end(kTrAncestors);
+  trace_stamp(th.last, kTrAncestors, 3);
 }
 
 // prev_bits[l] = slots[first + l * stride]: remembers, per layer, the abs-max the stored keys/values belong to.
@@ -309,10 +309,10 @@ ancestors_update_kernel(const int* __restrict__ anc_old, int* __restrict__ anc_n
 __global__ void history_commit_kernel(unsigned* __restrict__ prev_bits, const unsigned* __restrict__ slots, int first, int stride, int layers,
                                       unsigned* __restrict__ stats) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrCommit, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrCommit, 1);
+  trace_stamp_start(th, kTrCommit);
   const int l = threadIdx.x;
   if(l < layers) {
     const unsigned now = slots[first + l * stride];
@@ -324,7 +324,7 @@ __global__ void history_commit_kernel(unsigned* __restrict__ prev_bits, const un
     prev_bits[l] = now;
   }
   trace_stamp(tb, kTrCommit, 2);
-  trace_last_block_end(kTrCommit);
+  trace_stamp(th.last, kTrCommit, 3);
 }
 
 // ---- single-query attention --------------------------------------------------------------------
@@ -349,10 +349,10 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                   const float* __restrict__ log_mask, int heads, int len, int rows, int batch, int mode, float scale,
                   float* __restrict__ out, unsigned* absmax_slot, const int* __restrict__ anc, int anc_stride, int kv_rows) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrAttention1, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrAttention1, 1);
+  trace_stamp_start(th, kTrAttention1);
   extern __shared__ float sc_smem[];  // [heads][len] scores, then probabilities
   constexpr int G = DH / 4;
   const int r = blockIdx.x;
@@ -460,7 +460,7 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
       atomicMax(absmax_slot, m_abs);
   }
   trace_stamp(tb, kTrAttention1, 2);
-  trace_last_block_end(kTrAttention1);
+  trace_stamp(th.last, kTrAttention1, 3);
 }
 
 // Encoder self-attention (mode 2) with the keys and values of one (sentence, head) staged in shared memory: block
@@ -486,10 +486,10 @@ attention_enc_kernel(const float* __restrict__ q, const float* __restrict__ k, c
                      const float* __restrict__ log_mask, int heads, int len, float scale, float* __restrict__ out,
                      unsigned* absmax_slot) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrAttentionEnc, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrAttentionEnc, 1);
+  trace_stamp_start(th, kTrAttentionEnc);
   extern __shared__ float enc_smem[];
   constexpr int G = DH / 4;
   const int b = blockIdx.x, h = blockIdx.y;
@@ -579,7 +579,7 @@ attention_enc_kernel(const float* __restrict__ q, const float* __restrict__ k, c
       atomicMax(absmax_slot, m_abs);
   }
   trace_stamp(tb, kTrAttentionEnc, 2);
-  trace_last_block_end(kTrAttentionEnc);
+  trace_stamp(th.last, kTrAttentionEnc, 3);
 }
 
 // ---- output layer: log-softmax + per-row top-k --------------------------------------------------
@@ -645,10 +645,10 @@ __global__ void __launch_bounds__(256)
 lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ prev_scores, float* __restrict__ cand_score,
                 int* __restrict__ cand_word) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrLseTopk, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrLseTopk, 1);
+  trace_stamp_start(th, kTrLseTopk);
   extern __shared__ float lse_blocks[];   // [nb] block maxima, [nb] block sums
   __shared__ float s_v[256 * K];
   __shared__ int s_i[256 * K];
@@ -755,7 +755,7 @@ lse_topk_kernel(const float* __restrict__ logits, int vocab, const float* __rest
     cand_word[r * K + threadIdx.x] = s_i[threadIdx.x];
   }
   trace_stamp(tb, kTrLseTopk, 2);
-  trace_last_block_end(kTrLseTopk);
+  trace_stamp(th.last, kTrLseTopk, 3);
 }
 
 // Second half of the fused output layer: the GEMM's write-back left, per (row, block of 128 vocabulary entries),
@@ -768,10 +768,10 @@ lse_merge_kernel(const float* __restrict__ blk_max, const float* __restrict__ bl
                  const int* __restrict__ blk_topi, int nb, int k, const float* __restrict__ prev_scores, float* __restrict__ cand_score,
                  int* __restrict__ cand_word) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrLseMerge, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrLseMerge, 1);
+  trace_stamp_start(th, kTrLseMerge);
   extern __shared__ float lse_blocks[];
   __shared__ float s_v[256 * KT];
   __shared__ int s_i[256 * KT];
@@ -807,7 +807,7 @@ lse_merge_kernel(const float* __restrict__ blk_max, const float* __restrict__ bl
     cand_word[r * k + threadIdx.x] = s_i[threadIdx.x];
   }
   trace_stamp(tb, kTrLseMerge, 2);
-  trace_last_block_end(kTrLseMerge);
+  trace_stamp(th.last, kTrLseMerge, 3);
 }
 
 // Per sentence b: merge the beam x K row candidates (rows beam-major: row = j * batch + b) into the
@@ -817,14 +817,14 @@ template <int K>
 __global__ void nbest_merge_kernel(const float* __restrict__ cand_score, const int* __restrict__ cand_word, int beam, int batch,
                                    int vocab, float* __restrict__ out_score, int* __restrict__ out_beam, int* __restrict__ out_word) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrNbest, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrNbest, 1);
+  trace_stamp_start(th, kTrNbest);
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if(b >= batch) {
     trace_stamp(tb, kTrNbest, 2);
-    trace_last_block_end(kTrNbest);
+    trace_stamp(th.last, kTrNbest, 3);
     return;
   }
   TopK t;
@@ -850,16 +850,16 @@ __global__ void nbest_merge_kernel(const float* __restrict__ cand_score, const i
     out_word[b * K + n] = valid ? t.i[n] % vocab : 0;
   }
   trace_stamp(tb, kTrNbest, 2);
-  trace_last_block_end(kTrNbest);
+  trace_stamp(th.last, kTrNbest, 3);
 }
 
 // rows gather: out[i,:] = in[idx[i],:]  (16-byte copies when the row length allows it)
 __global__ void gather_rows_kernel(const float* __restrict__ in, const int* __restrict__ idx, int dim, float* __restrict__ out) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrGather, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrGather, 1);
+  trace_stamp_start(th, kTrGather);
   const int r = blockIdx.x;
   const float* src = in + static_cast<size_t>(idx[r]) * dim;
   float* dst = out + static_cast<size_t>(r) * dim;
@@ -873,7 +873,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const int* __re
       dst[i] = __ldg(src + i);
   }
   trace_stamp(tb, kTrGather, 2);
-  trace_last_block_end(kTrGather);
+  trace_stamp(th.last, kTrGather, 3);
 }
 
 // SSRU cell (src/rnn/cells.h:1052-1066): c' = c[hyp] * sigmoid(f) + x * (1 - sigmoid(f)); h = relu(c').
@@ -881,10 +881,10 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const int* __re
 __global__ void ssru_cell_kernel(const float* __restrict__ cell_old, const int* __restrict__ hyp, const float* __restrict__ xw,
                                  const float* __restrict__ f, int dim, float* __restrict__ cell_new, float* __restrict__ h_out) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrSsru, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrSsru, 1);
+  trace_stamp_start(th, kTrSsru);
   const int r = blockIdx.x;
   const float* c = cell_old + static_cast<size_t>(hyp ? hyp[r] : r) * dim;
   for(int i = threadIdx.x; i < dim; i += blockDim.x) {
@@ -897,7 +897,7 @@ __global__ void ssru_cell_kernel(const float* __restrict__ cell_old, const int* 
     h_out[o] = cn > 0.f ? cn : 0.f;
   }
   trace_stamp(tb, kTrSsru, 2);
-  trace_last_block_end(kTrSsru);
+  trace_stamp(th.last, kTrSsru, 3);
 }
 
 int g_attention_block_heads = 8;   // heads one block of attention1_kernel serves (0 = all heads of the row)

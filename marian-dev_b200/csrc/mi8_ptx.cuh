@@ -43,16 +43,36 @@ enum TraceKernel : int {
   kTrGemm = 1, kTrGemmPair, kTrQuantSlot, kTrQuantDual, kTrAddLn, kTrAttention1, kTrAttentionEnc, kTrLseTopk, kTrLseMerge,
   kTrNbest, kTrEmbed, kTrAncestors, kTrCommit, kTrGather, kTrSsru, kTrAbsmax, kTrQuantize, kTrGemmLogits, kTrGemmQuantA
 };
-__device__ __forceinline__ unsigned long long* trace_open() {
-  return (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == blockDim.x - 1) ? s_trace_buf : nullptr;
+// Every kernel reads the pointer ONCE, at its entry (before its wait for the preceding kernel, so the load overlaps that
+// kernel's tail), in the two threads that stamp: the last thread of block 0 and the last thread of the last block.  All other
+// threads get null.  The stamps sit outside every hot loop (a store the compiler cannot see through would hold it back there).  Nothing else of the timeline runs when it is off.
+struct TraceHandles {
+  unsigned long long* first;     // block 0: phases 0, 1, 2
+  unsigned long long* last;      // last block of the grid: phase 3
+  unsigned long long t_entry;    // the timer at kernel entry (phase 0 is written together with phase 1, see trace_stamp_start)
+};
+__device__ __forceinline__ TraceHandles trace_open_all() {
+  TraceHandles h;
+  h.first = nullptr;
+  h.last = nullptr;
+  h.t_entry = 0ull;
+#ifdef MI8_NO_TRACE
+  return h;
+#endif
+  if(threadIdx.x == blockDim.x - 1) {
+    const bool b0 = blockIdx.x == 0 && blockIdx.y == 0;
+    const bool bl = blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1 && (gridDim.x > 1 || gridDim.y > 1);
+    if(b0 || bl) {
+      // The load is only ISSUED here; nothing may depend on it before the kernel's wait for its predecessor, or the
+      // thread (and, through the next block-wide barrier, its whole block) would sit out an L2 round trip at start-up.
+      unsigned long long* t = s_trace_buf;
+      h.first = b0 ? t : nullptr;
+      h.last = bl ? t : nullptr;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(h.t_entry));
+    }
+  }
+  return h;
 }
-// The same for another thread of block 0 (a kernel whose roles live in different warps stamps from several).
-__device__ __forceinline__ unsigned long long* trace_open_thread(unsigned thread) {
-  return (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == thread) ? s_trace_buf : nullptr;
-}
-// ... and for the last block of the grid, whose end (phase 3) bounds the kernel's duration from the other side:
-// blocks are dispatched in index order, so it is among the last to finish.
-__device__ __forceinline__ void trace_last_block_end(int kernel, unsigned long long extra = 0ull);
 __device__ __forceinline__ void trace_stamp(unsigned long long* tb, int kernel, int phase, unsigned long long extra = 0ull) {
   if(tb != nullptr) {
     unsigned long long t;
@@ -64,9 +84,17 @@ __device__ __forceinline__ void trace_stamp(unsigned long long* tb, int kernel, 
     }
   }
 }
-__device__ __forceinline__ void trace_last_block_end(int kernel, unsigned long long extra) {
-  if(blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1 && threadIdx.x == blockDim.x - 1 && (gridDim.x > 1 || gridDim.y > 1))
-    trace_stamp(s_trace_buf, kernel, 3, extra);
+// Phases 0 (entry, with the time taken then) and 1 (now: the wait for the preceding kernel has returned), written together.
+__device__ __forceinline__ void trace_stamp_start(const TraceHandles& h, int kernel, unsigned long long extra = 0ull) {
+  unsigned long long* tb = h.first;
+  if(tb != nullptr) {
+    const unsigned long long idx = atomicAdd(tb, 1ull);
+    if(idx < tb[1]) {
+      tb[2 + 2 * idx] = h.t_entry;
+      tb[3 + 2 * idx] = (extra << 16) | (static_cast<unsigned long long>(kernel) << 8);
+    }
+    trace_stamp(tb, kernel, 1, extra);
+  }
 }
 #define MI8_DEFINE_TRACE_SETTER(name)                                                         \
   int name(unsigned long long* buf) {                                                         \

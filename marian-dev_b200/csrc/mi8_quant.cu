@@ -42,10 +42,10 @@ __global__ void __launch_bounds__(kBlock)
 mi8_absmax_kernel(const float* __restrict__ x, size_t n, unsigned* partials, unsigned* counter, float* d_absmax,
                   float* d_quant_mult, int* status) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrAbsmax, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrAbsmax, 1);
+  trace_stamp_start(th, kTrAbsmax);
   __shared__ unsigned red[kBlock / 32];
   __shared__ int is_last;
   unsigned m = 0u;
@@ -75,7 +75,7 @@ mi8_absmax_kernel(const float* __restrict__ x, size_t n, unsigned* partials, uns
   __syncthreads();
   if(!is_last) {
     trace_stamp(tb, kTrAbsmax, 2);
-    trace_last_block_end(kTrAbsmax);
+    trace_stamp(th.last, kTrAbsmax, 3);
     return;
   }
   __threadfence();
@@ -95,7 +95,7 @@ mi8_absmax_kernel(const float* __restrict__ x, size_t n, unsigned* partials, uns
       *d_quant_mult = (m == 0u) ? 1.0f : __fdiv_rn(127.0f, mx);
   }
   trace_stamp(tb, kTrAbsmax, 2);
-  trace_last_block_end(kTrAbsmax);
+  trace_stamp(th.last, kTrAbsmax, 3);
 }
 
 __device__ __forceinline__ int quantize_one(float v, float qm) {
@@ -112,10 +112,10 @@ __device__ __forceinline__ unsigned pack4(const float4& v, float qm) {
 __global__ void __launch_bounds__(kBlock)
 mi8_quantize_kernel(const float* __restrict__ x, size_t n, const float* __restrict__ d_quant_mult, int8_t* __restrict__ q) {
   pdl_launch_dependents();
-  unsigned long long* tb = trace_open();
-  trace_stamp(tb, kTrQuantize, 0);
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
   pdl_wait();
-  trace_stamp(tb, kTrQuantize, 1);
+  trace_stamp_start(th, kTrQuantize);
   const float qm = *d_quant_mult;
   const size_t n16 = n / 16;
   const float4* x4 = reinterpret_cast<const float4*>(x);
@@ -137,7 +137,7 @@ mi8_quantize_kernel(const float* __restrict__ x, size_t n, const float* __restri
   for(size_t i = n16 * 16 + tid; i < n; i += stride)
     q[i] = static_cast<int8_t>(quantize_one(x[i], qm));
   trace_stamp(tb, kTrQuantize, 2);
-  trace_last_block_end(kTrQuantize);
+  trace_stamp(th.last, kTrQuantize, 3);
 }
 
 // W fp32 [K,N] row-major -> Bt int8 [N,K] row-major.  A block moves a 32(k) x 32(n) tile through
