@@ -364,9 +364,8 @@ mi8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         ok = __all_sync(0xffffffffu, ok);
         if(!ok)
           break;
-        if(static_cast<int>(it) == p.withhold_item)
-          continue;   // test hook: this item's operands never arrive, so the roles that wait for them run out of patience
-        if(elect_one()) {
+        // (test hook: a withheld item's operands never arrive, so the roles that wait for them run out of patience)
+        if(elect_one() && static_cast<int>(it) != p.withhold_item) {
           uint8_t* st = tiles + s * T::kStageBytes;
           if(!pre) {
             mbar_arrive_expect_tx(&ctl->full[s], kQuantA ? T::kWBytes : T::kStageBytes);
@@ -904,9 +903,7 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
         ok = __all_sync(0xffffffffu, ok);
         if(!ok)
           break;
-        if(static_cast<int>(it) == p.withhold_item)
-          continue;   // test hook (both CTAs of the pair leave the item out)
-        if(elect_one()) {
+        if(elect_one() && static_cast<int>(it) != p.withhold_item) {   // (test hook: both CTAs of the pair leave a withheld item out)
           uint8_t* st = tiles + s * T::kStageBytes;
           if(!pre) {
             if(leader)
