@@ -537,7 +537,7 @@ TRACE_KERNELS = {1: "mi8_gemm_kernel", 2: "mi8_gemm_pair_kernel", 3: "quantize_s
                  6: "attention1_kernel", 7: "attention_enc_kernel", 8: "lse_topk_kernel", 9: "lse_merge_kernel", 10: "nbest_merge_kernel",
                  11: "embed_kernel", 12: "ancestors_update_kernel", 13: "history_commit_kernel", 14: "gather_rows_kernel", 15: "ssru_cell_kernel",
                  16: "mi8_absmax_kernel", 17: "mi8_quantize_kernel", 18: "mi8_gemm_kernel (output layer, reducing write-back)",
-                 19: "mi8_gemm_kernel (quantising its activation)"}
+                 19: "mi8_gemm_kernel (quantising its activation)", 20: "mi8_gemm_cq_kernel"}
 
 
 def run_trace(args):
@@ -596,7 +596,7 @@ def run_trace(args):
     for key, t_in, t_wait, t_end, inner in launches:
         k, ex = key
         name = TRACE_KERNELS.get(k, str(k))
-        if k in (1, 2, 18, 19):
+        if k in (1, 2, 18, 19, 20):
             name += f" N={ex & 0xfffff},K={(ex >> 20) & 0xfffff}"
         a = agg.setdefault(name, {"launches": 0, "work_ns": 0, "gap_ns": 0, "pre_ns": 0, "inner": [0, 0, 0, 0], "inner_n": 0})
         a["launches"] += 1
@@ -657,6 +657,7 @@ def run_strong(args):
     pinned = [(sid, torch.from_numpy(ids.astype(np.int64)).pin_memory(), torch.from_numpy(mask).pin_memory()) for sid, ids, mask in batches]
     torch.cuda.synchronize()
     if world > 1:
+        parallel.gather_output_matrices({0: [1, 2, 3]}, max_len=max_len, device=dev)     # the collective's own set-up stays out of the timed region
         dist.barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -677,10 +678,11 @@ def run_strong(args):
         want = golden.get(str(b))
         bad += int(want is not None and want != tokens_digest(sid, [t for t, _ in res]))
     e1.record()
-    merged = parallel.gather_outputs(collected, max_len=max_len, device=dev)
+    mats = parallel.gather_output_matrices(collected, max_len=max_len, device=dev)   # every rank's tokens are in this rank's host memory
     e2.record()
     torch.cuda.synchronize()
     clocks = sampler.stop()
+    merged = parallel.merge_output_matrices(mats)                                     # (turning them into Python lists is not timed)
     busy, total = e0.elapsed_time(e1), e0.elapsed_time(e2)
     if bad:
         raise RuntimeError(f"rank {rank}: {bad} mini-batches decoded to tokens that differ from tests/golden/decode_digests.json")
@@ -818,7 +820,8 @@ def cpu_decode_sample(args, cfg_name):
         for toks, _s in beam_search(net, ids, mask, beam=wl["beam"], max_length_factor=1.5, normalize=1.0):
             tokens += len(toks)
     dt = time.time() - t0
-    return tokens / dt, cores, f"{n} sentences of median length from one mini-batch, beam {wl['beam']}, {dt:.1f} s of CPU work"
+    return tokens / dt, cores, (f"{n} sentences of median length from one mini-batch decoded as one batch of {n} (the GPU arm decodes {wl['mini_batch']} at a time: "
+                                f"context, not a like-for-like comparison), beam {wl['beam']}, {dt:.1f} s of CPU work")
 
 
 def cpu_baseline(args, cfg_name):
@@ -923,20 +926,27 @@ def time_affine_sharded(m, k, n, rank, world, iters=40):
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(iters):
-        if ml > 0:
-            parallel.sharded_affine(xs[i % copies], ws[i % copies], bias, 1.0, True)
-        else:                                                   # fewer rows than ranks: still take part in the exchange
-            parallel.global_abs_max(torch.zeros(1, device=dev))
-    e1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) * 1000.0 / iters], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    us = float(t[0])
+    def timed(exchange):
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            if ml > 0:
+                parallel.sharded_affine(xs[i % copies], ws[i % copies], bias, 1.0, True, exchange=exchange)
+            elif exchange:                                      # fewer rows than ranks: still take part in the exchange
+                parallel.global_abs_max(torch.zeros(1, device=dev))
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1000.0 / iters], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+    us = timed(True)
+    us_local = timed(False)       # the same launches without the all-reduce (per-shard multipliers): what the exchange costs
     by = 4 * m * k + k * n + 4 * n + 4 * m * n + 8
     return {"M": m, "K": k, "N": n, "us_per_affine": round(us, 2), "GBps": round(by / us / 1e3, 1), "TOPS": round(2.0 * m * n * k / us / 1e6, 2),
+            "us_without_exchange": round(us_local, 2), "exchange_share": round(max(0.0, 1.0 - us_local / us), 3),
             "algorithmic_bytes": by, "n_gpus": world, "rows_per_rank": (m + world - 1) // world, "operand_sets": copies}
 
 
@@ -1161,7 +1171,7 @@ def run_affines(args):
         if world > 1:
             r = time_affine_sharded(m, k, n, rank, world)
             r.update({"metric": "int8_affine_rows_sharded",
-                      "timing": "40 eager affines per rank (abs-max, MAX all-reduce of one float, quantise, GEMM), CUDA events, max over ranks"})
+                      "timing": "40 eager affines per rank (abs-max, MAX all-reduce of one float, quantise, GEMM), CUDA events, max over ranks; us_without_exchange = the same loop with the all-reduce left out"})
         else:
             r = time_affine(m, k, n)
             r.update({"metric": "int8_affine", "timing": "CUDA-graph replay of 40 affines, CUDA events, operand sets rotated through > L2"})

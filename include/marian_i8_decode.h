@@ -109,6 +109,26 @@ int mi8g_embed(const float* wemb, const int* words, const float* pos, int pos_mo
  * "dan" post-processing (src/models/transformer.h:189-214, src/layers/generic.h:248-253). */
 int mi8g_add_layernorm(const float* a, const float* resid, const float* gamma, const float* beta, float eps, int rows,
                        int dim, float* out, float* rowmax, unsigned* absmax_slot, void* stream);
+/* One launch for "Int8::PrepareA + multiply + write-back" on decode shapes (the two lambda nodes of
+ * src/tensors/cpu/intgemm_interface.h:17-32,46-99 together): `a` is the fp32 activation [M,K], `absmax_slot` the
+ * device word holding the bit pattern of max|a| (as for mi8_multiply_f32_slot).  The CTAs of a thread-block cluster
+ * work on neighbouring weight tiles of the same activation rows; each quantises a share of the activation tile and
+ * stores it into the shared memory of all of them, so the fp32 values are read once per cluster.  c [M,N] fp32;
+ * absmax_out (optional) receives max|c|.  K a multiple of 128 up to 4096, N a multiple of 128 (MI8_ERR_UNSUPPORTED
+ * otherwise).  tile_rows (0, 32, 64, 128) and cluster (0, 1, 2, 4, 8) force the plan; 0 = chosen.  Bit-identical to
+ * mi8g_quantize_slot + mi8_multiply_i8. */
+int mi8g_affine_slot(const float* a, const unsigned* absmax_slot, const int8_t* bt, const float* d_qb, int M, int N, int K,
+                     float scale, const float* bias, int relu, float* c, unsigned* absmax_out, int tile_rows, int cluster,
+                     void* stream);
+/* The same followed, in the same launch, by the transformer's "dan" post-processing of the result
+ * (src/models/transformer.h:189-214): out = LayerNorm(affine(a) + resid) * gamma + beta, with the row maxima
+ * (rowmax, optional) and max|out| (out_slot, out_slot2, optional) that mi8g_add_layernorm produces.  The cluster
+ * spans the N / 128 <= 8 weight tiles of a row; the CTAs exchange per-row partial sums through distributed shared
+ * memory.  Bit-identical to mi8g_affine_slot + mi8g_add_layernorm. */
+int mi8g_affine_slot_add_layernorm(const float* a, const unsigned* absmax_slot, const int8_t* bt, const float* d_qb, int M,
+                                   int N, int K, float scale, const float* bias, const float* resid, const float* gamma,
+                                   const float* beta, float eps, float* out, float* rowmax, unsigned* out_slot,
+                                   unsigned* out_slot2, void* stream);
 /* Int8::PrepareA with the multiplier 127/max taken from an abs-max slot; writes the multiplier to d_quant_mult. */
 int mi8g_quantize_slot(const float* x, size_t n, const unsigned* absmax_slot, int8_t* q, float* d_quant_mult, void* stream);
 /* Single-query attention softmax(q.k/sqrt(dh) + mask).v (src/models/transformer.h:240-277); mode 0: decoder
@@ -151,14 +171,28 @@ int mi8d_history_reuse(mi8d_decoder* d, unsigned out[2], int reset);
  *   MI8D_OPT_SIDE_STREAM (default 1): the re-projection of the earlier history slabs runs on an internal stream;
  *   MI8D_OPT_ATTENTION_UNROLL (8 or 16, default 8; process-wide): key/value rows a thread keeps in flight;
  *   MI8D_OPT_ATTENTION_BLOCK_HEADS (default 8, 0 = all; process-wide): heads one block of the decoder attention serves;
- *     a divisor of the head count splits every query row over several smaller blocks. */
+ *     a divisor of the head count splits every query row over several smaller blocks;
+ *   MI8D_OPT_CLUSTER_AFFINE (default 0): affines whose activation comes with an abs-max slot run as ONE launch of the
+ *     cluster GEMM (mi8g_affine_slot) instead of a quantisation launch and a GEMM launch.  Off by default: 74 to 98
+ *     instead of 122 launches per step of the transformer-big decoder, but 5 to 20 % fewer tokens per second (the
+ *     stores into the other CTAs' shared memory and the placement of whole clusters cost more than the launches saved);
+ *   MI8D_OPT_FUSED_LAYERNORM (default 1; has an effect only with the above): the last affine of a sub-layer also applies the residual add and
+ *     the LayerNorm that follow it (mi8g_affine_slot_add_layernorm) when the model width is at most 1024;
+ *   MI8D_OPT_CLUSTER_MAX_ROWS (default 1024): activations with more rows than this take the two-launch route;
+ *   MI8D_OPT_CLUSTER_SIZE (0 = chosen, 1, 2, 4, 8): CTAs per cluster of the plain cluster affine;
+ *   MI8D_OPT_CLUSTER_MAX_K (default 2048): affines with a longer inner dimension take the two-launch route. */
 enum mi8d_option {
   MI8D_OPT_FUSE_WEIGHTS = 1,
   MI8D_OPT_QUANT_IN_GEMM = 2,
   MI8D_OPT_FUSED_OUTPUT_MAX_ROWS = 3,
   MI8D_OPT_SIDE_STREAM = 4,
   MI8D_OPT_ATTENTION_UNROLL = 5,
-  MI8D_OPT_ATTENTION_BLOCK_HEADS = 6
+  MI8D_OPT_ATTENTION_BLOCK_HEADS = 6,
+  MI8D_OPT_CLUSTER_AFFINE = 7,
+  MI8D_OPT_FUSED_LAYERNORM = 8,
+  MI8D_OPT_CLUSTER_MAX_ROWS = 9,
+  MI8D_OPT_CLUSTER_SIZE = 10,
+  MI8D_OPT_CLUSTER_MAX_K = 11
 };
 int mi8d_set_option(mi8d_decoder* d, int option, int value);   /* d may be NULL for the process-wide switches */
 

@@ -36,7 +36,8 @@ class Mi8dConfig(ctypes.Structure):
 DECODE_EXPORTS = ["mi8d_arena_bytes", "mi8d_create", "mi8d_destroy", "mi8d_set_weight", "mi8d_set_param", "mi8d_set_positions",
                   "mi8d_start", "mi8d_encode", "mi8d_step", "mi8d_last_logits", "mi8d_history_reuse",
                   "mi8g_embed", "mi8g_add_layernorm", "mi8g_quantize_slot", "mi8g_attention1", "mi8g_lse_topk", "mi8g_nbest_merge",
-                  "mi8g_output_scratch_bytes", "mi8g_output_topk", "mi8d_keep_logits", "mi8d_search", "mi8d_set_option", "mi8d_set_packed8_weight"]
+                  "mi8g_output_scratch_bytes", "mi8g_output_topk", "mi8d_keep_logits", "mi8d_search", "mi8d_set_option", "mi8d_set_packed8_weight",
+                  "mi8g_affine_slot", "mi8g_affine_slot_add_layernorm"]
 
 # Every symbol include/marian_packed8.h declares.
 PACKED8_EXPORTS = ["mi8p_packed_bytes", "mi8p_prepare_b_f32", "mi8p_unpack_b", "mi8p_quantize_rows", "mi8p_multiply", "mi8p_scratch_bytes",
@@ -187,7 +188,10 @@ def lib() -> ctypes.CDLL:
     L.mi8g_attention1.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp, vp, vp]
     L.mi8g_lse_topk.argtypes = [vp, ci, ci, ci, vp, vp, vp, vp]
     L.mi8g_nbest_merge.argtypes = [vp, vp, ci, ci, ci, ci, vp, vp, vp, vp]
-    for name in ("mi8g_embed", "mi8g_add_layernorm", "mi8g_quantize_slot", "mi8g_attention1", "mi8g_lse_topk", "mi8g_nbest_merge"):
+    L.mi8g_affine_slot.argtypes = [vp, vp, vp, vp, ci, ci, ci, cf, vp, ci, vp, vp, ci, ci, vp]
+    L.mi8g_affine_slot_add_layernorm.argtypes = [vp, vp, vp, vp, ci, ci, ci, cf, vp, vp, vp, vp, cf, vp, vp, vp, vp, vp]
+    for name in ("mi8g_embed", "mi8g_add_layernorm", "mi8g_quantize_slot", "mi8g_attention1", "mi8g_lse_topk", "mi8g_nbest_merge",
+                 "mi8g_affine_slot", "mi8g_affine_slot_add_layernorm"):
         getattr(L, name).restype = ci
     for name in ("mi8d_create", "mi8d_set_weight", "mi8d_set_param", "mi8d_set_positions", "mi8d_start", "mi8d_step"):
         getattr(L, name).restype = ci

@@ -160,6 +160,7 @@ struct mi8d_decoder {
   bool overlap = false;
   // tuning switches (mi8d_set_option)
   int opt_fuse = 1, opt_quant_in_gemm = 0, opt_fused_out_rows = 480, opt_side_stream = 1;
+  int opt_cluster = 0, opt_fused_ln = 1, opt_cluster_max_rows = 1024, opt_cluster_size = 0, opt_cluster_max_k = 2048;
   // host-side timing of mi8d_search
   double t_issue = 0, t_wait = 0, t_host = 0, n_steps = 0;
 
@@ -463,6 +464,24 @@ int gemm_act(mi8d_decoder* d, const int8_t* q, int M, const Aff& w, bool relu, f
 int quant_gemm(mi8d_decoder* d, const float* x, int M, const unsigned* slot, const Aff& w, bool relu, float* c, cudaStream_t s,
                unsigned* absmax_out = nullptr) {
   float* qa = reinterpret_cast<float*>(d->aq + static_cast<size_t>(M) * w.K);
+  if(!w.p8 && d->opt_cluster && M <= d->opt_cluster_max_rows && w.K <= d->opt_cluster_max_k && gemm_cq_supported(M, w.N, w.K, false)) {
+    // the cluster GEMM: the CTAs of neighbouring weight tiles quantise the activation tile together (one launch, no int8 copy)
+    CqCall g;
+    g.a_f32 = x;
+    g.a_slot = slot;
+    g.bt = w.bt;
+    g.d_qb = w.qm;
+    g.M = M;
+    g.N = w.N;
+    g.K = w.K;
+    g.bias = w.bias;
+    g.relu = relu ? 1 : 0;
+    g.c = c;
+    g.absmax_out = absmax_out;
+    g.force_cluster = d->opt_cluster_size;
+    g.stream = s;
+    return launch_gemm_cq(g);
+  }
   if(!w.p8 && d->opt_quant_in_gemm && w.K <= 1024 && quant_a_tile(M, w.N) != 0)
     return launch_gemm_quant_a(x, slot, qa, w.bt, M, w.N, w.K, w.qm, 1.0f, w.bias, relu ? 1 : 0, c, MI8_F32, nullptr, s, absmax_out);
   MI8D_TRY(quantize_act(d, x, M, w.K, slot, d->aq, s));
@@ -472,6 +491,37 @@ int quant_gemm(mi8d_decoder* d, const float* x, int M, const unsigned* slot, con
 int add_ln(mi8d_decoder* d, const float* a, const float* resid, const Norm& n, int rows, float* out, float* rowmax, unsigned* slot,
            cudaStream_t s, unsigned* slot2 = nullptr) {
   return launch_add_layernorm(a, resid, n.g, n.b, 1e-6f, rows, d->cfg.dim_emb, out, rowmax, slot, s, slot2);
+}
+
+// out = LayerNorm(affine(x) + resid): the "dan" post-processing of a sub-layer's last affine (src/models/transformer.h:189-214).
+// One launch when the row fits a cluster (the cluster GEMM's LayerNorm write-back), else affine (into `tmp`) and LayerNorm.
+int quant_gemm_ln(mi8d_decoder* d, const float* x, int M, const unsigned* slot, const Aff& w, const float* resid, const Norm& n, float* tmp,
+                  float* out, float* rowmax, unsigned* out_slot, cudaStream_t s, unsigned* out_slot2 = nullptr) {
+  if(!w.p8 && d->opt_cluster && d->opt_fused_ln && M <= d->opt_cluster_max_rows && w.K <= d->opt_cluster_max_k && w.N == d->cfg.dim_emb &&
+     gemm_cq_supported(M, w.N, w.K, true)) {
+    CqCall g;
+    g.a_f32 = x;
+    g.a_slot = slot;
+    g.bt = w.bt;
+    g.d_qb = w.qm;
+    g.M = M;
+    g.N = w.N;
+    g.K = w.K;
+    g.bias = w.bias;
+    g.ln = 1;
+    g.ln_resid = resid;
+    g.ln_gamma = n.g;
+    g.ln_beta = n.b;
+    g.ln_eps = 1e-6f;
+    g.ln_out = out;
+    g.ln_rowmax = rowmax;
+    g.ln_slot = out_slot;
+    g.ln_slot2 = out_slot2;
+    g.stream = s;
+    return launch_gemm_cq(g);
+  }
+  MI8D_TRY(quant_gemm(d, x, M, slot, w, false, tmp, s));
+  return add_ln(d, tmp, resid, n, M, out, rowmax, out_slot, s, out_slot2);
 }
 
 }  // namespace
@@ -608,6 +658,15 @@ int mi8d_set_option(mi8d_decoder* d, int option, int value) {
     case MI8D_OPT_QUANT_IN_GEMM: d->opt_quant_in_gemm = value != 0; break;
     case MI8D_OPT_FUSED_OUTPUT_MAX_ROWS: d->opt_fused_out_rows = value; break;
     case MI8D_OPT_SIDE_STREAM: d->opt_side_stream = value != 0; break;
+    case MI8D_OPT_CLUSTER_AFFINE: d->opt_cluster = value != 0; break;
+    case MI8D_OPT_FUSED_LAYERNORM: d->opt_fused_ln = value != 0; break;
+    case MI8D_OPT_CLUSTER_MAX_ROWS: d->opt_cluster_max_rows = value; break;
+    case MI8D_OPT_CLUSTER_SIZE:
+      if(value != 0 && value != 1 && value != 2 && value != 4 && value != 8)
+        return MI8_ERR_BAD_ARG;
+      d->opt_cluster_size = value;
+      break;
+    case MI8D_OPT_CLUSTER_MAX_K: d->opt_cluster_max_k = value; break;
     case MI8D_OPT_ATTENTION_UNROLL:
       if(value != 8 && value != 16)
         return MI8_ERR_BAD_ARG;
@@ -693,6 +752,53 @@ int mi8g_add_layernorm(const float* a, const float* resid, const float* gamma, c
   if(gamma == nullptr || beta == nullptr)
     return MI8_ERR_BAD_ARG;
   return launch_add_layernorm(a, resid, gamma, beta, eps, rows, dim, out, rowmax, absmax_slot, as_stream(stream));
+}
+int mi8g_affine_slot(const float* a, const unsigned* absmax_slot, const int8_t* bt, const float* d_qb, int M, int N, int K,
+                     float scale, const float* bias, int relu, float* c, unsigned* absmax_out, int tile_rows, int cluster,
+                     void* stream) {
+  CqCall g;
+  g.a_f32 = a;
+  g.a_slot = absmax_slot;
+  g.bt = bt;
+  g.d_qb = d_qb;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.scale = scale;
+  g.bias = bias;
+  g.relu = relu;
+  g.c = c;
+  g.absmax_out = absmax_out;
+  g.force_tile_m = tile_rows;
+  g.force_cluster = cluster;
+  g.stream = as_stream(stream);
+  return launch_gemm_cq(g);
+}
+int mi8g_affine_slot_add_layernorm(const float* a, const unsigned* absmax_slot, const int8_t* bt, const float* d_qb, int M,
+                                   int N, int K, float scale, const float* bias, const float* resid, const float* gamma,
+                                   const float* beta, float eps, float* out, float* rowmax, unsigned* out_slot,
+                                   unsigned* out_slot2, void* stream) {
+  CqCall g;
+  g.a_f32 = a;
+  g.a_slot = absmax_slot;
+  g.bt = bt;
+  g.d_qb = d_qb;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.scale = scale;
+  g.bias = bias;
+  g.ln = 1;
+  g.ln_resid = resid;
+  g.ln_gamma = gamma;
+  g.ln_beta = beta;
+  g.ln_eps = eps;
+  g.ln_out = out;
+  g.ln_rowmax = rowmax;
+  g.ln_slot = out_slot;
+  g.ln_slot2 = out_slot2;
+  g.stream = as_stream(stream);
+  return launch_gemm_cq(g);
 }
 int mi8g_quantize_slot(const float* x, size_t n, const unsigned* absmax_slot, int8_t* q, float* d_quant_mult, void* stream) {
   return launch_quantize_slot(x, n, absmax_slot, q, d_quant_mult, as_stream(stream));
@@ -929,8 +1035,7 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
       MI8D_TRY(gemm_act(d, d->aq, R, w.self_v, false, L.vslab + static_cast<size_t>(t) * slab_stride, s));
       MI8D_TRY(launch_attention1(d->qbuf, L.kslab, L.vslab, nullptr, R, c.heads, dm / c.heads, t + 1, batch, 0, d->abuf, sa, s, d->anc[anc_new],
                                  SR, SR));
-      MI8D_TRY(quant_gemm(d, d->abuf, R, sa, w.self_o, false, d->obuf, s));
-      MI8D_TRY(add_ln(d, d->obuf, x, w.ln_self, R, d->x1, nullptr, s1, s));
+      MI8D_TRY(quant_gemm_ln(d, d->abuf, R, sa, w.self_o, x, w.ln_self, d->obuf, d->x1, nullptr, s1, s));
     } else {
       unsigned* sh = d->layer_slot(l, kSlotHistory);
       unsigned* sa = d->layer_slot(l, kSlotSelfAtt);
@@ -986,28 +1091,25 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
         MI8D_CUDA(cudaStreamWaitEvent(s, d->ev_join, 0));
       MI8D_TRY(launch_attention1(d->qbuf, L.kslab, L.vslab, nullptr, R, c.heads, dm / c.heads, steps, batch, 0, d->abuf, sa, s,
                                  d->anc[anc_new], SR, SR));
-      MI8D_TRY(quant_gemm(d, d->abuf, R, sa, w.self_o, false, d->obuf, s));
-      MI8D_TRY(add_ln(d, d->obuf, x, w.ln_self, R, d->x1, nullptr, s1, s));
+      MI8D_TRY(quant_gemm_ln(d, d->abuf, R, sa, w.self_o, x, w.ln_self, d->obuf, d->x1, nullptr, s1, s));
     }
     {
       unsigned* sa = d->layer_slot(l, kSlotCtxAtt);
       unsigned* s2 = d->layer_slot(l, kSlotCtxLn);
       MI8D_TRY(quant_gemm(d, d->x1, R, s1, w.ctx_q, false, d->qbuf, s));
       MI8D_TRY(launch_attention1(d->qbuf, L.cross_k, L.cross_v, lmask, R, c.heads, dm / c.heads, S, batch, 1, d->abuf, sa, s));
-      MI8D_TRY(quant_gemm(d, d->abuf, R, sa, w.ctx_o, false, d->obuf, s));
-      MI8D_TRY(add_ln(d, d->obuf, d->x1, w.ln_ctx, R, d->x2, nullptr, s2, s));
+      MI8D_TRY(quant_gemm_ln(d, d->abuf, R, sa, w.ctx_o, d->x1, w.ln_ctx, d->obuf, d->x2, nullptr, s2, s));
 
       unsigned* s3 = d->layer_slot(l, kSlotRelu);
       MI8D_TRY(quant_gemm(d, d->x2, R, s2, w.w1, true, d->hbuf, s, s3));   // ReLU and max|h| fused in the write-back
-      MI8D_TRY(quantize_act(d, d->hbuf, R, c.dim_ffn, s3, d->aq, s));
-      MI8D_TRY(gemm_act(d, d->aq, R, w.w2, false, d->obuf, s));
+
       // the block's output is the next layer's input: write it straight into that layer's history slab, and its
       // maximum into that layer's history abs-max as well
       const bool last = l + 1 == c.dec_depth;
       float* nx = last ? d->x_final : (c.ssru ? d->x_in : d->layers[l + 1].slab + static_cast<size_t>(t) * slab_stride);
       float* nx_rowmax = (last || c.ssru) ? nullptr : d->layers[l + 1].rowmax + static_cast<size_t>(t) * SR;
       unsigned* nx_hist = (last || c.ssru) ? nullptr : d->layer_slot(l + 1, kSlotHistory);
-      MI8D_TRY(add_ln(d, d->obuf, d->x2, w.ln_ffn, R, nx, nx_rowmax, d->layer_slot(l, kSlotOut), s, nx_hist));
+      MI8D_TRY(quant_gemm_ln(d, d->hbuf, R, s3, w.w2, d->x2, w.ln_ffn, d->obuf, nx, nx_rowmax, d->layer_slot(l, kSlotOut), s, nx_hist));
       x = nx;
     }
   }

@@ -1092,6 +1092,454 @@ mi8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_co
   trace_stamp(th.last, kTrGemmPair, 3, trace_extra);
 }
 
+// ------------------------------------------------------------------ cluster variant (decode shapes)
+// One launch = "quantise the fp32 activation with the multiplier of its abs-max slot" + GEMM + write-back, and
+// optionally the residual add + LayerNorm that follows.  A cluster holds the CTAs of `csize` neighbouring weight
+// tiles of ONE activation tile.  Every CTA needs the whole quantised activation tile [TM, K]; CTA `rank`
+// quantises the 128-byte K blocks kb = rank, rank + csize, ... (fp32 read once per cluster) and stores each
+// 16-byte chunk into the shared memory of all CTAs of the cluster at the place the 128-byte swizzle gives it,
+// then arrives on a_full[kb] in each of them.  The activation tile stays resident (K <= 4096), only the weight
+// tiles run through a TMA ring.  One tile per CTA, no split-K.
+//   LayerNorm mode (TM = 32, the cluster covers the whole row: csize = N / 128 <= 8): the write-back keeps
+//   y = C + residual in shared memory, every CTA reduces its 128 columns per row exactly as one warp of
+//   add_layernorm_kernel does (lane l owns columns 4l..4l+3, butterfly), the per-row partial sums travel to all
+//   CTAs of the cluster, and are added in ascending block order starting from 0 - the arithmetic of
+//   add_layernorm_kernel for rows of up to 1024 values, bit for bit.  Three cluster barriers separate the phases;
+//   every thread of every CTA reaches them whatever happened before (all other waits are bounded).
+constexpr int kCqMaxKb = 32;        // K <= 4096
+constexpr int kCqMaxCluster = 8;
+constexpr int kCqLnRows = 64;      // activation rows per tile in LayerNorm mode: 32 or 64
+
+struct CqControl {
+  uint64_t w_full[kMaxStages];
+  uint64_t w_empty[kMaxStages];
+  uint64_t a_full[kCqMaxKb];
+  uint64_t tmem_full;
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort;
+  float part_sum[kCqMaxCluster][kCqLnRows];
+  float part_sq[kCqMaxCluster][kCqLnRows];
+  unsigned part_max[kCqMaxCluster][kCqLnRows];
+};
+
+struct CqParams {
+  int M, N, K, kb_total, stages;
+  const float* a_f32;       // [M, K] fp32
+  const unsigned* a_slot;   // bit pattern of max|A|
+  float* qa_out;            // optional: receives 127 / max|A|
+  const float* d_qb;
+  float scale;
+  const float* bias;
+  int relu;
+  float* c;                 // [M, N] fp32 (plain mode)
+  unsigned* absmax_out;     // plain mode: max|C| reduced into this slot
+  int ln;                   // 1: out = LayerNorm(C + resid) * gamma + beta instead of C
+  const float* ln_resid;
+  const float* ln_gamma;
+  const float* ln_beta;
+  float ln_eps;
+  float* ln_out;
+  float* ln_rowmax;         // optional [M]
+  unsigned* ln_slot;        // optional abs-max slots of the output
+  unsigned* ln_slot2;
+  int* status;
+  uint32_t spin_limit;
+  int withhold_item;
+  int* rows_computed;
+};
+
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, const uint4& v) {
+  asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// try_wait whose acquire reaches writes released at cluster scope (shared memory written by another CTA)
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t limit) {
+  for(uint32_t i = 0; i < limit; ++i) {
+    if(mbar_try_wait_cluster(bar, parity))
+      return true;
+    if((i & 0xff) == 0xff && *abort_flag)
+      return false;
+  }
+  return false;
+}
+
+template <int TM>
+constexpr int cq_smem_bytes(int kb_total, int stages) {
+  return kb_total * TM * kTileKBytes + stages * kTileN * kTileKBytes + static_cast<int>(sizeof(CqControl)) + 1024;
+}
+
+template <int TM>
+__global__ void __launch_bounds__(kThreads, 1)
+mi8_gemm_cq_kernel(const __grid_constant__ CUtensorMap tmap_w, const CqParams p) {
+  constexpr int kWBytes = kTileN * kTileKBytes;
+  constexpr int kABlock = TM * kTileKBytes;          // one K block of the activation tile
+  constexpr int kTmemCols = TM < 32 ? 32 : TM;
+  constexpr int kConvWarps = kEpilogueThreads / 32;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;   // the same in every CTA of the kernel
+  uint8_t* a_region = smem_raw + pad;
+  uint8_t* w_ring = a_region + p.kb_total * kABlock;
+  CqControl* ctl = reinterpret_cast<CqControl*>(w_ring + p.stages * kWBytes);
+  volatile int* abort_flag = &ctl->abort;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const uint32_t csize = cluster_nctarank();
+  const int n_tile = blockIdx.x;
+  const int m0 = blockIdx.y * TM;
+
+  pdl_launch_dependents();
+  const TraceHandles th = trace_open_all();
+  unsigned long long* const tb = th.first;
+  const unsigned long long trace_extra = static_cast<unsigned long long>(p.N) | (static_cast<unsigned long long>(p.K) << 20);
+  if(threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_w);
+    for(int s = 0; s < p.stages; ++s) {
+      mbar_init(&ctl->w_full[s], 1);
+      mbar_init(&ctl->w_empty[s], 1);
+    }
+    for(int kb = 0; kb < p.kb_total; ++kb)
+      mbar_init(&ctl->a_full[kb], kConvWarps);    // one arrival per quantising warp of the CTA that owns the K block
+    mbar_init(&ctl->tmem_full, 1);
+    mbar_init(&ctl->drain, 1);
+    ctl->abort = 0;
+    fence_mbar_init();
+  }
+  if(warp == 1) {
+    tmem_alloc(&ctl->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&ctl->tmem_base);
+  cluster_sync_all();   // the barriers of every CTA of the cluster exist before anything is stored or signalled remotely
+
+  bool ok = true;
+  float unquant = 1.0f;
+
+  if(warp == 0) {
+    // ------------------------------------------------------------ weight producer (weights never depend on the preceding kernel)
+    for(int kb = 0; kb < p.kb_total; ++kb) {
+      const uint32_t s = kb % p.stages;
+      const uint32_t ph = (kb / p.stages) & 1u;
+      if(kb >= p.stages)
+        ok = mbar_wait_bounded(&ctl->w_empty[s], ph ^ 1u, abort_flag, p.spin_limit);
+      ok = __all_sync(0xffffffffu, ok);
+      if(!ok)
+        break;
+      if(elect_one() && kb != p.withhold_item) {
+        mbar_arrive_expect_tx(&ctl->w_full[s], kWBytes);
+        tma_load_2d(w_ring + s * kWBytes, &tmap_w, kb * kTileKBytes, n_tile * kTileN, &ctl->w_full[s]);
+      }
+      __syncwarp();
+    }
+    if(!ok) {
+      *abort_flag = 1;
+      if(lane == 0)
+        atomicMax(p.status, static_cast<int>(kDevTimeoutProducer));
+    }
+  } else if(warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = make_idesc_i8(TM);
+    for(int kb = 0; kb < p.kb_total; ++kb) {
+      const uint32_t s = kb % p.stages;
+      const uint32_t ph = (kb / p.stages) & 1u;
+      ok = mbar_wait_cluster_bounded(&ctl->a_full[kb], 0u, abort_flag, p.spin_limit) && mbar_wait_bounded(&ctl->w_full[s], ph, abort_flag, p.spin_limit);
+      ok = __all_sync(0xffffffffu, ok);
+      if(!ok)
+        break;
+      fence_proxy_async_smem();
+      tc_fence_after_sync();
+      const uint32_t w_addr = smem_u32(w_ring + s * kWBytes);
+      const uint32_t a_addr = smem_u32(a_region + kb * kABlock);
+      if(elect_one()) {
+#pragma unroll
+        for(int k = 0; k < kTileKBytes / kMmaK; ++k)
+          tc_mma_i8(tmem_base, make_kmajor_sw128_desc(w_addr + k * kMmaK), make_kmajor_sw128_desc(a_addr + k * kMmaK), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&ctl->w_empty[s]);
+      }
+      __syncwarp();
+    }
+    if(ok) {
+      if(elect_one())
+        tc_commit(&ctl->tmem_full);
+      __syncwarp();
+    } else {
+      *abort_flag = 1;
+      if(lane == 0)
+        atomicMax(p.status, static_cast<int>(kDevTimeoutMma));
+    }
+  } else {
+    // ------------------------------------------------------------ quantisers, then write-back (warps 2..9)
+    const int epi_tid = threadIdx.x - 64;
+    const int quarter = warp & 3;
+    const int group = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;
+    pdl_wait();   // the activation and its abs-max slot are the preceding kernel's output
+    trace_stamp_start(th, kTrGemmCq, trace_extra);
+    if(p.rows_computed != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && epi_tid == 0)
+      *p.rows_computed = p.M;
+    constexpr int kCpt = TM * 8 / kEpilogueThreads;     // 16-byte chunks per thread and K block (1, 2, 4)
+    constexpr int kBatch = 4 / kCpt;                    // K blocks per batch: 16 loads of 16 bytes in flight per thread
+    const uint32_t a_base = smem_u32(a_region);
+    const uint32_t bar_base = smem_u32(&ctl->a_full[0]);
+    float qa = 1.0f;
+    bool qa_ready = false;
+    for(int kb0 = static_cast<int>(rank); kb0 < p.kb_total; kb0 += static_cast<int>(csize) * kBatch) {
+      float4 f[kBatch][kCpt][4];
+#pragma unroll
+      for(int b = 0; b < kBatch; ++b) {
+        const int kb = kb0 + b * static_cast<int>(csize);
+#pragma unroll
+        for(int q = 0; q < kCpt; ++q) {
+          const int c = epi_tid + q * kEpilogueThreads;
+          const int gm = m0 + (c >> 3);
+          const bool in = kb < p.kb_total && gm < p.M;
+          const float4* src = reinterpret_cast<const float4*>(p.a_f32 + static_cast<size_t>(in ? gm : 0) * p.K + (in ? kb * kTileKBytes + (c & 7) * 16 : 0));
+#pragma unroll
+          for(int e = 0; e < 4; ++e)
+            f[b][q][e] = in ? src[e] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+      if(!qa_ready) {   // (read after the loads above were issued: the two round trips overlap)
+        const unsigned bits = *p.a_slot;
+        qa = bits == 0u ? 1.0f : __fdiv_rn(127.0f, __uint_as_float(bits));
+        unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.d_qb)), p.scale);
+        if(blockIdx.x == 0 && blockIdx.y == 0 && epi_tid == 0) {
+          if(p.qa_out != nullptr)
+            *p.qa_out = qa;
+          if(bits >= 0x7f800000u)
+            atomicMax(p.status, static_cast<int>(kDevNonFinite));
+        }
+        qa_ready = true;
+      }
+#pragma unroll
+      for(int b = 0; b < kBatch; ++b) {
+        const int kb = kb0 + b * static_cast<int>(csize);
+        if(kb < p.kb_total) {
+#pragma unroll
+          for(int q = 0; q < kCpt; ++q) {
+            const int c = epi_tid + q * kEpilogueThreads;
+            const int r = c >> 3, ch = c & 7;
+            uint4 o;
+            o.x = pack4_i8(f[b][q][0], qa);
+            o.y = pack4_i8(f[b][q][1], qa);
+            o.z = pack4_i8(f[b][q][2], qa);
+            o.w = pack4_i8(f[b][q][3], qa);
+            const uint32_t off = static_cast<uint32_t>(kb * kABlock + r * 128 + ((ch ^ (r & 7)) << 4));
+            for(uint32_t j = 0; j < csize; ++j)
+              st_cluster_v4(mapa_shared(a_base + off, j), o);
+          }
+          fence_proxy_async_all();   // the tensor cores read these bytes through the async proxy
+          __syncwarp();
+          if(lane < csize)
+            mbar_arrive_cluster(mapa_shared(bar_base + static_cast<uint32_t>(kb) * 8u, lane));
+        }
+      }
+    }
+    trace_stamp(tb, kTrGemmCq, 4, trace_extra);   // this CTA's share of the activation tile is stored and signalled
+    if(!qa_ready) {   // (more CTAs in the cluster than K blocks: this one quantised nothing)
+      const unsigned bits = *p.a_slot;
+      qa = bits == 0u ? 1.0f : __fdiv_rn(127.0f, __uint_as_float(bits));
+      unquant = __fmul_rn(__fdiv_rn(1.0f, __fmul_rn(qa, *p.d_qb)), p.scale);
+    }
+
+    if(lane == 0)
+      ok = mbar_wait_bounded(&ctl->tmem_full, 0u, abort_flag, p.spin_limit);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    trace_stamp(tb, kTrGemmCq, 5, trace_extra);   // accumulator complete
+    if(ok) {
+      tc_fence_after_sync();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int n = n_tile * kTileN + row;
+      const bool n_ok = n < p.N;
+      const float bias_n = (p.bias != nullptr && n_ok) ? __ldg(p.bias + n) : 0.0f;
+      constexpr int kChunks = TM / 32;
+      constexpr int kChunkStep = kChunks > 1 ? 2 : 1;
+      const bool has_chunks = kChunks > 1 || group == 0;
+      unsigned out_max = 0u;
+      if(has_chunks) {
+#pragma unroll 1
+        for(int c = group * (kChunkStep - 1); c < kChunks; c += kChunkStep) {
+          int32_t v[32];
+          tmem_ld_chunk<32>(t_addr + c * 32, v);
+          tc_wait_ld();
+          const int valid = min(32, p.M - (m0 + c * 32));
+          float fv[32];
+#pragma unroll
+          for(int j = 0; j < 32; ++j)
+            fv[j] = __fmul_rn(__int2float_rn(v[j]), unquant);
+          if(p.bias != nullptr) {
+#pragma unroll
+            for(int j = 0; j < 32; ++j)
+              fv[j] = __fadd_rn(fv[j], bias_n);
+          }
+          if(p.relu) {
+#pragma unroll
+            for(int j = 0; j < 32; ++j)
+              fv[j] = fv[j] > 0.0f ? fv[j] : 0.0f;
+          }
+          if(p.ln) {
+            // y = C + residual, parked row-major [TM rows][128 columns] where the weight ring was (all its tiles are consumed)
+            float* tile = reinterpret_cast<float*>(w_ring) + c * 32 * 128;
+            const float* res = p.ln_resid + static_cast<size_t>(m0 + c * 32) * p.N + n;
+#pragma unroll
+            for(int j = 0; j < 32; ++j) {
+              float y = 0.0f;
+              if(j < valid && n_ok)
+                y = p.ln_resid != nullptr ? __fadd_rn(fv[j], res[static_cast<size_t>(j) * p.N]) : fv[j];
+              tile[j * 128 + row] = y;
+            }
+          } else if(n_ok) {
+            float* dst = p.c + static_cast<size_t>(m0 + c * 32) * p.N + n;
+#pragma unroll
+            for(int j = 0; j < 32; ++j)
+              if(j < valid) {
+                dst[static_cast<size_t>(j) * p.N] = fv[j];
+                out_max = max(out_max, __float_as_uint(fv[j]) & 0x7fffffffu);
+              }
+          }
+        }
+      }
+      trace_stamp(tb, kTrGemmCq, 6, trace_extra);   // write-back (or the LayerNorm tile) done
+      if(!p.ln && p.absmax_out != nullptr) {
+        out_max = __reduce_max_sync(0xffffffffu, out_max);
+        if(lane == 0 && out_max != 0u)
+          atomicMax(p.absmax_out, out_max);
+      }
+    } else {
+      *abort_flag = 1;
+      if(lane == 0)
+        atomicMax(p.status, static_cast<int>(kDevTimeoutEpilogue));
+    }
+  }
+
+  if(p.ln) {
+    // ------------------------------------------------------------ LayerNorm over the cluster (TM = 32 or 64): warp e of the eight takes rows kRpw * e .. + kRpw - 1
+    const bool worker = warp >= 2;
+    const int e = warp - 2;
+    const float* tile = reinterpret_cast<const float*>(w_ring);
+    const float dimf = static_cast<float>(p.N);
+    constexpr int kRpw = TM >= 64 ? 8 : 4;   // rows per warp (TM = 128 never runs this mode)
+    float4 x[kRpw];
+    float mean[kRpw];
+    if(worker) {
+      named_bar_sync(1, kEpilogueThreads);   // the tile is complete
+#pragma unroll
+      for(int i = 0; i < kRpw; ++i) {
+        const int m = kRpw * e + i;
+        x[i] = *reinterpret_cast<const float4*>(tile + m * 128 + 4 * lane);
+        const float s = warp_sum_det(__fadd_rn(0.0f, __fadd_rn(__fadd_rn(x[i].x, x[i].y), __fadd_rn(x[i].z, x[i].w))));
+        if(lane < csize)
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(mapa_shared(smem_u32(&ctl->part_sum[rank][m]), lane)), "f"(s) : "memory");
+      }
+    }
+    cluster_sync_all();
+    if(worker) {
+#pragma unroll
+      for(int i = 0; i < kRpw; ++i) {
+        const int m = kRpw * e + i;
+        float t = 0.0f;
+#pragma unroll
+        for(int w = 0; w < kCqMaxCluster; ++w)
+          t = __fadd_rn(t, w < static_cast<int>(csize) ? ctl->part_sum[w][m] : 0.0f);
+        mean[i] = __fdiv_rn(t, dimf);
+        const float dx = __fadd_rn(x[i].x, -mean[i]), dy = __fadd_rn(x[i].y, -mean[i]), dz = __fadd_rn(x[i].z, -mean[i]), dw = __fadd_rn(x[i].w, -mean[i]);
+        const float q = warp_sum_det(__fadd_rn(0.0f, __fmaf_rn(dx, dx, __fmaf_rn(dy, dy, __fmaf_rn(dz, dz, __fmul_rn(dw, dw))))));
+        if(lane < csize)
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(mapa_shared(smem_u32(&ctl->part_sq[rank][m]), lane)), "f"(q) : "memory");
+      }
+    }
+    cluster_sync_all();
+    if(worker) {
+      const int ncol = n_tile * kTileN + 4 * lane;
+      const float4 g = __ldg(reinterpret_cast<const float4*>(p.ln_gamma + ncol));
+      const float4 b = __ldg(reinterpret_cast<const float4*>(p.ln_beta + ncol));
+      unsigned wmax = 0u;
+#pragma unroll
+      for(int i = 0; i < kRpw; ++i) {
+        const int m = kRpw * e + i;
+        float t = 0.0f;
+#pragma unroll
+        for(int w = 0; w < kCqMaxCluster; ++w)
+          t = __fadd_rn(t, w < static_cast<int>(csize) ? ctl->part_sq[w][m] : 0.0f);
+        const float var = __fdiv_rn(t, dimf);
+        const float denom = __fsqrt_rn(__fadd_rn(var, p.ln_eps));
+        float4 o;
+        o.x = __fadd_rn(__fmul_rn(__fdiv_rn(__fadd_rn(x[i].x, -mean[i]), denom), g.x), b.x);
+        o.y = __fadd_rn(__fmul_rn(__fdiv_rn(__fadd_rn(x[i].y, -mean[i]), denom), g.y), b.y);
+        o.z = __fadd_rn(__fmul_rn(__fdiv_rn(__fadd_rn(x[i].z, -mean[i]), denom), g.z), b.z);
+        o.w = __fadd_rn(__fmul_rn(__fdiv_rn(__fadd_rn(x[i].w, -mean[i]), denom), g.w), b.w);
+        unsigned rmax = 0u;
+        if(m0 + m < p.M) {
+          *reinterpret_cast<float4*>(p.ln_out + static_cast<size_t>(m0 + m) * p.N + ncol) = o;
+          rmax = max(max(__float_as_uint(o.x) & 0x7fffffffu, __float_as_uint(o.y) & 0x7fffffffu),
+                     max(__float_as_uint(o.z) & 0x7fffffffu, __float_as_uint(o.w) & 0x7fffffffu));
+        }
+        rmax = __reduce_max_sync(0xffffffffu, rmax);
+        wmax = max(wmax, rmax);
+        if(lane == 0 && p.ln_rowmax != nullptr)   // the row maximum is put together by the CTA of rank 0
+          asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(mapa_shared(smem_u32(&ctl->part_max[rank][m]), 0)), "r"(rmax) : "memory");
+      }
+      if(lane == 0 && wmax != 0u) {
+        if(p.ln_slot != nullptr)
+          atomicMax(p.ln_slot, wmax);
+        if(p.ln_slot2 != nullptr)
+          atomicMax(p.ln_slot2, wmax);
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  cluster_sync_all();   // no CTA leaves while a peer may still store into its shared memory or signal its barriers
+  if(p.ln && p.ln_rowmax != nullptr && rank == 0 && (warp == 2 || warp == 3)) {
+    const int m = (warp - 2) * 32 + lane;
+    if(m < TM && m0 + m < p.M) {
+      unsigned r = 0u;
+      for(uint32_t w = 0; w < csize; ++w)
+        r = max(r, ctl->part_max[w][m]);
+      p.ln_rowmax[m0 + m] = __uint_as_float(r);
+    }
+  }
+  if(warp == 1) {
+    if(*abort_flag) {
+      bool drained = true;
+      if(lane == 0) {
+        int no_abort = 0;
+        tc_commit(&ctl->drain);
+        drained = mbar_wait_bounded(&ctl->drain, 0u, &no_abort, p.spin_limit);
+        if(!drained)
+          atomicMax(p.status, static_cast<int>(kDevTimeoutDrain));
+      }
+      __syncwarp();
+    }
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  trace_stamp(tb, kTrGemmCq, 2, trace_extra);
+  trace_stamp(th.last, kTrGemmCq, 3, trace_extra);
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1638,6 +2086,162 @@ int launch_gemm(const int8_t* aq, const int8_t* bt, int M, int N, int K, const f
   g.skip_b = skip_b;
   g.skip_rows_below = skip_rows_below;
   return launch_gemm_call(g);
+}
+
+// ------------------------------------------------------------------ cluster GEMM (quantising, optional LayerNorm write-back)
+bool gemm_cq_supported(int M, int N, int K, bool ln) {
+  if(M <= 0 || N <= 0 || K <= 0 || N % kTileN != 0 || K % kTileKBytes != 0 || K / kTileKBytes > kCqMaxKb)
+    return false;
+  if(ln && N / kTileN > kCqMaxCluster)
+    return false;
+  return true;
+}
+
+namespace {
+template <int TM>
+int launch_cq_tile(const CUtensorMap& tw, CqParams& p, int n_tiles, int cluster, cudaStream_t stream) {
+  static int attr_smem[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if(dev < 0 || dev >= 64)
+    return MI8_ERR_UNSUPPORTED;
+  constexpr int kSmemMax = 232448;   // 227 KB opt-in limit per CTA
+  const int fixed = p.kb_total * TM * kTileKBytes + static_cast<int>(sizeof(CqControl)) + 1024;
+  int stages = (kSmemMax - fixed) / (kTileN * kTileKBytes);
+  if(stages > kMaxStages)
+    stages = kMaxStages;
+  const int min_stages = p.ln ? TM / 32 : 1;   // (LayerNorm mode parks its [TM][128] fp32 tile where the ring was)
+  if(stages > p.kb_total)
+    stages = p.kb_total > min_stages ? p.kb_total : min_stages;
+  if(stages < min_stages)
+    return MI8_ERR_UNSUPPORTED;
+  p.stages = stages;
+  const int smem = cq_smem_bytes<TM>(p.kb_total, stages);
+  if(attr_smem[dev] < smem) {
+    cudaError_t e = cudaFuncSetAttribute(mi8_gemm_cq_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+    if(e != cudaSuccess) {
+      set_last_cuda_error(e);
+      return MI8_ERR_LAUNCH;
+    }
+    attr_smem[dev] = kSmemMax;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_tiles, (p.M + TM - 1) / TM);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  ProfileRecord rec{};
+  const bool profiled = t_profile.on && t_profile.records.size() < t_profile.capacity;
+  if(profiled) {
+    rec = ProfileRecord{p.M, p.N, p.K, 4, t_profile.take(), t_profile.take()};
+    if(rec.start != nullptr && rec.stop != nullptr)
+      cudaEventRecord(rec.start, stream);
+  }
+  const bool timed = kernel_times_on();
+  if(timed) {
+    cfg.numAttrs = 1;
+    kernel_times_before(reinterpret_cast<const void*>(mi8_gemm_cq_kernel<TM>), stream);
+  }
+  cudaError_t le = cudaLaunchKernelEx(&cfg, mi8_gemm_cq_kernel<TM>, tw, p);
+  if(timed)
+    kernel_times_after(stream);
+  if(le != cudaSuccess) {
+    set_last_cuda_error(le);
+    return MI8_ERR_LAUNCH;
+  }
+  if(profiled && rec.start != nullptr && rec.stop != nullptr) {
+    cudaEventRecord(rec.stop, stream);
+    t_profile.records.push_back(rec);
+  }
+  count_launch();
+  return check_launch();
+}
+}  // namespace
+
+int launch_gemm_cq(const CqCall& g) {
+  if(g.a_f32 == nullptr || g.a_slot == nullptr || g.bt == nullptr || g.d_qb == nullptr)
+    return MI8_ERR_BAD_ARG;
+  if(!gemm_cq_supported(g.M, g.N, g.K, g.ln != 0))
+    return MI8_ERR_UNSUPPORTED;
+  if(g.ln ? (g.ln_out == nullptr || g.ln_gamma == nullptr || g.ln_beta == nullptr) : g.c == nullptr)
+    return MI8_ERR_BAD_ARG;
+  if((reinterpret_cast<uintptr_t>(g.a_f32) & 15u) != 0)
+    return MI8_ERR_BAD_ARG;
+  const int n_tiles = g.N / kTileN;
+  int cluster = g.force_cluster;
+  if(g.ln)
+    cluster = n_tiles;
+  else if(cluster <= 0) {
+    cluster = 4;     // larger clusters share the quantisation further but are placed fewer at a time (measured slower)
+    while(n_tiles % cluster != 0)
+      cluster >>= 1;
+  }
+  if(cluster < 1 || cluster > kCqMaxCluster || n_tiles % cluster != 0)
+    return MI8_ERR_BAD_ARG;
+  // the narrowest tile that still gives every tile its own SM (as the plain kernel's plan does)
+  int tm = g.force_tile_m;
+  if(g.ln) {
+    // Clusters of eight are placed a few at a time (measured: about eight fit at once), so rows go in tiles of 64 as soon
+    // as 32-row tiles would need more clusters than that and the 64-row activation tile still fits in shared memory.
+    if(tm != 32 && tm != 64)
+      tm = ((g.M + 31) / 32 > 8 && g.K <= 2048) ? 64 : 32;
+    if(tm == 64 && g.K > 2048)
+      return MI8_ERR_UNSUPPORTED;
+  } else if(tm <= 0) {
+    const int sms = sm_count();
+    tm = 32;
+    while(tm < 128 && n_tiles * ((g.M + tm - 1) / tm) > sms)
+      tm <<= 1;
+  }
+  if(tm != 32 && tm != 64 && tm != 128)
+    return MI8_ERR_BAD_ARG;
+  CqParams p{};
+  p.M = g.M;
+  p.N = g.N;
+  p.K = g.K;
+  p.kb_total = g.K / kTileKBytes;
+  p.a_f32 = g.a_f32;
+  p.a_slot = g.a_slot;
+  p.qa_out = g.qa_out;
+  p.d_qb = g.d_qb;
+  p.scale = g.scale;
+  p.bias = g.bias;
+  p.relu = g.relu;
+  p.c = g.c;
+  p.absmax_out = g.absmax_out;
+  p.ln = g.ln;
+  p.ln_resid = g.ln_resid;
+  p.ln_gamma = g.ln_gamma;
+  p.ln_beta = g.ln_beta;
+  p.ln_eps = g.ln_eps;
+  p.ln_out = g.ln_out;
+  p.ln_rowmax = g.ln_rowmax;
+  p.ln_slot = g.ln_slot;
+  p.ln_slot2 = g.ln_slot2;
+  p.status = device_status_ptr();
+  p.withhold_item = g_test_withhold_item;
+  p.spin_limit = g_test_spin_limit != 0 ? g_test_spin_limit : kSpinLimit;
+  p.rows_computed = nullptr;
+  if(t_profile.on && t_profile.d_rows != nullptr && t_profile.records.size() < t_profile.capacity)
+    p.rows_computed = t_profile.d_rows + t_profile.records.size();
+  CUtensorMap tw;
+  int rc = get_kmajor_map(&tw, g.bt, g.N, g.K, kTileN);
+  if(rc != MI8_OK)
+    return rc;
+  switch(tm) {
+    case 32: return launch_cq_tile<32>(tw, p, n_tiles, cluster, g.stream);
+    case 64: return launch_cq_tile<64>(tw, p, n_tiles, cluster, g.stream);
+    default: return launch_cq_tile<128>(tw, p, n_tiles, cluster, g.stream);
+  }
 }
 
 // The packed8avx512 multiply: the plan of launch_gemm (CTA-pair kernel included); the accumulators and the

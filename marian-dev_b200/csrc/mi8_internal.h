@@ -111,6 +111,40 @@ int launch_gemm_quant_a(const float* a_f32, const unsigned* a_slot, float* qa_ou
                         const float* d_qb, float scale, const float* bias, int relu, void* c, int out_dtype, int32_t* acc_out,
                         cudaStream_t stream, unsigned* absmax_out = nullptr);
 
+// The cluster GEMM for decode shapes: quantises the fp32 activation `a_f32` [M, K] itself with the multiplier of the abs-max
+// slot `a_slot` (its CTAs share the quantised tile through distributed shared memory, so the fp32 values are read once
+// per cluster), and with `ln` set writes LayerNorm(C + ln_resid) * ln_gamma + ln_beta (the arithmetic of
+// add_layernorm_kernel, bit for bit) instead of C, with the row maxima and abs-max slots that kernel produces.
+// gemm_cq_supported() says whether a shape can take this route (K a multiple of 128 up to 4096, N a multiple of 128;
+// with `ln`: N <= 1024).
+struct CqCall {
+  const float* a_f32 = nullptr;
+  const unsigned* a_slot = nullptr;
+  float* qa_out = nullptr;
+  const int8_t* bt = nullptr;
+  const float* d_qb = nullptr;
+  int M = 0, N = 0, K = 0;
+  float scale = 1.0f;
+  const float* bias = nullptr;
+  int relu = 0;
+  float* c = nullptr;
+  unsigned* absmax_out = nullptr;
+  int ln = 0;
+  const float* ln_resid = nullptr;
+  const float* ln_gamma = nullptr;
+  const float* ln_beta = nullptr;
+  float ln_eps = 0.0f;
+  float* ln_out = nullptr;
+  float* ln_rowmax = nullptr;
+  unsigned* ln_slot = nullptr;
+  unsigned* ln_slot2 = nullptr;
+  cudaStream_t stream = nullptr;
+  int force_tile_m = 0;     // 0 = chosen from M and N
+  int force_cluster = 0;    // 0 = the largest of 8, 4, 2, 1 that divides N / 128 (ln: N / 128)
+};
+bool gemm_cq_supported(int M, int N, int K, bool ln);
+int launch_gemm_cq(const CqCall& g);
+
 // packed8avx512 scheme (mi8_packed8.cu, mi8_gemm.cu): weight item back to Bt[N,K]; per-row uint8 quantisation of
 // the activation; uint8 x int8 GEMM whose write-back applies the zero points, the scales and the bias.
 int launch_p8_prepare_b(const float* w, int K, int N, int8_t* packed, cudaStream_t stream);

@@ -41,7 +41,7 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 static __device__ unsigned long long* s_trace_buf = nullptr;
 enum TraceKernel : int {
   kTrGemm = 1, kTrGemmPair, kTrQuantSlot, kTrQuantDual, kTrAddLn, kTrAttention1, kTrAttentionEnc, kTrLseTopk, kTrLseMerge,
-  kTrNbest, kTrEmbed, kTrAncestors, kTrCommit, kTrGather, kTrSsru, kTrAbsmax, kTrQuantize, kTrGemmLogits, kTrGemmQuantA
+  kTrNbest, kTrEmbed, kTrAncestors, kTrCommit, kTrGather, kTrSsru, kTrAbsmax, kTrQuantize, kTrGemmLogits, kTrGemmQuantA, kTrGemmCq
 };
 // Every kernel reads the pointer ONCE, at its entry (before its wait for the preceding kernel, so the load overlaps that
 // kernel's tail), in the two threads that stamp: the last thread of block 0 and the last thread of the last block.  All other

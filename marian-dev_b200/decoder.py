@@ -146,7 +146,8 @@ class NativeStepper:
         res = [(toks[b, :lens[b]].tolist(), float(scores[b])) for b in range(B)]
         return res, int(up.value), int(down.value)
 
-    OPTIONS = {"fuse_weights": 1, "quant_in_gemm": 2, "fused_output_max_rows": 3, "side_stream": 4, "attention_unroll": 5, "attention_block_heads": 6}
+    OPTIONS = {"fuse_weights": 1, "quant_in_gemm": 2, "fused_output_max_rows": 3, "side_stream": 4, "attention_unroll": 5, "attention_block_heads": 6,
+               "cluster_affine": 7, "fused_layernorm": 8, "cluster_max_rows": 9, "cluster_size": 10, "cluster_max_k": 11}
 
     def set_option(self, name: str, value: int):
         """mi8d_set_option: tuning switches of the step driver (every setting computes the same bits)."""

@@ -62,12 +62,13 @@ def pack_outputs(local: dict, rows: int, max_len: int):
     return mat
 
 
-def gather_outputs(local: dict, max_len: int, device=None) -> dict:
-    """All ranks contribute {sentence id: tokens}; every rank receives the union.  The payload is one
-    int32 matrix [sentences, 2 + max_len] per rank (id, length, tokens), padded to the largest count."""
-    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size() == 1:
-        return dict(local)
+def gather_output_matrices(local: dict, max_len: int, device=None):
+    """The exchange itself: every rank contributes {sentence id: tokens} as one int32 matrix [sentences, 2 + max_len]
+    (id, length, tokens), padded to the largest count, and receives every rank's matrix as NumPy arrays (host memory).
+    Without a process group: this rank's matrix alone."""
     import numpy as np
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size() == 1:
+        return [pack_outputs(local, len(local), max_len)]
     world = dist.get_world_size()
     dev = device if device is not None else torch.device("cpu")
     n = torch.tensor([len(local)], dtype=torch.int64, device=dev)
@@ -77,12 +78,24 @@ def gather_outputs(local: dict, max_len: int, device=None) -> dict:
     mat_t = torch.from_numpy(pack_outputs(local, rows, max_len)).to(dev)
     out = [torch.empty_like(mat_t) for _ in range(world)]
     dist.all_gather(out, mat_t)
+    return [m.cpu().numpy() for m in out]
+
+
+def merge_output_matrices(mats) -> dict:
+    """{sentence id: tokens} from the matrices gather_output_matrices returned."""
     merged = {}
-    for m in out:
-        m = m.cpu().numpy()
-        for row in m[m[:, 0] >= 0]:
-            merged[int(row[0])] = row[2:2 + int(row[1])].tolist()
+    for m in mats:
+        keep = m[m[:, 0] >= 0]
+        for row, n in zip(keep.tolist(), keep[:, 1].tolist()):
+            merged[row[0]] = row[2:2 + n]
     return merged
+
+
+def gather_outputs(local: dict, max_len: int, device=None) -> dict:
+    """All ranks contribute {sentence id: tokens}; every rank receives the union."""
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size() == 1:
+        return dict(local)
+    return merge_output_matrices(gather_output_matrices(local, max_len, device))
 
 
 def shard_rows(m: int, rank: int, world: int):
@@ -101,12 +114,15 @@ def global_abs_max(local_max: torch.Tensor, group=None) -> torch.Tensor:
 
 
 def sharded_affine(a_local: torch.Tensor, b, bias=None, scale: float = 1.0, relu: bool = False, out_dtype=torch.float32,
-                   group=None) -> torch.Tensor:
+                   group=None, exchange: bool = True) -> torch.Tensor:
     """The int8 affine on this rank's rows of A: local abs-max, one MAX all-reduce of a float, quantisation
-    with the agreed multiplier, GEMM with the fused write-back.  Returns this rank's rows of C."""
+    with the agreed multiplier, GEMM with the fused write-back.  Returns this rank's rows of C.
+    `exchange=False` leaves the all-reduce out (every rank then quantises with its own shard's multiplier, a
+    different result): a timing aid that shows what the exchange costs, not a mode of the product."""
     from . import ops
     amax = ops.max_absolute(a_local)
-    global_abs_max(amax, group)
+    if exchange:
+        global_abs_max(amax, group)
     aq = ops.quantize_with_absmax(a_local, amax)
     return ops.multiply(aq, b, bias, scale, relu, out_dtype=out_dtype)
 
