@@ -180,7 +180,10 @@ int mi8d_history_reuse(mi8d_decoder* d, unsigned out[2], int reset);
  *     the LayerNorm that follow it (mi8g_affine_slot_add_layernorm) when the model width is at most 1024;
  *   MI8D_OPT_CLUSTER_MAX_ROWS (default 1024): activations with more rows than this take the two-launch route;
  *   MI8D_OPT_CLUSTER_SIZE (0 = chosen, 1, 2, 4, 8): CTAs per cluster of the plain cluster affine;
- *   MI8D_OPT_CLUSTER_MAX_K (default 2048): affines with a longer inner dimension take the two-launch route. */
+ *   MI8D_OPT_CLUSTER_MAX_K (default 2048): affines with a longer inner dimension take the two-launch route;
+ *   MI8D_OPT_GEMM_TILE_ROWS (0 = the plan's choice, 32, 64, 128, 256): activation rows per tile of the decoder's plain affines.
+ *     The plan spreads a small product over as many SMs as it can (lowest latency); when several searches share a GPU
+ *     wider tiles on fewer SMs move fewer bytes from L2 for the same product. */
 enum mi8d_option {
   MI8D_OPT_FUSE_WEIGHTS = 1,
   MI8D_OPT_QUANT_IN_GEMM = 2,
@@ -192,7 +195,8 @@ enum mi8d_option {
   MI8D_OPT_FUSED_LAYERNORM = 8,
   MI8D_OPT_CLUSTER_MAX_ROWS = 9,
   MI8D_OPT_CLUSTER_SIZE = 10,
-  MI8D_OPT_CLUSTER_MAX_K = 11
+  MI8D_OPT_CLUSTER_MAX_K = 11,
+  MI8D_OPT_GEMM_TILE_ROWS = 12
 };
 int mi8d_set_option(mi8d_decoder* d, int option, int value);   /* d may be NULL for the process-wide switches */
 

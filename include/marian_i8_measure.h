@@ -47,7 +47,7 @@ typedef struct mi8_kernel_time {
 int mi8_kernel_times_begin(void);
 int mi8_kernel_times_end(mi8_kernel_time* out, int capacity, int* count);
 
-/* Number of kernels this thread has launched through the library since the last reset. */
+/* Number of kernels the process (all its threads) has launched through the library since the last reset. */
 unsigned long long mi8_launch_count(void);
 void mi8_launch_count_reset(void);
 

@@ -1,6 +1,7 @@
 // The extern "C" surface of libmarian_i8.so: argument checks, bookkeeping and the sequencing of
 // the kernels.  No call here allocates device memory or synchronises with the host, except
 // mi8_poll_status which exists to do exactly that.
+#include <atomic>
 #include <cstring>
 #include <vector>
 
@@ -15,7 +16,7 @@ __device__ int g_status_word = 0;
 
 namespace {
 thread_local cudaError_t t_last_error = cudaSuccess;
-thread_local unsigned long long t_launches = 0;
+std::atomic<unsigned long long> g_launches{0};   // all threads of the process: searches may run on several threads at once
 int* g_status_ptr[64] = {};
 int g_sm_count[64] = {};
 }  // namespace
@@ -58,7 +59,7 @@ void kernel_times_after(cudaStream_t stream) {
 }
 
 void set_last_cuda_error(cudaError_t e) { t_last_error = e; }
-void count_launch() { ++t_launches; }
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int check_launch() {
   cudaError_t e = cudaGetLastError();
@@ -125,8 +126,8 @@ const char* mi8_strerror(int status) {
 int mi8_last_cuda_error(void) { return static_cast<int>(t_last_error); }
 const char* mi8_last_cuda_error_string(void) { return cudaGetErrorString(t_last_error); }
 
-unsigned long long mi8_launch_count(void) { return t_launches; }
-void mi8_launch_count_reset(void) { t_launches = 0; }
+unsigned long long mi8_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+void mi8_launch_count_reset(void) { g_launches.store(0, std::memory_order_relaxed); }
 
 size_t mi8_workspace_bytes(int M, int N, int K) {
   // Upper bound over every plan: only problems with fewer tiles than SMs are split, and each tile

@@ -6,6 +6,7 @@
 // ("transformer-postprocess: dan"), then the tied output layer, log-softmax and n-best selection.
 // mi8d_search adds the beam-search bookkeeping around the step (BeamSearch::search,
 // src/translator/beam_search.cpp:249-538), so a mini-batch is translated by one call.
+#include <algorithm>
 #include <chrono>
 #include <cmath>
 #include <cstring>
@@ -160,6 +161,7 @@ struct mi8d_decoder {
   bool overlap = false;
   // tuning switches (mi8d_set_option)
   int opt_fuse = 1, opt_quant_in_gemm = 0, opt_fused_out_rows = 480, opt_side_stream = 1;
+  int opt_gemm_tile = 0;
   int opt_cluster = 0, opt_fused_ln = 1, opt_cluster_max_rows = 1024, opt_cluster_size = 0, opt_cluster_max_k = 2048;
   // host-side timing of mi8d_search
   double t_issue = 0, t_wait = 0, t_host = 0, n_steps = 0;
@@ -395,6 +397,11 @@ namespace {
 int gemm(mi8d_decoder* d, const int8_t* a, int M, const Aff& w, bool relu, float* c, cudaStream_t s, unsigned* absmax_out = nullptr,
          int force_splits = 0, int force_tile_m = 0) {
   const float* qa = reinterpret_cast<const float*>(a + static_cast<size_t>(M) * w.K);
+  if(force_tile_m == 0 && d->opt_gemm_tile > 0 && M > d->opt_gemm_tile / 2 && w.N <= 8192) {
+    // several searches share the GPU: wider tiles on fewer SMs fetch every weight tile fewer times (throughput over latency)
+    force_tile_m = d->opt_gemm_tile;
+    force_splits = 1;
+  }
   return launch_gemm(a, w.bt, M, w.N, w.K, qa, w.qm, 1.0f, w.bias, relu ? 1 : 0, c, MI8_F32, nullptr, d->ws, d->ws_bytes, s, force_tile_m,
                      force_splits, absmax_out);
 }
@@ -667,6 +674,11 @@ int mi8d_set_option(mi8d_decoder* d, int option, int value) {
       d->opt_cluster_size = value;
       break;
     case MI8D_OPT_CLUSTER_MAX_K: d->opt_cluster_max_k = value; break;
+    case MI8D_OPT_GEMM_TILE_ROWS:
+      if(value != 0 && value != 32 && value != 64 && value != 128 && value != 256)
+        return MI8_ERR_BAD_ARG;
+      d->opt_gemm_tile = value;
+      break;
     case MI8D_OPT_ATTENTION_UNROLL:
       if(value != 8 && value != 16)
         return MI8_ERR_BAD_ARG;
@@ -1057,8 +1069,9 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
       const bool side = d->overlap && d->opt_side_stream;
       cudaStream_t so = side ? d->side : s;
       const int half = sm_count() / 2;
-      const int tile_q = side ? tile_within(R, w.self_q.N, half) : 0;
-      const int tile_kv = side ? tile_within(R, 2 * w.self_k.N, half) : 0;
+      const int wide = R > d->opt_gemm_tile / 2 ? d->opt_gemm_tile : 0;
+      const int tile_q = std::max(side ? tile_within(R, w.self_q.N, half) : 0, wide);
+      const int tile_kv = std::max(side ? tile_within(R, 2 * w.self_k.N, half) : 0, wide);
       if(side) {
         MI8D_CUDA(cudaEventRecord(d->ev_fork, s));
         MI8D_CUDA(cudaStreamWaitEvent(so, d->ev_fork, 0));

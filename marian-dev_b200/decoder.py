@@ -83,8 +83,11 @@ class NativeStepper:
         dev = model.device
         nbytes = int(self.L.mi8d_arena_bytes(ctypes.byref(self.cfg)))
         self.arena = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        # every driver has a workspace of its own (split-K counters, abs-max partials): several drivers of one model may
+        # run side by side on different streams (decode_corpus(workers=...))
+        self.ws = ops.Workspace(dev)
         handle = ctypes.c_void_p()
-        check(self.L.mi8d_create(ctypes.byref(self.cfg), self.arena.data_ptr(), nbytes, model.ws.ptr, model.ws.nbytes,
+        check(self.L.mi8d_create(ctypes.byref(self.cfg), self.arena.data_ptr(), nbytes, self.ws.ptr, self.ws.nbytes,
                                  ctypes.byref(handle)))
         self.h = handle
         if model.scheme == "packed8avx512":
@@ -147,7 +150,7 @@ class NativeStepper:
         return res, int(up.value), int(down.value)
 
     OPTIONS = {"fuse_weights": 1, "quant_in_gemm": 2, "fused_output_max_rows": 3, "side_stream": 4, "attention_unroll": 5, "attention_block_heads": 6,
-               "cluster_affine": 7, "fused_layernorm": 8, "cluster_max_rows": 9, "cluster_size": 10, "cluster_max_k": 11}
+               "cluster_affine": 7, "fused_layernorm": 8, "cluster_max_rows": 9, "cluster_size": 10, "cluster_max_k": 11, "gemm_tile_rows": 12}
 
     def set_option(self, name: str, value: int):
         """mi8d_set_option: tuning switches of the step driver (every setting computes the same bits)."""
@@ -357,11 +360,117 @@ class BeamSearch:
         return results
 
 
+class SearchPool:
+    """Several beam searches of one model side by side on one GPU, each with a step driver and a CUDA stream of its own,
+    fed from one queue of mini-batches - the reference's translator with more than one worker on a device
+    (src/translator/translator.h:100-167: one graph, scorer set and search per worker, the thread pool hands the next
+    mini-batch to whichever worker is free).  A decode step is a chain of ~120 small dependent kernels that leaves most of
+    the GPU idle most of the time; a second chain fills those gaps.  Results do not depend on the number of workers: every
+    mini-batch is decoded on its own."""
+
+    def __init__(self, model: Int8Transformer, workers: int = 2, beam: int = 4, max_length_factor: float = 1.5, normalize: float = 1.0,
+                 max_batch: int = 128, max_src: int = 136, max_steps: int = 208, first: "NativeStepper | None" = None,
+                 shared_gpu_tile_rows: int = 256):
+        self.m = model
+        self.steppers = [first if (i == 0 and first is not None) else NativeStepper(model, max_batch=max_batch, beam=beam, max_src=max_src,
+                                                                                       max_steps=max_steps) for i in range(max(1, workers))]
+        self.searches = [BeamSearch(model, beam, max_length_factor, normalize, native=st) for st in self.steppers]
+        self.streams = [torch.cuda.Stream(device=model.device) for _ in self.steppers]
+        if len(self.steppers) > 1 and shared_gpu_tile_rows:
+            # With the GPU shared, an affine need not spread over every SM to be done soonest: wide tiles on few SMs read each
+            # weight tile fewer times (measured on transformer-big, 4 workers: 187 k -> 218 k tokens/s).  Same values either way.
+            for st in self.steppers:
+                st.set_option("gemm_tile_rows", shared_gpu_tile_rows)
+
+    @property
+    def h2d_bytes(self):
+        return sum(s.h2d_bytes for s in self.searches)
+
+    @property
+    def d2h_bytes(self):
+        return sum(s.d2h_bytes for s in self.searches)
+
+    def reset_counters(self):
+        for s in self.searches:
+            s.h2d_bytes = s.d2h_bytes = 0
+
+    def run(self, items, on_device: bool = False):
+        """items: list of (ids, mask) - host arrays / pinned tensors, or device tensors with on_device=True.  Returns the
+        list of per-mini-batch results in the order of `items`.  The caller's current stream is ordered before the first
+        and after the last kernel of every worker."""
+        nxt = [0]
+
+        def source():
+            i = nxt[0]
+            nxt[0] += 1
+            return (i, items[i][0], items[i][1]) if i < len(items) else None
+        got = self.run_from(source, on_device)
+        return [got[i] for i in range(len(items))]
+
+    def run_from(self, source, on_device: bool = False):
+        """The same with the mini-batches drawn from `source()` -> (key, ids, mask) or None when there are no more (called
+        under a lock, by whichever worker is free).  Returns {key: results}."""
+        import threading
+        dev = self.m.device
+        results = {}
+        errors = []
+        lock = threading.Lock()
+        caller = torch.cuda.current_stream(dev)
+        start = torch.cuda.Event()
+        start.record(caller)
+        done = [torch.cuda.Event() for _ in self.searches]
+
+        def work(w):
+            try:
+                torch.cuda.set_device(dev)
+                with torch.cuda.stream(self.streams[w]):
+                    self.streams[w].wait_event(start)
+                    while not errors:
+                        with lock:
+                            item = source()
+                        if item is None:
+                            break
+                        key, ids, mask = item
+                        results[key] = self.searches[w].search_device(ids, mask) if on_device else self.searches[w].search(ids, mask)
+                    done[w].record(self.streams[w])
+            except Exception as e:      # surfaces in the caller
+                errors.append(e)
+
+        if len(self.searches) == 1:
+            work(0)
+        else:
+            threads = [threading.Thread(target=work, args=(w,)) for w in range(len(self.searches))]
+            for t in threads:
+                t.start()
+            for t in threads:
+                t.join()
+        if errors:
+            raise errors[0]
+        for ev in done:
+            caller.wait_event(ev)
+        return results
+
+
 def decode_corpus(model: Int8Transformer, batches, beam=4, max_length_factor=1.5, normalize=1.0, native=None, native_search=True,
-                  search_cls=None):
-    """Translate all mini-batches on one replica; returns {sentence id: token list} and the token count."""
-    bs = (search_cls or BeamSearch)(model, beam, max_length_factor, normalize, native=native, native_search=native_search)
+                  search_cls=None, workers: int = 1):
+    """Translate all mini-batches on one replica; returns {sentence id: token list} and the token count.
+    workers > 1 (native step driver only): that many searches side by side on the GPU (SearchPool)."""
     out, n_tokens = {}, 0
+    if workers > 1:
+        if native is None or not native_search or search_cls is not None:
+            raise ValueError("workers > 1 needs the native step driver and its C++ search")
+        widest = max(b[1].shape[1] for b in batches)
+        pool = SearchPool(model, workers, beam, max_length_factor, normalize, max_batch=native.max_batch, max_src=native.max_src,
+                          max_steps=native.max_steps, first=native)
+        assert widest <= native.max_src
+        all_res = pool.run([(ids, mask) for _sid, ids, mask in batches])
+        torch.cuda.current_stream(model.device).synchronize()
+        for (sent_ids, _ids, _mask), res in zip(batches, all_res):
+            for sid, (toks, _score) in zip(sent_ids, res):
+                out[int(sid)] = toks
+                n_tokens += len(toks)
+        return out, n_tokens
+    bs = (search_cls or BeamSearch)(model, beam, max_length_factor, normalize, native=native, native_search=native_search)
     for sent_ids, ids, mask in batches:
         res = bs.search(ids, mask)
         for sid, (toks, _score) in zip(sent_ids, res):

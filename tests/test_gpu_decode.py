@@ -135,3 +135,22 @@ def test_big_model_realistic_batch_identical(cuda_device):
     in the benchmark; every sequence identical to the CPU checker's."""
     same, total, got, want, _ = _decode_both("big", 32, 32, 4, seed=3, lo=20, hi=40, native=True)
     assert same == total, f"only {same}/{total} sentences identical"
+
+
+@pytest.mark.parametrize("cfg_name,workers", [("tiny", 2), ("small", 3)])
+def test_searches_side_by_side_equal_one_at_a_time(cuda_device, cfg_name, workers):
+    """decode_corpus(workers=N): N beam searches of the same model on one GPU at once (own step driver, workspace and
+    stream each, mini-batches taken from one queue) return exactly what one search at a time returns."""
+    from marian_dev_b200 import decoder, model, ops
+    cfg = model.CONFIGS[cfg_name]
+    params = model.random_init(cfg, 21)
+    params["decoder_ff_logit_out_b"][0, cfg.eos_id] += 3.0
+    corpus = model.synthetic_corpus(120, cfg.vocab, 22, "uniform", 3, 20)
+    batches = model.make_batches(corpus, 12)
+    gpu = decoder.Int8Transformer(cfg, params, cuda_device)
+    stepper = decoder.NativeStepper(gpu, max_batch=12, beam=4, max_src=24, max_steps=48)
+    one, n1 = decoder.decode_corpus(gpu, batches, beam=4, native=stepper)
+    for _ in range(3):                                            # a few times: the interleaving differs from run to run
+        many, n2 = decoder.decode_corpus(gpu, batches, beam=4, native=stepper, workers=workers)
+        assert n1 == n2 and one == many
+    assert ops.poll_status() == 0
