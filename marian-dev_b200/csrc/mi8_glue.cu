@@ -391,20 +391,50 @@ attention1_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 #pragma unroll
     for(int u = 0; u < U; ++u)
       kk[u] = (active && p0 + u < len) ? __ldg(reinterpret_cast<const float4*>(k + row_offset(p0 + u))) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float d[U];
 #pragma unroll
     for(int u = 0; u < U; ++u) {
-      float d = __fmul_rn(qv.x, kk[u].x);
-      d = __fmaf_rn(qv.y, kk[u].y, d);
-      d = __fmaf_rn(qv.z, kk[u].z, d);
-      d = __fmaf_rn(qv.w, kk[u].w, d);
+      d[u] = __fmul_rn(qv.x, kk[u].x);
+      d[u] = __fmaf_rn(qv.y, kk[u].y, d[u]);
+      d[u] = __fmaf_rn(qv.z, kk[u].z, d[u]);
+      d[u] = __fmaf_rn(qv.w, kk[u].w, d[u]);
+    }
+    // The butterfly of the G threads of a head, for U positions at once: at the level that pairs lanes j and j ^ o the two
+    // lanes split the positions still held between them - each sends the partial sums of the half it gives up and adds
+    // what it receives to the half it keeps - so a level costs half as many shuffles and additions as the one before,
+    // instead of one of each per position.  Every sum is "own + partner's" of the same two operands as in the plain
+    // butterfly, hence the same bits.  Once a lane holds a single position the remaining levels are the plain butterfly.
+    int pos = 0;
 #pragma unroll
-      for(int o = G / 2; o > 0; o >>= 1)
-        d = __fadd_rn(d, __shfl_xor_sync(0xffffffffu, d, o));
-      if(active && j == 0 && p0 + u < len) {
-        d = __fmul_rn(d, scale);
-        if(mask)
-          d = __fadd_rn(d, mask[p0 + u]);
-        srow[p0 + u] = d;
+    for(int lvl = 0; ((G / 2) >> lvl) > 0; ++lvl) {
+      const int o = (G / 2) >> lvl;
+      const int c = (U >> lvl) > 1 ? (U >> lvl) : 1;   // positions a lane holds before this level
+      if(c > 1) {
+        const bool upper = (j & o) != 0;
+#pragma unroll
+        for(int i = 0; i < c / 2; ++i) {
+          const float send = upper ? d[i] : d[i + c / 2];
+          const float keep = upper ? d[i + c / 2] : d[i];
+          d[i] = __fadd_rn(keep, __shfl_xor_sync(0xffffffffu, send, o));
+        }
+        pos += upper ? c / 2 : 0;
+      } else {
+        d[0] = __fadd_rn(d[0], __shfl_xor_sync(0xffffffffu, d[0], o));
+      }
+    }
+    // lanes that differ only in the bits of the plain levels hold the same position: the one with those bits clear writes
+    // (with more positions than lanes a lane ends up holding U / G neighbouring positions)
+    constexpr int kPlainMask = (U >= G) ? 0 : (G / U) - 1;
+    constexpr int kHeld = U > G ? U / G : 1;
+    if(active && (j & kPlainMask) == 0) {
+#pragma unroll
+      for(int i = 0; i < kHeld; ++i) {
+        if(p0 + pos + i < len) {
+          float sc = __fmul_rn(d[i], scale);
+          if(mask)
+            sc = __fadd_rn(sc, mask[p0 + pos + i]);
+          srow[p0 + pos + i] = sc;
+        }
       }
     }
   }
