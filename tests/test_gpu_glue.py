@@ -103,7 +103,7 @@ def test_attention_bit_exact(cuda_device, oracle, mode, rows, batch, length, hea
         assert np.abs(want[r0, sl] - w @ v[idx][:, sl].astype(np.float64)).max() < 1e-4
 
 
-@pytest.mark.parametrize("rows,vocab,k", [(3, 512, 1), (8, 32000, 4), (5, 1000, 8), (2, 300, 3), (7, 5000, 3), (4, 4100, 8), (3, 32000, 1),
+@pytest.mark.parametrize("rows,vocab,k", [(3, 512, 1), (8, 32000, 4), (5, 1000, 8), (2, 300, 3), (7, 5000, 3), (4, 4100, 8), (3, 32000, 1), (3, 1001, 2), (2, 130, 8),
                                            (600, 32000, 4)])
 def test_lse_topk_and_merge_bit_exact(cuda_device, oracle, rows, vocab, k):
     L, check = _lib()
