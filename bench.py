@@ -73,7 +73,7 @@ def workload(args):
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=6)
+    ap.add_argument("--steps", type=int, default=16)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="big", help="big (the benchmark), base, student, tiny (debugging)")
@@ -81,8 +81,9 @@ def parse_args():
     ap.add_argument("--beam", type=int, default=0, help="override the workload's beam size")
     ap.add_argument("--cpu-sentences", type=int, default=16, help="sentences in the CPU-baseline sample")
     ap.add_argument("--affine", default=None, help="M,K,N: time one int8 affine (abs-max + quantise + GEMM with bias and ReLU) instead of the decode")
-    ap.add_argument("--workers", type=int, default=DEFAULT_WORKERS,
-                    help="beam searches side by side on each GPU, each with its own step driver and stream (decoder.SearchPool)")
+    ap.add_argument("--workers", type=int, default=0,
+                    help="beam searches side by side on each GPU, each with its own step driver and stream (decoder.SearchPool); "
+                         "0 = chosen from --steps (4 unless so few mini-batches are timed that another count shares them out better)")
     ap.add_argument("--sweep", action="store_true", help="time the affine shape sweep M x K x N instead of the decode")
     ap.add_argument("--write-digests", default=None, metavar="PATH",
                     help="decode the whole corpus of the big and base workloads and write the per-mini-batch output digests (the "
@@ -291,8 +292,8 @@ def run_ours(args):
 
     world, rank, local_rank, dev, cfg, wl, batches, stepper, search = _setup(args)
     from marian_dev_b200 import decoder as decoder_mod
-    pool = decoder_mod.SearchPool(search.m, max(1, args.workers), beam=wl["beam"], max_length_factor=1.5, normalize=1.0, max_batch=wl["mini_batch"],
-                                  max_src=136, max_steps=208, first=stepper)
+    pool = decoder_mod.SearchPool(search.m, pick_workers(args.workers, args.steps), beam=wl["beam"], max_length_factor=1.5, normalize=1.0,
+                                  max_batch=wl["mini_batch"], max_src=136, max_steps=208, first=stepper)
     for st in pool.steppers:            # (after the pool set its own defaults)
         _apply_options(st, args)
     if args.legacy_sample:
@@ -544,7 +545,19 @@ def run_write_digests(args):
     print(json.dumps({"wrote": args.write_digests, "big_tokens": out["big"]["tokens"], "base_tokens": out["base"]["tokens"]}), flush=True)
 
 
-DEFAULT_WORKERS = 4     # beam searches side by side per GPU (measured on transformer-big: 1 -> 128 k, 2 -> 162 k, 3 -> 201 k, 4 -> 218 k, 5 -> 217 k tokens/s)
+# Beam searches side by side per GPU: measured speed-up over one search on transformer-big (wide GEMM tiles from 3 on).
+WORKER_SPEEDUP = {1: 1.0, 2: 1.27, 3: 1.55, 4: 1.72, 5: 1.70, 6: 1.57}
+
+
+def pick_workers(requested, n_batches):
+    """The requested count, or the one that gets `n_batches` mini-batches done soonest under a simple model (rounds of w
+    concurrent searches, each round w / speed-up(w) long): 4 once there are enough mini-batches to keep four busy."""
+    if requested > 0:
+        return requested
+    if n_batches <= 0:
+        return 4
+    best = min(WORKER_SPEEDUP, key=lambda w: (-(-n_batches // w) * w / WORKER_SPEEDUP[w], abs(w - 4)))
+    return min(best, n_batches)
 
 
 TRACE_KERNELS = {1: "mi8_gemm_kernel", 2: "mi8_gemm_pair_kernel", 3: "quantize_slot_kernel", 4: "quantize_dual_kernel", 5: "add_layernorm_kernel",
@@ -666,8 +679,8 @@ def run_strong(args):
     next_batch = parallel.shared_counter()
     order = batch_order(len(batches))
     from marian_dev_b200 import decoder as decoder_mod
-    pool = decoder_mod.SearchPool(search.m, max(1, args.workers), beam=wl["beam"], max_length_factor=1.5, normalize=1.0, max_batch=wl["mini_batch"],
-                                  max_src=136, max_steps=208, first=stepper)
+    pool = decoder_mod.SearchPool(search.m, pick_workers(args.workers, len(batches)), beam=wl["beam"], max_length_factor=1.5, normalize=1.0,
+                                  max_batch=wl["mini_batch"], max_src=136, max_steps=208, first=stepper)
     for st in pool.steppers:            # (after the pool set its own defaults)
         _apply_options(st, args)
     for i in range(args.warmup):
