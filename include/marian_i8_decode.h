@@ -183,7 +183,10 @@ int mi8d_history_reuse(mi8d_decoder* d, unsigned out[2], int reset);
  *   MI8D_OPT_CLUSTER_MAX_K (default 2048): affines with a longer inner dimension take the two-launch route;
  *   MI8D_OPT_GEMM_TILE_ROWS (0 = the plan's choice, 32, 64, 128, 256): activation rows per tile of the decoder's plain affines.
  *     The plan spreads a small product over as many SMs as it can (lowest latency); when several searches share a GPU
- *     wider tiles on fewer SMs move fewer bytes from L2 for the same product. */
+ *     wider tiles on fewer SMs move fewer bytes from L2 for the same product;
+ *   MI8D_OPT_BLOCKING_WAIT (default 0): how mi8d_search waits for a step's n-best lists.  0: cudaStreamSynchronize (spins on a
+ *     core); 1: a blocking-sync event (the thread sleeps; woken tens of microseconds late: 5 % fewer tokens/s on one GPU);
+ *     2: polls an event and yields the core between polls (for several searches per GPU and several GPUs per host). */
 enum mi8d_option {
   MI8D_OPT_FUSE_WEIGHTS = 1,
   MI8D_OPT_QUANT_IN_GEMM = 2,
@@ -196,7 +199,8 @@ enum mi8d_option {
   MI8D_OPT_CLUSTER_MAX_ROWS = 9,
   MI8D_OPT_CLUSTER_SIZE = 10,
   MI8D_OPT_CLUSTER_MAX_K = 11,
-  MI8D_OPT_GEMM_TILE_ROWS = 12
+  MI8D_OPT_GEMM_TILE_ROWS = 12,
+  MI8D_OPT_BLOCKING_WAIT = 13
 };
 int mi8d_set_option(mi8d_decoder* d, int option, int value);   /* d may be NULL for the process-wide switches */
 

@@ -6,6 +6,7 @@
 // ("transformer-postprocess: dan"), then the tied output layer, log-softmax and n-best selection.
 // mi8d_search adds the beam-search bookkeeping around the step (BeamSearch::search,
 // src/translator/beam_search.cpp:249-538), so a mini-batch is translated by one call.
+#include <thread>
 #include <algorithm>
 #include <chrono>
 #include <cmath>
@@ -158,6 +159,8 @@ struct mi8d_decoder {
   // stream with events, beside the query projection and the newest slab's keys/values.
   cudaStream_t side = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  cudaEvent_t ev_step = nullptr;   // blocking-sync event: the host thread sleeps instead of spinning while a step runs (opt_blocking_wait)
+  int opt_blocking_wait = 0;
   bool overlap = false;
   // tuning switches (mi8d_set_option)
   int opt_fuse = 1, opt_quant_in_gemm = 0, opt_fused_out_rows = 480, opt_side_stream = 1;
@@ -588,6 +591,10 @@ int mi8d_create(const mi8d_config* cfg, void* arena, size_t arena_bytes, void* w
     if(!ok)
       cudaGetLastError();
   }
+  if(cudaEventCreateWithFlags(&d->ev_step, cudaEventDisableTiming | cudaEventBlockingSync) != cudaSuccess) {
+    d->ev_step = nullptr;
+    cudaGetLastError();
+  }
   *out = d;
   return MI8_OK;
 }
@@ -595,6 +602,8 @@ int mi8d_create(const mi8d_config* cfg, void* arena, size_t arena_bytes, void* w
 void mi8d_destroy(mi8d_decoder* d) {
   if(d == nullptr)
     return;
+  if(d->ev_step != nullptr)
+    cudaEventDestroy(d->ev_step);
   if(d->side != nullptr) {
     cudaStreamSynchronize(d->side);
     cudaStreamDestroy(d->side);
@@ -674,6 +683,11 @@ int mi8d_set_option(mi8d_decoder* d, int option, int value) {
       d->opt_cluster_size = value;
       break;
     case MI8D_OPT_CLUSTER_MAX_K: d->opt_cluster_max_k = value; break;
+    case MI8D_OPT_BLOCKING_WAIT:
+      if(value < 0 || value > 2)
+        return MI8_ERR_BAD_ARG;
+      d->opt_blocking_wait = value;
+      break;
     case MI8D_OPT_GEMM_TILE_ROWS:
       if(value != 0 && value != 32 && value != 64 && value != 128 && value != 256)
         return MI8_ERR_BAD_ARG;
@@ -1244,7 +1258,21 @@ int mi8d_search(mi8d_decoder* d, const int* ids, const float* log_mask, int batc
       return rc;
     MI8D_CUDA(cudaMemcpyAsync(d->h_out, d->s_out, static_cast<size_t>(3 * cells) * sizeof(int), cudaMemcpyDeviceToHost, s));
     const clk::time_point t_b = clk::now();
-    MI8D_CUDA(cudaStreamSynchronize(s));
+    if(d->opt_blocking_wait == 2 && d->ev_step != nullptr) {
+      // several searches (and ranks) share the host's cores: poll, and hand the core to another thread between polls - as
+      // quick as spinning while cores are free, fair when there are more waiting threads than cores
+      MI8D_CUDA(cudaEventRecord(d->ev_step, s));
+      cudaError_t qe;
+      while((qe = cudaEventQuery(d->ev_step)) == cudaErrorNotReady)
+        std::this_thread::yield();
+      MI8D_CUDA(qe);
+    } else if(d->opt_blocking_wait && d->ev_step != nullptr) {
+      // sleep until the step's results have arrived (an interrupt wakes the thread: tens of microseconds later than polling)
+      MI8D_CUDA(cudaEventRecord(d->ev_step, s));
+      MI8D_CUDA(cudaEventSynchronize(d->ev_step));
+    } else {
+      MI8D_CUDA(cudaStreamSynchronize(s));
+    }
     const clk::time_point t_c = clk::now();
     d->t_host += secs(mark, t_a);
     d->t_issue += secs(t_a, t_b);

@@ -150,7 +150,7 @@ class NativeStepper:
         return res, int(up.value), int(down.value)
 
     OPTIONS = {"fuse_weights": 1, "quant_in_gemm": 2, "fused_output_max_rows": 3, "side_stream": 4, "attention_unroll": 5, "attention_block_heads": 6,
-               "cluster_affine": 7, "fused_layernorm": 8, "cluster_max_rows": 9, "cluster_size": 10, "cluster_max_k": 11, "gemm_tile_rows": 12}
+               "cluster_affine": 7, "fused_layernorm": 8, "cluster_max_rows": 9, "cluster_size": 10, "cluster_max_k": 11, "gemm_tile_rows": 12, "blocking_wait": 13}
 
     def set_option(self, name: str, value: int):
         """mi8d_set_option: tuning switches of the step driver (every setting computes the same bits)."""
@@ -381,6 +381,7 @@ class SearchPool:
             # weight tile fewer times (measured on transformer-big, 4 workers: 187 k -> 218 k tokens/s).  Same values either way.
             for st in self.steppers:
                 st.set_option("gemm_tile_rows", shared_gpu_tile_rows)
+                st.set_option("blocking_wait", 2)     # the workers' host threads poll and yield instead of spinning on a core each
 
     @property
     def h2d_bytes(self):
