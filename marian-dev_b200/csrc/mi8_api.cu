@@ -107,7 +107,7 @@ using namespace mi8;
 
 extern "C" {
 
-int mi8_version(void) { return 10100; }
+int mi8_version(void) { return 10200; }
 
 const char* mi8_strerror(int status) {
   switch(status) {

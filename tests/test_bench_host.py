@@ -40,3 +40,13 @@ def test_digest_depends_on_ids_lengths_and_tokens():
     assert a != bench.tokens_digest([3, 1], [[5, 6, 0], [7, 1]])
     assert a != bench.tokens_digest([3, 2], [[5, 6, 0], [7, 0]])
     assert a != bench.tokens_digest([3, 1], [[5, 6], [0, 7, 0]])
+
+
+def test_worker_count_follows_the_number_of_timed_mini_batches():
+    """bench.py runs several searches per GPU; the count is the caller's, or chosen so that few timed mini-batches are shared
+    out evenly (never more searches than mini-batches), and four once there are enough to keep four busy."""
+    import bench
+    assert bench.pick_workers(3, 100) == 3 and bench.pick_workers(1, 2) == 1          # an explicit request stands
+    assert [bench.pick_workers(0, k) for k in (1, 2, 3, 4)] == [1, 2, 3, 4]
+    assert all(bench.pick_workers(0, k) == 4 for k in (8, 12, 16, 32, 64))
+    assert all(1 <= bench.pick_workers(0, k) <= min(k, 6) for k in range(1, 40))

@@ -187,3 +187,14 @@ def test_gather_refuses_to_truncate():
     assert m.tolist() == [[2, 0, -1, -1], [4, 2, 9, 8], [-1, -1, -1, -1]]
     with pytest.raises(ValueError, match="3 tokens"):
         parallel.pack_outputs({1: [1, 2, 3]}, rows=1, max_len=2)
+
+
+def test_output_matrices_round_trip_without_a_process_group():
+    """gather_output_matrices (the exchange, what the benchmark times) and merge_output_matrices (the conversion to Python
+    lists, done afterwards) together equal gather_outputs; empty hypotheses and empty ranks survive."""
+    from marian_dev_b200 import parallel
+    local = {7: [5, 6, 0], 2: [], 11: [9] * 6}
+    mats = parallel.gather_output_matrices(local, max_len=6)
+    assert len(mats) == 1 and mats[0].shape == (3, 8) and mats[0].dtype.name == "int32"
+    assert parallel.merge_output_matrices(mats) == local
+    assert parallel.merge_output_matrices(parallel.gather_output_matrices({}, max_len=4)) == {}
