@@ -506,6 +506,9 @@ def run_ours(args):
                                  "warm-up on other mini-batches",
                        "tokens_counted": "best hypothesis per sentence, EOS included", "parallelism": f"replicas x{world}",
                        "searches_side_by_side_per_gpu": len(pool.searches),
+                       "gemm_tiles": ("256 activation rows per tile (several searches share the GPU: fewer fetches of every weight tile)"
+                                      if len(pool.searches) > 1 and not any(o.startswith("gemm_tile_rows") for o in args.option)
+                                      else "the plan's latency tiles unless an option says otherwise"),
                        "options": args.option, "legacy_sample": bool(args.legacy_sample),
                        "l2": "not flushed: one decode step streams ~0.2 GB of int8 weights plus fp32 logits and history, more than the 126 MB L2"},
             "e2e": {"value": round(tokens2 / (ms2 / 1e3), 1), "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
