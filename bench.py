@@ -100,7 +100,7 @@ def parse_args():
                     help="strong scaling: the whole fixed corpus, mini-batches taken from a shared counter by whichever rank is free")
     ap.add_argument("--glue", default=None, metavar="KERNEL",
                     help="time one glue kernel at the benchmark's decode shapes (attention1_self, attention1_cross, quantize_slot, "
-                         "add_layernorm, lse_topk), the form the ncu captures use")
+                         "add_layernorm, lse_topk, cluster_affine, cluster_affine_layernorm), the form the ncu captures use")
     ap.add_argument("--tile-sweep", default=None, metavar="M,K,N",
                     help="time the GEMM alone (operands already quantised) for every tile width and split-K factor the kernel offers")
     ap.add_argument("--packed8", action="store_true",
@@ -822,6 +822,29 @@ def run_glue(args):
         def run(i):
             check(L.mi8g_lse_topk(lg[i % sets].data_ptr(), R, V, 4, None, cs.data_ptr(), cw.data_ptr(), st))
         shape = f"{R} rows x {V} words, k = 4"
+    elif kind in ("cluster_affine", "cluster_affine_layernorm"):
+        # the optional cluster GEMM (mi8g_affine_slot*): Wo of an attention block, 512 x 1024 x 1024, from fp32 + abs-max slot
+        from marian_dev_b200 import ops
+        sets = 24
+        x = [torch.randn(R, d, device=dev) for _ in range(sets)]
+        slot.view(torch.float32)[0] = 6.0                      # max|x| of a standard normal tensor of this size, roughly; any bound works
+        w = [ops.prepareB(torch.randn(d, d, device=dev) * 0.03) for _ in range(sets)]
+        bias = torch.randn(d, device=dev) * 0.01
+        res = [torch.randn(R, d, device=dev) for _ in range(sets)]
+        g, b = torch.ones(d, device=dev), torch.zeros(d, device=dev)
+        out = torch.empty(R, d, device=dev)
+        by = R * d * 4 + d * d + 4 * d + R * d * 4 + (R * d * 4 if kind.endswith("layernorm") else 0)
+
+        def run(i):
+            j = i % sets
+            if kind.endswith("layernorm"):
+                check(L.mi8g_affine_slot_add_layernorm(x[j].data_ptr(), slot.data_ptr(), w[j].data.data_ptr(), w[j].quant_mult.data_ptr(), R, d, d, 1.0,
+                                                       bias.data_ptr(), res[j].data_ptr(), g.data_ptr(), b.data_ptr(), 1e-6, out.data_ptr(), None,
+                                                       slot[8:].data_ptr(), None, st))
+            else:
+                check(L.mi8g_affine_slot(x[j].data_ptr(), slot.data_ptr(), w[j].data.data_ptr(), w[j].quant_mult.data_ptr(), R, d, d, 1.0,
+                                         bias.data_ptr(), 0, out.data_ptr(), slot[8:].data_ptr(), 0, 0, st))
+        shape = f"{R} x {d} x {d}, fp32 activation + abs-max slot" + (" , + residual + LayerNorm" if kind.endswith("layernorm") else "")
     else:
         raise SystemExit(f"unknown kernel {kind}")
     iters = 200
