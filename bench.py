@@ -343,13 +343,17 @@ def run_ours(args):
     leg1 = [batches[b] for b in mine]
     resident = [(sid, torch.from_numpy(ids.astype(np.int64)).to(dev), torch.from_numpy(mask).to(dev)) for sid, ids, mask in leg1]
     sampler = ClockSampler(local_rank)
+    sampler.start()       # nvidia-smi takes a few hundred ms to come up (it opens the driver): it does so beside one more warm-up decode
+    settle = batches[(warm or mine)[0]]
+    pool.searches[0].search(settle[1], settle[2])
+    torch.cuda.synchronize()
+    time.sleep(0.25)
     launches_before = ops.launch_count()          # warm-up launches (lets a profiler skip them)
     ops.reset_launch_count()
     for st in pool.steppers:
         st.search_stats(reset=True)
     tokens = 0
     barrier()
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     collected = {}
@@ -708,7 +712,12 @@ def run_strong(args):
         parallel.gather_output_matrices({i: [0] * max_len for i in range(-(-wl["sentences"] // world))}, max_len=max_len, device=dev)
         dist.barrier()
     sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler.start()       # (comes up beside one more warm-up decode, see run_ours)
+    pool.searches[0].search(batches[order[0]][1], batches[order[0]][2])
+    torch.cuda.synchronize()
+    time.sleep(0.25)
+    if world > 1:
+        dist.barrier()
     e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
     e0.record()
     tokens, mine, bad = 0, [], 0

@@ -181,7 +181,8 @@ int mi8d_history_reuse(mi8d_decoder* d, unsigned out[2], int reset);
  *   MI8D_OPT_CLUSTER_MAX_ROWS (default 1024): activations with more rows than this take the two-launch route;
  *   MI8D_OPT_CLUSTER_SIZE (0 = chosen, 1, 2, 4, 8): CTAs per cluster of the plain cluster affine;
  *   MI8D_OPT_CLUSTER_MAX_K (default 2048): affines with a longer inner dimension take the two-launch route;
- *   MI8D_OPT_GEMM_TILE_ROWS (0 = the plan's choice, 32, 64, 128, 256): activation rows per tile of the decoder's plain affines.
+ *   MI8D_OPT_GEMM_TILE_ROWS (0 = the plan's choice, 32, 64, 128, 256, 512 = the two-CTA kernel): upper bound of the activation rows per
+ *     tile of the decoder's plain affines (the widest tile that the live rows still fill more than half of is used).
  *     The plan spreads a small product over as many SMs as it can (lowest latency); when several searches share a GPU
  *     wider tiles on fewer SMs move fewer bytes from L2 for the same product;
  *   MI8D_OPT_BLOCKING_WAIT (default 0): how mi8d_search waits for a step's n-best lists.  0: cudaStreamSynchronize (spins on a

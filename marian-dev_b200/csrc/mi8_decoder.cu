@@ -396,13 +396,26 @@ namespace {
       return rc_;           \
   } while(0)
 
+// MI8D_OPT_GEMM_TILE_ROWS: the widest tile up to the option's value that M still fills more than half of (512 = the
+// CTA-pair kernel, for more than 256 rows); 0 = leave the choice to the plan.
+int wide_tile(const mi8d_decoder* d, int M) {
+  int t = d->opt_gemm_tile;
+  if(t <= 0 || M <= 16)
+    return 0;
+  if(t == 512 && M <= 256)
+    t = 256;
+  while(t > 32 && M <= t / 2)
+    t >>= 1;
+  return t;
+}
+
 // aq (already quantised, multiplier behind the data) x weight -> c
 int gemm(mi8d_decoder* d, const int8_t* a, int M, const Aff& w, bool relu, float* c, cudaStream_t s, unsigned* absmax_out = nullptr,
          int force_splits = 0, int force_tile_m = 0) {
   const float* qa = reinterpret_cast<const float*>(a + static_cast<size_t>(M) * w.K);
-  if(force_tile_m == 0 && d->opt_gemm_tile > 0 && M > d->opt_gemm_tile / 2 && w.N <= 8192) {
+  if(force_tile_m == 0 && w.N <= 8192 && wide_tile(d, M) != 0) {
     // several searches share the GPU: wider tiles on fewer SMs fetch every weight tile fewer times (throughput over latency)
-    force_tile_m = d->opt_gemm_tile;
+    force_tile_m = wide_tile(d, M);
     force_splits = 1;
   }
   return launch_gemm(a, w.bt, M, w.N, w.K, qa, w.qm, 1.0f, w.bias, relu ? 1 : 0, c, MI8_F32, nullptr, d->ws, d->ws_bytes, s, force_tile_m,
@@ -689,7 +702,7 @@ int mi8d_set_option(mi8d_decoder* d, int option, int value) {
       d->opt_blocking_wait = value;
       break;
     case MI8D_OPT_GEMM_TILE_ROWS:
-      if(value != 0 && value != 32 && value != 64 && value != 128 && value != 256)
+      if(value != 0 && value != 32 && value != 64 && value != 128 && value != 256 && value != 512)
         return MI8_ERR_BAD_ARG;
       d->opt_gemm_tile = value;
       break;
@@ -1083,7 +1096,7 @@ int mi8d_step(mi8d_decoder* d, const int* hyp_idx, const int* prev_words, const 
       const bool side = d->overlap && d->opt_side_stream;
       cudaStream_t so = side ? d->side : s;
       const int half = sm_count() / 2;
-      const int wide = R > d->opt_gemm_tile / 2 ? d->opt_gemm_tile : 0;
+      const int wide = wide_tile(d, R);
       const int tile_q = std::max(side ? tile_within(R, w.self_q.N, half) : 0, wide);
       const int tile_kv = std::max(side ? tile_within(R, 2 * w.self_k.N, half) : 0, wide);
       if(side) {

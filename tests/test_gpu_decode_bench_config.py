@@ -72,7 +72,8 @@ def test_options_do_not_change_the_output(cuda_device):
         settings = [{}, {"fuse_weights": 0}, {"quant_in_gemm": 1}, {"fused_output_max_rows": 0}, {"fused_output_max_rows": 4096},
                     {"side_stream": 0}, {"attention_unroll": 16}, {"attention_block_heads": 2}, {"attention_block_heads": 0},
                     {"cluster_affine": 1}, {"cluster_affine": 1, "fused_layernorm": 0}, {"cluster_affine": 1, "cluster_size": 2},
-                    {"cluster_affine": 1, "cluster_max_rows": 8}, {"cluster_affine": 1, "cluster_max_k": 256}]
+                    {"cluster_affine": 1, "cluster_max_rows": 8}, {"cluster_affine": 1, "cluster_max_k": 256},
+                    {"gemm_tile_rows": 64}, {"gemm_tile_rows": 256}, {"gemm_tile_rows": 512}, {"blocking_wait": 1}, {"blocking_wait": 2}]
         for opts in settings:
             stepper = decoder.NativeStepper(gpu, max_batch=20, beam=beam, max_src=24, max_steps=48)
             for k, v in opts.items():
