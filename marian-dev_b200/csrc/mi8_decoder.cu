@@ -400,7 +400,7 @@ namespace {
 // CTA-pair kernel, for more than 256 rows); 0 = leave the choice to the plan.
 int wide_tile(const mi8d_decoder* d, int M) {
   int t = d->opt_gemm_tile;
-  if(t <= 0 || M <= 16)
+  if(t <= 0 || M <= 16 || M > 1024)   // (encoder-sized products already fill the GPU: the plan's two-CTA kernel is the fastest there)
     return 0;
   if(t == 512 && M <= 256)
     t = 256;
